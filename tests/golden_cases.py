@@ -1,0 +1,110 @@
+"""Shared driver for the golden fixtures: loads tests/golden/meta_ops.{json,npz} and runs one case
+against a backend (a namespace of functions over numpy arrays with the oracle's names)."""
+import json
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_manifest = json.load(open(os.path.join(HERE, "golden", "meta_ops.json")))
+CASES = _manifest["cases"]
+_npz = None
+
+
+def arrays():
+    global _npz
+    if _npz is None:
+        _npz = np.load(os.path.join(HERE, "golden", "meta_ops.npz"))
+    return _npz
+
+
+def case_ids():
+    return [c["name"] for c in CASES]
+
+
+EXACT_OPS = {"reindex", "reindex_var", "broadcast", "broadcast_var", "ternary"}
+
+
+def run_case(c, be):
+    """Returns (got, want, exact) for case `c` on backend `be`."""
+    A = arrays()
+    ins = [A[k] for k in c["inputs"]]
+    ex = [A[k] for k in c["extras"]]
+    want = A[c["out"]]
+    a = c["args"]
+    op = c["op"]
+    if op == "reindex":
+        if a.get("bf16_bits"):
+            got = be.reindex_bf16_bits(ins[0], a["shape"], a["indexes"], a["overflow_value"])
+        else:
+            got = be.reindex(ins[0], a["shape"], a["indexes"], a["overflow_value"],
+                             a["overflow_conditions"], ex)
+    elif op == "reindex_var":
+        got = be.reindex_var(ins[0], ex, a["overflow_value"], a["overflow_conditions"])
+    elif op == "reindex_reduce":
+        got = be.reindex_reduce(ins[0], a["op"], a["shape"], a["indexes"], a["overflow_conditions"], ex)
+    elif op == "broadcast":
+        got = be.broadcast(ins[0], a["shape"], a["dims"])
+    elif op == "broadcast_var":
+        got = be.broadcast_var(ins[0], ins[1], a["dims"])
+    elif op == "reduce":
+        d = a["dims"]
+        got = be.reduce(ins[0], a["op"], tuple(d) if isinstance(d, list) else d, a["keepdims"])
+    elif op == "binary":
+        got = be.binary(ins[0], ins[1], a["op"])
+    elif op == "unary":
+        got = be.unary(ins[0], a["op"])
+    elif op == "ternary":
+        got = be.ternary(*ins)
+    elif op == "conv":
+        got = be.conv2d(ins[0], ins[1], a["stride"], a["padding"], a["dilation"],
+                        ins[2] if a["bias"] else None)
+    elif op == "matmul":
+        got = be.matmul(ins[0], ins[1])
+    elif op == "matmul_transpose":
+        got = be.matmul_transpose(ins[0], ins[1])
+    elif op in ("softmax", "log_softmax"):
+        got = be.softmax(ins[0], a["dim"], op == "log_softmax")
+    elif op == "layer_norm":
+        got = be.layer_norm(ins[0], a["normalized_shape"], ins[1] if a["affine"] else None,
+                            ins[2] if a["affine"] else None, a["eps"])
+    elif op in ("batch_norm", "batch_norm_relu"):
+        got = be.batch_norm_train(ins[0], ins[1], ins[2], a["eps"], op == "batch_norm_relu")
+    elif op == "conv_bn_relu":
+        y = be.conv2d(ins[0], ins[1], a["stride"], a["padding"], a["dilation"], None)
+        got = be.batch_norm_train(y, ins[2], ins[3], a["eps"], True)
+    elif op == "maxpool2x2":
+        got = be.maxpool2x2(ins[0])
+    elif op == "maxpool2x2_bwd":
+        got = be.maxpool2x2_bwd(ins[0], ins[1])
+    elif op == "grad_reindex":
+        # reindex grad = reindex_reduce(add) of the upstream gradient (reindex_op.cc:76-80)
+        got = be.reindex_reduce(ins[1], "add", list(ins[0].shape), a["indexes"], [], [])
+    elif op == "grad_reindex_reduce_add":
+        # reindex_reduce(add) grad = reindex of the upstream gradient (reindex_reduce_op.cc:48-49)
+        got = be.reindex(ins[1], list(ins[0].shape), a["indexes"], 0, [], [])
+    else:
+        raise KeyError(op)
+    exact = op in EXACT_OPS or (want.dtype.kind in "iub" and op != "unary")
+    return np.asarray(got), want, exact
+
+
+def check(got, want, exact, rtol=1e-5):
+    """Bit-exact for gathers and integer work; for floating point
+    |got-want| <= rtol*|want| + rtol*max|want| (the reference's own -Ofast sums are order-unstable)."""
+    assert got.dtype == want.dtype, (got.dtype, want.dtype)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    if got.size == 0:
+        return
+    if exact:
+        assert np.array_equal(got, want, equal_nan=want.dtype.kind == "f"), \
+            f"mismatch at {np.argwhere(got != want)[:5].tolist()}"
+    else:
+        g, w = got.astype(np.float64), want.astype(np.float64)
+        fin = np.isfinite(w)
+        assert np.array_equal(fin, np.isfinite(g))
+        assert np.array_equal(g[~fin], w[~fin], equal_nan=True)
+        scale = np.max(np.abs(w[fin])) if fin.any() else 0.0
+        err = np.abs(g[fin] - w[fin])
+        tol = rtol * np.abs(w[fin]) + rtol * scale
+        assert (err <= tol).all(), f"max err {err.max():.3e} (scale {scale:.3e})"
