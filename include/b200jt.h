@@ -1,0 +1,155 @@
+/*
+ * b200jt.h -- C ABI of the B200 (sm_100a) kernels behind Jittor's meta-operator path.
+ *
+ * Conventions (all entry points):
+ *   - plain C types only; tensors are described by b200jt_tensor (row-major, contiguous, <= 10 dims,
+ *     like the reference's NanoVector shapes, python/jittor/src/misc/nano_vector.h:42-75);
+ *   - the caller owns every buffer (inputs, outputs, workspace): nothing is allocated inside, which is
+ *     the reference's rule too (the executor allocates all outputs before an op runs,
+ *     python/jittor/src/executor.cc:575-577); the one exception is marked below;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns;
+ *   - return value: 0 on success, <0 for an argument error, >0 for a CUDA error code;
+ *     b200jt_last_error() gives the message of the calling thread's last failure;
+ *   - device pointers must be valid on the current CUDA device.
+ *
+ * Paths in the comments are relative to the reference project root.
+ */
+#ifndef B200JT_H_
+#define B200JT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200JT_MAX_DIMS 10
+#define B200JT_MAX_EXTRAS 10
+
+/* dtype codes (the reference's dtype names, python/jittor/src/misc/nano_string.h) */
+enum b200jt_dtype {
+    B200JT_BOOL = 0, B200JT_INT8 = 1, B200JT_INT16 = 2, B200JT_INT32 = 3, B200JT_INT64 = 4,
+    B200JT_UINT8 = 5, B200JT_FLOAT16 = 6, B200JT_BFLOAT16 = 7, B200JT_FLOAT32 = 8, B200JT_FLOAT64 = 9
+};
+
+typedef struct b200jt_tensor {
+    void*   ptr;                       /* device pointer (may be NULL iff the tensor has 0 elements) */
+    int32_t dtype;                     /* enum b200jt_dtype */
+    int32_t ndim;                      /* 1..B200JT_MAX_DIMS */
+    int64_t shape[B200JT_MAX_DIMS];
+} b200jt_tensor;
+
+const char* b200jt_last_error(void);
+int         b200jt_version(void);
+
+/* Classifies index strings: returns 1 and fills coef[d*B200JT_MAX_DIMS + j], c0[d] if every index d is
+ * c0[d] + sum_j coef[d][j]*i_j (no @e loads), 0 if not affine, <0 on a syntax error. This is what the
+ * reference's tuners recover with expr::match on the same strings (python/jittor/src/opt/tuner/conv_tuner.cc:313-338). */
+int b200jt_index_affine(const int64_t* loop_shape, int ndim_loop, const int64_t* x_shape, int ndim_x,
+                        const char* const* indexes, int n_indexes, int64_t* coef, int64_t* c0);
+
+/* ---- meta-operators --------------------------------------------------------------------------- */
+
+/* y[i] = overflow(i) ? overflow_value : x[index_0(i), ..., index_m(i)].
+ * Replaces ReindexOp(Var* x, NanoVector shape, vector<string>&& indexes, float64 overflow_value,
+ *                    vector<string>&& overflow_conditions, vector<Var*>&& extras)
+ * python/jittor/src/ops/reindex_op.h:91 and its jit_run, python/jittor/src/ops/reindex_op.cc:111-139.
+ * `indexes` are C integer expressions over i0..in, shape symbols and @eK(...) loads of extras. */
+int b200jt_reindex(const b200jt_tensor* x, const b200jt_tensor* y,
+                   const char* const* indexes, int n_indexes, double overflow_value,
+                   const char* const* overflow_conditions, int n_conditions,
+                   const b200jt_tensor* extras, int n_extras, void* stream);
+
+/* x[:] = init(op); for every i of y: if !overflow(i): x[index(i)] = op(x[index(i)], y[i]).
+ * Replaces ReindexReduceOp(Var* y, NanoString op, NanoVector shape, vector<string>&& indexes,
+ *                          vector<string>&& overflow_conditions, vector<Var*>&& extras)
+ * python/jittor/src/ops/reindex_reduce_op.h:86, jit_run python/jittor/src/ops/reindex_reduce_op.cc:93-131.
+ * op: add multiply maximum minimum bitwise_and bitwise_or bitwise_xor logical_and logical_or logical_xor void.
+ * `workspace` must hold b200jt_reindex_reduce_workspace(...) bytes (may be 0). */
+size_t b200jt_reindex_reduce_workspace(const b200jt_tensor* y, const b200jt_tensor* x, const char* op,
+                                       const char* const* indexes, int n_indexes,
+                                       const char* const* overflow_conditions, int n_conditions,
+                                       const b200jt_tensor* extras, int n_extras);
+int b200jt_reindex_reduce(const b200jt_tensor* y, const b200jt_tensor* x, const char* op,
+                          const char* const* indexes, int n_indexes,
+                          const char* const* overflow_conditions, int n_conditions,
+                          const b200jt_tensor* extras, int n_extras,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* z[i] = x[i with the axes of bcast_mask zeroed]; x is passed with z's rank (size-1 axes where broadcast).
+ * Replaces BroadcastToOp(Var* x, NanoVector shape, uint dims_mask, uint keepdims_mask)
+ * python/jittor/src/ops/broadcast_to_op.h:90, jit_run python/jittor/src/ops/broadcast_to_op.cc:177-194. */
+int b200jt_broadcast_to(const b200jt_tensor* x, const b200jt_tensor* z, uint32_t bcast_mask, void* stream);
+
+/* y = reduce_op over the axes of reduce_mask (y passed with x's rank, size-1 on reduced axes).
+ * Replaces ReduceOp(Var* x, NanoString op, uint dims_mask, uint keepdims_mask)
+ * python/jittor/src/ops/reduce_op.h:19, jit_run python/jittor/src/ops/reduce_op.cc:374-399.
+ * op: add mean multiply maximum minimum bitwise_and/or/xor logical_and/or/xor. */
+size_t b200jt_reduce_workspace(const b200jt_tensor* x, const b200jt_tensor* y, const char* op, uint32_t reduce_mask);
+int b200jt_reduce(const b200jt_tensor* x, const b200jt_tensor* y, const char* op, uint32_t reduce_mask,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- element-wise ops fused around them ------------------------------------------------------- */
+
+/* z = op(x, y); x and y may have size-1 axes where z does not (the broadcast_to the reference inserts,
+ * python/jittor/src/ops/binary_op.cc:435-441, fused into the same kernel). All three have z's rank.
+ * Replaces BinaryOp(Var* x, Var* y, NanoString op), python/jittor/src/ops/binary_op.h:14, jit_run
+ * python/jittor/src/ops/binary_op.cc:563-570; scalar semantics python/jittor/src/type/common_op_type.cc:82-152. */
+int b200jt_binary(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* z, const char* op, void* stream);
+
+/* y = op(x); a dtype name as op is a cast. Replaces UnaryOp(Var* x, NanoString op), python/jittor/src/ops/unary_op.h:16. */
+int b200jt_unary(const b200jt_tensor* x, const b200jt_tensor* y, const char* op, void* stream);
+
+/* z = cond ? x : y. Replaces TernaryOp(Var* cond, Var* x, Var* y), python/jittor/src/ops/ternary_op.h:14. */
+int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200jt_tensor* y,
+                   const b200jt_tensor* z, void* stream);
+
+/* ---- fused chains (what op_compiler/FusedOp + the tuners produce for the nn callers) ----------- */
+
+/* Row softmax / log-softmax over the last axis of x[rows, cols], one read and one write.
+ * Replaces the chain of python/jittor/nn.py:527-535 and the inline kernel python/jittor/other/code_softmax.py:42-98.
+ * x, y: float32 or bfloat16 (fp32 math). */
+int b200jt_softmax(const b200jt_tensor* x, const b200jt_tensor* y, int log, void* stream);
+
+/* Row LayerNorm over the last axis: mean, E[x^2], var = max(E[x^2]-E[x]^2, 0), y = x*w + b with
+ * w = gamma/sqrt(var+eps), b = beta - mean*w. gamma/beta may be NULL (1 and 0).
+ * Replaces the chain of python/jittor/nn.py:778-787. x, y: float32 or bfloat16; gamma, beta: float32 [cols]. */
+int b200jt_layer_norm(const b200jt_tensor* x, const b200jt_tensor* gamma, const b200jt_tensor* beta,
+                      const b200jt_tensor* y, double eps, void* stream);
+
+/* c = op_a(a) . op_b(b), fp32 accumulation. Replaces the relay
+ * CublasMatmulOp(Var* a, Var* b, bool trans_a, bool trans_b), python/jittor/extern/cuda/cublas/ops/cublas_matmul_op.h:18,
+ * chosen by MatmulTuner for reduce.add(multiply(broadcast_to(a), broadcast_to(b))), python/jittor/src/opt/tuner/matmul_tuner.cc:21-102.
+ * a, b, c: float32 or bfloat16, same dtype. */
+size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c, int trans_a, int trans_b);
+int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
+                  int trans_a, int trans_b, void* workspace, size_t workspace_bytes, void* stream);
+
+/* y = conv2d(x, w), NCHW ("abcd") x, OIHW w, fp32 accumulation. Replaces the relay
+ * CudnnConvOp(Var* x, Var* w, int strideh, int stridew, int paddingh, int paddingw, int dilationh, int dilationw,
+ *             int groups, string xformat, string wformat, string yformat),
+ * python/jittor/extern/cuda/cudnn/ops/cudnn_conv_op.h:17, chosen by ConvTuner for
+ * reduce.add(multiply(reindex(x), broadcast_to(w))), python/jittor/src/opt/tuner/conv_tuner.cc:218-411.
+ * If stats != NULL (float32 [2*Cout], zeroed by the callee) it also receives per-channel sum(y) and sum(y*y):
+ * the reduce of python/jittor/nn.py:674-675 fused into the conv epilogue. */
+size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                               int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups);
+int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                  int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
+                  float* stats, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Per-channel sum(x) and sum(x*x) of x[N,C,H,W] into stats[2*C] (float32): the two reduce.mean of
+ * BatchNorm.execute, python/jittor/nn.py:674-675, in one pass, unnormalised so that ranks can be
+ * summed by an all-reduce (python/jittor/nn.py:676-678). */
+int b200jt_bn_stats(const b200jt_tensor* x, float* stats, void* stream);
+
+/* y = [relu](x*w + b), w = gamma/sqrt(var+eps), b = beta - mean*w with mean = stats[c]/count,
+ * var = max(stats[C+c]/count - mean^2, 0): python/jittor/nn.py:680-683 (+ nn.relu). */
+int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, double count, const float* gamma, const float* beta,
+                    double eps, int relu, const b200jt_tensor* y, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200JT_H_ */

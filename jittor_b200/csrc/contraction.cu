@@ -1,0 +1,70 @@
+// C entry points of the two contraction relays (matmul, conv2d): argument checks and the choice
+// between the tcgen05 tensor-core kernels (bfloat16, tile-aligned shapes) and the CUDA-core kernels
+// (float32, or shapes the tensor-core tiles do not cover).
+#include "gemm_simt.cuh"
+
+using namespace b200jt;
+
+extern "C" size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c, int trans_a, int trans_b) {
+    (void)a; (void)b; (void)c; (void)trans_a; (void)trans_b;
+    return 0;
+}
+
+extern "C" int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
+                             int trans_a, int trans_b, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    B200JT_CHECK_ARG(valid_tensor(a) && valid_tensor(b) && valid_tensor(c), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(a->ndim == 2 && b->ndim == 2 && c->ndim == 2, "matmul takes 2-D tensors");
+    B200JT_CHECK_ARG(a->dtype == b->dtype && a->dtype == c->dtype &&
+                     (a->dtype == B200JT_FLOAT32 || a->dtype == B200JT_BFLOAT16), "a, b, c must all be float32 or bfloat16");
+    const int64_t M = trans_a ? a->shape[1] : a->shape[0], K = trans_a ? a->shape[0] : a->shape[1];
+    const int64_t Kb = trans_b ? b->shape[1] : b->shape[0], N = trans_b ? b->shape[0] : b->shape[1];
+    B200JT_CHECK_ARG(K == Kb, "dimension not match, a:" + shape_str(a) + " b:" + shape_str(b));
+    B200JT_CHECK_ARG(c->shape[0] == M && c->shape[1] == N, "c has the wrong shape " + shape_str(c));
+    if (M == 0 || N == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    return matmul_simt(a->ptr, b->ptr, c->ptr, a->dtype, M, N, K, trans_a != 0, trans_b != 0, st);
+}
+
+static int conv_shape(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                      int sh, int sw, int ph, int pw, int dh, int dw, int groups, ConvShape* s) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(w) && valid_tensor(y), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(x->ndim == 4 && w->ndim == 4 && y->ndim == 4, "conv2d takes NCHW x, OIHW w, NCHW y");
+    B200JT_CHECK_ARG(groups == 1, "only groups == 1 is supported");
+    B200JT_CHECK_ARG(x->dtype == w->dtype && x->dtype == y->dtype &&
+                     (x->dtype == B200JT_FLOAT32 || x->dtype == B200JT_BFLOAT16), "x, w, y must all be float32 or bfloat16");
+    B200JT_CHECK_ARG(sh > 0 && sw > 0 && dh > 0 && dw > 0 && ph >= 0 && pw >= 0, "bad stride/padding/dilation");
+    s->N = (int)x->shape[0]; s->C = (int)x->shape[1]; s->H = (int)x->shape[2]; s->W = (int)x->shape[3];
+    s->Co = (int)w->shape[0]; s->KH = (int)w->shape[2]; s->KW = (int)w->shape[3];
+    B200JT_CHECK_ARG(w->shape[1] == s->C, "weight in-channels do not match x");
+    // output extent, python/jittor/nn.py:1006-1007
+    s->OH = (s->H + ph * 2 - s->KH * dh + dh - 1) / sh + 1;
+    s->OW = (s->W + pw * 2 - s->KW * dw + dw - 1) / sw + 1;
+    s->sh = sh; s->sw = sw; s->ph = ph; s->pw = pw; s->dh = dh; s->dw = dw;
+    B200JT_CHECK_ARG(s->OH > 0 && s->OW > 0, "empty output");
+    B200JT_CHECK_ARG(y->shape[0] == s->N && y->shape[1] == s->Co && y->shape[2] == s->OH && y->shape[3] == s->OW,
+                     "y has the wrong shape " + shape_str(y));
+    return 0;
+}
+
+extern "C" size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                                          int sh, int sw, int ph, int pw, int dh, int dw, int groups) {
+    (void)x; (void)w; (void)y; (void)sh; (void)sw; (void)ph; (void)pw; (void)dh; (void)dw; (void)groups;
+    return 0;
+}
+
+extern "C" int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                             int sh, int sw, int ph, int pw, int dh, int dw, int groups,
+                             float* stats, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    ConvShape s;
+    int rc = conv_shape(x, w, y, sh, sw, ph, pw, dh, dw, groups, &s);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (numel(y) != 0) {
+        rc = conv2d_simt(x->ptr, w->ptr, y->ptr, x->dtype, s, st);
+        if (rc) return rc;
+    }
+    if (stats) return b200jt_bn_stats(y, stats, stream);
+    return 0;
+}

@@ -1,0 +1,15 @@
+// Host entry points of the CUDA-core contraction kernels (gemm_simt.cu) and of the tcgen05 kernels.
+#pragma once
+#include "common.cuh"
+
+namespace b200jt {
+
+struct ConvShape {
+    int N, C, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+};
+
+int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int64_t N, int64_t K,
+                bool trans_a, bool trans_b, cudaStream_t st);
+int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
+
+}  // namespace b200jt

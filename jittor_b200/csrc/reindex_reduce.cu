@@ -1,0 +1,400 @@
+// reindex_reduce: x[:] = init(op); for every element i of y, unless it overflows: x[index(i)] = op(x[index(i)], y[i]).
+//
+// Paths, chosen on the host from the compiled index program:
+//   injective  -- affine index map that never sends two y elements to one x element (e.g. the 2x2 pool
+//                 backward): plain stores after the init fill, no atomics.
+//   privatised -- one indexed dim addressed through @e0(i0..in) ("scatter") and few bins: every CTA
+//                 accumulates into replicated shared-memory bins (replicas spread same-address
+//                 conflicts of skewed inputs over banks), writes one partial row to a workspace and a
+//                 second kernel folds the rows in fixed order -- deterministic for floating point.
+//   direct     -- same scatter form, many bins: 128-bit loads of values and indices, one red.global per
+//                 element (the bins live in L2).
+//   generic    -- bytecode-interpreted index, one atomic per element.
+#include "atomic_ops.cuh"
+#include "index_program.cuh"
+
+#include <algorithm>
+
+namespace b200jt {
+
+constexpr int kPrivThreads = 512;
+constexpr int kPrivMaxSmemBytes = 160 * 1024;
+constexpr int64_t kPrivMaxBinBytes = 32 * 1024;     // bins*sizeof(T) up to which the privatised path is used
+constexpr int kPrivGrid = kNumSMs;                  // one CTA per SM (dynamic smem limits residency to 1)
+
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kernel(T* __restrict__ x, int64_t n, T v) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] = v;
+}
+
+template <typename T, typename I>
+__global__ void __launch_bounds__(256)
+rr_generic_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant__ IndexProgram P,
+                  int64_t n, int op) {
+    const int nl = P.ndim_loop, nx = P.ndim_x;
+    for (int64_t flat = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; flat < n;
+         flat += (int64_t)gridDim.x * blockDim.x) {
+        I iv[kMaxDims];
+        int64_t r = flat;
+#pragma unroll 1
+        for (int d = nl - 1; d >= 0; d--) { int64_t s = P.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
+        I xid[kMaxDims];
+        if (eval_index_program<I>(P, iv, xid)) continue;
+        int64_t off = 0;
+        for (int d = 0; d < nx; d++) off = off * P.x_shape[d] + (int64_t)xid[d];
+        atomic_apply<T>(x + off, y[flat], op);
+    }
+}
+
+// ---- injective affine map: x[A.i + c] = op(init, y[i]) with plain stores -----------------------------
+// One thread takes 4 consecutive y elements (one 128-bit load for 4-byte types), advances the loop
+// coordinates like an odometer and pairs neighbouring x offsets into 8/16-byte stores.
+struct RRAffineArgs {
+    int32_t ndim_loop, ndim_x;
+    int64_t loop_shape[kMaxDims];
+    int64_t x_shape[kMaxDims];
+    int64_t coef[kMaxDims][kMaxDims];
+    int64_t c0[kMaxDims];
+    int32_t check_bounds;          // 0 when the host proved every index in range
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rr_affine_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant__ RRAffineArgs A,
+                 int64_t n, int op, T init) {
+    constexpr int VEC = 4;
+    const int nl = A.ndim_loop, nx = A.ndim_x;
+    const int64_t n_vec = (n + VEC - 1) / VEC;
+    const bool aligned = ((uintptr_t)y % (VEC * sizeof(T))) == 0;
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n_vec; v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t flat = v * VEC;
+        const int cnt = (int)(n - flat < VEC ? n - flat : VEC);
+        __align__(16) T val[VEC];
+        if (cnt == VEC && aligned && sizeof(T) * VEC == 16) *reinterpret_cast<uint4*>(val) = __ldcs(reinterpret_cast<const uint4*>(y + flat));
+        else for (int e = 0; e < cnt; e++) val[e] = y[flat + e];
+        int64_t iv[kMaxDims];
+        int64_t r = flat;
+#pragma unroll 1
+        for (int d = nl - 1; d >= 0; d--) { int64_t s = A.loop_shape[d]; iv[d] = r % s; r /= s; }
+        int64_t off[VEC];
+        bool ok[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+            int64_t o = 0; bool over = false;
+#pragma unroll 1
+            for (int d = 0; d < nx; d++) {
+                int64_t id = A.c0[d];
+                for (int j = 0; j < nl; j++) id += A.coef[d][j] * iv[j];
+                if (A.check_bounds) over |= (id < 0) | (id >= A.x_shape[d]);
+                o = o * A.x_shape[d] + id;
+            }
+            off[e] = o; ok[e] = !over && e < cnt;
+            // odometer step
+#pragma unroll 1
+            for (int d = nl - 1; d >= 0; d--) { if (++iv[d] < A.loop_shape[d]) break; iv[d] = 0; }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) val[e] = apply_op<T>(op, init, val[e]);
+        if constexpr (sizeof(T) == 4) {
+            const bool all = ok[0] & ok[1] & ok[2] & ok[3];
+            if (all && off[1] == off[0] + 1 && off[2] == off[0] + 2 && off[3] == off[0] + 3 && (((uintptr_t)(x + off[0])) & 15) == 0) {
+                *reinterpret_cast<uint4*>(x + off[0]) = *reinterpret_cast<uint4*>(val);
+                continue;
+            }
+            if (all && off[1] == off[0] + 1 && off[3] == off[2] + 1 && (((uintptr_t)(x + off[0])) & 7) == 0 && (((uintptr_t)(x + off[2])) & 7) == 0) {
+                *reinterpret_cast<uint2*>(x + off[0]) = *reinterpret_cast<uint2*>(val);
+                *reinterpret_cast<uint2*>(x + off[2]) = *reinterpret_cast<uint2*>(val + 2);
+                continue;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) if (ok[e]) x[off[e]] = val[e];
+    }
+}
+
+// ---- direct scatter, many bins: x[e0[i]] = op(x[e0[i]], y[i]) --------------------------------------
+template <typename T, typename E, int VEC>
+__global__ void __launch_bounds__(256)
+rr_direct_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __restrict__ x,
+                 int64_t n, int64_t bins, int op) {
+    const int64_t n_vec = n / VEC;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n_vec; v += stride) {
+        __align__(16) T val[VEC];
+        __align__(16) E ind[VEC];
+        if constexpr (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(val) = __ldcs(reinterpret_cast<const uint4*>(y) + v);
+        else {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) val[e] = y[v * VEC + e];
+        }
+        if constexpr (VEC * sizeof(E) == 16) *reinterpret_cast<uint4*>(ind) = __ldcs(reinterpret_cast<const uint4*>(idx) + v);
+        else {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) ind[e] = idx[v * VEC + e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+            int64_t b = (int64_t)ind[e];
+            if (b >= 0 && b < bins) atomic_apply<T>(x + b, val[e], op);
+        }
+    }
+    // tail
+    for (int64_t i = n_vec * VEC + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) {
+        int64_t b = (int64_t)idx[i];
+        if (b >= 0 && b < bins) atomic_apply<T>(x + b, y[i], op);
+    }
+}
+
+// ---- privatised scatter, few bins ------------------------------------------------------------------
+// smem layout: R replicas of `bins` elements; lane l of a warp updates replica (l % R).
+template <typename T, typename E, int VEC>
+__global__ void __launch_bounds__(kPrivThreads, 1)
+rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __restrict__ partial,
+                     int64_t n, int bins, int replicas, int op, bool is_bool) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* sm = reinterpret_cast<T*>(smem_raw);
+    const T init = init_value<T>(op, is_bool);
+    for (int i = threadIdx.x; i < bins * replicas; i += blockDim.x) sm[i] = init;
+    __syncthreads();
+    T* mine = sm + (threadIdx.x % replicas) * bins;
+    const int64_t n_vec = n / VEC;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n_vec; v += stride) {
+        __align__(16) T val[VEC];
+        __align__(16) E ind[VEC];
+        if constexpr (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(val) = __ldcs(reinterpret_cast<const uint4*>(y) + v);
+        else {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) val[e] = y[v * VEC + e];
+        }
+        if constexpr (VEC * sizeof(E) == 16) *reinterpret_cast<uint4*>(ind) = __ldcs(reinterpret_cast<const uint4*>(idx) + v);
+        else {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) ind[e] = idx[v * VEC + e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+            int64_t b = (int64_t)ind[e];
+            if (b >= 0 && b < bins) atomic_apply<T>(mine + b, val[e], op);
+        }
+    }
+    for (int64_t i = n_vec * VEC + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) {
+        int64_t b = (int64_t)idx[i];
+        if (b >= 0 && b < bins) atomic_apply<T>(mine + b, y[i], op);
+    }
+    __syncthreads();
+    // fold the replicas in fixed order and publish this CTA's row
+    for (int b = threadIdx.x; b < bins; b += blockDim.x) {
+        T acc = sm[b];
+        for (int r = 1; r < replicas; r++) acc = apply_op<T>(op, acc, sm[r * bins + b]);
+        partial[(int64_t)blockIdx.x * bins + b] = acc;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rr_fold_partials_kernel(const T* __restrict__ partial, T* __restrict__ x, int bins, int rows, int op, bool is_bool) {
+    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < bins; b += gridDim.x * blockDim.x) {
+        T acc = init_value<T>(op, is_bool);
+        for (int r = 0; r < rows; r++) acc = apply_op<T>(op, acc, partial[(int64_t)r * bins + b]);
+        x[b] = acc;
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+struct RRPlan {
+    enum Path { GENERIC, INJECTIVE, DIRECT, PRIVATISED } path = GENERIC;
+    int replicas = 1;
+    size_t workspace = 0;
+    size_t smem = 0;
+    bool in_range = false;      // injective path: every index of every y element is inside x
+    bool covers_all = false;    // ... and every x element is written: the init fill is skipped
+};
+
+static bool affine_injective(const IndexProgram& P) {
+    if (!P.is_affine) return false;
+    // flat coefficient of every loop axis
+    int64_t xs[kMaxDims]; int64_t st = 1;
+    for (int d = P.ndim_x - 1; d >= 0; d--) { xs[d] = st; st *= P.x_shape[d]; }
+    std::vector<std::pair<int64_t, int64_t>> terms;   // (|F_j|, n_j - 1)
+    for (int j = 0; j < P.ndim_loop; j++) {
+        if (P.loop_shape[j] <= 1) continue;
+        int64_t F = 0;
+        for (int d = 0; d < P.ndim_x; d++) F += P.coef[d][j] * xs[d];
+        if (F == 0) return false;
+        terms.push_back({F < 0 ? -F : F, P.loop_shape[j] - 1});
+    }
+    std::sort(terms.begin(), terms.end());
+    int64_t reach = 0;            // max offset reachable with the smaller terms
+    for (auto& t : terms) {
+        if (t.first <= reach) return false;
+        reach += t.first * t.second;
+    }
+    return true;
+}
+
+static bool op_supported(int op, int dtype) {
+    switch (op) {
+        case OP_ADD: case OP_MUL: case OP_MAX: case OP_MIN: case OP_VOID: return true;
+        case OP_BAND: case OP_BOR: case OP_BXOR: return !dtype_is_float(dtype);
+        case OP_LAND: case OP_LOR: case OP_LXOR: return true;
+    }
+    return false;
+}
+
+static RRPlan make_plan(const b200jt_tensor* y, const b200jt_tensor* x, int op, const IndexProgram& P) {
+    RRPlan plan;
+    const int es = dtype_size(x->dtype);
+    const int64_t bins = numel(x);
+    if (op != OP_VOID && affine_injective(P)) {
+        plan.path = RRPlan::INJECTIVE;
+        plan.in_range = true;
+        for (int d = 0; d < P.ndim_x; d++) {
+            int64_t lo = P.c0[d], hi = P.c0[d];
+            for (int j = 0; j < P.ndim_loop; j++) {
+                const int64_t span = P.coef[d][j] * (P.loop_shape[j] - 1);
+                if (span < 0) lo += span; else hi += span;
+            }
+            if (lo < 0 || hi >= P.x_shape[d]) plan.in_range = false;
+        }
+        plan.covers_all = plan.in_range && numel(y) == bins;
+        return plan;
+    }
+    if (P.is_direct_extra && op != OP_VOID &&
+        (P.extras[0].dtype == B200JT_INT32 || P.extras[0].dtype == B200JT_INT64) && es >= 4) {
+        if (bins * es <= kPrivMaxBinBytes && numel(y) >= (1 << 16)) {
+            plan.path = RRPlan::PRIVATISED;
+            int r = (int)(kPrivMaxSmemBytes / (bins * es));
+            plan.replicas = r >= 8 ? 8 : r >= 4 ? 4 : r >= 2 ? 2 : 1;
+            plan.smem = (size_t)plan.replicas * bins * es;
+            plan.workspace = (size_t)kPrivGrid * bins * es;
+        } else {
+            plan.path = RRPlan::DIRECT;
+        }
+    }
+    return plan;
+}
+
+template <typename T>
+static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, const IndexProgram& P,
+                     const RRPlan& plan, void* workspace, cudaStream_t st) {
+    const int64_t n = numel(y), bins = numel(x);
+    const bool is_bool = x->dtype == B200JT_BOOL;
+    const T* yp = (const T*)y->ptr;
+    T* xp = (T*)x->ptr;
+    if (plan.path == RRPlan::PRIVATISED) {
+        T* partial = (T*)workspace;
+        const bool e64 = P.extras[0].dtype == B200JT_INT64;
+        constexpr int VEC = 16 / sizeof(T);
+        const bool aligned = ((uintptr_t)yp % 16 == 0) && ((uintptr_t)P.extras[0].ptr % 16 == 0);
+#define B200JT_PRIV(E, V)                                                                                      \
+        do { auto k = rr_privatised_kernel<T, E, V>;                                                            \
+             B200JT_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrivMaxSmemBytes)); \
+             k<<<kPrivGrid, kPrivThreads, plan.smem, st>>>(yp, (const E*)P.extras[0].ptr, partial, n, (int)bins,   \
+                                                           plan.replicas, op, is_bool); } while (0)
+        if (e64) { if (aligned) B200JT_PRIV(int64_t, VEC); else B200JT_PRIV(int64_t, 1); }
+        else     { if (aligned) B200JT_PRIV(int32_t, VEC); else B200JT_PRIV(int32_t, 1); }
+#undef B200JT_PRIV
+        B200JT_LAUNCH_CHECK();
+        rr_fold_partials_kernel<T><<<grid_for(bins, 256), 256, 0, st>>>(partial, xp, (int)bins, kPrivGrid, op, is_bool);
+        B200JT_LAUNCH_CHECK();
+        return 0;
+    }
+    if (op != OP_VOID && bins > 0 && !(plan.path == RRPlan::INJECTIVE && plan.covers_all)) {
+        fill_kernel<T><<<grid_for(bins, 256), 256, 0, st>>>(xp, bins, init_value<T>(op, is_bool));
+        B200JT_LAUNCH_CHECK();
+    }
+    if (n == 0 || bins == 0) return 0;
+    if (plan.path == RRPlan::INJECTIVE) {
+        RRAffineArgs A; memset(&A, 0, sizeof(A));
+        A.ndim_loop = P.ndim_loop; A.ndim_x = P.ndim_x;
+        memcpy(A.loop_shape, P.loop_shape, sizeof(A.loop_shape));
+        memcpy(A.x_shape, P.x_shape, sizeof(A.x_shape));
+        memcpy(A.coef, P.coef, sizeof(A.coef));
+        memcpy(A.c0, P.c0, sizeof(A.c0));
+        A.check_bounds = plan.in_range ? 0 : 1;
+        rr_affine_kernel<T><<<grid_for((n + 3) / 4, 256), 256, 0, st>>>(yp, xp, A, n, op, init_value<T>(op, is_bool));
+        B200JT_LAUNCH_CHECK();
+        return 0;
+    }
+    if (plan.path == RRPlan::DIRECT) {
+        const bool e64 = P.extras[0].dtype == B200JT_INT64;
+        constexpr int VEC = 16 / sizeof(T);
+        const bool aligned = ((uintptr_t)yp % 16 == 0) && ((uintptr_t)P.extras[0].ptr % 16 == 0);
+        const unsigned grid = grid_for(n / VEC + 1, 256);
+        if (e64) {
+            if (aligned) rr_direct_kernel<T, int64_t, VEC><<<grid, 256, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op);
+            else rr_direct_kernel<T, int64_t, 1><<<grid, 256, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op);
+        } else {
+            if (aligned) rr_direct_kernel<T, int32_t, VEC><<<grid, 256, 0, st>>>(yp, (const int32_t*)P.extras[0].ptr, xp, n, bins, op);
+            else rr_direct_kernel<T, int32_t, 1><<<grid, 256, 0, st>>>(yp, (const int32_t*)P.extras[0].ptr, xp, n, bins, op);
+        }
+        B200JT_LAUNCH_CHECK();
+        return 0;
+    }
+    const bool small = n < (1LL << 31) && bins < (1LL << 31);
+    const unsigned grid = grid_for(n, 256);
+    if (small) rr_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>(yp, xp, P, n, op);
+    else       rr_generic_kernel<T, int64_t><<<grid, 256, 0, st>>>(yp, xp, P, n, op);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+static int prepare(const b200jt_tensor* y, const b200jt_tensor* x, const char* op_name,
+                   const char* const* indexes, int n_indexes, const char* const* conds, int n_conds,
+                   const b200jt_tensor* extras, int n_extras, IndexProgram* P, int* op, RRPlan* plan) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(y), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(x->dtype == y->dtype, "x and y must have the same dtype");
+    B200JT_CHECK_ARG(n_indexes == x->ndim, "Number of shape and indexes should be the same.");
+    B200JT_CHECK_ARG(n_extras >= 0 && n_extras <= B200JT_MAX_EXTRAS, "too many extras");
+    for (int k = 0; k < n_extras; k++) B200JT_CHECK_ARG(valid_tensor(&extras[k]), "invalid extras descriptor");
+    *op = strcmp(op_name, "void") == 0 ? OP_VOID : binary_op_from_name(op_name);
+    B200JT_CHECK_ARG(*op != OP_INVALID && *op != OP_MEAN && op_supported(*op, x->dtype),
+                     std::string("unsupported reindex_reduce op '") + op_name + "' for " + dtype_name(x->dtype));
+    std::string err;
+    if (!compile_index_program(y->shape, y->ndim, x->shape, x->ndim, indexes, n_indexes, conds, n_conds,
+                               extras, n_extras, P, &err))
+        return fail(-2, "b200jt_reindex_reduce: " + err);
+    *plan = make_plan(y, x, *op, *P);
+    return 0;
+}
+
+}  // namespace b200jt
+
+using namespace b200jt;
+
+extern "C" size_t b200jt_reindex_reduce_workspace(const b200jt_tensor* y, const b200jt_tensor* x, const char* op,
+                                                  const char* const* indexes, int n_indexes,
+                                                  const char* const* overflow_conditions, int n_conditions,
+                                                  const b200jt_tensor* extras, int n_extras) {
+    IndexProgram P; int opc; RRPlan plan;
+    if (prepare(y, x, op, indexes, n_indexes, overflow_conditions, n_conditions, extras, n_extras, &P, &opc, &plan) != 0)
+        return 0;
+    return plan.workspace;
+}
+
+extern "C" int b200jt_reindex_reduce(const b200jt_tensor* y, const b200jt_tensor* x, const char* op,
+                                     const char* const* indexes, int n_indexes,
+                                     const char* const* overflow_conditions, int n_conditions,
+                                     const b200jt_tensor* extras, int n_extras,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+    IndexProgram P; int opc; RRPlan plan;
+    int rc = prepare(y, x, op, indexes, n_indexes, overflow_conditions, n_conditions, extras, n_extras, &P, &opc, &plan);
+    if (rc) return rc;
+    B200JT_CHECK_ARG(workspace_bytes >= plan.workspace && (plan.workspace == 0 || workspace),
+                     "workspace too small: need " + std::to_string(plan.workspace) + " bytes");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x->dtype) {
+        case B200JT_BOOL: case B200JT_UINT8: return run_typed<uint8_t>(y, x, opc, P, plan, workspace, st);
+        case B200JT_INT8: return run_typed<int8_t>(y, x, opc, P, plan, workspace, st);
+        case B200JT_INT16: return run_typed<int16_t>(y, x, opc, P, plan, workspace, st);
+        case B200JT_INT32: return run_typed<int32_t>(y, x, opc, P, plan, workspace, st);
+        case B200JT_INT64: return run_typed<int64_t>(y, x, opc, P, plan, workspace, st);
+        case B200JT_FLOAT16: return run_typed<__half>(y, x, opc, P, plan, workspace, st);
+        case B200JT_BFLOAT16: return run_typed<__nv_bfloat16>(y, x, opc, P, plan, workspace, st);
+        case B200JT_FLOAT32: return run_typed<float>(y, x, opc, P, plan, workspace, st);
+        case B200JT_FLOAT64: return run_typed<double>(y, x, opc, P, plan, workspace, st);
+    }
+    return fail(-1, "b200jt_reindex_reduce: unsupported dtype");
+}

@@ -1,0 +1,282 @@
+// Fused row softmax / log-softmax and row LayerNorm over the last axis: one read and one write of
+// the [rows, cols] tensor (the reference's meta-op form reads x three times, python/jittor/nn.py:527-535,778-787).
+//
+//   reg kernel  -- the row lives in registers: CTA of 256 threads (or one warp for short rows), 128-bit
+//                  loads, warp-shuffle tree + one shared-memory hop, 128-bit stores. HBM-bound: 1R + 1W.
+//   pass kernel -- any cols / alignment: three sweeps by one CTA per row (re-reads hit L2).
+// IO dtype float32 or bfloat16; all math in float32.
+#include "common.cuh"
+#include <cfloat>
+
+namespace b200jt {
+
+enum RowOp : int { ROW_SOFTMAX = 0, ROW_LOG_SOFTMAX = 1, ROW_LAYERNORM = 2 };
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* out) {
+        float4 v = __ldcs(reinterpret_cast<const float4*>(p)); out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* in) {
+        __stcs(reinterpret_cast<float4*>(p), make_float4(in[0], in[1], in[2], in[3]));
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+        uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(h[i]); out[2 * i] = f.x; out[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* in) {
+        uint4 v; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+        __stcs(reinterpret_cast<uint4*>(p), v);
+    }
+};
+
+template <typename T> __device__ __forceinline__ float ld1(const T* p);
+template <> __device__ __forceinline__ float ld1<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ld1<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void st1(T* p, float v);
+template <> __device__ __forceinline__ void st1<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void st1<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+// Reduction over the GROUP threads that share a row: a warp (GROUP == 32) or the whole CTA.
+template <int GROUP, bool IS_MAX>
+__device__ __forceinline__ float group_reduce(float v, float* sm) {
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if constexpr (GROUP == 32) return v;
+    else {
+        constexpr int W = GROUP / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();                      // sm may still be read from the previous reduction
+        if (lane == 0) sm[warp] = v;
+        __syncthreads();
+        float t = lane < W ? sm[lane] : (IS_MAX ? -FLT_MAX : 0.f);
+        return IS_MAX ? warp_max(t) : warp_sum(t);
+    }
+}
+
+// GROUP threads per row, VPT 16-byte vectors per thread; requires cols % Vec16<T>::N == 0 and
+// cols <= GROUP * VPT * N.
+template <typename T, int GROUP, int VPT, int OP>
+__global__ void __launch_bounds__(256)
+row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ gamma,
+               const float* __restrict__ beta, int64_t rows, int cols, float eps) {
+    constexpr int N = Vec16<T>::N;
+    constexpr int ROWS_PER_CTA = 256 / GROUP;
+    __shared__ float sm[8];
+    const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
+    const int nvec = cols / N;
+    for (int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + g; row < rows;
+         row += (int64_t)gridDim.x * ROWS_PER_CTA) {
+        const T* xr = x + row * cols;
+        T* yr = y + row * cols;
+        float v[VPT][N];
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int vi = t + k * GROUP;
+            if (vi < nvec) Vec16<T>::load(xr + (int64_t)vi * N, v[k]);
+            else {
+#pragma unroll
+                for (int e = 0; e < N; e++) v[k][e] = (OP == ROW_LAYERNORM) ? 0.f : -FLT_MAX;
+            }
+        }
+        if constexpr (OP == ROW_LAYERNORM) {
+            float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+#pragma unroll
+                for (int e = 0; e < N; e++) { s1 += v[k][e]; s2 += v[k][e] * v[k][e]; }
+            s1 = group_reduce<GROUP, false>(s1, sm);
+            s2 = group_reduce<GROUP, false>(s2, sm);
+            const float rc = 1.0f / (float)cols;
+            const float mean = s1 * rc, m2 = s2 * rc;
+            const float var = fmaxf(m2 - mean * mean, 0.f);
+            const float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+            for (int k = 0; k < VPT; k++) {
+                const int vi = t + k * GROUP;
+                if (vi < nvec) {
+                    float o[N], gm[N], bt[N];
+#pragma unroll
+                    for (int q = 0; q < N / 4; q++) {
+                        const int c = vi * N + q * 4;
+                        float4 g4 = gamma ? __ldg(reinterpret_cast<const float4*>(gamma + c)) : make_float4(1.f, 1.f, 1.f, 1.f);
+                        float4 b4 = beta ? __ldg(reinterpret_cast<const float4*>(beta + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        gm[q * 4] = g4.x; gm[q * 4 + 1] = g4.y; gm[q * 4 + 2] = g4.z; gm[q * 4 + 3] = g4.w;
+                        bt[q * 4] = b4.x; bt[q * 4 + 1] = b4.y; bt[q * 4 + 2] = b4.z; bt[q * 4 + 3] = b4.w;
+                    }
+#pragma unroll
+                    for (int e = 0; e < N; e++) {
+                        const float w = gm[e] * rstd;
+                        o[e] = v[k][e] * w + (bt[e] - mean * w);
+                    }
+                    Vec16<T>::store(yr + (int64_t)vi * N, o);
+                }
+            }
+        } else {
+            float m = -FLT_MAX;
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+#pragma unroll
+                for (int e = 0; e < N; e++) m = fmaxf(m, v[k][e]);
+            m = group_reduce<GROUP, true>(m, sm);
+            float s = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+#pragma unroll
+                for (int e = 0; e < N; e++) {
+                    const float a = v[k][e] - m;
+                    const float ex = expf(a);
+                    s += (t + k * GROUP < nvec) ? ex : 0.f;
+                    v[k][e] = (OP == ROW_SOFTMAX) ? ex : a;
+                }
+            s = group_reduce<GROUP, false>(s, sm);
+            const float ls = logf(s);
+#pragma unroll
+            for (int k = 0; k < VPT; k++) {
+                const int vi = t + k * GROUP;
+                if (vi < nvec) {
+                    float o[N];
+#pragma unroll
+                    for (int e = 0; e < N; e++) o[e] = (OP == ROW_SOFTMAX) ? v[k][e] / s : v[k][e] - ls;
+                    Vec16<T>::store(yr + (int64_t)vi * N, o);
+                }
+            }
+        }
+    }
+}
+
+// Any cols: one CTA per row, three sweeps.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256)
+row_pass_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ gamma,
+                const float* __restrict__ beta, int64_t rows, int64_t cols, float eps) {
+    __shared__ float sm[8];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* xr = x + row * cols;
+        T* yr = y + row * cols;
+        if constexpr (OP == ROW_LAYERNORM) {
+            float s1 = 0.f, s2 = 0.f;
+            for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) { float a = ld1<T>(xr + c); s1 += a; s2 += a * a; }
+            s1 = group_reduce<256, false>(s1, sm);
+            s2 = group_reduce<256, false>(s2, sm);
+            const float rc = 1.0f / (float)cols;
+            const float mean = s1 * rc, m2 = s2 * rc;
+            const float var = fmaxf(m2 - mean * mean, 0.f);
+            for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+                const float w = (gamma ? gamma[c] : 1.f) / sqrtf(var + eps);
+                const float b = (beta ? beta[c] : 0.f) - mean * w;
+                st1<T>(yr + c, ld1<T>(xr + c) * w + b);
+            }
+        } else {
+            float m = -FLT_MAX;
+            for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, ld1<T>(xr + c));
+            m = group_reduce<256, true>(m, sm);
+            float s = 0.f;
+            for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += expf(ld1<T>(xr + c) - m);
+            s = group_reduce<256, false>(s, sm);
+            const float ls = logf(s);
+            for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+                const float a = ld1<T>(xr + c) - m;
+                st1<T>(yr + c, OP == ROW_SOFTMAX ? expf(a) / s : a - ls);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <typename T, int OP>
+static int launch_rows(const T* x, T* y, const float* gamma, const float* beta, int64_t rows, int64_t cols,
+                       float eps, cudaStream_t st) {
+    constexpr int N = Vec16<T>::N;
+    const bool vec_ok = cols % N == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+    const int64_t nvec = cols / N;
+#define B200JT_ROW(GROUP, VPT)                                                                      \
+    do { const int rpc = 256 / GROUP;                                                               \
+         int64_t ctas = (rows + rpc - 1) / rpc;                                                     \
+         unsigned grid = (unsigned)(ctas < (int64_t)kNumSMs * 64 ? ctas : (int64_t)kNumSMs * 64);   \
+         row_reg_kernel<T, GROUP, VPT, OP><<<grid, 256, 0, st>>>(x, y, gamma, beta, rows, (int)cols, eps); } while (0)
+    if (vec_ok && nvec <= 32 * 8) {
+        if (nvec <= 32) B200JT_ROW(32, 1);
+        else if (nvec <= 64) B200JT_ROW(32, 2);
+        else if (nvec <= 128) B200JT_ROW(32, 4);
+        else B200JT_ROW(32, 8);
+    } else if (vec_ok && nvec <= 256 * 8) {
+        if (nvec <= 256) B200JT_ROW(256, 1);
+        else if (nvec <= 512) B200JT_ROW(256, 2);
+        else if (nvec <= 1024) B200JT_ROW(256, 4);
+        else B200JT_ROW(256, 8);
+    } else {
+        unsigned grid = (unsigned)(rows < (int64_t)kNumSMs * 16 ? rows : (int64_t)kNumSMs * 16);
+        row_pass_kernel<T, OP><<<grid, 256, 0, st>>>(x, y, gamma, beta, rows, cols, eps);
+    }
+#undef B200JT_ROW
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+static int rows_cols(const b200jt_tensor* x, const b200jt_tensor* y, int64_t* rows, int64_t* cols) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(y), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(x->dtype == y->dtype && (x->dtype == B200JT_FLOAT32 || x->dtype == B200JT_BFLOAT16),
+                     "x and y must both be float32 or bfloat16");
+    B200JT_CHECK_ARG(numel(x) == numel(y), "x and y differ in size");
+    *cols = x->shape[x->ndim - 1];
+    *rows = *cols ? numel(x) / *cols : 0;
+    return 0;
+}
+
+}  // namespace b200jt
+
+using namespace b200jt;
+
+extern "C" int b200jt_softmax(const b200jt_tensor* x, const b200jt_tensor* y, int log, void* stream) {
+    int64_t rows, cols;
+    int rc = rows_cols(x, y, &rows, &cols);
+    if (rc) return rc;
+    if (rows == 0 || cols == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x->dtype == B200JT_FLOAT32) {
+        return log ? launch_rows<float, ROW_LOG_SOFTMAX>((const float*)x->ptr, (float*)y->ptr, nullptr, nullptr, rows, cols, 0.f, st)
+                   : launch_rows<float, ROW_SOFTMAX>((const float*)x->ptr, (float*)y->ptr, nullptr, nullptr, rows, cols, 0.f, st);
+    }
+    return log ? launch_rows<__nv_bfloat16, ROW_LOG_SOFTMAX>((const __nv_bfloat16*)x->ptr, (__nv_bfloat16*)y->ptr, nullptr, nullptr, rows, cols, 0.f, st)
+               : launch_rows<__nv_bfloat16, ROW_SOFTMAX>((const __nv_bfloat16*)x->ptr, (__nv_bfloat16*)y->ptr, nullptr, nullptr, rows, cols, 0.f, st);
+}
+
+extern "C" int b200jt_layer_norm(const b200jt_tensor* x, const b200jt_tensor* gamma, const b200jt_tensor* beta,
+                                 const b200jt_tensor* y, double eps, void* stream) {
+    int64_t rows, cols;
+    int rc = rows_cols(x, y, &rows, &cols);
+    if (rc) return rc;
+    const float* g = nullptr; const float* b = nullptr;
+    if (gamma) {
+        B200JT_CHECK_ARG(valid_tensor(gamma) && gamma->dtype == B200JT_FLOAT32 && numel(gamma) == cols, "gamma must be float32 [cols]");
+        g = (const float*)gamma->ptr;
+    }
+    if (beta) {
+        B200JT_CHECK_ARG(valid_tensor(beta) && beta->dtype == B200JT_FLOAT32 && numel(beta) == cols, "beta must be float32 [cols]");
+        b = (const float*)beta->ptr;
+    }
+    if (rows == 0 || cols == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x->dtype == B200JT_FLOAT32)
+        return launch_rows<float, ROW_LAYERNORM>((const float*)x->ptr, (float*)y->ptr, g, b, rows, cols, (float)eps, st);
+    return launch_rows<__nv_bfloat16, ROW_LAYERNORM>((const __nv_bfloat16*)x->ptr, (__nv_bfloat16*)y->ptr, g, b, rows, cols, (float)eps, st);
+}

@@ -1,0 +1,45 @@
+"""Process-per-GPU data parallelism over torch.distributed (NCCL on GPUs, gloo in CPU tests): the
+`Var.mpi_all_reduce` surface of the reference (python/jittor/extern/mpi/ops/mpi_all_reduce_op.cc:27-61)
+without MPI. Rank and world size come from the torchrun environment."""
+import os
+
+import torch
+import torch.distributed as tdist
+
+from . import var as V
+
+
+def init(backend=None):
+    """Joins the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (a no-op for one process)."""
+    if tdist.is_initialized() or int(os.environ.get("WORLD_SIZE", "1")) <= 1:
+        return
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    if backend == "nccl":
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    tdist.init_process_group(backend=backend)
+
+
+def in_mpi():
+    return tdist.is_available() and tdist.is_initialized() and tdist.get_world_size() > 1
+
+
+def world_size():
+    return tdist.get_world_size() if in_mpi() else 1
+
+
+def rank():
+    return tdist.get_rank() if in_mpi() else 0
+
+
+def mpi_all_reduce(x, op="add"):
+    """op 'add' or 'mean'; 'mean' is all_reduce(add) / world_size as in the reference (:32-37).
+    Without a process group the input is forwarded unchanged (:28-31)."""
+    x = V.to_var(x)
+    if not in_mpi():
+        return x
+    if op == "mean":
+        return mpi_all_reduce(x, "add") / world_size()
+    if op != "add":
+        raise ValueError(f"Not supported MPI op {op}")
+    return V.Var(x.shape, x.dtype, V.Op("mpi_all_reduce", [x], op="add"))

@@ -1,0 +1,221 @@
+"""The nn callers of the meta-operator path, written with the same meta-op expressions as the reference
+so that the executor sees the same graphs: matmul (python/jittor/nn.py:118-159), Conv (:1001-1021),
+softmax (:523-535), LayerNorm (:766-787), BatchNorm (:651-689), relu (:166-183), Pool via reindex."""
+import numpy as np
+
+from . import var as V
+from .flags import flags, flag_scope
+from .var import Var, to_var
+
+
+class Module:
+    def __call__(self, *a, **k):
+        return self.execute(*a, **k)
+
+    def execute(self, *a, **k):
+        raise NotImplementedError
+
+    def parameters(self):
+        return [v for v in self.__dict__.values() if isinstance(v, Var)]
+
+
+def matmul_transpose(a, b):
+    """c[..., n, k] = sum_m a[..., n, m] * b[k, m]  (python/jittor/nn.py:40-58)."""
+    a, b = to_var(a), to_var(b)
+    assert a.shape[-1] == b.shape[-1], (a.shape, b.shape)
+    if a.ndim != 2:
+        aa = a.reshape((-1, a.shape[-1]))
+        cc = matmul_transpose(aa, b)
+        return cc.reshape(list(a.shape[:-1]) + [-1])
+    assert a.ndim == 2 and b.ndim == 2
+    shape = list(a.shape)[:-1] + list(b.shape)
+    with flag_scope(amp_reg=flags.amp_reg | 36):
+        a = a.broadcast(shape, [len(shape) - 2])
+        b = b.broadcast(shape)
+        return (a * b).sum(len(shape) - 1)
+
+
+def matmul(a, b):
+    """Broadcast-multiply-sum matrix product, every branch of python/jittor/nn.py:118-159."""
+    a, b = to_var(a), to_var(b)
+    with flag_scope(amp_reg=flags.amp_reg | 36):
+        len_a, len_b = a.ndim, b.ndim
+        if len_b == 1:
+            return (a * b).sum(-1)
+        if len_a == 1:
+            return (a.broadcast(b, [-1]) * b).sum(0)
+        shape = []
+        len_c = max(len_a, len_b)
+        (n, m), (m_, k) = a.shape[-2:], b.shape[-2:]
+        assert m == m_, f"dimension not match, a.shape:{a.shape}, b.shape:{b.shape}"
+        if len_b == 2 and len_a > 2:
+            aa = a.reshape((-1, m))
+            cc = matmul(aa, b)
+            return cc.reshape(list(a.shape[:-1]) + [k])
+        for i in range(len_c - 2):
+            ai = len_a - (len_c - i)
+            bi = len_b - (len_c - i)
+            an = a.shape[ai] if ai >= 0 else 1
+            bn = b.shape[bi] if bi >= 0 else 1
+            if an != 1 and bn != 1:
+                assert an == bn, f"dimension not match, a.shape:{a.shape}, b.shape:{b.shape}"
+            shape.append(max(an, bn))
+        shape.extend([n, m, k])
+        a = a.broadcast(shape, [-1])
+        b = b.broadcast(shape, [-3])
+        return (a * b).sum(-2)
+
+
+bmm = matmul
+
+
+def relu(x):
+    x = to_var(x)
+    return V.ternary(x > 0.0, x, 0.0)
+
+
+def softmax(x, dim=None, log=False):
+    x = to_var(x)
+    if dim is None:
+        dim = ()
+    dtype, x = x.dtype, x._to_float()
+    if log:
+        a = x - x.max(dim, keepdims=True)
+        ret = a - a.exp().sum(dim, keepdims=True).log()
+    else:
+        e = (x - x.max(dim, keepdims=True)).exp()
+        ret = e / e.sum(dim, keepdims=True)
+    return ret.cast(dtype)
+
+
+def log_softmax(x, dim=None):
+    return softmax(x, dim, True)
+
+
+def _pair(v):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+
+
+def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """groups == 1 branch of Conv.execute (python/jittor/nn.py:1001-1021): reindex x to the 7-D window tensor,
+    broadcast w over [0,3,4], multiply, sum over [2,5,6]."""
+    x, weight = to_var(x), to_var(weight)
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    if groups != 1:
+        raise NotImplementedError("grouped convolution is not on the accelerated path")
+    N, C, H, W = x.shape
+    out_channels, Cw, Kh, Kw = weight.shape
+    assert C == Cw
+    oh = (H + padding[0] * 2 - Kh * dilation[0] + dilation[0] - 1) // stride[0] + 1
+    ow = (W + padding[1] * 2 - Kw * dilation[1] + dilation[1] - 1) // stride[1] + 1
+    assert oh > 0 and ow > 0
+    with flag_scope(amp_reg=flags.amp_reg | 36):
+        xx = x.reindex([N, out_channels, C, oh, ow, Kh, Kw], [
+            "i0",
+            "i2",
+            f"i3*{stride[0]}-{padding[0]}+i5*{dilation[0]}",
+            f"i4*{stride[1]}-{padding[1]}+i6*{dilation[1]}",
+        ])
+        ww = weight.broadcast(xx.shape, [0, 3, 4])
+        yy = xx * ww
+        y = yy.sum([2, 5, 6])
+    if bias is not None:
+        y = y + to_var(bias).broadcast(y.shape, [0, 2, 3])
+    return y
+
+
+class Conv(Module):
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True):
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size = _pair(kernel_size)
+        self.stride, self.padding, self.dilation, self.groups = _pair(stride), _pair(padding), _pair(dilation), groups
+        Kh, Kw = self.kernel_size
+        fan = in_channels * Kh * Kw
+        bound = 1.0 / np.sqrt(fan)
+        rng = np.random.default_rng(0)
+        self.weight = V.array(rng.uniform(-bound, bound, (out_channels, in_channels // groups, Kh, Kw)).astype(np.float32))
+        self.bias = V.array(rng.uniform(-bound, bound, (out_channels,)).astype(np.float32)) if bias else None
+
+    def execute(self, x):
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+
+
+Conv2d = Conv
+
+
+class LayerNorm(Module):
+    def __init__(self, normalized_shape, eps=1e-5, elementwise_affine=True):
+        if isinstance(normalized_shape, int):
+            normalized_shape = (normalized_shape,)
+        self.normalized_shape = tuple(normalized_shape)
+        self.eps = eps
+        self.elementwise_affine = elementwise_affine
+        self.weight = V.ones(self.normalized_shape) if elementwise_affine else 1.0
+        self.bias = V.zeros(self.normalized_shape) if elementwise_affine else 0.0
+
+    def execute(self, x):
+        x = to_var(x)
+        dtype = x.dtype
+        # fp32_guard (python/jittor/nn.py:731-750): half inputs are normalised in float32
+        guard = dtype in ("float16", "bfloat16")
+        if guard:
+            x = x.float32()
+        dims = [-i for i in range(len(self.normalized_shape), 0, -1)]
+        xmean = x.mean(dims=dims, keepdims=True)
+        x2mean = (x * x).mean(dims=dims, keepdims=True)
+        xvar = (x2mean - xmean * xmean).maximum(0.0)
+        w = self.weight / (xvar + self.eps).sqrt()
+        b = self.bias - xmean * w
+        y = x * w + b
+        return y.cast(dtype) if guard else y
+
+
+def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
+    m = LayerNorm(normalized_shape, eps, weight is not None)
+    if weight is not None:
+        m.weight, m.bias = to_var(weight), to_var(bias)
+    return m(x)
+
+
+class BatchNorm(Module):
+    def __init__(self, num_features, eps=1e-5, momentum=0.1, affine=True, is_train=True, sync=True):
+        self.sync, self.num_features, self.is_train = sync, num_features, is_train
+        self.eps, self.momentum, self.affine = eps, momentum, affine
+        self.weight = V.ones((num_features,)) if affine else 1.0
+        self.bias = V.zeros((num_features,)) if affine else 0.0
+        self.running_mean = V.zeros((num_features,))
+        self.running_var = V.ones((num_features,))
+
+    def execute(self, x):
+        from . import dist
+        x = to_var(x)
+        dims = [0] + list(range(2, x.ndim))
+        if self.is_train:
+            xmean = x.mean(dims=dims)
+            x2mean = (x * x).mean(dims=dims)
+            if self.sync and dist.in_mpi():
+                xmean = xmean.mpi_all_reduce("mean")
+                x2mean = x2mean.mpi_all_reduce("mean")
+            xvar = (x2mean - xmean * xmean).maximum(0.0)
+            w = self.weight / (xvar + self.eps).sqrt()
+            b = self.bias - xmean * w
+            return x * w.broadcast(x, dims) + b.broadcast(x, dims)
+        w = self.weight / (self.running_var + self.eps).sqrt()
+        b = self.bias - self.running_mean * w
+        return x * w.broadcast(x, dims) + b.broadcast(x, dims)
+
+
+BatchNorm2d = BatchNorm
+
+
+class ReLU(Module):
+    def execute(self, x):
+        return relu(x)
+
+
+def max_pool2x2(x):
+    """2x2 stride-2 max pooling through reindex + reduce(max) (the reindex path of python/jittor/pool.py)."""
+    x = to_var(x)
+    N, C, H, W = x.shape
+    xx = x.reindex([N, C, H // 2, W // 2, 2, 2], ["i0", "i1", "i2*2+i4", "i3*2+i5"])
+    return xx.reduce("maximum", [4, 5])
