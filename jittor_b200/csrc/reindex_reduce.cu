@@ -17,7 +17,7 @@
 
 namespace b200jt {
 
-constexpr int kPrivThreads = 512;
+constexpr int kPrivThreads = 1024;
 constexpr int kPrivMaxSmemBytes = 160 * 1024;
 constexpr int64_t kPrivMaxBinBytes = 32 * 1024;     // bins*sizeof(T) up to which the privatised path is used
 constexpr int kPrivGrid = kNumSMs;                  // one CTA per SM (dynamic smem limits residency to 1)
@@ -113,81 +113,165 @@ rr_affine_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_consta
     }
 }
 
-// ---- direct scatter, many bins: x[e0[i]] = op(x[e0[i]], y[i]) --------------------------------------
+// Fast form of the injective path when every index is provably in range: the x offset is one linear
+// function of the (merged) loop coordinates, off = c + sum_j F[j]*i_j. A thread owns 4 consecutive y
+// elements whose x offsets are off + delta[0..3] with a host-computed constant delta table (the 4 elements
+// stay inside the trailing loop axes), so the only index arithmetic is one 32-bit div/mod per outer axis.
+struct RRFlatArgs {
+    int32_t nd;                    // outer (merged) axes
+    uint32_t shape[kMaxDims];
+    int64_t F[kMaxDims];
+    int64_t c;
+    int64_t delta[4];
+    int32_t store_mode;            // 0 scalar, 1 two 8-byte stores, 2 one 16-byte store
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rr_flat_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant__ RRFlatArgs A,
+               uint32_t n_vec, int op, T init) {
+    static_assert(sizeof(T) == 4, "4-byte elements");
+    for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
+        uint4 raw = __ldcs(reinterpret_cast<const uint4*>(y) + v);
+        T val[4]; memcpy(val, &raw, 16);
+        uint32_t r = v;
+        int64_t off = A.c;
+#pragma unroll 1
+        for (int d = A.nd - 1; d >= 0; d--) {
+            const uint32_t s = A.shape[d];
+            const uint32_t q = r / s;
+            off += A.F[d] * (int64_t)(r - q * s);
+            r = q;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) val[e] = apply_op<T>(op, init, val[e]);
+        if (A.store_mode == 2) {
+            memcpy(&raw, val, 16);
+            __stcs(reinterpret_cast<uint4*>(x + off + A.delta[0]), raw);
+        } else if (A.store_mode == 1) {
+            uint2 lo, hi; memcpy(&lo, val, 8); memcpy(&hi, val + 2, 8);
+            __stcs(reinterpret_cast<uint2*>(x + off + A.delta[0]), lo);
+            __stcs(reinterpret_cast<uint2*>(x + off + A.delta[2]), hi);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) x[off + A.delta[e]] = val[e];
+        }
+    }
+}
+
+// ---- scatter through an index array: x[e0[i]] = op(x[e0[i]], y[i]) ----------------------------------
+// Loads are issued UNROLL vectors ahead so that enough bytes are in flight per SM to cover HBM latency.
+// f(bin, value, valid) is called by all 32 lanes of a warp together (valid == false on lanes past the end), so
+// that warp-collective code may run inside it.
+template <typename T, typename E, int VEC, int UNROLL, typename F>
+__device__ __forceinline__ void for_each_pair(const T* __restrict__ y, const E* __restrict__ idx, int64_t n, F&& f) {
+    const int64_t n_vec = n / VEC;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int lane = threadIdx.x & 31;
+    for (int64_t w0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x - lane); w0 < n_vec; w0 += stride * UNROLL) {
+        const int64_t v0 = w0 + lane;
+        __align__(16) T val[UNROLL][VEC];
+        __align__(16) E ind[UNROLL][VEC];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const int64_t v = v0 + u * stride;
+            if (v < n_vec) {
+                if constexpr (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(val[u]) = __ldcs(reinterpret_cast<const uint4*>(y) + v);
+                else {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) val[u][e] = y[v * VEC + e];
+                }
+                if constexpr (VEC * sizeof(E) == 16) *reinterpret_cast<uint4*>(ind[u]) = __ldcs(reinterpret_cast<const uint4*>(idx) + v);
+                else if constexpr (VEC * sizeof(E) == 32) {
+                    *reinterpret_cast<uint4*>(ind[u]) = __ldcs(reinterpret_cast<const uint4*>(idx) + 2 * v);
+                    *reinterpret_cast<uint4*>(ind[u] + VEC / 2) = __ldcs(reinterpret_cast<const uint4*>(idx) + 2 * v + 1);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) ind[u][e] = idx[v * VEC + e];
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) { ind[u][e] = (E)-1; val[u][e] = T(); }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            if (w0 + u * stride < n_vec) {                       // warp-uniform
+                const bool valid = v0 + u * stride < n_vec;
+#pragma unroll
+                for (int e = 0; e < VEC; e++) f((int64_t)ind[u][e], val[u][e], valid);
+            }
+        }
+    }
+    for (int64_t w = n_vec * VEC + blockIdx.x * (int64_t)blockDim.x + (threadIdx.x - lane); w < n; w += stride) {
+        const int64_t i = w + lane;
+        const bool valid = i < n;
+        f(valid ? (int64_t)idx[i] : (int64_t)-1, valid ? y[i] : T(), valid);
+    }
+}
+
+// Many bins: the bins live in L2 and every element costs one red.global. A per-CTA direct-mapped
+// shared-memory cache (slot = bin mod SLOTS, claimed by the first bin that arrives) absorbs the hot
+// head of skewed index distributions, whose same-address atomics would otherwise serialise in L2; the cache is
+// flushed with one atomic per used slot.
+constexpr int kCacheThreads = 1024;
+constexpr int kCacheSlots = 4096;
+
+template <typename T, typename E, int VEC>
+__global__ void __launch_bounds__(kCacheThreads, 2)
+rr_direct_cached_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __restrict__ x,
+                        int64_t n, int64_t bins, int op, T init) {
+    __shared__ int32_t tag[kCacheSlots];
+    __shared__ T acc[kCacheSlots];
+    for (int i = threadIdx.x; i < kCacheSlots; i += blockDim.x) { tag[i] = -1; acc[i] = init; }
+    __syncthreads();
+    for_each_pair<T, E, VEC, 2>(y, idx, n, [&](int64_t b, T v, bool valid) {
+        if (!valid || b < 0 || b >= bins) return;
+        const int s = (int)(b & (kCacheSlots - 1));
+        int32_t t = *reinterpret_cast<volatile int32_t*>(tag + s);
+        if (t == -1) { t = atomicCAS(tag + s, -1, (int32_t)b); if (t == -1) t = (int32_t)b; }
+        if (t == (int32_t)b) atomic_apply<T>(acc + s, v, op);
+        else atomic_apply<T>(x + b, v, op);
+    });
+    __syncthreads();
+    for (int i = threadIdx.x; i < kCacheSlots; i += blockDim.x) {
+        const int32_t t = tag[i];
+        if (t >= 0) atomic_apply<T>(x + t, acc[i], op);
+    }
+}
+
+// Plain variant (2^31 bins or more, or element types without a cache specialisation).
 template <typename T, typename E, int VEC>
 __global__ void __launch_bounds__(256)
 rr_direct_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __restrict__ x,
                  int64_t n, int64_t bins, int op) {
-    const int64_t n_vec = n / VEC;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n_vec; v += stride) {
-        __align__(16) T val[VEC];
-        __align__(16) E ind[VEC];
-        if constexpr (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(val) = __ldcs(reinterpret_cast<const uint4*>(y) + v);
-        else {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) val[e] = y[v * VEC + e];
-        }
-        if constexpr (VEC * sizeof(E) == 16) *reinterpret_cast<uint4*>(ind) = __ldcs(reinterpret_cast<const uint4*>(idx) + v);
-        else {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) ind[e] = idx[v * VEC + e];
-        }
-#pragma unroll
-        for (int e = 0; e < VEC; e++) {
-            int64_t b = (int64_t)ind[e];
-            if (b >= 0 && b < bins) atomic_apply<T>(x + b, val[e], op);
-        }
-    }
-    // tail
-    for (int64_t i = n_vec * VEC + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) {
-        int64_t b = (int64_t)idx[i];
-        if (b >= 0 && b < bins) atomic_apply<T>(x + b, y[i], op);
-    }
+    for_each_pair<T, E, VEC, 2>(y, idx, n, [&](int64_t b, T v, bool valid) {
+        if (valid && b >= 0 && b < bins) atomic_apply<T>(x + b, v, op);
+    });
 }
 
 // ---- privatised scatter, few bins ------------------------------------------------------------------
-// smem layout: R replicas of `bins` elements; lane l of a warp updates replica (l % R).
+// smem layout: R replicas of `bins` elements at a stride of bins+1 (so that the replicas of one bin sit in
+// different banks); lane l of a warp updates replica (l % R), which spreads the same-bin lanes of skewed inputs.
 template <typename T, typename E, int VEC>
 __global__ void __launch_bounds__(kPrivThreads, 1)
 rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __restrict__ partial,
                      int64_t n, int bins, int replicas, int op, bool is_bool) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sm = reinterpret_cast<T*>(smem_raw);
+    const int rstride = bins + 1;
     const T init = init_value<T>(op, is_bool);
-    for (int i = threadIdx.x; i < bins * replicas; i += blockDim.x) sm[i] = init;
+    for (int i = threadIdx.x; i < rstride * replicas; i += blockDim.x) sm[i] = init;
     __syncthreads();
-    T* mine = sm + (threadIdx.x % replicas) * bins;
-    const int64_t n_vec = n / VEC;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n_vec; v += stride) {
-        __align__(16) T val[VEC];
-        __align__(16) E ind[VEC];
-        if constexpr (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(val) = __ldcs(reinterpret_cast<const uint4*>(y) + v);
-        else {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) val[e] = y[v * VEC + e];
-        }
-        if constexpr (VEC * sizeof(E) == 16) *reinterpret_cast<uint4*>(ind) = __ldcs(reinterpret_cast<const uint4*>(idx) + v);
-        else {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) ind[e] = idx[v * VEC + e];
-        }
-#pragma unroll
-        for (int e = 0; e < VEC; e++) {
-            int64_t b = (int64_t)ind[e];
-            if (b >= 0 && b < bins) atomic_apply<T>(mine + b, val[e], op);
-        }
-    }
-    for (int64_t i = n_vec * VEC + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) {
-        int64_t b = (int64_t)idx[i];
-        if (b >= 0 && b < bins) atomic_apply<T>(mine + b, y[i], op);
-    }
+    T* mine = sm + (threadIdx.x % replicas) * rstride;
+    for_each_pair<T, E, VEC, 4>(y, idx, n, [&](int64_t b, T v, bool valid) {
+        if (valid && b >= 0 && b < bins) atomic_apply<T>(mine + b, v, op);
+    });
     __syncthreads();
     // fold the replicas in fixed order and publish this CTA's row
     for (int b = threadIdx.x; b < bins; b += blockDim.x) {
         T acc = sm[b];
-        for (int r = 1; r < replicas; r++) acc = apply_op<T>(op, acc, sm[r * bins + b]);
+        for (int r = 1; r < replicas; r++) acc = apply_op<T>(op, acc, sm[r * rstride + b]);
         partial[(int64_t)blockIdx.x * bins + b] = acc;
     }
 }
@@ -265,15 +349,69 @@ static RRPlan make_plan(const b200jt_tensor* y, const b200jt_tensor* x, int op, 
         (P.extras[0].dtype == B200JT_INT32 || P.extras[0].dtype == B200JT_INT64) && es >= 4) {
         if (bins * es <= kPrivMaxBinBytes && numel(y) >= (1 << 16)) {
             plan.path = RRPlan::PRIVATISED;
-            int r = (int)(kPrivMaxSmemBytes / (bins * es));
+            int r = (int)(kPrivMaxSmemBytes / ((bins + 1) * es));
             plan.replicas = r >= 8 ? 8 : r >= 4 ? 4 : r >= 2 ? 2 : 1;
-            plan.smem = (size_t)plan.replicas * bins * es;
+            plan.smem = (size_t)plan.replicas * (bins + 1) * es;
             plan.workspace = (size_t)kPrivGrid * bins * es;
         } else {
             plan.path = RRPlan::DIRECT;
         }
     }
     return plan;
+}
+
+// Builds the flat-offset description used by rr_flat_kernel; false if 4 consecutive y elements can leave the
+// trailing axes (then the odometer kernel is used).
+static bool make_flat_args(const IndexProgram& P, uintptr_t xbase, size_t es, RRFlatArgs* A) {
+    memset(A, 0, sizeof(*A));
+    int64_t xs[kMaxDims]; int64_t st = 1;
+    for (int d = P.ndim_x - 1; d >= 0; d--) { xs[d] = st; st *= P.x_shape[d]; }
+    int64_t F[kMaxDims], shp[kMaxDims]; int n = 0;
+    A->c = 0;
+    for (int d = 0; d < P.ndim_x; d++) A->c += P.c0[d] * xs[d];
+    for (int j = 0; j < P.ndim_loop; j++) {
+        int64_t f = 0;
+        for (int d = 0; d < P.ndim_x; d++) f += P.coef[d][j] * xs[d];
+        if (P.loop_shape[j] == 1) continue;
+        if (n && F[n - 1] == f * P.loop_shape[j]) { shp[n - 1] *= P.loop_shape[j]; F[n - 1] = f; }   // merge
+        else { F[n] = f; shp[n] = P.loop_shape[j]; n++; }
+    }
+    if (n == 0) return false;
+    // fold trailing axes until their product is a multiple of 4 elements
+    int64_t prod = 1; int t = n;
+    while (t > 0 && prod % 4 != 0) { t--; prod *= shp[t]; }
+    if (prod % 4 != 0) return false;
+    if (t == n - 1) {
+        // the inner axis alone holds whole vectors
+        for (int e = 0; e < 4; e++) A->delta[e] = e * F[n - 1];
+        shp[n - 1] /= 4; F[n - 1] *= 4;
+        t = n;
+    } else {
+        if (prod != 4) return false;             // the vector must cover the folded axes exactly
+        for (int e = 0; e < 4; e++) {
+            int64_t r = e, off = 0;
+            for (int j = n - 1; j >= t; j--) { off += (r % shp[j]) * F[j]; r /= shp[j]; }
+            A->delta[e] = off;
+        }
+    }
+    A->nd = 0;
+    for (int j = 0; j < t; j++) {
+        if (shp[j] == 1) continue;
+        if (shp[j] >= (1LL << 32)) return false;
+        A->shape[A->nd] = (uint32_t)shp[j]; A->F[A->nd] = F[j]; A->nd++;
+    }
+    // store mode: alignment must hold for every vector -> every F and c + delta must keep it
+    auto aligned_all = [&](int64_t first, int bytes) {
+        const int64_t k = bytes / (int64_t)es;
+        if ((xbase % bytes) != 0 || ((A->c + first) % k) != 0) return false;
+        for (int j = 0; j < A->nd; j++) if (A->F[j] % k != 0) return false;
+        return true;
+    };
+    const int64_t* d = A->delta;
+    if (d[1] == d[0] + 1 && d[2] == d[0] + 2 && d[3] == d[0] + 3 && aligned_all(d[0], 16)) A->store_mode = 2;
+    else if (d[1] == d[0] + 1 && d[3] == d[2] + 1 && aligned_all(d[0], 8) && aligned_all(d[2], 8)) A->store_mode = 1;
+    else A->store_mode = 0;
+    return true;
 }
 
 template <typename T>
@@ -306,6 +444,17 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         B200JT_LAUNCH_CHECK();
     }
     if (n == 0 || bins == 0) return 0;
+    if (plan.path == RRPlan::INJECTIVE && plan.in_range && sizeof(T) == 4 && n % 4 == 0 && n / 4 < (1LL << 32) &&
+        ((uintptr_t)yp % 16) == 0) {
+        RRFlatArgs FA;
+        if (make_flat_args(P, (uintptr_t)xp, sizeof(T), &FA)) {
+            if constexpr (sizeof(T) == 4) {
+                rr_flat_kernel<T><<<grid_for(n / 4, 256), 256, 0, st>>>(yp, xp, FA, (uint32_t)(n / 4), op, init_value<T>(op, is_bool));
+                B200JT_LAUNCH_CHECK();
+                return 0;
+            }
+        }
+    }
     if (plan.path == RRPlan::INJECTIVE) {
         RRAffineArgs A; memset(&A, 0, sizeof(A));
         A.ndim_loop = P.ndim_loop; A.ndim_x = P.ndim_x;
@@ -322,6 +471,21 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         const bool e64 = P.extras[0].dtype == B200JT_INT64;
         constexpr int VEC = 16 / sizeof(T);
         const bool aligned = ((uintptr_t)yp % 16 == 0) && ((uintptr_t)P.extras[0].ptr % 16 == 0);
+        if constexpr (sizeof(T) == 4 || sizeof(T) == 8) {
+            if (bins < (1LL << 31)) {
+                const T init = init_value<T>(op, is_bool);
+                const unsigned grid = 2 * kNumSMs;
+                if (e64) {
+                    if (aligned) rr_direct_cached_kernel<T, int64_t, VEC><<<grid, kCacheThreads, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op, init);
+                    else rr_direct_cached_kernel<T, int64_t, 1><<<grid, kCacheThreads, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op, init);
+                } else {
+                    if (aligned) rr_direct_cached_kernel<T, int32_t, VEC><<<grid, kCacheThreads, 0, st>>>(yp, (const int32_t*)P.extras[0].ptr, xp, n, bins, op, init);
+                    else rr_direct_cached_kernel<T, int32_t, 1><<<grid, kCacheThreads, 0, st>>>(yp, (const int32_t*)P.extras[0].ptr, xp, n, bins, op, init);
+                }
+                B200JT_LAUNCH_CHECK();
+                return 0;
+            }
+        }
         const unsigned grid = grid_for(n / VEC + 1, 256);
         if (e64) {
             if (aligned) rr_direct_kernel<T, int64_t, VEC><<<grid, 256, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op);

@@ -126,6 +126,12 @@ class Var:
     def fetch_sync(self):
         return self.numpy()
 
+    def fetch_into(self, host, non_blocking=True):
+        """Copies the value into a preallocated host torch tensor (pinned memory makes the copy a DMA that
+        can overlap later launches); call torch.cuda.current_stream().synchronize() before reading it."""
+        host.view(-1).copy_(self.torch().reshape(-1), non_blocking=non_blocking)
+        return host
+
     def item(self):
         if self.numel() != 1:
             raise ValueError("item() needs a Var with exactly one element")
