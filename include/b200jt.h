@@ -77,6 +77,22 @@ int b200jt_reindex_reduce(const b200jt_tensor* y, const b200jt_tensor* x, const 
                           const b200jt_tensor* extras, int n_extras,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same operation as b200jt_reindex_reduce for callers that may not allocate device memory when they call
+ * (inside an allocator callback, in a loop whose memory pool is frozen after start-up, behind a plugin
+ * interface without an allocation hook). It has no counterpart in the reference. The scratch rows the
+ * few-bins scatter needs are kept in a 4 MiB array that is part of the library image on every GPU that loads
+ * it; b200jt_reindex_reduce_noalloc_max_scratch() returns that size. A scatter whose plan needs more
+ * (float32 bins beyond about 7000) is refused with status -3 and a message naming both sizes; nothing is
+ * allocated or freed on any path. The first call on a device looks up the array's device address, so make
+ * that call before any stream capture. All calls share the one array and its contents persist between calls
+ * (every launch overwrites all rows it reads, nothing needs zeroing), therefore two calls that may overlap on
+ * the GPU -- different streams, or threads -- race and must be serialised by the caller. */
+size_t b200jt_reindex_reduce_noalloc_max_scratch(void);
+int b200jt_reindex_reduce_noalloc(const b200jt_tensor* y, const b200jt_tensor* x, const char* op,
+                                  const char* const* indexes, int n_indexes,
+                                  const char* const* overflow_conditions, int n_conditions,
+                                  const b200jt_tensor* extras, int n_extras, void* stream);
+
 /* z[i] = x[i with the axes of bcast_mask zeroed]; x is passed with z's rank (size-1 axes where broadcast).
  * Replaces BroadcastToOp(Var* x, NanoVector shape, uint dims_mask, uint keepdims_mask)
  * python/jittor/src/ops/broadcast_to_op.h:90, jit_run python/jittor/src/ops/broadcast_to_op.cc:177-194. */

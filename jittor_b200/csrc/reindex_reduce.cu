@@ -562,3 +562,54 @@ extern "C" int b200jt_reindex_reduce(const b200jt_tensor* y, const b200jt_tensor
     }
     return fail(-1, "b200jt_reindex_reduce: unsupported dtype");
 }
+
+// ---- allocation-free variant ----------------------------------------------------------------------
+// Some callers cannot hand over a workspace because they are not allowed to allocate device memory at
+// the point of the call: code running inside a memory-pool callback, a real-time loop whose allocator is
+// frozen after start-up, or a host runtime that gives a plugin no allocation hook at all. For them the
+// scratch rows of the privatised scatter live in a fixed array inside the library image. Every GPU that
+// loads the library carries these 4 MiB until the process exits.
+namespace b200jt {
+
+constexpr size_t kStaticScratchBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_rr_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; the kernels need its device address, which is looked up once per
+// device (with that device current) and cached.
+static int static_scratch_ptr(void** out) {
+    int dev = 0;
+    B200JT_CUDA(cudaGetDevice(&dev));
+    B200JT_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "device ordinal out of range");
+    if (!g_scratch_addr[dev]) {
+        void* p = nullptr;
+        B200JT_CUDA(cudaGetSymbolAddress(&p, g_rr_static_scratch));
+        g_scratch_addr[dev] = p;
+    }
+    *out = g_scratch_addr[dev];
+    return 0;
+}
+
+}  // namespace b200jt
+
+extern "C" size_t b200jt_reindex_reduce_noalloc_max_scratch(void) { return b200jt::kStaticScratchBytes; }
+
+extern "C" int b200jt_reindex_reduce_noalloc(const b200jt_tensor* y, const b200jt_tensor* x, const char* op,
+                                             const char* const* indexes, int n_indexes,
+                                             const char* const* overflow_conditions, int n_conditions,
+                                             const b200jt_tensor* extras, int n_extras, void* stream) {
+    IndexProgram P; int opc; RRPlan plan;
+    int rc = prepare(y, x, op, indexes, n_indexes, overflow_conditions, n_conditions, extras, n_extras, &P, &opc, &plan);
+    if (rc) return rc;
+    if (plan.workspace > kStaticScratchBytes)
+        return fail(-3, "b200jt_reindex_reduce_noalloc: this scatter needs " + std::to_string(plan.workspace) +
+                        " bytes of scratch, the built-in array holds " + std::to_string(kStaticScratchBytes) +
+                        "; use b200jt_reindex_reduce with a caller workspace");
+    void* scratch = nullptr;
+    rc = static_scratch_ptr(&scratch);
+    if (rc) return rc;
+    return b200jt_reindex_reduce(y, x, op, indexes, n_indexes, overflow_conditions, n_conditions, extras, n_extras,
+                                 scratch, kStaticScratchBytes, stream);
+}
