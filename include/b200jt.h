@@ -142,6 +142,12 @@ size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_tensor* b, c
 int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
                   int trans_a, int trans_b, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Status word of the tensor-core kernels (matmul, conv2d): every wait inside them is bounded; if one expires the
+ * kernel stops cleanly and records which (1 producer, 2 accumulator hand-back, 3 operand arrival, 4 accumulator
+ * ready). Returns 0 if none did since the last call, and clears the word. Synchronises the device. It plays the
+ * role of the reference's checkCudaErrors after a relay (python/jittor/extern/cuda/cublas/ops/cublas_matmul_op.cc:117). */
+int b200jt_device_status(void);
+
 /* y = conv2d(x, w), NCHW ("abcd") x, OIHW w, fp32 accumulation. Replaces the relay
  * CudnnConvOp(Var* x, Var* w, int strideh, int stridew, int paddingh, int paddingw, int dilationh, int dilationw,
  *             int groups, string xformat, string wformat, string yformat),

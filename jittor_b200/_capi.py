@@ -64,6 +64,7 @@ SIGNATURES = [
     ("b200jt_layer_norm", _i, [_TP, _TP, _TP, _TP, _d, _vp]),
     ("b200jt_matmul_workspace", _sz, [_TP, _TP, _TP, _i, _i]),
     ("b200jt_matmul", _i, [_TP, _TP, _TP, _i, _i, _vp, _sz, _vp]),
+    ("b200jt_device_status", _i, []),
     ("b200jt_conv2d_workspace", _sz, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i]),
     ("b200jt_conv2d", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i, _FP, _vp, _sz, _vp]),
     ("b200jt_bn_stats", _i, [_TP, _FP, _vp]),

@@ -5,14 +5,30 @@
 
 using namespace b200jt;
 
+static bool matmul_dims(const b200jt_tensor* a, const b200jt_tensor* b, int trans_a, int trans_b, int64_t* M, int64_t* N, int64_t* K) {
+    if (!valid_tensor(a) || !valid_tensor(b) || a->ndim != 2 || b->ndim != 2) return false;
+    *M = trans_a ? a->shape[1] : a->shape[0]; *K = trans_a ? a->shape[0] : a->shape[1];
+    *N = trans_b ? b->shape[0] : b->shape[1];
+    return (trans_b ? b->shape[1] : b->shape[0]) == *K;
+}
+
 extern "C" size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c, int trans_a, int trans_b) {
-    (void)a; (void)b; (void)c; (void)trans_a; (void)trans_b;
+    int64_t M, N, K;
+    if (!matmul_dims(a, b, trans_a, trans_b, &M, &N, &K) || !valid_tensor(c)) return 0;
+    if (a->dtype == B200JT_BFLOAT16 && matmul_tc_supported(M, N, K, a->ptr, b->ptr, c->ptr))
+        return matmul_tc_workspace(M, N, K, trans_a != 0, trans_b != 0);
     return 0;
+}
+
+/* Status word of the tensor-core kernels: 0, or the code of the first bounded wait that expired since the last call
+ * (1 producer, 2 accumulator hand-back, 3 operand arrival, 4 accumulator ready). Synchronises the device. */
+extern "C" int b200jt_device_status(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return tc_status_fetch_and_clear();
 }
 
 extern "C" int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
                              int trans_a, int trans_b, void* workspace, size_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     B200JT_CHECK_ARG(valid_tensor(a) && valid_tensor(b) && valid_tensor(c), "invalid tensor descriptor");
     B200JT_CHECK_ARG(a->ndim == 2 && b->ndim == 2 && c->ndim == 2, "matmul takes 2-D tensors");
     B200JT_CHECK_ARG(a->dtype == b->dtype && a->dtype == c->dtype &&
@@ -23,6 +39,11 @@ extern "C" int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, con
     B200JT_CHECK_ARG(c->shape[0] == M && c->shape[1] == N, "c has the wrong shape " + shape_str(c));
     if (M == 0 || N == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == B200JT_BFLOAT16 && matmul_tc_supported(M, N, K, a->ptr, b->ptr, c->ptr)) {
+        const size_t need = matmul_tc_workspace(M, N, K, trans_a != 0, trans_b != 0);
+        B200JT_CHECK_ARG(workspace_bytes >= need && (need == 0 || workspace), "workspace too small: need " + std::to_string(need) + " bytes");
+        return matmul_tc(a->ptr, b->ptr, c->ptr, M, N, K, trans_a != 0, trans_b != 0, workspace, st);
+    }
     return matmul_simt(a->ptr, b->ptr, c->ptr, a->dtype, M, N, K, trans_a != 0, trans_b != 0, st);
 }
 

@@ -10,6 +10,13 @@ struct ConvShape {
 
 int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int64_t N, int64_t K,
                 bool trans_a, bool trans_b, cudaStream_t st);
+// tcgen05 path (gemm_tcgen05.cu)
+bool matmul_tc_supported(int64_t M, int64_t N, int64_t K, const void* a, const void* b, const void* c);
+size_t matmul_tc_workspace(int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b);
+int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b,
+              void* workspace, cudaStream_t st);
+int tc_status_fetch_and_clear();
+
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
 
 }  // namespace b200jt

@@ -1,0 +1,359 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] . Bt[N,K]^T, fp32 accumulation in TMEM.
+//
+// The broadcast-multiply-sum matmul of the reference (python/jittor/nn.py:157-159) is a dense contraction; its
+// relay is cublasGemmEx (python/jittor/extern/cuda/cublas/ops/cublas_matmul_op.cc:117-123). Here it is one
+// persistent, warp-specialised kernel:
+//   warp 0     TMA producer: cp.async.bulk.tensor 2-D loads of 128x64 (A) and 256x64 (Bt) bf16 tiles, 128-byte
+//              swizzle, into a 4-stage shared-memory ring (192 KB), completion on mbarriers;
+//   warp 1     MMA issuer: one lane issues tcgen05.mma.cta_group::1.kind::f16 (M=128, N=256, K=16) on shared-memory
+//              descriptors; accumulators live in TMEM, 2 x 256 columns so the next tile starts while the previous
+//              one is drained; tcgen05.commit releases ring slots / publishes accumulators;
+//   warps 2-5  epilogue: tcgen05.ld (32 lanes x 32 columns), fp32 -> bf16, 16-byte global stores.
+// Tiles are scheduled statically (tile = blockIdx.x + i*gridDim.x) in groups of 8 tile-rows for L2 reuse; one CTA
+// per SM. Ragged M/N/K edges rely on TMA zero fill and masked stores. No cluster launch and no multicast.
+// Every mbarrier wait is bounded: on expiry the CTA records a status word, stops issuing, drains and frees TMEM.
+#include "gemm_simt.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace b200jt {
+
+namespace tc {
+
+constexpr int BM = 128, BN = 256, BK = 64;          // BK * 2 B = 128 B = swizzle width
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;                        // 6 warps
+constexpr uint32_t WAIT_LIMIT = 1u << 22;           // polls (with back-off) before a wait gives up: ~1 s
+
+__device__ int g_status = 0;                        // 0 ok; otherwise code of the first wait that gave up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and raises the CTA's abort flag) when the limit is reached or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    *abort_flag = code;
+    atomicCAS(&g_status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// K-major operand tile in the 128-byte-swizzle layout TMA writes: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);               // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                 // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                                 // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                                 // SWIZZLE_128B
+    return d;
+}
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, N and M encoded as N>>3, M>>4.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
+struct Tiles {
+    int tiles_m, tiles_n, total;
+    __device__ __forceinline__ void coords(int t, int& m, int& n) const {
+        constexpr int G = 8;                                   // tile-rows per group (L2 reuse of the Bt tiles)
+        const int per_group = G * tiles_n;
+        const int g = t / per_group, r = t - g * per_group;
+        const int rows = min(G, tiles_m - g * G);
+        m = g * G + r % rows;
+        n = r / rows;
+    }
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 __nv_bfloat16* __restrict__ c, int M, int N, int K) {
+    extern __shared__ unsigned char smem_raw[];
+    // operand tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                 // [STAGES] TMA -> MMA
+    uint64_t* empty = bars + STAGES;       // [STAGES] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;      // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * STAGES + 2; // [2] epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    Tiles T;
+    T.tiles_m = (M + BM - 1) / BM; T.tiles_n = (N + BN - 1) / BN; T.total = T.tiles_m * T.tiles_n;
+    const int k_blocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // all 512 TMEM columns: two 128 x 256 fp32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x) {
+                int tm, tn; T.coords(t, tm, tn);
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 1))) break;
+                    unsigned char* sa = smem + stage * STAGE_BYTES;
+                    mbar_expect_tx(full + stage, STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, full + stage, kb * BK, tm * BM);
+                    tma_load_2d(sa + A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // give copies that are already in flight a bounded chance to land before the CTA goes away
+                for (int s = 0; s < STAGES; s++)
+                    for (uint32_t i = 0; i < 4096 && !mbar_try(full + s, 0) && !mbar_try(full + s, 1); i++) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x, it++) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!(ok = mbar_wait(acc_empty + buf, acc_phase ^ 1, abort_flag, 2))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!(ok = mbar_wait(full + stage, phase, abort_flag, 3))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // advancing K by 16 bf16 = 32 B inside the swizzled 128-byte row: +2 in 16-byte units
+                        umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(empty + stage);                 // slot reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(acc_full + buf);             // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lane quadrants (warp % 4) ----------------
+        const int quad = warp & 3;
+        int it = 0;
+        bool ok = true;
+        const bool vec_ok = (N % 8 == 0) && (((uintptr_t)c & 15) == 0);
+        for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x, it++) {
+            int tm, tn; T.coords(t, tm, tn);
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            ok = mbar_wait(acc_full + buf, acc_phase, abort_flag, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = tm * BM + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+            __nv_bfloat16* crow = c + (int64_t)row * N + (int64_t)tn * BN;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ch++) {
+                uint32_t r[32];
+                tmem_ld32(taddr + ch * 32, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = tn * BN + ch * 32;
+                if (row < M && col0 < N) {
+                    if (vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            uint4 v;
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                            for (int e = 0; e < 4; e++)
+                                h[e] = __floats2bfloat162_rn(__uint_as_float(r[q * 8 + 2 * e]), __uint_as_float(r[q * 8 + 2 * e + 1]));
+                            *reinterpret_cast<uint4*>(crow + ch * 32 + q * 8) = v;
+                        }
+                    } else {
+                        for (int e = 0; e < 32 && col0 + e < N; e++) crow[ch * 32 + e] = __float2bfloat16(__uint_as_float(r[e]));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + buf);
+        }
+    }
+    // ---------------- teardown ----------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+// ---- bf16 transpose: out[c, r] = in[r, c] (used to bring an operand into K-major form) -------------------
+__global__ void __launch_bounds__(256)
+transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn) {
+    __shared__ __nv_bfloat16 tile[64][66];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;          // 32 x 8
+    for (int i = ty; i < 64; i += 8) {
+        const int r = r0 + i;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int cc = c0 + tx * 2 + j;
+            tile[i][tx * 2 + j] = (r < R && cc < Cn) ? in[(int64_t)r * Cn + cc] : __float2bfloat16(0.f);
+        }
+    }
+    __syncthreads();
+    for (int i = ty; i < 64; i += 8) {
+        const int cc = c0 + i;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int r = r0 + tx * 2 + j;
+            if (cc < Cn && r < R) out[(int64_t)cc * R + r] = tile[tx * 2 + j][i];
+        }
+    }
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+    });
+    return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with a {BK, box_rows} box and 128-byte swizzle
+static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
+bool matmul_tc_supported(int64_t M, int64_t N, int64_t K, const void* a, const void* b, const void* c) {
+    // TMA: 16-byte aligned bases and row pitches (K % 8); tiny problems stay on the CUDA-core kernel
+    return K % 8 == 0 && K >= 64 && M >= 128 && N >= 64 && M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31) &&
+           ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 2 == 0) && tc::encode_fn() != nullptr;
+}
+
+size_t matmul_tc_workspace(int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b) {
+    // operands that are not K-major are transposed into the workspace first
+    size_t bytes = 0;
+    if (trans_a) bytes += (size_t)M * K * 2;
+    if (!trans_b) bytes += (size_t)N * K * 2;
+    return bytes;
+}
+
+int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b,
+              void* workspace, cudaStream_t st) {
+    using namespace tc;
+    const __nv_bfloat16* ak = (const __nv_bfloat16*)a;      // [M, K]
+    const __nv_bfloat16* bk = (const __nv_bfloat16*)b;      // [N, K]
+    unsigned char* ws = (unsigned char*)workspace;
+    if (trans_a) {   // a is [K, M]
+        dim3 g((unsigned)((M + 63) / 64), (unsigned)((K + 63) / 64));
+        transpose_bf16_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)a, (__nv_bfloat16*)ws, (int)K, (int)M);
+        ak = (const __nv_bfloat16*)ws; ws += (size_t)M * K * 2;
+    }
+    if (!trans_b) {  // b is [K, N]
+        dim3 g((unsigned)((N + 63) / 64), (unsigned)((K + 63) / 64));
+        transpose_bf16_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)b, (__nv_bfloat16*)ws, (int)K, (int)N);
+        bk = (const __nv_bfloat16*)ws;
+    }
+    B200JT_LAUNCH_CHECK();
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, ak, M, K, BM) || !make_map(&mb, bk, N, K, BN))
+        return fail(-4, "matmul: cuTensorMapEncodeTiled failed");
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    B200JT_CUDA(attr_err);
+    const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+    const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+    gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+int tc_status_fetch_and_clear() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc::g_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) { int z = 0; cudaMemcpyToSymbol(tc::g_status, &z, sizeof(int)); }
+    return v;
+}
+
+}  // namespace b200jt

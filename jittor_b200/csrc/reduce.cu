@@ -97,14 +97,26 @@ __device__ __forceinline__ C shfl_down_c(C v, int delta) {
     }
 }
 
+// Typed element access: TX = void selects the run-time dtype switch, otherwise a plain typed load.
+template <typename TX, typename C>
+__device__ __forceinline__ C load_x(const void* x, int xdt, int64_t off) {
+    if constexpr (std::is_same<TX, void>::value) return load_as<C>(x, xdt, off);
+    else if constexpr (std::is_same<TX, __nv_bfloat16>::value) return (C)__bfloat162float(((const __nv_bfloat16*)x)[off]);
+    else return (C)((const TX*)x)[off];
+}
+
 // One CTA per (output, split). out: y (final, dtype ydt) when !to_partial, else partial[o*split + s] in class C.
-template <typename C>
+// The reduced index space is walked as (outer reduced axes) x (innermost reduced axis): threads stride the
+// innermost axis (contiguous when its stride is 1 -> coalesced, 16-byte loads for float32), the outer axes are
+// decomposed once per sweep.
+template <typename TX, typename C>
 __global__ void __launch_bounds__(256)
 reduce_row_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, int ydt,
                   const __grid_constant__ ReduceArgs A, int op, bool to_partial) {
     __shared__ C warp_acc[8];
     const C rcount = (C)A.rcount;
     const int64_t n_work = A.n_out * A.split;
+    const int64_t inner = A.rshape[A.nr - 1], istride = A.rstride[A.nr - 1];
     for (int64_t w = blockIdx.x; w < n_work; w += gridDim.x) {
         const int64_t o = w / A.split;
         const int s = (int)(w % A.split);
@@ -112,8 +124,40 @@ reduce_row_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, i
         const int64_t r0 = s * A.chunk;
         const int64_t r1 = r0 + A.chunk < A.n_red ? r0 + A.chunk : A.n_red;
         C acc = reduce_init<C>(op, ydt);
-        for (int64_t r = r0 + threadIdx.x; r < r1; r += blockDim.x)
-            acc = reduce_combine<C>(op, acc, reduce_load<C>(x, xdt, base + red_offset(A, r), op, rcount));
+        // [r0, r1) in units of the flattened reduced space; split into sweeps over the innermost axis
+        int64_t r = r0;
+        while (r < r1) {
+            const int64_t outer = r / inner, i0 = r - outer * inner;
+            const int64_t i1 = (r1 - r) < (inner - i0) ? i0 + (r1 - r) : inner;
+            int64_t obase = base;
+            if (A.nr > 1) {
+                int64_t q = outer;
+#pragma unroll 1
+                for (int d = A.nr - 2; d >= 0; d--) { const int64_t sh = A.rshape[d]; obase += (q % sh) * A.rstride[d]; q /= sh; }
+            }
+            bool done = false;
+            if constexpr (std::is_same<TX, float>::value && std::is_same<C, float>::value) {
+                const float* p = (const float*)x + obase + i0;
+                if (istride == 1 && (((uintptr_t)p) & 15) == 0 && ((i1 - i0) & 3) == 0) {
+                    const int64_t nv = (i1 - i0) >> 2;
+                    for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+                        const float4 f = __ldg(reinterpret_cast<const float4*>(p) + v);
+                        float e0 = f.x, e1 = f.y, e2 = f.z, e3 = f.w;
+                        if (op == OP_MEAN) { e0 *= rcount; e1 *= rcount; e2 *= rcount; e3 *= rcount; }
+                        acc = reduce_combine<C>(op, reduce_combine<C>(op, reduce_combine<C>(op, reduce_combine<C>(op, acc, e0), e1), e2), e3);
+                    }
+                    done = true;
+                }
+            }
+            if (!done) {
+                for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+                    C v = load_x<TX, C>(x, xdt, obase + i * istride);
+                    if (op == OP_MEAN) v = v * rcount;
+                    acc = reduce_combine<C>(op, acc, v);
+                }
+            }
+            r += i1 - i0;
+        }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) acc = reduce_combine<C>(op, acc, shfl_down_c<C>(acc, d));
         if ((threadIdx.x & 31) == 0) warp_acc[threadIdx.x >> 5] = acc;
@@ -127,8 +171,10 @@ reduce_row_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, i
     }
 }
 
-// One thread per (output, split). Partials are laid out [split][n_out].
-template <typename C>
+// One thread per (output, split); neighbouring threads own neighbouring outputs, so with the innermost axis kept
+// every step of the serial fold is a coalesced row read. The reduced coordinates advance like an odometer (no
+// division in the loop); four independent accumulators hide the load latency. Partials are laid out [split][n_out].
+template <typename TX, typename C>
 __global__ void __launch_bounds__(256)
 reduce_col_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, int ydt,
                   const __grid_constant__ ReduceArgs A, int op, bool to_partial) {
@@ -136,11 +182,44 @@ reduce_col_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, i
     const int s = blockIdx.y;
     const int64_t r0 = s * A.chunk;
     const int64_t r1 = r0 + A.chunk < A.n_red ? r0 + A.chunk : A.n_red;
+    const int nr = A.nr;
     for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < A.n_out; o += (int64_t)gridDim.x * blockDim.x) {
         const int64_t base = kept_offset(A, o);
-        C acc = reduce_init<C>(op, ydt);
-        for (int64_t r = r0; r < r1; r++)
-            acc = reduce_combine<C>(op, acc, reduce_load<C>(x, xdt, base + red_offset(A, r), op, rcount));
+        C acc0 = reduce_init<C>(op, ydt), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+        if (nr == 1) {
+            const int64_t st = A.rstride[0];
+            int64_t r = r0;
+            for (; r + 4 <= r1; r += 4) {
+                C v0 = load_x<TX, C>(x, xdt, base + r * st), v1 = load_x<TX, C>(x, xdt, base + (r + 1) * st);
+                C v2 = load_x<TX, C>(x, xdt, base + (r + 2) * st), v3 = load_x<TX, C>(x, xdt, base + (r + 3) * st);
+                if (op == OP_MEAN) { v0 *= rcount; v1 *= rcount; v2 *= rcount; v3 *= rcount; }
+                acc0 = reduce_combine<C>(op, acc0, v0); acc1 = reduce_combine<C>(op, acc1, v1);
+                acc2 = reduce_combine<C>(op, acc2, v2); acc3 = reduce_combine<C>(op, acc3, v3);
+            }
+            for (; r < r1; r++) {
+                C v = load_x<TX, C>(x, xdt, base + r * st);
+                if (op == OP_MEAN) v *= rcount;
+                acc0 = reduce_combine<C>(op, acc0, v);
+            }
+        } else {
+            int64_t idx[kMaxDims];
+            int64_t off = base, q = r0;
+#pragma unroll 1
+            for (int d = nr - 1; d >= 0; d--) { const int64_t sh = A.rshape[d]; idx[d] = q % sh; q /= sh; off += idx[d] * A.rstride[d]; }
+            for (int64_t r = r0; r < r1; r++) {
+                C v = load_x<TX, C>(x, xdt, off);
+                if (op == OP_MEAN) v *= rcount;
+                acc0 = reduce_combine<C>(op, acc0, v);
+#pragma unroll 1
+                for (int d = nr - 1; d >= 0; d--) {
+                    off += A.rstride[d];
+                    if (++idx[d] < A.rshape[d]) break;
+                    off -= A.rstride[d] * A.rshape[d];
+                    idx[d] = 0;
+                }
+            }
+        }
+        const C acc = reduce_combine<C>(op, reduce_combine<C>(op, acc0, acc1), reduce_combine<C>(op, acc2, acc3));
         if (to_partial) ((C*)out)[(int64_t)s * A.n_out + o] = acc; else store_as<C>(out, ydt, o, acc);
     }
 }
@@ -202,19 +281,30 @@ static ReducePlan make_plan(const b200jt_tensor* x, const b200jt_tensor* y, uint
     return P;
 }
 
+template <typename TX, typename C>
+static void launch_stage(const void* xp, int xdt, void* out, int ydt, const ReduceArgs& A, int op, bool part, bool row,
+                         cudaStream_t st) {
+    if (row) {
+        int64_t work = A.n_out * A.split;
+        unsigned grid = (unsigned)(work < (int64_t)kNumSMs * 16 ? work : (int64_t)kNumSMs * 16);
+        reduce_row_kernel<TX, C><<<grid, 256, 0, st>>>(xp, xdt, out, ydt, A, op, part);
+    } else {
+        dim3 grid(grid_for(A.n_out, 256), A.split);
+        reduce_col_kernel<TX, C><<<grid, 256, 0, st>>>(xp, xdt, out, ydt, A, op, part);
+    }
+}
+
 template <typename C>
 static int run_class(const b200jt_tensor* x, const b200jt_tensor* y, int op, const ReducePlan& P, void* ws, cudaStream_t st) {
     const ReduceArgs& A = P.A;
     const bool part = A.split > 1;
     void* out1 = part ? ws : y->ptr;
-    if (P.row) {
-        int64_t work = A.n_out * A.split;
-        unsigned grid = (unsigned)(work < (int64_t)kNumSMs * 16 ? work : (int64_t)kNumSMs * 16);
-        reduce_row_kernel<C><<<grid, 256, 0, st>>>(x->ptr, x->dtype, out1, y->dtype, A, op, part);
-    } else {
-        dim3 grid(grid_for(A.n_out, 256), A.split);
-        reduce_col_kernel<C><<<grid, 256, 0, st>>>(x->ptr, x->dtype, out1, y->dtype, A, op, part);
-    }
+    // typed loads for the common input dtypes of each accumulation class, run-time switch otherwise
+    if (std::is_same<C, float>::value && x->dtype == B200JT_FLOAT32) launch_stage<float, C>(x->ptr, x->dtype, out1, y->dtype, A, op, part, P.row, st);
+    else if (std::is_same<C, float>::value && x->dtype == B200JT_BFLOAT16) launch_stage<__nv_bfloat16, C>(x->ptr, x->dtype, out1, y->dtype, A, op, part, P.row, st);
+    else if (std::is_same<C, int64_t>::value && x->dtype == B200JT_INT32) launch_stage<int32_t, C>(x->ptr, x->dtype, out1, y->dtype, A, op, part, P.row, st);
+    else if (std::is_same<C, double>::value && x->dtype == B200JT_FLOAT64) launch_stage<double, C>(x->ptr, x->dtype, out1, y->dtype, A, op, part, P.row, st);
+    else launch_stage<void, C>(x->ptr, x->dtype, out1, y->dtype, A, op, part, P.row, st);
     B200JT_LAUNCH_CHECK();
     if (!part) return 0;
     // second stage over the partials (already scaled for mean)
@@ -225,8 +315,7 @@ static int run_class(const b200jt_tensor* x, const b200jt_tensor* y, int op, con
     const int cdt = class_dtype(P.cls);
     if (P.row) { B.kstride[0] = A.split; B.rstride[0] = 1; }
     else       { B.kstride[0] = 1; B.rstride[0] = A.n_out; }
-    dim3 grid(grid_for(B.n_out, 256), 1);
-    reduce_col_kernel<C><<<grid, 256, 0, st>>>(ws, cdt, y->ptr, y->dtype, B, op2, false);
+    launch_stage<C, C>(ws, cdt, y->ptr, y->dtype, B, op2, false, false, st);
     B200JT_LAUNCH_CHECK();
     return 0;
 }

@@ -12,33 +12,40 @@
 
 namespace b200jt {
 
+constexpr int kMaxTerms = 4;     // non-zero coefficients per index expression handled by the affine kernel
+
 struct AffineArgs {
     int32_t ndim_loop, ndim_x;
     int64_t loop_shape[kMaxDims];
     int64_t x_shape[kMaxDims];
-    int64_t coef[kMaxDims][kMaxDims];
     int64_t c0[kMaxDims];
+    int32_t nterm[kMaxDims];                 // sparse rows of the coefficient matrix
+    int32_t term_j[kMaxDims][kMaxTerms];
+    int64_t term_c[kMaxDims][kMaxTerms];
+    int64_t inner_coef[kMaxDims];            // coefficient of the innermost loop variable
 };
 
+// I = index type (uint32-sized arithmetic when every tensor is below 2^31 elements, as the reference's index_t).
 template <typename T, typename I, int VEC>
 __global__ void __launch_bounds__(256)
 reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_constant__ AffineArgs A,
                       int64_t n_vec, T fill) {
+    using U = typename std::conditional<sizeof(I) == 4, uint32_t, uint64_t>::type;
     const int nl = A.ndim_loop, nx = A.ndim_x;
     for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < n_vec;
          v += (int64_t)gridDim.x * blockDim.x) {
-        // vectors never straddle rows: the host picks VEC | inner
-        int64_t flat = v * VEC;
+        // vectors never straddle rows: the host picks VEC | innermost extent
+        const int64_t flat = v * VEC;
         I iv[kMaxDims];
-        int64_t r = flat;
+        U r = (U)flat;
 #pragma unroll 1
-        for (int d = nl - 1; d >= 0; d--) { int64_t s = A.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
+        for (int d = nl - 1; d >= 0; d--) { const U s = (U)A.loop_shape[d]; const U q = r / s; iv[d] = (I)(r - q * s); r = q; }
         I xid[kMaxDims];
 #pragma unroll 1
         for (int d = 0; d < nx; d++) {
-            int64_t a = A.c0[d];
-            for (int j = 0; j < nl; j++) a += A.coef[d][j] * (int64_t)iv[j];
-            xid[d] = (I)a;
+            I a = (I)A.c0[d];
+            for (int k = 0; k < A.nterm[d]; k++) a += (I)A.term_c[d][k] * iv[A.term_j[d][k]];
+            xid[d] = a;
         }
         __align__(16) T out[VEC];
 #pragma unroll
@@ -47,7 +54,7 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
             int64_t off = 0;
 #pragma unroll 1
             for (int d = 0; d < nx; d++) {
-                I id = xid[d] + (I)(A.coef[d][nl - 1] * e);
+                const I id = xid[d] + (I)A.inner_coef[d] * (I)e;
                 over |= (id < 0) | (id >= (I)A.x_shape[d]);
                 off = off * A.x_shape[d] + id;
             }
@@ -55,7 +62,6 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
         }
         if (VEC == 1) y[flat] = out[0];
         else {
-            // VEC * sizeof(T) is 4, 8 or 16 bytes and flat is a multiple of VEC
             if (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(y + flat) = *reinterpret_cast<uint4*>(out);
             else if (VEC * sizeof(T) == 8) *reinterpret_cast<uint2*>(y + flat) = *reinterpret_cast<uint2*>(out);
             else if (VEC * sizeof(T) == 4) *reinterpret_cast<uint32_t*>(y + flat) = *reinterpret_cast<uint32_t*>(out);
@@ -118,14 +124,24 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
     const bool small = numel(x) < (1LL << 31) && n < (1LL << 31);
     const T* xp = (const T*)x->ptr;
     T* yp = (T*)y->ptr;
-    if (P.is_affine && numel(x) > 0) {
-        AffineArgs A;
-        memset(&A, 0, sizeof(A));
+    bool sparse_ok = P.is_affine && numel(x) > 0;
+    AffineArgs A;
+    memset(&A, 0, sizeof(A));
+    if (sparse_ok) {
         A.ndim_loop = P.ndim_loop; A.ndim_x = P.ndim_x;
         memcpy(A.loop_shape, P.loop_shape, sizeof(A.loop_shape));
         memcpy(A.x_shape, P.x_shape, sizeof(A.x_shape));
-        memcpy(A.coef, P.coef, sizeof(A.coef));
         memcpy(A.c0, P.c0, sizeof(A.c0));
+        for (int d = 0; d < P.ndim_x && sparse_ok; d++) {
+            A.inner_coef[d] = P.coef[d][P.ndim_loop - 1];
+            for (int j = 0; j < P.ndim_loop; j++) {
+                if (!P.coef[d][j]) continue;
+                if (A.nterm[d] == kMaxTerms) { sparse_ok = false; break; }
+                A.term_j[d][A.nterm[d]] = j; A.term_c[d][A.nterm[d]] = P.coef[d][j]; A.nterm[d]++;
+            }
+        }
+    }
+    if (sparse_ok) {
         const int64_t inner = P.loop_shape[P.ndim_loop - 1];
         int vec = 16 / (int)sizeof(T);
         if (vec > 8) vec = 8;

@@ -268,3 +268,26 @@ def test_full_size_softmax_rows_sum_to_one(jt):
     assert (y >= 0).all()
     idem = nn.softmax(jt.array(x + 7.5), -1).torch()          # shift invariance
     assert torch.allclose(idem, y, atol=1e-6, rtol=1e-4)
+
+
+def test_matmul_bf16_full_size_tensor_core(jt):
+    """8192^3 (the benchmark's size) through nn.matmul -> tcgen05 kernel: 64 sampled rows against the CPU oracle
+    (fp32 accumulation on bf16-rounded inputs), the whole result against a float32 torch product, and the
+    kernel's bounded waits must not have expired."""
+    from jittor_b200 import nn, _capi as C
+    g = torch.Generator("cuda").manual_seed(4)
+    n = 8192
+    a = (torch.randn(n, n, device="cuda", generator=g) / n ** 0.5).bfloat16()
+    b = torch.randn(n, n, device="cuda", generator=g).bfloat16()
+    c = nn.matmul(jt.array(a), jt.array(b))
+    assert c.dtype == "bfloat16"
+    ct = c.torch()
+    assert C.lib.b200jt_device_status() == 0
+    rows = torch.randperm(n, generator=torch.Generator().manual_seed(1))[:64]
+    want = co.matmul(a[rows.cuda()].float().cpu().numpy(), b.float().cpu().numpy())
+    check(ct[rows.cuda()].float().cpu().numpy(), bf16_round(want), False, rtol=2e-2)
+    ref = (a.float() @ b.float())
+    assert (ct.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    # transposed forms of the tuner table reach the same kernel
+    ct2 = nn.matmul_transpose(jt.array(a), jt.array(b.t().contiguous())).torch()
+    assert torch.equal(ct2, ct)
