@@ -24,7 +24,8 @@ extern "C" size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_t
  * (1 producer, 2 accumulator hand-back, 3 operand arrival, 4 accumulator ready). Synchronises the device. */
 extern "C" int b200jt_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    return tc_status_fetch_and_clear();
+    const int a = tc_status_fetch_and_clear(), b = tcconv_status_fetch_and_clear();
+    return a ? a : b;
 }
 
 extern "C" int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
@@ -70,21 +71,30 @@ static int conv_shape(const b200jt_tensor* x, const b200jt_tensor* w, const b200
 
 extern "C" size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                                           int sh, int sw, int ph, int pw, int dh, int dw, int groups) {
-    (void)x; (void)w; (void)y; (void)sh; (void)sw; (void)ph; (void)pw; (void)dh; (void)dw; (void)groups;
+    ConvShape s;
+    if (conv_shape(x, w, y, sh, sw, ph, pw, dh, dw, groups, &s)) return 0;
+    if (x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) return conv2d_tc_workspace(s);
     return 0;
 }
 
 extern "C" int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                              int sh, int sw, int ph, int pw, int dh, int dw, int groups,
                              float* stats, void* workspace, size_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     ConvShape s;
     int rc = conv_shape(x, w, y, sh, sw, ph, pw, dh, dw, groups, &s);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if (numel(y) != 0) {
-        rc = conv2d_simt(x->ptr, w->ptr, y->ptr, x->dtype, s, st);
-        if (rc) return rc;
+        if (x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) {
+            const size_t need = conv2d_tc_workspace(s);
+            B200JT_CHECK_ARG(workspace_bytes >= need && workspace, "workspace too small: need " + std::to_string(need) + " bytes");
+            rc = conv2d_tc(x->ptr, w->ptr, y->ptr, stats, s, workspace, st);
+            if (rc == 1) return 0;             // statistics came out of the conv epilogue
+            if (rc) return rc;
+        } else {
+            rc = conv2d_simt(x->ptr, w->ptr, y->ptr, x->dtype, s, st);
+            if (rc) return rc;
+        }
     }
     if (stats) return b200jt_bn_stats(y, stats, stream);
     return 0;

@@ -1,0 +1,316 @@
+// Reindex-lowered conv2d (python/jittor/nn.py:1009-1017) as an implicit GEMM on tcgen05: bf16 in, fp32 accumulate in TMEM.
+//
+// The reference never materialises the 7-D window tensor; its relay is cudnnConvolutionForward
+// (python/jittor/extern/cuda/cudnn/ops/cudnn_conv_op.cc:293). Here:
+//   GEMM view   M = N*OH*OW output pixels, N = Cout, K = KH*KW*Cin, walked tap by tap in 64-channel blocks;
+//   layout      x is first copied NCHW -> NHWC (channels innermost) and w OIHW -> [tap][Cout][Cin], so that both
+//               operands are K-major and every TMA box starts at a channel offset that is a multiple of 64 (the
+//               16-byte start rule); the spatial shift of a tap is carried by the H/W box coordinates, which may be
+//               negative or past the edge -- TMA zero-fills, which is exactly the reindex overflow value 0;
+//   tile        128 pixels (two 8x8 spatial patches, each one 4-D TMA box of 64 rows x 128 B) x 256 output channels;
+//   pipeline    same persistent warp-specialised ring as the GEMM (TMA warp, MMA warp, 4 epilogue warps, TMEM
+//               double buffering), stride 1 only (the box is a dense window);
+//   epilogue    tcgen05.ld -> bf16 -> y in NCHW; optionally per-channel sum / sum of squares of the stored values
+//               (the two reduce.mean of BatchNorm, python/jittor/nn.py:674-675) accumulated per CTA in shared memory
+//               and flushed with one atomicAdd per channel.
+#include "gemm_simt.cuh"
+#include "tc_common.cuh"
+
+#include <mutex>
+
+namespace b200jt {
+namespace tcconv {
+
+using namespace tc;
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int PATCH = 8;                            // spatial patch edge: 8 x 8 = 64 pixels = half a tile
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STATS_BYTES = 2 * BN * 4;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + STATS_BYTES;
+constexpr int THREADS = 192;
+
+struct ConvArgs {
+    int N, C, H, W, Co, KH, KW, OH, OW, ph, pw, dh, dw;
+    int tiles_h, tiles_w;            // patches per image
+    int64_t patches;                 // N * tiles_h * tiles_w
+    int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ void patch_coords(const ConvArgs& A, int64_t q, int& n, int& h0, int& w0) {
+    const int per_img = A.tiles_h * A.tiles_w;
+    n = (int)(q / per_img);
+    const int r = (int)(q - (int64_t)n * per_img);
+    h0 = (r / A.tiles_w) * PATCH;
+    w0 = (r % A.tiles_w) * PATCH;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 __nv_bfloat16* __restrict__ y, float* __restrict__ stats, const __grid_constant__ ConvArgs A) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* sstat = (float*)(smem + STAGES * STAGE_BYTES + 256);      // [2][BN] per-CTA channel sums
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total = A.tiles_m * A.tiles_n;
+    const int cblocks = (A.C + BK - 1) / BK;
+    const int k_blocks = A.KH * A.KW * cblocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < 2 * BN; i += blockDim.x) sstat[i] = 0.f;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                const int tm = t / A.tiles_n, tn = t - tm * A.tiles_n;
+                int n0, h0, w0, n1, h1, w1;
+                patch_coords(A, 2 * (int64_t)tm, n0, h0, w0);
+                patch_coords(A, 2 * (int64_t)tm + 1, n1, h1, w1);       // past the last patch: n1 >= N, zero-filled
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    const int tap = kb / cblocks, cb = kb - tap * cblocks;
+                    const int kh = tap / A.KW, kw = tap - kh * A.KW;
+                    const int dy = kh * A.dh - A.ph, dx = kw * A.dw - A.pw;
+                    if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 11))) break;
+                    unsigned char* sa = smem + stage * STAGE_BYTES;
+                    mbar_expect_tx(full + stage, STAGE_BYTES);
+                    tma_load_4d(sa, &map_x, full + stage, cb * BK, w0 + dx, h0 + dy, n0);
+                    tma_load_4d(sa + A_BYTES / 2, &map_x, full + stage, cb * BK, w1 + dx, h1 + dy, n1);
+                    tma_load_2d(sa + A_BYTES, &map_w, full + stage, cb * BK, tap * A.Co + tn * BN);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                for (int s = 0; s < STAGES; s++)
+                    for (uint32_t i = 0; i < 4096 && !mbar_try(full + s, 0) && !mbar_try(full + s, 1); i++) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, it++) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!(ok = mbar_wait(acc_empty + buf, acc_phase ^ 1, abort_flag, 12))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; kb++) {
+                    if (!(ok = mbar_wait(full + stage, phase, abort_flag, 13))) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit(empty + stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(acc_full + buf);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        int it = 0;
+        bool ok = true;
+        const int64_t plane = (int64_t)A.OH * A.OW;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x, it++) {
+            const int tm = t / A.tiles_n, tn = t - tm * A.tiles_n;
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            ok = mbar_wait(acc_full + buf, acc_phase, abort_flag, 14);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // this lane's pixel: row r of the tile = patch (r / 64), position (r % 64) = hh*8 + ww
+            const int r = quad * 32 + lane;
+            const int64_t q = 2 * (int64_t)tm + (r >> 6);
+            int n, h0, w0;
+            patch_coords(A, q, n, h0, w0);
+            const int oh = h0 + ((r & 63) >> 3), ow = w0 + (r & 7);
+            const bool valid = q < A.patches && oh < A.OH && ow < A.OW;
+            __nv_bfloat16* yp = y + ((int64_t)n * A.Co) * plane + (int64_t)oh * A.OW + ow;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ch++) {
+                uint32_t v[32];
+                tmem_ld32(taddr + ch * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int co0 = tn * BN + ch * 32;
+#pragma unroll
+                for (int e = 0; e < 32; e++) {
+                    const __nv_bfloat16 b = __float2bfloat16(__uint_as_float(v[e]));
+                    const bool st = valid && co0 + e < A.Co;
+                    if (st) yp[(int64_t)(co0 + e) * plane] = b;
+                    if (stats) {
+                        // statistics of the value as stored; lanes of a warp are 32 pixels of the same channel
+                        float f = st ? __bfloat162float(b) : 0.f, f2 = f * f;
+#pragma unroll
+                        for (int d = 16; d > 0; d >>= 1) { f += __shfl_xor_sync(0xffffffffu, f, d); f2 += __shfl_xor_sync(0xffffffffu, f2, d); }
+                        if (lane == 0) { atomicAdd(sstat + ch * 32 + e, f); atomicAdd(sstat + BN + ch * 32 + e, f2); }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + buf);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (stats && A.tiles_n == 1) {
+        for (int i = threadIdx.x; i < BN; i += blockDim.x) {
+            if (i < A.Co) { atomicAdd(stats + i, sstat[i]); atomicAdd(stats + A.Co + i, sstat[BN + i]); }
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    }
+}
+
+// ---- layout passes -----------------------------------------------------------------------------------------
+// in[b][R][Cn] -> out[b][Cn][R] (bf16), 64x64 tiles, 16-byte global accesses on both sides.
+__global__ void __launch_bounds__(256)
+transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn) {
+    __shared__ __nv_bfloat16 tile[64][72];
+    const int64_t boff = (int64_t)blockIdx.z * R * Cn;
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int j = threadIdx.x & 7, i = threadIdx.x >> 3;          // 8 chunks of 8 elements x 32 rows
+    const bool vec_in = (Cn % 8 == 0), vec_out = (R % 8 == 0);
+#pragma unroll
+    for (int p = 0; p < 2; p++) {
+        const int r = r0 + i + p * 32, c = c0 + j * 8;
+        __align__(16) __nv_bfloat16 v[8];
+        if (r < R && vec_in && c + 8 <= Cn) *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(in + boff + (int64_t)r * Cn + c);
+        else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = (r < R && c + e < Cn) ? in[boff + (int64_t)r * Cn + c + e] : __float2bfloat16(0.f);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) tile[i + p * 32][j * 8 + e] = v[e];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < 2; p++) {
+        const int c = c0 + i + p * 32, r = r0 + j * 8;           // output row = input column
+        if (c >= Cn) continue;
+        __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = tile[j * 8 + e][i + p * 32];
+        if (vec_out && r + 8 <= R) *reinterpret_cast<uint4*>(out + boff + (int64_t)c * R + r) = *reinterpret_cast<uint4*>(v);
+        else {
+            for (int e = 0; e < 8 && r + e < R; e++) out[boff + (int64_t)c * R + r + e] = v[e];
+        }
+    }
+}
+
+// w[Co][C][KH*KW] -> wt[KH*KW][Co][C]
+__global__ void __launch_bounds__(256)
+weight_tap_major_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int C, int taps) {
+    const int64_t n = (int64_t)Co * C * taps;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C); const int64_t t2 = i / C;
+        const int co = (int)(t2 % Co); const int tap = (int)(t2 / Co);
+        wt[i] = w[((int64_t)co * C + c) * taps + tap];
+    }
+}
+
+static bool make_map_x(CUtensorMap* map, const void* base, const ConvShape& s) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)s.C, (cuuint64_t)s.W, (cuuint64_t)s.H, (cuuint64_t)s.N};
+    cuuint64_t strides[3] = {(cuuint64_t)s.C * 2, (cuuint64_t)s.W * s.C * 2, (cuuint64_t)s.H * s.W * s.C * 2};
+    cuuint32_t box[4] = {(cuuint32_t)BK, PATCH, PATCH, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool make_map_w(CUtensorMap* map, const void* base, const ConvShape& s) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)s.C, (cuuint64_t)s.Co * s.KH * s.KW};
+    cuuint64_t strides[1] = {(cuuint64_t)s.C * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BN};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tcconv
+
+bool conv2d_tc_supported(const ConvShape& s, const void* x, const void* w, const void* y) {
+    return s.sh == 1 && s.sw == 1 && s.C % 8 == 0 && s.C >= 64 && s.Co >= 64 && s.H >= 8 && s.W >= 8 &&
+           (int64_t)s.N * s.OH * s.OW >= 1024 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 2 == 0) &&
+           ((uintptr_t)y % 2 == 0) && tc::encode_fn() != nullptr;
+}
+
+size_t conv2d_tc_workspace(const ConvShape& s) {
+    const size_t xb = ((size_t)s.N * s.H * s.W * s.C * 2 + 1023) & ~(size_t)1023;
+    const size_t wb = ((size_t)s.Co * s.C * s.KH * s.KW * 2 + 1023) & ~(size_t)1023;
+    return xb + wb + 1024;
+}
+
+int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st) {
+    using namespace tcconv;
+    unsigned char* ws = (unsigned char*)(((uintptr_t)workspace + 1023) & ~(uintptr_t)1023);
+    __nv_bfloat16* xt = (__nv_bfloat16*)ws;
+    __nv_bfloat16* wt = (__nv_bfloat16*)(ws + (((size_t)s.N * s.H * s.W * s.C * 2 + 1023) & ~(size_t)1023));
+    const int HW = s.H * s.W;
+    {   // x[N][C][HW] -> xt[N][HW][C]
+        dim3 g((unsigned)((HW + 63) / 64), (unsigned)((s.C + 63) / 64), (unsigned)s.N);
+        transpose_bf16_batched_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW);
+        const int64_t nw = (int64_t)s.Co * s.C * s.KH * s.KW;
+        weight_tap_major_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW);
+        B200JT_LAUNCH_CHECK();
+    }
+    CUtensorMap mx, mw;
+    if (!make_map_x(&mx, xt, s) || !make_map_w(&mw, wt, s)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed");
+    ConvArgs A;
+    A.N = s.N; A.C = s.C; A.H = s.H; A.W = s.W; A.Co = s.Co; A.KH = s.KH; A.KW = s.KW; A.OH = s.OH; A.OW = s.OW;
+    A.ph = s.ph; A.pw = s.pw; A.dh = s.dh; A.dw = s.dw;
+    A.tiles_h = (s.OH + PATCH - 1) / PATCH; A.tiles_w = (s.OW + PATCH - 1) / PATCH;
+    A.patches = (int64_t)s.N * A.tiles_h * A.tiles_w;
+    A.tiles_m = (int)((A.patches + 1) / 2); A.tiles_n = (s.Co + BN - 1) / BN;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(conv_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    B200JT_CUDA(attr_err);
+    float* fused = (stats && A.tiles_n == 1) ? stats : nullptr;
+    if (fused) B200JT_CUDA(cudaMemsetAsync(stats, 0, sizeof(float) * 2 * s.Co, st));
+    const int total = A.tiles_m * A.tiles_n;
+    const int grid = total < kNumSMs ? total : kNumSMs;
+    conv_bf16_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, (__nv_bfloat16*)y, fused, A);
+    B200JT_LAUNCH_CHECK();
+    return fused ? 1 : 0;      // 1: statistics were produced by the epilogue
+}
+
+int tcconv_status_fetch_and_clear() { return tc::status_fetch_and_clear(); }
+
+}  // namespace b200jt

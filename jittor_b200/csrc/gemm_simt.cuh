@@ -17,6 +17,12 @@ int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64
               void* workspace, cudaStream_t st);
 int tc_status_fetch_and_clear();
 
+bool conv2d_tc_supported(const ConvShape& s, const void* x, const void* w, const void* y);
+size_t conv2d_tc_workspace(const ConvShape& s);
+// returns < 0 / > 1 on error, 0 on success, 1 on success with `stats` filled by the epilogue
+int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st);
+int tcconv_status_fetch_and_clear();
+
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
 
 }  // namespace b200jt

@@ -12,20 +12,16 @@
 
 namespace b200jt {
 
-constexpr int kMaxTerms = 4;     // non-zero coefficients per index expression handled by the affine kernel
-
 struct AffineArgs {
     int32_t ndim_loop, ndim_x;
     int64_t loop_shape[kMaxDims];
     int64_t x_shape[kMaxDims];
     int64_t c0[kMaxDims];
-    int32_t nterm[kMaxDims];                 // sparse rows of the coefficient matrix
-    int32_t term_j[kMaxDims][kMaxTerms];
-    int64_t term_c[kMaxDims][kMaxTerms];
-    int64_t inner_coef[kMaxDims];            // coefficient of the innermost loop variable
+    int64_t coef[kMaxDims][kMaxDims];
 };
 
-// I = index type (uint32-sized arithmetic when every tensor is below 2^31 elements, as the reference's index_t).
+// I = index type (32-bit arithmetic when every tensor is below 2^31 elements, as the reference's index_t).
+// All loops over axes are fully unrolled with uniform guards so that the coordinate arrays stay in registers.
 template <typename T, typename I, int VEC>
 __global__ void __launch_bounds__(256)
 reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_constant__ AffineArgs A,
@@ -38,25 +34,35 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
         const int64_t flat = v * VEC;
         I iv[kMaxDims];
         U r = (U)flat;
-#pragma unroll 1
-        for (int d = nl - 1; d >= 0; d--) { const U s = (U)A.loop_shape[d]; const U q = r / s; iv[d] = (I)(r - q * s); r = q; }
-        I xid[kMaxDims];
-#pragma unroll 1
-        for (int d = 0; d < nx; d++) {
-            I a = (I)A.c0[d];
-            for (int k = 0; k < A.nterm[d]; k++) a += (I)A.term_c[d][k] * iv[A.term_j[d][k]];
-            xid[d] = a;
+#pragma unroll
+        for (int d = kMaxDims - 1; d >= 0; d--) {
+            iv[d] = 0;
+            if (d < nl) { const U s = (U)A.loop_shape[d]; const U q = r / s; iv[d] = (I)(r - q * s); r = q; }
+        }
+        I xid[kMaxDims], xinner[kMaxDims], xs[kMaxDims];
+#pragma unroll
+        for (int d = 0; d < kMaxDims; d++) {
+            xid[d] = 0; xinner[d] = 0; xs[d] = 1;
+            if (d < nx) {
+                I a = (I)A.c0[d];
+#pragma unroll
+                for (int j = 0; j < kMaxDims; j++)
+                    if (j < nl) { const I cf = (I)A.coef[d][j]; if (cf != 0) a += cf * iv[j]; }
+                xid[d] = a; xinner[d] = (I)A.coef[d][nl - 1]; xs[d] = (I)A.x_shape[d];
+            }
         }
         __align__(16) T out[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; e++) {
             bool over = false;
             int64_t off = 0;
-#pragma unroll 1
-            for (int d = 0; d < nx; d++) {
-                const I id = xid[d] + (I)A.inner_coef[d] * (I)e;
-                over |= (id < 0) | (id >= (I)A.x_shape[d]);
-                off = off * A.x_shape[d] + id;
+#pragma unroll
+            for (int d = 0; d < kMaxDims; d++) {
+                if (d < nx) {
+                    const I id = xid[d] + xinner[d] * (I)e;
+                    over |= (id < 0) | (id >= xs[d]);
+                    off = off * xs[d] + id;
+                }
             }
             out[e] = over ? fill : x[off];
         }
@@ -124,24 +130,14 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
     const bool small = numel(x) < (1LL << 31) && n < (1LL << 31);
     const T* xp = (const T*)x->ptr;
     T* yp = (T*)y->ptr;
-    bool sparse_ok = P.is_affine && numel(x) > 0;
-    AffineArgs A;
-    memset(&A, 0, sizeof(A));
-    if (sparse_ok) {
+    if (P.is_affine && numel(x) > 0) {
+        AffineArgs A;
+        memset(&A, 0, sizeof(A));
         A.ndim_loop = P.ndim_loop; A.ndim_x = P.ndim_x;
         memcpy(A.loop_shape, P.loop_shape, sizeof(A.loop_shape));
         memcpy(A.x_shape, P.x_shape, sizeof(A.x_shape));
         memcpy(A.c0, P.c0, sizeof(A.c0));
-        for (int d = 0; d < P.ndim_x && sparse_ok; d++) {
-            A.inner_coef[d] = P.coef[d][P.ndim_loop - 1];
-            for (int j = 0; j < P.ndim_loop; j++) {
-                if (!P.coef[d][j]) continue;
-                if (A.nterm[d] == kMaxTerms) { sparse_ok = false; break; }
-                A.term_j[d][A.nterm[d]] = j; A.term_c[d][A.nterm[d]] = P.coef[d][j]; A.nterm[d]++;
-            }
-        }
-    }
-    if (sparse_ok) {
+        memcpy(A.coef, P.coef, sizeof(A.coef));
         const int64_t inner = P.loop_shape[P.ndim_loop - 1];
         int vec = 16 / (int)sizeof(T);
         if (vec > 8) vec = 8;

@@ -52,6 +52,8 @@ class DType(str):
 
 def canon(dt):
     """Accepts a name, a numpy dtype / type, a torch dtype or a Python type; returns the name."""
+    if type(dt) is DType:
+        return dt
     if isinstance(dt, str):
         name = {"float": "float32", "int": "int32", "double": "float64", "half": "float16"}.get(dt, dt)
     elif dt is float:
@@ -94,7 +96,18 @@ def _int_dtype(ds):
     return {3: "int64", 2: "int32", 1: "int16", 0: "int8"}[ds]
 
 
+_BIN_CACHE = {}
+
+
 def binary_dtype_infer(op, x, y, xscalar=False, yscalar=False):
+    key = (op, str(x), str(y), xscalar, yscalar, _FLAGS.amp_reg)
+    r = _BIN_CACHE.get(key)
+    if r is None:
+        r = _BIN_CACHE[key] = _binary_dtype_infer(op, x, y, xscalar, yscalar)
+    return r
+
+
+def _binary_dtype_infer(op, x, y, xscalar=False, yscalar=False):
     if op in BOOL_OPS:
         return DType("bool")
     ds = max(dsize(x), dsize(y))

@@ -51,8 +51,8 @@ class Var:
     __array_priority__ = 100
 
     def __init__(self, shape, dtype, op=None, data=None, is_scalar=False):
-        self._shape = Shape(_check_shape(shape))
-        self._dtype = dt.canon(dtype)
+        self._shape = shape if type(shape) is Shape else Shape(_check_shape(shape))
+        self._dtype = dtype if type(dtype) is dt.DType else dt.canon(dtype)
         self._op = op
         self._data = data            # contiguous torch tensor on the CUDA device once computed
         self.is_scalar = is_scalar
