@@ -2,18 +2,19 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
 
-One JSON line on stdout (rank 0). The default workload is the reindex_reduce scatter configuration
-(benchmark config 1): one step = one pass over its five parts
-    a-uniform / a-zipf : 2^24 int32 values into 2^20 bins (op add, bit-exact)
-    b-uniform / b-zipf : 2^24 fp32 values into 4096 bins
-    pool-bwd           : 2x2 max-pool backward as reindex_reduce add, [64,128,56,56,2,2] -> [64,128,112,112] fp32
-`value` is algorithmic GB/s with inputs resident in HBM, timed with CUDA events on the launching stream
-(max over ranks); `e2e` is the same step through the public API from pinned host buffers including the
-host->device copies and the device->host read of the results. Every part's input is larger than L2 and five
-different inputs are touched between two uses of one buffer, so no L2 flush is needed (stated in `config`).
-`--impl reference` times the CPU restatement of the reference's loop nests (oracle/meta_ops.c) on the host cores.
-With N > 1 (torchrun) every rank processes its own inputs (weak scaling); the scatter parts all-reduce their bins
-over NCCL, which is the reference's exchange step for a shared output.
+One JSON line on stdout (rank 0). Workloads are the benchmark configurations:
+    c2 (default)  reindex_reduce scatter: 2^24 int32 -> 2^20 bins and 2^24 fp32 -> 4096 bins, uniform and Zipf(1.1)
+                  indices, plus the 2x2 max-pool backward [64,128,56,56,2,2] -> [64,128,112,112]      (GB/s, HBM)
+    c3            fused row softmax and LayerNorm on [32768, 4096], fp32 and bf16 IO                  (GB/s, HBM)
+    c4            broadcast-multiply-sum matmul, bf16: 8192^3 and 16384 x 4096 x 4096                 (TFLOP/s)
+    c5            reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] -> global BatchNorm statistics (one NCCL
+                  all-reduce of 2*C floats) -> normalise + ReLU, batch-sharded over the ranks          (TFLOP/s)
+One step = one pass over the parts of the workload. `value` is algorithmic work / CUDA-event time with inputs
+resident in HBM (max over ranks); `e2e` is the same step through the public API from pinned host buffers including
+host->device copies and the device->host read of the results. Every part works on more bytes than the 126 MB L2
+and the parts rotate, so no L2 flush is issued (stated in `config`). `--impl reference` times the CPU restatement of the
+reference's loop nests (oracle/meta_ops.c) on the host cores, on a bounded sample. With N > 1 (torchrun) c2-c4 give every
+rank its own inputs (weak scaling; c2 all-reduces the scatter bins), c5 splits the batch (strong scaling).
 """
 import argparse
 import json
@@ -28,19 +29,6 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-N_VAL = 1 << 24
-BINS_A = 1 << 20
-BINS_B = 4096
-POOL_SHAPE = (64, 128, 56, 56, 2, 2)
-POOL_IDX = ["i0", "i1", "i2*2+i4", "i3*2+i5"]
-
-
-def algorithmic_bytes():
-    """inputs read once + outputs written once, intermediates free."""
-    pool = int(np.prod(POOL_SHAPE)) * 4
-    return {"a-uniform": N_VAL * 8 + BINS_A * 4, "a-zipf": N_VAL * 8 + BINS_A * 4,
-            "b-uniform": N_VAL * 8 + BINS_B * 4, "b-zipf": N_VAL * 8 + BINS_B * 4, "pool-bwd": 2 * pool}
-
 
 def zipf_indices(rng, n, bins, s=1.1):
     """Inverse-CDF draw from the truncated Zipf(s) over bin ranks; rank -> bin by a fixed permutation."""
@@ -48,26 +36,6 @@ def zipf_indices(rng, n, bins, s=1.1):
     cdf = np.cumsum(p / p.sum())
     rank = np.minimum(np.searchsorted(cdf, rng.random(n)), bins - 1)
     return rng.permutation(bins)[rank].astype(np.int32)
-
-
-def make_inputs(seed, pool_images=POOL_SHAPE[0]):
-    rng = np.random.default_rng(seed)       # seed = config index (+ rank)
-    vi = rng.integers(0, 100, size=N_VAL).astype(np.int32)
-    vf = rng.normal(size=N_VAL).astype(np.float32)
-    pshape = (pool_images,) + POOL_SHAPE[1:]
-    # pool gradient: N(0,1) where the element is its window's arg-max, else 0 (what the max-reduce grad emits)
-    g = rng.normal(size=pshape).astype(np.float32)
-    keep = rng.integers(0, 4, size=pshape[:4])
-    mask = np.zeros(pshape, dtype=bool).reshape(pshape[:4] + (4,))
-    np.put_along_axis(mask, keep[..., None], True, axis=-1)
-    g *= mask.reshape(pshape)
-    return {
-        "a-uniform": (vi, rng.integers(0, BINS_A, size=N_VAL).astype(np.int32), BINS_A),
-        "a-zipf": (vi, zipf_indices(rng, N_VAL, BINS_A), BINS_A),
-        "b-uniform": (vf, rng.integers(0, BINS_B, size=N_VAL).astype(np.int32), BINS_B),
-        "b-zipf": (vf, zipf_indices(rng, N_VAL, BINS_B), BINS_B),
-        "pool-bwd": (g, None, None),
-    }
 
 
 class ClockSampler:
@@ -88,7 +56,7 @@ class ClockSampler:
                     self.samples.append([f.strip() for f in out.split(",")])
             except Exception:
                 pass
-            time.sleep(0.1)
+            time.sleep(0.05)
 
     def __enter__(self):
         self.t.start()
@@ -108,40 +76,299 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
+# =====================================================================================================
+# Workloads. A workload knows its parts, the algorithmic work of each (bytes or FLOP), how to run a part on
+# device-resident inputs or from pinned host buffers, and how to run a bounded sample of it on the CPU oracle.
+# =====================================================================================================
+class C2Scatter:
+    key, metric, unit, bound, dtype, scaling = "c2", "meta-op GB/s", "GB/s", "hbm", "int32/f32", "weak"
+    N_VAL, BINS_A, BINS_B = 1 << 24, 1 << 20, 4096
+    POOL_SHAPE = (64, 128, 56, 56, 2, 2)
+    POOL_IDX = ["i0", "i1", "i2*2+i4", "i3*2+i5"]
+    description = ("config 1: reindex_reduce scatter-add 2^24 -> 2^20 int32 and -> 4096 fp32 (uniform + Zipf 1.1 "
+                   "indices) + 2x2 max-pool backward [64,128,112,112] fp32")
+    kernel_of = {"a-uniform": "rr_direct_cached_kernel<int,int,4>", "a-zipf": "rr_direct_cached_kernel<int,int,4>",
+                 "b-uniform": "rr_privatised_kernel<float,int,4>", "b-zipf": "rr_privatised_kernel<float,int,4>",
+                 "pool-bwd": "rr_flat_kernel<float>"}
+    launches = {"a-uniform": 2, "a-zipf": 2, "b-uniform": 2, "b-zipf": 2, "pool-bwd": 1}
+
+    def work(self):
+        pool = int(np.prod(self.POOL_SHAPE)) * 4
+        n = self.N_VAL
+        return {"a-uniform": n * 8 + self.BINS_A * 4, "a-zipf": n * 8 + self.BINS_A * 4,
+                "b-uniform": n * 8 + self.BINS_B * 4, "b-zipf": n * 8 + self.BINS_B * 4, "pool-bwd": 2 * pool}
+
+    def host_inputs(self, seed, pool_images=None):
+        rng = np.random.default_rng(seed)       # seed = config index (+ rank)
+        n = self.N_VAL
+        vi = rng.integers(0, 100, size=n).astype(np.int32)
+        vf = rng.normal(size=n).astype(np.float32)
+        pshape = (pool_images or self.POOL_SHAPE[0],) + self.POOL_SHAPE[1:]
+        # pool gradient: N(0,1) where the element is its window's arg-max, else 0 (what the max-reduce grad emits)
+        g = rng.normal(size=pshape).astype(np.float32)
+        keep = rng.integers(0, 4, size=pshape[:4])
+        mask = np.zeros(pshape[:4] + (4,), dtype=bool)
+        np.put_along_axis(mask, keep[..., None], True, axis=-1)
+        g *= mask.reshape(pshape)
+        return {"a-uniform": (vi, rng.integers(0, self.BINS_A, size=n).astype(np.int32), self.BINS_A),
+                "a-zipf": (vi, zipf_indices(rng, n, self.BINS_A), self.BINS_A),
+                "b-uniform": (vf, rng.integers(0, self.BINS_B, size=n).astype(np.int32), self.BINS_B),
+                "b-zipf": (vf, zipf_indices(rng, n, self.BINS_B), self.BINS_B),
+                "pool-bwd": (g, None, None)}
+
+    def setup(self, rank, world, jt, torch, multi):
+        self.jt, self.torch, self.multi = jt, torch, multi
+        self.host = self.host_inputs(1 + rank)
+        self.pinned = {k: tuple(torch.from_numpy(a).pin_memory() if a is not None else None for a in v[:2]) + (v[2],)
+                       for k, v in self.host.items()}
+        self.dev = {k: (jt.array(v[0]), jt.array(v[1]) if v[1] is not None else None, v[2])
+                    for k, v in self.pinned.items()}
+        sizes = {"a-uniform": self.BINS_A, "a-zipf": self.BINS_A, "b-uniform": self.BINS_B, "b-zipf": self.BINS_B,
+                 "pool-bwd": int(np.prod(self.POOL_SHAPE))}
+        self.out_host = {k: torch.empty(n, dtype=torch.int32 if k.startswith("a-") else torch.float32).pin_memory()
+                         for k, n in sizes.items()}
+        return list(self.dev)
+
+    def _scatter(self, val, idx, bins):
+        if idx is None:
+            return val.reindex_reduce("add", list(self.POOL_SHAPE[:2]) + [112, 112], self.POOL_IDX)
+        out = val.reindex_reduce("add", [bins], ["@e0(i0)"], extras=[idx])
+        return out.mpi_all_reduce("add") if self.multi else out      # shared output across ranks
+
+    def run(self, name):
+        return self._scatter(*self.dev[name]).sync()
+
+    def run_e2e(self, name):
+        hv, hi, bins = self.pinned[name]
+        v = self.jt.array(hv.cuda(non_blocking=True))
+        i = self.jt.array(hi.cuda(non_blocking=True)) if hi is not None else None
+        self._scatter(v, i, bins).fetch_into(self.out_host[name])
+
+    def e2e_bytes(self, names):
+        h2d = sum(a.numel() * a.element_size() for n in names for a in self.pinned[n][:2] if a is not None)
+        return h2d, sum(self.out_host[n].numel() * 4 for n in names)
+
+    def cpu(self, names):
+        from oracle import c_oracle as co
+        host = getattr(self, "host", None) or self.host_inputs(1, 8)
+        self.host = host
+        work, done = self.work(), 0
+        t0 = time.perf_counter()
+        for nm in names:
+            v, i, b = host[nm]
+            if i is None:
+                co.pool2x2_bwd(v[:8])
+                done += work[nm] * 8 // self.POOL_SHAPE[0]
+            else:
+                co.scatter_add(v, i, b)
+                done += work[nm]
+        return done, time.perf_counter() - t0, ("scatter parts at full size + 8 of 64 pool-bwd images; the scatter loop is "
+                                                "serial in the reference (1 core), pool-bwd uses OpenMP")
+
+
+class C3Rows:
+    key, metric, unit, bound, dtype, scaling = "c3", "meta-op GB/s", "GB/s", "hbm", "f32 (bf16 IO variants)", "weak"
+    ROWS, COLS = 32768, 4096
+    description = "config 2: fused row softmax and LayerNorm on [32768,4096], fp32 and bf16 IO with fp32 math"
+    kernel_of = {k: "row_reg_kernel" for k in ("softmax-f32", "layernorm-f32", "softmax-bf16", "layernorm-bf16")}
+    launches = {k: 1 for k in kernel_of}
+
+    def work(self):
+        n = self.ROWS * self.COLS
+        return {"softmax-f32": 8 * n, "layernorm-f32": 8 * n, "softmax-bf16": 4 * n, "layernorm-bf16": 4 * n}
+
+    def setup(self, rank, world, jt, torch, multi):
+        from jittor_b200 import nn
+        self.jt, self.torch, self.nn = jt, torch, nn
+        g = torch.Generator().manual_seed(2 + rank)
+        x = torch.randn(self.ROWS, self.COLS, generator=g)
+        self.h32 = x.pin_memory()
+        self.h16 = x.bfloat16().pin_memory()
+        # two device copies per dtype so that consecutive parts never reuse a buffer that is still in L2
+        self.x32 = [jt.array(self.h32), jt.array(self.h32.clone())]
+        self.x16 = [jt.array(self.h16), jt.array(self.h16.clone())]
+        self.gamma = jt.array((1 + 0.02 * torch.randn(self.COLS, generator=g)))
+        self.beta = jt.array(torch.zeros(self.COLS))
+        self.o32 = torch.empty(self.ROWS, self.COLS).pin_memory()
+        self.o16 = torch.empty(self.ROWS, self.COLS, dtype=torch.bfloat16).pin_memory()
+        return list(self.kernel_of)
+
+    def _op(self, name, x):
+        if name.startswith("softmax"):
+            return self.nn.softmax(x, -1)
+        return self.nn.layer_norm(x, (self.COLS,), self.gamma, self.beta)
+
+    def run(self, name):
+        x = (self.x32 if name.endswith("f32") else self.x16)[0 if name.startswith("softmax") else 1]
+        return self._op(name, x).sync()
+
+    def run_e2e(self, name):
+        f32 = name.endswith("f32")
+        x = self.jt.array((self.h32 if f32 else self.h16).cuda(non_blocking=True))
+        self._op(name, x).fetch_into(self.o32 if f32 else self.o16)
+
+    def e2e_bytes(self, names):
+        n = self.ROWS * self.COLS
+        b = sum(4 * n if nm.endswith("f32") else 2 * n for nm in names)
+        return b, b
+
+    def cpu(self, names):
+        from oracle import c_oracle as co
+        rows = 2048
+        x = np.random.default_rng(2).normal(size=(rows, self.COLS)).astype(np.float32)
+        g, z = np.ones(self.COLS, np.float32), np.zeros(self.COLS, np.float32)
+        done, t0 = 0, time.perf_counter()
+        for nm in names:
+            if nm.startswith("softmax"):
+                co.softmax_rows(x)
+            else:
+                co.layernorm_rows(x, g, z)
+            done += self.work()[nm] * rows // self.ROWS
+        return done, time.perf_counter() - t0, f"{rows} of {self.ROWS} rows per part, fp32 math (OpenMP over rows)"
+
+
+class C4Matmul:
+    key, metric, unit, bound, dtype, scaling = "c4", "matmul TFLOP/s", "TFLOP/s", "tensor", "bf16 (fp32 accumulate)", "weak"
+    SHAPES = {"8192x8192x8192": (8192, 8192, 8192), "16384x4096x4096": (16384, 4096, 4096)}
+    description = "config 3: broadcast-multiply-sum matmul A[M,K] x B[K,N], bf16 inputs ~ N(0,1/K), fp32 accumulate"
+    kernel_of = {k: "gemm_bf16_kernel (tcgen05)" for k in SHAPES}
+    launches = {k: 2 for k in SHAPES}        # operand transpose + GEMM
+
+    def work(self):
+        return {k: 2 * m * n * kk for k, (m, n, kk) in self.SHAPES.items()}
+
+    def setup(self, rank, world, jt, torch, multi):
+        from jittor_b200 import nn
+        self.jt, self.torch, self.nn = jt, torch, nn
+        g = torch.Generator().manual_seed(3 + rank)
+        self.hostab, self.dev, self.out = {}, {}, {}
+        for k, (m, n, kk) in self.SHAPES.items():
+            a = (torch.randn(m, kk, generator=g) / kk ** 0.5).bfloat16().pin_memory()
+            b = (torch.randn(kk, n, generator=g) / kk ** 0.5).bfloat16().pin_memory()
+            self.hostab[k] = (a, b)
+            self.dev[k] = (jt.array(a), jt.array(b))
+            self.out[k] = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+        return list(self.SHAPES)
+
+    def run(self, name):
+        a, b = self.dev[name]
+        return self.nn.matmul(a, b).sync()
+
+    def run_e2e(self, name):
+        a, b = self.hostab[name]
+        self.nn.matmul(self.jt.array(a.cuda(non_blocking=True)),
+                       self.jt.array(b.cuda(non_blocking=True))).fetch_into(self.out[name])
+
+    def e2e_bytes(self, names):
+        return (sum(a.numel() * 2 + b.numel() * 2 for a, b in (self.hostab[n] for n in names)),
+                sum(self.out[n].numel() * 2 for n in names))
+
+    def cpu(self, names):
+        from oracle import c_oracle as co
+        rows, done, secs = 256, 0, 0.0
+        rng = np.random.default_rng(3)
+        for nm in names:
+            m, n, kk = self.SHAPES[nm]
+            a = rng.normal(size=(rows, kk)).astype(np.float32)
+            b = rng.normal(size=(kk, n)).astype(np.float32)
+            t1 = time.perf_counter()
+            co.matmul(a, b)
+            secs += time.perf_counter() - t1
+            done += 2 * rows * n * kk
+        return done, secs, f"a slab of {rows} rows of A per shape, fp32 (OpenMP over rows)"
+
+
+class C5ConvBN:
+    key, metric, unit, bound, dtype, scaling = "c5", "conv TFLOP/s", "TFLOP/s", "tensor", "bf16 (fp32 accumulate)", "strong"
+    N, C, H, W, CO = 256, 256, 56, 56, 256
+    description = ("config 4: reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] s1 p1, then global BatchNorm statistics "
+                   "(one NCCL all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks")
+    kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)"}
+    launches = {"conv": 3, "conv-bn-relu": 5}
+
+    def work(self):
+        f = 2 * self.N * self.H * self.W * self.CO * self.C * 9
+        return {"conv": f, "conv-bn-relu": f}
+
+    def setup(self, rank, world, jt, torch, multi):
+        from jittor_b200 import nn
+        self.jt, self.torch, self.nn, self.world = jt, torch, nn, world
+        n = self.N // world
+        g = torch.Generator().manual_seed(4 + rank)
+        self.hx = torch.randn(n, self.C, self.H, self.W, generator=g).bfloat16().pin_memory()
+        gw = torch.Generator().manual_seed(4)          # weights are replicated
+        self.hw = (torch.randn(self.CO, self.C, 3, 3, generator=gw) * (2 / (9 * self.C)) ** 0.5).bfloat16().pin_memory()
+        self.x, self.w = jt.array(self.hx), jt.array(self.hw)
+        self.bn = nn.BatchNorm(self.CO, is_train=True, sync=True)
+        self.bn.weight.sync()
+        self.bn.bias.sync()
+        self.out = torch.empty(n, self.CO, self.H, self.W, dtype=torch.bfloat16).pin_memory()
+        return ["conv", "conv-bn-relu"]
+
+    def per_rank_work(self, name):
+        return self.work()[name] // self.world
+
+    def _op(self, name, x, w):
+        y = self.nn.conv2d(x, w, None, 1, 1, 1)
+        if name == "conv":
+            return y
+        with self.jt.flag_scope(amp_reg=2):            # keep 16-bit results: the activation is written as bf16
+            return self.nn.relu(self.bn(y))
+
+    def run(self, name):
+        return self._op(name, self.x, self.w).sync()
+
+    def run_e2e(self, name):
+        x = self.jt.array(self.hx.cuda(non_blocking=True))
+        w = self.jt.array(self.hw.cuda(non_blocking=True))
+        self._op(name, x, w).fetch_into(self.out)
+
+    def e2e_bytes(self, names):
+        return len(names) * (self.hx.numel() + self.hw.numel()) * 2, len(names) * self.out.numel() * 2
+
+    def cpu(self, names):
+        from oracle import c_oracle as co
+        imgs = 2
+        rng = np.random.default_rng(4)
+        x = rng.normal(size=(imgs, self.C, self.H, self.W)).astype(np.float32)
+        w = (rng.normal(size=(self.CO, self.C, 3, 3)) * (2 / (9 * self.C)) ** 0.5).astype(np.float32)
+        done, t0 = 0, time.perf_counter()
+        for nm in names:
+            y = co.conv2d(x, w, 1, 1, 1)
+            if nm != "conv":
+                co.bn_relu(y, np.ones(self.CO, np.float32), np.zeros(self.CO, np.float32))
+            done += self.work()[nm] * imgs // self.N
+        return done, time.perf_counter() - t0, f"{imgs} of {self.N} images per part, fp32 (OpenMP over image x channel)"
+
+
+WORKLOADS = {w.key: w for w in (C2Scatter, C3Rows, C4Matmul, C5ConvBN)}
+
+
+def scale_of(unit):
+    return 1e6 if unit == "GB/s" else 1e9          # work / ms -> GB/s (1e6) or TFLOP/s (1e9)
+
+
 def run_reference(args, rank, world):
     """The reference's CPU implementation of the step (C restatement of its loop nests), bounded sample."""
     if rank != 0:
         return
-    from oracle import c_oracle as co
-    pool_images = 8                                    # bounded sample: 8 of the 64 images of the pool part
-    inp = make_inputs(1, pool_images)
-    ab = algorithmic_bytes()
-    ab["pool-bwd"] = ab["pool-bwd"] * pool_images // POOL_SHAPE[0]
-    total = sum(ab.values())
-
-    def step():
-        for name, (val, idx, bins) in inp.items():
-            if idx is None:
-                co.pool2x2_bwd(val)
-            else:
-                co.scatter_add(val, idx, bins)
-
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
+    wl = WORKLOADS[args.workload]()
+    names = [n for n in wl.work() if not args.parts or n in args.parts.split(",")]
+    for _ in range(max(args.warmup, 0)):
+        wl.cpu(names)
+    done = secs = 0.0
+    sample = ""
     for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
-    val = total / dt / 1e9
-    sample = "the four scatter parts at full size + 8 of 64 images of pool-bwd, per step"
+        d, t, sample = wl.cpu(names)
+        done, secs = done + d, secs + t
+    val = done / secs / (1e9 if wl.unit == "GB/s" else 1e12)
     print(json.dumps({
-        "impl": "reference", "metric": "meta-op GB/s", "value": val, "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int32/f32", "data": "synthetic",
-        "config": {"workload": "config 1: reindex_reduce scatter-add (a,b x uniform,zipf) + pool-bwd", "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample,
-                         "note": "scatter loops are serial in the reference (1 core); pool-bwd uses OpenMP"},
-        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        "impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
+        "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype if wl.key == "c2" else "f32", "data": "synthetic",
+        "config": {"workload": wl.description, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": wl.unit, "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
 def main():
@@ -150,6 +377,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-baseline", type=int, default=1)
     ap.add_argument("--parts", default="", help="comma-separated subset of the parts (profiling aid)")
     ap.add_argument("--e2e", type=int, default=1)
@@ -168,26 +396,12 @@ def main():
     torch.cuda.set_device(local)
     dist.init("nccl")
     multi = dist.in_mpi()
-
-    ab = algorithmic_bytes()
-    total_bytes = sum(ab.values())
-    host = make_inputs(1 + rank)
-    pinned = {k: tuple(torch.from_numpy(a).pin_memory() if a is not None else None for a in v[:2]) + (v[2],)
-              for k, v in host.items()}
-    dev = {k: (jt.array(v[0]), jt.array(v[1]) if v[1] is not None else None, v[2]) for k, v in pinned.items()}
-    names = [n for n in dev if not args.parts or n in args.parts.split(",")]
-    ab = {n: ab[n] for n in names}
-    total_bytes = sum(ab.values())
-
-    def run_part(name, val, idx, bins):
-        if idx is None:
-            out = val.reindex_reduce("add", list(POOL_SHAPE[:2]) + [112, 112], POOL_IDX)
-        else:
-            out = val.reindex_reduce("add", [bins], ["@e0(i0)"], extras=[idx])
-            if multi:
-                out = out.mpi_all_reduce("add")      # shared output across ranks
-        out.sync()
-        return out
+    wl = WORKLOADS[args.workload]()
+    names = [n for n in wl.setup(rank, world, jt, torch, multi) if not args.parts or n in args.parts.split(",")]
+    work = {n: wl.work()[n] for n in names}
+    sc = scale_of(wl.unit)
+    # whole-job work per step: weak scaling multiplies the per-rank work, strong scaling keeps the total
+    job_work = sum(work.values()) * (world if wl.scaling == "weak" else 1)
 
     def barrier():
         if multi:
@@ -195,9 +409,10 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident throughput ------------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         for nm in names:
-            run_part(nm, *dev[nm])
+            wl.run(nm)
     barrier()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(args.steps)]
     with ClockSampler(local) as clocks:
@@ -205,24 +420,18 @@ def main():
         for s in range(args.steps):
             ev[s][0].record()
             for i, nm in enumerate(names):
-                run_part(nm, *dev[nm])
+                wl.run(nm)
                 ev[s][i + 1].record()
         barrier()
     step_ms = ev[0][0].elapsed_time(ev[-1][-1]) / args.steps
     part_ms = {nm: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) / args.steps
                for i, nm in enumerate(names)}
+    status = jt._capi.lib.b200jt_device_status()
 
-    # ---- end to end: pinned host -> device -> kernels -> host ----------------------------------------
-    out_host = {nm: torch.empty(ab_out, dtype=(torch.int32 if nm.startswith("a-") else torch.float32)).pin_memory()
-                for nm, ab_out in (("a-uniform", BINS_A), ("a-zipf", BINS_A), ("b-uniform", BINS_B), ("b-zipf", BINS_B),
-                                   ("pool-bwd", int(np.prod(POOL_SHAPE))))}
-
+    # ---- end to end: pinned host -> device -> kernels -> pinned host ------------------------------------
     def e2e_step():
         for nm in names:
-            hv, hi, bins = pinned[nm]
-            v = jt.array(hv.cuda(non_blocking=True))
-            i = jt.array(hi.cuda(non_blocking=True)) if hi is not None else None
-            run_part(nm, v, i, bins).fetch_into(out_host[nm])
+            wl.run_e2e(nm)
         torch.cuda.current_stream().synchronize()
 
     e2e_steps = max(2, min(args.steps, 5)) if args.e2e else 0
@@ -236,8 +445,7 @@ def main():
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / max(e2e_steps, 1)
-    h2d = sum(a.numel() * a.element_size() for n in names for a in pinned[n][:2] if a is not None)
-    d2h = sum(out_host[n].numel() * 4 for n in names)
+    h2d, d2h = wl.e2e_bytes(names)
 
     # ---- max over ranks ------------------------------------------------------------------------------
     times = torch.tensor([step_ms, e2e_ms] + [part_ms[n] for n in names], device="cuda", dtype=torch.float64)
@@ -250,50 +458,38 @@ def main():
         return
 
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured"
+    peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else None
+    if wl.bound == "hbm":
+        peak, peak_src = (peaks["hbm_gbs"], "measured") if peaks else (6650.0, "fallback")
     else:
-        peak, peak_src = 6650.0, "fallback"
-    parts = [{"part": n, "ms": part_ms[n], "GB/s": ab[n] / part_ms[n] / 1e6, "frac_of_hbm": ab[n] / part_ms[n] / 1e6 / peak}
-             for n in names]
+        peak, peak_src = (peaks["bf16_tflops"], "measured (burst)") if peaks else (1590.0, "fallback")
+    per_rank = wl.per_rank_work if hasattr(wl, "per_rank_work") else (lambda n: work[n])
+    parts = [{"part": n, "ms": part_ms[n], wl.unit: per_rank(n) / part_ms[n] / sc,
+              "frac_of_peak": per_rank(n) / part_ms[n] / sc / peak} for n in names]
     dom = max(names, key=lambda n: part_ms[n])
-    kernel_of = {"a-uniform": "rr_direct_kernel<int,int,4>", "a-zipf": "rr_direct_kernel<int,int,4>",
-                 "b-uniform": "rr_privatised_kernel<float,int,4>", "b-zipf": "rr_privatised_kernel<float,int,4>",
-                 "pool-bwd": "rr_affine_kernel<float>"}
-    achieved = ab[dom] / part_ms[dom] / 1e6
+    achieved = per_rank(dom) / part_ms[dom] / sc
     out = {
-        "metric": "meta-op GB/s", "value": world * total_bytes / step_ms / 1e6, "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int32/f32", "data": "synthetic",
-        "config": {"workload": "config 1: reindex_reduce scatter-add 2^24 -> 2^20 int32 and -> 4096 fp32 "
-                               "(uniform + Zipf 1.1 indices) + 2x2 max-pool backward [64,128,112,112] fp32",
-                   "algorithmic_bytes_per_step": total_bytes,
-                   "l2": "no flush: every part's input exceeds the 126 MB L2 and five inputs rotate",
-                   "parallelism": f"dp{world} (per-rank inputs; NCCL all-reduce of the scatter bins)" if world > 1 else "1 GPU"},
+        "metric": wl.metric, "value": job_work / step_ms / sc, "unit": wl.unit, "n_gpus": world,
+        "steps": args.steps, "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.description, "algorithmic_work_per_step": job_work,
+                   "l2": "no flush: every part touches more than the 126 MB L2 and the parts rotate",
+                   "parallelism": f"dp{world}" if world > 1 else "1 GPU"},
         "clocks": clocks.summary(),
-        "e2e": {"value": world * total_bytes / e2e_ms / 1e6, "unit": "GB/s", "ms_per_step": e2e_ms,
+        "e2e": {"value": job_work / e2e_ms / sc if e2e_steps else None, "unit": wl.unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": args.steps * sum(1 if n == "pool-bwd" else 2 for n in names),
-        "roofline": {"bound": "hbm", "kernel": kernel_of[dom], "part": dom, "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
-                     "note": "achieved = algorithmic bytes of the part / CUDA-event time of the part "
-                             "(its main kernel plus the init-fill or fold kernel)"},
+        "gpu_launches": args.steps * sum(wl.launches[n] for n in names),
+        "roofline": {"bound": wl.bound, "kernel": wl.kernel_of[dom], "part": dom, "achieved": achieved, "peak": peak,
+                     "unit": wl.unit, "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                     "note": "achieved = algorithmic work of the part / CUDA-event time of the part (its main kernel "
+                             "plus its small helper launches)"},
         "parts": parts,
+        "device_status": status,
     }
     if args.cpu_baseline and world == 1:
-        from oracle import c_oracle as co
-        t0 = time.perf_counter()
-        done = 0
-        for nm in ("a-uniform", "a-zipf", "b-uniform", "b-zipf"):
-            v, i, b = host[nm]
-            co.scatter_add(v, i, b)
-            done += ab[nm]
-        co.pool2x2_bwd(host["pool-bwd"][0][:8])
-        done += ab["pool-bwd"] * 8 // POOL_SHAPE[0]
-        dt = time.perf_counter() - t0
-        out["cpu_baseline"] = {"value": done / dt / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-                               "sample": "one pass: the four scatter parts at full size + 8 of 64 pool-bwd images",
-                               "note": "scatter loops are serial in the reference (1 core); pool-bwd uses OpenMP"}
+        done, secs, sample = wl.cpu(names)
+        out["cpu_baseline"] = {"value": done / secs / (1e9 if wl.unit == "GB/s" else 1e12), "unit": wl.unit,
+                               "cores": os.cpu_count(), "kind": "port", "sample": sample}
     print(json.dumps(out))
 
 

@@ -68,37 +68,45 @@ bn_stats_kernel(const T* __restrict__ x, float* __restrict__ stats, int N_, int 
 }
 
 // TX / TY: element types of x and y (the reference's dtype rules make bfloat16 x * float32 w a float32 result
-// unless amp flags keep 16 bit, so both combinations occur).
+// unless amp flags keep 16 bit, so both combinations occur). Every CTA first derives the per-channel scale and shift
+// into shared memory, then the whole tensor is walked as one stream of 16-byte vectors (one division per vector
+// finds the channel), so small planes do not leave lanes idle.
 template <typename TX, typename TY>
 __global__ void __launch_bounds__(256)
 bn_apply_kernel(const TX* __restrict__ x, TY* __restrict__ y, const float* __restrict__ stats, float rcount,
                 const float* __restrict__ gamma, const float* __restrict__ beta, float eps, int relu,
                 int64_t planes, int C, int64_t HW) {
-    constexpr int V = IO<TX>::N > IO<TY>::N ? IO<TX>::N : IO<TY>::N;     // elements per thread step
-    const bool vec = (HW % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
-    for (int64_t pl = blockIdx.x; pl < planes; pl += gridDim.x) {
-        const int c = (int)(pl % C);
+    extern __shared__ float ws_[];                 // [2][C]: scale, shift
+    float* sw = ws_; float* sb = ws_ + C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
         const float mean = stats[c] * rcount;
         const float var = fmaxf(stats[C + c] * rcount - mean * mean, 0.f);
         const float w = (gamma ? gamma[c] : 1.f) / sqrtf(var + eps);
-        const float b = (beta ? beta[c] : 0.f) - mean * w;
-        const TX* p = x + pl * HW;
-        TY* q = y + pl * HW;
-        if (vec) {
-            for (int64_t i = threadIdx.x * V; i < HW; i += (int64_t)blockDim.x * V) {
-                float v[V];
+        sw[c] = w; sb[c] = (beta ? beta[c] : 0.f) - mean * w;
+    }
+    __syncthreads();
+    constexpr int V = IO<TX>::N > IO<TY>::N ? IO<TX>::N : IO<TY>::N;     // elements per thread step
+    const bool vec = (HW % V == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+    if (vec) {
+        const int64_t vpp = HW / V, nvec = planes * vpp;
+        for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+            const int c = (int)((v / vpp) % C);
+            const float w = sw[c], b = sb[c];
+            const int64_t i = v * V;
+            float f[V];
 #pragma unroll
-                for (int k = 0; k < V / IO<TX>::N; k++) IO<TX>::load(p + i + k * IO<TX>::N, v + k * IO<TX>::N);
+            for (int k = 0; k < V / IO<TX>::N; k++) IO<TX>::load(x + i + k * IO<TX>::N, f + k * IO<TX>::N);
 #pragma unroll
-                for (int e = 0; e < V; e++) { float o = v[e] * w + b; v[e] = relu ? fmaxf(o, 0.f) : o; }
+            for (int e = 0; e < V; e++) { float o = f[e] * w + b; f[e] = relu ? fmaxf(o, 0.f) : o; }
 #pragma unroll
-                for (int k = 0; k < V / IO<TY>::N; k++) IO<TY>::store(q + i + k * IO<TY>::N, v + k * IO<TY>::N);
-            }
-        } else {
-            for (int64_t i = threadIdx.x; i < HW; i += blockDim.x) {
-                float o = IO<TX>::ld(p + i) * w + b;
-                IO<TY>::st(q + i, relu ? fmaxf(o, 0.f) : o);
-            }
+            for (int k = 0; k < V / IO<TY>::N; k++) IO<TY>::store(y + i + k * IO<TY>::N, f + k * IO<TY>::N);
+        }
+    } else {
+        const int64_t n = planes * HW;
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+            const int c = (int)((i / HW) % C);
+            float o = IO<TX>::ld(x + i) * sw[c] + sb[c];
+            IO<TY>::st(y + i, relu ? fmaxf(o, 0.f) : o);
         }
     }
 }
@@ -145,9 +153,11 @@ extern "C" int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, doubl
     if (numel(x) == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t planes = (int64_t)N_ * C;
-    unsigned grid = (unsigned)(planes < (int64_t)kNumSMs * 16 ? planes : (int64_t)kNumSMs * 16);
+    B200JT_CHECK_ARG(C <= 6144, "at most 6144 channels");
+    unsigned grid = grid_for(numel(x) / 8 + 1, 256);
+    const size_t smem = sizeof(float) * 2 * C;
     const float rc_ = (float)(1.0 / count);
-#define B200JT_BN(TX, TY) bn_apply_kernel<TX, TY><<<grid, 256, 0, st>>>((const TX*)x->ptr, (TY*)y->ptr, stats, rc_, gamma, beta, (float)eps, relu, planes, C, HW)
+#define B200JT_BN(TX, TY) bn_apply_kernel<TX, TY><<<grid, 256, smem, st>>>((const TX*)x->ptr, (TY*)y->ptr, stats, rc_, gamma, beta, (float)eps, relu, planes, C, HW)
     if (x->dtype == B200JT_FLOAT32) { if (y->dtype == B200JT_FLOAT32) B200JT_BN(float, float); else B200JT_BN(float, __nv_bfloat16); }
     else { if (y->dtype == B200JT_FLOAT32) B200JT_BN(__nv_bfloat16, float); else B200JT_BN(__nv_bfloat16, __nv_bfloat16); }
 #undef B200JT_BN

@@ -28,7 +28,8 @@ constexpr int PATCH = 8;                            // spatial patch edge: 8 x 8
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STATS_BYTES = 2 * BN * 4;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + STATS_BYTES;
+constexpr int OUT_STAGE_BYTES = 2 * 64 * 64 * 2;      // TMA-store staging: 2 patches x 64 channels x 64 pixels
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + STATS_BYTES + OUT_STAGE_BYTES;
 constexpr int THREADS = 192;
 
 struct ConvArgs {
@@ -46,8 +47,13 @@ __device__ __forceinline__ void patch_coords(const ConvArgs& A, int64_t q, int& 
     w0 = (r % A.tiles_w) * PATCH;
 }
 
+// TMA_OUT: the epilogue stages 64 channels x 128 pixels of bf16 in shared memory ([patch][channel][8x8]) and writes
+// them to y (NCHW) with two 4-D TMA box stores; edges are clipped by the tensor map. Needs OW % 8 == 0 (16-byte row
+// pitch); otherwise the lanes store their values directly.
+template <bool TMA_OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_y,
                  __nv_bfloat16* __restrict__ y, float* __restrict__ stats, const __grid_constant__ ConvArgs A) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -59,6 +65,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* sstat = (float*)(smem + STAGES * STAGE_BYTES + 256);      // [2][BN] per-CTA channel sums
+    unsigned char* stage_out = smem + STAGES * STAGE_BYTES + 256 + STATS_BYTES;   // [2 patches][64 ch][64 px] bf16
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total = A.tiles_m * A.tiles_n;
@@ -155,23 +162,72 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const bool valid = q < A.patches && oh < A.OH && ow < A.OW;
             __nv_bfloat16* yp = y + ((int64_t)n * A.Co) * plane + (int64_t)oh * A.OW + ow;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+            const bool issuer = threadIdx.x == 64;          // first epilogue thread drives the TMA stores
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ch++) {
+                const int co0 = tn * BN + ch * 32;
+                if (TMA_OUT && (ch & 1) == 0) {
+                    // staging buffer free again? (the previous round's stores must have read it)
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
                 uint32_t v[32];
                 tmem_ld32(taddr + ch * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int co0 = tn * BN + ch * 32;
+                float f[32];
+                if (TMA_OUT) {
+                    __nv_bfloat16* sp = reinterpret_cast<__nv_bfloat16*>(stage_out) + (r >> 6) * (64 * 64) + (ch & 1) * (32 * 64) + (r & 63);
 #pragma unroll
-                for (int e = 0; e < 32; e++) {
-                    const __nv_bfloat16 b = __float2bfloat16(__uint_as_float(v[e]));
-                    const bool st = valid && co0 + e < A.Co;
-                    if (st) yp[(int64_t)(co0 + e) * plane] = b;
-                    if (stats) {
-                        // statistics of the value as stored; lanes of a warp are 32 pixels of the same channel
-                        float f = st ? __bfloat162float(b) : 0.f, f2 = f * f;
+                    for (int e = 0; e < 32; e++) {
+                        const __nv_bfloat16 b = __float2bfloat16(__uint_as_float(v[e]));
+                        sp[e * 64] = b;
+                        f[e] = (valid && co0 + e < A.Co) ? __bfloat162float(b) : 0.f;
+                    }
+                } else {
 #pragma unroll
-                        for (int d = 16; d > 0; d >>= 1) { f += __shfl_xor_sync(0xffffffffu, f, d); f2 += __shfl_xor_sync(0xffffffffu, f2, d); }
-                        if (lane == 0) { atomicAdd(sstat + ch * 32 + e, f); atomicAdd(sstat + BN + ch * 32 + e, f2); }
+                    for (int e = 0; e < 32; e++) {
+                        const __nv_bfloat16 b = __float2bfloat16(__uint_as_float(v[e]));
+                        const bool st = valid && co0 + e < A.Co;
+                        if (st) yp[(int64_t)(co0 + e) * plane] = b;
+                        f[e] = st ? __bfloat162float(b) : 0.f;      // statistics of the value as stored
+                    }
+                }
+                if (stats) {
+                    // lanes are 32 pixels, f[] 32 channels: halving exchange leaves lane L with the sum of channel L
+                    float g[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) g[e] = f[e] * f[e];
+#pragma unroll
+                    for (int s = 16; s > 0; s >>= 1) {
+                        const bool up = (lane & s) != 0;
+#pragma unroll
+                        for (int i = 0; i < s; i++) {
+                            const float keep = up ? f[i + s] : f[i], send = up ? f[i] : f[i + s];
+                            f[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+                            const float keep2 = up ? g[i + s] : g[i], send2 = up ? g[i] : g[i + s];
+                            g[i] = keep2 + __shfl_xor_sync(0xffffffffu, send2, s);
+                        }
+                    }
+                    atomicAdd(sstat + ch * 32 + lane, f[0]);
+                    atomicAdd(sstat + BN + ch * 32 + lane, g[0]);
+                }
+                if (TMA_OUT && (ch & 1) == 1) {
+                    // 64 channels staged: make the writes visible to the async proxy, then two box stores
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (issuer) {
+                        const int cbase = tn * BN + (ch - 1) * 32;
+#pragma unroll
+                        for (int pp = 0; pp < 2; pp++) {
+                            const int64_t qq = 2 * (int64_t)tm + pp;
+                            if (qq < A.patches && cbase < A.Co) {
+                                int nn, hh0, ww0;
+                                patch_coords(A, qq, nn, hh0, ww0);
+                                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                                             ::"l"(&map_y), "r"(smem_u32(stage_out + pp * (64 * 64 * 2))), "r"(ww0), "r"(hh0), "r"(cbase), "r"(nn) : "memory");
+                            }
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
             }
@@ -179,6 +235,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + buf);
         }
+        if (TMA_OUT && threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -194,10 +251,11 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 }
 
 // ---- layout passes -----------------------------------------------------------------------------------------
-// in[b][R][Cn] -> out[b][Cn][R] (bf16), 64x64 tiles, 16-byte global accesses on both sides.
+// in[b][R][Cn] -> out[b][Cn][R] (bf16), 64x64 tiles, 16-byte global accesses on both sides. The tile is kept as
+// 32-bit pairs with an odd pitch (33 words) so that the column reads of the second phase spread over the banks.
 __global__ void __launch_bounds__(256)
 transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn) {
-    __shared__ __nv_bfloat16 tile[64][72];
+    __shared__ __nv_bfloat16 tile[64][66];
     const int64_t boff = (int64_t)blockIdx.z * R * Cn;
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
     const int j = threadIdx.x & 7, i = threadIdx.x >> 3;          // 8 chunks of 8 elements x 32 rows
@@ -206,13 +264,14 @@ transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat1
     for (int p = 0; p < 2; p++) {
         const int r = r0 + i + p * 32, c = c0 + j * 8;
         __align__(16) __nv_bfloat16 v[8];
-        if (r < R && vec_in && c + 8 <= Cn) *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(in + boff + (int64_t)r * Cn + c);
+        if (r < R && vec_in && c + 8 <= Cn) *reinterpret_cast<uint4*>(v) = __ldcs(reinterpret_cast<const uint4*>(in + boff + (int64_t)r * Cn + c));
         else {
 #pragma unroll
             for (int e = 0; e < 8; e++) v[e] = (r < R && c + e < Cn) ? in[boff + (int64_t)r * Cn + c + e] : __float2bfloat16(0.f);
         }
+        uint32_t* row = reinterpret_cast<uint32_t*>(&tile[i + p * 32][0]);
 #pragma unroll
-        for (int e = 0; e < 8; e++) tile[i + p * 32][j * 8 + e] = v[e];
+        for (int e = 0; e < 4; e++) row[j * 4 + e] = reinterpret_cast<const uint32_t*>(v)[e];
     }
     __syncthreads();
 #pragma unroll
@@ -222,7 +281,7 @@ transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat1
         __align__(16) __nv_bfloat16 v[8];
 #pragma unroll
         for (int e = 0; e < 8; e++) v[e] = tile[j * 8 + e][i + p * 32];
-        if (vec_out && r + 8 <= R) *reinterpret_cast<uint4*>(out + boff + (int64_t)c * R + r) = *reinterpret_cast<uint4*>(v);
+        if (vec_out && r + 8 <= R) __stcs(reinterpret_cast<uint4*>(out + boff + (int64_t)c * R + r), *reinterpret_cast<uint4*>(v));
         else {
             for (int e = 0; e < 8 && r + e < R; e++) out[boff + (int64_t)c * R + r + e] = v[e];
         }
@@ -263,6 +322,18 @@ static bool make_map_w(CUtensorMap* map, const void* base, const ConvShape& s) {
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static bool make_map_y(CUtensorMap* map, const void* base, const ConvShape& s) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)s.OW, (cuuint64_t)s.OH, (cuuint64_t)s.Co, (cuuint64_t)s.N};
+    cuuint64_t strides[3] = {(cuuint64_t)s.OW * 2, (cuuint64_t)s.OH * s.OW * 2, (cuuint64_t)s.Co * s.OH * s.OW * 2};
+    cuuint32_t box[4] = {PATCH, PATCH, 64, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace tcconv
 
 bool conv2d_tc_supported(const ConvShape& s, const void* x, const void* w, const void* y) {
@@ -300,13 +371,22 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     A.tiles_m = (int)((A.patches + 1) / 2); A.tiles_n = (s.Co + BN - 1) / BN;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(conv_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(conv_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(conv_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
     B200JT_CUDA(attr_err);
+    // TMA stores need a 16-byte aligned base and row pitch
+    const bool tma_out = (s.OW % 8 == 0) && ((uintptr_t)y % 16 == 0);
+    CUtensorMap my = mx;
+    if (tma_out && !make_map_y(&my, y, s)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed (y)");
     float* fused = (stats && A.tiles_n == 1) ? stats : nullptr;
     if (fused) B200JT_CUDA(cudaMemsetAsync(stats, 0, sizeof(float) * 2 * s.Co, st));
     const int total = A.tiles_m * A.tiles_n;
     const int grid = total < kNumSMs ? total : kNumSMs;
-    conv_bf16_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, (__nv_bfloat16*)y, fused, A);
+    if (tma_out) conv_bf16_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, my, (__nv_bfloat16*)y, fused, A);
+    else conv_bf16_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, my, (__nv_bfloat16*)y, fused, A);
     B200JT_LAUNCH_CHECK();
     return fused ? 1 : 0;      // 1: statistics were produced by the epilogue
 }

@@ -72,6 +72,17 @@ __device__ __forceinline__ float group_reduce(float v, float* sm) {
     }
 }
 
+template <int N>
+__device__ __forceinline__ void load_gb(const float* __restrict__ gamma, const float* __restrict__ beta, int c, float* g, float* b) {
+#pragma unroll
+    for (int q = 0; q < N / 4; q++) {
+        const float4 g4 = gamma ? __ldg(reinterpret_cast<const float4*>(gamma + c + q * 4)) : make_float4(1.f, 1.f, 1.f, 1.f);
+        const float4 b4 = beta ? __ldg(reinterpret_cast<const float4*>(beta + c + q * 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        g[q * 4] = g4.x; g[q * 4 + 1] = g4.y; g[q * 4 + 2] = g4.z; g[q * 4 + 3] = g4.w;
+        b[q * 4] = b4.x; b[q * 4 + 1] = b4.y; b[q * 4 + 2] = b4.z; b[q * 4 + 3] = b4.w;
+    }
+}
+
 // GROUP threads per row, VPT 16-byte vectors per thread; requires cols % Vec16<T>::N == 0 and
 // cols <= GROUP * VPT * N.
 template <typename T, int GROUP, int VPT, int OP>
@@ -83,6 +94,16 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
     __shared__ float sm[8];
     const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
     const int nvec = cols / N;
+    // a thread owns the same columns in every row it visits: keep their gamma / beta in registers when they fit
+    constexpr bool CACHE_GB = (OP == ROW_LAYERNORM) && (VPT * N <= 16);
+    float gm[CACHE_GB ? VPT : 1][N], bt[CACHE_GB ? VPT : 1][N];
+    if constexpr (CACHE_GB) {
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int vi = t + k * GROUP;
+            if (vi < nvec) load_gb<N>(gamma, beta, vi * N, gm[k], bt[k]);
+        }
+    }
     for (int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + g; row < rows;
          row += (int64_t)gridDim.x * ROWS_PER_CTA) {
         const T* xr = x + row * cols;
@@ -113,19 +134,15 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
             for (int k = 0; k < VPT; k++) {
                 const int vi = t + k * GROUP;
                 if (vi < nvec) {
-                    float o[N], gm[N], bt[N];
+                    float o[N];
+                    if constexpr (CACHE_GB) {
 #pragma unroll
-                    for (int q = 0; q < N / 4; q++) {
-                        const int c = vi * N + q * 4;
-                        float4 g4 = gamma ? __ldg(reinterpret_cast<const float4*>(gamma + c)) : make_float4(1.f, 1.f, 1.f, 1.f);
-                        float4 b4 = beta ? __ldg(reinterpret_cast<const float4*>(beta + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        gm[q * 4] = g4.x; gm[q * 4 + 1] = g4.y; gm[q * 4 + 2] = g4.z; gm[q * 4 + 3] = g4.w;
-                        bt[q * 4] = b4.x; bt[q * 4 + 1] = b4.y; bt[q * 4 + 2] = b4.z; bt[q * 4 + 3] = b4.w;
-                    }
+                        for (int e = 0; e < N; e++) { const float w = gm[k][e] * rstd; o[e] = v[k][e] * w + (bt[k][e] - mean * w); }
+                    } else {
+                        float g1[N], b1[N];
+                        load_gb<N>(gamma, beta, vi * N, g1, b1);
 #pragma unroll
-                    for (int e = 0; e < N; e++) {
-                        const float w = gm[e] * rstd;
-                        o[e] = v[k][e] * w + (bt[e] - mean * w);
+                        for (int e = 0; e < N; e++) { const float w = g1[e] * rstd; o[e] = v[k][e] * w + (b1[e] - mean * w); }
                     }
                     Vec16<T>::store(yr + (int64_t)vi * N, o);
                 }
@@ -143,19 +160,19 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
 #pragma unroll
                 for (int e = 0; e < N; e++) {
                     const float a = v[k][e] - m;
-                    const float ex = expf(a);
+                    const float ex = __expf(a);             // ex2.approx(a * log2 e): relative error ~1e-6 for a in [-88, 0]
                     s += (t + k * GROUP < nvec) ? ex : 0.f;
                     v[k][e] = (OP == ROW_SOFTMAX) ? ex : a;
                 }
             s = group_reduce<GROUP, false>(s, sm);
-            const float ls = logf(s);
+            const float ls = logf(s), inv = 1.0f / s;
 #pragma unroll
             for (int k = 0; k < VPT; k++) {
                 const int vi = t + k * GROUP;
                 if (vi < nvec) {
                     float o[N];
 #pragma unroll
-                    for (int e = 0; e < N; e++) o[e] = (OP == ROW_SOFTMAX) ? v[k][e] / s : v[k][e] - ls;
+                    for (int e = 0; e < N; e++) o[e] = (OP == ROW_SOFTMAX) ? v[k][e] * inv : v[k][e] - ls;
                     Vec16<T>::store(yr + (int64_t)vi * N, o);
                 }
             }
@@ -211,7 +228,7 @@ static int launch_rows(const T* x, T* y, const float* gamma, const float* beta, 
 #define B200JT_ROW(GROUP, VPT)                                                                      \
     do { const int rpc = 256 / GROUP;                                                               \
          int64_t ctas = (rows + rpc - 1) / rpc;                                                     \
-         unsigned grid = (unsigned)(ctas < (int64_t)kNumSMs * 64 ? ctas : (int64_t)kNumSMs * 64);   \
+         unsigned grid = (unsigned)(ctas < (int64_t)kNumSMs * 16 ? ctas : (int64_t)kNumSMs * 16);   \
          row_reg_kernel<T, GROUP, VPT, OP><<<grid, 256, 0, st>>>(x, y, gamma, beta, rows, (int)cols, eps); } while (0)
     if (vec_ok && nvec <= 32 * 8) {
         if (nvec <= 32) B200JT_ROW(32, 1);

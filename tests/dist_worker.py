@@ -1,0 +1,40 @@
+"""Worker of tests/test_dist_gloo.py: run under torchrun with 2 ranks on CPU (gloo)."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import jittor_b200 as jt                      # noqa: E402
+from jittor_b200 import dist, executor, nn    # noqa: E402
+
+
+def main():
+    dist.init("gloo")
+    rank, world = dist.rank(), dist.world_size()
+    assert dist.in_mpi() and world == 2
+    # 1. the all-reduce node sums the ranks' tensors (host tensors stand in for device buffers)
+    v = jt.Var([4], "float32")
+    v._data = torch.full((4,), float(rank + 1))
+    out = v.mpi_all_reduce("add")
+    out.sync()
+    assert torch.equal(out._data, torch.full((4,), 3.0)), out._data
+    # 2. 'mean' is add / world_size, as in the reference
+    m = v.mpi_all_reduce("mean")
+    assert m._op.kind == "binary" and m._op.attrs["op"] == "divide"
+    assert m._op.inputs[0]._op.kind == "mpi_all_reduce" and m._op.inputs[1]._const == 2
+    # 3. sync BatchNorm (+ReLU, fed by a conv) is still recognised as one plan with the all-reduce inside
+    x, w = jt.Var([4, 8, 10, 10], "float32"), jt.Var([16, 8, 3, 3], "float32")
+    bn = nn.BatchNorm(16, is_train=True, sync=True)
+    y = nn.relu(bn(nn.conv2d(x, w, None, 1, 1, 1)))
+    plan = executor._match_batchnorm(y)
+    assert plan is not None and plan.leaves[:2] == [x, w]
+    # 4. rank-divergent data, identical reduction: packed statistics message
+    stats = torch.tensor([float(rank), 10.0 * (rank + 1)])
+    torch.distributed.all_reduce(stats)
+    assert stats.tolist() == [1.0, 30.0]
+    print(f"rank {rank} ok")
+
+
+if __name__ == "__main__":
+    main()
