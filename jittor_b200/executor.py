@@ -557,11 +557,13 @@ def _match_scale_shift(root):
     return dict(x=x, weight=weight, bias=bias, eps=float(_const(eps)), xmean=xmean, x2mean=x2mean, wb=wb, bb=bb)
 
 
-def _mean_of(node, src_check):
-    """node = reduce.mean(u, ...) possibly followed by mpi_all_reduce(add)/world. Returns (reduce node, synced)."""
+def _mean_of(node, src_check, unwrap=lambda n: n):
+    """node = reduce.mean(u, ...) possibly followed by mpi_all_reduce(add)/world, with `unwrap` stripping a
+    dtype round trip on either side of the all-reduce. Returns (reduce node, synced)."""
     synced = False
+    node = unwrap(node)
     if _node(node, "binary", op="divide") and _node(node._op.inputs[0], "mpi_all_reduce"):
-        node = node._op.inputs[0]._op.inputs[0]
+        node = unwrap(node._op.inputs[0]._op.inputs[0])
         synced = True
     if not _node(node, "reduce", op="mean"):
         return None
@@ -674,8 +676,8 @@ def _match_batchnorm(v):
             return n._op.inputs[0]
         return n
 
-    r1 = _mean_of(unwrap(m["xmean"]), is_x)
-    r2 = _mean_of(unwrap(m["x2mean"]), is_xx)
+    r1 = _mean_of(m["xmean"], is_x, unwrap)
+    r2 = _mean_of(m["x2mean"], is_xx, unwrap)
     if r1 is None or r2 is None or r1[1] != r2[1]:
         return None
     for r in (r1, r2):

@@ -29,6 +29,12 @@ def main():
     y = nn.relu(bn(nn.conv2d(x, w, None, 1, 1, 1)))
     plan = executor._match_batchnorm(y)
     assert plan is not None and plan.leaves[:2] == [x, w]
+    xb, wb = jt.Var([4, 64, 16, 16], "bfloat16"), jt.Var([64, 64, 3, 3], "bfloat16")
+    bnb = nn.BatchNorm(64, is_train=True, sync=True)
+    with jt.flag_scope(amp_reg=2):
+        yb = nn.relu(bnb(nn.conv2d(xb, wb, None, 1, 1, 1)))
+    planb = executor._match_batchnorm(yb)
+    assert yb.dtype == "bfloat16" and planb is not None and planb.leaves[:2] == [xb, wb]
     # 4. rank-divergent data, identical reduction: packed statistics message
     stats = torch.tensor([float(rank), 10.0 * (rank + 1)])
     torch.distributed.all_reduce(stats)
