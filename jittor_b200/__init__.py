@@ -6,7 +6,8 @@ from ._capi import B200Error
 from .flags import flags, flag_scope
 from .var import (Var, array, to_var, empty, zeros, ones, reindex, reindex_var, reindex_reduce, broadcast,
                   broadcast_var, reduce, binary, unary, ternary, ternary_out_hint, reshape, transpose, index)
-from . import dtypes, executor, nn, dist
+from . import dtypes, executor, nn, dist, op_register
+from .op_register import code, has_op, get_op_info, register_op, compile_custom_op, compile_custom_ops
 from .dtypes import binary_dtype_infer
 
 __version__ = "0.1.0"
@@ -37,6 +38,9 @@ for _op in dtypes.DTYPES:
 float = float32   # noqa: F821
 int = int32       # noqa: F821
 matmul = nn.matmul
+
+
+op_register._register_builtins()
 
 
 def cast(x, dtype):

@@ -7,7 +7,7 @@
 
 namespace b200jt {
 
-constexpr int BM = 64, BN = 64, BK = 16;
+constexpr int BK = 16;
 
 template <typename T> __device__ __forceinline__ float to_f(T v);
 template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
@@ -16,23 +16,32 @@ template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
 
+// A loader describes the two operands as functions A(m, k), B(k, n) and the output offset C(m, n). The part of the
+// address that depends only on the row m is computed once per thread (Row) because a thread stages the same rows of
+// the A tile in every k step.
 struct MatmulLoader {
     int64_t a_sm, a_sk, b_sk, b_sn, c_sm;
-    template <typename T> __device__ __forceinline__ float A(const T* a, int64_t m, int64_t k) const { return to_f<T>(a[m * a_sm + k * a_sk]); }
+    struct Row { int64_t off; };
+    __device__ __forceinline__ Row row(int64_t m) const { return Row{m * a_sm}; }
+    template <typename T> __device__ __forceinline__ float A(const T* a, const Row& r, int64_t k) const { return to_f<T>(a[r.off + k * a_sk]); }
     template <typename T> __device__ __forceinline__ float B(const T* b, int64_t k, int64_t n) const { return to_f<T>(b[k * b_sk + n * b_sn]); }
     __device__ __forceinline__ int64_t C(int64_t m, int64_t n) const { return m * c_sm + n; }
 };
 
 struct ConvLoader {
     int C_, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
-    template <typename T> __device__ __forceinline__ float A(const T* x, int64_t m, int64_t k) const {
-        const int ow = (int)(m % OW); int64_t t = m / OW;
+    struct Row { int64_t base; int ih0, iw0; };          // image base offset and top-left input coordinate of the window
+    __device__ __forceinline__ Row row(int64_t m) const {
+        const int ow = (int)(m % OW); const int64_t t = m / OW;
         const int oh = (int)(t % OH); const int64_t n = t / OH;
-        const int kw = (int)(k % KW); int t2 = (int)(k / KW);
+        return Row{n * C_ * (int64_t)H * W, oh * sh - ph, ow * sw - pw};
+    }
+    template <typename T> __device__ __forceinline__ float A(const T* x, const Row& r, int64_t k) const {
+        const int kw = (int)(k % KW); const int t2 = (int)(k / KW);
         const int kh = t2 % KH; const int c = t2 / KH;
-        const int ih = oh * sh - ph + kh * dh, iw = ow * sw - pw + kw * dw;
+        const int ih = r.ih0 + kh * dh, iw = r.iw0 + kw * dw;
         if (ih < 0 || ih >= H || iw < 0 || iw >= W) return 0.f;
-        return to_f<T>(x[((n * C_ + c) * H + ih) * (int64_t)W + iw]);
+        return to_f<T>(x[r.base + ((int64_t)c * H + ih) * W + iw]);
     }
     template <typename T> __device__ __forceinline__ float B(const T* w, int64_t k, int64_t n) const {
         return to_f<T>(w[n * ((int64_t)C_ * KH * KW) + k]);
@@ -43,50 +52,74 @@ struct ConvLoader {
     }
 };
 
-template <typename T, typename L>
+// TM x TN output tile per CTA of 256 threads (16 x 16), (TM/16) x (TN/16) outputs per thread.
+template <typename T, typename L, int TM, int TN>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ c,
                  int64_t M, int64_t N, int64_t K, const L ld) {
-    __shared__ float As[BK][BM + 4];
-    __shared__ float Bs[BK][BN + 4];
+    constexpr int RM = TM / 16, RN = TN / 16;
+    constexpr int LA = TM * BK / 256, LB = TN * BK / 256;         // staged elements per thread
+    __shared__ float As[BK][TM + 4];
+    __shared__ float Bs[BK][TN + 4];
     const int tid = threadIdx.x;
-    const int tx = tid % 16, ty = tid / 16;            // 16 x 16 threads, 4 x 4 outputs each
-    const int64_t m0 = (int64_t)blockIdx.x * BM, n0 = (int64_t)blockIdx.y * BN;
-    float acc[4][4] = {};
+    const int tx = tid % 16, ty = tid / 16;
+    const int64_t m0 = (int64_t)blockIdx.x * TM, n0 = (int64_t)blockIdx.y * TN;
+    // consecutive threads walk m (the contiguous axis of NCHW pixels); a thread keeps its row across k steps
+    const int a_mm = tid % TM, a_k0 = tid / TM;
+    const int64_t a_m = m0 + a_mm;
+    const typename L::Row arow = ld.row(a_m < M ? a_m : 0);
+    const int b_nn = tid % TN, b_k0 = tid / TN;
+    float acc[RM][RN] = {};
     for (int64_t k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            // A tile: consecutive threads walk m (the contiguous axis of NCHW pixels)
-            const int e = tid + i * 256;
-            const int mm = e % BM, kk = e / BM;
-            const int64_t m = m0 + mm, k = k0 + kk;
-            As[kk][mm] = (m < M && k < K) ? ld.template A<T>(a, m, k) : 0.f;
-            const int nn = e % BN, kb = e / BN;
-            const int64_t n = n0 + nn, k2 = k0 + kb;
-            Bs[kb][nn] = (n < N && k2 < K) ? ld.template B<T>(b, k2, n) : 0.f;
+        for (int i = 0; i < LA; i++) {
+            const int kk = a_k0 + i * (256 / TM);
+            const int64_t k = k0 + kk;
+            As[kk][a_mm] = (a_m < M && k < K) ? ld.template A<T>(a, arow, k) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < LB; i++) {
+            const int kb = b_k0 + i * (256 / TN);
+            const int64_t n = n0 + b_nn, k2 = k0 + kb;
+            Bs[kb][b_nn] = (n < N && k2 < K) ? ld.template B<T>(b, k2, n) : 0.f;
         }
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < BK; kk++) {
-            float av[4], bv[4];
+            float av[RM], bv[RN];
 #pragma unroll
-            for (int i = 0; i < 4; i++) { av[i] = As[kk][ty * 4 + i]; bv[i] = Bs[kk][tx * 4 + i]; }
+            for (int i = 0; i < RM; i++) av[i] = As[kk][ty * RM + i];
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+            for (int j = 0; j < RN; j++) bv[j] = Bs[kk][tx * RN + j];
 #pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+            for (int i = 0; i < RM; i++)
+#pragma unroll
+                for (int j = 0; j < RN; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int64_t m = m0 + ty * 4 + i;
+    for (int i = 0; i < RM; i++) {
+        const int64_t m = m0 + ty * RM + i;
         if (m >= M) continue;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int64_t n = n0 + tx * 4 + j;
+        for (int j = 0; j < RN; j++) {
+            const int64_t n = n0 + tx * RN + j;
             if (n < N) c[ld.C(m, n)] = from_f<T>(acc[i][j]);
         }
+    }
+}
+
+// 64x64 tiles when they fill the machine, 32x32 tiles for small problems (latency-bound: more CTAs in flight).
+template <typename T, typename L>
+static void launch_simt(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, const L& ld, cudaStream_t st) {
+    const int64_t big = ((M + 63) / 64) * ((N + 63) / 64);
+    if (big >= 2 * kNumSMs) {
+        dim3 grid((unsigned)((M + 63) / 64), (unsigned)((N + 63) / 64));
+        gemm_simt_kernel<T, L, 64, 64><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
+    } else {
+        dim3 grid((unsigned)((M + 31) / 32), (unsigned)((N + 31) / 32));
+        gemm_simt_kernel<T, L, 32, 32><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
     }
 }
 
@@ -96,11 +129,8 @@ int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int
     L.a_sm = trans_a ? 1 : K; L.a_sk = trans_a ? M : 1;
     L.b_sk = trans_b ? 1 : N; L.b_sn = trans_b ? K : 1;
     L.c_sm = N;
-    dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));
-    if (dtype == B200JT_FLOAT32)
-        gemm_simt_kernel<float, MatmulLoader><<<grid, 256, 0, st>>>((const float*)a, (const float*)b, (float*)c, M, N, K, L);
-    else
-        gemm_simt_kernel<__nv_bfloat16, MatmulLoader><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)c, M, N, K, L);
+    if (dtype == B200JT_FLOAT32) launch_simt<float, MatmulLoader>(a, b, c, M, N, K, L, st);
+    else launch_simt<__nv_bfloat16, MatmulLoader>(a, b, c, M, N, K, L, st);
     B200JT_LAUNCH_CHECK();
     return 0;
 }
@@ -108,11 +138,8 @@ int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st) {
     ConvLoader L{s.C, s.H, s.W, s.Co, s.KH, s.KW, s.OH, s.OW, s.sh, s.sw, s.ph, s.pw, s.dh, s.dw};
     const int64_t M = (int64_t)s.N * s.OH * s.OW, N = s.Co, K = (int64_t)s.C * s.KH * s.KW;
-    dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));
-    if (dtype == B200JT_FLOAT32)
-        gemm_simt_kernel<float, ConvLoader><<<grid, 256, 0, st>>>((const float*)x, (const float*)w, (float*)y, M, N, K, L);
-    else
-        gemm_simt_kernel<__nv_bfloat16, ConvLoader><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, M, N, K, L);
+    if (dtype == B200JT_FLOAT32) launch_simt<float, ConvLoader>(x, w, y, M, N, K, L, st);
+    else launch_simt<__nv_bfloat16, ConvLoader>(x, w, y, M, N, K, L, st);
     B200JT_LAUNCH_CHECK();
     return 0;
 }

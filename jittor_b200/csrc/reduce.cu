@@ -140,11 +140,22 @@ reduce_row_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, i
                 const float* p = (const float*)x + obase + i0;
                 if (istride == 1 && (((uintptr_t)p) & 15) == 0 && ((i1 - i0) & 3) == 0) {
                     const int64_t nv = (i1 - i0) >> 2;
-                    for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
-                        const float4 f = __ldg(reinterpret_cast<const float4*>(p) + v);
-                        float e0 = f.x, e1 = f.y, e2 = f.z, e3 = f.w;
-                        if (op == OP_MEAN) { e0 *= rcount; e1 *= rcount; e2 *= rcount; e3 *= rcount; }
-                        acc = reduce_combine<C>(op, reduce_combine<C>(op, reduce_combine<C>(op, reduce_combine<C>(op, acc, e0), e1), e2), e3);
+                    // four independent 16-byte loads in flight per thread
+                    for (int64_t v0 = threadIdx.x; v0 < nv; v0 += 4 * blockDim.x) {
+                        float4 f[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int64_t v = v0 + u * blockDim.x;
+                            const float idv = reduce_init<float>(op == OP_MEAN ? OP_ADD : op, B200JT_FLOAT32);
+                            f[u] = v < nv ? __ldcs(reinterpret_cast<const float4*>(p) + v) : make_float4(idv, idv, idv, idv);
+                            if (op == OP_MEAN && v >= nv) f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            float e0 = f[u].x, e1 = f[u].y, e2 = f[u].z, e3 = f[u].w;
+                            if (op == OP_MEAN) { e0 *= rcount; e1 *= rcount; e2 *= rcount; e3 *= rcount; }
+                            acc = reduce_combine<C>(op, reduce_combine<C>(op, reduce_combine<C>(op, reduce_combine<C>(op, acc, e0), e1), e2), e3);
+                        }
                     }
                     done = true;
                 }
@@ -189,12 +200,18 @@ reduce_col_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, i
         if (nr == 1) {
             const int64_t st = A.rstride[0];
             int64_t r = r0;
-            for (; r + 4 <= r1; r += 4) {
-                C v0 = load_x<TX, C>(x, xdt, base + r * st), v1 = load_x<TX, C>(x, xdt, base + (r + 1) * st);
-                C v2 = load_x<TX, C>(x, xdt, base + (r + 2) * st), v3 = load_x<TX, C>(x, xdt, base + (r + 3) * st);
-                if (op == OP_MEAN) { v0 *= rcount; v1 *= rcount; v2 *= rcount; v3 *= rcount; }
-                acc0 = reduce_combine<C>(op, acc0, v0); acc1 = reduce_combine<C>(op, acc1, v1);
-                acc2 = reduce_combine<C>(op, acc2, v2); acc3 = reduce_combine<C>(op, acc3, v3);
+            for (; r + 8 <= r1; r += 8) {
+                C v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] = load_x<TX, C>(x, xdt, base + (r + u) * st);
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    if (op == OP_MEAN) v[u] *= rcount;
+                    if ((u & 3) == 0) acc0 = reduce_combine<C>(op, acc0, v[u]);
+                    else if ((u & 3) == 1) acc1 = reduce_combine<C>(op, acc1, v[u]);
+                    else if ((u & 3) == 2) acc2 = reduce_combine<C>(op, acc2, v[u]);
+                    else acc3 = reduce_combine<C>(op, acc3, v[u]);
+                }
             }
             for (; r < r1; r++) {
                 C v = load_x<TX, C>(x, xdt, base + r * st);
@@ -259,7 +276,7 @@ static ReducePlan make_plan(const b200jt_tensor* x, const b200jt_tensor* y, uint
     const bool inner_reduced = n > 0 && red[n - 1];
     P.row = inner_reduced && A.n_red >= 256;
     A.split = 1; A.chunk = A.n_red;
-    const int64_t target = 4LL * kNumSMs;
+    const int64_t target = 8LL * kNumSMs;
     if (P.row) {
         if (A.n_out < target && A.n_red >= 16384) {
             int64_t s = (target + A.n_out - 1) / A.n_out;

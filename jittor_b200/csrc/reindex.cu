@@ -21,8 +21,9 @@ struct AffineArgs {
 };
 
 // I = index type (32-bit arithmetic when every tensor is below 2^31 elements, as the reference's index_t).
-// All loops over axes are fully unrolled with uniform guards so that the coordinate arrays stay in registers.
-template <typename T, typename I, int VEC>
+// NL / NX are compile-time upper bounds of the two ranks: all loops over axes are fully unrolled to them (with
+// uniform guards for the actual ranks) so that the coordinate arrays stay in registers.
+template <typename T, typename I, int VEC, int NL, int NX>
 __global__ void __launch_bounds__(256)
 reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_constant__ AffineArgs A,
                       int64_t n_vec, T fill) {
@@ -32,22 +33,22 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
          v += (int64_t)gridDim.x * blockDim.x) {
         // vectors never straddle rows: the host picks VEC | innermost extent
         const int64_t flat = v * VEC;
-        I iv[kMaxDims];
+        I iv[NL];
         U r = (U)flat;
 #pragma unroll
-        for (int d = kMaxDims - 1; d >= 0; d--) {
+        for (int d = NL - 1; d >= 0; d--) {
             iv[d] = 0;
             if (d < nl) { const U s = (U)A.loop_shape[d]; const U q = r / s; iv[d] = (I)(r - q * s); r = q; }
         }
-        I xid[kMaxDims], xinner[kMaxDims], xs[kMaxDims];
+        I xid[NX], xinner[NX], xs[NX];
 #pragma unroll
-        for (int d = 0; d < kMaxDims; d++) {
+        for (int d = 0; d < NX; d++) {
             xid[d] = 0; xinner[d] = 0; xs[d] = 1;
             if (d < nx) {
                 I a = (I)A.c0[d];
 #pragma unroll
-                for (int j = 0; j < kMaxDims; j++)
-                    if (j < nl) { const I cf = (I)A.coef[d][j]; if (cf != 0) a += cf * iv[j]; }
+                for (int j = 0; j < NL; j++)
+                    if (j < nl) a += (I)A.coef[d][j] * iv[j];
                 xid[d] = a; xinner[d] = (I)A.coef[d][nl - 1]; xs[d] = (I)A.x_shape[d];
             }
         }
@@ -57,7 +58,7 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
             bool over = false;
             int64_t off = 0;
 #pragma unroll
-            for (int d = 0; d < kMaxDims; d++) {
+            for (int d = 0; d < NX; d++) {
                 if (d < nx) {
                     const I id = xid[d] + xinner[d] * (I)e;
                     over |= (id < 0) | (id >= xs[d]);
@@ -78,6 +79,19 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
             }
         }
     }
+}
+
+template <typename T, int VEC>
+static void launch_affine(const T* xp, T* yp, const AffineArgs& A, int64_t nv, T fill, bool small, cudaStream_t st) {
+    const unsigned grid = grid_for(nv, 256);
+    const int nl = A.ndim_loop, nx = A.ndim_x;
+#define B200JT_AFF(NL, NX) reindex_affine_kernel<T, int32_t, VEC, NL, NX><<<grid, 256, 0, st>>>(xp, yp, A, nv, fill)
+    if (!small) { reindex_affine_kernel<T, int64_t, VEC, kMaxDims, kMaxDims><<<grid, 256, 0, st>>>(xp, yp, A, nv, fill); return; }
+    if (nl <= 2) { if (nx <= 2) B200JT_AFF(2, 2); else if (nx <= 4) B200JT_AFF(2, 4); else B200JT_AFF(2, kMaxDims); }
+    else if (nl <= 4) { if (nx <= 2) B200JT_AFF(4, 2); else if (nx <= 4) B200JT_AFF(4, 4); else B200JT_AFF(4, kMaxDims); }
+    else if (nl <= 8) { if (nx <= 2) B200JT_AFF(8, 2); else if (nx <= 4) B200JT_AFF(8, 4); else B200JT_AFF(8, kMaxDims); }
+    else { if (nx <= 4) B200JT_AFF(kMaxDims, 4); else B200JT_AFF(kMaxDims, kMaxDims); }
+#undef B200JT_AFF
 }
 
 template <typename T, typename I>
@@ -139,21 +153,11 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
         memcpy(A.c0, P.c0, sizeof(A.c0));
         memcpy(A.coef, P.coef, sizeof(A.coef));
         const int64_t inner = P.loop_shape[P.ndim_loop - 1];
-        int vec = 16 / (int)sizeof(T);
-        if (vec > 8) vec = 8;
-        while (vec > 1 && (inner % vec != 0 || ((uintptr_t)yp % (vec * sizeof(T))) != 0)) vec >>= 1;
-        const int64_t nv = n / vec;
-        const unsigned grid = grid_for(nv, 256);
-#define B200JT_AFFINE(V)                                                                             \
-        if (small) reindex_affine_kernel<T, int32_t, V><<<grid, 256, 0, st>>>(xp, yp, A, nv, fill);   \
-        else       reindex_affine_kernel<T, int64_t, V><<<grid, 256, 0, st>>>(xp, yp, A, nv, fill)
-        switch (vec) {
-            case 8: B200JT_AFFINE(8); break;
-            case 4: B200JT_AFFINE(4); break;
-            case 2: B200JT_AFFINE(2); break;
-            default: B200JT_AFFINE(1);
-        }
-#undef B200JT_AFFINE
+        // one 16-byte (8-byte for 1-byte elements) output vector per thread when rows and alignment allow it
+        constexpr int VMAX = 16 / sizeof(T) > 8 ? 8 : 16 / sizeof(T);
+        const bool vec_ok = VMAX > 1 && inner % VMAX == 0 && ((uintptr_t)yp % (VMAX * sizeof(T))) == 0;
+        if (vec_ok) launch_affine<T, VMAX>(xp, yp, A, n / VMAX, fill, small, st);
+        else launch_affine<T, 1>(xp, yp, A, n, fill, small, st);
     } else {
         unsigned grid = grid_for(n, 256);
         if (small) reindex_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>(xp, yp, P, n, fill);

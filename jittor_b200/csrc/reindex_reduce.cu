@@ -276,13 +276,27 @@ rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __re
     }
 }
 
+// Folds the per-CTA rows into x in a fixed order (deterministic): a CTA owns 32 bins, its 8 warps take the rows
+// r = w, w+8, ... (coalesced 128-byte reads), then warp 0 combines the 8 partial sums in warp order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rr_fold_partials_kernel(const T* __restrict__ partial, T* __restrict__ x, int bins, int rows, int op, bool is_bool) {
-    for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < bins; b += gridDim.x * blockDim.x) {
+    __shared__ T part[8][33];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int b0 = blockIdx.x * 32; b0 < bins; b0 += gridDim.x * 32) {
+        const int b = b0 + lane;
         T acc = init_value<T>(op, is_bool);
-        for (int r = 0; r < rows; r++) acc = apply_op<T>(op, acc, partial[(int64_t)r * bins + b]);
-        x[b] = acc;
+        if (b < bins)
+            for (int r = w; r < rows; r += 8) acc = apply_op<T>(op, acc, partial[(int64_t)r * bins + b]);
+        part[w][lane] = acc;
+        __syncthreads();
+        if (w == 0 && b < bins) {
+            T t = part[0][lane];
+#pragma unroll
+            for (int k = 1; k < 8; k++) t = apply_op<T>(op, t, part[k][lane]);
+            x[b] = t;
+        }
+        __syncthreads();
     }
 }
 
@@ -435,7 +449,7 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         else     { if (aligned) B200JT_PRIV(int32_t, VEC); else B200JT_PRIV(int32_t, 1); }
 #undef B200JT_PRIV
         B200JT_LAUNCH_CHECK();
-        rr_fold_partials_kernel<T><<<grid_for(bins, 256), 256, 0, st>>>(partial, xp, (int)bins, kPrivGrid, op, is_bool);
+        rr_fold_partials_kernel<T><<<grid_for((bins + 31) / 32 * 256, 256), 256, 0, st>>>(partial, xp, (int)bins, kPrivGrid, op, is_bool);
         B200JT_LAUNCH_CHECK();
         return 0;
     }

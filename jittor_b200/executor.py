@@ -238,8 +238,20 @@ _RUNNERS = {"reindex": _run_reindex, "reindex_reduce": _run_reindex_reduce, "bro
 
 
 # --------------------------------------------------------------------------------- contraction patterns
+_AFFINE_CACHE = {}
+
+
 def index_affine(loop_shape, x_shape, indexes):
-    """(coef[d][j], c0[d]) if all indexes are affine in the loop variables, else None."""
+    """(coef[d][j], c0[d]) if all indexes are affine in the loop variables, else None (memoised)."""
+    key = (tuple(loop_shape), tuple(x_shape), tuple(indexes))
+    if key not in _AFFINE_CACHE:
+        if len(_AFFINE_CACHE) > 4096:
+            _AFFINE_CACHE.clear()
+        _AFFINE_CACHE[key] = _index_affine(loop_shape, x_shape, indexes)
+    return _AFFINE_CACHE[key]
+
+
+def _index_affine(loop_shape, x_shape, indexes):
     n = len(indexes)
     ls = (ctypes.c_int64 * len(loop_shape))(*loop_shape)
     xs = (ctypes.c_int64 * len(x_shape))(*x_shape)

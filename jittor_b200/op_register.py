@@ -1,0 +1,259 @@
+"""Op registry and the inline-CUDA op `jt.code`.
+
+The reference keeps a name -> constructor registry (python/jittor/src/ops/op_register.h:14-33; `has_op`,
+`get_op_info(name).get_constructor`) that its tuners use to find relay ops and that `compile_custom_ops` fills with
+user ops. Here the registry maps the same names to Python callables over Vars: the built-in meta-operators, the relay
+names the tuners look up (`cublas_matmul`, `cudnn_conv`, `nccl_all_reduce`), and anything registered with
+`register_op`.
+
+`code(shape, dtype, inputs, cuda_src=..., cuda_header=...)` is the inline op of python/jittor/src/ops/code_op.h:24-46
+with the macro set of python/jittor/src/ops/code_op.cc:186-231: `@ARGS_DEF`, `@ARGS`, `@PRECALC`, `@inK(i,j,..)`,
+`@out(i,..)` / `@outK(..)`, `inK_shapeJ`, `inK_strideJ`, `inK_type`, leading `__global__` / `__device__` functions
+hoisted out of the body. The source is compiled with nvcc for sm_100a into a cache directory, loaded with ctypes and
+launched on the current stream. C++ op classes written against the reference's own headers cannot be compiled here;
+`compile_custom_op` says so.
+"""
+import ctypes
+import hashlib
+import os
+import re
+import subprocess
+import tempfile
+
+from . import var as V
+from ._capi import B200Error, TORCH_DTYPES, require_cuda
+
+_REGISTRY = {}
+
+
+class OpInfo:
+    def __init__(self, name, fn, doc=""):
+        self.name, self.fn, self.doc = name, fn, doc
+
+    def get_constructor(self, *signature):
+        return self.fn
+
+    def __call__(self, *a, **k):
+        return self.fn(*a, **k)
+
+
+def register_op(name, fn, doc=""):
+    """Registers `fn(*vars, **attrs) -> Var` under `name` (the role of op_registe)."""
+    _REGISTRY[name] = OpInfo(name, fn, doc)
+    return fn
+
+
+def has_op(name):
+    return name in _REGISTRY
+
+
+def get_op_info(name):
+    if name not in _REGISTRY:
+        raise KeyError(f"Op {name} not registered")
+    return _REGISTRY[name]
+
+
+def compile_custom_op(header, source, op_name, warp=True):
+    raise NotImplementedError(
+        "compile_custom_op builds C++ Op classes against the reference's core headers, which this package does not "
+        "provide; use jittor_b200.code(..., cuda_src=...) for inline CUDA or register_op(name, fn) for a Python op")
+
+
+compile_custom_ops = compile_custom_op
+
+
+def _register_builtins():
+    from . import nn, dist
+    register_op("reindex", V.reindex)
+    register_op("reindex_reduce", V.reindex_reduce)
+    register_op("broadcast_to", V.broadcast)
+    register_op("reduce", V.reduce)
+    register_op("binary", V.binary)
+    register_op("unary", V.unary)
+    register_op("ternary", V.ternary)
+    register_op("code", code)
+
+    def cublas_matmul(a, b, trans_a, trans_b):
+        """Relay signature of matmul_tuner.cc:93-95."""
+        a, b = V.to_var(a), V.to_var(b)
+        if trans_a:
+            a = a.transpose(1, 0)
+        return nn.matmul_transpose(a, b) if trans_b else nn.matmul(a, b)
+
+    def cudnn_conv(x, w, strideh, stridew, paddingh, paddingw, dilationh=1, dilationw=1, groups=1,
+                   xformat="abcd", wformat="oihw", yformat=""):
+        """Relay signature of conv_tuner.cc:370-373 (NCHW / OIHW only)."""
+        if xformat != "abcd" or wformat != "oihw" or yformat not in ("", "abcd"):
+            raise NotImplementedError("only abcd / oihw layouts")
+        return nn.conv2d(x, w, None, (strideh, stridew), (paddingh, paddingw), (dilationh, dilationw), groups)
+
+    register_op("cublas_matmul", cublas_matmul)
+    register_op("cudnn_conv", cudnn_conv)
+    register_op("nccl_all_reduce", lambda x: dist.mpi_all_reduce(x, "add"))
+    register_op("mpi_all_reduce", dist.mpi_all_reduce)
+
+
+# ----------------------------------------------------------------------------------------------- jt.code
+_CTYPES = {"bool": "bool", "int8": "int8_t", "int16": "int16_t", "int32": "int32_t", "int64": "int64_t", "uint8": "uint8_t",
+           "float16": "__half", "bfloat16": "__nv_bfloat16", "float32": "float", "float64": "double"}
+_CACHE_DIR = os.environ.get("JITTOR_B200_CACHE", os.path.join(os.path.expanduser("~"), ".cache", "jittor_b200"))
+_LOADED = {}
+
+
+def _split_leading_functions(src):
+    """Leading functions (text starting with '_', i.e. __global__/__device__, up to the matching brace) are hoisted
+    in front of the entry function; the rest is its body (code_op.cc:155-178)."""
+    i, n, head = 0, len(src), []
+    while i < n:
+        if src[i] in " \t\n":
+            head.append(src[i])
+            i += 1
+        elif src[i] == "_":
+            depth = 0
+            while i < n:
+                head.append(src[i])
+                if src[i] == "{":
+                    depth += 1
+                elif src[i] == "}":
+                    depth -= 1
+                    if depth == 0:
+                        i += 1
+                        break
+                i += 1
+        else:
+            break
+    return "".join(head), src[i:]
+
+
+def expand_code_source(cuda_src, cuda_header, in_meta, out_meta):
+    """Returns the full .cu text. in_meta / out_meta: lists of (dtype name, ndim)."""
+    names = [f"in{i}" for i in range(len(in_meta))] + [f"out{i}" for i in range(len(out_meta))]
+    metas = list(in_meta) + list(out_meta)
+    args_def, args, precalc, defines = [], [], [], []
+    for nm, (dt, nd) in zip(names, metas):
+        defines.append(f"typedef {_CTYPES[dt]} {nm}_type;")
+        defines.append(f"#define {nm}_stride{nd - 1} 1")
+        args_def.append(f"{nm}_type* __restrict__ {nm}_p")
+        args.append(f"{nm}_p")
+        for j in range(nd):
+            args_def.append(f"index_t {nm}_shape{j}")
+            args.append(f"{nm}_shape{j}")
+        for j in range(nd - 2, -1, -1):
+            precalc.append(f"auto {nm}_stride{j} = {nm}_stride{j + 1} * {nm}_shape{j + 1};")
+    args_def.append("int __tmp")
+    args.append("0")
+
+    def access(m):
+        nm = m.group(1)
+        if nm == "out":
+            nm = "out0"
+        idx = [s.strip() for s in _split_args(m.group(2))]
+        return f"{nm}_p[" + "+".join(f"({e})*{nm}_stride{j}" for j, e in enumerate(idx)) + "]"
+
+    def expand(text):
+        text = text.replace("@ARGS_DEF", ", ".join(args_def)).replace("@ARGS", ", ".join(args))
+        text = text.replace("@PRECALC", "\n".join(precalc))
+        prev = None
+        while prev != text:          # nested accesses resolve inside-out
+            prev = text
+            text = re.sub(r"@(in\d+|out\d*)\(([^()@]*(?:\([^()@]*\)[^()@]*)*)\)", access, text)
+        if "@" in text:
+            bad = re.search(r"@\w+", text)
+            raise B200Error(f"jt.code: unsupported macro {bad.group(0) if bad else '@'}")
+        # launches without an explicit stream go to the stream the executor passes in
+        return re.sub(r"<<<\s*([^,<>]+?)\s*,\s*([^,<>]+?)\s*>>>", r"<<<\1, \2, 0, __stream>>>", text)
+
+    head, body = _split_leading_functions(cuda_src)
+    unpack = []
+    k = 0
+    for nm, (dt, nd) in zip(names, metas):
+        unpack.append(f"    {nm}_type* __restrict__ {nm}_p = ({nm}_type*)__ptrs[{names.index(nm)}];")
+        for j in range(nd):
+            unpack.append(f"    index_t {nm}_shape{j} = (index_t)__shapes[{k}];")
+            k += 1
+    return "\n".join([
+        "#include <cuda_runtime.h>", "#include <cuda_bf16.h>", "#include <cuda_fp16.h>", "#include <stdint.h>",
+        "typedef int64_t int64; typedef int32_t int32; typedef float float32; typedef double float64;",
+        "typedef int index_t;", *defines, "static cudaStream_t __stream = 0;", expand(cuda_header or ""), expand(head),
+        'extern "C" int b200jt_code_entry(void** __ptrs, const int64_t* __shapes, void* __s) {',
+        "    __stream = (cudaStream_t)__s;", *unpack, expand(body),
+        "    return (int)cudaGetLastError();", "}", ""])
+
+
+def _split_args(s):
+    out, depth, cur = [], 0, []
+    for ch in s:
+        if ch == "," and depth == 0:
+            out.append("".join(cur))
+            cur = []
+        else:
+            depth += ch == "("
+            depth -= ch == ")"
+            cur.append(ch)
+    out.append("".join(cur))
+    return out
+
+
+def compile_code_source(text):
+    """nvcc -> shared object in the cache directory (keyed by the source hash); returns its path."""
+    key = hashlib.sha1(text.encode()).hexdigest()[:20]
+    so = os.path.join(_CACHE_DIR, f"code_{key}.so")
+    if not os.path.exists(so):
+        os.makedirs(_CACHE_DIR, exist_ok=True)
+        with tempfile.TemporaryDirectory() as tmp:
+            cu = os.path.join(tmp, f"code_{key}.cu")
+            with open(cu, "w") as f:
+                f.write(text)
+            cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-shared",
+                   "-Xcompiler", "-fPIC", "-o", so + ".tmp", cu]
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise B200Error("jt.code: nvcc failed\n" + res.stderr[-4000:] + "\n--- source ---\n" + text)
+            os.replace(so + ".tmp", so)
+    return so
+
+
+def code(shape, dtype, inputs=(), cuda_src="", cuda_header="", cpu_src="", cpu_header="", **unused):
+    """Inline CUDA op. `shape` / `dtype` may be lists for several outputs (then a list of Vars is returned)."""
+    if not cuda_src:
+        raise B200Error("jt.code: only cuda_src is supported (there is no CPU path)")
+    multi = len(shape) > 0 and isinstance(shape[0], (list, tuple, V.Shape))
+    shapes = [list(s) for s in shape] if multi else [list(shape)]
+    dtypes = list(dtype) if multi else [dtype]
+    inputs = [V.to_var(i) for i in inputs]
+    in_meta = [(str(v.dtype), v.ndim) for v in inputs]
+    out_meta = [(str(V.dt.canon(d)), len(s)) for d, s in zip(dtypes, shapes)]
+    text = expand_code_source(cuda_src, cuda_header, in_meta, out_meta)
+
+    def run(*tensors):
+        import torch
+        require_cuda()
+        so = compile_code_source(text)
+        lib = _LOADED.get(so)
+        if lib is None:
+            lib = _LOADED[so] = ctypes.CDLL(so)
+            lib.b200jt_code_entry.restype = ctypes.c_int
+            lib.b200jt_code_entry.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p]
+        outs = [torch.empty(s, dtype=TORCH_DTYPES[m[0]], device="cuda") for s, m in zip(shapes, out_meta)]
+        allt = list(tensors) + outs
+        ptrs = (ctypes.c_void_p * len(allt))(*[t.data_ptr() for t in allt])
+        dims = [d for t, (_, nd) in zip(allt, in_meta + out_meta) for d in (list(t.shape) + [1] * nd)[:nd]]
+        shp = (ctypes.c_int64 * max(len(dims), 1))(*dims)
+        rc = lib.b200jt_code_entry(ptrs, shp, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise B200Error(f"jt.code: CUDA error {rc} after launch")
+        return outs
+
+    if not multi:
+        return V.Var(shapes[0], out_meta[0][0], V.Op("custom", inputs, fn=lambda *t: run(*t)[0]))
+    # several outputs: one node computes all of them, the others pick their tensor from it
+    box = {}
+
+    def run_all(*t):
+        box["outs"] = run(*t)
+        return box["outs"][0]
+
+    first = V.Var(shapes[0], out_meta[0][0], V.Op("custom", inputs, fn=run_all))
+    rest = [V.Var(s, m[0], V.Op("custom", [first], fn=(lambda k: lambda _f: box["outs"][k])(k)))
+            for k, (s, m) in enumerate(zip(shapes[1:], out_meta[1:]), start=1)]
+    return [first] + rest
