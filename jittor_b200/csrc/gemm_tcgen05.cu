@@ -21,16 +21,23 @@ namespace b200jt {
 
 namespace tc {
 
-constexpr int BM = 128, BN = 256, BK = 64;          // BK * 2 B = 128 B = swizzle width
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int BM = 128, BN = 256, BK = 64;          // one MMA tile; BK * 2 B = 128 B = swizzle width
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
 constexpr int THREADS = 192;                        // 6 warps
 
+// MT = number of 128-row MMA tiles a CTA stacks per output tile. MT = 2 re-uses every Bt stage for two MMAs
+// (64 KB of operands per 8.4 MFLOP instead of 48 KB per 4.2 MFLOP), so the same 192 KB ring covers 1.5x more time
+// of tensor work -- enough to hide an HBM miss -- at the price of a single TMEM accumulator set (512 columns).
+template <int MT> struct Cfg {
+    static constexpr int STAGES = MT == 1 ? 4 : 3;
+    static constexpr int STAGE_BYTES = MT * A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int NBUF = 2 / MT;             // accumulator sets in the 512 TMEM columns
+};
+
 struct Tiles {
-    int tiles_m, tiles_n, total;
+    int tiles_m, tiles_n, total, G;                          // G: tile-rows per group (L2 reuse of the Bt tiles)
     __device__ __forceinline__ void coords(int t, int& m, int& n) const {
-        constexpr int G = 8;                                   // tile-rows per group (L2 reuse of the Bt tiles)
         const int per_group = G * tiles_n;
         const int g = t / per_group, r = t - g * per_group;
         const int rows = min(G, tiles_m - g * G);
@@ -39,9 +46,11 @@ struct Tiles {
     }
 };
 
+template <int MT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 __nv_bfloat16* __restrict__ c, int M, int N, int K) {
+                 __nv_bfloat16* __restrict__ c, int M, int N, int K, int group) {
+    constexpr int STAGES = Cfg<MT>::STAGES, STAGE_BYTES = Cfg<MT>::STAGE_BYTES, NBUF = Cfg<MT>::NBUF;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -55,12 +64,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     Tiles T;
-    T.tiles_m = (M + BM - 1) / BM; T.tiles_n = (N + BN - 1) / BN; T.total = T.tiles_m * T.tiles_n;
+    T.tiles_m = (M + MT * BM - 1) / (MT * BM); T.tiles_n = (N + BN - 1) / BN; T.total = T.tiles_m * T.tiles_n; T.G = group;
     const int k_blocks = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
+        for (int b = 0; b < NBUF; b++) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -85,8 +94,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 1))) break;
                     unsigned char* sa = smem + stage * STAGE_BYTES;
                     mbar_expect_tx(full + stage, STAGE_BYTES);
-                    tma_load_2d(sa, &map_a, full + stage, kb * BK, tm * BM);
-                    tma_load_2d(sa + A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
+#pragma unroll
+                    for (int j = 0; j < MT; j++) tma_load_2d(sa + j * A_BYTES, &map_a, full + stage, kb * BK, (tm * MT + j) * BM);
+                    tma_load_2d(sa + MT * A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -104,20 +114,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x, it++) {
-                const int buf = it & 1;
-                const uint32_t acc_phase = (it >> 1) & 1;
+                const int buf = it % NBUF;
+                const uint32_t acc_phase = (it / NBUF) & 1;
                 if (!(ok = mbar_wait(acc_empty + buf, acc_phase ^ 1, abort_flag, 2))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + buf * BN;
+                const uint32_t tmem_d = tmem_base + buf * (MT * BN);
                 for (int kb = 0; kb < k_blocks; kb++) {
                     if (!(ok = mbar_wait(full + stage, phase, abort_flag, 3))) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+                    const uint64_t db = make_smem_desc(sa + MT * A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        // advancing K by 16 bf16 = 32 B inside the swizzled 128-byte row: +2 in 16-byte units
-                        umma_f16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    for (int j = 0; j < MT; j++) {
+                        const uint64_t da = make_smem_desc(sa + j * A_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            // advancing K by 16 bf16 = 32 B inside the swizzled 128-byte row: +2 in 16-byte units
+                            umma_f16(tmem_d + j * BN, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                        }
                     }
                     umma_commit(empty + stage);                 // slot reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -133,14 +147,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool vec_ok = (N % 8 == 0) && (((uintptr_t)c & 15) == 0);
         for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x, it++) {
             int tm, tn; T.coords(t, tm, tn);
-            const int buf = it & 1;
-            const uint32_t acc_phase = (it >> 1) & 1;
+            const int buf = it % NBUF;
+            const uint32_t acc_phase = (it / NBUF) & 1;
             ok = mbar_wait(acc_full + buf, acc_phase, abort_flag, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = tm * BM + quad * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int j = 0; j < MT; j++) {
+            const int row = (tm * MT + j) * BM + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * (MT * BN) + j * BN;
             __nv_bfloat16* crow = c + (int64_t)row * N + (int64_t)tn * BN;
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ch++) {
@@ -163,6 +179,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         for (int e = 0; e < 32 && col0 + e < N; e++) crow[ch * 32 + e] = __float2bfloat16(__uint_as_float(r[e]));
                     }
                 }
+            }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -268,11 +285,26 @@ int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64
         return fail(-4, "matmul: cuTensorMapEncodeTiled failed");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM_BYTES);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES);
+    });
     B200JT_CUDA(attr_err);
-    const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
-    const int grid = tiles < kNumSMs ? tiles : kNumSMs;
-    gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K);
+    // 256-row tiles when they still fill the machine for several waves, 128-row tiles otherwise
+    const int64_t tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const char* genv = getenv("B200JT_GEMM_G");
+    const int group = genv ? atoi(genv) : 8;
+    const char* force = getenv("B200JT_GEMM_MT");
+    const bool two = force ? atoi(force) == 2 : tiles2 >= 4 * kNumSMs;
+    if (two) {
+        const int grid = tiles2 < kNumSMs ? (int)tiles2 : kNumSMs;
+        gemm_bf16_kernel<2><<<grid, THREADS, Cfg<2>::SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K, group);
+    } else {
+        const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+        const int grid = tiles < kNumSMs ? (int)tiles : kNumSMs;
+        gemm_bf16_kernel<1><<<grid, THREADS, Cfg<1>::SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K, group);
+    }
     B200JT_LAUNCH_CHECK();
     return 0;
 }
