@@ -1,6 +1,6 @@
 """Benchmark of the meta-operator hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|meta] [--impl reference]
 
 One JSON line on stdout (rank 0). Workloads are the benchmark configurations:
     c2 (default)  reindex_reduce scatter: 2^24 int32 -> 2^20 bins and 2^24 fp32 -> 4096 bins, uniform and Zipf(1.1)
@@ -341,7 +341,84 @@ class C5ConvBN:
         return done, time.perf_counter() - t0, f"{imgs} of {self.N} images per part, fp32 (OpenMP over image x channel)"
 
 
-WORKLOADS = {w.key: w for w in (C2Scatter, C3Rows, C4Matmul, C5ConvBN)}
+class MetaOps:
+    """The four meta-operators on their own (not fused): what a chain costs when it is not one of the recognised forms."""
+    key, metric, unit, bound, dtype, scaling = "meta", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
+    ROWS, COLS = 32768, 4096
+    description = ("plain meta-operators on [32768,4096] fp32: reindex (pad by 2 columns; transpose), reduce (row sum, "
+                   "column sum), broadcast fused into a binary add, and the conv-window reindex of config 0 "
+                   "([4,32,32,32] -> [4,64,32,32,32,3,3])")
+    kernel_of = {"reindex-pad": "reindex_affine_kernel", "reindex-transpose": "reindex_affine_kernel",
+                 "reindex-conv-window": "reindex_affine_kernel", "reduce-row-sum": "reduce_row_kernel",
+                 "reduce-col-sum": "reduce_col_kernel", "broadcast-add": "binary_kernel"}
+    launches = {"reindex-pad": 1, "reindex-transpose": 1, "reindex-conv-window": 1, "reduce-row-sum": 1,
+                "reduce-col-sum": 2, "broadcast-add": 1}
+    WIN = [4, 64, 32, 32, 32, 3, 3]
+
+    def work(self):
+        n = self.ROWS * self.COLS
+        win = int(np.prod(self.WIN))
+        return {"reindex-pad": 4 * n + 4 * self.ROWS * (self.COLS + 4), "reindex-transpose": 8 * n,
+                "reindex-conv-window": 4 * win + 4 * 4 * 32 * 32 * 32, "reduce-row-sum": 4 * n + 4 * self.ROWS,
+                "reduce-col-sum": 4 * n + 4 * self.COLS, "broadcast-add": 8 * n + 4 * self.COLS}
+
+    def setup(self, rank, world, jt, torch, multi):
+        self.jt, self.torch = jt, torch
+        g = torch.Generator().manual_seed(9 + rank)
+        self.hx = torch.randn(self.ROWS, self.COLS, generator=g).pin_memory()
+        self.x = [jt.array(self.hx), jt.array(self.hx.clone())]
+        self.b = jt.array(torch.randn(self.COLS, generator=g))
+        self.xs = jt.array(torch.rand(4, 32, 32, 32, generator=g))
+        self.k = 0
+        return list(self.kernel_of)
+
+    def _op(self, name, x):
+        if name == "reindex-pad":
+            return x.reindex([self.ROWS, self.COLS + 4], ["i0", "i1-2"])
+        if name == "reindex-transpose":
+            return x.reindex([self.COLS, self.ROWS], ["i1", "i0"])
+        if name == "reindex-conv-window":
+            return self.xs.reindex(self.WIN, ["i0", "i2", "i3*1-1+i5*1", "i4*1-1+i6*1"])
+        if name == "reduce-row-sum":
+            return x.sum(1)
+        if name == "reduce-col-sum":
+            return x.sum(0)
+        return x + self.b
+
+    def run(self, name):
+        self.k += 1
+        return self._op(name, self.x[self.k & 1]).sync()
+
+    def run_e2e(self, name):
+        x = self.jt.array(self.hx.cuda(non_blocking=True))
+        self._op(name, x).sync()
+
+    def e2e_bytes(self, names):
+        return len(names) * self.hx.numel() * 4, 0
+
+    def cpu(self, names):
+        rows = 2048
+        x = np.random.default_rng(9).normal(size=(rows, self.COLS)).astype(np.float32)
+        from oracle import meta_ops_ref as ref
+        done, t0 = 0, time.perf_counter()
+        for nm in names:
+            if nm == "reindex-pad":
+                ref.reindex(x, [rows, self.COLS + 4], ["i0", "i1-2"])
+            elif nm == "reindex-transpose":
+                ref.reindex(x, [self.COLS, rows], ["i1", "i0"])
+            elif nm == "reduce-row-sum":
+                ref.reduce(x, "add", (1,))
+            elif nm == "reduce-col-sum":
+                ref.reduce(x, "add", (0,))
+            elif nm == "broadcast-add":
+                ref.binary(x, np.ones(self.COLS, np.float32), "add")
+            else:
+                continue
+            done += self.work()[nm] * rows // self.ROWS
+        return max(done, 1), time.perf_counter() - t0, f"{rows} of {self.ROWS} rows per part through the numpy oracle (1 core)"
+
+
+WORKLOADS = {w.key: w for w in (C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps)}
 
 
 def scale_of(unit):

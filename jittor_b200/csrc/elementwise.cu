@@ -118,17 +118,6 @@ binary_kernel(const void* __restrict__ x, int xdt, const void* __restrict__ y, i
     }
 }
 
-// float32 fast path: contiguous, same shape, 128-bit accesses
-__global__ void __launch_bounds__(256)
-binary_f32_vec_kernel(const float4* __restrict__ x, const float4* __restrict__ y, float4* __restrict__ z, int64_t n4, int op) {
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
-        float4 a = x[i], b = y[i], r;
-        r.x = binary_compute<float>(op, a.x, b.x); r.y = binary_compute<float>(op, a.y, b.y);
-        r.z = binary_compute<float>(op, a.z, b.z); r.w = binary_compute<float>(op, a.w, b.w);
-        z[i] = r;
-    }
-}
-
 template <typename C>
 __global__ void __launch_bounds__(256)
 unary_kernel(const void* __restrict__ x, int xdt, void* __restrict__ y, int ydt, int64_t n, int op) {
@@ -149,6 +138,72 @@ ternary_kernel(const void* __restrict__ c, int cdt, const void* __restrict__ x, 
         if (!same_shape) bcast_offsets(A, i, xo, yo, co);
         bool cond = load_as<double>(c, cdt, co) != 0;
         store_as<C>(z, zdt, i, cond ? load_as<C>(x, xdt, xo) : load_as<C>(y, ydt, yo));
+    }
+}
+
+// ---- fast paths: float32 / bfloat16, op known at compile time, 16-byte accesses --------------------------------
+// Operand modes of y relative to z (x is always full; non-commutative ops get SWAP when the roles are exchanged):
+//   FULL   same shape                        SCALAR one element
+//   SUFFIX y is z's trailing block (bias over rows): index = i mod numel(y)
+//   PREFIX y has z's leading axes and size-1 trailing axes (per-row scalar): index = i / (numel(z) / numel(y))
+enum BMode : int { B_FULL = 0, B_SCALAR, B_SUFFIX, B_PREFIX };
+
+template <typename T> struct V16;
+template <> struct V16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void ld(const float* p, float* o) { float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+    static __device__ __forceinline__ void st(float* p, const float* o) { *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]); }
+    static __device__ __forceinline__ float ld1(const float* p) { return *p; }
+};
+template <> struct V16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float* o) {
+        uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+    }
+    static __device__ __forceinline__ void st(__nv_bfloat16* p, const float* o) {
+        uint4 v; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = v;
+    }
+    static __device__ __forceinline__ float ld1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+};
+
+template <typename T, int OP, int MODE, bool SWAP>
+__global__ void __launch_bounds__(256)
+binary_fast_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ z, uint32_t n_vec, uint32_t ydiv) {
+    constexpr int N = V16<T>::N;
+    for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
+        float a[N], b[N], r[N];
+        V16<T>::ld(x + (size_t)v * N, a);
+        if (MODE == B_FULL) V16<T>::ld(y + (size_t)v * N, b);
+        else if (MODE == B_SUFFIX) V16<T>::ld(y + (size_t)(v % ydiv) * N, b);          // ydiv = numel(y) / N
+        else {
+            const float s = V16<T>::ld1(y + (MODE == B_SCALAR ? 0u : v / ydiv));       // ydiv = inner / N
+#pragma unroll
+            for (int e = 0; e < N; e++) b[e] = s;
+        }
+#pragma unroll
+        for (int e = 0; e < N; e++) r[e] = SWAP ? binary_compute<float>(OP, b[e], a[e]) : binary_compute<float>(OP, a[e], b[e]);
+        V16<T>::st(z + (size_t)v * N, r);
+    }
+}
+
+template <typename TI, typename TO, int OP>
+__global__ void __launch_bounds__(256)
+unary_fast_kernel(const TI* __restrict__ x, TO* __restrict__ y, uint32_t n8) {
+    // 8 elements per thread: two 16-byte vectors of float32 or one of bfloat16
+    for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v < n8; v += gridDim.x * blockDim.x) {
+        float a[8];
+#pragma unroll
+        for (int k = 0; k < 8 / V16<TI>::N; k++) V16<TI>::ld(x + (size_t)v * 8 + k * V16<TI>::N, a + k * V16<TI>::N);
+#pragma unroll
+        for (int e = 0; e < 8; e++) a[e] = unary_compute<float>(OP, a[e], true);
+#pragma unroll
+        for (int k = 0; k < 8 / V16<TO>::N; k++) V16<TO>::st(y + (size_t)v * 8 + k * V16<TO>::N, a + k * V16<TO>::N);
     }
 }
 
@@ -194,6 +249,98 @@ static int compute_class(int a, int b) {
     return 2;
 }
 
+// classification of an operand against z for the fast path
+static int bcast_mode(const b200jt_tensor* t, const b200jt_tensor* z, int64_t* div, int vecn) {
+    const int64_t nt = numel(t), nz = numel(z);
+    if (nt == nz) { *div = 1; return B_FULL; }
+    if (nt == 1) { *div = 1; return B_SCALAR; }
+    // suffix: leading axes of t are 1, the rest equal z
+    int d = 0;
+    while (d < z->ndim && t->shape[d] == 1) d++;
+    bool suffix = true;
+    for (int k = d; k < z->ndim; k++) suffix &= t->shape[k] == z->shape[k];
+    if (suffix && nt % vecn == 0) { *div = nt / vecn; return B_SUFFIX; }
+    // prefix: trailing axes of t are 1, the leading ones equal z
+    int e = z->ndim;
+    while (e > 0 && t->shape[e - 1] == 1) e--;
+    bool prefix = true;
+    for (int k = 0; k < e; k++) prefix &= t->shape[k] == z->shape[k];
+    const int64_t inner = nz / nt;
+    if (prefix && inner % vecn == 0) { *div = inner / vecn; return B_PREFIX; }
+    return -1;
+}
+
+template <typename T, int OP>
+static bool launch_binary_fast(const void* x, const void* y, void* z, int mode, bool swap, uint32_t n_vec, uint32_t div, cudaStream_t st) {
+    const unsigned grid = grid_for(n_vec, 256);
+#define B200JT_BF(M, S) binary_fast_kernel<T, OP, M, S><<<grid, 256, 0, st>>>((const T*)x, (const T*)y, (T*)z, n_vec, div)
+    switch (mode) {
+        case B_FULL: if (swap) B200JT_BF(B_FULL, true); else B200JT_BF(B_FULL, false); break;
+        case B_SCALAR: if (swap) B200JT_BF(B_SCALAR, true); else B200JT_BF(B_SCALAR, false); break;
+        case B_SUFFIX: if (swap) B200JT_BF(B_SUFFIX, true); else B200JT_BF(B_SUFFIX, false); break;
+        case B_PREFIX: if (swap) B200JT_BF(B_PREFIX, true); else B200JT_BF(B_PREFIX, false); break;
+        default: return false;
+    }
+#undef B200JT_BF
+    return true;
+}
+
+template <typename T>
+static bool binary_fast(int op, const void* x, const void* y, void* z, int mode, bool swap, uint32_t n_vec, uint32_t div, cudaStream_t st) {
+    switch (op) {
+        case OP_ADD: return launch_binary_fast<T, OP_ADD>(x, y, z, mode, swap, n_vec, div, st);
+        case OP_SUB: return launch_binary_fast<T, OP_SUB>(x, y, z, mode, swap, n_vec, div, st);
+        case OP_MUL: return launch_binary_fast<T, OP_MUL>(x, y, z, mode, swap, n_vec, div, st);
+        case OP_DIV: return launch_binary_fast<T, OP_DIV>(x, y, z, mode, swap, n_vec, div, st);
+        case OP_MAX: return launch_binary_fast<T, OP_MAX>(x, y, z, mode, swap, n_vec, div, st);
+        case OP_MIN: return launch_binary_fast<T, OP_MIN>(x, y, z, mode, swap, n_vec, div, st);
+    }
+    return false;
+}
+
+// Returns true if the fast path took the call.
+static bool try_binary_fast(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* z, int op, cudaStream_t st) {
+    const int dt = z->dtype;
+    if ((dt != B200JT_FLOAT32 && dt != B200JT_BFLOAT16) || x->dtype != dt || y->dtype != dt) return false;
+    const int vecn = dt == B200JT_FLOAT32 ? 4 : 8;
+    const int64_t n = numel(z);
+    if (n % vecn != 0 || n / vecn >= (1LL << 32)) return false;
+    if ((((uintptr_t)x->ptr | (uintptr_t)y->ptr | (uintptr_t)z->ptr) & 15) != 0) return false;
+    const b200jt_tensor* full = x; const b200jt_tensor* other = y; bool swap = false;
+    if (numel(x) != n) { full = y; other = x; swap = true; }
+    if (numel(full) != n) return false;
+    int64_t div = 1;
+    const int mode = bcast_mode(other, z, &div, vecn);
+    if (mode < 0 || div >= (1LL << 32)) return false;
+    if (dt == B200JT_FLOAT32) return binary_fast<float>(op, full->ptr, other->ptr, z->ptr, mode, swap, (uint32_t)(n / vecn), (uint32_t)div, st);
+    return binary_fast<__nv_bfloat16>(op, full->ptr, other->ptr, z->ptr, mode, swap, (uint32_t)(n / vecn), (uint32_t)div, st);
+}
+
+template <typename TI, typename TO>
+static bool unary_fast(int uc, const void* x, void* y, uint32_t n8, cudaStream_t st) {
+    const unsigned grid = grid_for(n8, 256);
+#define B200JT_UF(OP) case OP: unary_fast_kernel<TI, TO, OP><<<grid, 256, 0, st>>>((const TI*)x, (TO*)y, n8); return true
+    switch (uc) {
+        B200JT_UF(U_CAST); B200JT_UF(U_NEG); B200JT_UF(U_ABS); B200JT_UF(U_EXP); B200JT_UF(U_LOG); B200JT_UF(U_SQRT);
+        B200JT_UF(U_TANH); B200JT_UF(U_SIGMOID);
+    }
+#undef B200JT_UF
+    return false;
+}
+
+static bool try_unary_fast(const b200jt_tensor* x, const b200jt_tensor* y, int uc, cudaStream_t st) {
+    const bool xf = x->dtype == B200JT_FLOAT32, xb = x->dtype == B200JT_BFLOAT16;
+    const bool yf = y->dtype == B200JT_FLOAT32, yb = y->dtype == B200JT_BFLOAT16;
+    const int64_t n = numel(x);
+    if (!(xf || xb) || !(yf || yb) || n % 8 != 0 || n / 8 >= (1LL << 32)) return false;
+    if ((((uintptr_t)x->ptr | (uintptr_t)y->ptr) & 15) != 0) return false;
+    const uint32_t n8 = (uint32_t)(n / 8);
+    if (xf && yf) return unary_fast<float, float>(uc, x->ptr, y->ptr, n8, st);
+    if (xf && yb) return unary_fast<float, __nv_bfloat16>(uc, x->ptr, y->ptr, n8, st);
+    if (xb && yf) return unary_fast<__nv_bfloat16, float>(uc, x->ptr, y->ptr, n8, st);
+    return unary_fast<__nv_bfloat16, __nv_bfloat16>(uc, x->ptr, y->ptr, n8, st);
+}
+
 }  // namespace b200jt
 
 using namespace b200jt;
@@ -216,9 +363,8 @@ extern "C" int b200jt_binary(const b200jt_tensor* x, const b200jt_tensor* y, con
     int cc = cmp ? compute_class(x->dtype, y->dtype) : compute_class(z->dtype, z->dtype);
     if (!cmp && oc == OP_POW && cc == 2) cc = 2;
     const unsigned grid = grid_for(n, 256);
-    if (same && cc == 0 && x->dtype == B200JT_FLOAT32 && y->dtype == B200JT_FLOAT32 && z->dtype == B200JT_FLOAT32 &&
-        n % 4 == 0 && ((uintptr_t)x->ptr | (uintptr_t)y->ptr | (uintptr_t)z->ptr) % 16 == 0) {
-        binary_f32_vec_kernel<<<grid_for(n / 4, 256), 256, 0, st>>>((const float4*)x->ptr, (const float4*)y->ptr, (float4*)z->ptr, n / 4, oc);
+    if (try_binary_fast(x, y, z, oc, st)) {
+        // float32 / bfloat16 with a compile-time op and 16-byte accesses
     } else if (cc == 0) binary_kernel<float><<<grid, 256, 0, st>>>(x->ptr, x->dtype, y->ptr, y->dtype, z->ptr, z->dtype, A, n, oc, same);
     else if (cc == 1)   binary_kernel<double><<<grid, 256, 0, st>>>(x->ptr, x->dtype, y->ptr, y->dtype, z->ptr, z->dtype, A, n, oc, same);
     else                binary_kernel<int64_t><<<grid, 256, 0, st>>>(x->ptr, x->dtype, y->ptr, y->dtype, z->ptr, z->dtype, A, n, oc, same);
@@ -238,6 +384,7 @@ extern "C" int b200jt_unary(const b200jt_tensor* x, const b200jt_tensor* y, cons
     int cc = uc == U_CAST ? compute_class(x->dtype, x->dtype)
                           : (dtype_is_float(y->dtype) ? compute_class(y->dtype, y->dtype) : compute_class(x->dtype, x->dtype));
     const unsigned grid = grid_for(n, 256);
+    if (try_unary_fast(x, y, uc, st)) { B200JT_LAUNCH_CHECK(); return 0; }
     if (cc == 0)      unary_kernel<float><<<grid, 256, 0, st>>>(x->ptr, x->dtype, y->ptr, y->dtype, n, uc);
     else if (cc == 1) unary_kernel<double><<<grid, 256, 0, st>>>(x->ptr, x->dtype, y->ptr, y->dtype, n, uc);
     else              unary_kernel<int64_t><<<grid, 256, 0, st>>>(x->ptr, x->dtype, y->ptr, y->dtype, n, uc);

@@ -109,10 +109,12 @@ __device__ __forceinline__ C load_x(const void* x, int xdt, int64_t off) {
 // The reduced index space is walked as (outer reduced axes) x (innermost reduced axis): threads stride the
 // innermost axis (contiguous when its stride is 1 -> coalesced, 16-byte loads for float32), the outer axes are
 // decomposed once per sweep.
-template <typename TX, typename C>
+// OPK >= 0 fixes the op at compile time (the switches in reduce_combine fold away); OPK < 0 takes it at run time.
+template <typename TX, typename C, int OPK>
 __global__ void __launch_bounds__(256)
 reduce_row_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, int ydt,
-                  const __grid_constant__ ReduceArgs A, int op, bool to_partial) {
+                  const __grid_constant__ ReduceArgs A, int op_rt, bool to_partial) {
+    const int op = OPK >= 0 ? OPK : op_rt;
     __shared__ C warp_acc[8];
     const C rcount = (C)A.rcount;
     const int64_t n_work = A.n_out * A.split;
@@ -185,10 +187,11 @@ reduce_row_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, i
 // One thread per (output, split); neighbouring threads own neighbouring outputs, so with the innermost axis kept
 // every step of the serial fold is a coalesced row read. The reduced coordinates advance like an odometer (no
 // division in the loop); four independent accumulators hide the load latency. Partials are laid out [split][n_out].
-template <typename TX, typename C>
+template <typename TX, typename C, int OPK>
 __global__ void __launch_bounds__(256)
 reduce_col_kernel(const void* __restrict__ x, int xdt, void* __restrict__ out, int ydt,
-                  const __grid_constant__ ReduceArgs A, int op, bool to_partial) {
+                  const __grid_constant__ ReduceArgs A, int op_rt, bool to_partial) {
+    const int op = OPK >= 0 ? OPK : op_rt;
     const C rcount = (C)A.rcount;
     const int s = blockIdx.y;
     const int64_t r0 = s * A.chunk;
@@ -298,17 +301,32 @@ static ReducePlan make_plan(const b200jt_tensor* x, const b200jt_tensor* y, uint
     return P;
 }
 
-template <typename TX, typename C>
-static void launch_stage(const void* xp, int xdt, void* out, int ydt, const ReduceArgs& A, int op, bool part, bool row,
-                         cudaStream_t st) {
+template <typename TX, typename C, int OPK>
+static void launch_stage_op(const void* xp, int xdt, void* out, int ydt, const ReduceArgs& A, int op, bool part, bool row,
+                            cudaStream_t st) {
     if (row) {
         int64_t work = A.n_out * A.split;
         unsigned grid = (unsigned)(work < (int64_t)kNumSMs * 16 ? work : (int64_t)kNumSMs * 16);
-        reduce_row_kernel<TX, C><<<grid, 256, 0, st>>>(xp, xdt, out, ydt, A, op, part);
+        reduce_row_kernel<TX, C, OPK><<<grid, 256, 0, st>>>(xp, xdt, out, ydt, A, op, part);
     } else {
         dim3 grid(grid_for(A.n_out, 256), A.split);
-        reduce_col_kernel<TX, C><<<grid, 256, 0, st>>>(xp, xdt, out, ydt, A, op, part);
+        reduce_col_kernel<TX, C, OPK><<<grid, 256, 0, st>>>(xp, xdt, out, ydt, A, op, part);
     }
+}
+
+template <typename TX, typename C>
+static void launch_stage(const void* xp, int xdt, void* out, int ydt, const ReduceArgs& A, int op, bool part, bool row,
+                         cudaStream_t st) {
+    // the common ops of typed inputs get a compile-time op; everything else shares the run-time variant
+    if constexpr (!std::is_same<TX, void>::value) {
+        switch (op) {
+            case OP_ADD: return launch_stage_op<TX, C, OP_ADD>(xp, xdt, out, ydt, A, op, part, row, st);
+            case OP_MEAN: return launch_stage_op<TX, C, OP_MEAN>(xp, xdt, out, ydt, A, op, part, row, st);
+            case OP_MAX: return launch_stage_op<TX, C, OP_MAX>(xp, xdt, out, ydt, A, op, part, row, st);
+            case OP_MIN: return launch_stage_op<TX, C, OP_MIN>(xp, xdt, out, ydt, A, op, part, row, st);
+        }
+    }
+    launch_stage_op<TX, C, -1>(xp, xdt, out, ydt, A, op, part, row, st);
 }
 
 template <typename C>

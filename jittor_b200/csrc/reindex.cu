@@ -53,19 +53,33 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
             }
         }
         __align__(16) T out[VEC];
+        // x offset and validity are linear in the position e inside the vector: off(e) = off0 + e*dflat, and every
+        // index stays in range on an interval of e
+        I off0 = 0, dflat = 0;
+        int lo = 0, hi = VEC - 1;
+        bool slow = false;
 #pragma unroll
-        for (int e = 0; e < VEC; e++) {
-            bool over = false;
-            int64_t off = 0;
-#pragma unroll
-            for (int d = 0; d < NX; d++) {
-                if (d < nx) {
-                    const I id = xid[d] + xinner[d] * (I)e;
-                    over |= (id < 0) | (id >= xs[d]);
-                    off = off * xs[d] + id;
-                }
+        for (int d = 0; d < NX; d++) {
+            if (d < nx) {
+                off0 = off0 * xs[d] + xid[d];
+                dflat = dflat * xs[d] + xinner[d];
+                if (xinner[d] == 0) { if (xid[d] < 0 || xid[d] >= xs[d]) hi = -1; }
+                else if (xinner[d] == 1) { lo = max(lo, (int)min((I)VEC, -xid[d])); hi = min(hi, (int)max((I)-1, xs[d] - 1 - xid[d])); }
+                else slow = true;
             }
-            out[e] = over ? fill : x[off];
+        }
+        if (!slow) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) out[e] = (e >= lo && e <= hi) ? x[off0 + (I)e * dflat] : fill;
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) {
+                bool over = false;
+#pragma unroll
+                for (int d = 0; d < NX; d++)
+                    if (d < nx) { const I id = xid[d] + xinner[d] * (I)e; over |= (id < 0) | (id >= xs[d]); }
+                out[e] = over ? fill : x[off0 + (I)e * dflat];
+            }
         }
         if (VEC == 1) y[flat] = out[0];
         else {
@@ -78,6 +92,49 @@ reindex_affine_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_c
                 for (int e = 0; e < VEC; e++) y[flat + e] = out[e];
             }
         }
+    }
+}
+
+// Rows whose length is not a multiple of the vector (e.g. the 3x3 inner axes of a conv window): a thread still
+// produces VEC consecutive flat outputs and one wide store, advancing the loop coordinates like an odometer.
+template <typename T, int VEC, int NL, int NX>
+__global__ void __launch_bounds__(256)
+reindex_affine_flat_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_constant__ AffineArgs A,
+                           uint32_t n_vec, T fill) {
+    const int nl = A.ndim_loop, nx = A.ndim_x;
+    for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += gridDim.x * blockDim.x) {
+        const uint32_t flat = v * VEC;
+        int iv[NL];
+        uint32_t r = flat;
+#pragma unroll
+        for (int d = NL - 1; d >= 0; d--) {
+            iv[d] = 0;
+            if (d < nl) { const uint32_t s = (uint32_t)A.loop_shape[d]; const uint32_t q = r / s; iv[d] = (int)(r - q * s); r = q; }
+        }
+        __align__(16) T out[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+            int off = 0; bool over = false;
+#pragma unroll
+            for (int d = 0; d < NX; d++) {
+                if (d < nx) {
+                    int a = (int)A.c0[d];
+#pragma unroll
+                    for (int j = 0; j < NL; j++) if (j < nl) a += (int)A.coef[d][j] * iv[j];
+                    over |= (a < 0) | (a >= (int)A.x_shape[d]);
+                    off = off * (int)A.x_shape[d] + a;
+                }
+            }
+            out[e] = over ? fill : x[off];
+            // odometer step
+            bool carry = true;
+#pragma unroll
+            for (int d = NL - 1; d >= 0; d--) {
+                if (d < nl && carry) { if (++iv[d] < (int)A.loop_shape[d]) carry = false; else iv[d] = 0; }
+            }
+        }
+        if (VEC * sizeof(T) == 16) *reinterpret_cast<uint4*>(y + flat) = *reinterpret_cast<uint4*>(out);
+        else *reinterpret_cast<uint2*>(y + flat) = *reinterpret_cast<uint2*>(out);
     }
 }
 
@@ -117,6 +174,82 @@ reindex_generic_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_
     }
 }
 
+// ---- pure axis permutations (what jt.transpose lowers to) ------------------------------------------------------
+// y[.., a, .., b] = x[.., b, .., a]: x is contiguous along loop axis q, y along the last loop axis. 32 x 32 tiles go
+// through shared memory so that both the reads and the writes are coalesced; the other axes are a batch.
+struct PermArgs {
+    int32_t nbatch_dims;
+    int64_t bshape[kMaxDims], bxstride[kMaxDims], bystride[kMaxDims];
+    int64_t A, B;                 // extents of loop axis q and of the last loop axis
+    int64_t x_sb, y_sa;           // x stride along the last loop axis, y stride along axis q
+    int64_t tiles_a, tiles_b, batch;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+reindex_permute_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_constant__ PermArgs P) {
+    __shared__ T tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
+    const int64_t total = P.tiles_a * P.tiles_b * P.batch;
+    for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const int64_t ta = t % P.tiles_a; int64_t r = t / P.tiles_a;
+        const int64_t tb = r % P.tiles_b; r /= P.tiles_b;
+        int64_t xb = 0, yb = 0;
+#pragma unroll 1
+        for (int d = P.nbatch_dims - 1; d >= 0; d--) { const int64_t i = r % P.bshape[d]; r /= P.bshape[d]; xb += i * P.bxstride[d]; yb += i * P.bystride[d]; }
+        const int64_t a0 = ta * 32, b0 = tb * 32;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int64_t b = b0 + ty + k * 8, a = a0 + tx;
+            if (a < P.A && b < P.B) tile[ty + k * 8][tx] = x[xb + b * P.x_sb + a];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int64_t a = a0 + ty + k * 8, b = b0 + tx;
+            if (a < P.A && b < P.B) y[yb + a * P.y_sa + b] = tile[tx][ty + k * 8];
+        }
+        __syncthreads();
+    }
+}
+
+// Fills P if the program is a pure permutation whose contiguous axes differ; false otherwise.
+static bool make_perm_args(const IndexProgram& Q, PermArgs* P) {
+    const int n = Q.ndim_loop;
+    if (!Q.is_affine || Q.ndim_x != n || n < 2) return false;
+    int var_of[kMaxDims]; bool used[kMaxDims] = {false};
+    for (int d = 0; d < n; d++) {
+        if (Q.c0[d] != 0) return false;
+        int j1 = -1;
+        for (int j = 0; j < n; j++) {
+            if (Q.coef[d][j] == 0) continue;
+            if (Q.coef[d][j] != 1 || j1 >= 0) return false;
+            j1 = j;
+        }
+        if (j1 < 0 || used[j1] || Q.x_shape[d] != Q.loop_shape[j1]) return false;
+        used[j1] = true; var_of[d] = j1;
+    }
+    const int q = var_of[n - 1];
+    if (q == n - 1) return false;                       // same contiguous axis: the affine kernel is already coalesced
+    int64_t xs[kMaxDims], ys[kMaxDims]; int64_t st = 1;
+    for (int d = n - 1; d >= 0; d--) { xs[d] = st; st *= Q.x_shape[d]; }
+    st = 1;
+    for (int d = n - 1; d >= 0; d--) { ys[d] = st; st *= Q.loop_shape[d]; }
+    int64_t xstride_of_var[kMaxDims];
+    for (int d = 0; d < n; d++) xstride_of_var[var_of[d]] = xs[d];
+    memset(P, 0, sizeof(*P));
+    P->A = Q.loop_shape[q]; P->B = Q.loop_shape[n - 1];
+    P->x_sb = xstride_of_var[n - 1]; P->y_sa = ys[q];
+    P->batch = 1;
+    for (int j = 0; j < n - 1; j++) {
+        if (j == q || Q.loop_shape[j] == 1) continue;
+        P->bshape[P->nbatch_dims] = Q.loop_shape[j]; P->bxstride[P->nbatch_dims] = xstride_of_var[j];
+        P->bystride[P->nbatch_dims] = ys[j]; P->nbatch_dims++; P->batch *= Q.loop_shape[j];
+    }
+    P->tiles_a = (P->A + 31) / 32; P->tiles_b = (P->B + 31) / 32;
+    return true;
+}
+
 template <typename T>
 static T make_fill(double v, int dtype) {
     // Tx(overflow_value) with C conversion rules (reindex_op.cc:138)
@@ -144,6 +277,14 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
     const bool small = numel(x) < (1LL << 31) && n < (1LL << 31);
     const T* xp = (const T*)x->ptr;
     T* yp = (T*)y->ptr;
+    PermArgs PA;
+    if (numel(x) > 0 && make_perm_args(P, &PA)) {
+        const int64_t total = PA.tiles_a * PA.tiles_b * PA.batch;
+        const unsigned grid = (unsigned)(total < (int64_t)kNumSMs * 32 ? total : (int64_t)kNumSMs * 32);
+        reindex_permute_kernel<T><<<grid, 256, 0, st>>>(xp, yp, PA);
+        B200JT_LAUNCH_CHECK();
+        return 0;
+    }
     if (P.is_affine && numel(x) > 0) {
         AffineArgs A;
         memset(&A, 0, sizeof(A));
@@ -156,8 +297,13 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
         // one 16-byte (8-byte for 1-byte elements) output vector per thread when rows and alignment allow it
         constexpr int VMAX = 16 / sizeof(T) > 8 ? 8 : 16 / sizeof(T);
         const bool vec_ok = VMAX > 1 && inner % VMAX == 0 && ((uintptr_t)yp % (VMAX * sizeof(T))) == 0;
+        const bool flat_ok = VMAX > 1 && small && n % VMAX == 0 && ((uintptr_t)yp % (VMAX * sizeof(T))) == 0 &&
+                             P.ndim_loop <= 8 && P.ndim_x <= 4;
         if (vec_ok) launch_affine<T, VMAX>(xp, yp, A, n / VMAX, fill, small, st);
-        else launch_affine<T, 1>(xp, yp, A, n, fill, small, st);
+        else if (flat_ok) {
+            const uint32_t nv = (uint32_t)(n / VMAX);
+            reindex_affine_flat_kernel<T, VMAX, 8, 4><<<grid_for(nv, 256), 256, 0, st>>>(xp, yp, A, nv, fill);
+        } else launch_affine<T, 1>(xp, yp, A, n, fill, small, st);
     } else {
         unsigned grid = grid_for(n, 256);
         if (small) reindex_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>(xp, yp, P, n, fill);
