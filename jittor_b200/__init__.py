@@ -9,6 +9,7 @@ from .var import (Var, array, to_var, empty, zeros, ones, reindex, reindex_var, 
 from . import dtypes, executor, nn, dist, op_register
 from .op_register import code, has_op, get_op_info, register_op, compile_custom_op, compile_custom_ops
 from .dtypes import binary_dtype_infer
+from .grad import grad
 
 __version__ = "0.1.0"
 
