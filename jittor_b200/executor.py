@@ -49,6 +49,9 @@ def realize(roots):
             if pending:
                 stack.extend(pending)
                 continue
+            for l in plan.leaves:
+                if l._pending is not None:           # produced by a collective on another stream
+                    l.wait()
             out = plan.run()
             v._data = out.reshape(list(v.shape))
             plans.pop(id(v), None)
@@ -217,6 +220,8 @@ def _run_reshape(v, op):
 
 
 def _run_all_reduce(v, op):
+    """Sum over the ranks, in stream order. (Launching it asynchronously next to the following kernels was measured
+    slower: the persistent one-CTA-per-SM kernels lose an SM to the collective and fall into a second wave.)"""
     out = op.inputs[0]._data.clone()
     if tdist.is_available() and tdist.is_initialized() and tdist.get_world_size() > 1:
         tdist.all_reduce(out, op=tdist.ReduceOp.SUM)

@@ -58,6 +58,7 @@ class Var:
         self.is_scalar = is_scalar
         self._name = None
         self._const = None           # the Python number this Var was made from, if any
+        self._pending = None         # handle of a collective still in flight on another stream
         self.compile_options = {}
 
     # ---- metadata -----------------------------------------------------------------------------
@@ -108,9 +109,17 @@ class Var:
             torch.cuda.current_stream().synchronize()
         return self
 
+    def wait(self):
+        """Makes the current stream wait for a collective that produced this Var (no host blocking)."""
+        if self._pending is not None:
+            self._pending.wait()
+            self._pending = None
+        return self
+
     def torch(self):
         """The computed value as a torch CUDA tensor (no copy)."""
         self.sync()
+        self.wait()
         return self._data.view(list(self._shape))
 
     @property
@@ -126,10 +135,19 @@ class Var:
     def fetch_sync(self):
         return self.numpy()
 
-    def fetch_into(self, host, non_blocking=True):
+    def fetch_into(self, host, non_blocking=True, stream=None):
         """Copies the value into a preallocated host torch tensor (pinned memory makes the copy a DMA that
-        can overlap later launches); call torch.cuda.current_stream().synchronize() before reading it."""
-        host.view(-1).copy_(self.torch().reshape(-1), non_blocking=non_blocking)
+        can overlap later launches). With `stream`, the copy is queued on that stream after the producing work,
+        so that it overlaps the next host->device copy (PCIe is full duplex); synchronise the stream that carried
+        the copy before reading `host`."""
+        src = self.torch().reshape(-1)
+        if stream is None:
+            host.view(-1).copy_(src, non_blocking=non_blocking)
+            return host
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            host.view(-1).copy_(src, non_blocking=non_blocking)
+        src.record_stream(stream)
         return host
 
     def item(self):

@@ -17,7 +17,7 @@ def main():
     v = jt.Var([4], "float32")
     v._data = torch.full((4,), float(rank + 1))
     out = v.mpi_all_reduce("add")
-    out.sync()
+    out.sync().wait()
     assert torch.equal(out._data, torch.full((4,), 3.0)), out._data
     # 2. 'mean' is add / world_size, as in the reference
     m = v.mpi_all_reduce("mean")
