@@ -91,6 +91,8 @@ class C2Scatter:
                  "b-uniform": "rr_privatised_kernel<float,int,4>", "b-zipf": "rr_privatised_kernel<float,int,4>",
                  "pool-bwd": "rr_flat_kernel<float>"}
     launches = {"a-uniform": 2, "a-zipf": 2, "b-uniform": 2, "b-zipf": 2, "pool-bwd": 1}
+    # DRAM bytes (read + written) of the main kernel per launch, from the ncu captures summarised under profiles/
+    traffic = {"a-uniform": 144.5e6, "a-zipf": 147.3e6, "b-uniform": 137.6e6, "b-zipf": 137.7e6, "pool-bwd": 776.2e6}
 
     def work(self):
         pool = int(np.prod(self.POOL_SHAPE)) * 4
@@ -172,6 +174,7 @@ class C3Rows:
     description = "config 2: fused row softmax and LayerNorm on [32768,4096], fp32 and bf16 IO with fp32 math"
     kernel_of = {k: "row_reg_kernel" for k in ("softmax-f32", "layernorm-f32", "softmax-bf16", "layernorm-bf16")}
     launches = {k: 1 for k in kernel_of}
+    traffic = {"softmax-f32": 1023.4e6, "layernorm-f32": 1023.3e6, "softmax-bf16": 488.3e6, "layernorm-bf16": 488.1e6}
 
     def work(self):
         n = self.ROWS * self.COLS
@@ -285,6 +288,7 @@ class C5ConvBN:
                    "(one NCCL all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks")
     kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)"}
     launches = {"conv": 3, "conv-bn-relu": 5}
+    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6}
 
     def work(self):
         f = 2 * self.N * self.H * self.W * self.CO * self.C * 9
@@ -458,6 +462,7 @@ def main():
     ap.add_argument("--cpu-baseline", type=int, default=1)
     ap.add_argument("--parts", default="", help="comma-separated subset of the parts (profiling aid)")
     ap.add_argument("--e2e", type=int, default=1)
+    ap.add_argument("--graph", type=int, default=1, help="replay the step from a CUDA graph in the timed region")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
@@ -491,18 +496,53 @@ def main():
         for nm in names:
             wl.run(nm)
     barrier()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(args.steps)]
+    # (1) per-part times: direct launches with an event after every part
+    psteps = min(args.steps, 10)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(psteps)]
+    barrier()
+    for s in range(psteps):
+        ev[s][0].record()
+        for i, nm in enumerate(names):
+            wl.run(nm)
+            ev[s][i + 1].record()
+    barrier()
+    part_ms = {nm: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(psteps)) / psteps
+               for i, nm in enumerate(names)}
+    # (2) the timed region: K steps. One step (kernels and collectives of all parts) is captured into a CUDA graph and
+    # replayed, so that the device is not waiting for the Python launch path (it matters when the per-rank work is
+    # small); without --graph, or if capture fails, the steps are launched directly.
+    graph = None
+    if args.graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for nm in names:
+                    wl.run(nm)
+            torch.cuda.current_stream().wait_stream(side)
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                keep = [wl.run(nm) for nm in names]
+            graph.replay()
+            barrier()
+        except Exception as exc:                     # noqa: BLE001
+            print(f"[bench] CUDA graph capture unavailable ({type(exc).__name__}: {exc}); launching directly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         barrier()
+        e_beg.record()
         for s in range(args.steps):
-            ev[s][0].record()
-            for i, nm in enumerate(names):
-                wl.run(nm)
-                ev[s][i + 1].record()
+            if graph is not None:
+                graph.replay()
+            else:
+                for nm in names:
+                    wl.run(nm)
+        e_end.record()
         barrier()
-    step_ms = ev[0][0].elapsed_time(ev[-1][-1]) / args.steps
-    part_ms = {nm: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) / args.steps
-               for i, nm in enumerate(names)}
+    step_ms = e_beg.elapsed_time(e_end) / args.steps
     status = jt._capi.lib.b200jt_device_status()
 
     # ---- end to end: pinned host -> device -> kernels -> pinned host ------------------------------------
@@ -562,10 +602,12 @@ def main():
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": args.steps * sum(wl.launches[n] for n in names),
         "roofline": {"bound": wl.bound, "kernel": wl.kernel_of[dom], "part": dom, "achieved": achieved, "peak": peak,
-                     "unit": wl.unit, "frac": achieved / peak, "peak_source": peak_src, "traffic": None,
+                     "unit": wl.unit, "frac": achieved / peak, "peak_source": peak_src,
+                     "traffic": getattr(wl, "traffic", {}).get(dom),
                      "note": "achieved = algorithmic work of the part / CUDA-event time of the part (its main kernel "
                              "plus its small helper launches)"},
         "parts": parts,
+        "cuda_graph": graph is not None,
         "device_status": status,
     }
     if args.cpu_baseline and world == 1:
