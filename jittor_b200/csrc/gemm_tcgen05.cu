@@ -15,6 +15,7 @@
 #include "gemm_simt.cuh"
 #include "tc_common.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace b200jt {
@@ -46,10 +47,12 @@ struct Tiles {
     }
 };
 
-template <int MT>
+// BMN: B is given as [K, N] (N contiguous) and used as an MN-major operand -- four 64 x 64 TMA boxes per stage -- instead
+// of being transposed into K-major form by a separate pass.
+template <int MT, bool BMN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 __nv_bfloat16* __restrict__ c, int M, int N, int K, int group) {
+                 __nv_bfloat16* __restrict__ c, int M, int N, int K, int group, uint32_t b_lbo, uint32_t b_sbo) {
     constexpr int STAGES = Cfg<MT>::STAGES, STAGE_BYTES = Cfg<MT>::STAGE_BYTES, NBUF = Cfg<MT>::NBUF;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -96,7 +99,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     mbar_expect_tx(full + stage, STAGE_BYTES);
 #pragma unroll
                     for (int j = 0; j < MT; j++) tma_load_2d(sa + j * A_BYTES, &map_a, full + stage, kb * BK, (tm * MT + j) * BM);
-                    tma_load_2d(sa + MT * A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
+                    if (BMN) {
+#pragma unroll
+                        for (int cch = 0; cch < BN / 64; cch++)
+                            tma_load_2d(sa + MT * A_BYTES + cch * (64 * BK * 2), &map_b, full + stage, tn * BN + cch * 64, kb * BK);
+                    } else {
+                        tma_load_2d(sa + MT * A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -109,7 +118,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BM, BN);
+            constexpr uint32_t idesc = make_idesc(BM, BN, BMN);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
@@ -123,15 +132,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!(ok = mbar_wait(full + stage, phase, abort_flag, 3))) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                    const uint64_t db = make_smem_desc(sa + MT * A_BYTES);
+                    const uint64_t db = BMN ? make_smem_desc_mn(sa + MT * A_BYTES, b_lbo, b_sbo) : make_smem_desc(sa + MT * A_BYTES);
+                    // advancing K by 16: K-major +32 B inside the swizzled row (+2 units of 16 B); MN-major 16 rows of 128 B
+                    constexpr int B_KSTEP = BMN ? (UMMA_K * 128) / 16 : 2;
 #pragma unroll
                     for (int j = 0; j < MT; j++) {
                         const uint64_t da = make_smem_desc(sa + j * A_BYTES);
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; k++) {
-                            // advancing K by 16 bf16 = 32 B inside the swizzled 128-byte row: +2 in 16-byte units
-                            umma_f16(tmem_d + j * BN, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-                        }
+                        for (int k = 0; k < BK / UMMA_K; k++)
+                            umma_f16(tmem_d + j * BN, da + 2 * k, db + B_KSTEP * k, idesc, (kb | k) != 0);
                     }
                     umma_commit(empty + stage);                 // slot reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -255,11 +264,16 @@ bool matmul_tc_supported(int64_t M, int64_t N, int64_t K, const void* a, const v
            ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 2 == 0) && tc::encode_fn() != nullptr;
 }
 
+static bool b_mn_direct(int64_t N, bool trans_b) {
+    const char* e = getenv("B200JT_GEMM_BMN");
+    return !trans_b && N % 8 == 0 && !(e && atoi(e) == 0);
+}
+
 size_t matmul_tc_workspace(int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b) {
-    // operands that are not K-major are transposed into the workspace first
+    // A that is not K-major is transposed into the workspace first; B [K, N] is consumed directly as an MN-major operand
     size_t bytes = 0;
     if (trans_a) bytes += (size_t)M * K * 2;
-    if (!trans_b) bytes += (size_t)N * K * 2;
+    if (!trans_b && !b_mn_direct(N, trans_b)) bytes += (size_t)N * K * 2;
     return bytes;
 }
 
@@ -274,21 +288,24 @@ int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64
         transpose_bf16_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)a, (__nv_bfloat16*)ws, (int)K, (int)M);
         ak = (const __nv_bfloat16*)ws; ws += (size_t)M * K * 2;
     }
-    if (!trans_b) {  // b is [K, N]
+    const bool bmn = b_mn_direct(N, trans_b);
+    if (!trans_b && !bmn) {  // b is [K, N]
         dim3 g((unsigned)((N + 63) / 64), (unsigned)((K + 63) / 64));
         transpose_bf16_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)b, (__nv_bfloat16*)ws, (int)K, (int)N);
         bk = (const __nv_bfloat16*)ws;
     }
     B200JT_LAUNCH_CHECK();
     CUtensorMap ma, mb;
-    if (!make_map(&ma, ak, M, K, BM) || !make_map(&mb, bk, N, K, BN))
+    // K-major operands: boxes of 64 K-elements x rows; MN-major B: boxes of 64 N-elements x 64 K-rows of b[K, N]
+    if (!make_map(&ma, ak, M, K, BM) || !(bmn ? make_map(&mb, b, K, N, 64) : make_map(&mb, bk, N, K, BN)))
         return fail(-4, "matmul: cuTensorMapEncodeTiled failed");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM_BYTES);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES);
+        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM_BYTES);
+        if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES);
+        if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM_BYTES);
+        if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES);
     });
     B200JT_CUDA(attr_err);
     // 256-row tiles when they still fill the machine for several waves, 128-row tiles otherwise
@@ -297,14 +314,15 @@ int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64
     const int group = genv ? atoi(genv) : 8;
     const char* force = getenv("B200JT_GEMM_MT");
     const bool two = force ? atoi(force) == 2 : tiles2 >= 4 * kNumSMs;
-    if (two) {
-        const int grid = tiles2 < kNumSMs ? (int)tiles2 : kNumSMs;
-        gemm_bf16_kernel<2><<<grid, THREADS, Cfg<2>::SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K, group);
-    } else {
-        const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-        const int grid = tiles < kNumSMs ? (int)tiles : kNumSMs;
-        gemm_bf16_kernel<1><<<grid, THREADS, Cfg<1>::SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K, group);
-    }
+    // MN-major B: 64-column chunks are 8 KB apart (leading offset), 8-row groups along K 1 KB apart (stride offset)
+    const uint32_t lbo = 64 * BK * 2, sbo = 1024;
+    const int64_t tiles1 = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = (int)std::min<int64_t>(two ? tiles2 : tiles1, kNumSMs);
+#define B200JT_GEMM(MT_, BMN_) gemm_bf16_kernel<MT_, BMN_><<<grid, THREADS, Cfg<MT_>::SMEM_BYTES, st>>>( \
+        ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K, group, lbo, sbo)
+    if (two) { if (bmn) B200JT_GEMM(2, true); else B200JT_GEMM(2, false); }
+    else     { if (bmn) B200JT_GEMM(1, true); else B200JT_GEMM(1, false); }
+#undef B200JT_GEMM
     B200JT_LAUNCH_CHECK();
     return 0;
 }
