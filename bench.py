@@ -235,7 +235,8 @@ class C4Matmul:
     SHAPES = {"8192x8192x8192": (8192, 8192, 8192), "16384x4096x4096": (16384, 4096, 4096)}
     description = "config 3: broadcast-multiply-sum matmul A[M,K] x B[K,N], bf16 inputs ~ N(0,1/K), fp32 accumulate"
     kernel_of = {k: "gemm_bf16_kernel (tcgen05)" for k in SHAPES}
-    launches = {k: 2 for k in SHAPES}        # operand transpose + GEMM
+    launches = {k: 1 for k in SHAPES}
+    traffic = {"8192x8192x8192": 1011.8e6, "16384x4096x4096": 450.9e6}
 
     def work(self):
         return {k: 2 * m * n * kk for k, (m, n, kk) in self.SHAPES.items()}
