@@ -91,6 +91,7 @@ class C2Scatter:
                  "b-uniform": "rr_privatised_kernel<float,int,4>", "b-zipf": "rr_privatised_kernel<float,int,4>",
                  "pool-bwd": "rr_flat_kernel<float>"}
     launches = {"a-uniform": 2, "a-zipf": 2, "b-uniform": 2, "b-zipf": 2, "pool-bwd": 1}
+    all_reduced = ("a-uniform", "a-zipf", "b-uniform", "b-zipf")     # parts whose output is summed over the ranks
     # DRAM bytes (read + written) of the main kernel per launch, from the ncu captures summarised under profiles/
     traffic = {"a-uniform": 144.5e6, "a-zipf": 147.3e6, "b-uniform": 137.6e6, "b-zipf": 137.7e6, "pool-bwd": 776.2e6}
 
@@ -289,6 +290,7 @@ class C5ConvBN:
                    "(one NCCL all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks")
     kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)"}
     launches = {"conv": 3, "conv-bn-relu": 5}
+    all_reduced = ("conv-bn-relu",)
     traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6}
 
     def work(self):
@@ -479,6 +481,7 @@ def main():
     torch.cuda.set_device(local)
     dist.init("nccl")
     multi = dist.in_mpi()
+    peer_kernel = dist.peer_comm() is not None
     wl = WORKLOADS[args.workload]()
     names = [n for n in wl.setup(rank, world, jt, torch, multi) if not args.parts or n in args.parts.split(",")]
     work = {n: wl.work()[n] for n in names}
@@ -601,7 +604,9 @@ def main():
         "clocks": clocks.summary(),
         "e2e": {"value": job_work / e2e_ms / sc if e2e_steps else None, "unit": wl.unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": args.steps * sum(wl.launches[n] for n in names),
+        "gpu_launches": args.steps * sum(wl.launches[n] + (1 if peer_kernel and n in getattr(wl, "all_reduced", ()) else 0)
+                                         for n in names),
+        "collective": None if not multi else ("peer-kernel (NVLink loads/stores, one launch per rank)" if peer_kernel else "nccl"),
         "roofline": {"bound": wl.bound, "kernel": wl.kernel_of[dom], "part": dom, "achieved": achieved, "peak": peak,
                      "unit": wl.unit, "frac": achieved / peak, "peak_source": peak_src,
                      "traffic": getattr(wl, "traffic", {}).get(dom),

@@ -142,9 +142,9 @@ size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_tensor* b, c
 int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
                   int trans_a, int trans_b, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Status word of the tensor-core kernels (matmul, conv2d): every wait inside them is bounded; if one expires the
- * kernel stops cleanly and records which (1 producer, 2 accumulator hand-back, 3 operand arrival, 4 accumulator
- * ready). Returns 0 if none did since the last call, and clears the word. Synchronises the device. It plays the
+/* Status word of the kernels that wait (matmul, conv2d, peer all-reduce): every wait inside them is bounded; if
+ * one expires the kernel stops cleanly and records which (1 producer, 2 accumulator hand-back, 3 operand arrival,
+ * 4 accumulator ready, 5 a peer's flag in b200jt_peer_all_reduce). Returns 0 if none did since the last call, and clears the word. Synchronises the device. It plays the
  * role of the reference's checkCudaErrors after a relay (python/jittor/extern/cuda/cublas/ops/cublas_matmul_op.cc:117). */
 int b200jt_device_status(void);
 
@@ -170,6 +170,35 @@ int b200jt_bn_stats(const b200jt_tensor* x, float* stats, void* stream);
  * var = max(stats[C+c]/count - mean^2, 0): python/jittor/nn.py:680-683 (+ nn.relu). */
 int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, double count, const float* gamma, const float* beta,
                     double eps, int relu, const b200jt_tensor* y, void* stream);
+
+/* ---- all-reduce over NVLink peer mappings --------------------------------------------------------
+ * y = op over the ranks of x, one kernel per rank that reads and writes the other ranks' memory directly: replaces
+ * the relay NcclAllReduceOp(Var* x), python/jittor/extern/cuda/nccl/ops/nccl_all_reduce_op.h:14, jit_run
+ * python/jittor/extern/cuda/nccl/ops/nccl_all_reduce_op.cc:46-58 (ncclAllReduce(xp, yp, y->num, T, ncclSum, comm, 0)),
+ * which MpiAllReduceOp forwards to on CUDA (python/jittor/extern/mpi/ops/mpi_all_reduce_op.cc:39-47). The reference
+ * sums only; "maximum" and "minimum" are accepted too (what a scatter-max onto a shared output needs).
+ * Set-up, once per process: every rank creates a segment (device memory holding flags and four staging areas of
+ * data_bytes each; the IPC handle is what the other ranks open), the 64-byte handles are exchanged by the host
+ * (rank order), and b200jt_peer_comm_create maps them. A call reduces count elements of dtype (float32/64, int32/64,
+ * float16/bfloat16 with float32 accumulation) from src into dst (may alias), count*size <= data_bytes; all ranks
+ * must issue the same sequence of calls. Sums run in rank order on every rank: all ranks receive identical bits.
+ * Only kernel launches are issued, so calls can be captured in a CUDA graph. A peer that does not arrive within
+ * wait_ms makes the kernel return with status 5 (b200jt_device_status); the communicator must then be rebuilt. */
+#define B200JT_IPC_HANDLE_BYTES 64
+#define B200JT_PEER_MAX_RANKS 8
+size_t b200jt_peer_segment_bytes(size_t data_bytes);
+int b200jt_peer_segment_create(size_t data_bytes, void** segment, unsigned char* ipc_handle);
+int b200jt_peer_comm_create(int rank, int world, void* own_segment, const unsigned char* ipc_handles,
+                            size_t data_bytes, double wait_ms, void** comm);
+int b200jt_peer_comm_destroy(void* comm);
+size_t b200jt_peer_max_bytes(const void* comm);
+int b200jt_peer_all_reduce(void* comm, const void* src, void* dst, int64_t count, int dtype, const char* op, void* stream);
+/* The same job with all ranks on ONE device (test aid and single-GPU emulation): `world` communicators whose segments
+ * live side by side, and one cooperative launch that plays every rank (blocks wait on one another, so they have
+ * to be co-resident; messages are limited accordingly by the launch failing, never by a hang). */
+int b200jt_peer_comm_create_local(int world, size_t data_bytes, double wait_ms, void** comms);
+int b200jt_peer_all_reduce_local(void* const* comms, int world, const void* const* srcs, void* const* dsts,
+                                 int64_t count, int dtype, const char* op, void* stream);
 
 #ifdef __cplusplus
 }

@@ -69,6 +69,15 @@ SIGNATURES = [
     ("b200jt_conv2d", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i, _FP, _vp, _sz, _vp]),
     ("b200jt_bn_stats", _i, [_TP, _FP, _vp]),
     ("b200jt_bn_apply", _i, [_TP, _FP, _d, _FP, _FP, _d, _i, _TP, _vp]),
+    ("b200jt_peer_segment_bytes", _sz, [_sz]),
+    ("b200jt_peer_segment_create", _i, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    ("b200jt_peer_comm_create", _i, [_i, _i, _vp, ctypes.c_char_p, _sz, _d, ctypes.POINTER(_vp)]),
+    ("b200jt_peer_comm_destroy", _i, [_vp]),
+    ("b200jt_peer_max_bytes", _sz, [_vp]),
+    ("b200jt_peer_all_reduce", _i, [_vp, _vp, _vp, ctypes.c_int64, _i, ctypes.c_char_p, _vp]),
+    ("b200jt_peer_comm_create_local", _i, [_i, _sz, _d, ctypes.POINTER(_vp)]),
+    ("b200jt_peer_all_reduce_local", _i, [ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), ctypes.POINTER(_vp),
+                                          ctypes.c_int64, _i, ctypes.c_char_p, _vp]),
 ]
 for _name, _res, _args in SIGNATURES:
     _fn = getattr(lib, _name)

@@ -21,11 +21,11 @@ extern "C" size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_t
 }
 
 /* Status word of the tensor-core kernels: 0, or the code of the first bounded wait that expired since the last call
- * (1 producer, 2 accumulator hand-back, 3 operand arrival, 4 accumulator ready). Synchronises the device. */
+ * (1 producer, 2 accumulator hand-back, 3 operand arrival, 4 accumulator ready; 5: a peer's flag in the all-reduce kernel). Synchronises the device. */
 extern "C" int b200jt_device_status(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    const int a = tc_status_fetch_and_clear(), b = tcconv_status_fetch_and_clear();
-    return a ? a : b;
+    const int a = tc_status_fetch_and_clear(), b = tcconv_status_fetch_and_clear(), c = peer_status_fetch_and_clear();
+    return a ? a : b ? b : c;
 }
 
 extern "C" int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,

@@ -22,6 +22,7 @@ size_t conv2d_tc_workspace(const ConvShape& s);
 // returns < 0 / > 1 on error, 0 on success, 1 on success with `stats` filled by the epilogue
 int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st);
 int tcconv_status_fetch_and_clear();
+int peer_status_fetch_and_clear();          // peer_allreduce.cu
 
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
 

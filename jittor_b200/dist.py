@@ -18,6 +18,38 @@ def init(backend=None):
     if backend == "nccl":
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     tdist.init_process_group(backend=backend)
+    if backend == "nccl" and os.environ.get("B200JT_PEER_ALLREDUCE", "1") != "0":
+        connect_peers()
+
+
+_PEER = None
+
+
+def connect_peers(data_bytes=None, wait_ms=None):
+    """Sets up the NVLink peer all-reduce kernel for messages up to `data_bytes` (collective; see peer.PeerComm).
+    Larger messages, other dtypes and jobs where the set-up fails keep going through NCCL."""
+    global _PEER
+    from . import peer
+    if _PEER is not None:
+        _PEER.close()
+    _PEER = peer.PeerComm.connect(data_bytes, wait_ms)
+    return _PEER
+
+
+def peer_comm():
+    return _PEER
+
+
+def all_reduce_sum(src, out=None):
+    """Sum of a device tensor over the ranks, in stream order: the peer kernel when it applies, else NCCL."""
+    if _PEER is not None and _PEER.usable(src):
+        return _PEER.all_reduce(src, torch.empty_like(src) if out is None else out, "add")
+    if out is None:
+        out = src.clone()
+    elif out.data_ptr() != src.data_ptr():
+        out.copy_(src)
+    tdist.all_reduce(out, op=tdist.ReduceOp.SUM)
+    return out
 
 
 def in_mpi():

@@ -222,10 +222,11 @@ def _run_reshape(v, op):
 def _run_all_reduce(v, op):
     """Sum over the ranks, in stream order. (Launching it asynchronously next to the following kernels was measured
     slower: the persistent one-CTA-per-SM kernels lose an SM to the collective and fall into a second wave.)"""
-    out = op.inputs[0]._data.clone()
+    x = op.inputs[0]._data
     if tdist.is_available() and tdist.is_initialized() and tdist.get_world_size() > 1:
-        tdist.all_reduce(out, op=tdist.ReduceOp.SUM)
-    return out
+        from . import dist
+        return dist.all_reduce_sum(x)
+    return x.clone()
 
 
 def _run_fill(v, op):
@@ -724,7 +725,8 @@ def _match_batchnorm(v):
             C.check(C.lib.b200jt_bn_stats(C.desc(xd), ctypes.c_void_p(stats.data_ptr()), C.stream_ptr()), "bn_stats")
         count = float(x.numel() // Cn)
         if synced and tdist.is_initialized() and tdist.get_world_size() > 1:
-            tdist.all_reduce(stats, op=tdist.ReduceOp.SUM)     # sum and sum of squares in ONE 2*C message
+            from . import dist
+            dist.all_reduce_sum(stats, out=stats)              # sum and sum of squares in ONE 2*C message
             count *= tdist.get_world_size()
 
         def param(p, fill):

@@ -1,0 +1,63 @@
+"""Worker of tests/test_peer_multi_gpu.py: run under torchrun with one rank per GPU (NCCL). Checks the peer
+all-reduce kernel against NCCL on the same tensors, then the Var-level all-reduce and sync BatchNorm through it."""
+import os
+import sys
+
+import torch
+import torch.distributed as tdist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import jittor_b200 as jt                      # noqa: E402
+from jittor_b200 import _capi as C, dist, nn  # noqa: E402
+
+
+def main():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init("nccl")
+    rank, world = dist.rank(), dist.world_size()
+    pc = dist.peer_comm()
+    assert pc is not None, "peer communicator was not set up"
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    for rep in range(3):
+        for dtype in (torch.float32, torch.int32, torch.bfloat16):
+            for count in (1, 512, 4099, 100_000, 1 << 20, (2 << 20) + 5):
+                if count * torch.empty(0, dtype=dtype).element_size() > pc.max_bytes:
+                    continue
+                if dtype.is_floating_point:
+                    x = torch.randn(count, generator=g, device="cuda").to(dtype)
+                else:
+                    x = torch.randint(0, 100, (count,), generator=g, device="cuda", dtype=dtype)
+                got = pc.all_reduce(x, torch.empty_like(x))
+                # rank-ordered reference: gather every rank's tensor and add them in order
+                parts = [torch.empty_like(x) for _ in range(world)]
+                tdist.all_gather(parts, x)
+                acc = parts[0].float() if dtype == torch.bfloat16 else parts[0].clone()
+                for p in parts[1:]:
+                    acc = acc + (p.float() if dtype == torch.bfloat16 else p)
+                assert torch.equal(got, acc.to(dtype)), (rep, dtype, count)
+    # Var-level: scatter-add onto a shared output, all-reduced
+    idx = torch.randint(0, 1 << 16, (1 << 20,), generator=g, device="cuda", dtype=torch.int32)
+    val = torch.randint(0, 100, (1 << 20,), generator=g, device="cuda", dtype=torch.int32)
+    out = jt.array(val).reindex_reduce("add", [1 << 16], ["@e0(i0)"], extras=[jt.array(idx)]).mpi_all_reduce("add")
+    got = out.sync()._data
+    local = torch.zeros(1 << 16, dtype=torch.int32, device="cuda").index_add_(0, idx.long(), val)
+    tdist.all_reduce(local)
+    assert torch.equal(got, local)
+    # sync BatchNorm statistics over the ranks' batches
+    x = torch.randn(8, 64, 16, 16, generator=g, device="cuda")
+    bn = nn.BatchNorm(64, is_train=True, sync=True)
+    y = nn.relu(bn(jt.array(x))).sync()._data
+    allx = [torch.empty_like(x) for _ in range(world)]
+    tdist.all_gather(allx, x)
+    full = torch.cat(allx)
+    mean = full.mean((0, 2, 3), keepdim=True)
+    var = full.var((0, 2, 3), unbiased=False, keepdim=True)
+    want = torch.relu((x - mean) / torch.sqrt(var + 1e-5))
+    assert torch.allclose(y, want, rtol=1e-4, atol=1e-4), (y - want).abs().max()
+    assert C.lib.b200jt_device_status() == 0
+    tdist.barrier()
+    print(f"rank {rank} ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
