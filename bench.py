@@ -289,7 +289,7 @@ class C5ConvBN:
     description = ("config 4: reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] s1 p1, then global BatchNorm statistics "
                    "(one NCCL all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks")
     kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)"}
-    launches = {"conv": 3, "conv-bn-relu": 5}
+    launches = {"conv": 2, "conv-bn-relu": 3}
     all_reduced = ("conv-bn-relu",)
     traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6}
 

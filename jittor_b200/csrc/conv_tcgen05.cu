@@ -27,10 +27,12 @@ constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int PATCH = 8;                            // spatial patch edge: 8 x 8 = 64 pixels = half a tile
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STATS_BYTES = 2 * BN * 4;
+constexpr int STATS_MAX_CO = 512;                   // widest layer whose statistics the epilogue can keep per CTA
+constexpr int STATS_BYTES = 2 * STATS_MAX_CO * 4;
 constexpr int OUT_STAGE_BYTES = 2 * 64 * 64 * 2;      // TMA-store staging: 2 patches x 64 channels x 64 pixels
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + STATS_BYTES + OUT_STAGE_BYTES;
 constexpr int THREADS = 192;
+constexpr double kNarrowTilePenalty = 1.5;         // measured cost per FLOP of 128-wide tiles relative to 256-wide ones (1.37 ms vs 0.92 ms)
 
 struct ConvArgs {
     int N, C, H, W, Co, KH, KW, OH, OW, ph, pw, dh, dw;
@@ -50,7 +52,9 @@ __device__ __forceinline__ void patch_coords(const ConvArgs& A, int64_t q, int& 
 // TMA_OUT: the epilogue stages 64 channels x 128 pixels of bf16 in shared memory ([patch][channel][8x8]) and writes
 // them to y (NCHW) with two 4-D TMA box stores; edges are clipped by the tensor map. Needs OW % 8 == 0 (16-byte row
 // pitch); otherwise the lanes store their values directly.
-template <bool TMA_OUT>
+// BN_T: output channels per tile (256, or 128 when that fills the last wave of the persistent grid better; the
+// shared-memory ring keeps the 256-channel stage size either way).
+template <bool TMA_OUT, int BN_T>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_y,
@@ -64,7 +68,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     uint64_t* acc_empty = bars + 2 * STAGES + 2;
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* sstat = (float*)(smem + STAGES * STAGE_BYTES + 256);      // [2][BN] per-CTA channel sums
+    float* sstat = (float*)(smem + STAGES * STAGE_BYTES + 256);      // [2][STATS_MAX_CO] per-CTA channel sums
     unsigned char* stage_out = smem + STAGES * STAGE_BYTES + 256 + STATS_BYTES;   // [2 patches][64 ch][64 px] bf16
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -78,7 +82,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < 2 * BN; i += blockDim.x) sstat[i] = 0.f;
+    for (int i = threadIdx.x; i < 2 * STATS_MAX_CO; i += blockDim.x) sstat[i] = 0.f;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -103,10 +107,10 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     const int dy = kh * A.dh - A.ph, dx = kw * A.dw - A.pw;
                     if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 11))) break;
                     unsigned char* sa = smem + stage * STAGE_BYTES;
-                    mbar_expect_tx(full + stage, STAGE_BYTES);
+                    mbar_expect_tx(full + stage, A_BYTES + BN_T * BK * 2);
                     tma_load_4d(sa, &map_x, full + stage, cb * BK, w0 + dx, h0 + dy, n0);
                     tma_load_4d(sa + A_BYTES / 2, &map_x, full + stage, cb * BK, w1 + dx, h1 + dy, n1);
-                    tma_load_2d(sa + A_BYTES, &map_w, full + stage, cb * BK, tap * A.Co + tn * BN);
+                    tma_load_2d(sa + A_BYTES, &map_w, full + stage, cb * BK, tap * A.Co + tn * BN_T);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -117,7 +121,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BM, BN);
+            constexpr uint32_t idesc = make_idesc(BM, BN_T);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
@@ -164,8 +168,8 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
             const bool issuer = threadIdx.x == 64;          // first epilogue thread drives the TMA stores
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ch++) {
-                const int co0 = tn * BN + ch * 32;
+            for (int ch = 0; ch < BN_T / 32; ch++) {
+                const int co0 = tn * BN_T + ch * 32;
                 if (TMA_OUT && (ch & 1) == 0) {
                     // staging buffer free again? (the previous round's stores must have read it)
                     if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -208,15 +212,17 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                             g[i] = keep2 + __shfl_xor_sync(0xffffffffu, send2, s);
                         }
                     }
-                    atomicAdd(sstat + ch * 32 + lane, f[0]);
-                    atomicAdd(sstat + BN + ch * 32 + lane, g[0]);
+                    if (co0 + lane < A.Co) {
+                        atomicAdd(sstat + co0 + lane, f[0]);
+                        atomicAdd(sstat + STATS_MAX_CO + co0 + lane, g[0]);
+                    }
                 }
                 if (TMA_OUT && (ch & 1) == 1) {
                     // 64 channels staged: make the writes visible to the async proxy, then two box stores
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (issuer) {
-                        const int cbase = tn * BN + (ch - 1) * 32;
+                        const int cbase = tn * BN_T + (ch - 1) * 32;
 #pragma unroll
                         for (int pp = 0; pp < 2; pp++) {
                             const int64_t qq = 2 * (int64_t)tm + pp;
@@ -239,9 +245,10 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (stats && A.tiles_n == 1) {
-        for (int i = threadIdx.x; i < BN; i += blockDim.x) {
-            if (i < A.Co) { atomicAdd(stats + i, sstat[i]); atomicAdd(stats + A.Co + i, sstat[BN + i]); }
+    if (stats) {
+        for (int i = threadIdx.x; i < A.Co; i += blockDim.x) {
+            atomicAdd(stats + i, sstat[i]);
+            atomicAdd(stats + A.Co + i, sstat[STATS_MAX_CO + i]);
         }
     }
     if (warp == 1) {
@@ -253,10 +260,24 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 // ---- layout passes -----------------------------------------------------------------------------------------
 // in[b][R][Cn] -> out[b][Cn][R] (bf16), 64x64 tiles, 16-byte global accesses on both sides. The tile is kept as
 // 32-bit pairs with an odd pitch (33 words) so that the column reads of the second phase spread over the banks.
+// The first wz slices (blockIdx.z < wz) of the same grid re-order the weights instead (w[Co][C][taps] -> wt[taps][Co][C]), so
+// that both layout passes of a convolution are one launch.
 __global__ void __launch_bounds__(256)
-transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn) {
+transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn, int wz,
+                              const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int C, int taps) {
     __shared__ __nv_bfloat16 tile[64][66];
-    const int64_t boff = (int64_t)blockIdx.z * R * Cn;
+    if ((int)blockIdx.z < wz) {
+        const int64_t n = (int64_t)Co * C * taps;
+        const int64_t nblk = (int64_t)gridDim.x * gridDim.y * wz;
+        const int64_t blk = ((int64_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        for (int64_t i = blk * blockDim.x + threadIdx.x; i < n; i += nblk * blockDim.x) {
+            const int c = (int)(i % C); const int64_t t2 = i / C;
+            const int co = (int)(t2 % Co); const int tap = (int)(t2 / Co);
+            wt[i] = w[((int64_t)co * C + c) * taps + tap];
+        }
+        return;
+    }
+    const int64_t boff = (int64_t)((int)blockIdx.z - wz) * R * Cn;
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
     const int j = threadIdx.x & 7, i = threadIdx.x >> 3;          // 8 chunks of 8 elements x 32 rows
     const bool vec_in = (Cn % 8 == 0), vec_out = (R % 8 == 0);
@@ -288,17 +309,6 @@ transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat1
     }
 }
 
-// w[Co][C][KH*KW] -> wt[KH*KW][Co][C]
-__global__ void __launch_bounds__(256)
-weight_tap_major_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int C, int taps) {
-    const int64_t n = (int64_t)Co * C * taps;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = (int)(i % C); const int64_t t2 = i / C;
-        const int co = (int)(t2 % Co); const int tap = (int)(t2 / Co);
-        wt[i] = w[((int64_t)co * C + c) * taps + tap];
-    }
-}
-
 static bool make_map_x(CUtensorMap* map, const void* base, const ConvShape& s) {
     auto fn = encode_fn();
     if (!fn) return false;
@@ -310,12 +320,12 @@ static bool make_map_x(CUtensorMap* map, const void* base, const ConvShape& s) {
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-static bool make_map_w(CUtensorMap* map, const void* base, const ConvShape& s) {
+static bool make_map_w(CUtensorMap* map, const void* base, const ConvShape& s, int bn) {
     auto fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)s.C, (cuuint64_t)s.Co * s.KH * s.KW};
     cuuint64_t strides[1] = {(cuuint64_t)s.C * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BN};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -354,39 +364,50 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     __nv_bfloat16* xt = (__nv_bfloat16*)ws;
     __nv_bfloat16* wt = (__nv_bfloat16*)(ws + (((size_t)s.N * s.H * s.W * s.C * 2 + 1023) & ~(size_t)1023));
     const int HW = s.H * s.W;
-    {   // x[N][C][HW] -> xt[N][HW][C]
-        dim3 g((unsigned)((HW + 63) / 64), (unsigned)((s.C + 63) / 64), (unsigned)s.N);
-        transpose_bf16_batched_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW);
+    {   // x[N][C][HW] -> xt[N][HW][C], and the weights tap-major, in one launch
         const int64_t nw = (int64_t)s.Co * s.C * s.KH * s.KW;
-        weight_tap_major_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW);
+        const unsigned gx = (unsigned)((HW + 63) / 64), gy = (unsigned)((s.C + 63) / 64);
+        const int64_t per_slice = (int64_t)gx * gy * 256;
+        const unsigned wz = (unsigned)std::min<int64_t>(32, std::max<int64_t>(1, (nw + per_slice - 1) / per_slice));
+        dim3 g(gx, gy, (unsigned)s.N + wz);
+        transpose_bf16_batched_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW, (int)wz,
+                                                          (const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW);
         B200JT_LAUNCH_CHECK();
     }
-    CUtensorMap mx, mw;
-    if (!make_map_x(&mx, xt, s) || !make_map_w(&mw, wt, s)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed");
     ConvArgs A;
     A.N = s.N; A.C = s.C; A.H = s.H; A.W = s.W; A.Co = s.Co; A.KH = s.KH; A.KW = s.KW; A.OH = s.OH; A.OW = s.OW;
     A.ph = s.ph; A.pw = s.pw; A.dh = s.dh; A.dw = s.dw;
     A.tiles_h = (s.OH + PATCH - 1) / PATCH; A.tiles_w = (s.OW + PATCH - 1) / PATCH;
     A.patches = (int64_t)s.N * A.tiles_h * A.tiles_w;
-    A.tiles_m = (int)((A.patches + 1) / 2); A.tiles_n = (s.Co + BN - 1) / BN;
+    A.tiles_m = (int)((A.patches + 1) / 2);
+    // Tile width: the grid is persistent with a static round-robin, so its time is ceil(tiles / SMs) rounds. 128-wide
+    // tiles do a little worse per FLOP (more operand bytes per MMA) but halve the granularity of the last round.
+    auto rounds = [&](int bn) { const int64_t t = (int64_t)A.tiles_m * ((s.Co + bn - 1) / bn); return (double)((t + kNumSMs - 1) / kNumSMs) * bn; };
+    static const int forced_bn = [] { const char* e = getenv("B200JT_CONV_BN"); return e ? atoi(e) : 0; }();
+    const int bn = forced_bn == 128 || forced_bn == 256 ? forced_bn : (rounds(128) * kNarrowTilePenalty < rounds(256) ? 128 : 256);
+    A.tiles_n = (s.Co + bn - 1) / bn;
+    CUtensorMap mx, mw;
+    if (!make_map_x(&mx, xt, s) || !make_map_w(&mw, wt, s, bn)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(conv_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(conv_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        const void* kernels[] = {(const void*)conv_bf16_kernel<true, 256>, (const void*)conv_bf16_kernel<false, 256>,
+                                 (const void*)conv_bf16_kernel<true, 128>, (const void*)conv_bf16_kernel<false, 128>};
+        for (const void* k : kernels)
+            if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     });
     B200JT_CUDA(attr_err);
     // TMA stores need a 16-byte aligned base and row pitch
     const bool tma_out = (s.OW % 8 == 0) && ((uintptr_t)y % 16 == 0);
     CUtensorMap my = mx;
     if (tma_out && !make_map_y(&my, y, s)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed (y)");
-    float* fused = (stats && A.tiles_n == 1) ? stats : nullptr;
+    float* fused = (stats && s.Co <= STATS_MAX_CO) ? stats : nullptr;
     if (fused) B200JT_CUDA(cudaMemsetAsync(stats, 0, sizeof(float) * 2 * s.Co, st));
     const int total = A.tiles_m * A.tiles_n;
     const int grid = total < kNumSMs ? total : kNumSMs;
-    if (tma_out) conv_bf16_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, my, (__nv_bfloat16*)y, fused, A);
-    else conv_bf16_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, my, (__nv_bfloat16*)y, fused, A);
+    auto kern = bn == 256 ? (tma_out ? conv_bf16_kernel<true, 256> : conv_bf16_kernel<false, 256>)
+                          : (tma_out ? conv_bf16_kernel<true, 128> : conv_bf16_kernel<false, 128>);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, my, (__nv_bfloat16*)y, fused, A);
     B200JT_LAUNCH_CHECK();
     return fused ? 1 : 0;      // 1: statistics were produced by the epilogue
 }

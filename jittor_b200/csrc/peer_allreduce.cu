@@ -5,7 +5,7 @@
 // Every rank owns one `segment` of device memory, exported to the other ranks as a CUDA IPC handle:
 //     [ flags : kMaxBlocks x kMaxRanks u32 ][ epochs : kMaxBlocks u32 ][ in[0] | in[1] | out[0] | out[1] : data_bytes each ]
 // Block b of rank r only ever talks to block b of the other ranks:
-//   small messages (one shot):  copy its chunk of src into in[parity] of its own segment, flag every peer, wait for
+//   small messages (one shot, while (world-1) * bytes <= 4 MiB):  copy its chunk of src into in[parity] of its own segment, flag every peer, wait for
 //       every peer's flag, then sum that chunk over the ranks' segments IN RANK ORDER (so all ranks get the same
 //       bits) straight into dst;
 //   large messages (two shot):  the same hand-off, then rank r sums only slice r and writes the result into
@@ -24,17 +24,17 @@ namespace b200jt {
 namespace peer {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxBlocks = 64;
+constexpr int kMaxBlocks = 128;
 constexpr int kThreads = 512;
 constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * 4;
 constexpr size_t kEpochBytes = (size_t)kMaxBlocks * 4;
-constexpr size_t kHeaderBytes = 4096;                       // flags + epochs, padded so the data halves stay 256-B aligned
+constexpr size_t kHeaderBytes = 8192;                       // flags + epochs, padded so the data halves stay 256-B aligned
 static_assert(kFlagBytes + kEpochBytes <= kHeaderBytes, "header too small");
-constexpr size_t kOneShotMaxBytes = 256 << 10;
+constexpr size_t kOneShotMaxRemoteBytes = 4 << 20;      // one shot while a rank reads at most this much from its peers
 
 static __device__ int g_status = 0;
 
-struct DevComm {                    // lives in device memory, one per (emulated) rank
+struct DevComm {                    // one per (emulated) rank, passed to the kernel by value
     unsigned char* seg[kMaxRanks];  // every rank's segment as mapped into THIS process
     int rank, world;
     unsigned long long data_bytes;  // capacity of each of the four data halves
@@ -42,7 +42,7 @@ struct DevComm {                    // lives in device memory, one per (emulated
 };
 
 struct Launch {                     // by-value kernel argument; entry blockIdx.y is the rank this block plays
-    const DevComm* comm[kMaxRanks];
+    DevComm comm[kMaxRanks];
     const void* src[kMaxRanks];
     void* dst[kMaxRanks];
 };
@@ -70,20 +70,29 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // One flag round of block `b`: tell every peer that this rank reached `value`, then wait until every peer did.
+// The block's earlier writes are ordered before the flags by the barrier plus the release store of the flagging
+// thread (release is cumulative over what that thread observed through the barrier); the peers' writes are ordered
+// before this block's later reads by the acquire fence of the polling thread plus the closing barrier.
 // Returns false for the whole block if a wait ran out.
 __device__ bool flag_round(const DevComm& c, int b, uint32_t value, int* ok_smem) {
-    __threadfence_system();
     __syncthreads();
     const int t = threadIdx.x;
     if (t < c.world && t != c.rank) {
         st_release_sys(flag_of(c.seg[t], b, c.rank), value);
         const uint32_t* mine = flag_of(c.seg[c.rank], b, t);
-        const unsigned long long t0 = global_ns();
         uint32_t spins = 0;
-        while ((int32_t)(ld_acquire_sys(mine) - value) < 0) {
-            if (++spins > 256) {
-                __nanosleep(spins > 4096 ? 200 : 20);
+        unsigned long long t0 = 0;
+        while ((int32_t)(ld_relaxed_sys(mine) - value) < 0) {
+            if (++spins > 512) {
+                if (t0 == 0) t0 = global_ns();
+                __nanosleep(spins > 8192 ? 200 : 20);
                 if ((spins & 255) == 0 && global_ns() - t0 > c.wait_ns) {
                     *ok_smem = 0;
                     atomicCAS(&g_status, 0, 5);
@@ -91,9 +100,9 @@ __device__ bool flag_round(const DevComm& c, int b, uint32_t value, int* ok_smem
                 }
             }
         }
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
     }
     __syncthreads();
-    __threadfence_system();
     return *ok_smem != 0;
 }
 
@@ -141,73 +150,124 @@ template <typename T, int V> __device__ __forceinline__ void store_user(T* base,
     }
 }
 
-template <typename T, int V, int OP> __device__ __forceinline__ Pack<T, V> reduce_over_ranks(const DevComm& c, int parity, long long i) {
+// Sum (max, min) of `U` packs, kThreads apart starting at i, over the ranks' in[parity] halves: all loads are issued
+// before the first use, so that a thread keeps U * world 16-byte NVLink reads in flight.
+template <typename T, int V, int OP, int U>
+__device__ __forceinline__ void reduce_over_ranks(const DevComm& c, int parity, int i, int hi, Pack<T, V> (&o)[U]) {
     using A = typename Acc<T>::type;
-    Pack<T, V> p[kMaxRanks];
+    Pack<T, V> p[kMaxRanks][U];
 #pragma unroll
-    for (int k = 0; k < kMaxRanks; k++)
-        if (k < c.world) p[k] = load_seg<T, V>(reinterpret_cast<const T*>(half_of(c.seg[k], c.data_bytes, parity)) + i * V);
-    Pack<T, V> o;
+    for (int k = 0; k < kMaxRanks; k++) {
+        if (k < c.world) {
+            const T* base = reinterpret_cast<const T*>(half_of(c.seg[k], c.data_bytes, parity));
 #pragma unroll
-    for (int e = 0; e < V; e++) {
-        A acc = (A)p[0].v[e];
-#pragma unroll
-        for (int k = 1; k < kMaxRanks; k++)
-            if (k < c.world) acc = combine<OP, A>(acc, (A)p[k].v[e]);        // rank order: the same bits on every rank
-        o.v[e] = (T)acc;
+            for (int u = 0; u < U; u++)
+                if (i + u * kThreads < hi) p[k][u] = load_seg<T, V>(base + (size_t)(i + u * kThreads) * V);
+        }
     }
-    return o;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+#pragma unroll
+        for (int e = 0; e < V; e++) {
+            A acc = (A)p[0][u].v[e];
+#pragma unroll
+            for (int k = 1; k < kMaxRanks; k++)
+                if (k < c.world) acc = combine<OP, A>(acc, (A)p[k][u].v[e]);     // rank order: the same bits on every rank
+            o[u].v[e] = (T)acc;
+        }
+    }
 }
+
+// The packs block b owns: chunk b (per packs) of each of `slices` slices, as one flat index space of slices*per entries.
+struct BlockPacks {
+    int slice, per, b, nv, slices;
+    __device__ __forceinline__ int total() const { return slices * per; }
+    __device__ __forceinline__ int at(int f) const {            // pack index, or -1 for padding
+        const int s = f / per, j = f - s * per;
+        const int i = s * slice + per * b + j;
+        return (f < slices * per && i < min(nv, (s + 1) * slice)) ? i : -1;
+    }
+};
 
 // The message is cut into 16-byte packs (nv of them, the last one possibly partial); which block handles which pack
 // depends on the byte count only, so that all ranks agree whatever the alignment of their src/dst pointers.
 template <typename T, int OP, bool TWO_SHOT>
 __global__ void __launch_bounds__(kThreads) peer_all_reduce_kernel(Launch L, long long count) {
     constexpr int V = 16 / (int)sizeof(T);
+    constexpr int UC = 4;               // packs in flight per thread in the copies
+    constexpr int UR = 2;               // ... and per rank in the reduction
     __shared__ int ok;
     __shared__ DevComm c;
-    if (threadIdx.x == 0) { c = *L.comm[blockIdx.y]; ok = 1; }
+    if (threadIdx.x == 0) { c = L.comm[blockIdx.y]; ok = 1; }
     __syncthreads();
     const T* src = static_cast<const T*>(L.src[blockIdx.y]);
     T* dst = static_cast<T*>(L.dst[blockIdx.y]);
     const bool src_vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0, dst_vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-    const long long nv = (count + V - 1) / V;
+    const int nv = (int)((count + V - 1) / V);
     const int b = blockIdx.x, nb = gridDim.x, W = c.world, r = c.rank;
     uint32_t* epoch_ptr = epoch_of(c.seg[r], b);
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ptr);
     const int parity = (epoch >> 1) & 1;
     T* in_own = reinterpret_cast<T*>(half_of(c.seg[r], c.data_bytes, parity));
-    __syncthreads();
 
-    if (!TWO_SHOT) {
-        const long long per = (nv + nb - 1) / nb, lo = per * b, hi = min(nv, lo + per);
-        for (long long i = lo + threadIdx.x; i < hi; i += kThreads) store_seg<T, V>(in_own + i * V, load_user<T, V>(src, i, count, src_vec));
-        if (flag_round(c, b, epoch + 1, &ok))
-            for (long long i = lo + threadIdx.x; i < hi; i += kThreads)
-                store_user<T, V>(dst, i, count, dst_vec, reduce_over_ranks<T, V, OP>(c, parity, i));
-    } else {
-        // slice s = packs [s*slice, (s+1)*slice) is reduced by rank s; block b handles chunk b of every slice
-        const long long slice = (nv + W - 1) / W, per = (slice + nb - 1) / nb;
-        for (int s = 0; s < W; s++) {
-            const long long lo = s * slice + per * b, hi = min(min(nv, (s + 1) * slice), lo + per);
-            for (long long i = lo + threadIdx.x; i < hi; i += kThreads) store_seg<T, V>(in_own + i * V, load_user<T, V>(src, i, count, src_vec));
-        }
-        bool fine = flag_round(c, b, epoch + 1, &ok);
-        if (fine) {
-            const long long lo = r * slice + per * b, hi = min(min(nv, (r + 1) * slice), lo + per);
-            for (long long i = lo + threadIdx.x; i < hi; i += kThreads) {
-                const Pack<T, V> o = reduce_over_ranks<T, V, OP>(c, parity, i);
+    // slice s = packs [s*slice, (s+1)*slice) is reduced by rank s (two shot) or there is one slice every rank reduces
+    BlockPacks mine;
+    mine.slices = TWO_SHOT ? W : 1;
+    mine.slice = TWO_SHOT ? (nv + W - 1) / W : nv;
+    mine.per = (mine.slice + nb - 1) / nb;
+    mine.b = b; mine.nv = nv;
+    const int lo = (TWO_SHOT ? r * mine.slice : 0) + mine.per * b;
+    const int hi = min(min(nv, (TWO_SHOT ? r + 1 : 1) * mine.slice), lo + mine.per);
+
+    // 1. this block's packs of src -> in[parity] of the own segment
+    for (int f0 = threadIdx.x; f0 < mine.total(); f0 += UC * kThreads) {
+        int idx[UC];
+        Pack<T, V> p[UC];
 #pragma unroll
-                for (int k = 0; k < kMaxRanks; k++)
-                    if (k < W) store_seg<T, V>(reinterpret_cast<T*>(half_of(c.seg[k], c.data_bytes, 2 + parity)) + i * V, o);
-            }
-            fine = flag_round(c, b, epoch + 2, &ok);
+        for (int u = 0; u < UC; u++) {
+            idx[u] = mine.at(f0 + u * kThreads);
+            if (idx[u] >= 0) p[u] = load_user<T, V>(src, idx[u], count, src_vec);
         }
+#pragma unroll
+        for (int u = 0; u < UC; u++)
+            if (idx[u] >= 0) store_seg<T, V>(in_own + (size_t)idx[u] * V, p[u]);
+    }
+    bool fine = flag_round(c, b, epoch + 1, &ok);
+    // 2. reduce over the ranks: everything into dst (one shot), or the own slice into out[parity] of every rank
+    if (fine) {
+        for (int i = lo + threadIdx.x; i < hi; i += UR * kThreads) {
+            Pack<T, V> o[UR];
+            reduce_over_ranks<T, V, OP, UR>(c, parity, i, hi, o);
+#pragma unroll
+            for (int u = 0; u < UR; u++) {
+                const int iu = i + u * kThreads;
+                if (iu >= hi) continue;
+                if (!TWO_SHOT) {
+                    store_user<T, V>(dst, iu, count, dst_vec, o[u]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < kMaxRanks; k++)
+                        if (k < W) store_seg<T, V>(reinterpret_cast<T*>(half_of(c.seg[k], c.data_bytes, 2 + parity)) + (size_t)iu * V, o[u]);
+                }
+            }
+        }
+    }
+    if (TWO_SHOT) {
+        if (fine) fine = flag_round(c, b, epoch + 2, &ok);
+        // 3. out[parity] of the own segment (filled by all ranks) -> dst
         if (fine) {
             const T* out_own = reinterpret_cast<const T*>(half_of(c.seg[r], c.data_bytes, 2 + parity));
-            for (int s = 0; s < W; s++) {
-                const long long lo = s * slice + per * b, hi = min(min(nv, (s + 1) * slice), lo + per);
-                for (long long i = lo + threadIdx.x; i < hi; i += kThreads) store_user<T, V>(dst, i, count, dst_vec, load_seg<T, V>(out_own + i * V));
+            for (int f0 = threadIdx.x; f0 < mine.total(); f0 += UC * kThreads) {
+                int idx[UC];
+                Pack<T, V> p[UC];
+#pragma unroll
+                for (int u = 0; u < UC; u++) {
+                    idx[u] = mine.at(f0 + u * kThreads);
+                    if (idx[u] >= 0) p[u] = load_seg<T, V>(out_own + (size_t)idx[u] * V);
+                }
+#pragma unroll
+                for (int u = 0; u < UC; u++)
+                    if (idx[u] >= 0) store_user<T, V>(dst, idx[u], count, dst_vec, p[u]);
             }
         }
     }
@@ -221,7 +281,7 @@ struct Comm {
     unsigned char* segs[kMaxRanks] = {};
     bool opened[kMaxRanks] = {};        // mapped through an IPC handle (to be closed), not owned
     bool owns_segment = false;
-    DevComm* dev = nullptr;
+    DevComm dev{};                      // what the kernel receives
 };
 
 static size_t segment_bytes(size_t data_bytes) { return kHeaderBytes + 4 * data_bytes; }
@@ -231,8 +291,7 @@ static int upload(Comm* c, double wait_ms) {
     for (int i = 0; i < c->world; i++) h.seg[i] = c->segs[i];
     h.rank = c->rank; h.world = c->world; h.data_bytes = c->data_bytes;
     h.wait_ns = (unsigned long long)(wait_ms * 1e6);
-    if (!c->dev) B200JT_CUDA(cudaMalloc(&c->dev, sizeof(DevComm)));
-    B200JT_CUDA(cudaMemcpy(c->dev, &h, sizeof(h), cudaMemcpyHostToDevice));
+    c->dev = h;
     return 0;
 }
 
@@ -240,7 +299,7 @@ template <typename T, int OP>
 static int launch_t(const Launch& L, int ranks_in_grid, int world, int64_t count, cudaStream_t st) {
     const size_t bytes = (size_t)count * sizeof(T);
     const long long nv = (long long)((bytes + 15) / 16);
-    const bool two = bytes > kOneShotMaxBytes;
+    const bool two = bytes * (size_t)(world - 1) > kOneShotMaxRemoteBytes;
     const long long unit = two ? (nv + world - 1) / world : nv;             // packs one rank reduces
     // an emulated job keeps every rank's blocks co-resident: at most one block per SM over all ranks
     const int cap = ranks_in_grid == 1 ? kMaxBlocks : std::max(1, std::min(kMaxBlocks, kNumSMs / ranks_in_grid));
@@ -304,7 +363,8 @@ namespace b200jt { int peer_status_fetch_and_clear() { return peer::status_fetch
 extern "C" size_t b200jt_peer_segment_bytes(size_t data_bytes) { return peer::segment_bytes(data_bytes); }
 
 extern "C" int b200jt_peer_segment_create(size_t data_bytes, void** segment, unsigned char* ipc_handle) {
-    B200JT_CHECK_ARG(segment && ipc_handle && data_bytes > 0 && data_bytes % 256 == 0, "data_bytes must be a positive multiple of 256");
+    B200JT_CHECK_ARG(segment && ipc_handle && data_bytes > 0 && data_bytes % 256 == 0 && data_bytes <= ((size_t)1 << 30),
+                     "data_bytes must be a positive multiple of 256, at most 1 GiB");
     void* p = nullptr;
     B200JT_CUDA(cudaMalloc(&p, peer::segment_bytes(data_bytes)));
     B200JT_CUDA(cudaMemset(p, 0, peer::segment_bytes(data_bytes)));
@@ -348,7 +408,8 @@ extern "C" int b200jt_peer_comm_create(int rank, int world, void* own_segment, c
 
 extern "C" int b200jt_peer_comm_create_local(int world, size_t data_bytes, double wait_ms, void** comms) {
     B200JT_CHECK_ARG(comms && world >= 2 && world <= peer::kMaxRanks, "world must be 2..8");
-    B200JT_CHECK_ARG(data_bytes > 0 && data_bytes % 256 == 0 && wait_ms > 0, "data_bytes must be a positive multiple of 256, wait_ms positive");
+    B200JT_CHECK_ARG(data_bytes > 0 && data_bytes % 256 == 0 && data_bytes <= ((size_t)1 << 30) && wait_ms > 0,
+                     "data_bytes must be a positive multiple of 256, at most 1 GiB; wait_ms positive");
     unsigned char* segs[peer::kMaxRanks] = {};
     for (int i = 0; i < world; i++) {
         B200JT_CUDA(cudaMalloc(&segs[i], peer::segment_bytes(data_bytes)));
@@ -372,7 +433,6 @@ extern "C" int b200jt_peer_comm_destroy(void* comm) {
     cudaDeviceSynchronize();
     for (int i = 0; i < c->world; i++) if (c->opened[i]) cudaIpcCloseMemHandle(c->segs[i]);
     if (c->owns_segment && c->segs[c->rank]) cudaFree(c->segs[c->rank]);
-    if (c->dev) cudaFree(c->dev);
     delete c;
     return 0;
 }
