@@ -93,6 +93,16 @@ int b200jt_reindex_reduce_noalloc(const b200jt_tensor* y, const b200jt_tensor* x
                                   const char* const* overflow_conditions, int n_conditions,
                                   const b200jt_tensor* extras, int n_extras, void* stream);
 
+/* out = x; for every element i of data: out[index_0(i), ...] = op(out[...], data[i]); op "void" assigns.
+ * Replaces SetitemOp(Var* x, VarSlices&& slices, Var* y, NanoString op), python/jittor/src/ops/setitem_op.h:24, jit_run
+ * python/jittor/src/ops/setitem_op.cc:268-366: the host turns the slices into one index expression per axis of x
+ * (loop variable, start + step * loop variable, constant, formula string, or @eK load of an index Var) and broadcasts
+ * data to the shape of the sliced region. x and out may be the same buffer (the reference's in-place form).
+ * op: void add multiply maximum minimum bitwise_and/or/xor logical_and/or/xor. */
+int b200jt_setitem(const b200jt_tensor* x, const b200jt_tensor* data, const b200jt_tensor* out, const char* op,
+                   const char* const* indexes, int n_indexes,
+                   const b200jt_tensor* extras, int n_extras, void* stream);
+
 /* z[i] = x[i with the axes of bcast_mask zeroed]; x is passed with z's rank (size-1 axes where broadcast).
  * Replaces BroadcastToOp(Var* x, NanoVector shape, uint dims_mask, uint keepdims_mask)
  * python/jittor/src/ops/broadcast_to_op.h:90, jit_run python/jittor/src/ops/broadcast_to_op.cc:177-194. */

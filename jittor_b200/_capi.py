@@ -54,6 +54,7 @@ SIGNATURES = [
     ("b200jt_reindex_reduce", _i, [_TP, _TP, ctypes.c_char_p, _SP, _i, _SP, _i, _TP, _i, _vp, _sz, _vp]),
     ("b200jt_reindex_reduce_noalloc_max_scratch", _sz, []),
     ("b200jt_reindex_reduce_noalloc", _i, [_TP, _TP, ctypes.c_char_p, _SP, _i, _SP, _i, _TP, _i, _vp]),
+    ("b200jt_setitem", _i, [_TP, _TP, _TP, ctypes.c_char_p, _SP, _i, _TP, _i, _vp]),
     ("b200jt_broadcast_to", _i, [_TP, _TP, _u32, _vp]),
     ("b200jt_reduce_workspace", _sz, [_TP, _TP, ctypes.c_char_p, _u32]),
     ("b200jt_reduce", _i, [_TP, _TP, ctypes.c_char_p, _u32, _vp, _sz, _vp]),

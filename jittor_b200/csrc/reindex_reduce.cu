@@ -577,6 +577,51 @@ extern "C" int b200jt_reindex_reduce(const b200jt_tensor* y, const b200jt_tensor
     return fail(-1, "b200jt_reindex_reduce: unsupported dtype");
 }
 
+// ---- setitem: accumulate into a copy of x instead of into the op's identity -------------------------------
+// out = x; for every element i of data: out[index(i)] = op(out[index(i)], data[i]); op "void" assigns. This is the
+// loop of SetitemOp::jit_run (python/jittor/src/ops/setitem_op.cc:312-366): the copy, then one read-modify-write per
+// element of the sliced region. Elements whose index falls outside out are skipped (the reference does not check).
+// "add" (and the other ops with an atomic form) are exact under duplicate indices; "void" keeps one of the
+// duplicates, as on the reference's CUDA path.
+extern "C" int b200jt_setitem(const b200jt_tensor* x, const b200jt_tensor* data, const b200jt_tensor* out, const char* op,
+                              const char* const* indexes, int n_indexes,
+                              const b200jt_tensor* extras, int n_extras, void* stream) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(out) && valid_tensor(data), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(x->dtype == out->dtype && x->ndim == out->ndim, "x and out must have the same dtype and shape");
+    for (int d = 0; d < x->ndim; d++) B200JT_CHECK_ARG(x->shape[d] == out->shape[d], "x and out must have the same shape");
+    IndexProgram P; int opc; RRPlan plan;
+    int rc = prepare(data, out, op, indexes, n_indexes, nullptr, 0, extras, n_extras, &P, &opc, &plan);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t bins = numel(out);
+    if (bins == 0) return 0;
+    if (x->ptr != out->ptr)
+        B200JT_CUDA(cudaMemcpyAsync(out->ptr, x->ptr, (size_t)bins * dtype_size(x->dtype), cudaMemcpyDeviceToDevice, st));
+    const int64_t n = numel(data);
+    if (n == 0) return 0;
+    const bool small = n < (1LL << 31) && bins < (1LL << 31);
+    const unsigned grid = grid_for(n, 256);
+#define B200JT_SETITEM(T)                                                                                        \
+    do { if (small) rr_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, n, opc);  \
+         else       rr_generic_kernel<T, int64_t><<<grid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, n, opc);  \
+    } while (0)
+    switch (out->dtype) {
+        case B200JT_BOOL: case B200JT_UINT8: B200JT_SETITEM(uint8_t); break;
+        case B200JT_INT8: B200JT_SETITEM(int8_t); break;
+        case B200JT_INT16: B200JT_SETITEM(int16_t); break;
+        case B200JT_INT32: B200JT_SETITEM(int32_t); break;
+        case B200JT_INT64: B200JT_SETITEM(int64_t); break;
+        case B200JT_FLOAT16: B200JT_SETITEM(__half); break;
+        case B200JT_BFLOAT16: B200JT_SETITEM(__nv_bfloat16); break;
+        case B200JT_FLOAT32: B200JT_SETITEM(float); break;
+        case B200JT_FLOAT64: B200JT_SETITEM(double); break;
+        default: return fail(-1, "b200jt_setitem: unsupported dtype");
+    }
+#undef B200JT_SETITEM
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
 // ---- allocation-free variant ----------------------------------------------------------------------
 // Some callers cannot hand over a workspace because they are not allowed to allocate device memory at
 // the point of the call: code running inside a memory-pool callback, a real-time loop whose allocator is

@@ -690,3 +690,138 @@ def maxpool2x2_bwd(x, dy):
     cond = binary(xx, broadcast(out, shape6, [4, 5]), "equal")
     dxx = ternary(cond, broadcast(np.asarray(dy), shape6, [4, 5]), np.zeros(shape6, np.float32))
     return reindex_reduce(dxx, "add", list(x.shape), idx)
+
+
+# --------------------------------------------------------------------------- getitem / setitem
+def _resolve_slices(in_shape, slices):
+    """GetitemOp::infer_slices, python/jittor/src/ops/getitem_op.cc:66-187. `slices`: tuple of int, slice, Ellipsis,
+    None, str (formula over the output loop variables) and integer numpy arrays (index Vars).
+    Returns (per input axis: ("loop", o) | ("slice", o, start, step) | ("int", v) | ("str", text) | ("var", array),
+    out_shape, first output axis of the index arrays, number of axes they span)."""
+    slices = list(slices) if isinstance(slices, tuple) else [slices]
+    nin = len(in_shape)
+    arrays = [s for s in slices if isinstance(s, np.ndarray)]
+    var_dim = max((a.ndim for a in arrays), default=0)
+    axes, out_shape, fov = [], [], -1
+    vid = i = 0
+    while i < nin:
+        if vid >= len(slices):                                   # :78-85 axes past the last slice pass through
+            axes.append(("loop", len(out_shape))); out_shape.append(in_shape[i]); i += 1
+            continue
+        s = slices[vid]
+        if isinstance(s, np.ndarray):                            # :87-113 index arrays broadcast from the right
+            if fov < 0:
+                fov = len(out_shape)
+                out_shape += [1] * var_dim
+            for j in range(s.ndim):
+                o = fov + var_dim - 1 - j
+                n = s.shape[s.ndim - 1 - j]
+                if not (out_shape[o] == n or out_shape[o] == 1 or n == 1):
+                    raise ValueError("Shape not match")
+                if out_shape[o] == 1:
+                    out_shape[o] = n
+            axes.append(("var", s)); vid += 1; i += 1
+        elif s is Ellipsis:                                      # :115-130
+            remain = len(slices) - vid - 1 - sum(1 for t in slices[vid + 1:] if t is None)
+            for _ in range((nin - i) - remain):
+                axes.append(("loop", len(out_shape))); out_shape.append(in_shape[i]); i += 1
+            vid += 1
+        elif s is None:                                          # :132-137
+            out_shape.append(1); vid += 1
+        elif isinstance(s, str):                                 # :147-150
+            axes.append(("str", s)); vid += 1; i += 1
+        elif isinstance(s, slice):                               # :151-176
+            if s.start is None and s.stop is None and s.step is None:
+                axes.append(("loop", len(out_shape))); out_shape.append(in_shape[i])
+            else:
+                idx = range(*s.indices(in_shape[i]))
+                axes.append(("slice", len(out_shape), idx.start, idx.step)); out_shape.append(len(idx))
+            vid += 1; i += 1
+        else:                                                    # :139-146
+            v = int(s)
+            if v < 0:
+                v += in_shape[i]
+            if not 0 <= v < in_shape[i]:
+                raise IndexError("slice overflow")
+            axes.append(("int", v)); vid += 1; i += 1
+    for s in slices[vid:]:                                       # :178-185
+        if s is None:
+            out_shape.append(1)
+        elif s is not Ellipsis:
+            raise IndexError("Too many slices")
+    return axes, out_shape, fov, var_dim
+
+
+def _slice_flat_index(in_shape, axes, out_shape, fov, var_dim, wrap):
+    """Flat input offset for every point of the loop nest over out_shape (getitem_op.cc:560-577)."""
+    grids = np.indices(tuple(out_shape), dtype=np.int64, sparse=True)
+    env = {f"i{d}": g for d, g in enumerate(grids)}
+    flat = np.zeros(tuple(out_shape), dtype=np.int64)
+    for d, ax in enumerate(axes):
+        kind = ax[0]
+        if kind == "loop":
+            iid = grids[ax[1]]
+        elif kind == "slice":
+            iid = grids[ax[1]] * ax[3] + ax[2]
+        elif kind == "int":
+            iid = np.int64(ax[1])
+        elif kind == "str":
+            iid = _eval(_Parser(ax[1]).parse(), env, [])
+        else:
+            a = ax[1]
+            off = fov + var_dim - a.ndim
+            sub = tuple(grids[off + j] if a.shape[j] == out_shape[off + j] else np.int64(0) for j in range(a.ndim))
+            iid = a[sub].astype(np.int64) if a.ndim else a.astype(np.int64)
+        iid = np.broadcast_to(iid, tuple(out_shape))
+        if wrap:
+            iid = np.where(iid < 0, iid + in_shape[d], iid)      # :573 `if (iid<0) iid += ishape`
+        flat = flat * in_shape[d] + iid
+    return flat
+
+
+def getitem(x, slices):
+    """GetitemOp::jit_run, python/jittor/src/ops/getitem_op.cc:512-580."""
+    x = np.asarray(x)
+    axes, out_shape, fov, var_dim = _resolve_slices(list(x.shape), slices)
+    if not out_shape:
+        out_shape = [1]
+    flat = _slice_flat_index(x.shape, axes, out_shape, fov, var_dim, True)
+    return x.reshape(-1)[flat]
+
+
+def setitem(x, slices, data, op="void"):
+    """SetitemOp::jit_run, python/jittor/src/ops/setitem_op.cc:268-366: copy, then out[iid] = op(out[iid], data[did])
+    in loop order (the last duplicate wins for 'void'); data broadcasts from the right (:72-85) and is cast to x's
+    dtype (`(Ti)dp[did]`)."""
+    x = np.asarray(x)
+    axes, out_shape, fov, var_dim = _resolve_slices(list(x.shape), slices)
+    if not out_shape:
+        out_shape = [1]
+    flat = _slice_flat_index(x.shape, axes, out_shape, fov, var_dim, False).reshape(-1)
+    data = np.broadcast_to(np.asarray(data).astype(x.dtype), tuple(out_shape)).reshape(-1)
+    out = x.copy().reshape(-1)
+    if op == "void":
+        out[flat] = data
+    else:
+        uf = {"add": np.add, "multiply": np.multiply, "maximum": np.maximum, "minimum": np.minimum,
+              "bitwise_and": np.bitwise_and, "bitwise_or": np.bitwise_or, "bitwise_xor": np.bitwise_xor}[op]
+        uf.at(out, flat, data)
+    return out.reshape(x.shape)
+
+
+def scatter(x, dim, index, src, reduce="void"):
+    """python/jittor/misc.py:1563-1605."""
+    index, src = np.asarray(index), np.asarray(src)
+    if src.shape != index.shape and src.size != 1:
+        src = src[tuple(slice(None, s) for s in index.shape)]
+    idx = [f"i{i}" for i in range(index.ndim)]
+    idx[dim] = index
+    return setitem(x, tuple(idx), src, reduce)
+
+
+def gather(x, dim, index):
+    """python/jittor/misc.py:1610-1645."""
+    index = np.asarray(index)
+    idx = [f"i{i}" for i in range(index.ndim)]
+    idx[dim] = index
+    return getitem(x, tuple(idx))

@@ -1,0 +1,176 @@
+"""Generate `next_ops.{json,npz}`: golden fixtures for the callers either side of the meta-operator path (slicing,
+scatter/gather, pooling, grouped / transposed convolution, the data-parallel optimiser step), from the reference's own
+CPU implementation. Same recipe and same bridge as make_golden.py:
+
+    HOME=/tmp/jt_home PYTHONPATH=<reference>/python nvcc_path="" use_mkl=0 use_mpi=0 \
+        cache_name=oracle python tests/golden/make_golden_next.py
+
+Slices are stored as a list of items: {"i": int} | {"s": [start, stop, step]} | "..." | null | {"f": formula} |
+{"v": k} (the k-th array of the case's `extras`).
+"""
+import ctypes
+import json
+import os
+
+import numpy as np
+
+import jittor as jt
+from jittor import nn
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+jt.flags.enable_tuner = 0
+rng = np.random.default_rng(20240607)
+ARRAYS, CASES = {}, []
+
+
+def to_jt(a):
+    a = np.ascontiguousarray(a)
+    v = jt.empty(list(a.shape), str(a.dtype))
+    v.sync()
+    if a.nbytes:
+        ctypes.memmove(v.raw_ptr, a.ctypes.data, a.nbytes)
+    return v
+
+
+def to_np(v):
+    v.sync()
+    out = np.empty(tuple(v.shape), dtype=str(v.dtype))
+    if out.nbytes:
+        ctypes.memmove(out.ctypes.data, v.raw_ptr, out.nbytes)
+    return out
+
+
+def put(name, arr):
+    ARRAYS[name] = np.ascontiguousarray(arr)
+    return name
+
+
+def case(name, op, args, inputs, out, extras=()):
+    assert name not in [c["name"] for c in CASES], name
+    CASES.append({"name": name, "op": op, "args": args,
+                  "inputs": [put(f"{name}/in{i}", a) for i, a in enumerate(inputs)],
+                  "extras": [put(f"{name}/ex{i}", a) for i, a in enumerate(extras)],
+                  "out": put(f"{name}/out", out), "out_dtype": str(out.dtype), "out_shape": list(out.shape)})
+
+
+def f32(*shape):
+    return rng.uniform(-1, 1, size=shape).astype(np.float32)
+
+
+def i32(*shape, lo=0, hi=100):
+    return rng.integers(lo, hi, size=shape).astype(np.int32)
+
+
+def encode(slices, extras):
+    enc = []
+    for s in slices if isinstance(slices, tuple) else (slices,):
+        if isinstance(s, np.ndarray):
+            extras.append(s)
+            enc.append({"v": len(extras) - 1})
+        elif isinstance(s, slice):
+            enc.append({"s": [s.start, s.stop, s.step]})
+        elif s is Ellipsis:
+            enc.append("...")
+        elif s is None:
+            enc.append(None)
+        elif isinstance(s, str):
+            enc.append({"f": s})
+        else:
+            enc.append({"i": int(s)})
+    return enc
+
+
+def jt_slices(slices):
+    return tuple(to_jt(s) if isinstance(s, np.ndarray) else s for s in (slices if isinstance(slices, tuple) else (slices,)))
+
+
+def do_getitem(name, x, slices):
+    extras = []
+    enc = encode(slices, extras)
+    y = to_jt(x).getitem(jt_slices(slices))
+    case(name, "getitem", {"slices": enc}, [x], to_np(y), extras)
+
+
+def do_setitem(name, x, slices, data, op="void"):
+    extras = []
+    enc = encode(slices, extras)
+    y = to_jt(x).setitem(jt_slices(slices), to_jt(data), op)
+    case(name, "setitem", {"slices": enc, "op": op}, [x, data], to_np(y), extras)
+
+
+x3 = f32(4, 5, 6)
+xi = i32(4, 5, 6)
+do_getitem("getitem_int", x3, 1)
+do_getitem("getitem_neg_int", x3, (-1, 2))
+do_getitem("getitem_all_ints", x3, (1, 2, 3))
+do_getitem("getitem_slice", x3, (slice(1, 3),))
+do_getitem("getitem_slice_step", x3, (slice(None), slice(0, 5, 2), slice(1, None, 3)))
+do_getitem("getitem_slice_neg_step", x3, (slice(None, None, -1), slice(4, 0, -2)))
+do_getitem("getitem_slice_neg_bounds", x3, (slice(-3, -1), slice(None, -2)))
+do_getitem("getitem_empty_slice", x3, (slice(3, 1),))
+do_getitem("getitem_ellipsis", x3, (Ellipsis, 2))
+do_getitem("getitem_ellipsis_mid", x3, (1, Ellipsis, slice(0, 2)))
+do_getitem("getitem_none", x3, (None, slice(None), 0))
+do_getitem("getitem_none_tail", x3, (slice(None), 1, None, slice(2, 4), None))
+do_getitem("getitem_var_1d", x3, (np.array([3, 0, 0, 2, 1], np.int32),))
+do_getitem("getitem_var_negative", x3, (np.array([-1, 0, -4], np.int32),))
+do_getitem("getitem_var_int64", xi, (slice(None), np.array([4, 4, 1], np.int64)))
+do_getitem("getitem_var_2d", x3, (slice(None), np.array([[0, 1, 2], [2, 3, 4]], np.int32)))
+do_getitem("getitem_two_vars", x3, (np.array([[0], [3]], np.int32), np.array([1, 2, 4], np.int32)))
+do_getitem("getitem_vars_broadcast", x3, (slice(None), np.array([[0, 1, 2], [2, 3, 4]], np.int32), np.array([5, 0, 1], np.int32)))
+do_getitem("getitem_vars_separated", x3, (np.array([1, 2], np.int32), slice(None), np.array([0, 5], np.int32)))
+do_getitem("getitem_var_slice_int", x3, (np.array([2, 2, 0], np.int32), slice(1, 4), 3))
+do_getitem("getitem_formula", x3, ("i0", np.array([[0, 4], [1, 1], [2, 0], [3, 3]], np.int32), "i1"))
+do_getitem("getitem_int8", rng.integers(-100, 100, size=(7, 9)).astype(np.int8), (slice(1, 6, 2), slice(None, None, -1)))
+do_getitem("getitem_float64", rng.normal(size=(6, 3)), (np.array([5, 1], np.int32), 2))
+do_getitem("getitem_1d_large", f32(100000), (slice(3, 99999, 7),))
+
+do_setitem("setitem_int", x3, 1, f32(5, 6))
+do_setitem("setitem_scalar", x3, (slice(1, 3), slice(None, None, 2)), np.array([7.0], np.float32))
+do_setitem("setitem_slice_bcast", x3, (slice(None), slice(1, 4)), f32(6))
+do_setitem("setitem_slice_bcast_mid", x3, (slice(0, 2),), f32(5, 1))
+do_setitem("setitem_neg_step", xi, (slice(None, None, -1), 0), i32(4, 6))
+do_setitem("setitem_ellipsis", x3, (Ellipsis, 5), f32(4, 5))
+do_setitem("setitem_none", x3, (None, 2), f32(1, 5, 6))
+do_setitem("setitem_var_unique", x3, (np.array([3, 0, 2], np.int32),), f32(3, 5, 6))
+do_setitem("setitem_var_2axes", x3, (np.array([0, 1, 3], np.int32), np.array([4, 4, 0], np.int32)), f32(3, 6))
+do_setitem("setitem_var_add_dup", x3, (np.array([1, 1, 1, 0], np.int32),), f32(4, 5, 6), "add")
+do_setitem("setitem_int_add_dup", xi, (slice(None), np.array([2, 2, 4, 2], np.int32)), i32(4, 4, 6), "add")
+do_setitem("setitem_var_max", x3, (np.array([1, 1, 2], np.int32),), f32(3, 5, 6), "maximum")
+do_setitem("setitem_var_min", x3, (np.array([1, 1, 2], np.int32),), f32(3, 5, 6), "minimum")
+do_setitem("setitem_var_mul", x3, (slice(None), np.array([0, 3], np.int32)), f32(4, 2, 6), "multiply")
+do_setitem("setitem_cast_data", xi, (slice(1, 2),), f32(1, 5, 6) * 50)
+
+
+def do_scatter(name, x, dim, index, src, reduce="void"):
+    y = to_jt(x).scatter(dim, to_jt(index), to_jt(src), reduce)
+    case(name, "scatter", {"dim": dim, "reduce": reduce}, [x, src], to_np(y), [index])
+
+
+def do_gather(name, x, dim, index):
+    y = to_jt(x).gather(dim, to_jt(index))
+    case(name, "gather", {"dim": dim}, [x], to_np(y), [index])
+
+
+srcs = np.arange(1, 11, dtype=np.int32).reshape(2, 5)
+do_scatter("scatter_dim0", np.zeros((3, 5), np.int32), 0, np.array([[0, 1, 2, 0]], np.int32), srcs)
+do_scatter("scatter_dim1", np.zeros((3, 5), np.int32), 1, np.array([[0, 1, 2], [0, 1, 4]], np.int32), srcs)
+do_scatter("scatter_scalar_mul", np.full((2, 4), 2.0, np.float32), 1, np.array([[2], [3]], np.int32),
+           np.array([1.23], np.float32), "multiply")
+do_scatter("scatter_scalar_add", np.full((2, 4), 2.0, np.float32), 1, np.array([[2], [3]], np.int32),
+           np.array([1.23], np.float32), "add")
+perm = np.stack([rng.permutation(50) for _ in range(8)]).astype(np.int32)
+do_scatter("scatter_perm_dim1", f32(8, 64), 1, perm, f32(8, 50))
+do_scatter("scatter_add_dup_3d", f32(5, 6, 7), 2, i32(5, 6, 20, hi=7), f32(5, 6, 20), "add")
+do_scatter("scatter_add_dup_dim0_int", i32(9, 4), 0, i32(30, 4, hi=9), i32(30, 4), "add")
+do_gather("gather_dim1", np.array([[1, 2], [3, 4]], np.int32), 1, np.array([[0, 0], [1, 0]], np.int32))
+do_gather("gather_dim0", np.array([[1, 2], [3, 4]], np.int32), 0, np.array([[0, 0], [1, 0]], np.int32))
+do_gather("gather_3d_dim2", f32(5, 6, 7), 2, i32(5, 6, 11, hi=7))
+do_gather("gather_3d_dim0_smaller", f32(5, 6, 7), 0, i32(3, 4, 7, hi=5))
+do_gather("gather_int64_index", f32(10, 3), 0, rng.integers(0, 10, size=(4, 3)).astype(np.int64))
+
+np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
+with open(os.path.join(HERE, "next_ops.json"), "w") as f:
+    json.dump({"generator": "tests/golden/make_golden_next.py", "reference_version": jt.__version__, "cases": CASES},
+              f, indent=1)
+print("cases:", len(CASES), "arrays:", len(ARRAYS), "npz bytes:", os.path.getsize(os.path.join(HERE, "next_ops.npz")))

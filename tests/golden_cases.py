@@ -6,28 +6,51 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-_manifest = json.load(open(os.path.join(HERE, "golden", "meta_ops.json")))
-CASES = _manifest["cases"]
-_npz = None
+# meta_ops: the path itself; next_ops: its callers (slicing, scatter/gather, pooling, conv variants, optimiser step)
+_FILES = ("meta_ops", "next_ops")
+CASES = []
+for _f in _FILES:
+    for _c in json.load(open(os.path.join(HERE, "golden", _f + ".json")))["cases"]:
+        _c["file"] = _f
+        CASES.append(_c)
+_npz = {}
 
 
-def arrays():
-    global _npz
-    if _npz is None:
-        _npz = np.load(os.path.join(HERE, "golden", "meta_ops.npz"))
-    return _npz
+def arrays(which="meta_ops"):
+    if which not in _npz:
+        _npz[which] = np.load(os.path.join(HERE, "golden", which + ".npz"))
+    return _npz[which]
+
+
+def decode_slices(enc, extras):
+    """Inverse of the encoding of tests/golden/make_golden_next.py: index arrays come back as numpy arrays."""
+    out = []
+    for e in enc:
+        if e is None:
+            out.append(None)
+        elif e == "...":
+            out.append(Ellipsis)
+        elif "i" in e:
+            out.append(int(e["i"]))
+        elif "s" in e:
+            out.append(slice(*e["s"]))
+        elif "f" in e:
+            out.append(e["f"])
+        else:
+            out.append(extras[e["v"]])
+    return tuple(out)
 
 
 def case_ids():
     return [c["name"] for c in CASES]
 
 
-EXACT_OPS = {"reindex", "reindex_var", "broadcast", "broadcast_var", "ternary"}
+EXACT_OPS = {"reindex", "reindex_var", "broadcast", "broadcast_var", "ternary", "getitem", "gather"}
 
 
 def run_case(c, be):
     """Returns (got, want, exact) for case `c` on backend `be`."""
-    A = arrays()
+    A = arrays(c.get("file", "meta_ops"))
     ins = [A[k] for k in c["inputs"]]
     ex = [A[k] for k in c["extras"]]
     want = A[c["out"]]
@@ -83,6 +106,14 @@ def run_case(c, be):
     elif op == "grad_reindex_reduce_add":
         # reindex_reduce(add) grad = reindex of the upstream gradient (reindex_reduce_op.cc:48-49)
         got = be.reindex(ins[1], list(ins[0].shape), a["indexes"], 0, [], [])
+    elif op == "getitem":
+        got = be.getitem(ins[0], decode_slices(a["slices"], ex))
+    elif op == "setitem":
+        got = be.setitem(ins[0], decode_slices(a["slices"], ex), ins[1], a["op"])
+    elif op == "scatter":
+        got = be.scatter(ins[0], a["dim"], ex[0], ins[1], a["reduce"])
+    elif op == "gather":
+        got = be.gather(ins[0], a["dim"], ex[0])
     else:
         raise KeyError(op)
     exact = op in EXACT_OPS or (want.dtype.kind in "iub" and op != "unary")

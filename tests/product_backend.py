@@ -10,7 +10,27 @@ def _np(v):
     return v.numpy()
 
 
+def _jt_slices(slices):
+    return tuple(jt.array(s) if isinstance(s, np.ndarray) else s for s in slices)
+
+
 class ProductBackend:
+    @staticmethod
+    def getitem(x, slices):
+        return _np(jt.array(x)[_jt_slices(slices)])
+
+    @staticmethod
+    def setitem(x, slices, data, op="void"):
+        return _np(jt.array(x).setitem(_jt_slices(slices), jt.array(data), op))
+
+    @staticmethod
+    def scatter(x, dim, index, src, reduce="void"):
+        return _np(jt.array(x).scatter(dim, jt.array(index), jt.array(src), reduce))
+
+    @staticmethod
+    def gather(x, dim, index):
+        return _np(jt.array(x).gather(dim, jt.array(index)))
+
     @staticmethod
     def reindex(x, shape, indexes, overflow_value=0, overflow_conditions=(), extras=()):
         return _np(jt.array(x).reindex(shape, indexes, overflow_value, list(overflow_conditions),
