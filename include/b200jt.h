@@ -181,6 +181,19 @@ int b200jt_bn_stats(const b200jt_tensor* x, float* stats, void* stream);
 int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, double count, const float* gamma, const float* beta,
                     double eps, int relu, const b200jt_tensor* y, void* stream);
 
+/* ---- pooling ----------------------------------------------------------------------------------------
+ * y[n,c,oh,ow] = op over the window rows [oh*sh-ph, +kh) x columns [ow*sw-pw, +kw) of x[n,c], clipped to x. Replaces the
+ * jt.code kernels of Pool.execute, python/jittor/pool.py:42-197 (forward body :54-81, backward body :82-95):
+ * op "maximum" / "minimum" start from the op's init value; "mean" divides by kh*kw when count_include_pad, else by the
+ * clipped window area. y's spatial shape selects floor or ceil mode (python/jittor/pool.py:46-53). indices (maximum
+ * only, may be NULL) receives p*W+q of the first largest element, -1 for an empty window (:70-81).
+ * Backward: dx[n,c,p,q] = sum of dy over the windows in which x[n,c,p,q] is the FIRST element (row-major) equal to
+ * y (maximum / minimum), or sum of dy/count over the windows containing it (mean). dtypes: float32/64, float16, bfloat16. */
+int b200jt_pool2d(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indices, const char* op,
+                  int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream);
+int b200jt_pool2d_backward(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* dy, const b200jt_tensor* dx,
+                           const char* op, int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream);
+
 /* ---- all-reduce over NVLink peer mappings --------------------------------------------------------
  * y = op over the ranks of x, one kernel per rank that reads and writes the other ranks' memory directly: replaces
  * the relay NcclAllReduceOp(Var* x), python/jittor/extern/cuda/nccl/ops/nccl_all_reduce_op.h:14, jit_run

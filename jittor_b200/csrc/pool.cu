@@ -1,0 +1,195 @@
+// 2-D pooling, forward and backward: the kernels `Pool.execute` builds with jt.code in the reference
+// (python/jittor/pool.py:54-95 forward body, :96-118 backward body) as fixed sm_100a kernels.
+//
+// Window of output (oh, ow): rows [oh*sh - ph, oh*sh - ph + kh) x columns [ow*sw - pw, ow*sw - pw + kw), clipped to the
+// input (padding is never read). maximum / minimum fold the clipped window starting from the op's init value; mean
+// divides the clipped sum by kh*kw (count_include_pad) or by the clipped area.
+// Backward: the reference scatters with atomicAdd, one thread per window; for maximum / minimum only the FIRST element
+// of the window (row-major scan) that equals the pooled value receives the gradient. Here every INPUT element gathers
+// from the windows that contain it instead (at most ceil(kh/sh) * ceil(kw/sw) of them), re-deriving "am I the first
+// match" by scanning the part of the window that precedes it: no atomics, no zero fill, deterministic.
+#include "atomic_ops.cuh"
+
+namespace b200jt {
+namespace pool {
+
+struct Geo {
+    int N, C, H, W, OH, OW, kh, kw, sh, sw, ph, pw;
+    int count_include_pad;
+};
+
+template <typename T> struct AccOf { using type = float; };
+template <> struct AccOf<double> { using type = double; };
+
+template <typename T> __device__ __forceinline__ typename AccOf<T>::type ld(const T* p) { return (typename AccOf<T>::type)(*p); }
+template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <> __device__ __forceinline__ float ld<__half>(const __half* p) { return __half2float(*p); }
+template <typename T, typename A> __device__ __forceinline__ T cvt(A v) { return (T)v; }
+template <> __device__ __forceinline__ __nv_bfloat16 cvt<__nv_bfloat16, float>(float v) { return __float2bfloat16(v); }
+template <> __device__ __forceinline__ __half cvt<__half, float>(float v) { return __float2half(v); }
+
+// OP: 0 maximum, 1 minimum, 2 mean
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int32_t* __restrict__ indices,
+                                                       Geo g, T init) {
+    using A = typename AccOf<T>::type;
+    const int64_t total = (int64_t)g.N * g.C * g.OH * g.OW;
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+        const int ow = (int)(o % g.OW); const int64_t t = o / g.OW;
+        const int oh = (int)(t % g.OH); const int64_t nc = t / g.OH;
+        int p0 = oh * g.sh - g.ph, q0 = ow * g.sw - g.pw;
+        const int p1 = min(p0 + g.kh, g.H), q1 = min(q0 + g.kw, g.W);
+        p0 = max(p0, 0); q0 = max(q0, 0);
+        const T* xp = x + nc * (int64_t)g.H * g.W;
+        if (OP == 2) {
+            A acc = 0;
+            for (int p = p0; p < p1; p++)
+                for (int q = q0; q < q1; q++) acc += ld<T>(xp + (int64_t)p * g.W + q);
+            const int count = g.count_include_pad ? g.kh * g.kw : (p1 - p0) * (q1 - q0);
+            y[o] = cvt<T, A>(acc / (A)count);
+        } else {
+            A best = ld<T>(&init);
+            int where = -1;
+            for (int p = p0; p < p1; p++)
+                for (int q = q0; q < q1; q++) {
+                    const A v = ld<T>(xp + (int64_t)p * g.W + q);
+                    // a strict comparison keeps the first extreme element, as the reference's index variant does
+                    if (OP == 0 ? best < v : v < best) { best = v; where = p * g.W + q; }
+                }
+            y[o] = cvt<T, A>(best);
+            if (indices) indices[o] = where;
+        }
+    }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
+                                                       T* __restrict__ dx, Geo g) {
+    using A = typename AccOf<T>::type;
+    const int64_t total = (int64_t)g.N * g.C * g.H * g.W;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int q = (int)(e % g.W); const int64_t t = e / g.W;
+        const int p = (int)(t % g.H); const int64_t nc = t / g.H;
+        const T* xp = x + nc * (int64_t)g.H * g.W;
+        const T* yp = y + nc * (int64_t)g.OH * g.OW;
+        const T* dp = dy + nc * (int64_t)g.OH * g.OW;
+        // windows containing row p: oh*sh - ph <= p < oh*sh - ph + kh
+        const int oh_lo = max(0, (p + g.ph - g.kh + g.sh) / g.sh), oh_hi = min(g.OH - 1, (p + g.ph) / g.sh);
+        const int ow_lo = max(0, (q + g.pw - g.kw + g.sw) / g.sw), ow_hi = min(g.OW - 1, (q + g.pw) / g.sw);
+        const A mine = ld<T>(xp + (int64_t)p * g.W + q);
+        A acc = 0;
+        for (int oh = oh_lo; oh <= oh_hi; oh++) {
+            int p0 = oh * g.sh - g.ph;
+            const int p1 = min(p0 + g.kh, g.H);
+            p0 = max(p0, 0);
+            if (p < p0 || p >= p1) continue;
+            for (int ow = ow_lo; ow <= ow_hi; ow++) {
+                int q0 = ow * g.sw - g.pw;
+                const int q1 = min(q0 + g.kw, g.W);
+                q0 = max(q0, 0);
+                if (q < q0 || q >= q1) continue;
+                const A d = ld<T>(dp + (int64_t)oh * g.OW + ow);
+                if (OP == 2) {
+                    const int count = g.count_include_pad ? g.kh * g.kw : (p1 - p0) * (q1 - q0);
+                    acc += d / (A)count;
+                } else {
+                    const A v = ld<T>(yp + (int64_t)oh * g.OW + ow);
+                    if (!(mine == v)) continue;
+                    bool first = true;
+                    for (int pp = p0; pp <= p && first; pp++) {
+                        const int qe = pp == p ? q : q1;
+                        for (int qq = q0; qq < qe; qq++)
+                            if (ld<T>(xp + (int64_t)pp * g.W + qq) == v) { first = false; break; }
+                    }
+                    if (first) acc += d;
+                }
+            }
+        }
+        dx[e] = cvt<T, A>(acc);
+    }
+}
+
+static int parse(const b200jt_tensor* x, const b200jt_tensor* y, const char* op, int kh, int kw, int sh, int sw, int ph, int pw,
+                 int count_include_pad, Geo* g, int* opc) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(y) && x->ndim == 4 && y->ndim == 4, "pool2d takes NCHW tensors");
+    B200JT_CHECK_ARG(x->dtype == y->dtype, "x and y must have the same dtype");
+    B200JT_CHECK_ARG(kh > 0 && kw > 0, "kernel_size must be greater than zero");
+    B200JT_CHECK_ARG(sh > 0 && sw > 0, "stride must be greater than zero");
+    B200JT_CHECK_ARG(ph >= 0 && pw >= 0, "padding must be non-negative");
+    B200JT_CHECK_ARG(x->shape[0] == y->shape[0] && x->shape[1] == y->shape[1], "batch / channel mismatch between x and y");
+    B200JT_CHECK_ARG(op != nullptr, "op is null");
+    *opc = !strcmp(op, "maximum") ? 0 : !strcmp(op, "minimum") ? 1 : !strcmp(op, "mean") ? 2 : -1;
+    B200JT_CHECK_ARG(*opc >= 0, std::string("pool2d op must be maximum, minimum or mean, got '") + op + "'");
+    for (int d = 0; d < 4; d++)
+        B200JT_CHECK_ARG(x->shape[d] < (1LL << 31) && y->shape[d] < (1LL << 31), "dimension too large");
+    g->N = (int)x->shape[0]; g->C = (int)x->shape[1]; g->H = (int)x->shape[2]; g->W = (int)x->shape[3];
+    g->OH = (int)y->shape[2]; g->OW = (int)y->shape[3];
+    g->kh = kh; g->kw = kw; g->sh = sh; g->sw = sw; g->ph = ph; g->pw = pw; g->count_include_pad = count_include_pad;
+    return 0;
+}
+
+template <typename T>
+static int run_fwd(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indices, const Geo& g, int opc, cudaStream_t st) {
+    const int64_t total = numel(y);
+    if (total == 0) return 0;
+    const unsigned grid = grid_for(total, 256);
+    const T* xp = (const T*)x->ptr; T* yp = (T*)y->ptr;
+    if (opc == 0) pool_fwd_kernel<T, 0><<<grid, 256, 0, st>>>(xp, yp, indices, g, init_value<T>(OP_MAX));
+    else if (opc == 1) pool_fwd_kernel<T, 1><<<grid, 256, 0, st>>>(xp, yp, indices, g, init_value<T>(OP_MIN));
+    else pool_fwd_kernel<T, 2><<<grid, 256, 0, st>>>(xp, yp, indices, g, init_value<T>(OP_ADD));
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int run_bwd(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* dy, const b200jt_tensor* dx,
+                   const Geo& g, int opc, cudaStream_t st) {
+    const int64_t total = numel(x);
+    if (total == 0) return 0;
+    const unsigned grid = grid_for(total, 256);
+    const T *xp = (const T*)x->ptr, *yp = (const T*)y->ptr, *dp = (const T*)dy->ptr; T* op = (T*)dx->ptr;
+    if (opc == 0) pool_bwd_kernel<T, 0><<<grid, 256, 0, st>>>(xp, yp, dp, op, g);
+    else if (opc == 1) pool_bwd_kernel<T, 1><<<grid, 256, 0, st>>>(xp, yp, dp, op, g);
+    else pool_bwd_kernel<T, 2><<<grid, 256, 0, st>>>(xp, yp, dp, op, g);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace pool
+}  // namespace b200jt
+
+using namespace b200jt;
+
+extern "C" int b200jt_pool2d(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indices, const char* op,
+                             int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream) {
+    pool::Geo g; int opc;
+    if (int rc = pool::parse(x, y, op, kh, kw, sh, sw, ph, pw, count_include_pad, &g, &opc)) return rc;
+    B200JT_CHECK_ARG(!indices || opc == 0, "indices are only produced for maximum");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x->dtype) {
+        case B200JT_FLOAT32: return pool::run_fwd<float>(x, y, indices, g, opc, st);
+        case B200JT_FLOAT64: return pool::run_fwd<double>(x, y, indices, g, opc, st);
+        case B200JT_BFLOAT16: return pool::run_fwd<__nv_bfloat16>(x, y, indices, g, opc, st);
+        case B200JT_FLOAT16: return pool::run_fwd<__half>(x, y, indices, g, opc, st);
+    }
+    return fail(-1, "b200jt_pool2d: dtype must be float32, float64, float16 or bfloat16");
+}
+
+extern "C" int b200jt_pool2d_backward(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* dy,
+                                      const b200jt_tensor* dx, const char* op,
+                                      int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream) {
+    pool::Geo g; int opc;
+    if (int rc = pool::parse(x, y, op, kh, kw, sh, sw, ph, pw, count_include_pad, &g, &opc)) return rc;
+    B200JT_CHECK_ARG(valid_tensor(dy) && valid_tensor(dx) && dy->ndim == 4 && dx->ndim == 4 &&
+                     dy->dtype == x->dtype && dx->dtype == x->dtype, "dy, dx must be NCHW tensors of x's dtype");
+    for (int d = 0; d < 4; d++)
+        B200JT_CHECK_ARG(dy->shape[d] == y->shape[d] && dx->shape[d] == x->shape[d], "dy must have y's shape and dx x's shape");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x->dtype) {
+        case B200JT_FLOAT32: return pool::run_bwd<float>(x, y, dy, dx, g, opc, st);
+        case B200JT_FLOAT64: return pool::run_bwd<double>(x, y, dy, dx, g, opc, st);
+        case B200JT_BFLOAT16: return pool::run_bwd<__nv_bfloat16>(x, y, dy, dx, g, opc, st);
+        case B200JT_FLOAT16: return pool::run_bwd<__half>(x, y, dy, dx, g, opc, st);
+    }
+    return fail(-1, "b200jt_pool2d_backward: dtype must be float32, float64, float16 or bfloat16");
+}

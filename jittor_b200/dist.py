@@ -75,3 +75,64 @@ def mpi_all_reduce(x, op="add"):
     if op != "add":
         raise ValueError(f"Not supported MPI op {op}")
     return V.Var(x.shape, x.dtype, V.Op("mpi_all_reduce", [x], op="add"))
+
+
+def mpi_broadcast(x, root=0):
+    """Every rank receives root's value (python/jittor/extern/mpi/ops/mpi_broadcast_op.cc; the CUDA relay is
+    ncclBroadcast, python/jittor/extern/cuda/nccl/ops/nccl_broadcast_op.cc). Eager: the value is needed now."""
+    x = V.to_var(x)
+    if not in_mpi():
+        return x
+    x.sync()
+    out = x._data.clone()
+    tdist.broadcast(out, src=root)
+    return V.Var(x.shape, x.dtype, data=out)
+
+
+def all_reduce_buckets(tensors, bucket_bytes=None):
+    """Sums a list of tensors over the ranks in as few collectives as possible: tensors of one dtype are packed back
+    to back into flat buckets of at most `bucket_bytes` (default: what the peer kernel takes in one call, else 32 MiB),
+    each bucket is reduced once, and the results are returned as views into the buckets, in the input order. This
+    replaces the reference's one all-reduce per gradient (python/jittor/optim.py:196-198)."""
+    if not tensors:
+        return []
+    if bucket_bytes is None:
+        bucket_bytes = _PEER.max_bytes if _PEER is not None else 32 << 20
+    out = [None] * len(tensors)
+    by_dtype = {}
+    for i, t in enumerate(tensors):
+        by_dtype.setdefault(t.dtype, []).append(i)
+    for dtype, ids in by_dtype.items():
+        bucket, used = [], 0
+        esize = tensors[ids[0]].element_size()
+
+        def flush():
+            nonlocal bucket, used
+            if not bucket:
+                return
+            flat = torch.empty(used // esize, dtype=dtype, device=tensors[bucket[0]].device)
+            off = 0
+            for i in bucket:
+                n = tensors[i].numel()
+                flat[off:off + n].copy_(tensors[i].reshape(-1))
+                off += _round_up(n * esize, 16) // esize
+            flat = all_reduce_sum(flat, out=flat)
+            off = 0
+            for i in bucket:
+                n = tensors[i].numel()
+                out[i] = flat[off:off + n].view(tensors[i].shape)
+                off += _round_up(n * esize, 16) // esize
+            bucket, used = [], 0
+
+        for i in ids:
+            nbytes = _round_up(tensors[i].numel() * esize, 16)       # 16-byte slots keep every view vector-aligned
+            if bucket and used + nbytes > bucket_bytes:
+                flush()
+            bucket.append(i)
+            used += nbytes
+        flush()
+    return out
+
+
+def _round_up(n, m):
+    return (n + m - 1) // m * m

@@ -140,6 +140,9 @@ def _op_grad(out, dout, k):
         return _unbroadcast(g, x.shape)
     if kind == "reshape":
         return dout.reshape(list(x.shape))
+    if kind == "custom":
+        rule = a.get("grad")                      # relays bring their own backward (e.g. the pooling kernels)
+        return rule(out, dout, k) if rule is not None else None
     if kind == "mpi_all_reduce":
         from . import dist
         return dist.mpi_all_reduce(dout, "add")

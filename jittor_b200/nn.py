@@ -16,7 +16,34 @@ class Module:
         raise NotImplementedError
 
     def parameters(self):
-        return [v for v in self.__dict__.values() if isinstance(v, Var)]
+        """Vars held by this module and its sub-modules (also inside lists / tuples / dicts), in attribute order."""
+        out, seen = [], set()
+
+        def visit(obj):
+            if isinstance(obj, Var):
+                if id(obj) not in seen:
+                    seen.add(id(obj))
+                    out.append(obj)
+            elif isinstance(obj, Module):
+                for v in obj.__dict__.values():
+                    visit(v)
+            elif isinstance(obj, (list, tuple)):
+                for v in obj:
+                    visit(v)
+            elif isinstance(obj, dict):
+                for v in obj.values():
+                    visit(v)
+
+        visit(self)
+        return out
+
+    def mpi_param_broadcast(self, root=0):
+        """python/jittor/__init__.py:1761-1764."""
+        from . import dist
+        if not dist.in_mpi():
+            return
+        for p in self.parameters():
+            p.update(p.mpi_broadcast(root))
 
 
 def matmul_transpose(a, b):

@@ -89,7 +89,15 @@ class Var:
         return self
 
     def stop_grad(self):
+        self._stop_grad = True
         return self
+
+    def start_grad(self):
+        self._stop_grad = False
+        return self
+
+    def is_stop_grad(self):
+        return getattr(self, "_stop_grad", False)
 
     def stop_fuse(self):
         return self
@@ -257,6 +265,10 @@ class Var:
         return transpose(self, perm)
 
     permute = transpose
+
+    def mpi_broadcast(self, root=0):
+        from . import dist
+        return dist.mpi_broadcast(self, root)
 
     def mpi_all_reduce(self, op="add"):
         from . import dist

@@ -825,3 +825,108 @@ def gather(x, dim, index):
     idx = [f"i{i}" for i in range(index.ndim)]
     idx[dim] = index
     return getitem(x, tuple(idx))
+
+
+# --------------------------------------------------------------------------- optimiser steps
+def optim_steps(x, y, w, kind, steps, lr, momentum=0, weight_decay=0, dampening=0, nesterov=False,
+                eps=1e-8, betas=(0.9, 0.999)):
+    """`steps` updates of w on loss = sum((x @ w - y)^2) / N with the reference's SGD (python/jittor/optim.py:325-345)
+    or Adam (:420-437) formulas, in float32 like the reference's graph; the gradient is 2/N * x^T (x w - y)."""
+    f = np.float32
+    x, y, w = x.astype(f), y.astype(f), w.astype(f).copy()
+    v, m = np.zeros_like(w), np.zeros_like(w)
+    for n in range(1, steps + 1):
+        d = x @ w - y
+        g = (x.T @ (d * f(2.0))) * f(1.0 / x.shape[0])
+        if kind == "sgd":
+            dp = w * f(weight_decay) + g
+            v = f(momentum) * v + dp * f(1 - dampening)
+            w = w - (dp + f(momentum) * v) * f(lr) if nesterov else w - v * f(lr)
+        else:
+            b0, b1 = betas
+            g = w * f(weight_decay) + g
+            m = f(b0) * m + f(1 - b0) * g
+            v = f(b1) * v + f(1 - b1) * g * g
+            step = f(lr) * np.sqrt(f(1 - b1 ** n)) / f(1 - b0 ** n)
+            w = w - m * step / (np.sqrt(v) + f(eps))
+    return w.astype(f)
+
+
+# --------------------------------------------------------------------------- pooling
+def _pool_geometry(H, W, k, s, p, ceil_mode):
+    """Output size rules of Pool.execute, python/jittor/pool.py:46-53."""
+    if not ceil_mode:
+        return (H + p[0] * 2 - k[0]) // s[0] + 1, (W + p[1] * 2 - k[1]) // s[1] + 1
+    return (H + p[0] * 2 - k[0] + s[0] - 1) // s[0] + 1, (W + p[1] * 2 - k[1] + s[1] - 1) // s[1] + 1
+
+
+def _pair(v):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+
+
+def pool2d(x, kernel_size, op, stride=None, padding=0, ceil_mode=False, count_include_pad=True, return_indices=False):
+    """Forward of Pool.execute (python/jittor/pool.py:42-95,187-197): the jt.code loops over the clipped window for
+    maximum / minimum (always) and mean (ceil mode); mean in floor mode is reindex + reduce(mean), i.e. zero padding
+    and a division by kh*kw."""
+    x = np.asarray(x)
+    k, s, p = _pair(kernel_size), _pair(stride if stride else kernel_size), _pair(padding)
+    cip = bool(count_include_pad) and padding != 0
+    N, C, H, W = x.shape
+    h, w = _pool_geometry(H, W, k, s, p, ceil_mode)
+    code_op = op in ("maximum", "minimum") or (op == "mean" and ceil_mode)
+    y = np.empty((N, C, h, w), dtype=x.dtype)
+    idx = np.full((N, C, h, w), -1, dtype=np.int32)
+    acc_t = np.float64 if x.dtype == np.float64 else np.float32
+    for i2 in range(h):
+        for i3 in range(w):
+            k2, k3 = i2 * s[0] - p[0], i3 * s[1] - p[1]
+            k2_, k3_ = min(k2 + k[0], H), min(k3 + k[1], W)
+            k2, k3 = max(0, k2), max(0, k3)
+            win = x[:, :, k2:k2_, k3:k3_].reshape(N, C, -1)
+            if op == "mean":
+                count = k[0] * k[1] if (cip or not code_op) else (k2_ - k2) * (k3_ - k3)
+                with np.errstate(divide="ignore", invalid="ignore"):
+                    y[:, :, i2, i3] = (win.astype(acc_t).sum(-1) / acc_t(count)).astype(x.dtype)
+            elif win.shape[-1] == 0:
+                y[:, :, i2, i3] = _init_value(op, x.dtype)
+            else:
+                y[:, :, i2, i3] = win.max(-1) if op == "maximum" else win.min(-1)
+                if return_indices:
+                    a = win.argmax(-1)                       # first largest element (:70-79 uses a strict `<`)
+                    ww = k3_ - k3
+                    idx[:, :, i2, i3] = (k2 + a // ww) * W + (k3 + a % ww)
+    return (y, idx) if return_indices else y
+
+
+def pool2d_backward(x, dy, kernel_size, op, stride=None, padding=0, ceil_mode=False, count_include_pad=True):
+    """Gradient of pool2d w.r.t. x. Code-op route (python/jittor/pool.py:96-118): per window, the first element (row
+    major) equal to the pooled value receives dy (maximum / minimum), or every element receives dy/count (mean). The
+    floor-mode mean is the meta-op route, whose gradient is dy/(kh*kw) on every in-range window element."""
+    x, dy = np.asarray(x), np.asarray(dy)
+    k, s, p = _pair(kernel_size), _pair(stride if stride else kernel_size), _pair(padding)
+    cip = bool(count_include_pad) and padding != 0
+    N, C, H, W = x.shape
+    h, w = _pool_geometry(H, W, k, s, p, ceil_mode)
+    code_op = op in ("maximum", "minimum") or (op == "mean" and ceil_mode)
+    y = pool2d(x, kernel_size, op, stride, padding, ceil_mode, count_include_pad)
+    dx = np.zeros(x.shape, dtype=np.float64)
+    for i2 in range(h):
+        for i3 in range(w):
+            k2, k3 = i2 * s[0] - p[0], i3 * s[1] - p[1]
+            k2_, k3_ = min(k2 + k[0], H), min(k3 + k[1], W)
+            k2, k3 = max(0, k2), max(0, k3)
+            if k2_ <= k2 or k3_ <= k3:
+                continue
+            d = dy[:, :, i2, i3].astype(np.float64)
+            if op == "mean":
+                count = k[0] * k[1] if (cip or not code_op) else (k2_ - k2) * (k3_ - k3)
+                dx[:, :, k2:k2_, k3:k3_] += (d / count)[:, :, None, None]
+            else:
+                win = x[:, :, k2:k2_, k3:k3_].reshape(N, C, -1)
+                hit = win == y[:, :, i2, i3][:, :, None]
+                first = hit.argmax(-1)
+                has = hit.any(-1)
+                ww = k3_ - k3
+                n_i, c_i = np.nonzero(has)
+                np.add.at(dx, (n_i, c_i, k2 + first[n_i, c_i] // ww, k3 + first[n_i, c_i] % ww), d[n_i, c_i])
+    return dx.astype(x.dtype)

@@ -39,6 +39,24 @@ def main():
     stats = torch.tensor([float(rank), 10.0 * (rank + 1)])
     torch.distributed.all_reduce(stats)
     assert stats.tolist() == [1.0, 30.0]
+    # 5. bucketed gradient exchange: mixed dtypes and sizes, a bucket limit that forces several collectives
+    gen = torch.Generator().manual_seed(7 + rank)
+    shapes = [(3, 5), (1,), (17,), (4, 4, 4), (2, 9)]
+    ts = [torch.randn(s, generator=gen) for s in shapes] + [torch.randint(0, 9, (11,), generator=gen, dtype=torch.int32)]
+    want = []
+    for t in ts:
+        w = t.clone()
+        torch.distributed.all_reduce(w)
+        want.append(w)
+    for limit in (64, 1 << 20):
+        got = dist.all_reduce_buckets([t.clone() for t in ts], bucket_bytes=limit)
+        for g, w, t in zip(got, want, ts):
+            assert g.shape == t.shape and g.dtype == t.dtype and torch.equal(g, w), (limit, g, w)
+    # 6. parameter broadcast from rank 0
+    p = jt.Var([3], "float32")
+    p._data = torch.full((3,), float(10 + rank))
+    b = dist.mpi_broadcast(p, 0)
+    assert torch.equal(b._data, torch.full((3,), 10.0))
     print(f"rank {rank} ok")
 
 

@@ -169,6 +169,65 @@ do_gather("gather_3d_dim2", f32(5, 6, 7), 2, i32(5, 6, 11, hi=7))
 do_gather("gather_3d_dim0_smaller", f32(5, 6, 7), 0, i32(3, 4, 7, hi=5))
 do_gather("gather_int64_index", f32(10, 3), 0, rng.integers(0, 10, size=(4, 3)).astype(np.int64))
 
+
+
+# ---- optimiser steps on a small least-squares problem: loss = sum((x @ w - y)^2) / N ------------------------------
+def do_optim(name, kind, steps, **kw):
+    x, y, w0 = f32(32, 6), f32(32, 3), f32(6, 3)
+    w = to_jt(w0)
+    vx, vy = to_jt(x), to_jt(y)
+    opt = (jt.optim.SGD if kind == "sgd" else jt.optim.Adam)([w], **kw)
+    for _ in range(steps):
+        d = jt.matmul(vx, w) - vy
+        loss = (d * d).sum() * (1.0 / 32)
+        opt.step(loss)
+    case(name, "optim", dict(kind=kind, steps=steps, **{k: (list(v) if isinstance(v, tuple) else v) for k, v in kw.items()}),
+         [x, y, w0], to_np(w))
+
+
+do_optim("sgd_plain", "sgd", 3, lr=0.1)
+do_optim("sgd_momentum_wd", "sgd", 4, lr=0.05, momentum=0.9, weight_decay=0.01)
+do_optim("sgd_nesterov_dampening", "sgd", 4, lr=0.05, momentum=0.8, dampening=0.1, nesterov=True)
+do_optim("adam_default", "adam", 4, lr=0.01)
+do_optim("adam_wd_betas", "adam", 3, lr=0.02, eps=1e-6, betas=(0.8, 0.9), weight_decay=0.1)
+
+
+
+# ---- pooling: forward, and backward through jt.grad with a random upstream gradient -------------------------------
+from jittor import pool as jpool
+
+
+def do_pool(name, x, kernel_size, op, stride=None, padding=0, ceil_mode=False, count_include_pad=True, backward=True):
+    args = dict(kernel_size=kernel_size, op=op, stride=stride, padding=padding, ceil_mode=ceil_mode,
+                count_include_pad=count_include_pad)
+    vx = to_jt(x)
+    layer = jpool.Pool(kernel_size, stride, padding, ceil_mode=ceil_mode, count_include_pad=count_include_pad, op=op)
+    y = layer(vx)
+    ynp = to_np(y)
+    case(name, "pool2d", args, [x], ynp)
+    if backward:
+        dy = f32(*ynp.shape)
+        dx = jt.grad((y * to_jt(dy)).sum(), vx)
+        case(name + "_bwd", "pool2d_bwd", args, [x, dy], to_np(dx))
+
+
+ties = rng.integers(0, 3, size=(2, 3, 9, 11)).astype(np.float32)        # many equal values: the first-match rule decides
+do_pool("pool_max_2x2", f32(2, 3, 8, 10), 2, "maximum")
+do_pool("pool_max_3x3_s2_p1", f32(2, 3, 9, 11), 3, "maximum", 2, 1)
+do_pool("pool_max_ties", ties, 3, "maximum", 2, 1)
+do_pool("pool_max_ties_overlap_s1", ties, 2, "maximum", 1, 0)
+do_pool("pool_max_ceil", f32(1, 2, 10, 10), 3, "maximum", 2, 0, True)
+do_pool("pool_max_rect", f32(2, 2, 12, 9), (3, 2), "maximum", (2, 1), (1, 0))
+do_pool("pool_min_3x3_s2_p1", f32(2, 3, 9, 11), 3, "minimum", 2, 1)
+do_pool("pool_min_ties", ties, 2, "minimum", 2, 0)
+do_pool("pool_mean_2x2", f32(2, 3, 8, 10), 2, "mean")
+do_pool("pool_mean_3x3_s2_p1", f32(2, 3, 9, 11), 3, "mean", 2, 1)
+do_pool("pool_mean_p1_no_count_pad", f32(2, 3, 9, 11), 3, "mean", 2, 1, False, False)
+do_pool("pool_mean_ceil", f32(1, 2, 10, 10), 3, "mean", 2, 0, True)
+do_pool("pool_mean_ceil_p1_count_pad", f32(1, 2, 10, 10), 3, "mean", 2, 1, True, True)
+do_pool("pool_mean_ceil_p1_no_count_pad", f32(1, 2, 10, 10), 3, "mean", 2, 1, True, False)
+do_pool("pool_max_64ch", f32(2, 64, 28, 28), 3, "maximum", 2, 1)
+
 np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
 with open(os.path.join(HERE, "next_ops.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_golden_next.py", "reference_version": jt.__version__, "cases": CASES},

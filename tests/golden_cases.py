@@ -48,6 +48,10 @@ def case_ids():
 EXACT_OPS = {"reindex", "reindex_var", "broadcast", "broadcast_var", "ternary", "getitem", "gather"}
 
 
+def _kw(v):
+    return tuple(v) if isinstance(v, list) else v
+
+
 def run_case(c, be):
     """Returns (got, want, exact) for case `c` on backend `be`."""
     A = arrays(c.get("file", "meta_ops"))
@@ -114,6 +118,15 @@ def run_case(c, be):
         got = be.scatter(ins[0], a["dim"], ex[0], ins[1], a["reduce"])
     elif op == "gather":
         got = be.gather(ins[0], a["dim"], ex[0])
+    elif op == "pool2d":
+        got = be.pool2d(ins[0], _kw(a["kernel_size"]), a["op"], _kw(a["stride"]), _kw(a["padding"]), a["ceil_mode"],
+                        a["count_include_pad"])
+    elif op == "pool2d_bwd":
+        got = be.pool2d_backward(ins[0], ins[1], _kw(a["kernel_size"]), a["op"], _kw(a["stride"]), _kw(a["padding"]),
+                                 a["ceil_mode"], a["count_include_pad"])
+    elif op == "optim":
+        kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in a.items() if k not in ("kind", "steps")}
+        got = be.optim_steps(ins[0], ins[1], ins[2], a["kind"], a["steps"], **kw)
     else:
         raise KeyError(op)
     exact = op in EXACT_OPS or (want.dtype.kind in "iub" and op != "unary")

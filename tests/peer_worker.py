@@ -54,6 +54,32 @@ def main():
     var = full.var((0, 2, 3), unbiased=False, keepdim=True)
     want = torch.relu((x - mean) / torch.sqrt(var + 1e-5))
     assert torch.allclose(y, want, rtol=1e-4, atol=1e-4), (y - want).abs().max()
+    # data-parallel SGD: each rank holds a slice of the batch; the bucketed, averaged gradients must give every rank
+    # the parameters of a single-process run over the whole batch
+    from jittor_b200 import optim
+    gw = torch.Generator(device="cuda").manual_seed(5)
+    w0 = torch.randn(16, 4, generator=gw, device="cuda")
+    b0 = torch.randn(4, generator=gw, device="cuda")
+    xs = torch.randn(8, 16, generator=g, device="cuda")
+    ys = torch.randn(8, 4, generator=g, device="cuda")
+    w, b = jt.array(w0.clone()), jt.array(b0.clone())
+    opt = optim.SGD([w, b], lr=0.1, momentum=0.9)
+    for _ in range(3):
+        d = nn.matmul(jt.array(xs), w) + b - jt.array(ys)
+        opt.step((d * d).sum() * (1.0 / 8))
+    ax = [torch.empty_like(xs) for _ in range(world)]
+    ay = [torch.empty_like(ys) for _ in range(world)]
+    tdist.all_gather(ax, xs)
+    tdist.all_gather(ay, ys)
+    fx, fy = torch.cat(ax), torch.cat(ay)
+    tw, tb = w0.clone().requires_grad_(), b0.clone().requires_grad_()
+    topt = torch.optim.SGD([tw, tb], lr=0.1, momentum=0.9)
+    for _ in range(3):
+        topt.zero_grad()
+        (((fx @ tw + tb - fy) ** 2).sum() / fx.shape[0]).backward()
+        topt.step()
+    assert torch.allclose(w.torch(), tw.detach(), rtol=1e-4, atol=1e-5), (w.torch() - tw).abs().max()
+    assert torch.allclose(b.torch(), tb.detach(), rtol=1e-4, atol=1e-5)
     assert C.lib.b200jt_device_status() == 0
     tdist.barrier()
     print(f"rank {rank} ok", flush=True)

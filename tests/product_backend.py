@@ -16,6 +16,31 @@ def _jt_slices(slices):
 
 class ProductBackend:
     @staticmethod
+    def pool2d(x, kernel_size, op, stride=None, padding=0, ceil_mode=False, count_include_pad=True):
+        from jittor_b200 import pool
+        layer = pool.Pool(kernel_size, stride, padding, ceil_mode=ceil_mode, count_include_pad=count_include_pad, op=op)
+        return _np(layer(jt.array(x)))
+
+    @staticmethod
+    def pool2d_backward(x, dy, kernel_size, op, stride=None, padding=0, ceil_mode=False, count_include_pad=True):
+        from jittor_b200 import pool
+        layer = pool.Pool(kernel_size, stride, padding, ceil_mode=ceil_mode, count_include_pad=count_include_pad, op=op)
+        vx = jt.array(x)
+        return _np(jt.grad((layer(vx) * jt.array(dy)).sum(), vx))
+
+    @staticmethod
+    def optim_steps(x, y, w, kind, steps, **kw):
+        from jittor_b200 import optim
+        w = jt.array(w)
+        vx, vy = jt.array(x), jt.array(y)
+        opt = (optim.SGD if kind == "sgd" else optim.Adam)([w], **kw)
+        for _ in range(steps):
+            d = nn.matmul(vx, w) - vy
+            loss = (d * d).sum() * (1.0 / x.shape[0])
+            opt.step(loss)
+        return _np(w)
+
+    @staticmethod
     def getitem(x, slices):
         return _np(jt.array(x)[_jt_slices(slices)])
 
