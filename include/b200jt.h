@@ -163,6 +163,7 @@ int b200jt_device_status(void);
  *             int groups, string xformat, string wformat, string yformat),
  * python/jittor/extern/cuda/cudnn/ops/cudnn_conv_op.h:17, chosen by ConvTuner for
  * reduce.add(multiply(reindex(x), broadcast_to(w))), python/jittor/src/opt/tuner/conv_tuner.cc:218-411.
+ * groups > 1: w is [Cout, Cin/groups, KH, KW] (python/jittor/nn.py:1022-1056); grouped shapes run on the CUDA-core kernel.
  * If stats != NULL (float32 [2*Cout], zeroed by the callee) it also receives per-channel sum(y) and sum(y*y):
  * the reduce of python/jittor/nn.py:674-675 fused into the conv epilogue. */
 size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
@@ -170,6 +171,15 @@ size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, c
 int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                   int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
                   float* stats, void* workspace, size_t workspace_bytes, void* stream);
+
+/* y = conv_transpose2d(x, w): y[n,o,ho,wo] = sum x[n,i,hi,wi] * w[i,o,kh,kw] over ho = hi*stride - pad + kh*dil (same for w),
+ * x NCHW, w [Cin, Cout/groups, KH, KW], fp32 accumulation. y's spatial shape carries the output_padding. Replaces the
+ * relay CudnnConvBackwardXOp(Var* w, Var* y, int height, int width, int strideh, ..., int groups, ...),
+ * python/jittor/extern/cuda/cudnn/ops/cudnn_conv_backward_x_op.h:20, which ConvTuner selects for
+ * reindex_reduce.add(multiply(broadcast(x), broadcast(w))), python/jittor/src/opt/tuner/conv_tuner.cc:375-397 -- the graph
+ * ConvTranspose.execute builds (python/jittor/nn.py:1429-1491). */
+int b200jt_conv2d_transpose(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                            int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups, void* stream);
 
 /* Per-channel sum(x) and sum(x*x) of x[N,C,H,W] into stats[2*C] (float32): the two reduce.mean of
  * BatchNorm.execute, python/jittor/nn.py:674-675, in one pass, unnormalised so that ranks can be

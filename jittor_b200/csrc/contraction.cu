@@ -52,13 +52,15 @@ static int conv_shape(const b200jt_tensor* x, const b200jt_tensor* w, const b200
                       int sh, int sw, int ph, int pw, int dh, int dw, int groups, ConvShape* s) {
     B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(w) && valid_tensor(y), "invalid tensor descriptor");
     B200JT_CHECK_ARG(x->ndim == 4 && w->ndim == 4 && y->ndim == 4, "conv2d takes NCHW x, OIHW w, NCHW y");
-    B200JT_CHECK_ARG(groups == 1, "only groups == 1 is supported");
+    B200JT_CHECK_ARG(groups >= 1, "groups must be positive");
     B200JT_CHECK_ARG(x->dtype == w->dtype && x->dtype == y->dtype &&
                      (x->dtype == B200JT_FLOAT32 || x->dtype == B200JT_BFLOAT16), "x, w, y must all be float32 or bfloat16");
     B200JT_CHECK_ARG(sh > 0 && sw > 0 && dh > 0 && dw > 0 && ph >= 0 && pw >= 0, "bad stride/padding/dilation");
     s->N = (int)x->shape[0]; s->C = (int)x->shape[1]; s->H = (int)x->shape[2]; s->W = (int)x->shape[3];
     s->Co = (int)w->shape[0]; s->KH = (int)w->shape[2]; s->KW = (int)w->shape[3];
-    B200JT_CHECK_ARG(w->shape[1] == s->C, "weight in-channels do not match x");
+    B200JT_CHECK_ARG(s->C % groups == 0 && s->Co % groups == 0, "in_channels and out_channels must be divisible by groups");
+    B200JT_CHECK_ARG(w->shape[1] == s->C / groups, "weight in-channels do not match x");
+    s->groups = groups;
     // output extent, python/jittor/nn.py:1006-1007
     s->OH = (s->H + ph * 2 - s->KH * dh + dh - 1) / sh + 1;
     s->OW = (s->W + pw * 2 - s->KW * dw + dw - 1) / sw + 1;
@@ -73,7 +75,7 @@ extern "C" size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_t
                                           int sh, int sw, int ph, int pw, int dh, int dw, int groups) {
     ConvShape s;
     if (conv_shape(x, w, y, sh, sw, ph, pw, dh, dw, groups, &s)) return 0;
-    if (x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) return conv2d_tc_workspace(s);
+    if (groups == 1 && x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) return conv2d_tc_workspace(s);
     return 0;
 }
 
@@ -85,7 +87,7 @@ extern "C" int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, con
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if (numel(y) != 0) {
-        if (x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) {
+        if (groups == 1 && x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) {
             const size_t need = conv2d_tc_workspace(s);
             B200JT_CHECK_ARG(workspace_bytes >= need && workspace, "workspace too small: need " + std::to_string(need) + " bytes");
             rc = conv2d_tc(x->ptr, w->ptr, y->ptr, stats, s, workspace, st);
@@ -98,4 +100,27 @@ extern "C" int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, con
     }
     if (stats) return b200jt_bn_stats(y, stats, stream);
     return 0;
+}
+
+extern "C" int b200jt_conv2d_transpose(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                                       int sh, int sw, int ph, int pw, int dh, int dw, int groups, void* stream) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(w) && valid_tensor(y), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(x->ndim == 4 && w->ndim == 4 && y->ndim == 4, "conv2d_transpose takes NCHW x, IOHW w, NCHW y");
+    B200JT_CHECK_ARG(x->dtype == w->dtype && x->dtype == y->dtype &&
+                     (x->dtype == B200JT_FLOAT32 || x->dtype == B200JT_BFLOAT16), "x, w, y must all be float32 or bfloat16");
+    B200JT_CHECK_ARG(sh > 0 && sw > 0 && dh > 0 && dw > 0 && ph >= 0 && pw >= 0 && groups >= 1, "bad stride/padding/dilation/groups");
+    ConvShape s;
+    s.N = (int)x->shape[0]; s.C = (int)x->shape[1]; s.H = (int)x->shape[2]; s.W = (int)x->shape[3];
+    s.KH = (int)w->shape[2]; s.KW = (int)w->shape[3];
+    s.Co = (int)w->shape[1] * groups;
+    B200JT_CHECK_ARG(w->shape[0] == s.C && s.C % groups == 0, "weight in-channels do not match x");
+    s.OH = (int)y->shape[2]; s.OW = (int)y->shape[3];
+    // the output extent is (H-1)*stride - 2*padding + dilation*(K-1) + 1 + output_padding with output_padding < max(stride, dilation)
+    const int64_t oh0 = (int64_t)(s.H - 1) * sh - 2 * ph + (int64_t)(s.KH - 1) * dh + 1;
+    const int64_t ow0 = (int64_t)(s.W - 1) * sw - 2 * pw + (int64_t)(s.KW - 1) * dw + 1;
+    B200JT_CHECK_ARG(y->shape[0] == s.N && y->shape[1] == s.Co && s.OH >= oh0 && s.OH < oh0 + std::max(sh, dh) &&
+                     s.OW >= ow0 && s.OW < ow0 + std::max(sw, dw), "y has the wrong shape " + shape_str(y));
+    s.sh = sh; s.sw = sw; s.ph = ph; s.pw = pw; s.dh = dh; s.dw = dw; s.groups = groups;
+    if (numel(y) == 0) return 0;
+    return conv2d_transpose_simt(x->ptr, w->ptr, y->ptr, x->dtype, s, (cudaStream_t)stream);
 }

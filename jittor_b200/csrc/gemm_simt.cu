@@ -26,15 +26,19 @@ struct MatmulLoader {
     template <typename T> __device__ __forceinline__ float A(const T* a, const Row& r, int64_t k) const { return to_f<T>(a[r.off + k * a_sk]); }
     template <typename T> __device__ __forceinline__ float B(const T* b, int64_t k, int64_t n) const { return to_f<T>(b[k * b_sk + n * b_sn]); }
     __device__ __forceinline__ int64_t C(int64_t m, int64_t n) const { return m * c_sm + n; }
+    __device__ __forceinline__ int64_t a_group(int) const { return 0; }
+    __device__ __forceinline__ int64_t b_group(int) const { return 0; }
+    __device__ __forceinline__ int64_t c_group(int) const { return 0; }
 };
 
+// Grouped convolution: blockIdx.z is the group; C_ / Co are the channels of ONE group, Ct / CoT those of the tensors.
 struct ConvLoader {
-    int C_, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+    int C_, Ct, H, W, Co, CoT, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
     struct Row { int64_t base; int ih0, iw0; };          // image base offset and top-left input coordinate of the window
     __device__ __forceinline__ Row row(int64_t m) const {
         const int ow = (int)(m % OW); const int64_t t = m / OW;
         const int oh = (int)(t % OH); const int64_t n = t / OH;
-        return Row{n * C_ * (int64_t)H * W, oh * sh - ph, ow * sw - pw};
+        return Row{n * Ct * (int64_t)H * W, oh * sh - ph, ow * sw - pw};
     }
     template <typename T> __device__ __forceinline__ float A(const T* x, const Row& r, int64_t k) const {
         const int kw = (int)(k % KW); const int t2 = (int)(k / KW);
@@ -48,8 +52,45 @@ struct ConvLoader {
     }
     __device__ __forceinline__ int64_t C(int64_t m, int64_t n) const {
         const int64_t pix = m % ((int64_t)OH * OW), img = m / ((int64_t)OH * OW);
-        return (img * Co + n) * ((int64_t)OH * OW) + pix;
+        return (img * CoT + n) * ((int64_t)OH * OW) + pix;
     }
+    __device__ __forceinline__ int64_t a_group(int g) const { return (int64_t)g * C_ * H * W; }
+    __device__ __forceinline__ int64_t b_group(int g) const { return (int64_t)g * Co * ((int64_t)C_ * KH * KW); }
+    __device__ __forceinline__ int64_t c_group(int g) const { return (int64_t)g * Co * ((int64_t)OH * OW); }
+};
+
+// Transposed convolution in gather form: y[n,o,ho,wo] = sum over (i,kh,kw) of x[n,i,(ho+ph-kh*dh)/sh,(wo+pw-kw*dw)/sw] *
+// w[i,o,kh,kw] wherever the divisions are exact and in range (the scatter of python/jittor/nn.py:1437-1449 read from
+// the output side). M = N*OH*OW output pixels, N = out channels of a group, K = (in channels of a group)*KH*KW.
+struct ConvTLoader {
+    int Ci, CiT, H, W, Co, CoT, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;   // H, W: input extent; OH, OW: output extent
+    struct Row { int64_t base; int oh, ow; };
+    __device__ __forceinline__ Row row(int64_t m) const {
+        const int ow = (int)(m % OW); const int64_t t = m / OW;
+        const int oh = (int)(t % OH); const int64_t n = t / OH;
+        return Row{n * CiT * (int64_t)H * W, oh + ph, ow + pw};
+    }
+    template <typename T> __device__ __forceinline__ float A(const T* x, const Row& r, int64_t k) const {
+        const int kw = (int)(k % KW); const int t2 = (int)(k / KW);
+        const int kh = t2 % KH; const int c = t2 / KH;
+        const int a = r.oh - kh * dh, b = r.ow - kw * dw;
+        if (a < 0 || b < 0 || a % sh || b % sw) return 0.f;
+        const int ih = a / sh, iw = b / sw;
+        if (ih >= H || iw >= W) return 0.f;
+        return to_f<T>(x[r.base + ((int64_t)c * H + ih) * W + iw]);
+    }
+    template <typename T> __device__ __forceinline__ float B(const T* w, int64_t k, int64_t n) const {
+        const int64_t taps = (int64_t)KH * KW;
+        const int64_t c = k / taps, tap = k - c * taps;
+        return to_f<T>(w[(c * Co + n) * taps + tap]);                  // w[i][o within group][kh][kw]
+    }
+    __device__ __forceinline__ int64_t C(int64_t m, int64_t n) const {
+        const int64_t pix = m % ((int64_t)OH * OW), img = m / ((int64_t)OH * OW);
+        return (img * CoT + n) * ((int64_t)OH * OW) + pix;
+    }
+    __device__ __forceinline__ int64_t a_group(int g) const { return (int64_t)g * Ci * H * W; }
+    __device__ __forceinline__ int64_t b_group(int g) const { return (int64_t)g * Ci * Co * ((int64_t)KH * KW); }
+    __device__ __forceinline__ int64_t c_group(int g) const { return (int64_t)g * Co * ((int64_t)OH * OW); }
 };
 
 // TM x TN output tile per CTA of 256 threads (16 x 16), (TM/16) x (TN/16) outputs per thread.
@@ -59,6 +100,7 @@ gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict
                  int64_t M, int64_t N, int64_t K, const L ld) {
     constexpr int RM = TM / 16, RN = TN / 16;
     constexpr int LA = TM * BK / 256, LB = TN * BK / 256;         // staged elements per thread
+    a += ld.a_group(blockIdx.z); b += ld.b_group(blockIdx.z); c += ld.c_group(blockIdx.z);
     __shared__ float As[BK][TM + 4];
     __shared__ float Bs[BK][TN + 4];
     const int tid = threadIdx.x;
@@ -112,13 +154,14 @@ gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict
 
 // 64x64 tiles when they fill the machine, 32x32 tiles for small problems (latency-bound: more CTAs in flight).
 template <typename T, typename L>
-static void launch_simt(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, const L& ld, cudaStream_t st) {
-    const int64_t big = ((M + 63) / 64) * ((N + 63) / 64);
-    if (big >= 2 * kNumSMs) {
-        dim3 grid((unsigned)((M + 63) / 64), (unsigned)((N + 63) / 64));
+static void launch_simt(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, const L& ld, cudaStream_t st,
+                        int groups = 1) {
+    const int64_t big = ((M + 63) / 64) * ((N + 63) / 64) * groups;
+    if (big >= 2 * kNumSMs && N > 32) {
+        dim3 grid((unsigned)((M + 63) / 64), (unsigned)((N + 63) / 64), (unsigned)groups);
         gemm_simt_kernel<T, L, 64, 64><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
     } else {
-        dim3 grid((unsigned)((M + 31) / 32), (unsigned)((N + 31) / 32));
+        dim3 grid((unsigned)((M + 31) / 32), (unsigned)((N + 31) / 32), (unsigned)groups);
         gemm_simt_kernel<T, L, 32, 32><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
     }
 }
@@ -136,10 +179,22 @@ int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int
 }
 
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st) {
-    ConvLoader L{s.C, s.H, s.W, s.Co, s.KH, s.KW, s.OH, s.OW, s.sh, s.sw, s.ph, s.pw, s.dh, s.dw};
-    const int64_t M = (int64_t)s.N * s.OH * s.OW, N = s.Co, K = (int64_t)s.C * s.KH * s.KW;
-    if (dtype == B200JT_FLOAT32) launch_simt<float, ConvLoader>(x, w, y, M, N, K, L, st);
-    else launch_simt<__nv_bfloat16, ConvLoader>(x, w, y, M, N, K, L, st);
+    const int G = s.groups > 0 ? s.groups : 1;
+    ConvLoader L{s.C / G, s.C, s.H, s.W, s.Co / G, s.Co, s.KH, s.KW, s.OH, s.OW, s.sh, s.sw, s.ph, s.pw, s.dh, s.dw};
+    const int64_t M = (int64_t)s.N * s.OH * s.OW, N = s.Co / G, K = (int64_t)(s.C / G) * s.KH * s.KW;
+    if (dtype == B200JT_FLOAT32) launch_simt<float, ConvLoader>(x, w, y, M, N, K, L, st, G);
+    else launch_simt<__nv_bfloat16, ConvLoader>(x, w, y, M, N, K, L, st, G);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+// s: C/H/W describe the INPUT x, Co/OH/OW the OUTPUT y of the transposed convolution.
+int conv2d_transpose_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st) {
+    const int G = s.groups > 0 ? s.groups : 1;
+    ConvTLoader L{s.C / G, s.C, s.H, s.W, s.Co / G, s.Co, s.KH, s.KW, s.OH, s.OW, s.sh, s.sw, s.ph, s.pw, s.dh, s.dw};
+    const int64_t M = (int64_t)s.N * s.OH * s.OW, N = s.Co / G, K = (int64_t)(s.C / G) * s.KH * s.KW;
+    if (dtype == B200JT_FLOAT32) launch_simt<float, ConvTLoader>(x, w, y, M, N, K, L, st, G);
+    else launch_simt<__nv_bfloat16, ConvTLoader>(x, w, y, M, N, K, L, st, G);
     B200JT_LAUNCH_CHECK();
     return 0;
 }

@@ -6,6 +6,7 @@ namespace b200jt {
 
 struct ConvShape {
     int N, C, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+    int groups = 1;
 };
 
 int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int64_t N, int64_t K,
@@ -25,5 +26,6 @@ int tcconv_status_fetch_and_clear();
 int peer_status_fetch_and_clear();          // peer_allreduce.cu
 
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
+int conv2d_transpose_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
 
 }  // namespace b200jt

@@ -61,6 +61,13 @@ def realize(roots):
 def _make_plan(v):
     if v._op is None:
         raise C.B200Error("Var has neither data nor a producer")
+    relay = getattr(v, "_relay", None)
+    if relay is not None:                       # grouped / transposed convolution built by nn with its relay record
+        kind, x, w, geo, groups = relay
+        if x.dtype in ("float32", "bfloat16") and w.dtype in ("float32", "bfloat16"):
+            if kind == "conv2d":
+                return Plan([x, w], lambda: run_conv2d(x, w, geo, v.dtype, groups=groups))
+            return Plan([x, w], lambda: run_conv2d_transpose(x, w, geo, groups, list(v.shape), v.dtype))
     for matcher in _MATCHERS:
         p = matcher(v)
         if p is not None:
@@ -331,7 +338,17 @@ def conv_geometry(rx, ww):
     return x, w, (sh, sw, ph, pw, dh, dw)
 
 
-def run_conv2d(x, w, geo, out_dtype, stats=None):
+def run_conv2d_transpose(x, w, geo, groups, out_shape, out_dtype):
+    sh, sw, ph, pw, dh, dw = geo
+    xd = x._data
+    wd = _cast(w._data, x.dtype)
+    out = _empty(out_shape, x.dtype)
+    C.check(C.lib.b200jt_conv2d_transpose(C.desc(xd), C.desc(wd), C.desc(out), sh, sw, ph, pw, dh, dw, groups, C.stream_ptr()),
+            f"conv2d_transpose x{list(x.shape)} w{list(w.shape)} geo{geo} groups {groups}")
+    return _cast(out, out_dtype)
+
+
+def run_conv2d(x, w, geo, out_dtype, stats=None, groups=1):
     sh, sw, ph, pw, dh, dw = geo
     N, Ci, H, W = x.shape
     Co, _, KH, KW = w.shape
@@ -340,7 +357,7 @@ def run_conv2d(x, w, geo, out_dtype, stats=None):
     xd, wd = x._data, w._data
     wd = _cast(wd, x.dtype)
     out = _empty([N, Co, OH, OW], x.dtype)
-    args = (C.desc(xd), C.desc(wd), C.desc(out), sh, sw, ph, pw, dh, dw, 1)
+    args = (C.desc(xd), C.desc(wd), C.desc(out), sh, sw, ph, pw, dh, dw, groups)
     nbytes = C.lib.b200jt_conv2d_workspace(*args)
     ws, wsp = _workspace(nbytes)
     sp = ctypes.c_void_p(stats.data_ptr()) if stats is not None else ctypes.c_void_p(0)

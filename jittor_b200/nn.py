@@ -124,18 +124,32 @@ def _pair(v):
 
 
 def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
-    """groups == 1 branch of Conv.execute (python/jittor/nn.py:1001-1021): reindex x to the 7-D window tensor,
-    broadcast w over [0,3,4], multiply, sum over [2,5,6]."""
+    """Conv.execute (python/jittor/nn.py:1001-1056). groups == 1: reindex x to the 7-D window tensor, broadcast w over
+    [0,3,4], multiply, sum over [2,5,6]. groups > 1: x and w are both re-indexed to [N,G,oc/G,C/G,oh,ow,Kh,Kw], multiplied
+    and folded by reindex_reduce('add') (nn.py:1022-1051). The executor recognises the first form by its index
+    expressions; the second carries a relay record (the role of the reference's compile_options {"G","C"} hint) so that
+    it runs as one grouped implicit-GEMM launch instead of materialising the 8-D product."""
     x, weight = to_var(x), to_var(weight)
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
-    if groups != 1:
-        raise NotImplementedError("grouped convolution is not on the accelerated path")
     N, C, H, W = x.shape
     out_channels, Cw, Kh, Kw = weight.shape
-    assert C == Cw
     oh = (H + padding[0] * 2 - Kh * dilation[0] + dilation[0] - 1) // stride[0] + 1
     ow = (W + padding[1] * 2 - Kw * dilation[1] + dilation[1] - 1) // stride[1] + 1
     assert oh > 0 and ow > 0
+    if groups != 1:
+        G, CpG, ocg = groups, C // groups, out_channels // groups
+        assert C % G == 0 and out_channels % G == 0 and Cw == CpG
+        shape = [N, G, ocg, CpG, oh, ow, Kh, Kw]
+        xx = x.reindex(shape, ["i0", f"i1*{CpG}+i3",
+                               f"i4*{stride[0]}-{padding[0]}+i6*{dilation[0]}",
+                               f"i5*{stride[1]}-{padding[1]}+i7*{dilation[1]}"])
+        ww = weight.reindex(shape, [f"i1*{ocg}+i2", "i3", "i6", "i7"])
+        y = (xx * ww).reindex_reduce("add", [N, out_channels, oh, ow], ["i0", f"i1*{ocg}+i2", "i4", "i5"])
+        y._relay = ("conv2d", x, weight, stride + padding + dilation, G)
+        if bias is not None:
+            y = y + to_var(bias).broadcast(y.shape, [0, 2, 3])
+        return y
+    assert C == Cw
     with flag_scope(amp_reg=flags.amp_reg | 36):
         xx = x.reindex([N, out_channels, C, oh, ow, Kh, Kw], [
             "i0",
@@ -149,6 +163,66 @@ def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
     if bias is not None:
         y = y + to_var(bias).broadcast(y.shape, [0, 2, 3])
     return y
+
+
+def conv_transpose2d(x, weight, bias=None, stride=1, padding=0, output_padding=0, groups=1, dilation=1):
+    """ConvTranspose.execute (python/jittor/nn.py:1429-1491): weight is [Cin, Cout/groups, Kh, Kw]; x and w are broadcast
+    (groups == 1) or re-indexed (groups > 1) to the full loop nest, multiplied, and scattered into the output with
+    reindex_reduce('add'). The result Var carries a relay record so that the nest runs as one implicit-GEMM launch
+    (gather form) instead of being materialised."""
+    x, weight = to_var(x), to_var(weight)
+    stride, padding, dilation, output_padding = _pair(stride), _pair(padding), _pair(dilation), _pair(output_padding)
+    if x.ndim != 4:
+        raise RuntimeError(f"Expected 4D (batched) input to conv_transpose2d, but got input of size: {list(x.shape)}")
+    assert output_padding[0] < max(stride[0], dilation[0]) and output_padding[1] < max(stride[1], dilation[1]), \
+        "output padding must be smaller than max(stride, dilation)"
+    N, C, H, W = x.shape
+    i, o, h, w = weight.shape
+    assert C == i
+    h_out = (H - 1) * stride[0] + output_padding[0] - 2 * padding[0] + 1 + (h - 1) * dilation[0]
+    w_out = (W - 1) * stride[1] + output_padding[1] - 2 * padding[1] + 1 + (w - 1) * dilation[1]
+    hid = f"*{stride[0]}-{padding[0]}+"
+    wid = f"*{stride[1]}-{padding[1]}+"
+    if groups == 1:
+        shape = [N, i, o, H, W, h, w]
+        xx = x.broadcast(shape, (2, 5, 6))
+        ww = weight.broadcast(shape, (0, 3, 4))
+        y = (ww * xx).reindex_reduce("add", [N, o, h_out, w_out],
+                                     ["i0", "i2", f"i3{hid}i5*{dilation[0]}", f"i4{wid}i6*{dilation[1]}"])
+    else:
+        G, CpG, oc = groups, C // groups, o * groups
+        shape = [N, G, o, CpG, H, W, h, w]
+        xx = x.reindex(shape, ["i0", f"i1*{CpG}+i3", "i4", "i5"])
+        ww = weight.reindex(shape, [f"i1*{CpG}+i3", "i2", "i6", "i7"])
+        y = (ww * xx).reindex_reduce("add", [N, oc, h_out, w_out],
+                                     ["i0", f"i1*{o}+i2", f"i4{hid}i6*{dilation[0]}", f"i5{wid}i7*{dilation[1]}"])
+    y._relay = ("conv2d_transpose", x, weight, stride + padding + dilation, groups)
+    if bias is not None:
+        y = y + to_var(bias).broadcast(y.shape, [0, 2, 3])
+    return y
+
+
+class ConvTranspose(Module):
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, output_padding=0, groups=1, bias=True,
+                 dilation=1):
+        assert in_channels % groups == 0, "in_channels must be divisible by groups"
+        assert out_channels % groups == 0, "out_channels must be divisible by groups"
+        self.in_channels, self.out_channels, self.groups = in_channels, out_channels, groups
+        self.kernel_size = _pair(kernel_size)
+        self.stride, self.padding, self.dilation = _pair(stride), _pair(padding), _pair(dilation)
+        self.output_padding = _pair(output_padding)
+        Kh, Kw = self.kernel_size
+        rng = np.random.default_rng(0)
+        bound = 1.0 / np.sqrt(out_channels // groups * Kh * Kw)
+        self.weight = V.array(rng.uniform(-bound, bound, (in_channels, out_channels // groups, Kh, Kw)).astype(np.float32))
+        self.bias = V.array(rng.uniform(-bound, bound, (out_channels,)).astype(np.float32)) if bias else None
+
+    def execute(self, x):
+        return conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding, self.output_padding, self.groups,
+                                self.dilation)
+
+
+ConvTranspose2d = ConvTranspose
 
 
 class Conv(Module):

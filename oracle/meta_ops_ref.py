@@ -930,3 +930,54 @@ def pool2d_backward(x, dy, kernel_size, op, stride=None, padding=0, ceil_mode=Fa
                 n_i, c_i = np.nonzero(has)
                 np.add.at(dx, (n_i, c_i, k2 + first[n_i, c_i] // ww, k3 + first[n_i, c_i] % ww), d[n_i, c_i])
     return dx.astype(x.dtype)
+
+
+# --------------------------------------------------------------------------- grouped / transposed convolution
+def conv2d_grouped(x, w, stride=1, padding=0, dilation=1, groups=1, bias=None):
+    """Conv.execute with groups > 1, python/jittor/nn.py:1022-1051, composed from this file's meta-ops exactly as
+    the reference composes its own: two reindex to [N,G,oc/G,C/G,oh,ow,Kh,Kw], multiply, reindex_reduce('add')."""
+    x, w = np.asarray(x), np.asarray(w)
+    s, p, d = _pair(stride), _pair(padding), _pair(dilation)
+    N, C, H, W = x.shape
+    oc, _, Kh, Kw = w.shape
+    G, CpG, ocg = groups, C // groups, oc // groups
+    oh = (H + p[0] * 2 - Kh * d[0] + d[0] - 1) // s[0] + 1
+    ow = (W + p[1] * 2 - Kw * d[1] + d[1] - 1) // s[1] + 1
+    shape = [N, G, ocg, CpG, oh, ow, Kh, Kw]
+    xx = reindex(x, shape, ["i0", f"i1*{CpG}+i3", f"i4*{s[0]}-{p[0]}+i6*{d[0]}", f"i5*{s[1]}-{p[1]}+i7*{d[1]}"])
+    ww = reindex(w, shape, [f"i1*{ocg}+i2", "i3", "i6", "i7"])
+    y = reindex_reduce(binary(xx, ww, "multiply"), "add", [N, oc, oh, ow], ["i0", f"i1*{ocg}+i2", "i4", "i5"])
+    if bias is not None:
+        y = binary(y, broadcast(np.asarray(bias), y.shape, [0, 2, 3]), "add")
+    return y
+
+
+def conv_transpose2d(x, w, stride=1, padding=0, output_padding=0, groups=1, dilation=1, bias=None):
+    """ConvTranspose.execute, python/jittor/nn.py:1429-1491: y[n, g*oc_g+o, hi*s-p+kh*d, wi*s-p+kw*d] += x[n, g*ic_g+i,
+    hi, wi] * w[g*ic_g+i, o, kh, kw]. (The reference's groups > 1 branch mixes up the per-group channel counts and is
+    only meaningful for in_channels == out_channels, where it computes exactly this.)"""
+    x, w = np.asarray(x), np.asarray(w)
+    s, p, d, op_ = _pair(stride), _pair(padding), _pair(dilation), _pair(output_padding)
+    N, C, H, W = x.shape
+    _, o, Kh, Kw = w.shape
+    G, icg = groups, C // groups
+    h_out = (H - 1) * s[0] + op_[0] - 2 * p[0] + 1 + (Kh - 1) * d[0]
+    w_out = (W - 1) * s[1] + op_[1] - 2 * p[1] + 1 + (Kw - 1) * d[1]
+    y = np.zeros((N, o * G, h_out, w_out), dtype=np.float64)
+    for g in range(G):
+        xg = x[:, g * icg:(g + 1) * icg].astype(np.float64)
+        wg = w[g * icg:(g + 1) * icg].astype(np.float64)
+        for kh in range(Kh):
+            for kw in range(Kw):
+                contrib = np.einsum("nihw,io->nohw", xg, wg[:, :, kh, kw])
+                for hi in range(H):
+                    ho = hi * s[0] - p[0] + kh * d[0]
+                    if not 0 <= ho < h_out:
+                        continue
+                    wo = np.arange(W) * s[1] - p[1] + kw * d[1]
+                    ok = (wo >= 0) & (wo < w_out)
+                    y[:, g * o:(g + 1) * o, ho, wo[ok]] += contrib[:, :, hi, ok]
+    y = y.astype(x.dtype)
+    if bias is not None:
+        y = binary(y, broadcast(np.asarray(bias), y.shape, [0, 2, 3]), "add")
+    return y

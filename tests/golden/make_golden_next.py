@@ -228,6 +228,49 @@ do_pool("pool_mean_ceil_p1_count_pad", f32(1, 2, 10, 10), 3, "mean", 2, 1, True,
 do_pool("pool_mean_ceil_p1_no_count_pad", f32(1, 2, 10, 10), 3, "mean", 2, 1, True, False)
 do_pool("pool_max_64ch", f32(2, 64, 28, 28), 3, "maximum", 2, 1)
 
+
+
+# ---- grouped convolution and transposed convolution through the reference's nn layers ------------------------------
+def do_gconv(name, x, w, stride, padding, dilation, groups, bias=None):
+    m = nn.Conv(x.shape[1], w.shape[0], (w.shape[2], w.shape[3]), stride, padding, dilation, groups, bias is not None)
+    m.weight = to_jt(w)
+    if bias is not None:
+        m.bias = to_jt(bias)
+    y = m(to_jt(x))
+    case(name, "conv_grouped", dict(stride=stride, padding=padding, dilation=dilation, groups=groups, bias=bias is not None),
+         [x, w] + ([bias] if bias is not None else []), to_np(y))
+
+
+def do_tconv(name, x, w, stride, padding, output_padding, groups, dilation, bias=None):
+    m = nn.ConvTranspose(x.shape[1], w.shape[1] * groups, (w.shape[2], w.shape[3]), stride, padding, output_padding,
+                         groups, bias is not None, dilation)
+    m.weight = to_jt(w)
+    if bias is not None:
+        m.bias = to_jt(bias)
+    y = m(to_jt(x))
+    case(name, "conv_transpose", dict(stride=stride, padding=padding, output_padding=output_padding, groups=groups,
+                                      dilation=dilation, bias=bias is not None),
+         [x, w] + ([bias] if bias is not None else []), to_np(y))
+
+
+def wgt(*shape):
+    return (rng.normal(size=shape) * 0.2).astype(np.float32)
+
+
+do_gconv("gconv_g2", f32(2, 8, 9, 9), wgt(12, 4, 3, 3), 1, 1, 1, 2)
+do_gconv("gconv_g4_s2_bias", f32(2, 8, 10, 11), wgt(8, 2, 3, 3), 2, 1, 1, 4, f32(8))
+do_gconv("gconv_g2_dilated", f32(1, 6, 12, 12), wgt(4, 3, 3, 3), 1, 2, 2, 2)
+do_gconv("gconv_depthwise", f32(2, 16, 10, 10), wgt(16, 1, 3, 3), 1, 1, 1, 16)
+do_gconv("gconv_depthwise_mult2_s2", f32(2, 6, 11, 9), wgt(12, 1, 3, 3), 2, 1, 1, 6)
+do_gconv("gconv_g8_1x1", f32(2, 64, 7, 7), wgt(64, 8, 1, 1), 1, 0, 1, 8)
+do_tconv("tconv_basic", f32(2, 4, 5, 6), wgt(4, 3, 3, 3), 1, 0, 0, 1, 1)
+do_tconv("tconv_s2_p1_op1_bias", f32(2, 4, 5, 6), wgt(4, 6, 3, 3), 2, 1, 1, 1, 1, f32(6))
+do_tconv("tconv_s3_k2", f32(1, 3, 4, 4), wgt(3, 5, 2, 2), 3, 0, 2, 1, 1)
+do_tconv("tconv_dilated", f32(1, 3, 6, 6), wgt(3, 2, 3, 3), 1, 1, 0, 1, 2)
+do_tconv("tconv_rect_kernel", f32(2, 3, 5, 7), wgt(3, 4, 2, 4), (2, 1), (0, 1), 0, 1, 1)
+do_tconv("tconv_g2_in_eq_out", f32(2, 6, 5, 5), wgt(6, 3, 3, 3), 2, 1, 1, 2, 1)
+do_tconv("tconv_g4_in_eq_out", f32(1, 8, 4, 6), wgt(8, 2, 4, 4), 2, 1, 0, 4, 1, f32(8))
+
 np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
 with open(os.path.join(HERE, "next_ops.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_golden_next.py", "reference_version": jt.__version__, "cases": CASES},

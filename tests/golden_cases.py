@@ -124,6 +124,12 @@ def run_case(c, be):
     elif op == "pool2d_bwd":
         got = be.pool2d_backward(ins[0], ins[1], _kw(a["kernel_size"]), a["op"], _kw(a["stride"]), _kw(a["padding"]),
                                  a["ceil_mode"], a["count_include_pad"])
+    elif op == "conv_grouped":
+        got = be.conv2d_grouped(ins[0], ins[1], _kw(a["stride"]), _kw(a["padding"]), _kw(a["dilation"]), a["groups"],
+                                ins[2] if a["bias"] else None)
+    elif op == "conv_transpose":
+        got = be.conv_transpose2d(ins[0], ins[1], _kw(a["stride"]), _kw(a["padding"]), _kw(a["output_padding"]),
+                                  a["groups"], _kw(a["dilation"]), ins[2] if a["bias"] else None)
     elif op == "optim":
         kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in a.items() if k not in ("kind", "steps")}
         got = be.optim_steps(ins[0], ins[1], ins[2], a["kind"], a["steps"], **kw)

@@ -16,6 +16,16 @@ def _jt_slices(slices):
 
 class ProductBackend:
     @staticmethod
+    def conv2d_grouped(x, w, stride, padding, dilation, groups, bias=None):
+        return _np(nn.conv2d(jt.array(x), jt.array(w), None if bias is None else jt.array(bias), stride, padding,
+                             dilation, groups))
+
+    @staticmethod
+    def conv_transpose2d(x, w, stride, padding, output_padding, groups, dilation, bias=None):
+        return _np(nn.conv_transpose2d(jt.array(x), jt.array(w), None if bias is None else jt.array(bias), stride,
+                                       padding, output_padding, groups, dilation))
+
+    @staticmethod
     def pool2d(x, kernel_size, op, stride=None, padding=0, ceil_mode=False, count_include_pad=True):
         from jittor_b200 import pool
         layer = pool.Pool(kernel_size, stride, padding, ceil_mode=ceil_mode, count_include_pad=count_include_pad, op=op)
