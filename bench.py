@@ -425,7 +425,73 @@ class MetaOps:
         return max(done, 1), time.perf_counter() - t0, f"{rows} of {self.ROWS} rows per part through the numpy oracle (1 core)"
 
 
-WORKLOADS = {w.key: w for w in (C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps)}
+class NextOps:
+    """The callers either side of the path: pooling kernels, getitem gather, setitem scatter-add."""
+    key, metric, unit, bound, dtype, scaling = "next", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
+    SHAPE = (64, 128, 112, 112)
+    ROWS, COLS, PICK = 1 << 20, 64, 1 << 19
+    description = ("callers of the path: 3x3 stride-2 pad-1 max-pool forward and backward on [64,128,112,112] fp32, "
+                   "getitem x[idx] of 2^19 rows out of [2^20,64] fp32, setitem x[idx] += v on the same shapes")
+    kernel_of = {"maxpool-fwd": "pool_fwd_kernel", "maxpool-bwd": "pool_bwd_kernel", "getitem-rows": "reindex kernel",
+                 "setitem-add-rows": "rr_generic_kernel"}
+    launches = {"maxpool-fwd": 1, "maxpool-bwd": 1, "getitem-rows": 1, "setitem-add-rows": 1}
+
+    def work(self):
+        n = int(np.prod(self.SHAPE)) * 4
+        o = self.SHAPE[0] * self.SHAPE[1] * 56 * 56 * 4
+        rows = self.PICK * self.COLS * 4
+        return {"maxpool-fwd": n + o, "maxpool-bwd": 2 * n + 2 * o, "getitem-rows": 2 * rows + self.PICK * 4,
+                "setitem-add-rows": 2 * self.ROWS * self.COLS * 4 + 2 * rows + self.PICK * 4}
+
+    def setup(self, rank, world, jt, torch, multi):
+        from jittor_b200 import pool
+        self.jt, self.torch, self.pool = jt, torch, pool
+        g = torch.Generator().manual_seed(11 + rank)
+        self.hx = torch.randn(*self.SHAPE, generator=g).pin_memory()
+        self.x = jt.array(self.hx)
+        self.y = pool.max_pool2d(self.x, 3, 2, 1).sync()
+        self.dy = jt.array(torch.randn(self.SHAPE[0], self.SHAPE[1], 56, 56, generator=g))
+        self.table = jt.array(torch.randn(self.ROWS, self.COLS, generator=g))
+        self.idx = jt.array(torch.randperm(self.ROWS, generator=g)[:self.PICK].to(torch.int32))
+        self.vals = jt.array(torch.randn(self.PICK, self.COLS, generator=g))
+        return list(self.launches)
+
+    def _op(self, name, x):
+        if name == "maxpool-fwd":
+            return self.pool.max_pool2d(x, 3, 2, 1)
+        if name == "maxpool-bwd":
+            return self.y._op.attrs["grad"](self.y, self.dy, 0)
+        if name == "getitem-rows":
+            return self.table[self.idx]
+        return self.table.setitem((self.idx,), self.vals, "add")
+
+    def run(self, name):
+        return self._op(name, self.x).sync()
+
+    def run_e2e(self, name):
+        x = self.jt.array(self.hx.cuda(non_blocking=True))
+        self._op(name, x).sync()
+
+    def e2e_bytes(self, names):
+        return len(names) * self.hx.numel() * 4, 0
+
+    def cpu(self, names):
+        from oracle import meta_ops_ref as ref
+        x = np.random.default_rng(11).normal(size=(2, 16, 112, 112)).astype(np.float32)
+        done, t0 = 0, time.perf_counter()
+        frac = x.size / float(np.prod(self.SHAPE))
+        for nm in names:
+            if nm == "maxpool-fwd":
+                ref.pool2d(x, 3, "maximum", 2, 1)
+            elif nm == "maxpool-bwd":
+                ref.pool2d_backward(x, np.ones((2, 16, 56, 56), np.float32), 3, "maximum", 2, 1)
+            else:
+                continue
+            done += self.work()[nm] * frac
+        return max(done, 1), time.perf_counter() - t0, "2x16 of 64x128 images per pooling part through the numpy oracle (1 core)"
+
+
+WORKLOADS = {w.key: w for w in (C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps, NextOps)}
 
 
 def scale_of(unit):

@@ -258,9 +258,12 @@ bool compile_index_program(const int64_t* loop_shape, int ndim_loop, const int64
 
     bool affine = (n_conds == 0);
     bool direct = (n_indexes == 1 && n_conds == 0 && n_extras >= 1);
+    std::vector<size_t> seg_begin, seg_end;          // code range of every expression (indexes, then conditions)
     for (int d = 0; d < n_indexes; d++) {
         Affine a;
+        seg_begin.push_back(C.code.size());
         if (!C.compile_one(indexes[d], &a)) { *err = C.err; return false; }
+        seg_end.push_back(C.code.size());
         if (d == 0 && !C.direct_candidate) direct = false;
         C.emit(IX_STORE_XID, d);
         if (a.ok) { P->c0[d] = a.c; for (int j = 0; j < kMaxDims; j++) P->coef[d][j] = a.coef[j]; }
@@ -268,7 +271,9 @@ bool compile_index_program(const int64_t* loop_shape, int ndim_loop, const int64
     }
     for (int k = 0; k < n_conds; k++) {
         Affine a;
+        seg_begin.push_back(C.code.size());
         if (!C.compile_one(conds[k], &a)) { *err = C.err; return false; }
+        seg_end.push_back(C.code.size());
         C.emit(IX_STORE_COND);
     }
     if (C.max_depth > kIxStack) { *err = "index expression too deep"; return false; }
@@ -282,6 +287,31 @@ bool compile_index_program(const int64_t* loop_shape, int ndim_loop, const int64
         for (int d = 0; direct && d < ndim_loop; d++) direct = e.shape[d] == loop_shape[d];
     }
     P->is_direct_extra = direct;
+    // inner run: count, per loop variable, the expressions that read it
+    {
+        std::vector<int> readers(kMaxDims, 0);
+        auto reads = [&](size_t e, int j) {
+            for (size_t pc = seg_begin[e]; pc < seg_end[e]; pc++) {
+                const int op = C.code[pc] & 0xff;
+                if (op == IX_CONST64) { pc += 2; continue; }
+                if (op == IX_LOOPVAR && (C.code[pc] >> 8) == j) return true;
+            }
+            return false;
+        };
+        for (size_t e = 0; e < seg_begin.size(); e++)
+            for (int j = 0; j < ndim_loop; j++) if (reads(e, j)) readers[j]++;
+        int k = 0; int64_t run = 1;
+        while (k < ndim_loop && k < ndim_x) {
+            const int j = ndim_loop - 1 - k, d = ndim_x - 1 - k;
+            const bool identity = seg_end[d] - seg_begin[d] == 1 && (C.code[seg_begin[d]] & 0xff) == IX_LOOPVAR &&
+                                  (C.code[seg_begin[d]] >> 8) == j;
+            if (!identity || readers[j] != 1 || loop_shape[j] != x_shape[d]) break;
+            run *= loop_shape[j];
+            k++;
+        }
+        P->inner_dims = k;
+        P->inner_elems = run;
+    }
     return true;
 }
 

@@ -47,6 +47,11 @@ struct IndexProgram {
     // "direct scatter/gather": one indexed dim, index = @e0(i0..in) with identity subscripts and
     // extras[0] shaped like the loop tensor (x[e0[i]] <- y[i])
     int32_t is_direct_extra;
+    // "inner run": the last inner_dims loop axes map one-to-one onto the last inner_dims axes of x (index = that loop
+    // variable, equal extents) and nothing else reads them, so inner_elems consecutive loop elements address
+    // inner_elems consecutive x elements and the program only has to be evaluated once per run
+    int32_t inner_dims;
+    int64_t inner_elems;
 };
 
 // Compiles the strings. Returns false and sets `err` on a syntax error (the reference rejects the

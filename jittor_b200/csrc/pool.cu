@@ -28,24 +28,37 @@ template <typename T, typename A> __device__ __forceinline__ T cvt(A v) { return
 template <> __device__ __forceinline__ __nv_bfloat16 cvt<__nv_bfloat16, float>(float v) { return __float2bfloat16(v); }
 template <> __device__ __forceinline__ __half cvt<__half, float>(float v) { return __float2half(v); }
 
-// OP: 0 maximum, 1 minimum, 2 mean
-template <typename T, int OP>
+// OP: 0 maximum, 1 minimum, 2 mean. KS: 0 = window and stride read from the geometry record, else a compile-time
+// (kernel, stride) pair code so that the window arithmetic folds to constants for the common layers:
+// 1: 2x2 stride 2, 2: 3x3 stride 2, 3: 3x3 stride 1.
+template <int KS> struct Win {
+    __device__ __forceinline__ static int kh(const Geo& g) { return KS == 1 ? 2 : KS >= 2 ? 3 : g.kh; }
+    __device__ __forceinline__ static int kw(const Geo& g) { return KS == 1 ? 2 : KS >= 2 ? 3 : g.kw; }
+    __device__ __forceinline__ static int sh(const Geo& g) { return KS == 1 || KS == 2 ? 2 : KS == 3 ? 1 : g.sh; }
+    __device__ __forceinline__ static int sw(const Geo& g) { return KS == 1 || KS == 2 ? 2 : KS == 3 ? 1 : g.sw; }
+};
+
+// Thread layout of both kernels: blockDim (32, 8) covers 32 columns x 8 rows of one image plane, blockIdx.z walks the
+// N*C planes (grid-stride), so no division is needed to find a thread's coordinates.
+template <typename T, int OP, int KS>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int32_t* __restrict__ indices,
                                                        Geo g, T init) {
     using A = typename AccOf<T>::type;
-    const int64_t total = (int64_t)g.N * g.C * g.OH * g.OW;
-    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
-        const int ow = (int)(o % g.OW); const int64_t t = o / g.OW;
-        const int oh = (int)(t % g.OH); const int64_t nc = t / g.OH;
-        int p0 = oh * g.sh - g.ph, q0 = ow * g.sw - g.pw;
-        const int p1 = min(p0 + g.kh, g.H), q1 = min(q0 + g.kw, g.W);
-        p0 = max(p0, 0); q0 = max(q0, 0);
+    using Wn = Win<KS>;
+    const int ow = blockIdx.x * 32 + threadIdx.x, oh = blockIdx.y * 8 + threadIdx.y;
+    if (ow >= g.OW || oh >= g.OH) return;
+    int p0 = oh * Wn::sh(g) - g.ph, q0 = ow * Wn::sw(g) - g.pw;
+    const int p1 = min(p0 + Wn::kh(g), g.H), q1 = min(q0 + Wn::kw(g), g.W);
+    p0 = max(p0, 0); q0 = max(q0, 0);
+    const int64_t planes = (int64_t)g.N * g.C;
+    for (int64_t nc = blockIdx.z; nc < planes; nc += gridDim.z) {
         const T* xp = x + nc * (int64_t)g.H * g.W;
+        const int64_t o = (nc * g.OH + oh) * g.OW + ow;
         if (OP == 2) {
             A acc = 0;
             for (int p = p0; p < p1; p++)
                 for (int q = q0; q < q1; q++) acc += ld<T>(xp + (int64_t)p * g.W + q);
-            const int count = g.count_include_pad ? g.kh * g.kw : (p1 - p0) * (q1 - q0);
+            const int count = g.count_include_pad ? Wn::kh(g) * Wn::kw(g) : (p1 - p0) * (q1 - q0);
             y[o] = cvt<T, A>(acc / (A)count);
         } else {
             A best = ld<T>(&init);
@@ -62,36 +75,37 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
     }
 }
 
-template <typename T, int OP>
+template <typename T, int OP, int KS>
 __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy,
                                                        T* __restrict__ dx, Geo g) {
     using A = typename AccOf<T>::type;
-    const int64_t total = (int64_t)g.N * g.C * g.H * g.W;
-    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-        const int q = (int)(e % g.W); const int64_t t = e / g.W;
-        const int p = (int)(t % g.H); const int64_t nc = t / g.H;
+    using Wn = Win<KS>;
+    const int q = blockIdx.x * 32 + threadIdx.x, p = blockIdx.y * 8 + threadIdx.y;
+    if (q >= g.W || p >= g.H) return;
+    const int kh = Wn::kh(g), kw = Wn::kw(g), sh = Wn::sh(g), sw = Wn::sw(g);
+    // windows containing row p: oh*sh - ph <= p < oh*sh - ph + kh
+    const int oh_lo = max(0, (p + g.ph - kh + sh) / sh), oh_hi = min(g.OH - 1, (p + g.ph) / sh);
+    const int ow_lo = max(0, (q + g.pw - kw + sw) / sw), ow_hi = min(g.OW - 1, (q + g.pw) / sw);
+    const int64_t planes = (int64_t)g.N * g.C;
+    for (int64_t nc = blockIdx.z; nc < planes; nc += gridDim.z) {
         const T* xp = x + nc * (int64_t)g.H * g.W;
         const T* yp = y + nc * (int64_t)g.OH * g.OW;
         const T* dp = dy + nc * (int64_t)g.OH * g.OW;
-        // windows containing row p: oh*sh - ph <= p < oh*sh - ph + kh
-        const int oh_lo = max(0, (p + g.ph - g.kh + g.sh) / g.sh), oh_hi = min(g.OH - 1, (p + g.ph) / g.sh);
-        const int ow_lo = max(0, (q + g.pw - g.kw + g.sw) / g.sw), ow_hi = min(g.OW - 1, (q + g.pw) / g.sw);
         const A mine = ld<T>(xp + (int64_t)p * g.W + q);
         A acc = 0;
         for (int oh = oh_lo; oh <= oh_hi; oh++) {
-            int p0 = oh * g.sh - g.ph;
-            const int p1 = min(p0 + g.kh, g.H);
+            int p0 = oh * sh - g.ph;
+            const int p1 = min(p0 + kh, g.H);
             p0 = max(p0, 0);
             if (p < p0 || p >= p1) continue;
             for (int ow = ow_lo; ow <= ow_hi; ow++) {
-                int q0 = ow * g.sw - g.pw;
-                const int q1 = min(q0 + g.kw, g.W);
+                int q0 = ow * sw - g.pw;
+                const int q1 = min(q0 + kw, g.W);
                 q0 = max(q0, 0);
                 if (q < q0 || q >= q1) continue;
-                const A d = ld<T>(dp + (int64_t)oh * g.OW + ow);
                 if (OP == 2) {
-                    const int count = g.count_include_pad ? g.kh * g.kw : (p1 - p0) * (q1 - q0);
-                    acc += d / (A)count;
+                    const int count = g.count_include_pad ? kh * kw : (p1 - p0) * (q1 - q0);
+                    acc += ld<T>(dp + (int64_t)oh * g.OW + ow) / (A)count;
                 } else {
                     const A v = ld<T>(yp + (int64_t)oh * g.OW + ow);
                     if (!(mine == v)) continue;
@@ -101,12 +115,27 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ x, 
                         for (int qq = q0; qq < qe; qq++)
                             if (ld<T>(xp + (int64_t)pp * g.W + qq) == v) { first = false; break; }
                     }
-                    if (first) acc += d;
+                    if (first) acc += ld<T>(dp + (int64_t)oh * g.OW + ow);
                 }
             }
         }
-        dx[e] = cvt<T, A>(acc);
+        dx[(nc * g.H + p) * (int64_t)g.W + q] = cvt<T, A>(acc);
     }
+}
+
+static int window_code(const Geo& g) {
+    if (g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2) return 1;
+    if (g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2) return 2;
+    if (g.kh == 3 && g.kw == 3 && g.sh == 1 && g.sw == 1) return 3;
+    return 0;
+}
+
+static dim3 plane_grid(int w, int h, int64_t planes) {
+    const unsigned gx = (unsigned)((w + 31) / 32), gy = (unsigned)((h + 7) / 8);
+    // enough plane slices to fill the machine a few times over, each block then strides over the remaining planes
+    const int64_t want = ((int64_t)kNumSMs * 16 + (int64_t)gx * gy - 1) / ((int64_t)gx * gy);
+    const unsigned gz = (unsigned)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(planes, 65535), want));
+    return dim3(gx, gy, gz);
 }
 
 static int parse(const b200jt_tensor* x, const b200jt_tensor* y, const char* op, int kh, int kw, int sh, int sw, int ph, int pw,
@@ -128,15 +157,35 @@ static int parse(const b200jt_tensor* x, const b200jt_tensor* y, const char* op,
     return 0;
 }
 
+template <typename T, int OP>
+static void launch_fwd(const T* xp, T* yp, int32_t* indices, const Geo& g, T init, cudaStream_t st) {
+    const dim3 grid = plane_grid(g.OW, g.OH, (int64_t)g.N * g.C), block(32, 8);
+    switch (window_code(g)) {
+        case 1: pool_fwd_kernel<T, OP, 1><<<grid, block, 0, st>>>(xp, yp, indices, g, init); break;
+        case 2: pool_fwd_kernel<T, OP, 2><<<grid, block, 0, st>>>(xp, yp, indices, g, init); break;
+        case 3: pool_fwd_kernel<T, OP, 3><<<grid, block, 0, st>>>(xp, yp, indices, g, init); break;
+        default: pool_fwd_kernel<T, OP, 0><<<grid, block, 0, st>>>(xp, yp, indices, g, init);
+    }
+}
+
+template <typename T, int OP>
+static void launch_bwd(const T* xp, const T* yp, const T* dp, T* op, const Geo& g, cudaStream_t st) {
+    const dim3 grid = plane_grid(g.W, g.H, (int64_t)g.N * g.C), block(32, 8);
+    switch (window_code(g)) {
+        case 1: pool_bwd_kernel<T, OP, 1><<<grid, block, 0, st>>>(xp, yp, dp, op, g); break;
+        case 2: pool_bwd_kernel<T, OP, 2><<<grid, block, 0, st>>>(xp, yp, dp, op, g); break;
+        case 3: pool_bwd_kernel<T, OP, 3><<<grid, block, 0, st>>>(xp, yp, dp, op, g); break;
+        default: pool_bwd_kernel<T, OP, 0><<<grid, block, 0, st>>>(xp, yp, dp, op, g);
+    }
+}
+
 template <typename T>
 static int run_fwd(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indices, const Geo& g, int opc, cudaStream_t st) {
-    const int64_t total = numel(y);
-    if (total == 0) return 0;
-    const unsigned grid = grid_for(total, 256);
+    if (numel(y) == 0) return 0;
     const T* xp = (const T*)x->ptr; T* yp = (T*)y->ptr;
-    if (opc == 0) pool_fwd_kernel<T, 0><<<grid, 256, 0, st>>>(xp, yp, indices, g, init_value<T>(OP_MAX));
-    else if (opc == 1) pool_fwd_kernel<T, 1><<<grid, 256, 0, st>>>(xp, yp, indices, g, init_value<T>(OP_MIN));
-    else pool_fwd_kernel<T, 2><<<grid, 256, 0, st>>>(xp, yp, indices, g, init_value<T>(OP_ADD));
+    if (opc == 0) launch_fwd<T, 0>(xp, yp, indices, g, init_value<T>(OP_MAX), st);
+    else if (opc == 1) launch_fwd<T, 1>(xp, yp, indices, g, init_value<T>(OP_MIN), st);
+    else launch_fwd<T, 2>(xp, yp, indices, g, init_value<T>(OP_ADD), st);
     B200JT_LAUNCH_CHECK();
     return 0;
 }
@@ -144,13 +193,11 @@ static int run_fwd(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indi
 template <typename T>
 static int run_bwd(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* dy, const b200jt_tensor* dx,
                    const Geo& g, int opc, cudaStream_t st) {
-    const int64_t total = numel(x);
-    if (total == 0) return 0;
-    const unsigned grid = grid_for(total, 256);
+    if (numel(x) == 0) return 0;
     const T *xp = (const T*)x->ptr, *yp = (const T*)y->ptr, *dp = (const T*)dy->ptr; T* op = (T*)dx->ptr;
-    if (opc == 0) pool_bwd_kernel<T, 0><<<grid, 256, 0, st>>>(xp, yp, dp, op, g);
-    else if (opc == 1) pool_bwd_kernel<T, 1><<<grid, 256, 0, st>>>(xp, yp, dp, op, g);
-    else pool_bwd_kernel<T, 2><<<grid, 256, 0, st>>>(xp, yp, dp, op, g);
+    if (opc == 0) launch_bwd<T, 0>(xp, yp, dp, op, g, st);
+    else if (opc == 1) launch_bwd<T, 1>(xp, yp, dp, op, g, st);
+    else launch_bwd<T, 2>(xp, yp, dp, op, g, st);
     B200JT_LAUNCH_CHECK();
     return 0;
 }

@@ -47,6 +47,30 @@ rr_generic_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_const
     }
 }
 
+// Row form of the generic kernel: the program is evaluated once per run of `inner` consecutive y elements, which land
+// on `inner` consecutive x elements (x[idx[i], :] op= y[i, :]); one warp per run.
+template <typename T, typename I>
+__global__ void __launch_bounds__(256)
+rr_rows_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant__ IndexProgram P,
+               int64_t rows, int64_t inner, int op) {
+    const int nl = P.ndim_loop - P.inner_dims, nx = P.ndim_x;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t row = warp; row < rows; row += nwarps) {
+        I iv[kMaxDims];
+        int64_t r = row;
+        for (int d = P.ndim_loop - 1; d >= nl; d--) iv[d] = 0;
+#pragma unroll 1
+        for (int d = nl - 1; d >= 0; d--) { int64_t s = P.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
+        I xid[kMaxDims];
+        if (eval_index_program<I>(P, iv, xid)) continue;
+        int64_t off = 0;
+        for (int d = 0; d < nx; d++) off = off * P.x_shape[d] + (int64_t)xid[d];
+        const T* src = y + row * inner;
+        for (int64_t i = lane; i < inner; i += 32) atomic_apply<T>(x + off + i, src[i], op);
+    }
+}
+
 // ---- injective affine map: x[A.i + c] = op(init, y[i]) with plain stores -----------------------------
 // One thread takes 4 consecutive y elements (one 128-bit load for 4-byte types), advances the loop
 // coordinates like an odometer and pairs neighbouring x offsets into 8/16-byte stores.
@@ -512,6 +536,14 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         return 0;
     }
     const bool small = n < (1LL << 31) && bins < (1LL << 31);
+    if (P.inner_dims > 0 && P.inner_elems * (int64_t)sizeof(T) >= 64) {
+        const int64_t rows = n / P.inner_elems;
+        const unsigned rgrid = grid_for(rows * 32, 256);
+        if (small) rr_rows_kernel<T, int32_t><<<rgrid, 256, 0, st>>>(yp, xp, P, rows, P.inner_elems, op);
+        else       rr_rows_kernel<T, int64_t><<<rgrid, 256, 0, st>>>(yp, xp, P, rows, P.inner_elems, op);
+        B200JT_LAUNCH_CHECK();
+        return 0;
+    }
     const unsigned grid = grid_for(n, 256);
     if (small) rr_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>(yp, xp, P, n, op);
     else       rr_generic_kernel<T, int64_t><<<grid, 256, 0, st>>>(yp, xp, P, n, op);
@@ -601,9 +633,15 @@ extern "C" int b200jt_setitem(const b200jt_tensor* x, const b200jt_tensor* data,
     if (n == 0) return 0;
     const bool small = n < (1LL << 31) && bins < (1LL << 31);
     const unsigned grid = grid_for(n, 256);
+    const bool by_rows = P.inner_dims > 0 && P.inner_elems * dtype_size(out->dtype) >= 64;
+    const int64_t rows = by_rows ? n / P.inner_elems : 0;
+    const unsigned rgrid = grid_for(rows * 32, 256);
 #define B200JT_SETITEM(T)                                                                                        \
-    do { if (small) rr_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, n, opc);  \
-         else       rr_generic_kernel<T, int64_t><<<grid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, n, opc);  \
+    do { if (by_rows) {                                                                                          \
+             if (small) rr_rows_kernel<T, int32_t><<<rgrid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, rows, P.inner_elems, opc); \
+             else       rr_rows_kernel<T, int64_t><<<rgrid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, rows, P.inner_elems, opc); \
+         } else if (small) rr_generic_kernel<T, int32_t><<<grid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, n, opc);  \
+         else              rr_generic_kernel<T, int64_t><<<grid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, n, opc);  \
     } while (0)
     switch (out->dtype) {
         case B200JT_BOOL: case B200JT_UINT8: B200JT_SETITEM(uint8_t); break;

@@ -1,0 +1,150 @@
+"""GPU parity of the callers either side of the path at sizes beyond the fixtures: slicing / scatter / gather against
+the numpy oracle and against independent torch formulations, pooling forward / backward against the oracle, grouped and
+transposed convolution against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def jt():
+    import jittor_b200
+    return jittor_b200
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from oracle import meta_ops_ref
+    return meta_ops_ref
+
+
+def test_getitem_rows_large(jt):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1 << 16, 48, generator=g)
+    idx = torch.randint(-(1 << 16), 1 << 16, (100_000,), generator=g, dtype=torch.int32)      # negatives wrap once
+    got = jt.array(table)[jt.array(idx)].torch().cpu()
+    assert torch.equal(got, table[idx.long()])
+
+
+def test_getitem_mixed_matches_oracle(jt, ref):
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(37, 29, 41)).astype(np.float32)
+    a = rng.integers(0, 29, size=(5, 1)).astype(np.int32)
+    b = rng.integers(0, 41, size=(7,)).astype(np.int64)
+    sl = (slice(30, 2, -3), a, b)
+    want = ref.getitem(x, sl)
+    got = jt.array(x)[slice(30, 2, -3), jt.array(a), jt.array(b)].numpy()
+    assert np.array_equal(got, want)
+
+
+def test_setitem_add_duplicates_int_exact(jt):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randint(0, 10, (5000, 16), generator=g, dtype=torch.int32)
+    idx = torch.randint(0, 5000, (200_000,), generator=g, dtype=torch.int32)
+    v = torch.randint(0, 10, (200_000, 16), generator=g, dtype=torch.int32)
+    got = jt.array(x).setitem((jt.array(idx),), jt.array(v), "add").torch().cpu()
+    want = x.clone().index_add_(0, idx.long(), v)
+    assert torch.equal(got, want)
+
+
+def test_setitem_python_syntax_rebinds(jt):
+    x = jt.array(np.zeros((4, 6), np.float32))
+    x[1:3, ::2] = 5.0
+    want = np.zeros((4, 6), np.float32)
+    want[1:3, ::2] = 5.0
+    assert np.array_equal(x.numpy(), want)
+    x[jt.array(np.array([0, 3], np.int32))] = jt.array(np.arange(12, dtype=np.float32).reshape(2, 6))
+    want[[0, 3]] = np.arange(12, dtype=np.float32).reshape(2, 6)
+    assert np.array_equal(x.numpy(), want)
+
+
+def test_scatter_gather_roundtrip(jt):
+    g = torch.Generator().manual_seed(3)
+    perm = torch.stack([torch.randperm(300, generator=g) for _ in range(64)]).to(torch.int32)
+    src = torch.randn(64, 300, generator=g)
+    out = jt.array(torch.zeros(64, 300)).scatter(1, jt.array(perm), jt.array(src))
+    back = out.gather(1, jt.array(perm)).torch().cpu()
+    assert torch.equal(back, src)
+    assert torch.equal(out.torch().cpu(), torch.zeros(64, 300).scatter_(1, perm.long(), src))
+
+
+@pytest.mark.parametrize("op,k,s,p,ceil,cip", [("maximum", 3, 2, 1, False, True), ("minimum", 2, 2, 0, False, True),
+                                               ("mean", 3, 2, 1, True, False), ("mean", 3, 1, 1, False, True),
+                                               ("maximum", (2, 3), (1, 2), (0, 1), True, True)])
+def test_pool_matches_oracle(jt, ref, op, k, s, p, ceil, cip):
+    from jittor_b200 import pool
+    rng = np.random.default_rng(4)
+    x = np.round(rng.normal(size=(3, 5, 33, 30)) * 2).astype(np.float32) / 2        # coarse values: ties are frequent
+    layer = pool.Pool(k, s, p, ceil_mode=ceil, count_include_pad=cip, op=op)
+    vx = jt.array(x)
+    y = layer(vx)
+    want = ref.pool2d(x, k, op, s, p, ceil, cip)
+    assert np.allclose(y.numpy(), want, rtol=1e-6, atol=1e-6)
+    dy = rng.normal(size=want.shape).astype(np.float32)
+    dx = jt.grad((y * jt.array(dy)).sum(), vx).numpy()
+    wdx = ref.pool2d_backward(x, dy, k, op, s, p, ceil, cip)
+    assert np.allclose(dx, wdx, rtol=1e-5, atol=1e-5)
+
+
+def test_pool_return_indices_and_bf16(jt, ref):
+    from jittor_b200 import pool
+    rng = np.random.default_rng(5)
+    x = rng.normal(size=(2, 4, 17, 19)).astype(np.float32)
+    y, idx = pool.max_pool2d(jt.array(x), 3, 2, 1, return_indices=True)
+    wy, widx = ref.pool2d(x, 3, "maximum", 2, 1, return_indices=True)
+    assert np.array_equal(y.numpy(), wy) and np.array_equal(idx.numpy(), widx)
+    xb = torch.from_numpy(x).bfloat16()
+    yb = pool.max_pool2d(jt.array(xb), 3, 2, 1).torch().float().cpu().numpy()
+    assert np.array_equal(yb, ref.pool2d(xb.float().numpy(), 3, "maximum", 2, 1))
+
+
+def test_grouped_and_transposed_conv_match_oracle(jt, ref):
+    from jittor_b200 import nn
+    rng = np.random.default_rng(6)
+    x = rng.normal(size=(3, 32, 20, 23)).astype(np.float32)
+    w = (rng.normal(size=(64, 4, 3, 3)) * 0.1).astype(np.float32)
+    got = nn.conv2d(jt.array(x), jt.array(w), None, 2, 1, 1, groups=8).numpy()
+    want = ref.conv2d_grouped(x, w, 2, 1, 1, 8)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    wd = (rng.normal(size=(32, 1, 3, 3)) * 0.3).astype(np.float32)                    # depthwise
+    got = nn.conv2d(jt.array(x), jt.array(wd), None, 1, 1, 1, groups=32).numpy()
+    want = ref.conv2d_grouped(x, wd, 1, 1, 1, 32)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    wt = (rng.normal(size=(32, 12, 4, 4)) * 0.1).astype(np.float32)
+    got = nn.conv_transpose2d(jt.array(x), jt.array(wt), None, 2, 1, 1).numpy()
+    want = ref.conv_transpose2d(x, wt, 2, 1, 1)
+    assert got.shape == want.shape
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    wtg = (rng.normal(size=(32, 3, 3, 3)) * 0.1).astype(np.float32)                   # 4 groups, 32 -> 12 channels
+    got = nn.conv_transpose2d(jt.array(x), jt.array(wtg), None, (2, 1), (1, 0), 0, groups=4, dilation=(1, 2)).numpy()
+    want = ref.conv_transpose2d(x, wtg, (2, 1), (1, 0), 0, 4, (1, 2))
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+
+
+def test_optimizer_accumulates_and_matches_torch(jt):
+    from jittor_b200 import nn, optim
+    g = torch.Generator().manual_seed(7)
+    x, y = torch.randn(64, 10, generator=g), torch.randn(64, 3, generator=g)
+    w0 = torch.randn(10, 3, generator=g)
+    w = jt.array(w0.clone())
+    opt = optim.SGD([w], lr=0.05, momentum=0.9, weight_decay=0.01, nesterov=True)
+    tw = w0.clone().cuda().requires_grad_()
+    topt = torch.optim.SGD([tw], lr=0.05, momentum=0.9, weight_decay=0.01, nesterov=True)
+    for _ in range(5):
+        d = nn.matmul(jt.array(x), w) - jt.array(y)
+        opt.step((d * d).sum() * (1.0 / 64))
+        topt.zero_grad()
+        (((x.cuda() @ tw - y.cuda()) ** 2).sum() / 64).backward()
+        topt.step()
+    assert torch.allclose(w.torch(), tw.detach(), rtol=1e-4, atol=1e-5)
+    # backward twice, then one step: the gradients add up (python/jittor/optim.py:205-219)
+    w2 = jt.array(w0.clone())
+    opt2 = optim.SGD([w2], lr=0.1)
+    for _ in range(2):
+        d = nn.matmul(jt.array(x), w2) - jt.array(y)
+        opt2.backward((d * d).sum() * (1.0 / 64))
+    opt2.step()
+    gr = (2.0 / 64) * x.T @ (x @ w0 - y)
+    assert torch.allclose(w2.torch().cpu(), w0 - 0.1 * 2 * gr, rtol=1e-4, atol=1e-5)
