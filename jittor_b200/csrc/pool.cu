@@ -54,6 +54,38 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
     for (int64_t nc = blockIdx.z; nc < planes; nc += gridDim.z) {
         const T* xp = x + nc * (int64_t)g.H * g.W;
         const int64_t o = (nc * g.OH + oh) * g.OW + ow;
+        if (KS != 0) {
+            // compile-time window: all loads are issued before the first use (a rolled loop would wait for every
+            // element in turn), out-of-range taps are predicated off
+            constexpr int KH = KS == 1 ? 2 : 3, KW = KH;
+            const int pb = oh * Wn::sh(g) - g.ph, qb = ow * Wn::sw(g) - g.pw;
+            A vals[KH * KW];
+            bool ok[KH * KW];
+#pragma unroll
+            for (int a = 0; a < KH; a++)
+#pragma unroll
+                for (int b = 0; b < KW; b++) {
+                    const int p = pb + a, q = qb + b;
+                    ok[a * KW + b] = (unsigned)p < (unsigned)g.H && (unsigned)q < (unsigned)g.W;
+                    vals[a * KW + b] = ok[a * KW + b] ? ld<T>(xp + (int64_t)p * g.W + q) : (A)0;
+                }
+            if (OP == 2) {
+                A acc = 0;
+#pragma unroll
+                for (int t = 0; t < KH * KW; t++) acc += vals[t];
+                const int count = g.count_include_pad ? KH * KW : (p1 - p0) * (q1 - q0);
+                y[o] = cvt<T, A>(acc / (A)count);
+            } else {
+                A best = ld<T>(&init);
+                int where = -1;
+#pragma unroll
+                for (int t = 0; t < KH * KW; t++)
+                    if (ok[t] && (OP == 0 ? best < vals[t] : vals[t] < best)) { best = vals[t]; where = (pb + t / KW) * g.W + qb + t % KW; }
+                y[o] = cvt<T, A>(best);
+                if (indices) indices[o] = where;
+            }
+            continue;
+        }
         if (OP == 2) {
             A acc = 0;
             for (int p = p0; p < p1; p++)
@@ -93,6 +125,47 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ x, 
         const T* dp = dy + nc * (int64_t)g.OH * g.OW;
         const A mine = ld<T>(xp + (int64_t)p * g.W + q);
         A acc = 0;
+        if (KS != 0) {
+            // at most NW x NW windows contain this element; their pooled values and gradients are fetched up front
+            constexpr int NW = KS == 1 ? 1 : KS == 2 ? 2 : 3;
+            A yv[NW * NW], dv[NW * NW];
+            bool in[NW * NW];
+#pragma unroll
+            for (int a = 0; a < NW; a++)
+#pragma unroll
+                for (int b = 0; b < NW; b++) {
+                    const int oh = oh_lo + a, ow = ow_lo + b;
+                    in[a * NW + b] = oh <= oh_hi && ow <= ow_hi;
+                    const int64_t o = (int64_t)oh * g.OW + ow;
+                    yv[a * NW + b] = in[a * NW + b] && OP != 2 ? ld<T>(yp + o) : (A)0;
+                    dv[a * NW + b] = in[a * NW + b] ? ld<T>(dp + o) : (A)0;
+                }
+#pragma unroll
+            for (int a = 0; a < NW; a++)
+#pragma unroll
+                for (int b = 0; b < NW; b++) {
+                    if (!in[a * NW + b]) continue;
+                    const int oh = oh_lo + a, ow = ow_lo + b;
+                    int p0 = oh * sh - g.ph, q0 = ow * sw - g.pw;
+                    const int p1 = min(p0 + kh, g.H), q1 = min(q0 + kw, g.W);
+                    p0 = max(p0, 0); q0 = max(q0, 0);
+                    if (OP == 2) {
+                        const int count = g.count_include_pad ? kh * kw : (p1 - p0) * (q1 - q0);
+                        acc += dv[a * NW + b] / (A)count;
+                    } else {
+                        if (!(mine == yv[a * NW + b])) continue;
+                        bool first = true;
+                        for (int pp = p0; pp <= p && first; pp++) {
+                            const int qe = pp == p ? q : q1;
+                            for (int qq = q0; qq < qe; qq++)
+                                if (ld<T>(xp + (int64_t)pp * g.W + qq) == mine) { first = false; break; }
+                        }
+                        if (first) acc += dv[a * NW + b];
+                    }
+                }
+            dx[(nc * g.H + p) * (int64_t)g.W + q] = cvt<T, A>(acc);
+            continue;
+        }
         for (int oh = oh_lo; oh <= oh_hi; oh++) {
             int p0 = oh * sh - g.ph;
             const int p1 = min(p0 + kh, g.H);

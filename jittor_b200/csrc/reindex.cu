@@ -175,8 +175,9 @@ reindex_generic_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_
 }
 
 // ---- row gather: the index program is evaluated once per run of `inner` consecutive elements ----------------------
-// (x[idx[i], :] style gathers: embedding look-ups, getitem with an index Var on a leading axis). One warp per run; all
-// lanes evaluate the program (same result, no exchange needed) and then copy the run, 16 bytes per lane when aligned.
+// (x[idx[i], :] style gathers: embedding look-ups, getitem with an index Var on a leading axis). A warp takes 32 runs
+// at a time: every lane interprets the program for ONE of them, then the offsets are passed around with shuffles and
+// the whole warp copies each run, 16 bytes per lane when aligned.
 template <typename T, typename I>
 __global__ void __launch_bounds__(256)
 reindex_rows_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_constant__ IndexProgram P,
@@ -185,29 +186,38 @@ reindex_rows_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_con
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     constexpr int V = 16 / sizeof(T);
-    for (int64_t row = warp; row < rows; row += nwarps) {
-        I iv[kMaxDims];
-        int64_t r = row;
-        for (int d = P.ndim_loop - 1; d >= nl; d--) iv[d] = 0;
-#pragma unroll 1
-        for (int d = nl - 1; d >= 0; d--) { int64_t s = P.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
-        I xid[kMaxDims];
-        const bool over = eval_index_program<I>(P, iv, xid);
-        int64_t off = 0;
-        for (int d = 0; d < nx; d++) off = off * P.x_shape[d] + (int64_t)xid[d];
-        const T* src = x + off;
-        T* dst = y + row * inner;
-        const bool vec = inner % V == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 &&
-                         (over || (reinterpret_cast<uintptr_t>(src) & 15) == 0);
-        if (vec) {
-            uint4 f;
-            T* fp = reinterpret_cast<T*>(&f);
+    const bool vec_shape = inner % V == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    uint4 f;
+    {
+        T* fp = reinterpret_cast<T*>(&f);
 #pragma unroll
-            for (int e = 0; e < V; e++) fp[e] = fill;
-            for (int64_t i = lane; i < inner / V; i += 32)
-                reinterpret_cast<uint4*>(dst)[i] = over ? f : reinterpret_cast<const uint4*>(src)[i];
-        } else {
-            for (int64_t i = lane; i < inner; i += 32) dst[i] = over ? fill : src[i];
+        for (int e = 0; e < V; e++) fp[e] = fill;
+    }
+    for (int64_t row0 = warp * 32; row0 < rows; row0 += nwarps * 32) {
+        const int64_t row = row0 + lane;
+        long long off = -1;                                   // -1: overflow (fill), else element offset of the run in x
+        if (row < rows) {
+            I iv[kMaxDims];
+            int64_t r = row;
+            for (int d = P.ndim_loop - 1; d >= nl; d--) iv[d] = 0;
+#pragma unroll 1
+            for (int d = nl - 1; d >= 0; d--) { int64_t s = P.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
+            I xid[kMaxDims];
+            if (!eval_index_program<I>(P, iv, xid)) {
+                off = 0;
+                for (int d = 0; d < nx; d++) off = off * P.x_shape[d] + (long long)xid[d];
+            }
+        }
+        const int active = (int)min((int64_t)32, rows - row0);
+        for (int k = 0; k < active; k++) {
+            const long long o = __shfl_sync(0xffffffffu, off, k);
+            T* dst = y + (row0 + k) * inner;
+            if (vec_shape && (o < 0 || o % V == 0)) {
+                const uint4* src = reinterpret_cast<const uint4*>(x + (o < 0 ? 0 : o));
+                for (int64_t i = lane; i < inner / V; i += 32) reinterpret_cast<uint4*>(dst)[i] = o < 0 ? f : src[i];
+            } else {
+                for (int64_t i = lane; i < inner; i += 32) dst[i] = o < 0 ? fill : x[o + i];
+            }
         }
     }
 }
@@ -344,7 +354,7 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
         } else launch_affine<T, 1>(xp, yp, A, n, fill, small, st);
     } else if (P.inner_dims > 0 && P.inner_elems * (int64_t)sizeof(T) >= 64 && numel(x) > 0) {
         const int64_t rows = n / P.inner_elems;
-        const unsigned grid = grid_for(rows * 32, 256);
+        const unsigned grid = grid_for(rows, 256);
         if (small) reindex_rows_kernel<T, int32_t><<<grid, 256, 0, st>>>(xp, yp, P, rows, P.inner_elems, fill);
         else       reindex_rows_kernel<T, int64_t><<<grid, 256, 0, st>>>(xp, yp, P, rows, P.inner_elems, fill);
     } else {

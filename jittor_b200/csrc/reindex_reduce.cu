@@ -48,7 +48,8 @@ rr_generic_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_const
 }
 
 // Row form of the generic kernel: the program is evaluated once per run of `inner` consecutive y elements, which land
-// on `inner` consecutive x elements (x[idx[i], :] op= y[i, :]); one warp per run.
+// on `inner` consecutive x elements (x[idx[i], :] op= y[i, :]). A warp takes 32 runs at a time: every lane interprets
+// the program for one of them, the offsets go round by shuffle and the whole warp applies each run.
 template <typename T, typename I>
 __global__ void __launch_bounds__(256)
 rr_rows_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant__ IndexProgram P,
@@ -56,18 +57,28 @@ rr_rows_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant
     const int nl = P.ndim_loop - P.inner_dims, nx = P.ndim_x;
     const int lane = threadIdx.x & 31;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    for (int64_t row = warp; row < rows; row += nwarps) {
-        I iv[kMaxDims];
-        int64_t r = row;
-        for (int d = P.ndim_loop - 1; d >= nl; d--) iv[d] = 0;
+    for (int64_t row0 = warp * 32; row0 < rows; row0 += nwarps * 32) {
+        const int64_t row = row0 + lane;
+        long long off = -1;                                   // -1: index outside x, the run is skipped
+        if (row < rows) {
+            I iv[kMaxDims];
+            int64_t r = row;
+            for (int d = P.ndim_loop - 1; d >= nl; d--) iv[d] = 0;
 #pragma unroll 1
-        for (int d = nl - 1; d >= 0; d--) { int64_t s = P.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
-        I xid[kMaxDims];
-        if (eval_index_program<I>(P, iv, xid)) continue;
-        int64_t off = 0;
-        for (int d = 0; d < nx; d++) off = off * P.x_shape[d] + (int64_t)xid[d];
-        const T* src = y + row * inner;
-        for (int64_t i = lane; i < inner; i += 32) atomic_apply<T>(x + off + i, src[i], op);
+            for (int d = nl - 1; d >= 0; d--) { int64_t s = P.loop_shape[d]; iv[d] = (I)(r % s); r /= s; }
+            I xid[kMaxDims];
+            if (!eval_index_program<I>(P, iv, xid)) {
+                off = 0;
+                for (int d = 0; d < nx; d++) off = off * P.x_shape[d] + (long long)xid[d];
+            }
+        }
+        const int active = (int)min((int64_t)32, rows - row0);
+        for (int k = 0; k < active; k++) {
+            const long long o = __shfl_sync(0xffffffffu, off, k);
+            if (o < 0) continue;
+            const T* src = y + (row0 + k) * inner;
+            for (int64_t i = lane; i < inner; i += 32) atomic_apply<T>(x + o + i, src[i], op);
+        }
     }
 }
 
@@ -538,7 +549,7 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
     const bool small = n < (1LL << 31) && bins < (1LL << 31);
     if (P.inner_dims > 0 && P.inner_elems * (int64_t)sizeof(T) >= 64) {
         const int64_t rows = n / P.inner_elems;
-        const unsigned rgrid = grid_for(rows * 32, 256);
+        const unsigned rgrid = grid_for(rows, 256);
         if (small) rr_rows_kernel<T, int32_t><<<rgrid, 256, 0, st>>>(yp, xp, P, rows, P.inner_elems, op);
         else       rr_rows_kernel<T, int64_t><<<rgrid, 256, 0, st>>>(yp, xp, P, rows, P.inner_elems, op);
         B200JT_LAUNCH_CHECK();
@@ -635,7 +646,7 @@ extern "C" int b200jt_setitem(const b200jt_tensor* x, const b200jt_tensor* data,
     const unsigned grid = grid_for(n, 256);
     const bool by_rows = P.inner_dims > 0 && P.inner_elems * dtype_size(out->dtype) >= 64;
     const int64_t rows = by_rows ? n / P.inner_elems : 0;
-    const unsigned rgrid = grid_for(rows * 32, 256);
+    const unsigned rgrid = grid_for(rows, 256);
 #define B200JT_SETITEM(T)                                                                                        \
     do { if (by_rows) {                                                                                          \
              if (small) rr_rows_kernel<T, int32_t><<<rgrid, 256, 0, st>>>((const T*)data->ptr, (T*)out->ptr, P, rows, P.inner_elems, opc); \
