@@ -181,6 +181,13 @@ int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_t
 int b200jt_conv2d_transpose(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                             int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups, void* stream);
 
+/* dw[o,c,kh,kw] = sum over (n,oh,ow) of dy[n,o,oh,ow] * x[n,c,oh*stride-pad+kh*dil, ...]: the weight gradient of conv2d
+ * (groups == 1), fp32 accumulation. Replaces the relay CudnnConvBackwardWOp(Var* x, Var* y, int kh, int kw, int strideh, ...),
+ * python/jittor/extern/cuda/cudnn/ops/cudnn_conv_backward_w_op.h:20, which ConvTuner selects for
+ * reduce.add(multiply(reindex(x), broadcast(dy))), python/jittor/src/opt/tuner/conv_tuner.cc:375-397. */
+int b200jt_conv2d_backward_w(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                             int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, void* stream);
+
 /* Per-channel sum(x) and sum(x*x) of x[N,C,H,W] into stats[2*C] (float32): the two reduce.mean of
  * BatchNorm.execute, python/jittor/nn.py:674-675, in one pass, unnormalised so that ranks can be
  * summed by an all-reduce (python/jittor/nn.py:676-678). */
@@ -195,14 +202,19 @@ int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, double count, co
  * y[n,c,oh,ow] = op over the window rows [oh*sh-ph, +kh) x columns [ow*sw-pw, +kw) of x[n,c], clipped to x. Replaces the
  * jt.code kernels of Pool.execute, python/jittor/pool.py:42-197 (forward body :54-81, backward body :82-95):
  * op "maximum" / "minimum" start from the op's init value; "mean" divides by kh*kw when count_include_pad, else by the
- * clipped window area. y's spatial shape selects floor or ceil mode (python/jittor/pool.py:46-53). indices (maximum
- * only, may be NULL) receives p*W+q of the first largest element, -1 for an empty window (:70-81).
+ * clipped window area. y's spatial shape selects floor or ceil mode (python/jittor/pool.py:46-53). indices (maximum /
+ * minimum, may be NULL) receives p*W+q of the first extreme element, -1 for an empty window (:70-81).
  * Backward: dx[n,c,p,q] = sum of dy over the windows in which x[n,c,p,q] is the FIRST element (row-major) equal to
  * y (maximum / minimum), or sum of dy/count over the windows containing it (mean). dtypes: float32/64, float16, bfloat16. */
 int b200jt_pool2d(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indices, const char* op,
                   int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream);
 int b200jt_pool2d_backward(const b200jt_tensor* x, const b200jt_tensor* y, const b200jt_tensor* dy, const b200jt_tensor* dx,
                            const char* op, int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream);
+/* The same gradient for maximum / minimum from the index map the forward produced (x and y only give the geometry, they
+ * are not read): element (p, q) receives dy of every window whose index is p*W+q. Identical results, less traffic. */
+int b200jt_pool2d_backward_indices(const b200jt_tensor* x, const b200jt_tensor* y, const int32_t* indices,
+                                   const b200jt_tensor* dy, const b200jt_tensor* dx,
+                                   int kh, int kw, int sh, int sw, int ph, int pw, void* stream);
 
 /* ---- all-reduce over NVLink peer mappings --------------------------------------------------------
  * y = op over the ranks of x, one kernel per rank that reads and writes the other ranks' memory directly: replaces

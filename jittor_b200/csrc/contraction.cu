@@ -124,3 +124,13 @@ extern "C" int b200jt_conv2d_transpose(const b200jt_tensor* x, const b200jt_tens
     if (numel(y) == 0) return 0;
     return conv2d_transpose_simt(x->ptr, w->ptr, y->ptr, x->dtype, s, (cudaStream_t)stream);
 }
+
+extern "C" int b200jt_conv2d_backward_w(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                        int sh, int sw, int ph, int pw, int dh, int dw_, void* stream) {
+    ConvShape s;
+    int rc = conv_shape(x, dw, dy, sh, sw, ph, pw, dh, dw_, 1, &s);        // same shape relations as the forward conv
+    if (rc) return rc;
+    if (numel(dw) == 0) return 0;
+    if (numel(dy) == 0) return fail(-1, "b200jt_conv2d_backward_w: empty dy");
+    return conv2d_backward_w_simt(x->ptr, dy->ptr, dw->ptr, x->dtype, s, (cudaStream_t)stream);
+}

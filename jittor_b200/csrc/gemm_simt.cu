@@ -93,6 +93,32 @@ struct ConvTLoader {
     __device__ __forceinline__ int64_t c_group(int g) const { return (int64_t)g * Co * ((int64_t)OH * OW); }
 };
 
+// Weight gradient of the convolution: dw[o,c,kh,kw] = sum over (n,oh,ow) of dy[n,o,oh,ow] * x[n,c,oh*sh-ph+kh*dh,ow*sw-pw+kw*dw]
+// (the reduce over [0,3,4] of reindex(x) * broadcast(dy) that the reduce / broadcast gradient rules produce).
+// M = Cout, N = Cin*KH*KW, K = batch*OH*OW, accumulated in ascending k.
+struct ConvWgradLoader {
+    int Ci, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+    struct Row { int64_t off; };
+    __device__ __forceinline__ Row row(int64_t m) const { return Row{m * (int64_t)OH * OW}; }
+    template <typename T> __device__ __forceinline__ float A(const T* dy, const Row& r, int64_t k) const {
+        const int64_t pix = k % ((int64_t)OH * OW), n = k / ((int64_t)OH * OW);
+        return to_f<T>(dy[n * Co * (int64_t)OH * OW + r.off + pix]);
+    }
+    template <typename T> __device__ __forceinline__ float B(const T* x, int64_t k, int64_t n2) const {
+        const int ow = (int)(k % OW); const int64_t t = k / OW;
+        const int oh = (int)(t % OH); const int64_t img = t / OH;
+        const int kw = (int)(n2 % KW); const int t2 = (int)(n2 / KW);
+        const int kh = t2 % KH; const int c = t2 / KH;
+        const int ih = oh * sh - ph + kh * dh, iw = ow * sw - pw + kw * dw;
+        if (ih < 0 || ih >= H || iw < 0 || iw >= W) return 0.f;
+        return to_f<T>(x[((img * Ci + c) * H + ih) * (int64_t)W + iw]);
+    }
+    __device__ __forceinline__ int64_t C(int64_t m, int64_t n2) const { return m * ((int64_t)Ci * KH * KW) + n2; }
+    __device__ __forceinline__ int64_t a_group(int) const { return 0; }
+    __device__ __forceinline__ int64_t b_group(int) const { return 0; }
+    __device__ __forceinline__ int64_t c_group(int) const { return 0; }
+};
+
 // TM x TN output tile per CTA of 256 threads (16 x 16), (TM/16) x (TN/16) outputs per thread.
 template <typename T, typename L, int TM, int TN>
 __global__ void __launch_bounds__(256)
@@ -195,6 +221,16 @@ int conv2d_transpose_simt(const void* x, const void* w, void* y, int dtype, cons
     const int64_t M = (int64_t)s.N * s.OH * s.OW, N = s.Co / G, K = (int64_t)(s.C / G) * s.KH * s.KW;
     if (dtype == B200JT_FLOAT32) launch_simt<float, ConvTLoader>(x, w, y, M, N, K, L, st, G);
     else launch_simt<__nv_bfloat16, ConvTLoader>(x, w, y, M, N, K, L, st, G);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+// dw = wgrad(x, dy); s describes the forward convolution (C = in channels, Co = out channels, OH/OW = dy's extent).
+int conv2d_backward_w_simt(const void* x, const void* dy, void* dw, int dtype, const ConvShape& s, cudaStream_t st) {
+    ConvWgradLoader L{s.C, s.H, s.W, s.Co, s.KH, s.KW, s.OH, s.OW, s.sh, s.sw, s.ph, s.pw, s.dh, s.dw};
+    const int64_t M = s.Co, N = (int64_t)s.C * s.KH * s.KW, K = (int64_t)s.N * s.OH * s.OW;
+    if (dtype == B200JT_FLOAT32) launch_simt<float, ConvWgradLoader>(dy, x, dw, M, N, K, L, st);
+    else launch_simt<__nv_bfloat16, ConvWgradLoader>(dy, x, dw, M, N, K, L, st);
     B200JT_LAUNCH_CHECK();
     return 0;
 }

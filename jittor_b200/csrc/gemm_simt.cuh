@@ -26,6 +26,7 @@ int tcconv_status_fetch_and_clear();
 int peer_status_fetch_and_clear();          // peer_allreduce.cu
 
 int conv2d_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
+int conv2d_backward_w_simt(const void* x, const void* dy, void* dw, int dtype, const ConvShape& s, cudaStream_t st);
 int conv2d_transpose_simt(const void* x, const void* w, void* y, int dtype, const ConvShape& s, cudaStream_t st);
 
 }  // namespace b200jt

@@ -55,35 +55,47 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
         const T* xp = x + nc * (int64_t)g.H * g.W;
         const int64_t o = (nc * g.OH + oh) * g.OW + ow;
         if (KS != 0) {
-            // compile-time window: all loads are issued before the first use (a rolled loop would wait for every
-            // element in turn), out-of-range taps are predicated off
-            constexpr int KH = KS == 1 ? 2 : 3, KW = KH;
+            // compile-time window: all loads of PL planes are issued before the first use (a rolled loop would wait
+            // for every element in turn; one plane alone leaves too few bytes in flight), out-of-range taps predicated
+            constexpr int KH = KS == 1 ? 2 : 3, KW = KH, PL = 4;
             const int pb = oh * Wn::sh(g) - g.ph, qb = ow * Wn::sw(g) - g.pw;
-            A vals[KH * KW];
+            A vals[PL][KH * KW];
             bool ok[KH * KW];
 #pragma unroll
             for (int a = 0; a < KH; a++)
 #pragma unroll
-                for (int b = 0; b < KW; b++) {
-                    const int p = pb + a, q = qb + b;
-                    ok[a * KW + b] = (unsigned)p < (unsigned)g.H && (unsigned)q < (unsigned)g.W;
-                    vals[a * KW + b] = ok[a * KW + b] ? ld<T>(xp + (int64_t)p * g.W + q) : (A)0;
-                }
-            if (OP == 2) {
-                A acc = 0;
+                for (int b = 0; b < KW; b++)
+                    ok[a * KW + b] = (unsigned)(pb + a) < (unsigned)g.H && (unsigned)(qb + b) < (unsigned)g.W;
 #pragma unroll
-                for (int t = 0; t < KH * KW; t++) acc += vals[t];
-                const int count = g.count_include_pad ? KH * KW : (p1 - p0) * (q1 - q0);
-                y[o] = cvt<T, A>(acc / (A)count);
-            } else {
-                A best = ld<T>(&init);
-                int where = -1;
+            for (int u = 0; u < PL; u++) {
+                const int64_t pl = nc + (int64_t)u * gridDim.z;
+                const T* xu = x + pl * (int64_t)g.H * g.W;
 #pragma unroll
                 for (int t = 0; t < KH * KW; t++)
-                    if (ok[t] && (OP == 0 ? best < vals[t] : vals[t] < best)) { best = vals[t]; where = (pb + t / KW) * g.W + qb + t % KW; }
-                y[o] = cvt<T, A>(best);
-                if (indices) indices[o] = where;
+                    vals[u][t] = (ok[t] && pl < planes) ? ld<T>(xu + (int64_t)(pb + t / KW) * g.W + qb + t % KW) : (A)0;
             }
+#pragma unroll
+            for (int u = 0; u < PL; u++) {
+                const int64_t pl = nc + (int64_t)u * gridDim.z;
+                if (pl >= planes) break;
+                const int64_t ou = (pl * g.OH + oh) * g.OW + ow;
+                if (OP == 2) {
+                    A acc = 0;
+#pragma unroll
+                    for (int t = 0; t < KH * KW; t++) acc += vals[u][t];
+                    const int count = g.count_include_pad ? KH * KW : (p1 - p0) * (q1 - q0);
+                    y[ou] = cvt<T, A>(acc / (A)count);
+                } else {
+                    A best = ld<T>(&init);
+                    int where = -1;
+#pragma unroll
+                    for (int t = 0; t < KH * KW; t++)
+                        if (ok[t] && (OP == 0 ? best < vals[u][t] : vals[u][t] < best)) { best = vals[u][t]; where = (pb + t / KW) * g.W + qb + t % KW; }
+                    y[ou] = cvt<T, A>(best);
+                    if (indices) indices[ou] = where;
+                }
+            }
+            nc += (int64_t)(PL - 1) * gridDim.z;
             continue;
         }
         if (OP == 2) {
@@ -196,6 +208,66 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(const T* __restrict__ x, 
     }
 }
 
+// Backward of maximum / minimum from the forward's index map: input element (p, q) receives dy of every window whose
+// recorded first extreme element it is. No comparison of values, no scan, and x is not read at all.
+template <typename T, int KS>
+__global__ void __launch_bounds__(256) pool_bwd_indices_kernel(const int32_t* __restrict__ idx, const T* __restrict__ dy,
+                                                               T* __restrict__ dx, Geo g) {
+    using A = typename AccOf<T>::type;
+    using Wn = Win<KS>;
+    const int q = blockIdx.x * 32 + threadIdx.x, p = blockIdx.y * 8 + threadIdx.y;
+    if (q >= g.W || p >= g.H) return;
+    const int kh = Wn::kh(g), kw = Wn::kw(g), sh = Wn::sh(g), sw = Wn::sw(g);
+    const int oh_lo = max(0, (p + g.ph - kh + sh) / sh), oh_hi = min(g.OH - 1, (p + g.ph) / sh);
+    const int ow_lo = max(0, (q + g.pw - kw + sw) / sw), ow_hi = min(g.OW - 1, (q + g.pw) / sw);
+    const int me = p * g.W + q;
+    const int64_t planes = (int64_t)g.N * g.C;
+    constexpr int PL = 4;
+    for (int64_t nc = blockIdx.z; nc < planes; nc += (int64_t)PL * gridDim.z) {
+        A acc[PL];
+#pragma unroll
+        for (int u = 0; u < PL; u++) acc[u] = 0;
+        if (KS != 0) {
+            constexpr int NW = KS == 1 ? 1 : KS == 2 ? 2 : 3;
+            int iv[PL][NW * NW];
+            A dv[PL][NW * NW];
+#pragma unroll
+            for (int u = 0; u < PL; u++) {
+                const int64_t pl = nc + (int64_t)u * gridDim.z;
+#pragma unroll
+                for (int a = 0; a < NW; a++)
+#pragma unroll
+                    for (int b = 0; b < NW; b++) {
+                        const int oh = oh_lo + a, ow = ow_lo + b;
+                        const bool in = oh <= oh_hi && ow <= ow_hi && pl < planes;
+                        const int64_t o = (pl * g.OH + oh) * g.OW + ow;
+                        iv[u][a * NW + b] = in ? idx[o] : -2;
+                        dv[u][a * NW + b] = in ? ld<T>(dy + o) : (A)0;
+                    }
+            }
+#pragma unroll
+            for (int u = 0; u < PL; u++)
+#pragma unroll
+                for (int t = 0; t < NW * NW; t++) if (iv[u][t] == me) acc[u] += dv[u][t];
+        } else {
+            for (int u = 0; u < PL; u++) {
+                const int64_t pl = nc + (int64_t)u * gridDim.z;
+                if (pl >= planes) break;
+                for (int oh = oh_lo; oh <= oh_hi; oh++)
+                    for (int ow = ow_lo; ow <= ow_hi; ow++) {
+                        const int64_t o = (pl * g.OH + oh) * g.OW + ow;
+                        if (idx[o] == me) acc[u] += ld<T>(dy + o);
+                    }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PL; u++) {
+            const int64_t pl = nc + (int64_t)u * gridDim.z;
+            if (pl < planes) dx[(pl * g.H + p) * (int64_t)g.W + q] = cvt<T, A>(acc[u]);
+        }
+    }
+}
+
 static int window_code(const Geo& g) {
     if (g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2) return 1;
     if (g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2) return 2;
@@ -253,6 +325,21 @@ static void launch_bwd(const T* xp, const T* yp, const T* dp, T* op, const Geo& 
 }
 
 template <typename T>
+static int run_bwd_indices(const int32_t* idx, const b200jt_tensor* dy, const b200jt_tensor* dx, const Geo& g, cudaStream_t st) {
+    if (numel(dx) == 0) return 0;
+    const dim3 grid = plane_grid(g.W, g.H, ((int64_t)g.N * g.C + 3) / 4), block(32, 8);
+    const T* dp = (const T*)dy->ptr; T* op = (T*)dx->ptr;
+    switch (window_code(g)) {
+        case 1: pool_bwd_indices_kernel<T, 1><<<grid, block, 0, st>>>(idx, dp, op, g); break;
+        case 2: pool_bwd_indices_kernel<T, 2><<<grid, block, 0, st>>>(idx, dp, op, g); break;
+        case 3: pool_bwd_indices_kernel<T, 3><<<grid, block, 0, st>>>(idx, dp, op, g); break;
+        default: pool_bwd_indices_kernel<T, 0><<<grid, block, 0, st>>>(idx, dp, op, g);
+    }
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
 static int run_fwd(const b200jt_tensor* x, const b200jt_tensor* y, int32_t* indices, const Geo& g, int opc, cudaStream_t st) {
     if (numel(y) == 0) return 0;
     const T* xp = (const T*)x->ptr; T* yp = (T*)y->ptr;
@@ -284,7 +371,7 @@ extern "C" int b200jt_pool2d(const b200jt_tensor* x, const b200jt_tensor* y, int
                              int kh, int kw, int sh, int sw, int ph, int pw, int count_include_pad, void* stream) {
     pool::Geo g; int opc;
     if (int rc = pool::parse(x, y, op, kh, kw, sh, sw, ph, pw, count_include_pad, &g, &opc)) return rc;
-    B200JT_CHECK_ARG(!indices || opc == 0, "indices are only produced for maximum");
+    B200JT_CHECK_ARG(!indices || opc != 2, "indices are only produced for maximum and minimum");
     cudaStream_t st = (cudaStream_t)stream;
     switch (x->dtype) {
         case B200JT_FLOAT32: return pool::run_fwd<float>(x, y, indices, g, opc, st);
@@ -312,4 +399,25 @@ extern "C" int b200jt_pool2d_backward(const b200jt_tensor* x, const b200jt_tenso
         case B200JT_FLOAT16: return pool::run_bwd<__half>(x, y, dy, dx, g, opc, st);
     }
     return fail(-1, "b200jt_pool2d_backward: dtype must be float32, float64, float16 or bfloat16");
+}
+
+extern "C" int b200jt_pool2d_backward_indices(const b200jt_tensor* x, const b200jt_tensor* y, const int32_t* indices,
+                                              const b200jt_tensor* dy, const b200jt_tensor* dx,
+                                              int kh, int kw, int sh, int sw, int ph, int pw, void* stream) {
+    pool::Geo g; int opc;
+    if (int rc = pool::parse(x, y, "maximum", kh, kw, sh, sw, ph, pw, 1, &g, &opc)) return rc;
+    B200JT_CHECK_ARG(indices != nullptr, "indices is null");
+    B200JT_CHECK_ARG(valid_tensor(dy) && valid_tensor(dx) && dy->ndim == 4 && dx->ndim == 4 &&
+                     dy->dtype == x->dtype && dx->dtype == x->dtype, "dy, dx must be NCHW tensors of x's dtype");
+    for (int d = 0; d < 4; d++)
+        B200JT_CHECK_ARG(dy->shape[d] == y->shape[d] && dx->shape[d] == x->shape[d], "dy must have y's shape and dx x's shape");
+    B200JT_CHECK_ARG((int64_t)g.H * g.W < (1LL << 31), "plane too large for int32 indices");
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x->dtype) {
+        case B200JT_FLOAT32: return pool::run_bwd_indices<float>(indices, dy, dx, g, st);
+        case B200JT_FLOAT64: return pool::run_bwd_indices<double>(indices, dy, dx, g, st);
+        case B200JT_BFLOAT16: return pool::run_bwd_indices<__nv_bfloat16>(indices, dy, dx, g, st);
+        case B200JT_FLOAT16: return pool::run_bwd_indices<__half>(indices, dy, dx, g, st);
+    }
+    return fail(-1, "b200jt_pool2d_backward_indices: dtype must be float32, float64, float16 or bfloat16");
 }

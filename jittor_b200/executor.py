@@ -291,24 +291,12 @@ def _mul_operands(v, rank):
     return v._op, a, b
 
 
-def conv_geometry(rx, ww):
-    """Checks that rx = reindex(x) and ww = broadcast_to(w) are the NCHW/OIHW conv lowering of
-    python/jittor/nn.py:1009-1016 and solves (sh, sw, ph, pw, dh, dw) from the index strings, as ConvTuner
-    does (python/jittor/src/opt/tuner/conv_tuner.cc:313-338). Returns (x, w, geometry) or None."""
-    if not (_node(rx, "reindex") and _node(ww, "broadcast_to")):
-        return None
-    a = rx._op.attrs
-    x, w = rx._op.inputs[0], ww._op.inputs[0]
-    if len(rx._op.inputs) != 1 or a["overflow_conditions"] or a["overflow_value"] != 0:
-        return None
-    if x.ndim != 4 or w.ndim != 4 or rx.ndim != 7:
-        return None
-    if ww._op.attrs["bcast_mask"] != 0b0011001 or ww._op.attrs["keepdims_mask"] != 0:
-        return None
-    N, Co, Ci, OH, OW, KH, KW = rx.shape
-    if list(w.shape) != [Co, Ci, KH, KW] or x.shape[0] != N or x.shape[1] != Ci:
-        return None
-    aff = index_affine(list(rx.shape), list(x.shape), a["indexes"])
+def _conv_index_geometry(loop_shape, x_shape, indexes):
+    """Solves (sh, sw, ph, pw, dh, dw) from the four index strings of the conv lowering over the 7-D loop nest
+    [N, Co, Ci, OH, OW, KH, KW] (python/jittor/nn.py:1009-1014), as ConvTuner does with expr::match
+    (python/jittor/src/opt/tuner/conv_tuner.cc:313-338). None if the strings are not that lowering."""
+    N, Co, Ci, OH, OW, KH, KW = loop_shape
+    aff = index_affine(list(loop_shape), list(x_shape), indexes)
     if aff is None:
         return None
     coef, c0 = aff
@@ -332,10 +320,110 @@ def conv_geometry(rx, ww):
         sw = max(sw, 1)
     if min(sh, sw, dh, dw) < 1 or ph < 0 or pw < 0:
         return None
-    H, W = x.shape[2], x.shape[3]
+    H, W = x_shape[2], x_shape[3]
     if OH != (H + 2 * ph - KH * dh + dh - 1) // sh + 1 or OW != (W + 2 * pw - KW * dw + dw - 1) // sw + 1:
         return None
-    return x, w, (sh, sw, ph, pw, dh, dw)
+    return (sh, sw, ph, pw, dh, dw)
+
+
+_MASK_W, _MASK_Y = 0b0011001, 0b1100100     # axes a weight / an output gradient is broadcast over in the 7-D nest
+
+
+def _bcast_of(v, mask, shape4):
+    """v = broadcast_to(u) over exactly the axes of `mask` with u of shape `shape4`: returns u, else None."""
+    if not _node(v, "broadcast_to") or v._op.attrs["bcast_mask"] != mask or v._op.attrs["keepdims_mask"] != 0:
+        return None
+    u = v._op.inputs[0]
+    return u if list(u.shape) == list(shape4) else None
+
+
+def conv_geometry(rx, ww):
+    """Checks that rx = reindex(x) and ww = broadcast_to(w) are the NCHW/OIHW conv lowering of
+    python/jittor/nn.py:1009-1016. Returns (x, w, geometry) or None."""
+    if not (_node(rx, "reindex") and _node(ww, "broadcast_to")):
+        return None
+    a = rx._op.attrs
+    x = rx._op.inputs[0]
+    if len(rx._op.inputs) != 1 or a["overflow_conditions"] or a["overflow_value"] != 0:
+        return None
+    if x.ndim != 4 or rx.ndim != 7:
+        return None
+    N, Co, Ci, OH, OW, KH, KW = rx.shape
+    w = _bcast_of(ww, _MASK_W, [Co, Ci, KH, KW])
+    if w is None or x.shape[0] != N or x.shape[1] != Ci:
+        return None
+    geo = _conv_index_geometry(list(rx.shape), list(x.shape), a["indexes"])
+    return None if geo is None else (x, w, geo)
+
+
+def _match_conv_dgrad(v):
+    """dx = reindex_reduce.add(multiply(broadcast(w), broadcast(dy))) with the conv's index strings: what the reindex /
+    broadcast gradient rules make of a conv, and one of the forms ConvTuner relays (conv_tuner.cc:375-397, to
+    cudnn_conv_backward_x). Runs as a transposed convolution; stride-1 bf16 layers run on the tensor-core conv with
+    the weights flipped and transposed (a gather by the reindex kernel)."""
+    if not _node(v, "reindex_reduce", op="add") or v.ndim != 4:
+        return None
+    a = v._op.attrs
+    m = v._op.inputs[0]
+    if len(v._op.inputs) != 1 or a["overflow_conditions"] or not _node(m, "binary", op="multiply") or m.ndim != 7:
+        return None
+    N, Co, Ci, OH, OW, KH, KW = m.shape
+    p, q = m._op.inputs
+    w = _bcast_of(p, _MASK_W, [Co, Ci, KH, KW])
+    dy = _bcast_of(q, _MASK_Y, [N, Co, OH, OW])
+    if w is None or dy is None:
+        w, dy = _bcast_of(q, _MASK_W, [Co, Ci, KH, KW]), _bcast_of(p, _MASK_Y, [N, Co, OH, OW])
+    if w is None or dy is None or list(v.shape[:2]) != [N, Ci]:
+        return None
+    if dy.dtype not in ("float32", "bfloat16") or w.dtype not in ("float32", "bfloat16"):
+        return None
+    geo = _conv_index_geometry(list(m.shape), list(v.shape), a["indexes"])
+    if geo is None:
+        return None
+    sh, sw, ph, pw, dh, dw = geo
+    fp, fq = dh * (KH - 1) - ph, dw * (KW - 1) - pw
+    if sh == 1 and sw == 1 and fp >= 0 and fq >= 0 and dy.dtype == "bfloat16":
+        from . import var as V
+        wf = V.reindex(w, [Ci, Co, KH, KW], ["i1", "i0", f"{KH - 1}-i2", f"{KW - 1}-i3"])
+        return Plan([dy, wf], lambda: run_conv2d(dy, wf, (1, 1, fp, fq, dh, dw), v.dtype))
+    return Plan([dy, w], lambda: run_conv2d_transpose(dy, w, geo, 1, list(v.shape), v.dtype))
+
+
+def _match_conv_wgrad(v):
+    """dw = reduce.add over [0,3,4] of multiply(reindex(x), broadcast(dy)) (conv_tuner.cc:375-397, relayed there to
+    cudnn_conv_backward_w)."""
+    got = _mul_operands(v, 7)
+    if got is None:
+        return None
+    rop, p, q = got
+    if rop.attrs["reduce_mask"] != _MASK_W or rop.attrs["keepdims_mask"] != 0:
+        return None
+    rx, bd = (p, q) if _node(p, "reindex") else (q, p)
+    if not _node(rx, "reindex"):
+        return None
+    a = rx._op.attrs
+    x = rx._op.inputs[0]
+    if len(rx._op.inputs) != 1 or a["overflow_conditions"] or a["overflow_value"] != 0 or x.ndim != 4:
+        return None
+    N, Co, Ci, OH, OW, KH, KW = rx.shape
+    dy = _bcast_of(bd, _MASK_Y, [N, Co, OH, OW])
+    if dy is None or list(x.shape[:2]) != [N, Ci]:
+        return None
+    if x.dtype not in ("float32", "bfloat16") or dy.dtype not in ("float32", "bfloat16"):
+        return None
+    geo = _conv_index_geometry(list(rx.shape), list(x.shape), a["indexes"])
+    if geo is None:
+        return None
+
+    def run():
+        xd = x._data
+        dyd = _cast(dy._data, x.dtype)
+        out = _empty([Co, Ci, KH, KW], x.dtype)
+        C.check(C.lib.b200jt_conv2d_backward_w(C.desc(xd), C.desc(dyd), C.desc(out), *geo, C.stream_ptr()),
+                f"conv2d_backward_w x{list(x.shape)} dy{list(dy.shape)} geo{geo}")
+        return _cast(out, v.dtype)
+
+    return Plan([x, dy], run)
 
 
 def run_conv2d_transpose(x, w, geo, groups, out_shape, out_dtype):
@@ -762,4 +850,4 @@ def _match_batchnorm(v):
     return Plan(leaves, run)
 
 
-_MATCHERS = [_match_conv, _match_matmul, _match_batched_matmul, _match_softmax, _match_layernorm, _match_batchnorm]
+_MATCHERS = [_match_conv, _match_conv_dgrad, _match_conv_wgrad, _match_matmul, _match_batched_matmul, _match_softmax, _match_layernorm, _match_batchnorm]

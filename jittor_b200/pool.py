@@ -21,21 +21,33 @@ def _pair(v):
     return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
 
 
-def _run_pool(op, k, s, p, cip, oshape, want_indices):
+def _run_pool(op, k, s, p, cip, oshape, want_indices, keep=None):
+    """Forward relay. For maximum / minimum the index map is always written (one extra int32 per output); `keep`, a dict
+    shared with the backward relay, holds on to it so that the backward needs neither x nor a scan."""
+    with_idx = op != "mean"
+
     def run(xd):
         xd = xd.contiguous()
         y = torch.empty(oshape, dtype=xd.dtype, device=xd.device)
-        idx = torch.empty(oshape, dtype=torch.int32, device=xd.device) if want_indices else None
-        C.check(C.lib.b200jt_pool2d(C.desc(xd), C.desc(y), ctypes.c_void_p(idx.data_ptr() if want_indices else 0),
+        idx = torch.empty(oshape, dtype=torch.int32, device=xd.device) if with_idx else None
+        C.check(C.lib.b200jt_pool2d(C.desc(xd), C.desc(y), ctypes.c_void_p(idx.data_ptr() if with_idx else 0),
                                     op.encode(), k[0], k[1], s[0], s[1], p[0], p[1], int(cip), C.stream_ptr()), "pool2d")
+        if keep is not None and with_idx:
+            keep["idx"] = idx
         return idx if want_indices else y
     return run
 
 
-def _run_pool_bwd(op, k, s, p, cip, xshape, oshape):
+def _run_pool_bwd(op, k, s, p, cip, xshape, oshape, keep):
     def run(xd, yd, dyd):
         xd, yd, dyd = xd.view(xshape).contiguous(), yd.view(oshape).contiguous(), dyd.view(oshape).contiguous()
         dx = torch.empty_like(xd)
+        idx = keep.get("idx")
+        if idx is not None:
+            C.check(C.lib.b200jt_pool2d_backward_indices(C.desc(xd), C.desc(yd), ctypes.c_void_p(idx.data_ptr()), C.desc(dyd),
+                                                         C.desc(dx), k[0], k[1], s[0], s[1], p[0], p[1], C.stream_ptr()),
+                    "pool2d_backward_indices")
+            return dx
         C.check(C.lib.b200jt_pool2d_backward(C.desc(xd), C.desc(yd), C.desc(dyd), C.desc(dx), op.encode(),
                                              k[0], k[1], s[0], s[1], p[0], p[1], int(cip), C.stream_ptr()), "pool2d_backward")
         return dx
@@ -83,12 +95,13 @@ class Pool(Module):
                            ["i0", "i1", f"i2*{s[0]}-{p[0]}+i4", f"i3*{s[1]}-{p[1]}+i5"])
             return xx.reduce(self.op, [4, 5])
         oshape, xshape, op, cip = [N, Cn, h, w], list(x.shape), self.op, self.count_include_pad
+        keep = {}
 
         def grad_rule(out, dout, which):
-            node = V.Op("custom", [x, out, dout], fn=_run_pool_bwd(op, k, s, p, cip, xshape, oshape), name="pool2d_backward")
+            node = V.Op("custom", [x, out, dout], fn=_run_pool_bwd(op, k, s, p, cip, xshape, oshape, keep), name="pool2d_backward")
             return V.Var(xshape, x.dtype, node)
 
-        y = V.Var(oshape, x.dtype, V.Op("custom", [x], fn=_run_pool(op, k, s, p, cip, oshape, False), name="pool2d",
+        y = V.Var(oshape, x.dtype, V.Op("custom", [x], fn=_run_pool(op, k, s, p, cip, oshape, False, keep), name="pool2d",
                                          grad=grad_rule))
         if not self.return_indices:
             return y

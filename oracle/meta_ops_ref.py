@@ -981,3 +981,22 @@ def conv_transpose2d(x, w, stride=1, padding=0, output_padding=0, groups=1, dila
     if bias is not None:
         y = binary(y, broadcast(np.asarray(bias), y.shape, [0, 2, 3]), "add")
     return y
+
+
+def conv_grad(x, w, dy, stride, padding, dilation, want_dw):
+    """Gradient of sum(conv2d(x, w) * dy) w.r.t. x or w, composed from this file's meta-ops with the reference's rules:
+    reduce.add <-> broadcast (python/jittor/src/ops/reduce_op.cc:339-343, broadcast_to_op.cc:112-117) and
+    reindex <-> reindex_reduce.add (reindex_op.cc:76-80) applied to the lowering of python/jittor/nn.py:1009-1017."""
+    x, w, dy = np.asarray(x), np.asarray(w), np.asarray(dy)
+    n, c, h, wd = x.shape
+    co, _, kh, kw = w.shape
+    s, p, d = stride, padding, dilation
+    oh, ow = dy.shape[2], dy.shape[3]
+    shape7 = [n, co, c, oh, ow, kh, kw]
+    idx = ["i0", "i2", f"i3*{s}-{p}+i5*{d}", f"i4*{s}-{p}+i6*{d}"]
+    dm = broadcast(dy, shape7, [2, 5, 6])
+    if want_dw:
+        xx = reindex(x, shape7, idx)
+        return reduce(binary(xx, dm, "multiply"), "add", [0, 3, 4])
+    ww = broadcast(w, shape7, [0, 3, 4])
+    return reindex_reduce(binary(ww, dm, "multiply"), "add", list(x.shape), idx)

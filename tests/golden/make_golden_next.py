@@ -271,6 +271,26 @@ do_tconv("tconv_rect_kernel", f32(2, 3, 5, 7), wgt(3, 4, 2, 4), (2, 1), (0, 1), 
 do_tconv("tconv_g2_in_eq_out", f32(2, 6, 5, 5), wgt(6, 3, 3, 3), 2, 1, 1, 2, 1)
 do_tconv("tconv_g4_in_eq_out", f32(1, 8, 4, 6), wgt(8, 2, 4, 4), 2, 1, 0, 4, 1, f32(8))
 
+
+
+# ---- gradients of the reindex-lowered conv (data and weight) through jt.grad --------------------------------------
+def do_conv_grad(name, x, w, stride, padding, dilation):
+    m = nn.Conv(x.shape[1], w.shape[0], (w.shape[2], w.shape[3]), stride, padding, dilation, 1, False)
+    vx, vw = to_jt(x), to_jt(w)
+    m.weight = vw
+    y = m(vx)
+    dy = f32(*y.shape)
+    dx, dw = jt.grad((y * to_jt(dy)).sum(), [vx, vw])
+    args = dict(stride=stride, padding=padding, dilation=dilation)
+    case(name + "_dx", "conv_dgrad", args, [x, w, dy], to_np(dx))
+    case(name + "_dw", "conv_wgrad", args, [x, w, dy], to_np(dw))
+
+
+do_conv_grad("conv_grad_s1_p1", f32(2, 5, 9, 10), wgt(7, 5, 3, 3), 1, 1, 1)
+do_conv_grad("conv_grad_s2_p1", f32(2, 4, 11, 9), wgt(6, 4, 3, 3), 2, 1, 1)
+do_conv_grad("conv_grad_dilated", f32(1, 3, 12, 12), wgt(4, 3, 3, 3), 1, 2, 2)
+do_conv_grad("conv_grad_1x1_s2", f32(2, 8, 8, 8), wgt(5, 8, 1, 1), 2, 0, 1)
+
 np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
 with open(os.path.join(HERE, "next_ops.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_golden_next.py", "reference_version": jt.__version__, "cases": CASES},

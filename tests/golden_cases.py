@@ -130,6 +130,8 @@ def run_case(c, be):
     elif op == "conv_transpose":
         got = be.conv_transpose2d(ins[0], ins[1], _kw(a["stride"]), _kw(a["padding"]), _kw(a["output_padding"]),
                                   a["groups"], _kw(a["dilation"]), ins[2] if a["bias"] else None)
+    elif op in ("conv_dgrad", "conv_wgrad"):
+        got = be.conv_grad(ins[0], ins[1], ins[2], a["stride"], a["padding"], a["dilation"], op == "conv_wgrad")
     elif op == "optim":
         kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in a.items() if k not in ("kind", "steps")}
         got = be.optim_steps(ins[0], ins[1], ins[2], a["kind"], a["steps"], **kw)

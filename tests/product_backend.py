@@ -16,6 +16,12 @@ def _jt_slices(slices):
 
 class ProductBackend:
     @staticmethod
+    def conv_grad(x, w, dy, stride, padding, dilation, want_dw):
+        vx, vw = jt.array(x), jt.array(w)
+        y = nn.conv2d(vx, vw, None, stride, padding, dilation)
+        return _np(jt.grad((y * jt.array(dy)).sum(), vw if want_dw else vx))
+
+    @staticmethod
     def conv2d_grouped(x, w, stride, padding, dilation, groups, bias=None):
         return _np(nn.conv2d(jt.array(x), jt.array(w), None if bias is None else jt.array(bias), stride, padding,
                              dilation, groups))

@@ -148,3 +148,29 @@ def test_optimizer_accumulates_and_matches_torch(jt):
     opt2.step()
     gr = (2.0 / 64) * x.T @ (x @ w0 - y)
     assert torch.allclose(w2.torch().cpu(), w0 - 0.1 * 2 * gr, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype,stride,pad,dil", [("float32", 1, 1, 1), ("float32", 2, 1, 1), ("float32", 1, 2, 2),
+                                                  ("bfloat16", 1, 1, 1)])
+def test_conv_backward_matches_torch(jt, dtype, stride, pad, dil):
+    """jt.grad through the reindex-lowered conv: the executor recognises the data- and weight-gradient graphs and runs
+    them as transposed convolution / flipped-weight convolution and as the weight-gradient implicit GEMM."""
+    from jittor_b200 import executor, nn
+    g = torch.Generator().manual_seed(8)
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    C = 64 if dtype == "bfloat16" else 6
+    x = torch.randn(4, C, 18, 20, generator=g).to(td).cuda()
+    w = (torch.randn(C, C, 3, 3, generator=g) * 0.1).to(td).cuda()
+    vx, vw = jt.array(x), jt.array(w)
+    y = nn.conv2d(vx, vw, None, stride, pad, dil)
+    dy = torch.randn(*y.shape, generator=g).to(td).cuda()
+    dx, dw = jt.grad((y * jt.array(dy)).sum(), [vx, vw])
+    assert executor._match_conv_dgrad(dx) is not None
+    tx, tw = x.float().requires_grad_(), w.float().requires_grad_()
+    ty = torch.nn.functional.conv2d(tx, tw, None, stride, pad, dil)
+    (ty * dy.float()).sum().backward()
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    for got, want in ((dx.torch().float(), tx.grad), (dw.torch().float(), tw.grad)):
+        assert got.shape == want.shape
+        err = (got - want).abs().max().item()
+        assert err <= tol * want.abs().max().item() + 1e-6, (err, want.abs().max().item())
