@@ -261,6 +261,54 @@ reindex_permute_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_
     }
 }
 
+// 4-byte elements with every extent, stride and base a multiple of 4 elements: 64 x 64 tiles, 16-byte global accesses on
+// both sides (the 32 x 32 kernel moves 4 bytes per lane). Pitch 65 keeps the transposing shared-memory accesses at most
+// 2-way conflicted.
+__global__ void __launch_bounds__(256)
+reindex_permute_vec4_kernel(const uint32_t* __restrict__ x, uint32_t* __restrict__ y, const __grid_constant__ PermArgs P) {
+    __shared__ uint32_t tile[64][65];
+    const int c4 = threadIdx.x & 15, r0 = threadIdx.x >> 4;     // 16 vectors per 64-element row, 16 rows per pass
+    const int64_t tiles_a = (P.A + 63) / 64, tiles_b = (P.B + 63) / 64;
+    const int64_t total = tiles_a * tiles_b * P.batch;
+    for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const int64_t ta = t % tiles_a; int64_t r = t / tiles_a;
+        const int64_t tb = r % tiles_b; r /= tiles_b;
+        int64_t xb = 0, yb = 0;
+#pragma unroll 1
+        for (int d = P.nbatch_dims - 1; d >= 0; d--) { const int64_t i = r % P.bshape[d]; r /= P.bshape[d]; xb += i * P.bxstride[d]; yb += i * P.bystride[d]; }
+        const int64_t a0 = ta * 64, b0 = tb * 64;
+        uint4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int64_t b = b0 + r0 + k * 16, a = a0 + c4 * 4;
+            v[k] = (a < P.A && b < P.B) ? __ldcs(reinterpret_cast<const uint4*>(x + xb + b * P.x_sb + a)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            uint32_t* row = &tile[r0 + k * 16][c4 * 4];
+            row[0] = v[k].x; row[1] = v[k].y; row[2] = v[k].z; row[3] = v[k].w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int ar = r0 + k * 16;                         // output row = input column
+            const int64_t a = a0 + ar, b = b0 + c4 * 4;
+            if (a < P.A && b < P.B) {
+                uint4 o;
+                o.x = tile[c4 * 4 + 0][ar]; o.y = tile[c4 * 4 + 1][ar]; o.z = tile[c4 * 4 + 2][ar]; o.w = tile[c4 * 4 + 3][ar];
+                __stcs(reinterpret_cast<uint4*>(y + yb + a * P.y_sa + b), o);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+static bool perm_vec4_ok(const PermArgs& P, const void* x, const void* y) {
+    if (P.A % 4 || P.B % 4 || P.x_sb % 4 || P.y_sa % 4 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return false;
+    for (int d = 0; d < P.nbatch_dims; d++) if (P.bxstride[d] % 4 || P.bystride[d] % 4) return false;
+    return P.A >= 64 && P.B >= 64;
+}
+
 // Fills P if the program is a pure permutation whose contiguous axes differ; false otherwise.
 static bool make_perm_args(const IndexProgram& Q, PermArgs* P) {
     const int n = Q.ndim_loop;
@@ -327,6 +375,13 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
     T* yp = (T*)y->ptr;
     PermArgs PA;
     if (numel(x) > 0 && make_perm_args(P, &PA)) {
+        if (sizeof(T) == 4 && perm_vec4_ok(PA, xp, yp)) {
+            const int64_t total = ((PA.A + 63) / 64) * ((PA.B + 63) / 64) * PA.batch;
+            const unsigned grid = (unsigned)(total < (int64_t)kNumSMs * 16 ? total : (int64_t)kNumSMs * 16);
+            reindex_permute_vec4_kernel<<<grid, 256, 0, st>>>((const uint32_t*)xp, (uint32_t*)yp, PA);
+            B200JT_LAUNCH_CHECK();
+            return 0;
+        }
         const int64_t total = PA.tiles_a * PA.tiles_b * PA.batch;
         const unsigned grid = (unsigned)(total < (int64_t)kNumSMs * 32 ? total : (int64_t)kNumSMs * 32);
         reindex_permute_kernel<T><<<grid, 256, 0, st>>>(xp, yp, PA);
