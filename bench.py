@@ -440,7 +440,8 @@ class NextOps:
         n = int(np.prod(self.SHAPE)) * 4
         o = self.SHAPE[0] * self.SHAPE[1] * 56 * 56 * 4
         rows = self.PICK * self.COLS * 4
-        return {"maxpool-fwd": n + o, "maxpool-bwd": 2 * n + 2 * o, "getitem-rows": 2 * rows + self.PICK * 4,
+        # backward: index map + output gradient in, input gradient out (x and y are not read by the index-based kernel)
+        return {"maxpool-fwd": n + o, "maxpool-bwd": n + 2 * o, "getitem-rows": 2 * rows + self.PICK * 4,
                 "setitem-add-rows": 2 * self.ROWS * self.COLS * 4 + 2 * rows + self.PICK * 4}
 
     def setup(self, rank, world, jt, torch, multi):

@@ -87,12 +87,12 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(const T* __restrict__ x, 
                     y[ou] = cvt<T, A>(acc / (A)count);
                 } else {
                     A best = ld<T>(&init);
-                    int where = -1;
+                    int tap = -1;
 #pragma unroll
                     for (int t = 0; t < KH * KW; t++)
-                        if (ok[t] && (OP == 0 ? best < vals[u][t] : vals[u][t] < best)) { best = vals[u][t]; where = (pb + t / KW) * g.W + qb + t % KW; }
+                        if (ok[t] && (OP == 0 ? best < vals[u][t] : vals[u][t] < best)) { best = vals[u][t]; tap = t; }
                     y[ou] = cvt<T, A>(best);
-                    if (indices) indices[ou] = where;
+                    if (indices) indices[ou] = tap < 0 ? -1 : (pb + tap / KW) * g.W + qb + tap % KW;
                 }
             }
             nc += (int64_t)(PL - 1) * gridDim.z;
@@ -268,6 +268,132 @@ __global__ void __launch_bounds__(256) pool_bwd_indices_kernel(const int32_t* __
     }
 }
 
+// Backward from the index map for stride-2 windows of edge <= 3: a thread owns a 2 x 2 block of input elements. The
+// windows that can contain any of them form at most a 2 x 2 set, whose indices and gradients are fetched once; an
+// element receives a window's gradient exactly when the window's index names it (no range test is needed: a window
+// cannot name an element outside itself).
+template <typename T, int KS>
+__global__ void __launch_bounds__(256) pool_bwd_indices_s2_kernel(const int32_t* __restrict__ idx, const T* __restrict__ dy,
+                                                                  T* __restrict__ dx, Geo g) {
+    using A = typename AccOf<T>::type;
+    constexpr int K = KS == 1 ? 2 : 3, PL = 2;
+    const int q0 = (blockIdx.x * 32 + threadIdx.x) * 2, p0 = (blockIdx.y * 8 + threadIdx.y) * 2;
+    if (q0 >= g.W || p0 >= g.H) return;
+    const int oh0 = max(0, (p0 + g.ph - K + 2) / 2), ow0 = max(0, (q0 + g.pw - K + 2) / 2);
+    const bool r1 = oh0 + 1 < g.OH, c1 = ow0 + 1 < g.OW;
+    const bool has_p1 = p0 + 1 < g.H, has_q1 = q0 + 1 < g.W;
+    const int me00 = p0 * g.W + q0;
+    const int64_t planes = (int64_t)g.N * g.C, oplane = (int64_t)g.OH * g.OW, iplane = (int64_t)g.H * g.W;
+    const int64_t obase = (int64_t)oh0 * g.OW + ow0;
+    const bool pair_store = (g.W % 2 == 0) && has_q1 && sizeof(T) == 4 && (reinterpret_cast<uintptr_t>(dx) & 7) == 0;
+    for (int64_t nc = blockIdx.z; nc < planes; nc += (int64_t)PL * gridDim.z) {
+        int iv[PL][4];
+        A dv[PL][4];
+#pragma unroll
+        for (int u = 0; u < PL; u++) {
+            const int64_t pl = nc + (int64_t)u * gridDim.z;
+            const bool live = pl < planes;
+            const int32_t* ip = idx + pl * oplane + obase;
+            const T* dp = dy + pl * oplane + obase;
+            iv[u][0] = live ? ip[0] : -2;                     dv[u][0] = live ? ld<T>(dp) : (A)0;
+            iv[u][1] = live && c1 ? ip[1] : -2;               dv[u][1] = live && c1 ? ld<T>(dp + 1) : (A)0;
+            iv[u][2] = live && r1 ? ip[g.OW] : -2;            dv[u][2] = live && r1 ? ld<T>(dp + g.OW) : (A)0;
+            iv[u][3] = live && r1 && c1 ? ip[g.OW + 1] : -2;  dv[u][3] = live && r1 && c1 ? ld<T>(dp + g.OW + 1) : (A)0;
+        }
+#pragma unroll
+        for (int u = 0; u < PL; u++) {
+            const int64_t pl = nc + (int64_t)u * gridDim.z;
+            if (pl >= planes) break;
+            A acc[4] = {0, 0, 0, 0};                           // (p0,q0) (p0,q0+1) (p0+1,q0) (p0+1,q0+1)
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const int d = iv[u][t] - me00;
+                acc[0] += d == 0 ? dv[u][t] : (A)0;
+                acc[1] += d == 1 ? dv[u][t] : (A)0;
+                acc[2] += d == g.W ? dv[u][t] : (A)0;
+                acc[3] += d == g.W + 1 ? dv[u][t] : (A)0;
+            }
+            T* out = dx + pl * iplane + me00;
+            if (pair_store) {
+                float2 a = make_float2((float)acc[0], (float)acc[1]);
+                *reinterpret_cast<float2*>(out) = a;
+                if (has_p1) { float2 b = make_float2((float)acc[2], (float)acc[3]); *reinterpret_cast<float2*>(out + g.W) = b; }
+            } else {
+                out[0] = cvt<T, A>(acc[0]);
+                if (has_q1) out[1] = cvt<T, A>(acc[1]);
+                if (has_p1) { out[g.W] = cvt<T, A>(acc[2]); if (has_q1) out[g.W + 1] = cvt<T, A>(acc[3]); }
+            }
+        }
+    }
+}
+
+// Forward for stride-2 windows of edge <= 3 with padding 0 or 1 on rows of a multiple of 4 elements: a thread produces
+// two horizontally adjacent outputs from ONE 16-byte load per input row plus the two neighbouring elements, instead of
+// 2 x K strided 4-byte loads per row.
+template <int OP, int KS>
+__global__ void __launch_bounds__(256) pool_fwd_s2_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ indices,
+                                                          Geo g, float init) {
+    constexpr int K = KS == 1 ? 2 : 3, PL = 2;
+    const int ow0 = (blockIdx.x * 32 + threadIdx.x) * 2, oh = blockIdx.y * 8 + threadIdx.y;
+    if (ow0 >= g.OW || oh >= g.OH) return;
+    const int pb = oh * 2 - g.ph, c0 = ow0 * 2;                 // first window row; column of the aligned 16-byte load
+    const bool two = ow0 + 1 < g.OW;
+    bool rok[K];
+#pragma unroll
+    for (int a = 0; a < K; a++) rok[a] = (unsigned)(pb + a) < (unsigned)g.H;
+    const bool left = c0 - 1 >= 0, mid = c0 + 3 < g.W, right = c0 + 4 < g.W;   // W % 4 == 0: the vector is all in or all out
+    const float pad = OP == 2 ? 0.f : init;
+    const int64_t planes = (int64_t)g.N * g.C, iplane = (int64_t)g.H * g.W;
+    for (int64_t nc = blockIdx.z; nc < planes; nc += (int64_t)PL * gridDim.z) {
+        float v[PL][K][6];                                      // columns c0-1 .. c0+4
+#pragma unroll
+        for (int u = 0; u < PL; u++) {
+            const int64_t pl = nc + (int64_t)u * gridDim.z;
+            const float* xu = x + pl * iplane + (int64_t)pb * g.W + c0;
+#pragma unroll
+            for (int a = 0; a < K; a++) {
+                const bool ok = rok[a] && pl < planes;
+                const float* row = xu + (int64_t)a * g.W;
+                const float4 m = ok && mid ? *reinterpret_cast<const float4*>(row) : make_float4(pad, pad, pad, pad);
+                v[u][a][0] = ok && left ? row[-1] : pad;
+                v[u][a][1] = m.x; v[u][a][2] = m.y; v[u][a][3] = m.z; v[u][a][4] = m.w;
+                v[u][a][5] = ok && right ? row[4] : pad;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PL; u++) {
+            const int64_t pl = nc + (int64_t)u * gridDim.z;
+            if (pl >= planes) break;
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                if (j == 1 && !two) break;
+                const int ow = ow0 + j;
+                const int qb = ow * 2 - g.pw;                   // first window column; slot of tap b is 2j - pw + b + 1
+                float best = pad, acc = 0.f;
+                int tap = -1;
+#pragma unroll
+                for (int a = 0; a < K; a++)
+#pragma unroll
+                    for (int b = 0; b < K; b++) {
+                        const float val = g.pw ? v[u][a][2 * j + b] : v[u][a][2 * j + b + 1];
+                        const bool in = rok[a] && (unsigned)(qb + b) < (unsigned)g.W;
+                        if (OP == 2) acc += in ? val : 0.f;
+                        else if (in && (OP == 0 ? best < val : val < best)) { best = val; tap = a * K + b; }
+                    }
+                const int64_t o = (pl * g.OH + oh) * g.OW + ow;
+                if (OP == 2) {
+                    const int p1 = min(pb + K, g.H), q1 = min(qb + K, g.W);
+                    const int count = g.count_include_pad ? K * K : (p1 - max(pb, 0)) * (q1 - max(qb, 0));
+                    y[o] = acc / (float)count;
+                } else {
+                    y[o] = best;
+                    if (indices) indices[o] = tap < 0 ? -1 : (pb + tap / K) * g.W + qb + tap % K;
+                }
+            }
+        }
+    }
+}
+
 static int window_code(const Geo& g) {
     if (g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2) return 1;
     if (g.kh == 3 && g.kw == 3 && g.sh == 2 && g.sw == 2) return 2;
@@ -305,6 +431,15 @@ static int parse(const b200jt_tensor* x, const b200jt_tensor* y, const char* op,
 template <typename T, int OP>
 static void launch_fwd(const T* xp, T* yp, int32_t* indices, const Geo& g, T init, cudaStream_t st) {
     const dim3 grid = plane_grid(g.OW, g.OH, (int64_t)g.N * g.C), block(32, 8);
+    if constexpr (sizeof(T) == 4) {
+        const int code = window_code(g);
+        if ((code == 1 || code == 2) && g.W % 4 == 0 && (g.pw == 0 || g.pw == 1) && ((uintptr_t)xp & 15) == 0) {
+            const dim3 grid2 = plane_grid((g.OW + 1) / 2, g.OH, ((int64_t)g.N * g.C + 1) / 2);
+            if (code == 1) pool_fwd_s2_kernel<OP, 1><<<grid2, block, 0, st>>>((const float*)xp, (float*)yp, indices, g, (float)init);
+            else pool_fwd_s2_kernel<OP, 2><<<grid2, block, 0, st>>>((const float*)xp, (float*)yp, indices, g, (float)init);
+            return;
+        }
+    }
     switch (window_code(g)) {
         case 1: pool_fwd_kernel<T, OP, 1><<<grid, block, 0, st>>>(xp, yp, indices, g, init); break;
         case 2: pool_fwd_kernel<T, OP, 2><<<grid, block, 0, st>>>(xp, yp, indices, g, init); break;
@@ -327,11 +462,13 @@ static void launch_bwd(const T* xp, const T* yp, const T* dp, T* op, const Geo& 
 template <typename T>
 static int run_bwd_indices(const int32_t* idx, const b200jt_tensor* dy, const b200jt_tensor* dx, const Geo& g, cudaStream_t st) {
     if (numel(dx) == 0) return 0;
-    const dim3 grid = plane_grid(g.W, g.H, ((int64_t)g.N * g.C + 3) / 4), block(32, 8);
+    const int64_t planes = (int64_t)g.N * g.C;
+    const dim3 grid = plane_grid(g.W, g.H, (planes + 3) / 4), block(32, 8);
+    const dim3 grid2 = plane_grid((g.W + 1) / 2, (g.H + 1) / 2, (planes + 1) / 2);
     const T* dp = (const T*)dy->ptr; T* op = (T*)dx->ptr;
     switch (window_code(g)) {
-        case 1: pool_bwd_indices_kernel<T, 1><<<grid, block, 0, st>>>(idx, dp, op, g); break;
-        case 2: pool_bwd_indices_kernel<T, 2><<<grid, block, 0, st>>>(idx, dp, op, g); break;
+        case 1: pool_bwd_indices_s2_kernel<T, 1><<<grid2, block, 0, st>>>(idx, dp, op, g); break;
+        case 2: pool_bwd_indices_s2_kernel<T, 2><<<grid2, block, 0, st>>>(idx, dp, op, g); break;
         case 3: pool_bwd_indices_kernel<T, 3><<<grid, block, 0, st>>>(idx, dp, op, g); break;
         default: pool_bwd_indices_kernel<T, 0><<<grid, block, 0, st>>>(idx, dp, op, g);
     }
