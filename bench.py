@@ -432,9 +432,10 @@ class NextOps:
     ROWS, COLS, PICK = 1 << 20, 64, 1 << 19
     description = ("callers of the path: 3x3 stride-2 pad-1 max-pool forward and backward on [64,128,112,112] fp32, "
                    "getitem x[idx] of 2^19 rows out of [2^20,64] fp32, setitem x[idx] += v on the same shapes")
-    kernel_of = {"maxpool-fwd": "pool_fwd_kernel", "maxpool-bwd": "pool_bwd_kernel", "getitem-rows": "reindex kernel",
-                 "setitem-add-rows": "rr_generic_kernel"}
+    kernel_of = {"maxpool-fwd": "pool_fwd_s2_kernel", "maxpool-bwd": "pool_bwd_indices_s2_kernel",
+                 "getitem-rows": "reindex_rows_kernel", "setitem-add-rows": "rr_rows_kernel (+ table copy)"}
     launches = {"maxpool-fwd": 1, "maxpool-bwd": 1, "getitem-rows": 1, "setitem-add-rows": 1}
+    traffic = {"maxpool-fwd": 584.9e6, "maxpool-bwd": 566.8e6, "getitem-rows": 241.1e6, "setitem-add-rows": 365.8e6}
 
     def work(self):
         n = int(np.prod(self.SHAPE)) * 4
