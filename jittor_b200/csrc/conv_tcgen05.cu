@@ -260,12 +260,15 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 // ---- layout passes -----------------------------------------------------------------------------------------
 // in[b][R][Cn] -> out[b][Cn][R] (bf16), 64x64 tiles, 16-byte global accesses on both sides. The tile is kept as
 // 32-bit pairs with an odd pitch (33 words) so that the column reads of the second phase spread over the banks.
-// The first wz slices (blockIdx.z < wz) of the same grid re-order the weights instead (w[Co][C][taps] -> wt[taps][Co][C]), so
+// Block (0,0,0) also zeroes `zero[0..n_zero)`. The first wz slices (blockIdx.z < wz) of the same grid re-order the weights instead (w[Co][C][taps] -> wt[taps][Co][C]), so
 // that both layout passes of a convolution are one launch.
 __global__ void __launch_bounds__(256)
 transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn, int wz,
-                              const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int C, int taps) {
+                              const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int C, int taps,
+                              float* __restrict__ zero, int n_zero) {
     __shared__ __nv_bfloat16 tile[64][66];
+    if (zero && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)       // the statistics the conv epilogue adds into
+        for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero[i] = 0.f;
     if ((int)blockIdx.z < wz) {
         const int64_t n = (int64_t)Co * C * taps;
         const int64_t nblk = (int64_t)gridDim.x * gridDim.y * wz;
@@ -370,8 +373,9 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
         const int64_t per_slice = (int64_t)gx * gy * 256;
         const unsigned wz = (unsigned)std::min<int64_t>(32, std::max<int64_t>(1, (nw + per_slice - 1) / per_slice));
         dim3 g(gx, gy, (unsigned)s.N + wz);
+        float* zero = (stats && s.Co <= STATS_MAX_CO) ? stats : nullptr;   // zeroed here instead of by a memset node
         transpose_bf16_batched_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW, (int)wz,
-                                                          (const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW);
+                                                          (const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW, zero, 2 * s.Co);
         B200JT_LAUNCH_CHECK();
     }
     ConvArgs A;
@@ -402,7 +406,6 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     CUtensorMap my = mx;
     if (tma_out && !make_map_y(&my, y, s)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed (y)");
     float* fused = (stats && s.Co <= STATS_MAX_CO) ? stats : nullptr;
-    if (fused) B200JT_CUDA(cudaMemsetAsync(stats, 0, sizeof(float) * 2 * s.Co, st));
     const int total = A.tiles_m * A.tiles_n;
     const int grid = total < kNumSMs ? total : kNumSMs;
     auto kern = bn == 256 ? (tma_out ? conv_bf16_kernel<true, 256> : conv_bf16_kernel<false, 256>)

@@ -3,13 +3,14 @@
 // this path (batch-norm statistics, scatter outputs), where a ring/tree collective is latency-bound.
 //
 // Every rank owns one `segment` of device memory, exported to the other ranks as a CUDA IPC handle:
-//     [ flags : kMaxBlocks x kMaxRanks u32 ][ epochs : kMaxBlocks u32 ][ in[0] | in[1] | out[0] | out[1] : data_bytes each ]
+//     [ flags : kMaxBlocks x kMaxRanks u32 ][ epochs : kMaxBlocks u32 ][ in[0] | in[1] | out[0] | out[1] : data_bytes (+ pad) each ]
 // Block b of rank r only ever talks to block b of the other ranks:
 //   small messages (one shot, while (world-1) * bytes <= 4 MiB):  copy its chunk of src into in[parity] of its own segment, flag every peer, wait for
 //       every peer's flag, then sum that chunk over the ranks' segments IN RANK ORDER (so all ranks get the same
 //       bits) straight into dst;
-//   large messages (two shot):  the same hand-off, then rank r sums only slice r and writes the result into
-//       out[parity] of EVERY rank, a second flag round, and each rank copies out[parity] into dst.
+//   large messages (two shot):  rank r PUSHES its chunk of slice s from src into slot r of rank s's in[parity] (posted
+//       writes), flag round, then rank r sums the world slots of slice r from its own memory and writes the result
+//       into out[parity] of EVERY rank, a second flag round, and each rank copies out[parity] into dst.
 // Flags carry a per-block epoch that only grows (kept in device memory, so a captured launch can be replayed);
 // in/out alternate between two halves by call parity, which is what lets the one-shot form skip a closing flag
 // round: a peer can only overwrite half p again two calls later, after it has seen this rank enter the next call.
@@ -30,6 +31,7 @@ constexpr size_t kFlagBytes = (size_t)kMaxBlocks * kMaxRanks * 4;
 constexpr size_t kEpochBytes = (size_t)kMaxBlocks * 4;
 constexpr size_t kHeaderBytes = 8192;                       // flags + epochs, padded so the data halves stay 256-B aligned
 static_assert(kFlagBytes + kEpochBytes <= kHeaderBytes, "header too small");
+constexpr size_t kHalfPad = 256;
 constexpr size_t kOneShotMaxRemoteBytes = 4 << 20;      // one shot while a rank reads at most this much from its peers
 
 static __device__ int g_status = 0;
@@ -54,7 +56,8 @@ __device__ __forceinline__ uint32_t* epoch_of(unsigned char* seg, int block) {
     return reinterpret_cast<uint32_t*>(seg + kFlagBytes) + block;
 }
 __device__ __forceinline__ unsigned char* half_of(unsigned char* seg, unsigned long long data_bytes, int which) {
-    return seg + kHeaderBytes + (size_t)which * data_bytes;     // which: 0,1 = in[parity], 2,3 = out[parity]
+    // which: 0,1 = in[parity], 2,3 = out[parity]; kHalfPad spare bytes per half: world slots of ceil(packs/world) packs
+    return seg + kHeaderBytes + (size_t)which * (data_bytes + kHalfPad);
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -219,35 +222,82 @@ __global__ void __launch_bounds__(kThreads) peer_all_reduce_kernel(Launch L, lon
     const int lo = (TWO_SHOT ? r * mine.slice : 0) + mine.per * b;
     const int hi = min(min(nv, (TWO_SHOT ? r + 1 : 1) * mine.slice), lo + mine.per);
 
-    // 1. this block's packs of src -> in[parity] of the own segment
-    for (int f0 = threadIdx.x; f0 < mine.total(); f0 += UC * kThreads) {
-        int idx[UC];
-        Pack<T, V> p[UC];
+    bool fine;
+    if (!TWO_SHOT) {
+        // 1. this block's packs of src -> in[parity] of the own segment
+        for (int f0 = threadIdx.x; f0 < mine.total(); f0 += UC * kThreads) {
+            int idx[UC];
+            Pack<T, V> p[UC];
 #pragma unroll
-        for (int u = 0; u < UC; u++) {
-            idx[u] = mine.at(f0 + u * kThreads);
-            if (idx[u] >= 0) p[u] = load_user<T, V>(src, idx[u], count, src_vec);
+            for (int u = 0; u < UC; u++) {
+                idx[u] = mine.at(f0 + u * kThreads);
+                if (idx[u] >= 0) p[u] = load_user<T, V>(src, idx[u], count, src_vec);
+            }
+#pragma unroll
+            for (int u = 0; u < UC; u++)
+                if (idx[u] >= 0) store_seg<T, V>(in_own + (size_t)idx[u] * V, p[u]);
         }
+        fine = flag_round(c, b, epoch + 1, &ok);
+        // 2. reduce over the ranks straight into dst
+        if (fine) {
+            for (int i = lo + threadIdx.x; i < hi; i += UR * kThreads) {
+                Pack<T, V> o[UR];
+                reduce_over_ranks<T, V, OP, UR>(c, parity, i, hi, o);
 #pragma unroll
-        for (int u = 0; u < UC; u++)
-            if (idx[u] >= 0) store_seg<T, V>(in_own + (size_t)idx[u] * V, p[u]);
-    }
-    bool fine = flag_round(c, b, epoch + 1, &ok);
-    // 2. reduce over the ranks: everything into dst (one shot), or the own slice into out[parity] of every rank
-    if (fine) {
-        for (int i = lo + threadIdx.x; i < hi; i += UR * kThreads) {
-            Pack<T, V> o[UR];
-            reduce_over_ranks<T, V, OP, UR>(c, parity, i, hi, o);
+                for (int u = 0; u < UR; u++)
+                    if (i + u * kThreads < hi) store_user<T, V>(dst, i + u * kThreads, count, dst_vec, o[u]);
+            }
+        }
+    } else {
+        // 1. push: this block's chunk of slice s goes from src straight into slot r of rank s's in[parity] (posted NVLink
+        //    writes; no local staging pass and no remote reads later)
+        for (int f0 = threadIdx.x; f0 < mine.total(); f0 += UC * kThreads) {
+            int idx[UC];
+            Pack<T, V> p[UC];
 #pragma unroll
-            for (int u = 0; u < UR; u++) {
-                const int iu = i + u * kThreads;
-                if (iu >= hi) continue;
-                if (!TWO_SHOT) {
-                    store_user<T, V>(dst, iu, count, dst_vec, o[u]);
-                } else {
+            for (int u = 0; u < UC; u++) {
+                idx[u] = mine.at(f0 + u * kThreads);
+                if (idx[u] >= 0) p[u] = load_user<T, V>(src, idx[u], count, src_vec);
+            }
+#pragma unroll
+            for (int u = 0; u < UC; u++) {
+                if (idx[u] < 0) continue;
+                const int s = idx[u] / mine.slice, j = idx[u] - s * mine.slice;
+                T* slot = reinterpret_cast<T*>(half_of(c.seg[s], c.data_bytes, parity)) + ((size_t)r * mine.slice + j) * V;
+                store_seg<T, V>(slot, p[u]);
+            }
+        }
+        fine = flag_round(c, b, epoch + 1, &ok);
+        // 2. reduce the W slots of the own slice (local reads, rank order) and write the result to every rank's out[parity]
+        if (fine) {
+            using A = typename Acc<T>::type;
+            for (int i = lo + threadIdx.x; i < hi; i += UR * kThreads) {
+                Pack<T, V> p[kMaxRanks][UR];
+#pragma unroll
+                for (int k = 0; k < kMaxRanks; k++)
+                    if (k < W) {
+#pragma unroll
+                        for (int u = 0; u < UR; u++) {
+                            const int iu = i + u * kThreads;
+                            if (iu < hi) p[k][u] = load_seg<T, V>(in_own + ((size_t)k * mine.slice + (iu - r * mine.slice)) * V);
+                        }
+                    }
+#pragma unroll
+                for (int u = 0; u < UR; u++) {
+                    const int iu = i + u * kThreads;
+                    if (iu >= hi) continue;
+                    Pack<T, V> o;
+#pragma unroll
+                    for (int e = 0; e < V; e++) {
+                        A acc = (A)p[0][u].v[e];
+#pragma unroll
+                        for (int k = 1; k < kMaxRanks; k++)
+                            if (k < W) acc = combine<OP, A>(acc, (A)p[k][u].v[e]);
+                        o.v[e] = (T)acc;
+                    }
 #pragma unroll
                     for (int k = 0; k < kMaxRanks; k++)
-                        if (k < W) store_seg<T, V>(reinterpret_cast<T*>(half_of(c.seg[k], c.data_bytes, 2 + parity)) + (size_t)iu * V, o[u]);
+                        if (k < W) store_seg<T, V>(reinterpret_cast<T*>(half_of(c.seg[k], c.data_bytes, 2 + parity)) + (size_t)iu * V, o);
                 }
             }
         }
@@ -284,7 +334,7 @@ struct Comm {
     DevComm dev{};                      // what the kernel receives
 };
 
-static size_t segment_bytes(size_t data_bytes) { return kHeaderBytes + 4 * data_bytes; }
+static size_t segment_bytes(size_t data_bytes) { return kHeaderBytes + 4 * (data_bytes + kHalfPad); }
 
 static int upload(Comm* c, double wait_ms) {
     DevComm h{};

@@ -65,27 +65,12 @@ __device__ __forceinline__ C reduce_init(int op, int ydt) {
     return (C)0;
 }
 
-template <typename C>
-__device__ __forceinline__ C reduce_load(const void* x, int xdt, int64_t off, int op, C rcount) {
-    C v = load_as<C>(x, xdt, off);
-    if (op == OP_MEAN) v = v * rcount;
-    return v;
-}
-
 __device__ __forceinline__ int64_t kept_offset(const ReduceArgs& A, int64_t o) {
     int64_t off = 0;
 #pragma unroll 1
     for (int d = A.nk - 1; d >= 0; d--) { int64_t s = A.kshape[d]; off += (o % s) * A.kstride[d]; o /= s; }
     return off;
 }
-__device__ __forceinline__ int64_t red_offset(const ReduceArgs& A, int64_t r) {
-    if (A.nr == 1) return r * A.rstride[0];
-    int64_t off = 0;
-#pragma unroll 1
-    for (int d = A.nr - 1; d >= 0; d--) { int64_t s = A.rshape[d]; off += (r % s) * A.rstride[d]; r /= s; }
-    return off;
-}
-
 template <typename C>
 __device__ __forceinline__ C shfl_down_c(C v, int delta) {
     if constexpr (sizeof(C) == 8) {
