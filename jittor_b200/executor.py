@@ -415,15 +415,16 @@ def _match_conv_wgrad(v):
     if geo is None:
         return None
 
-    def run():
-        xd = x._data
-        dyd = _cast(dy._data, x.dtype)
-        out = _empty([Co, Ci, KH, KW], x.dtype)
-        C.check(C.lib.b200jt_conv2d_backward_w(C.desc(xd), C.desc(dyd), C.desc(out), *geo, C.stream_ptr()),
-                f"conv2d_backward_w x{list(x.shape)} dy{list(dy.shape)} geo{geo}")
-        return _cast(out, v.dtype)
+    return Plan([x, dy], lambda: run_conv2d_backward_w(x, dy, geo, [Co, Ci, KH, KW], v.dtype))
 
-    return Plan([x, dy], run)
+
+def run_conv2d_backward_w(x, dy, geo, w_shape, out_dtype):
+    xd = x._data.view(list(x.shape))
+    dyd = _cast(dy._data.view(list(dy.shape)), x.dtype)
+    out = _empty(w_shape, x.dtype)
+    C.check(C.lib.b200jt_conv2d_backward_w(C.desc(xd), C.desc(dyd), C.desc(out), *geo, C.stream_ptr()),
+            f"conv2d_backward_w x{list(x.shape)} dy{list(dy.shape)} geo{geo}")
+    return _cast(out, out_dtype)
 
 
 def run_conv2d_transpose(x, w, geo, groups, out_shape, out_dtype):

@@ -87,8 +87,37 @@ def _register_builtins():
             raise NotImplementedError("only abcd / oihw layouts")
         return nn.conv2d(x, w, None, (strideh, stridew), (paddingh, paddingw), (dilationh, dilationw), groups)
 
+    def _relayed(x, w_or_dy, shape, run):
+        """A Var produced by one relay launch (inputs synced by the executor first)."""
+        node = V.Op("custom", [V.to_var(x), V.to_var(w_or_dy)], fn=run, name="relay")
+        return V.Var(shape, V.to_var(x).dtype, node)
+
+    def cudnn_conv_backward_x(w, dy, height, width, strideh, stridew, paddingh, paddingw, dilationh=1, dilationw=1, groups=1,
+                              xformat="abcd", wformat="oihw", yformat="abcd"):
+        """Relay signature of conv_tuner.cc:382-389: dx[N, Cin, height, width] from w (OIHW) and dy."""
+        if xformat != "abcd" or wformat != "oihw" or yformat != "abcd" or groups != 1:
+            raise NotImplementedError("only abcd / oihw layouts, groups == 1")
+        from . import executor
+        w, dy = V.to_var(w), V.to_var(dy)
+        shape = [dy.shape[0], w.shape[1], height, width]
+        geo = (strideh, stridew, paddingh, paddingw, dilationh, dilationw)
+        return _relayed(dy, w, shape, lambda dyd, wd: executor.run_conv2d_transpose(dy, w, geo, 1, shape, dy.dtype))
+
+    def cudnn_conv_backward_w(x, dy, kh, kw, strideh, stridew, paddingh, paddingw, dilationh=1, dilationw=1, groups=1,
+                              xformat="abcd", wformat="oihw", yformat="abcd"):
+        """Relay signature of conv_tuner.cc:390-396: dw[Cout, Cin, kh, kw] from x and dy."""
+        if xformat != "abcd" or wformat != "oihw" or yformat != "abcd" or groups != 1:
+            raise NotImplementedError("only abcd / oihw layouts, groups == 1")
+        from . import executor
+        x, dy = V.to_var(x), V.to_var(dy)
+        shape = [dy.shape[1], x.shape[1], kh, kw]
+        geo = (strideh, stridew, paddingh, paddingw, dilationh, dilationw)
+        return _relayed(x, dy, shape, lambda xd, dyd: executor.run_conv2d_backward_w(x, dy, geo, shape, x.dtype))
+
     register_op("cublas_matmul", cublas_matmul)
     register_op("cudnn_conv", cudnn_conv)
+    register_op("cudnn_conv_backward_x", cudnn_conv_backward_x)
+    register_op("cudnn_conv_backward_w", cudnn_conv_backward_w)
     register_op("nccl_all_reduce", lambda x: dist.mpi_all_reduce(x, "add"))
     register_op("mpi_all_reduce", dist.mpi_all_reduce)
 

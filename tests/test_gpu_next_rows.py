@@ -174,3 +174,20 @@ def test_conv_backward_matches_torch(jt, dtype, stride, pad, dil):
         assert got.shape == want.shape
         err = (got - want).abs().max().item()
         assert err <= tol * want.abs().max().item() + 1e-6, (err, want.abs().max().item())
+
+
+def test_backward_relays_under_the_tuner_names(jt):
+    """cudnn_conv_backward_x / _w are registered with the signatures ConvTuner uses (conv_tuner.cc:382-396)."""
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(2, 5, 9, 11, generator=g).cuda()
+    w = (torch.randn(7, 5, 3, 3, generator=g) * 0.2).cuda()
+    tx, tw = x.clone().requires_grad_(), w.clone().requires_grad_()
+    ty = torch.nn.functional.conv2d(tx, tw, None, 2, 1, 1)
+    dy = torch.randn(*ty.shape, generator=g).cuda()
+    (ty * dy).sum().backward()
+    make_dx = jt.get_op_info("cudnn_conv_backward_x").get_constructor()
+    make_dw = jt.get_op_info("cudnn_conv_backward_w").get_constructor()
+    dx = make_dx(jt.array(w), jt.array(dy), 9, 11, 2, 2, 1, 1, 1, 1)
+    dw = make_dw(jt.array(x), jt.array(dy), 3, 3, 2, 2, 1, 1, 1, 1)
+    assert torch.allclose(dx.torch(), tx.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(dw.torch(), tw.grad, rtol=1e-4, atol=1e-4)
