@@ -72,6 +72,21 @@ __device__ __forceinline__ float group_reduce(float v, float* sm) {
     }
 }
 
+// Two sums over the GROUP threads of a row with one shared-memory exchange (sm holds 16 floats).
+template <int GROUP>
+__device__ __forceinline__ void group_sum2(float& a, float& b, float* sm) {
+    a = warp_sum(a); b = warp_sum(b);
+    if constexpr (GROUP > 32) {
+        constexpr int W = GROUP / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();
+        if (lane == 0) { sm[warp] = a; sm[8 + warp] = b; }
+        __syncthreads();
+        a = warp_sum(lane < W ? sm[lane] : 0.f);
+        b = warp_sum(lane < W ? sm[8 + lane] : 0.f);
+    }
+}
+
 template <int N>
 __device__ __forceinline__ void load_gb(const float* __restrict__ gamma, const float* __restrict__ beta, int c, float* g, float* b) {
 #pragma unroll
@@ -91,7 +106,7 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
                const float* __restrict__ beta, int64_t rows, int cols, float eps) {
     constexpr int N = Vec16<T>::N;
     constexpr int ROWS_PER_CTA = 256 / GROUP;
-    __shared__ float sm[8];
+    __shared__ float sm[16];
     const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
     const int nvec = cols / N;
     // a thread owns the same columns in every row it visits: keep their gamma / beta in registers when they fit
@@ -124,8 +139,7 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
             for (int k = 0; k < VPT; k++)
 #pragma unroll
                 for (int e = 0; e < N; e++) { s1 += v[k][e]; s2 += v[k][e] * v[k][e]; }
-            s1 = group_reduce<GROUP, false>(s1, sm);
-            s2 = group_reduce<GROUP, false>(s2, sm);
+            group_sum2<GROUP>(s1, s2, sm);
             const float rc = 1.0f / (float)cols;
             const float mean = s1 * rc, m2 = s2 * rc;
             const float var = fmaxf(m2 - mean * mean, 0.f);

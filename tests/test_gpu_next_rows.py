@@ -191,3 +191,50 @@ def test_backward_relays_under_the_tuner_names(jt):
     dw = make_dw(jt.array(x), jt.array(dy), 3, 3, 2, 2, 1, 1, 1, 1)
     assert torch.allclose(dx.torch(), tx.grad, rtol=1e-4, atol=1e-5)
     assert torch.allclose(dw.torch(), tw.grad, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64", "float16", "bfloat16", "int32", "int64", "int16", "int8", "uint8"])
+def test_getitem_setitem_every_dtype(jt, ref, dtype):
+    rng = np.random.default_rng(10)
+    npdt = np.float32 if dtype == "bfloat16" else np.dtype(dtype)
+    x = rng.integers(0, 50, size=(40, 24)).astype(npdt)
+    v = rng.integers(0, 50, size=(15, 24)).astype(npdt)
+    idx = rng.permutation(40)[:15].astype(np.int32)              # unique rows: 'void' is deterministic
+
+    def to_jt(a):
+        return jt.array(torch.from_numpy(a).bfloat16()) if dtype == "bfloat16" else jt.array(a)
+
+    def back(vr):
+        return vr.torch().float().cpu().numpy() if dtype == "bfloat16" else vr.numpy()
+
+    assert np.array_equal(back(to_jt(x)[jt.array(idx)]), ref.getitem(x, (idx,)))
+    assert np.array_equal(back(to_jt(x)[3:30:4, jt.array(idx % 24)]), ref.getitem(x, (slice(3, 30, 4), idx % 24)))
+    assert np.array_equal(back(to_jt(x).setitem((jt.array(idx),), to_jt(v))), ref.setitem(x, (idx,), v))
+    dup = np.array([1, 1, 1, 5, 5, 0, 39, 39, 2, 2, 2, 2, 7, 8, 9], np.int32)
+    got = back(to_jt(x).setitem((jt.array(dup),), to_jt(v), "add"))
+    want = ref.setitem(x.astype(np.float64) if dtype in ("float16", "bfloat16") else x, (dup,), v, "add")
+    if dtype in ("float16", "bfloat16"):
+        assert np.allclose(got, want, rtol=2e-2, atol=1.0)      # small integers: exact up to the 16-bit rounding of sums
+    else:
+        assert np.array_equal(got, want.astype(npdt))
+    assert np.array_equal(back(to_jt(x).setitem((jt.array(dup),), to_jt(v), "maximum")), ref.setitem(x, (dup,), v, "maximum"))
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float16", "bfloat16"])
+@pytest.mark.parametrize("k,s,p", [(3, 2, 1), (2, 2, 0), (3, 1, 1), (4, 3, 2)])
+def test_pool_other_dtypes_and_windows(jt, ref, dtype, k, s, p):
+    from jittor_b200 import pool
+    rng = np.random.default_rng(11)
+    x = (rng.integers(-20, 20, size=(2, 3, 19, 22)) / 4).astype(np.float64)      # exactly representable in 16 bits
+    td = {"float64": torch.float64, "float16": torch.float16, "bfloat16": torch.bfloat16}[dtype]
+    vx = jt.array(torch.from_numpy(x).to(td))
+    for op in ("maximum", "mean"):
+        layer = pool.Pool(k, s, p, op=op, ceil_mode=(op == "mean"))
+        y = layer(vx)
+        want = ref.pool2d(x, k, op, s, p, op == "mean")
+        got = y.torch().double().cpu().numpy()
+        assert np.allclose(got, want, rtol=1e-2 if dtype != "float64" else 1e-12, atol=1e-2 if dtype != "float64" else 1e-12)
+        dy = (rng.integers(-8, 8, size=want.shape) / 2).astype(np.float64)
+        dx = jt.grad((y * jt.array(torch.from_numpy(dy).to(td))).sum(), vx).torch().double().cpu().numpy()
+        wdx = ref.pool2d_backward(x, dy, k, op, s, p, op == "mean")
+        assert np.allclose(dx, wdx, rtol=2e-2 if dtype != "float64" else 1e-12, atol=5e-2 if dtype != "float64" else 1e-12)
