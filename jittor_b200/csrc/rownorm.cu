@@ -72,21 +72,6 @@ __device__ __forceinline__ float group_reduce(float v, float* sm) {
     }
 }
 
-// Two sums over the GROUP threads of a row with one shared-memory exchange (sm holds 16 floats).
-template <int GROUP>
-__device__ __forceinline__ void group_sum2(float& a, float& b, float* sm) {
-    a = warp_sum(a); b = warp_sum(b);
-    if constexpr (GROUP > 32) {
-        constexpr int W = GROUP / 32;
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        __syncthreads();
-        if (lane == 0) { sm[warp] = a; sm[8 + warp] = b; }
-        __syncthreads();
-        a = warp_sum(lane < W ? sm[lane] : 0.f);
-        b = warp_sum(lane < W ? sm[8 + lane] : 0.f);
-    }
-}
-
 template <int N>
 __device__ __forceinline__ void load_gb(const float* __restrict__ gamma, const float* __restrict__ beta, int c, float* g, float* b) {
 #pragma unroll
@@ -98,15 +83,39 @@ __device__ __forceinline__ void load_gb(const float* __restrict__ gamma, const f
     }
 }
 
+// Sums (or maxima) of NV values per thread over the GROUP threads of a row with ONE shared-memory exchange
+// (sm holds NV * 8 floats).
+template <int GROUP, bool IS_MAX, int NV>
+__device__ __forceinline__ void group_reduce_n(float (&v)[NV], float* sm) {
+#pragma unroll
+    for (int i = 0; i < NV; i++) v[i] = IS_MAX ? warp_max(v[i]) : warp_sum(v[i]);
+    if constexpr (GROUP > 32) {
+        constexpr int W = GROUP / 32;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();                      // sm may still be read from the previous reduction
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < NV; i++) sm[i * 8 + warp] = v[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const float t = lane < W ? sm[i * 8 + lane] : (IS_MAX ? -FLT_MAX : 0.f);
+            v[i] = IS_MAX ? warp_max(t) : warp_sum(t);
+        }
+    }
+}
+
 // GROUP threads per row, VPT 16-byte vectors per thread; requires cols % Vec16<T>::N == 0 and
-// cols <= GROUP * VPT * N.
+// cols <= GROUP * VPT * N. RPI rows are taken per round (their reductions share the shared-memory exchanges).
 template <typename T, int GROUP, int VPT, int OP>
 __global__ void __launch_bounds__(256)
 row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ gamma,
                const float* __restrict__ beta, int64_t rows, int cols, float eps) {
     constexpr int N = Vec16<T>::N;
     constexpr int ROWS_PER_CTA = 256 / GROUP;
-    __shared__ float sm[16];
+    constexpr int RPI = 1;          // two rows per round were measured slower (fewer CTAs in flight outweigh the shared exchange)
+    __shared__ float sm[32];
     const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
     const int nvec = cols / N;
     // a thread owns the same columns in every row it visits: keep their gamma / beta in registers when they fit
@@ -119,75 +128,102 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
             if (vi < nvec) load_gb<N>(gamma, beta, vi * N, gm[k], bt[k]);
         }
     }
-    for (int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + g; row < rows;
-         row += (int64_t)gridDim.x * ROWS_PER_CTA) {
-        const T* xr = x + row * cols;
-        T* yr = y + row * cols;
-        float v[VPT][N];
+    for (int64_t row0 = ((int64_t)blockIdx.x * ROWS_PER_CTA + g) * RPI; row0 < rows;
+         row0 += (int64_t)gridDim.x * ROWS_PER_CTA * RPI) {
+        float v[RPI][VPT][N];
+        bool live[RPI];
 #pragma unroll
-        for (int k = 0; k < VPT; k++) {
-            const int vi = t + k * GROUP;
-            if (vi < nvec) Vec16<T>::load(xr + (int64_t)vi * N, v[k]);
-            else {
+        for (int r = 0; r < RPI; r++) {
+            live[r] = row0 + r < rows;
+            const T* xr = x + (row0 + r) * cols;
 #pragma unroll
-                for (int e = 0; e < N; e++) v[k][e] = (OP == ROW_LAYERNORM) ? 0.f : -FLT_MAX;
+            for (int k = 0; k < VPT; k++) {
+                const int vi = t + k * GROUP;
+                if (vi < nvec && live[r]) Vec16<T>::load(xr + (int64_t)vi * N, v[r][k]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < N; e++) v[r][k][e] = (OP == ROW_LAYERNORM) ? 0.f : -FLT_MAX;
+                }
             }
         }
         if constexpr (OP == ROW_LAYERNORM) {
-            float s1 = 0.f, s2 = 0.f;
+            float s[2 * RPI];
 #pragma unroll
-            for (int k = 0; k < VPT; k++)
+            for (int r = 0; r < RPI; r++) {
+                float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-                for (int e = 0; e < N; e++) { s1 += v[k][e]; s2 += v[k][e] * v[k][e]; }
-            group_sum2<GROUP>(s1, s2, sm);
+                for (int k = 0; k < VPT; k++)
+#pragma unroll
+                    for (int e = 0; e < N; e++) { s1 += v[r][k][e]; s2 += v[r][k][e] * v[r][k][e]; }
+                s[2 * r] = s1; s[2 * r + 1] = s2;
+            }
+            group_reduce_n<GROUP, false, 2 * RPI>(s, sm);
             const float rc = 1.0f / (float)cols;
-            const float mean = s1 * rc, m2 = s2 * rc;
-            const float var = fmaxf(m2 - mean * mean, 0.f);
-            const float rstd = 1.0f / sqrtf(var + eps);
 #pragma unroll
-            for (int k = 0; k < VPT; k++) {
-                const int vi = t + k * GROUP;
-                if (vi < nvec) {
-                    float o[N];
-                    if constexpr (CACHE_GB) {
+            for (int r = 0; r < RPI; r++) {
+                if (!live[r]) continue;
+                T* yr = y + (row0 + r) * cols;
+                const float mean = s[2 * r] * rc, m2 = s[2 * r + 1] * rc;
+                const float var = fmaxf(m2 - mean * mean, 0.f);
+                const float rstd = 1.0f / sqrtf(var + eps);
 #pragma unroll
-                        for (int e = 0; e < N; e++) { const float w = gm[k][e] * rstd; o[e] = v[k][e] * w + (bt[k][e] - mean * w); }
-                    } else {
-                        float g1[N], b1[N];
-                        load_gb<N>(gamma, beta, vi * N, g1, b1);
+                for (int k = 0; k < VPT; k++) {
+                    const int vi = t + k * GROUP;
+                    if (vi < nvec) {
+                        float o[N];
+                        if constexpr (CACHE_GB) {
 #pragma unroll
-                        for (int e = 0; e < N; e++) { const float w = g1[e] * rstd; o[e] = v[k][e] * w + (b1[e] - mean * w); }
+                            for (int e = 0; e < N; e++) { const float w = gm[k][e] * rstd; o[e] = v[r][k][e] * w + (bt[k][e] - mean * w); }
+                        } else {
+                            float g1[N], b1[N];
+                            load_gb<N>(gamma, beta, vi * N, g1, b1);
+#pragma unroll
+                            for (int e = 0; e < N; e++) { const float w = g1[e] * rstd; o[e] = v[r][k][e] * w + (b1[e] - mean * w); }
+                        }
+                        Vec16<T>::store(yr + (int64_t)vi * N, o);
                     }
-                    Vec16<T>::store(yr + (int64_t)vi * N, o);
                 }
             }
         } else {
-            float m = -FLT_MAX;
+            float m[RPI];
 #pragma unroll
-            for (int k = 0; k < VPT; k++)
+            for (int r = 0; r < RPI; r++) {
+                m[r] = -FLT_MAX;
 #pragma unroll
-                for (int e = 0; e < N; e++) m = fmaxf(m, v[k][e]);
-            m = group_reduce<GROUP, true>(m, sm);
-            float s = 0.f;
+                for (int k = 0; k < VPT; k++)
 #pragma unroll
-            for (int k = 0; k < VPT; k++)
+                    for (int e = 0; e < N; e++) m[r] = fmaxf(m[r], v[r][k][e]);
+            }
+            group_reduce_n<GROUP, true, RPI>(m, sm);
+            float sum[RPI];
 #pragma unroll
-                for (int e = 0; e < N; e++) {
-                    const float a = v[k][e] - m;
-                    const float ex = __expf(a);             // ex2.approx(a * log2 e): relative error ~1e-6 for a in [-88, 0]
-                    s += (t + k * GROUP < nvec) ? ex : 0.f;
-                    v[k][e] = (OP == ROW_SOFTMAX) ? ex : a;
-                }
-            s = group_reduce<GROUP, false>(s, sm);
-            const float ls = logf(s), inv = 1.0f / s;
+            for (int r = 0; r < RPI; r++) {
+                sum[r] = 0.f;
 #pragma unroll
-            for (int k = 0; k < VPT; k++) {
-                const int vi = t + k * GROUP;
-                if (vi < nvec) {
-                    float o[N];
+                for (int k = 0; k < VPT; k++)
 #pragma unroll
-                    for (int e = 0; e < N; e++) o[e] = (OP == ROW_SOFTMAX) ? v[k][e] * inv : v[k][e] - ls;
-                    Vec16<T>::store(yr + (int64_t)vi * N, o);
+                    for (int e = 0; e < N; e++) {
+                        const float a = v[r][k][e] - m[r];
+                        const float ex = __expf(a);         // ex2.approx(a * log2 e): relative error ~1e-6 for a in [-88, 0]
+                        sum[r] += (t + k * GROUP < nvec) ? ex : 0.f;
+                        v[r][k][e] = (OP == ROW_SOFTMAX) ? ex : a;
+                    }
+            }
+            group_reduce_n<GROUP, false, RPI>(sum, sm);
+#pragma unroll
+            for (int r = 0; r < RPI; r++) {
+                if (!live[r]) continue;
+                T* yr = y + (row0 + r) * cols;
+                const float ls = logf(sum[r]), inv = 1.0f / sum[r];
+#pragma unroll
+                for (int k = 0; k < VPT; k++) {
+                    const int vi = t + k * GROUP;
+                    if (vi < nvec) {
+                        float o[N];
+#pragma unroll
+                        for (int e = 0; e < N; e++) o[e] = (OP == ROW_SOFTMAX) ? v[r][k][e] * inv : v[r][k][e] - ls;
+                        Vec16<T>::store(yr + (int64_t)vi * N, o);
+                    }
                 }
             }
         }
