@@ -136,3 +136,33 @@ def all_reduce_buckets(tensors, bucket_bytes=None):
 
 def _round_up(n, m):
     return (n + m - 1) // m * m
+
+
+# ---- departure of a rank between steps -------------------------------------------------------------------------------
+# A collective whose peer is gone can only end in a time-out (NCCL) or a bounded wait running out (the peer kernel).
+# Ranks therefore announce that they leave through the job's key-value store, between steps and with nothing of theirs
+# in flight, and the others ask the store before their next step instead of finding out on the device.
+def _store():
+    return tdist.distributed_c10d._get_default_store()
+
+
+def leave():
+    """Announces that this rank stops taking part (call between steps; then exit or idle)."""
+    if in_mpi():
+        _store().set(f"b200jt/left/{rank()}", "1")
+
+
+def departed():
+    """Ranks that have announced their departure (one non-blocking store query per rank)."""
+    if not in_mpi():
+        return []
+    st = _store()
+    return [r for r in range(world_size()) if r != rank() and st.check([f"b200jt/left/{r}"])]
+
+
+def check_peers():
+    """Raises before the next collective is launched if a peer has left."""
+    gone = departed()
+    if gone:
+        from ._capi import B200Error
+        raise B200Error(f"rank(s) {gone} left the job: the next collective would never complete")

@@ -57,6 +57,24 @@ def main():
     p._data = torch.full((3,), float(10 + rank))
     b = dist.mpi_broadcast(p, 0)
     assert torch.equal(b._data, torch.full((3,), 10.0))
+    # 7. a rank leaves between steps: the other one learns of it from the store, not from a collective that hangs
+    import time
+    assert dist.departed() == []
+    dist.check_peers()
+    torch.distributed.barrier()
+    if rank == 1:
+        dist.leave()
+        print(f"rank {rank} ok")
+        return
+    deadline = time.time() + 30
+    while dist.departed() != [1] and time.time() < deadline:
+        time.sleep(0.05)
+    assert dist.departed() == [1]
+    try:
+        dist.check_peers()
+        raise AssertionError("check_peers did not raise")
+    except jt.B200Error as e:
+        assert "rank(s) [1] left" in str(e)
     print(f"rank {rank} ok")
 
 
