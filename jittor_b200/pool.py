@@ -140,3 +140,52 @@ def avg_pool2d(x, kernel_size, stride=None, padding=0, ceil_mode=False, count_in
 
 def max_pool2d(x, kernel_size, stride=None, padding=0, dilation=None, return_indices=None, ceil_mode=False):
     return MaxPool2d(kernel_size, stride, padding, dilation, return_indices, ceil_mode)(x)
+
+
+def _adaptive_geometry(x, output_size, who):
+    if isinstance(output_size, int):
+        oh = ow = output_size
+    elif isinstance(output_size, (tuple, list)):
+        oh = x.shape[2] if output_size[0] is None else output_size[0]
+        ow = x.shape[3] if output_size[1] is None else output_size[1]
+    else:
+        raise TypeError(f"{who} only support int, tuple or list input. Not support {type(output_size)} yet.")
+    return oh, ow
+
+
+def _adaptive(x, output_size, op, who):
+    """AdaptiveAvgPool2d / AdaptiveMaxPool2d.execute (python/jittor/pool.py:405-466): stride floor(H/oh), window
+    H - (oh-1)*stride, written with the meta-operators exactly as the reference does (so the gradient is theirs too)."""
+    x = V.to_var(x)
+    oh, ow = _adaptive_geometry(x, output_size, who)
+    if oh == 1 and ow == 1:
+        return x.reduce(op, [2, 3], keepdims=True)
+    N, Cn, H, W = x.shape
+    sh, sw = H // oh, W // ow
+    ksh, ksw = H - (oh - 1) * sh, W - (ow - 1) * sw
+    h, w = (H - ksh) // sh + 1, (W - ksw) // sw + 1
+    xx = x.reindex([N, Cn, h, w, ksh, ksw], ["i0", "i1", f"i2*{sh}+i4", f"i3*{sw}+i5"])
+    return xx.reduce(op, [4, 5])
+
+
+class AdaptiveAvgPool2d(Module):
+    def __init__(self, output_size):
+        self.output_size = output_size
+
+    def execute(self, x):
+        return _adaptive(x, self.output_size, "mean", "AdaptiveAvgPool2d")
+
+
+class AdaptiveMaxPool2d(Module):
+    def __init__(self, output_size, return_indices=False):
+        self.output_size, self.return_indices = output_size, return_indices
+
+    def execute(self, x):
+        if self.return_indices:
+            x = V.to_var(x)
+            oh, ow = _adaptive_geometry(x, self.output_size, "AdaptiveMaxPool2d")
+            if not (oh == 1 and ow == 1):
+                sh, sw = x.shape[2] // oh, x.shape[3] // ow
+                k = (x.shape[2] - (oh - 1) * sh, x.shape[3] - (ow - 1) * sw)
+                return MaxPool2d(kernel_size=k, stride=(sh, sw), return_indices=True)(x)
+        return _adaptive(x, self.output_size, "maximum", "AdaptiveMaxPool2d")

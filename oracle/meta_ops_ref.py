@@ -1000,3 +1000,21 @@ def conv_grad(x, w, dy, stride, padding, dilation, want_dw):
         return reduce(binary(xx, dm, "multiply"), "add", [0, 3, 4])
     ww = broadcast(w, shape7, [0, 3, 4])
     return reindex_reduce(binary(ww, dm, "multiply"), "add", list(x.shape), idx)
+
+
+def adaptive_pool2d(x, output_size, op):
+    """AdaptiveAvgPool2d / AdaptiveMaxPool2d.execute, python/jittor/pool.py:405-466, from this file's reindex + reduce."""
+    x = np.asarray(x)
+    N, C, H, W = x.shape
+    if isinstance(output_size, int):
+        oh = ow = output_size
+    else:
+        oh = H if output_size[0] is None else output_size[0]
+        ow = W if output_size[1] is None else output_size[1]
+    if oh == 1 and ow == 1:
+        return reduce(x, op, [2, 3], True)
+    sh, sw = H // oh, W // ow
+    ksh, ksw = H - (oh - 1) * sh, W - (ow - 1) * sw
+    h, w = (H - ksh) // sh + 1, (W - ksw) // sw + 1
+    xx = reindex(x, [N, C, h, w, ksh, ksw], ["i0", "i1", f"i2*{sh}+i4", f"i3*{sw}+i5"])
+    return reduce(xx, op, [4, 5])

@@ -291,6 +291,20 @@ do_conv_grad("conv_grad_s2_p1", f32(2, 4, 11, 9), wgt(6, 4, 3, 3), 2, 1, 1)
 do_conv_grad("conv_grad_dilated", f32(1, 3, 12, 12), wgt(4, 3, 3, 3), 1, 2, 2)
 do_conv_grad("conv_grad_1x1_s2", f32(2, 8, 8, 8), wgt(5, 8, 1, 1), 2, 0, 1)
 
+
+
+# ---- adaptive pooling (meta-operator lowering in the reference) ----------------------------------------------------
+def do_adaptive(name, x, output_size, op):
+    layer = (jpool.AdaptiveAvgPool2d if op == "mean" else jpool.AdaptiveMaxPool2d)(output_size)
+    case(name, "adaptive_pool", {"output_size": list(output_size) if isinstance(output_size, tuple) else output_size, "op": op},
+         [x], to_np(layer(to_jt(x))))
+
+
+do_adaptive("adaptive_avg_7", f32(2, 3, 21, 30), 7, "mean")
+do_adaptive("adaptive_avg_1", f32(2, 3, 9, 11), 1, "mean")
+do_adaptive("adaptive_avg_rect_none", f32(1, 4, 10, 13), (None, 4), "mean")
+do_adaptive("adaptive_max_5x3", f32(2, 3, 17, 10), (5, 3), "maximum")
+
 np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
 with open(os.path.join(HERE, "next_ops.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_golden_next.py", "reference_version": jt.__version__, "cases": CASES},

@@ -132,6 +132,8 @@ def run_case(c, be):
                                   a["groups"], _kw(a["dilation"]), ins[2] if a["bias"] else None)
     elif op in ("conv_dgrad", "conv_wgrad"):
         got = be.conv_grad(ins[0], ins[1], ins[2], a["stride"], a["padding"], a["dilation"], op == "conv_wgrad")
+    elif op == "adaptive_pool":
+        got = be.adaptive_pool2d(ins[0], _kw(a["output_size"]), a["op"])
     elif op == "optim":
         kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in a.items() if k not in ("kind", "steps")}
         got = be.optim_steps(ins[0], ins[1], ins[2], a["kind"], a["steps"], **kw)

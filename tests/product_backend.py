@@ -16,6 +16,12 @@ def _jt_slices(slices):
 
 class ProductBackend:
     @staticmethod
+    def adaptive_pool2d(x, output_size, op):
+        from jittor_b200 import pool
+        layer = (pool.AdaptiveAvgPool2d if op == "mean" else pool.AdaptiveMaxPool2d)(output_size)
+        return _np(layer(jt.array(x)))
+
+    @staticmethod
     def conv_grad(x, w, dy, stride, padding, dilation, want_dw):
         vx, vw = jt.array(x), jt.array(w)
         y = nn.conv2d(vx, vw, None, stride, padding, dilation)
