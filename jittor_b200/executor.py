@@ -585,6 +585,57 @@ def _softmax_rows(u, r):
     return (u.numel() // cols if cols else 0), cols
 
 
+def _match_pool(v):
+    """y = reduce.{maximum,minimum,mean} over axes [4,5] of reindex(x, [N,C,h,w,kh,kw], [i0, i1, i2*sh-ph+i4, i3*sw-pw+i5]):
+    the pooling lowering of python/jittor/pool.py:187-197 (also the adaptive pools, :419-432) as one pooling-kernel
+    launch instead of a materialised window tensor. Padding reads as 0 in that lowering, which the kernel reproduces for
+    mean (divide by kh*kw); maximum / minimum are only relayed when no window leaves the input."""
+    if not _node(v, "reduce") or v._op.attrs["op"] not in ("maximum", "minimum", "mean"):
+        return None
+    if v._op.attrs["reduce_mask"] != 0b110000 or v._op.attrs["keepdims_mask"] != 0:
+        return None
+    rx = v._op.inputs[0]
+    if not _node(rx, "reindex") or rx.ndim != 6 or len(rx._op.inputs) != 1:
+        return None
+    a = rx._op.attrs
+    x = rx._op.inputs[0]
+    if x.ndim != 4 or a["overflow_conditions"] or a["overflow_value"] != 0 or x.dtype != v.dtype:
+        return None
+    if str(x.dtype) not in ("float32", "float64", "float16", "bfloat16"):
+        return None
+    N, Cn, h, w, kh, kw = rx.shape
+    if list(x.shape[:2]) != [N, Cn] or min(h, w, kh, kw) < 1:
+        return None
+    aff = index_affine(list(rx.shape), list(x.shape), a["indexes"])
+    if aff is None:
+        return None
+    coef, c0 = aff
+    if coef[0] != [1, 0, 0, 0, 0, 0] or c0[0] != 0 or coef[1] != [0, 1, 0, 0, 0, 0] or c0[1] != 0:
+        return None
+    if coef[2][0] or coef[2][1] or coef[2][3] or coef[2][5] or coef[3][0] or coef[3][1] or coef[3][2] or coef[3][4]:
+        return None
+    sh, sw, ph, pw = coef[2][2], coef[3][3], -c0[2], -c0[3]
+    if (kh > 1 and coef[2][4] != 1) or (kw > 1 and coef[3][5] != 1):
+        return None
+    sh, sw = (sh if h > 1 else max(sh, 1)), (sw if w > 1 else max(sw, 1))
+    if sh < 1 or sw < 1 or ph < 0 or pw < 0:
+        return None
+    H, W = x.shape[2], x.shape[3]
+    op = v._op.attrs["op"]
+    inside = ph == 0 and pw == 0 and (h - 1) * sh + kh <= H and (w - 1) * sw + kw <= W
+    if op != "mean" and not inside:
+        return None
+
+    def run():
+        xd = x._data.view(list(x.shape))
+        out = _empty([N, Cn, h, w], x.dtype)
+        C.check(C.lib.b200jt_pool2d(C.desc(xd), C.desc(out), ctypes.c_void_p(0), op.encode(), kh, kw, sh, sw, ph, pw, 1,
+                                    C.stream_ptr()), f"pool2d x{list(x.shape)} k{(kh, kw)} s{(sh, sw)} p{(ph, pw)}")
+        return out
+
+    return Plan([x], run)
+
+
 def _match_softmax(v):
     """softmax / log-softmax over the last axis (or over everything) written with meta-ops as in
     python/jittor/nn.py:527-535, including the float32 round trip of bfloat16 inputs."""
@@ -851,4 +902,4 @@ def _match_batchnorm(v):
     return Plan(leaves, run)
 
 
-_MATCHERS = [_match_conv, _match_conv_dgrad, _match_conv_wgrad, _match_matmul, _match_batched_matmul, _match_softmax, _match_layernorm, _match_batchnorm]
+_MATCHERS = [_match_conv, _match_conv_dgrad, _match_conv_wgrad, _match_pool, _match_matmul, _match_batched_matmul, _match_softmax, _match_layernorm, _match_batchnorm]

@@ -93,3 +93,23 @@ def test_optimizer_bookkeeping_without_a_device():
             self.shared = self.first.weight            # the same Var twice is one parameter
 
     assert len(Net().parameters()) == 6
+
+
+def test_pooling_lowering_is_recognised():
+    """reduce over [4,5] of the window reindex (python/jittor/pool.py:187-197, :419-432) becomes one pooling launch;
+    maximum with padding is not relayed (the lowering reads padding as 0, the kernel clips the window)."""
+    x = jt.Var([2, 3, 10, 12], "float32")
+    assert executor._match_pool(pool.avg_pool2d(x, 2)) is not None
+    assert executor._match_pool(pool.avg_pool2d(x, 3, 2, 1)) is not None
+    assert executor._match_pool(pool.AdaptiveAvgPool2d(5)(x)) is not None
+    assert executor._match_pool(pool.AdaptiveMaxPool2d((5, 3))(x)) is not None
+    saved = pool.pool_use_code_op
+    try:
+        pool.pool_use_code_op = False
+        assert executor._match_pool(pool.max_pool2d(x, 2, 2, 0)) is not None
+        assert executor._match_pool(pool.max_pool2d(x, 3, 2, 1)) is None
+    finally:
+        pool.pool_use_code_op = saved
+    assert executor._match_pool(x.reindex([2, 3, 5, 6, 2, 2], ["i0", "i1", "i2*2+i4", "i3*2+i5"]).sum([4, 5])) is None
+    bf = jt.Var([2, 3, 10, 12], "bfloat16")
+    assert executor._match_pool(pool.avg_pool2d(bf, 2)) is None            # float32 result of a bf16 reduce: not the relay
