@@ -595,11 +595,20 @@ def _match_pool(v):
     if v._op.attrs["reduce_mask"] != 0b110000 or v._op.attrs["keepdims_mask"] != 0:
         return None
     rx = v._op.inputs[0]
+    # 16-bit mean / add: the reduce constructor widens to float32 first (python/jittor/src/ops/reduce_op.cc:260-266) and the
+    # caller narrows the result again, so rounding the kernel's float32 accumulator to 16 bits here loses nothing
+    widened = _node(rx, "unary", op="float32") and str(v.dtype) == "float32"
+    if widened:
+        rx = rx._op.inputs[0]
     if not _node(rx, "reindex") or rx.ndim != 6 or len(rx._op.inputs) != 1:
         return None
     a = rx._op.attrs
     x = rx._op.inputs[0]
-    if x.ndim != 4 or a["overflow_conditions"] or a["overflow_value"] != 0 or x.dtype != v.dtype:
+    if x.ndim != 4 or a["overflow_conditions"] or a["overflow_value"] != 0:
+        return None
+    if widened and str(x.dtype) not in ("float16", "bfloat16"):
+        return None
+    if not widened and x.dtype != v.dtype:
         return None
     if str(x.dtype) not in ("float32", "float64", "float16", "bfloat16"):
         return None
@@ -631,7 +640,7 @@ def _match_pool(v):
         out = _empty([N, Cn, h, w], x.dtype)
         C.check(C.lib.b200jt_pool2d(C.desc(xd), C.desc(out), ctypes.c_void_p(0), op.encode(), kh, kw, sh, sw, ph, pw, 1,
                                     C.stream_ptr()), f"pool2d x{list(x.shape)} k{(kh, kw)} s{(sh, sw)} p{(ph, pw)}")
-        return out
+        return _cast(out, v.dtype)
 
     return Plan([x], run)
 

@@ -238,3 +238,25 @@ def test_pool_other_dtypes_and_windows(jt, ref, dtype, k, s, p):
         dx = jt.grad((y * jt.array(torch.from_numpy(dy).to(td))).sum(), vx).torch().double().cpu().numpy()
         wdx = ref.pool2d_backward(x, dy, k, op, s, p, op == "mean")
         assert np.allclose(dx, wdx, rtol=2e-2 if dtype != "float64" else 1e-12, atol=5e-2 if dtype != "float64" else 1e-12)
+
+
+def test_average_pooling_lowering_bf16_and_adaptive(jt, ref):
+    """Floor-mode avg_pool2d and the adaptive pools are the reindex + reduce lowering in the reference; the executor
+    relays them to the pooling kernel. bf16: mean accumulated in float32, rounded once."""
+    from jittor_b200 import pool
+    rng = np.random.default_rng(12)
+    x = rng.normal(size=(3, 5, 20, 26)).astype(np.float32)
+    xb = torch.from_numpy(x).bfloat16()
+    got = pool.avg_pool2d(jt.array(xb), 3, 2, 1).torch().float().cpu().numpy()
+    want = torch.from_numpy(ref.pool2d(xb.float().numpy(), 3, "mean", 2, 1)).bfloat16().float().numpy()
+    assert np.allclose(got, want, rtol=1e-2, atol=1e-2)
+    got = pool.AdaptiveAvgPool2d((4, None))(jt.array(x)).numpy()
+    assert np.allclose(got, ref.adaptive_pool2d(x, (4, None), "mean"), rtol=1e-5, atol=1e-6)
+    got = pool.AdaptiveMaxPool2d(5)(jt.array(x)).numpy()
+    assert np.array_equal(got, ref.adaptive_pool2d(x, 5, "maximum"))
+    # gradient of the lowering still follows the meta-operator rules
+    vx = jt.array(x)
+    y = pool.avg_pool2d(vx, 2)
+    dy = rng.normal(size=tuple(y.shape)).astype(np.float32)
+    dx = jt.grad((y * jt.array(dy)).sum(), vx).numpy()
+    assert np.allclose(dx, ref.pool2d_backward(x, dy, 2, "mean"), rtol=1e-5, atol=1e-6)

@@ -111,5 +111,8 @@ def test_pooling_lowering_is_recognised():
     finally:
         pool.pool_use_code_op = saved
     assert executor._match_pool(x.reindex([2, 3, 5, 6, 2, 2], ["i0", "i1", "i2*2+i4", "i3*2+i5"]).sum([4, 5])) is None
+    # 16-bit mean: cast(float32) -> reduce -> cast back (reduce_op.cc:260-266); the inner reduce is the relayed node
     bf = jt.Var([2, 3, 10, 12], "bfloat16")
-    assert executor._match_pool(pool.avg_pool2d(bf, 2)) is None            # float32 result of a bf16 reduce: not the relay
+    y = pool.avg_pool2d(bf, 2)
+    assert str(y.dtype) == "bfloat16" and y._op.kind == "unary"
+    assert executor._match_pool(y._op.inputs[0]) is not None
