@@ -165,6 +165,38 @@ def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
     return y
 
 
+def conv1d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """Conv1d.execute (python/jittor/nn.py:1097-1125): the signal gets a trailing axis of extent 1, the weight
+    [O, C/groups, K] likewise, and the 2-D convolution runs with kernel (K, 1), stride (s, 1), padding (p, 0)."""
+    x, weight = to_var(x), to_var(weight)
+    if x.ndim != 3:
+        raise ValueError("Input shape must be `(N, C, L)`!")
+    N, C, L = x.shape
+    O, Cg, K = weight.shape
+    y = conv2d(x.reshape([N, C, L, 1]), weight.reshape([O, Cg, K, 1]), bias, (stride, 1), (padding, 0), (dilation, 1), groups)
+    return y.reshape([N, O, y.shape[2]])
+
+
+class Conv1d(Module):
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1, bias=True):
+        assert in_channels > 0, "in_channels must be positive"
+        assert out_channels > 0, "out_channels must be positive"
+        if groups <= 0:
+            raise ValueError("groups must be a positive integer")
+        assert in_channels % groups == 0, "in_channels must be divisible by groups"
+        assert out_channels % groups == 0, "out_channels must be divisible by groups"
+        self.in_channels, self.out_channels, self.groups = in_channels, out_channels, groups
+        self.kernel_size, self.stride, self.padding, self.dilation = kernel_size, stride, padding, dilation
+        rng = np.random.default_rng(0)
+        bound = 1.0 / np.sqrt(in_channels * kernel_size)
+        self.weight = V.array(rng.uniform(-bound, bound, (out_channels, in_channels // groups, kernel_size)).astype(np.float32))
+        self.bias = V.array(rng.uniform(-bound, bound, (out_channels,)).astype(np.float32)) if bias else None
+
+    def execute(self, x):
+        assert x.shape[1] == self.in_channels
+        return conv1d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+
+
 def conv_transpose2d(x, weight, bias=None, stride=1, padding=0, output_padding=0, groups=1, dilation=1):
     """ConvTranspose.execute (python/jittor/nn.py:1429-1491): weight is [Cin, Cout/groups, Kh, Kw]; x and w are broadcast
     (groups == 1) or re-indexed (groups > 1) to the full loop nest, multiplied, and scattered into the output with

@@ -1018,3 +1018,23 @@ def adaptive_pool2d(x, output_size, op):
     h, w = (H - ksh) // sh + 1, (W - ksw) // sw + 1
     xx = reindex(x, [N, C, h, w, ksh, ksw], ["i0", "i1", f"i2*{sh}+i4", f"i3*{sw}+i5"])
     return reduce(xx, op, [4, 5])
+
+
+def conv1d(x, w, stride=1, padding=0, dilation=1, groups=1, bias=None):
+    """Conv1d.execute, python/jittor/nn.py:1097-1125: a 2-D convolution with a trailing axis of extent 1."""
+    x, w = np.asarray(x), np.asarray(w)
+    x4, w4 = x[..., None], w[..., None]
+    s, p, d = (stride, 1), (padding, 0), (dilation, 1)
+    if groups == 1:
+        N, C, L, _ = x4.shape
+        O, _, K, _ = w4.shape
+        oh = (L + p[0] * 2 - K * d[0] + d[0] - 1) // s[0] + 1
+        shape7 = [N, O, C, oh, 1, K, 1]
+        xx = reindex(x4, shape7, ["i0", "i2", f"i3*{s[0]}-{p[0]}+i5*{d[0]}", "i4*1-0+i6*1"])
+        ww = broadcast(w4, shape7, [0, 3, 4])
+        y = reduce(binary(xx, ww, "multiply"), "add", [2, 5, 6])
+        if bias is not None:
+            y = binary(y, broadcast(np.asarray(bias), y.shape, [0, 2, 3]), "add")
+    else:
+        y = conv2d_grouped(x4, w4, s, p, d, groups, bias)
+    return y[..., 0]

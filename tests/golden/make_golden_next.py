@@ -305,6 +305,24 @@ do_adaptive("adaptive_avg_1", f32(2, 3, 9, 11), 1, "mean")
 do_adaptive("adaptive_avg_rect_none", f32(1, 4, 10, 13), (None, 4), "mean")
 do_adaptive("adaptive_max_5x3", f32(2, 3, 17, 10), (5, 3), "maximum")
 
+
+
+# ---- Conv1d through the reference's layer ---------------------------------------------------------------------------
+def do_conv1d(name, x, w, stride, padding, dilation, groups, bias=None):
+    m = nn.Conv1d(x.shape[1], w.shape[0], w.shape[2], stride, padding, dilation, groups, bias is not None)
+    m.weight = to_jt(w)
+    if bias is not None:
+        m.bias = to_jt(bias)
+        m._conv[0].bias = m.bias
+    y = m(to_jt(x))
+    case(name, "conv1d", dict(stride=stride, padding=padding, dilation=dilation, groups=groups, bias=bias is not None),
+         [x, w] + ([bias] if bias is not None else []), to_np(y))
+
+
+do_conv1d("conv1d_basic", f32(2, 6, 40), wgt(8, 6, 3), 1, 0, 1, 1)
+do_conv1d("conv1d_s2_p1_bias", f32(3, 4, 33), wgt(5, 4, 5), 2, 1, 1, 1, f32(5))
+do_conv1d("conv1d_dilated_grouped", f32(2, 8, 50), wgt(12, 2, 3), 1, 2, 2, 4)
+
 np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
 with open(os.path.join(HERE, "next_ops.json"), "w") as f:
     json.dump({"generator": "tests/golden/make_golden_next.py", "reference_version": jt.__version__, "cases": CASES},

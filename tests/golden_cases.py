@@ -134,6 +134,8 @@ def run_case(c, be):
         got = be.conv_grad(ins[0], ins[1], ins[2], a["stride"], a["padding"], a["dilation"], op == "conv_wgrad")
     elif op == "adaptive_pool":
         got = be.adaptive_pool2d(ins[0], _kw(a["output_size"]), a["op"])
+    elif op == "conv1d":
+        got = be.conv1d(ins[0], ins[1], a["stride"], a["padding"], a["dilation"], a["groups"], ins[2] if a["bias"] else None)
     elif op == "optim":
         kw = {k: (tuple(v) if isinstance(v, list) else v) for k, v in a.items() if k not in ("kind", "steps")}
         got = be.optim_steps(ins[0], ins[1], ins[2], a["kind"], a["steps"], **kw)

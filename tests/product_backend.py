@@ -16,6 +16,11 @@ def _jt_slices(slices):
 
 class ProductBackend:
     @staticmethod
+    def conv1d(x, w, stride, padding, dilation, groups, bias=None):
+        return _np(nn.conv1d(jt.array(x), jt.array(w), None if bias is None else jt.array(bias), stride, padding, dilation,
+                             groups))
+
+    @staticmethod
     def adaptive_pool2d(x, output_size, op):
         from jittor_b200 import pool
         layer = (pool.AdaptiveAvgPool2d if op == "mean" else pool.AdaptiveMaxPool2d)(output_size)
