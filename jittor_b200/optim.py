@@ -157,3 +157,52 @@ class Adam(Optimizer):
                 step_size = lr * math.sqrt(1 - b1 ** n) / (1 - b0 ** n)
                 p.update(p - m * step_size / (V.unary(v, "sqrt") + eps))
         self.post_step()
+
+
+class RMSprop(Optimizer):
+    """python/jittor/optim.py:347-387."""
+
+    def __init__(self, params, lr=1e-2, eps=1e-8, alpha=0.99):
+        super().__init__(params, lr)
+        self.eps, self.alpha = eps, alpha
+        for pg in self.param_groups:
+            pg["values"] = [V.zeros(list(p.shape), p.dtype) for p in pg["params"]]
+
+    def add_param_group(self, group):
+        group["values"] = [V.zeros(list(p.shape), p.dtype) for p in group["params"]]
+        super().add_param_group(group)
+
+    def step(self, loss=None, retain_graph=False):
+        self.pre_step(loss, retain_graph)
+        for pg in self.param_groups:
+            lr, eps, alpha = pg.get("lr", self.lr), pg.get("eps", self.eps), pg.get("alpha", self.alpha)
+            for i, (p, g) in enumerate(zip(pg["params"], pg["grads"])):
+                if p.is_stop_grad():
+                    continue
+                v = pg["values"][i]
+                v.update(v * alpha + g * g * (1 - alpha))
+                p.update(p - g * lr / (V.unary(v, "sqrt") + eps))
+        self.post_step()
+
+
+class AdamW(Adam):
+    """python/jittor/optim.py:440-491: decoupled weight decay, bias corrections applied to the denominator."""
+
+    def step(self, loss=None, retain_graph=False):
+        self.pre_step(loss, retain_graph)
+        n = float(self.n_step)
+        for pg in self.param_groups:
+            lr = pg.get("lr", self.lr)
+            eps = pg.get("eps", self.eps)
+            weight_decay = pg.get("weight_decay", self.weight_decay)
+            b0, b1 = pg.get("betas", self.betas)
+            for i, (p, g) in enumerate(zip(pg["params"], pg["grads"])):
+                if p.is_stop_grad():
+                    continue
+                v, m = pg["values"][i], pg["m"][i]
+                p.update(p * (1 - lr * weight_decay))
+                m.update(m * b0 + g * (1 - b0))
+                v.update(v * b1 + g * g * (1 - b1))
+                denom = V.unary(v, "sqrt") / math.sqrt(1 - b1 ** n) + eps
+                p.update(p - m * (lr / (1 - b0 ** n)) / denom)
+        self.post_step()

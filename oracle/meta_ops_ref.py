@@ -829,7 +829,7 @@ def gather(x, dim, index):
 
 # --------------------------------------------------------------------------- optimiser steps
 def optim_steps(x, y, w, kind, steps, lr, momentum=0, weight_decay=0, dampening=0, nesterov=False,
-                eps=1e-8, betas=(0.9, 0.999)):
+                eps=1e-8, betas=(0.9, 0.999), alpha=0.99):
     """`steps` updates of w on loss = sum((x @ w - y)^2) / N with the reference's SGD (python/jittor/optim.py:325-345)
     or Adam (:420-437) formulas, in float32 like the reference's graph; the gradient is 2/N * x^T (x w - y)."""
     f = np.float32
@@ -842,6 +842,16 @@ def optim_steps(x, y, w, kind, steps, lr, momentum=0, weight_decay=0, dampening=
             dp = w * f(weight_decay) + g
             v = f(momentum) * v + dp * f(1 - dampening)
             w = w - (dp + f(momentum) * v) * f(lr) if nesterov else w - v * f(lr)
+        elif kind == "rmsprop":
+            v = f(alpha) * v + f(1 - alpha) * g * g                                   # optim.py:384-385
+            w = w - f(lr) * g / (np.sqrt(v) + f(eps))
+        elif kind == "adamw":
+            b0, b1 = betas                                                            # optim.py:471-491
+            w = w * f(1 - lr * weight_decay)
+            m = f(b0) * m + f(1 - b0) * g
+            v = f(b1) * v + f(1 - b1) * g * g
+            denom = np.sqrt(v) / np.sqrt(f(1 - b1 ** n)) + f(eps)
+            w = w - f(lr / (1 - b0 ** n)) * m / denom
         else:
             b0, b1 = betas
             g = w * f(weight_decay) + g

@@ -176,7 +176,7 @@ def do_optim(name, kind, steps, **kw):
     x, y, w0 = f32(32, 6), f32(32, 3), f32(6, 3)
     w = to_jt(w0)
     vx, vy = to_jt(x), to_jt(y)
-    opt = (jt.optim.SGD if kind == "sgd" else jt.optim.Adam)([w], **kw)
+    opt = {"sgd": jt.optim.SGD, "adam": jt.optim.Adam, "adamw": jt.optim.AdamW, "rmsprop": jt.optim.RMSprop}[kind]([w], **kw)
     for _ in range(steps):
         d = jt.matmul(vx, w) - vy
         loss = (d * d).sum() * (1.0 / 32)
@@ -322,6 +322,11 @@ def do_conv1d(name, x, w, stride, padding, dilation, groups, bias=None):
 do_conv1d("conv1d_basic", f32(2, 6, 40), wgt(8, 6, 3), 1, 0, 1, 1)
 do_conv1d("conv1d_s2_p1_bias", f32(3, 4, 33), wgt(5, 4, 5), 2, 1, 1, 1, f32(5))
 do_conv1d("conv1d_dilated_grouped", f32(2, 8, 50), wgt(12, 2, 3), 1, 2, 2, 4)
+
+
+do_optim("adamw_wd", "adamw", 4, lr=0.02, weight_decay=0.1)
+do_optim("rmsprop_default", "rmsprop", 4, lr=0.01)
+do_optim("rmsprop_alpha", "rmsprop", 3, lr=0.02, eps=1e-6, alpha=0.9)
 
 np.savez_compressed(os.path.join(HERE, "next_ops.npz"), **ARRAYS)
 with open(os.path.join(HERE, "next_ops.json"), "w") as f:

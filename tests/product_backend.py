@@ -60,7 +60,7 @@ class ProductBackend:
         from jittor_b200 import optim
         w = jt.array(w)
         vx, vy = jt.array(x), jt.array(y)
-        opt = (optim.SGD if kind == "sgd" else optim.Adam)([w], **kw)
+        opt = {"sgd": optim.SGD, "adam": optim.Adam, "adamw": optim.AdamW, "rmsprop": optim.RMSprop}[kind]([w], **kw)
         for _ in range(steps):
             d = nn.matmul(vx, w) - vy
             loss = (d * d).sum() * (1.0 / x.shape[0])
