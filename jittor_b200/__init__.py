@@ -43,6 +43,11 @@ int = int32       # noqa: F821
 matmul = nn.matmul
 
 
+# the reference re-exports the pooling layers and optimisers from jittor.nn (python/jittor/nn.py:21-22)
+for _name in ("Pool", "MaxPool2d", "AvgPool2d", "AdaptiveAvgPool2d", "AdaptiveMaxPool2d", "pool", "avg_pool2d", "max_pool2d"):
+    setattr(nn, _name, getattr(pool, _name))
+for _name in ("Optimizer", "SGD", "Adam", "AdamW", "RMSprop"):
+    setattr(nn, _name, getattr(optim, _name))
 op_register._register_builtins()
 
 
