@@ -73,7 +73,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
-                "samples": len(self.samples), "window": "per-part timing, timed region and untimed repeats of the same step"}
+                "samples": len(self.samples), "window": "timed region and untimed repeats of the same step"}
 
 
 # =====================================================================================================
@@ -568,10 +568,6 @@ def main():
         for nm in names:
             wl.run(nm)
     barrier()
-    # clocks are sampled from here to the end of the timed region (one nvidia-smi query takes longer than a short
-    # timed region, so the per-part measurement, which runs the same kernels, is part of the sampled window)
-    clocks = ClockSampler(local)
-    clocks.__enter__()
     # (1) per-part times: direct launches with an event after every part
     psteps = min(args.steps, 10)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(psteps)]
@@ -607,6 +603,9 @@ def main():
             graph = None
             torch.cuda.synchronize()
     e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # clocks are sampled from here on: through the timed region and the untimed repeats of the same step that follow
+    clocks = ClockSampler(local)
+    clocks.__enter__()
     barrier()
     e_beg.record()
     for s in range(args.steps):
