@@ -106,47 +106,3 @@ class LocalJob:
             if c:
                 C.lib.b200jt_peer_comm_destroy(c)
         self._comms = (ctypes.c_void_p * self.world)()
-
-
-def _latency_table():
-    """Latency of the peer kernel next to NCCL for the message sizes of the path; run one process per GPU:
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m jittor_b200.peer"""
-    from . import dist
-    dist.init("nccl")
-    pc = dist.peer_comm()
-    rank = dist.rank()
-
-    def timeit(fn, n=200):
-        for _ in range(10):
-            fn()
-        tdist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device="cuda")
-        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
-        return t.item()
-
-    if rank == 0:
-        print(f"world {dist.world_size()}  peer kernel: {'yes' if pc else 'unavailable'}")
-        print(f"{'bytes':>10} {'peer us':>9} {'nccl us':>9}")
-    for nbytes in (2048, 16384, 262144, 1 << 20, 4 << 20, 8 << 20):
-        x = torch.ones(nbytes // 4, device="cuda")
-        y = torch.empty_like(x)
-        z = x.clone()
-        tp = timeit(lambda: pc.all_reduce(x, y)) if pc and pc.usable(x) else float("nan")
-        tn = timeit(lambda: tdist.all_reduce(z))
-        if rank == 0:
-            print(f"{nbytes:>10} {tp:>9.1f} {tn:>9.1f}", flush=True)
-    if C.lib.b200jt_device_status() != 0:
-        raise C.B200Error("a bounded wait expired during the measurement")
-    tdist.barrier()
-    tdist.destroy_process_group()
-
-
-if __name__ == "__main__":
-    _latency_table()

@@ -2,10 +2,10 @@
 
 It exists for callers that cannot allocate device memory at call time (allocator callbacks, loops with a
 frozen memory pool, plugin hosts without an allocation hook): its scratch is an array inside the library.
-The test runs it twice in a row on the same inputs and compares each result with the regular entry point
-(caller-provided workspace): bit-exact for int32, and the fp32 tolerance of the other parity tests
-(|d| <= 1e-5*|ref| + 1e-5*max|ref|), because the order of shared-memory atomics is not fixed. This file is
-named to be collected last, so a run that stops at the first failure has already run everything else.
+The test runs it twice in a row on the same inputs (the built-in array keeps what the previous call left in it)
+and compares each result with the CPU oracle's scatter loop and with the regular entry point (caller-provided
+workspace): bit-exact for int32, and the fp32 tolerance of the other parity tests
+(|d| <= 1e-5*|ref| + 1e-5*max|ref|), because the order of shared-memory atomics is not fixed.
 """
 import ctypes
 
@@ -37,17 +37,20 @@ def test_noalloc_matches_workspace_entry_point_twice(dtype, bins):
     idx = torch.randint(0, bins, (n,), device="cuda", dtype=torch.int32, generator=g)
     val = (torch.randn(n, device="cuda", generator=g) if dtype == torch.float32
            else torch.randint(0, 100, (n,), device="cuda", dtype=torch.int32, generator=g))
+    from oracle import c_oracle as co
     rc, want = _scatter(C, "b200jt_reindex_reduce", val, idx, bins)
     assert rc == 0, C.lib.b200jt_last_error()
+    oracle = torch.from_numpy(co.scatter_add(val.cpu().numpy(), idx.cpu().numpy(), bins)).cuda()
     for _ in range(2):                                   # the scratch keeps the previous call's rows
         rc, got = _scatter(C, "b200jt_reindex_reduce_noalloc", val, idx, bins)
         assert rc == 0, C.lib.b200jt_last_error()
-        if dtype == torch.int32:
-            assert torch.equal(got, want)
-        else:
-            w = want.double()
-            tol = 1e-5 * w.abs() + 1e-5 * w.abs().max()
-            assert bool(((got.double() - w).abs() <= tol).all())
+        for ref in (oracle, want):
+            if dtype == torch.int32:
+                assert torch.equal(got, ref)
+            else:
+                w = ref.double()
+                tol = 1e-5 * w.abs() + 1e-5 * w.abs().max()
+                assert bool(((got.double() - w).abs() <= tol).all())
 
 
 def test_noalloc_rejects_scratch_beyond_the_builtin_array():
