@@ -152,6 +152,14 @@ size_t b200jt_matmul_workspace(const b200jt_tensor* a, const b200jt_tensor* b, c
 int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
                   int trans_a, int trans_b, void* workspace, size_t workspace_bytes, void* stream);
 
+/* c[i] = op_a(a[i]) . op_b(b[i]), i < batch, in one launch: a [Ba, ., .], b [Bb, ., .], c [batch, M, N], Ba and Bb equal to
+ * batch or 1 (an operand with batch extent 1 is shared by all products). Replaces the relay
+ * CublasBatchedMatmulOp(Var* a, Var* b, bool trans_a, bool trans_b), python/jittor/extern/cuda/cublas/ops/cublas_batched_matmul_op.h:21,
+ * jit_run python/jittor/extern/cuda/cublas/ops/cublas_batched_matmul_op.cc:100-175 (cublasGemmStridedBatchedEx), which
+ * nn.matmul / nn.bmm call for [..., n, m] x [..., m, k] (python/jittor/nn.py:127-131). float32 or bfloat16, fp32 accumulation. */
+int b200jt_batched_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
+                          int trans_a, int trans_b, void* stream);
+
 /* Status word of the kernels that wait (matmul, conv2d, peer all-reduce): every wait inside them is bounded; if
  * one expires the kernel stops cleanly and records which (1 producer, 2 accumulator hand-back, 3 operand arrival,
  * 4 accumulator ready, 5 a peer's flag in b200jt_peer_all_reduce). Returns 0 if none did since the last call, and clears the word. Synchronises the device. It plays the
@@ -194,9 +202,12 @@ int b200jt_conv2d_backward_w(const b200jt_tensor* x, const b200jt_tensor* dy, co
 int b200jt_bn_stats(const b200jt_tensor* x, float* stats, void* stream);
 
 /* y = [relu](x*w + b), w = gamma/sqrt(var+eps), b = beta - mean*w with mean = stats[c]/count,
- * var = max(stats[C+c]/count - mean^2, 0): python/jittor/nn.py:680-683 (+ nn.relu). */
+ * var = max(stats[C+c]/count - mean^2, 0): python/jittor/nn.py:680-683 (+ nn.relu). If running_mean / running_var
+ * (float32 [C], both or neither) are given they are updated in place, running += (batch - running) * momentum, the
+ * two Var.update calls of python/jittor/nn.py:684-688. */
 int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, double count, const float* gamma, const float* beta,
-                    double eps, int relu, const b200jt_tensor* y, void* stream);
+                    double eps, int relu, const b200jt_tensor* y,
+                    float* running_mean, float* running_var, double momentum, void* stream);
 
 /* ---- pooling ----------------------------------------------------------------------------------------
  * y[n,c,oh,ow] = op over the window rows [oh*sh-ph, +kh) x columns [ow*sw-pw, +kw) of x[n,c], clipped to x. Replaces the
@@ -233,6 +244,7 @@ int b200jt_pool2d_backward_indices(const b200jt_tensor* x, const b200jt_tensor* 
 #define B200JT_PEER_MAX_RANKS 8
 size_t b200jt_peer_segment_bytes(size_t data_bytes);
 int b200jt_peer_segment_create(size_t data_bytes, void** segment, unsigned char* ipc_handle);
+int b200jt_peer_segment_destroy(void* segment);   /* only for a segment no communicator took over (set-up failed elsewhere) */
 int b200jt_peer_comm_create(int rank, int world, void* own_segment, const unsigned char* ipc_handles,
                             size_t data_bytes, double wait_ms, void** comm);
 int b200jt_peer_comm_destroy(void* comm);

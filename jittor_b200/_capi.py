@@ -65,18 +65,20 @@ SIGNATURES = [
     ("b200jt_layer_norm", _i, [_TP, _TP, _TP, _TP, _d, _vp]),
     ("b200jt_matmul_workspace", _sz, [_TP, _TP, _TP, _i, _i]),
     ("b200jt_matmul", _i, [_TP, _TP, _TP, _i, _i, _vp, _sz, _vp]),
+    ("b200jt_batched_matmul", _i, [_TP, _TP, _TP, _i, _i, _vp]),
     ("b200jt_device_status", _i, []),
     ("b200jt_conv2d_workspace", _sz, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i]),
     ("b200jt_conv2d", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i, _FP, _vp, _sz, _vp]),
     ("b200jt_conv2d_transpose", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_conv2d_backward_w", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_bn_stats", _i, [_TP, _FP, _vp]),
-    ("b200jt_bn_apply", _i, [_TP, _FP, _d, _FP, _FP, _d, _i, _TP, _vp]),
+    ("b200jt_bn_apply", _i, [_TP, _FP, _d, _FP, _FP, _d, _i, _TP, _FP, _FP, _d, _vp]),
     ("b200jt_pool2d", _i, [_TP, _TP, _vp, ctypes.c_char_p, _i, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_pool2d_backward", _i, [_TP, _TP, _TP, _TP, ctypes.c_char_p, _i, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_pool2d_backward_indices", _i, [_TP, _TP, _vp, _TP, _TP, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_peer_segment_bytes", _sz, [_sz]),
     ("b200jt_peer_segment_create", _i, [_sz, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    ("b200jt_peer_segment_destroy", _i, [_vp]),
     ("b200jt_peer_comm_create", _i, [_i, _i, _vp, ctypes.c_char_p, _sz, _d, ctypes.POINTER(_vp)]),
     ("b200jt_peer_comm_destroy", _i, [_vp]),
     ("b200jt_peer_max_bytes", _sz, [_vp]),

@@ -75,7 +75,8 @@ template <typename TX, typename TY>
 __global__ void __launch_bounds__(256)
 bn_apply_kernel(const TX* __restrict__ x, TY* __restrict__ y, const float* __restrict__ stats, float rcount,
                 const float* __restrict__ gamma, const float* __restrict__ beta, float eps, int relu,
-                int64_t planes, int C, int64_t HW) {
+                int64_t planes, int C, int64_t HW,
+                float* __restrict__ running_mean, float* __restrict__ running_var, float momentum) {
     extern __shared__ float ws_[];                 // [2][C]: scale, shift
     float* sw = ws_; float* sb = ws_ + C;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
@@ -83,6 +84,11 @@ bn_apply_kernel(const TX* __restrict__ x, TY* __restrict__ y, const float* __res
         const float var = fmaxf(stats[C + c] * rcount - mean * mean, 0.f);
         const float w = (gamma ? gamma[c] : 1.f) / sqrtf(var + eps);
         sw[c] = w; sb[c] = (beta ? beta[c] : 0.f) - mean * w;
+        // running += (batch - running) * momentum (python/jittor/nn.py:684-688), done once, by the first CTA
+        if (running_mean && blockIdx.x == 0) {
+            running_mean[c] += (mean - running_mean[c]) * momentum;
+            running_var[c] += (var - running_var[c]) * momentum;
+        }
     }
     __syncthreads();
     constexpr int V = IO<TX>::N > IO<TY>::N ? IO<TX>::N : IO<TY>::N;     // elements per thread step
@@ -143,13 +149,15 @@ extern "C" int b200jt_bn_stats(const b200jt_tensor* x, float* stats, void* strea
 }
 
 extern "C" int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, double count, const float* gamma, const float* beta,
-                               double eps, int relu, const b200jt_tensor* y, void* stream) {
+                               double eps, int relu, const b200jt_tensor* y,
+                               float* running_mean, float* running_var, double momentum, void* stream) {
     int N_, C; int64_t HW;
     int rc = nchw(x, &N_, &C, &HW);
     if (rc) return rc;
     B200JT_CHECK_ARG(valid_tensor(y) && numel(y) == numel(x) && (y->dtype == B200JT_FLOAT32 || y->dtype == B200JT_BFLOAT16),
                      "y must have x's size and be float32 or bfloat16");
     B200JT_CHECK_ARG(stats != nullptr && count > 0, "stats is NULL or count <= 0");
+    B200JT_CHECK_ARG((running_mean == nullptr) == (running_var == nullptr), "running_mean and running_var go together");
     if (numel(x) == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t planes = (int64_t)N_ * C;
@@ -157,7 +165,7 @@ extern "C" int b200jt_bn_apply(const b200jt_tensor* x, const float* stats, doubl
     unsigned grid = grid_for(numel(x) / 8 + 1, 256);
     const size_t smem = sizeof(float) * 2 * C;
     const float rc_ = (float)(1.0 / count);
-#define B200JT_BN(TX, TY) bn_apply_kernel<TX, TY><<<grid, 256, smem, st>>>((const TX*)x->ptr, (TY*)y->ptr, stats, rc_, gamma, beta, (float)eps, relu, planes, C, HW)
+#define B200JT_BN(TX, TY) bn_apply_kernel<TX, TY><<<grid, 256, smem, st>>>((const TX*)x->ptr, (TY*)y->ptr, stats, rc_, gamma, beta, (float)eps, relu, planes, C, HW, running_mean, running_var, (float)momentum)
     if (x->dtype == B200JT_FLOAT32) { if (y->dtype == B200JT_FLOAT32) B200JT_BN(float, float); else B200JT_BN(float, __nv_bfloat16); }
     else { if (y->dtype == B200JT_FLOAT32) B200JT_BN(__nv_bfloat16, float); else B200JT_BN(__nv_bfloat16, __nv_bfloat16); }
 #undef B200JT_BN

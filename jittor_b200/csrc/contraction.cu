@@ -48,6 +48,30 @@ extern "C" int b200jt_matmul(const b200jt_tensor* a, const b200jt_tensor* b, con
     return matmul_simt(a->ptr, b->ptr, c->ptr, a->dtype, M, N, K, trans_a != 0, trans_b != 0, st);
 }
 
+// c[i] = op_a(a[i]) . op_b(b[i]) for i < batch; a: [Ba, ., .], b: [Bb, ., .], c: [batch, M, N] with Ba, Bb in {1, batch}
+// (extent 1 shares the operand). One launch: tcgen05 for bfloat16 shapes its tiles cover, else the CUDA-core kernel with
+// the batch in grid z.
+extern "C" int b200jt_batched_matmul(const b200jt_tensor* a, const b200jt_tensor* b, const b200jt_tensor* c,
+                                     int trans_a, int trans_b, void* stream) {
+    B200JT_CHECK_ARG(valid_tensor(a) && valid_tensor(b) && valid_tensor(c), "invalid tensor descriptor");
+    B200JT_CHECK_ARG(a->ndim == 3 && b->ndim == 3 && c->ndim == 3, "batched matmul takes 3-D tensors [batch, rows, cols]");
+    B200JT_CHECK_ARG(a->dtype == b->dtype && a->dtype == c->dtype &&
+                     (a->dtype == B200JT_FLOAT32 || a->dtype == B200JT_BFLOAT16), "a, b, c must all be float32 or bfloat16");
+    const int64_t batch = c->shape[0];
+    const int64_t M = trans_a ? a->shape[2] : a->shape[1], K = trans_a ? a->shape[1] : a->shape[2];
+    const int64_t Kb = trans_b ? b->shape[2] : b->shape[1], N = trans_b ? b->shape[1] : b->shape[2];
+    B200JT_CHECK_ARG(K == Kb, "dimension not match, a:" + shape_str(a) + " b:" + shape_str(b));
+    B200JT_CHECK_ARG((a->shape[0] == batch || a->shape[0] == 1) && (b->shape[0] == batch || b->shape[0] == 1),
+                     "batch extents must equal c's or be 1, a:" + shape_str(a) + " b:" + shape_str(b) + " c:" + shape_str(c));
+    B200JT_CHECK_ARG(c->shape[1] == M && c->shape[2] == N, "c has the wrong shape " + shape_str(c));
+    if (batch == 0 || M == 0 || N == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == B200JT_BFLOAT16 && batched_matmul_tc_supported(batch, M, N, K, trans_a != 0, trans_b != 0, a->ptr, b->ptr, c->ptr))
+        return batched_matmul_tc(a->ptr, b->ptr, c->ptr, batch, a->shape[0], b->shape[0], M, N, K, trans_b != 0, st);
+    return batched_matmul_simt(a->ptr, b->ptr, c->ptr, a->dtype, batch, a->shape[0], b->shape[0], M, N, K,
+                               trans_a != 0, trans_b != 0, st);
+}
+
 static int conv_shape(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                       int sh, int sw, int ph, int pw, int dh, int dw, int groups, ConvShape* s) {
     B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(w) && valid_tensor(y), "invalid tensor descriptor");

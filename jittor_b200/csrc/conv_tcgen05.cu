@@ -387,7 +387,8 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     // Tile width: the grid is persistent with a static round-robin, so its time is ceil(tiles / SMs) rounds. 128-wide
     // tiles do a little worse per FLOP (more operand bytes per MMA) but halve the granularity of the last round.
     auto rounds = [&](int bn) { const int64_t t = (int64_t)A.tiles_m * ((s.Co + bn - 1) / bn); return (double)((t + kNumSMs - 1) / kNumSMs) * bn; };
-    static const int forced_bn = [] { const char* e = getenv("B200JT_CONV_BN"); return e ? atoi(e) : 0; }();
+    const char* bn_env = getenv("B200JT_CONV_BN");          // read on every call: tests force each variant in turn
+    const int forced_bn = bn_env ? atoi(bn_env) : 0;
     const int bn = forced_bn == 128 || forced_bn == 256 ? forced_bn : (rounds(128) * kNarrowTilePenalty < rounds(256) ? 128 : 256);
     A.tiles_n = (s.Co + bn - 1) / bn;
     CUtensorMap mx, mw;

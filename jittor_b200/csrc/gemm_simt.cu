@@ -5,6 +5,8 @@
 // 64x64x16 tiles, 256 threads, 4x4 outputs per thread, operands staged in shared memory.
 #include "gemm_simt.cuh"
 
+#include <algorithm>
+
 namespace b200jt {
 
 constexpr int BK = 16;
@@ -29,6 +31,14 @@ struct MatmulLoader {
     __device__ __forceinline__ int64_t a_group(int) const { return 0; }
     __device__ __forceinline__ int64_t b_group(int) const { return 0; }
     __device__ __forceinline__ int64_t c_group(int) const { return 0; }
+};
+
+// Strided-batched matmul: blockIdx.z is the batch index; a batch stride of 0 shares that operand between all products.
+struct BatchedMatmulLoader : MatmulLoader {
+    int64_t a_bs, b_bs, c_bs;
+    __device__ __forceinline__ int64_t a_group(int g) const { return (int64_t)g * a_bs; }
+    __device__ __forceinline__ int64_t b_group(int g) const { return (int64_t)g * b_bs; }
+    __device__ __forceinline__ int64_t c_group(int g) const { return (int64_t)g * c_bs; }
 };
 
 // Grouped convolution: blockIdx.z is the group; C_ / Co are the channels of ONE group, Ct / CoT those of the tensors.
@@ -200,6 +210,26 @@ int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int
     L.c_sm = N;
     if (dtype == B200JT_FLOAT32) launch_simt<float, MatmulLoader>(a, b, c, M, N, K, L, st);
     else launch_simt<__nv_bfloat16, MatmulLoader>(a, b, c, M, N, K, L, st);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+int batched_matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t batch, int64_t a_batch, int64_t b_batch,
+                        int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b, cudaStream_t st) {
+    BatchedMatmulLoader L;
+    L.a_sm = trans_a ? 1 : K; L.a_sk = trans_a ? M : 1;
+    L.b_sk = trans_b ? 1 : N; L.b_sn = trans_b ? K : 1;
+    L.c_sm = N;
+    L.a_bs = a_batch > 1 ? M * K : 0; L.b_bs = b_batch > 1 ? K * N : 0; L.c_bs = M * N;
+    const size_t es = dtype == B200JT_FLOAT32 ? 4 : 2;
+    for (int64_t b0 = 0; b0 < batch; b0 += 32768) {                 // grid.z is limited to 65535
+        const int g = (int)std::min<int64_t>(32768, batch - b0);
+        const char* ap = (const char*)a + (size_t)(b0 * L.a_bs) * es;
+        const char* bp = (const char*)b + (size_t)(b0 * L.b_bs) * es;
+        char* cp = (char*)c + (size_t)(b0 * L.c_bs) * es;
+        if (dtype == B200JT_FLOAT32) launch_simt<float, BatchedMatmulLoader>(ap, bp, cp, M, N, K, L, st, g);
+        else launch_simt<__nv_bfloat16, BatchedMatmulLoader>(ap, bp, cp, M, N, K, L, st, g);
+    }
     B200JT_LAUNCH_CHECK();
     return 0;
 }

@@ -11,11 +11,17 @@ struct ConvShape {
 
 int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int64_t N, int64_t K,
                 bool trans_a, bool trans_b, cudaStream_t st);
+int batched_matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t batch, int64_t a_batch, int64_t b_batch,
+                        int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b, cudaStream_t st);
 // tcgen05 path (gemm_tcgen05.cu)
 bool matmul_tc_supported(int64_t M, int64_t N, int64_t K, const void* a, const void* b, const void* c);
 size_t matmul_tc_workspace(int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b);
 int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b,
               void* workspace, cudaStream_t st);
+bool batched_matmul_tc_supported(int64_t batch, int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b,
+                                 const void* a, const void* b, const void* c);
+int batched_matmul_tc(const void* a, const void* b, void* c, int64_t batch, int64_t a_batch, int64_t b_batch,
+                      int64_t M, int64_t N, int64_t K, bool trans_b, cudaStream_t st);
 int tc_status_fetch_and_clear();
 
 bool conv2d_tc_supported(const ConvShape& s, const void* x, const void* w, const void* y);

@@ -49,10 +49,14 @@ struct Tiles {
 
 // BMN: B is given as [K, N] (N contiguous) and used as an MN-major operand -- four 64 x 64 TMA boxes per stage -- instead
 // of being transposed into K-major form by a separate pass.
-template <int MT, bool BMN>
+// BATCH: the maps are 3-D ([batch][rows][cols]) and the tile index runs over batch x tiles; an operand whose batch
+// extent is 1 is shared by all products (its batch coordinate stays 0). This is the strided-batched product the
+// reference relays to cublasGemmStridedBatchedEx (python/jittor/extern/cuda/cublas/ops/cublas_batched_matmul_op.cc:160).
+template <int MT, bool BMN, bool BATCH = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 __nv_bfloat16* __restrict__ c, int M, int N, int K, int group, uint32_t b_lbo, uint32_t b_sbo) {
+                 __nv_bfloat16* __restrict__ c, int M, int N, int K, int group, uint32_t b_lbo, uint32_t b_sbo,
+                 int batch = 1, int a_batched = 0, int b_batched = 0) {
     constexpr int STAGES = Cfg<MT>::STAGES, STAGE_BYTES = Cfg<MT>::STAGE_BYTES, NBUF = Cfg<MT>::NBUF;
     extern __shared__ unsigned char smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
@@ -69,6 +73,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     Tiles T;
     T.tiles_m = (M + MT * BM - 1) / (MT * BM); T.tiles_n = (N + BN - 1) / BN; T.total = T.tiles_m * T.tiles_n; T.G = group;
     const int k_blocks = (K + BK - 1) / BK;
+    const int per_batch = T.total;
+    const int all_tiles = BATCH ? per_batch * batch : per_batch;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
@@ -91,20 +97,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x) {
-                int tm, tn; T.coords(t, tm, tn);
+            for (int t = blockIdx.x; t < all_tiles && ok; t += gridDim.x) {
+                const int bi = BATCH ? t / per_batch : 0;
+                int tm, tn; T.coords(BATCH ? t - bi * per_batch : t, tm, tn);
+                const int ba = a_batched ? bi : 0, bb = b_batched ? bi : 0;
                 for (int kb = 0; kb < k_blocks; kb++) {
                     if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 1))) break;
                     unsigned char* sa = smem + stage * STAGE_BYTES;
                     mbar_expect_tx(full + stage, STAGE_BYTES);
 #pragma unroll
-                    for (int j = 0; j < MT; j++) tma_load_2d(sa + j * A_BYTES, &map_a, full + stage, kb * BK, (tm * MT + j) * BM);
+                    for (int j = 0; j < MT; j++) {
+                        if (BATCH) tma_load_3d(sa + j * A_BYTES, &map_a, full + stage, kb * BK, (tm * MT + j) * BM, ba);
+                        else tma_load_2d(sa + j * A_BYTES, &map_a, full + stage, kb * BK, (tm * MT + j) * BM);
+                    }
                     if (BMN) {
 #pragma unroll
-                        for (int cch = 0; cch < BN / 64; cch++)
-                            tma_load_2d(sa + MT * A_BYTES + cch * (64 * BK * 2), &map_b, full + stage, tn * BN + cch * 64, kb * BK);
+                        for (int cch = 0; cch < BN / 64; cch++) {
+                            if (BATCH) tma_load_3d(sa + MT * A_BYTES + cch * (64 * BK * 2), &map_b, full + stage, tn * BN + cch * 64, kb * BK, bb);
+                            else tma_load_2d(sa + MT * A_BYTES + cch * (64 * BK * 2), &map_b, full + stage, tn * BN + cch * 64, kb * BK);
+                        }
                     } else {
-                        tma_load_2d(sa + MT * A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
+                        if (BATCH) tma_load_3d(sa + MT * A_BYTES, &map_b, full + stage, kb * BK, tn * BN, bb);
+                        else tma_load_2d(sa + MT * A_BYTES, &map_b, full + stage, kb * BK, tn * BN);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -122,7 +136,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x, it++) {
+            for (int t = blockIdx.x; t < all_tiles && ok; t += gridDim.x, it++) {
                 const int buf = it % NBUF;
                 const uint32_t acc_phase = (it / NBUF) & 1;
                 if (!(ok = mbar_wait(acc_empty + buf, acc_phase ^ 1, abort_flag, 2))) break;
@@ -154,8 +168,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         int it = 0;
         bool ok = true;
         const bool vec_ok = (N % 8 == 0) && (((uintptr_t)c & 15) == 0);
-        for (int t = blockIdx.x; t < T.total && ok; t += gridDim.x, it++) {
-            int tm, tn; T.coords(t, tm, tn);
+        for (int t = blockIdx.x; t < all_tiles && ok; t += gridDim.x, it++) {
+            const int bi = BATCH ? t / per_batch : 0;
+            int tm, tn; T.coords(BATCH ? t - bi * per_batch : t, tm, tn);
             const int buf = it % NBUF;
             const uint32_t acc_phase = (it / NBUF) & 1;
             ok = mbar_wait(acc_full + buf, acc_phase, abort_flag, 4);
@@ -166,7 +181,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int j = 0; j < MT; j++) {
             const int row = (tm * MT + j) * BM + quad * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * (MT * BN) + j * BN;
-            __nv_bfloat16* crow = c + (int64_t)row * N + (int64_t)tn * BN;
+            __nv_bfloat16* crow = c + ((int64_t)bi * M + row) * N + (int64_t)tn * BN;
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ch++) {
                 uint32_t r[32];
@@ -256,6 +271,20 @@ static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t c
     return r == CUDA_SUCCESS;
 }
 
+// 3-D bf16 [batch][rows][cols] with a {BK, box_rows, 1} box: one box has the shared-memory layout of the 2-D form
+static bool make_map_3d(CUtensorMap* map, const void* base, int64_t batch, int64_t rows, int64_t cols, int box_rows) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 }  // namespace tc
 
 bool matmul_tc_supported(int64_t M, int64_t N, int64_t K, const void* a, const void* b, const void* c) {
@@ -323,6 +352,47 @@ int matmul_tc(const void* a, const void* b, void* c, int64_t M, int64_t N, int64
     if (two) { if (bmn) B200JT_GEMM(2, true); else B200JT_GEMM(2, false); }
     else     { if (bmn) B200JT_GEMM(1, true); else B200JT_GEMM(1, false); }
 #undef B200JT_GEMM
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
+// One launch for `batch` products c[i] = a[i or 0] . b[i or 0] (a [.., M, K] K-major; b [.., K, N] consumed MN-major, or
+// [.., N, K] when trans_b). The caller has checked batched_matmul_tc_supported.
+bool batched_matmul_tc_supported(int64_t batch, int64_t M, int64_t N, int64_t K, bool trans_a, bool trans_b,
+                                 const void* a, const void* b, const void* c) {
+    if (trans_a || !matmul_tc_supported(M, N, K, a, b, c) || batch >= (1LL << 31)) return false;
+    if ((M * K) % 8 != 0 || (N * K) % 8 != 0) return false;            // 16-byte batch pitch of the tensor maps
+    return trans_b || b_mn_direct(N, trans_b);
+}
+
+int batched_matmul_tc(const void* a, const void* b, void* c, int64_t batch, int64_t a_batch, int64_t b_batch,
+                      int64_t M, int64_t N, int64_t K, bool trans_b, cudaStream_t st) {
+    using namespace tc;
+    const bool bmn = !trans_b;
+    CUtensorMap ma, mb;
+    if (!make_map_3d(&ma, a, a_batch, M, K, BM) ||
+        !(bmn ? make_map_3d(&mb, b, b_batch, K, N, 64) : make_map_3d(&mb, b, b_batch, N, K, BN)))
+        return fail(-4, "batched matmul: cuTensorMapEncodeTiled failed");
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM_BYTES);
+        if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES);
+        if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM_BYTES);
+        if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<2, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM_BYTES);
+    });
+    B200JT_CUDA(attr_err);
+    const int64_t tiles2 = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
+    const int64_t tiles1 = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
+    if (tiles1 >= (1LL << 31)) return fail(-1, "batched matmul: too many tiles");
+    const bool two = tiles2 >= 4 * kNumSMs && M > BM;
+    const uint32_t lbo = 64 * BK * 2, sbo = 1024;
+    const int grid = (int)std::min<int64_t>(two ? tiles2 : tiles1, kNumSMs);
+#define B200JT_BGEMM(MT_, BMN_) gemm_bf16_kernel<MT_, BMN_, true><<<grid, THREADS, Cfg<MT_>::SMEM_BYTES, st>>>( \
+        ma, mb, (__nv_bfloat16*)c, (int)M, (int)N, (int)K, 8, lbo, sbo, (int)batch, a_batch > 1 ? 1 : 0, b_batch > 1 ? 1 : 0)
+    if (two) { if (bmn) B200JT_BGEMM(2, true); else B200JT_BGEMM(2, false); }
+    else     { if (bmn) B200JT_BGEMM(1, true); else B200JT_BGEMM(1, false); }
+#undef B200JT_BGEMM
     B200JT_LAUNCH_CHECK();
     return 0;
 }

@@ -11,7 +11,8 @@
 //   large messages (two shot):  rank r PUSHES its chunk of slice s from src into slot r of rank s's in[parity] (posted
 //       writes), flag round, then rank r sums the world slots of slice r from its own memory and writes the result
 //       into out[parity] of EVERY rank, a second flag round, and each rank copies out[parity] into dst.
-// Flags carry a per-block epoch that only grows (kept in device memory, so a captured launch can be replayed);
+// Flags carry a per-block epoch that only grows (kept in device memory, so a captured launch can be replayed; every
+// call advances the epochs of all blocks, used or not, so all blocks of all ranks agree on the call count);
 // in/out alternate between two halves by call parity, which is what lets the one-shot form skip a closing flag
 // round: a peer can only overwrite half p again two calls later, after it has seen this rank enter the next call.
 // Every wait is bounded by wall time (%globaltimer); a wait that runs out records status 5, the block stops taking
@@ -323,6 +324,10 @@ __global__ void __launch_bounds__(kThreads) peer_all_reduce_kernel(Launch L, lon
     }
     __syncthreads();
     if (threadIdx.x == 0) *epoch_ptr = epoch + 2;
+    // Blocks this launch did not use keep step with the call count, so that a later, larger message finds the same
+    // epoch -- hence the same staging half -- in every block (the block count follows the message size).
+    if (b == 0)
+        for (int i = nb + threadIdx.x; i < kMaxBlocks; i += kThreads) *epoch_of(c.seg[r], i) += 2;
 }
 
 struct Comm {
@@ -425,6 +430,11 @@ extern "C" int b200jt_peer_segment_create(size_t data_bytes, void** segment, uns
     if (e != cudaSuccess) { cudaFree(p); return fail((int)e, std::string("b200jt_peer_segment_create: cudaIpcGetMemHandle: ") + cudaGetErrorString(e)); }
     memcpy(ipc_handle, &h, sizeof(h));
     *segment = p;
+    return 0;
+}
+
+extern "C" int b200jt_peer_segment_destroy(void* segment) {
+    if (segment) B200JT_CUDA(cudaFree(segment));
     return 0;
 }
 

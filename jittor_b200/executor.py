@@ -56,6 +56,11 @@ def realize(roots):
             v._data = out.reshape(list(v.shape))
             plans.pop(id(v), None)
             stack.pop()
+            pending_update = getattr(v, "_bn_running", None)
+            if pending_update is not None:          # a BatchNorm output computed op by op: move its running statistics now
+                v._bn_running = None
+                module, xmean, xvar = pending_update
+                module._update_running(xmean, xvar)
 
 
 def _make_plan(v):
@@ -517,8 +522,7 @@ def _match_matmul(v):
 
 
 def _match_batched_matmul(v):
-    """The [..., n, m, k] product of nn.matmul (python/jittor/nn.py:140-159): batch axes are looped on the host,
-    each slice is one 2-D matmul."""
+    """The [..., n, m, k] product of nn.matmul (python/jittor/nn.py:140-159) as one strided-batched launch."""
     if not _node(v, "reduce", op="add"):
         return None
     m = v._op.inputs[0]
@@ -547,15 +551,34 @@ def _match_batched_matmul(v):
         out = _empty(batch + [n, kk], a.dtype)
         ab = _pad_shape(list(a.shape[:-2]), len(batch))
         bb = _pad_shape(list(b.shape[:-2]), len(batch))
-        a3 = a._data.reshape(ab + [n, k_])
-        b3 = b._data.reshape(bb + [k_, kk])
+        # the longest run of trailing batch axes over which each operand is either complete or shared goes to ONE
+        # launch (python/jittor/extern/cuda/cublas/ops/cublas_batched_matmul_op.cc:160 does the same for equal batch
+        # shapes); leading axes with mixed stretching are walked on the host
+        k0 = len(batch)
+        while k0 > 0:
+            ta, tb, tc = ab[k0 - 1:], bb[k0 - 1:], batch[k0 - 1:]
+            if (ta == tc or all(s == 1 for s in ta)) and (tb == tc or all(s == 1 for s in tb)):
+                k0 -= 1
+            else:
+                break
+        inner = 1
+        for s in batch[k0:]:
+            inner *= s
+
+        def flat(t, bshape, rows, cols):
+            lead = list(bshape[:k0])
+            tail = 1
+            for s in bshape[k0:]:
+                tail *= s
+            return t.reshape(lead + [tail, rows, cols])
+
+        a3, b3, o3 = flat(a._data, ab, n, k_), flat(b._data, bb, k_, kk), out.reshape(batch[:k0] + [inner, n, kk])
         import itertools
-        for idx in itertools.product(*[range(s) for s in batch]):
+        for idx in itertools.product(*[range(s) for s in batch[:k0]]):
             ai = tuple(i if s != 1 else 0 for i, s in zip(idx, ab))
             bi = tuple(i if s != 1 else 0 for i, s in zip(idx, bb))
-            at, bt, ot = a3[ai], b3[bi], out[idx]
-            C.check(C.lib.b200jt_matmul(C.desc(at), C.desc(bt), C.desc(ot), 0, 0, ctypes.c_void_p(0), 0,
-                                        C.stream_ptr()), "batched matmul")
+            C.check(C.lib.b200jt_batched_matmul(C.desc(a3[ai]), C.desc(b3[bi]), C.desc(o3[idx]), 0, 0, C.stream_ptr()),
+                    f"batched matmul a{list(a.shape)} b{list(b.shape)}")
         return _cast(out, v.dtype)
 
     return Plan([a, b], run)
@@ -880,6 +903,13 @@ def _match_batchnorm(v):
             geo = conv_geometry(got[1], got[2]) or conv_geometry(got[2], got[1])
             conv = geo
     leaves = ([conv[0], conv[1]] if conv else [x]) + [p[1] for p in (g, b) if p[0] == "var"]
+    running = getattr(root, "_bn_running", None)
+    if running is not None:
+        rm, rv = running[0].running_mean, running[0].running_var
+        if rm.dtype == "float32" and rv.dtype == "float32" and rm.numel() == Cn and rv.numel() == Cn:
+            leaves += [rm, rv]
+        else:
+            running = None
 
     def run():
         stats = torch.empty(2 * Cn, dtype=torch.float32, device="cuda")
@@ -902,10 +932,16 @@ def _match_batchnorm(v):
 
         gt, bt = param(g, 1.0), param(b, 0.0)
         out = _empty(x.shape, v.dtype)
+        rmp = rvp = 0
+        momentum = 0.0
+        if running is not None and getattr(root, "_bn_running", None) is not None:
+            root._bn_running = None                # consumed here: the kernel updates the running statistics in place
+            rmp, rvp, momentum = running[0].running_mean._data.data_ptr(), running[0].running_var._data.data_ptr(), running[0].momentum
         C.check(C.lib.b200jt_bn_apply(C.desc(xd), ctypes.c_void_p(stats.data_ptr()), count,
                                       ctypes.c_void_p(gt.data_ptr() if gt is not None else 0),
                                       ctypes.c_void_p(bt.data_ptr() if bt is not None else 0),
-                                      m["eps"], int(relu), C.desc(out), C.stream_ptr()), "bn_apply")
+                                      m["eps"], int(relu), C.desc(out), ctypes.c_void_p(rmp), ctypes.c_void_p(rvp),
+                                      float(momentum), C.stream_ptr()), "bn_apply")
         return out
 
     return Plan(leaves, run)

@@ -161,7 +161,7 @@ def grad(loss, targets, retain_graph=True):
         v, done = stack.pop()
         if done:
             need = id(v) in tids
-            if v._op is not None:
+            if v._op is not None and not v.is_stop_grad():
                 need = need or any(needs.get(id(i), False) for i in v._op.inputs)
             needs[id(v)] = need
             order.append(v)
@@ -170,7 +170,7 @@ def grad(loss, targets, retain_graph=True):
             continue
         seen.add(id(v))
         stack.append((v, True))
-        if v._op is not None and id(v) not in tids:
+        if v._op is not None and id(v) not in tids and not v.is_stop_grad():     # no gradient flows through stop_grad Vars
             for i in v._op.inputs:
                 if id(i) not in seen:
                     stack.append((i, False))

@@ -316,8 +316,16 @@ class BatchNorm(Module):
         self.eps, self.momentum, self.affine = eps, momentum, affine
         self.weight = V.ones((num_features,)) if affine else 1.0
         self.bias = V.zeros((num_features,)) if affine else 0.0
-        self.running_mean = V.zeros((num_features,))
-        self.running_var = V.ones((num_features,))
+        self.running_mean = V.zeros((num_features,)).stop_grad()
+        self.running_var = V.ones((num_features,)).stop_grad()
+
+    def _update_running(self, xmean, xvar):
+        """running += (batch - running) * momentum (python/jittor/nn.py:684-688), for results the fused kernels did not
+        produce; the fused BatchNorm plan does the same inside its normalise kernel."""
+        for name, batch in (("running_mean", xmean), ("running_var", xvar)):
+            run = getattr(self, name)
+            new = (run + (batch.reshape((-1,)).float32() - run) * self.momentum).float32()
+            run.assign(new).stop_grad()
 
     def execute(self, x):
         from . import dist
@@ -332,7 +340,11 @@ class BatchNorm(Module):
             xvar = (x2mean - xmean * xmean).maximum(0.0)
             w = self.weight / (xvar + self.eps).sqrt()
             b = self.bias - xmean * w
-            return x * w.broadcast(x, dims) + b.broadcast(x, dims)
+            norm_x = x * w.broadcast(x, dims) + b.broadcast(x, dims)
+            # the running statistics move when norm_x is computed: the executor either folds the update into the fused
+            # normalise kernel or calls _update_running once the batch statistics exist
+            norm_x._bn_running = (self, xmean, xvar)
+            return norm_x
         w = self.weight / (self.running_var + self.eps).sqrt()
         b = self.bias - self.running_mean * w
         return x * w.broadcast(x, dims) + b.broadcast(x, dims)

@@ -53,7 +53,9 @@ class PeerComm:
         tdist.all_gather_object(verdicts, (ok, err))
         if not all(v[0] for v in verdicts):
             if ok:
-                C.lib.b200jt_peer_comm_destroy(comm)
+                C.lib.b200jt_peer_comm_destroy(comm)       # frees the segment it took over
+            elif seg:
+                C.lib.b200jt_peer_segment_destroy(seg)     # exported here, but the job as a whole could not connect
             if rank == 0:
                 why = next((v[1] for v in verdicts if not v[0] and v[1]), "") or next((e[2] for e in everyone if not e[0]), "")
                 print(f"[jittor_b200] peer all-reduce unavailable, using NCCL: {why}", flush=True)

@@ -291,3 +291,87 @@ def test_matmul_bf16_full_size_tensor_core(jt):
     # transposed forms of the tuner table reach the same kernel
     ct2 = nn.matmul_transpose(jt.array(a), jt.array(b.t().contiguous())).torch()
     assert torch.equal(ct2, ct)
+
+
+# ------------------------------------------------------------------------------------------------ batched matmul (one launch)
+@pytest.mark.parametrize("ashape,bshape", [((10, 3, 4), (10, 4, 5)), ((8, 1, 3, 4), (10, 4, 5)), ((2, 3, 33, 17), (2, 3, 17, 9)),
+                                           ((5, 70, 40), (1, 40, 30)), ((1, 64, 64), (7, 64, 64))])
+def test_batched_matmul_fp32(jt, ashape, bshape):
+    from jittor_b200 import nn
+    rng = np.random.default_rng(sum(ashape))
+    a, b = rng.normal(size=ashape).astype(np.float32), rng.normal(size=bshape).astype(np.float32)
+    got = nn.matmul(jt.array(a), jt.array(b)).numpy()
+    want = ref.matmul(a, b)
+    check(got, want, False)
+
+
+@pytest.mark.parametrize("ashape,bshape", [((6, 256, 128), (6, 128, 256)),      # tensor-core kernel, batch in the tile index
+                                           ((3, 2, 200, 72), (3, 2, 72, 136)),  # ragged tiles inside every batch slice
+                                           ((4, 256, 128), (1, 128, 256)),      # shared right operand
+                                           ((4, 128, 64), (4, 64, 100))])       # N % 8 != 0: CUDA-core kernel, batch in grid z
+def test_batched_matmul_bf16(jt, ashape, bshape):
+    from jittor_b200 import nn, _capi as C
+    rng = np.random.default_rng(sum(bshape))
+    a, b = bf16_round(rng.normal(size=ashape) / np.sqrt(ashape[-1])), bf16_round(rng.normal(size=bshape))
+    c = nn.matmul(to_bf16_var(jt, a), to_bf16_var(jt, b))
+    assert c.dtype == "bfloat16"
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64)).astype(np.float32)
+    # per-slice oracle: fp32 accumulation on bf16-rounded inputs
+    a3 = np.broadcast_to(a, want.shape[:-2] + a.shape[-2:]).reshape((-1,) + a.shape[-2:])
+    b3 = np.broadcast_to(b, want.shape[:-2] + b.shape[-2:]).reshape((-1,) + b.shape[-2:])
+    want = np.stack([co.matmul(x, y) for x, y in zip(a3, b3)]).reshape(want.shape)
+    check(c.numpy(), bf16_round(want), False, rtol=2e-2)
+    assert C.lib.b200jt_device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ BatchNorm running statistics
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batchnorm_train_then_eval(jt, dtype):
+    """Three training steps move running_mean / running_var as python/jittor/nn.py:684-688 does (the fused normalise
+    kernel updates them in place), and evaluation then normalises with them."""
+    from jittor_b200 import nn
+    rng = np.random.default_rng(17)
+    Cn = 12
+    bn = nn.BatchNorm(Cn, momentum=0.3, is_train=True, sync=False)
+    rm, rv = np.zeros(Cn, np.float32), np.ones(Cn, np.float32)
+    for step in range(3):
+        x = (rng.normal(size=(6, Cn, 9, 7)) * (1 + step) + step).astype(np.float32)
+        if dtype == "bfloat16":
+            x = bf16_round(x)
+        xv = to_bf16_var(jt, x) if dtype == "bfloat16" else jt.array(x)
+        with jt.flag_scope(amp_reg=2 if dtype == "bfloat16" else 0):
+            y = bn(xv)
+            y.sync()
+        mean = x.astype(np.float64).mean((0, 2, 3))
+        var = np.maximum((x.astype(np.float64) ** 2).mean((0, 2, 3)) - mean ** 2, 0)
+        rm = (rm + (mean - rm) * 0.3).astype(np.float32)
+        rv = (rv + (var - rv) * 0.3).astype(np.float32)
+        check(bn.running_mean.numpy(), rm, False, rtol=1e-4)
+        check(bn.running_var.numpy(), rv, False, rtol=1e-4)
+    assert bn.running_mean.is_stop_grad() and bn.running_var.is_stop_grad()
+    bn.is_train = False
+    x = rng.normal(size=(2, Cn, 5, 5)).astype(np.float32)
+    got = bn(jt.array(x)).numpy()
+    want = (x - rm[None, :, None, None]) / np.sqrt(rv[None, :, None, None] + 1e-5)
+    check(got, want.astype(np.float32), False, rtol=1e-4)
+
+
+def test_batchnorm_running_statistics_without_the_fused_plan(jt):
+    """float64 inputs are normalised op by op; the running statistics still move once the output is computed."""
+    from jittor_b200 import nn
+    rng = np.random.default_rng(18)
+    x = rng.normal(size=(4, 5, 6, 6)) + 2.0
+    bn = nn.BatchNorm(5, momentum=0.1, is_train=True, sync=False)
+    bn(jt.array(x)).sync()
+    mean = x.mean((0, 2, 3))
+    var = (x ** 2).mean((0, 2, 3)) - mean ** 2
+    check(bn.running_mean.numpy(), (0.1 * mean).astype(np.float32), False, rtol=1e-5)
+    check(bn.running_var.numpy(), (1 + 0.1 * (var - 1)).astype(np.float32), False, rtol=1e-5)
+
+
+def test_grad_stops_at_stop_grad(jt):
+    x = jt.array(np.arange(6, dtype=np.float32).reshape(2, 3))
+    y = (x * 2.0).stop_grad()
+    z = (y * x).sum()
+    g = jt.grad(z, x).numpy()
+    assert np.array_equal(g, np.arange(6, dtype=np.float32).reshape(2, 3) * 2)      # d/dx (c*x) with c = y held constant

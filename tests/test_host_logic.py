@@ -168,14 +168,14 @@ def test_softmax_layernorm_batchnorm_patterns():
     bn = nn.BatchNorm(5, is_train=True, sync=False)
     bn.weight, bn.bias = ph([5]), ph([5])
     y = bn(xi)
-    assert executor._match_batchnorm(y).leaves == [xi, bn.weight, bn.bias]
-    assert executor._match_batchnorm(nn.relu(y)).leaves == [xi, bn.weight, bn.bias]
+    assert executor._match_batchnorm(y).leaves == [xi, bn.weight, bn.bias, bn.running_mean, bn.running_var]
+    assert executor._match_batchnorm(nn.relu(y)).leaves == [xi, bn.weight, bn.bias, bn.running_mean, bn.running_var]
     # conv feeding BatchNorm+ReLU: one plan from (x, w) to the activation
     xc, wc = ph([4, 8, 10, 10]), ph([16, 8, 3, 3])
     bn2 = nn.BatchNorm(16, is_train=True, sync=False)
     bn2.weight, bn2.bias = ph([16]), ph([16])
     z = nn.relu(bn2(nn.conv2d(xc, wc, None, 1, 1, 1)))
-    assert executor._match_batchnorm(z).leaves == [xc, wc, bn2.weight, bn2.bias]
+    assert executor._match_batchnorm(z).leaves == [xc, wc, bn2.weight, bn2.bias, bn2.running_mean, bn2.running_var]
 
 
 def test_error_cases_of_the_reference():

@@ -95,3 +95,22 @@ def test_absent_peer_runs_into_the_wait_bound_and_leaves_the_context_usable():
         assert torch.equal(dsts[0], rank_ordered(srcs, "add"))
     finally:
         job.close()
+
+
+def test_alternating_message_sizes_keep_all_blocks_on_one_call_count():
+    """The block count follows the message size; blocks a small call leaves idle must still advance with the call
+    count, or a later large call would mix staging halves between its blocks. Sizes in 16-byte packs: 512 / 600 / 512
+    (one and two blocks), then one-block and 128-block messages in turn, one-shot and two-shot."""
+    from jittor_b200 import peer
+    job = peer.LocalJob(4, data_bytes=4 << 20)
+    try:
+        counts = [2048, 2400, 2048, 4, 1 << 18, 4, 1 << 20, 2400, 1 << 18, 1, 1 << 20]
+        for seed, count in enumerate(counts * 2):
+            srcs = make(4, count, torch.float32, 100 + seed)
+            dsts = [torch.full_like(s, -3) for s in srcs]
+            job.all_reduce(srcs, dsts, "add")
+            want = rank_ordered(srcs, "add")
+            for d in dsts:
+                assert torch.equal(d, want), (seed, count)
+    finally:
+        job.close()
