@@ -1,8 +1,10 @@
 """Benchmark of the meta-operator hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|meta] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|meta|next] [--impl reference]
 
-One JSON line on stdout (rank 0). Workloads are the benchmark configurations:
+One JSON line on stdout (rank 0). The default run measures c2 (the headline keys of the line) and then c1, c3, c4, c5
+with the same method into "workloads"; --workload X measures X alone. Workloads are the benchmark configurations:
+    c1            reindex-lowered conv2d fp32 [4,32,32,32] * [64,32,3,3], L2 flushed before every repetition    (GB/s and TFLOP/s)
     c2 (default)  reindex_reduce scatter: 2^24 int32 -> 2^20 bins and 2^24 fp32 -> 4096 bins, uniform and Zipf(1.1)
                   indices, plus the 2x2 max-pool backward [64,128,56,56,2,2] -> [64,128,112,112]      (GB/s, HBM)
     c3            fused row softmax and LayerNorm on [32768, 4096], fp32 and bf16 IO                  (GB/s, HBM)
@@ -80,6 +82,65 @@ class ClockSampler:
 # Workloads. A workload knows its parts, the algorithmic work of each (bytes or FLOP), how to run a part on
 # device-resident inputs or from pinned host buffers, and how to run a bounded sample of it on the CPU oracle.
 # =====================================================================================================
+class C1ConvF32:
+    """Config 0: the reindex-lowered conv2d in fp32 at the size the reference's CPU path runs. 1.6 MB of operands: the
+    whole problem sits in L2, so L2 is flushed (a 256 MB fill) before every timed repetition."""
+    key, metric, unit, bound, dtype, scaling = "c1", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
+    N, C, H, W, CO = 4, 32, 32, 32, 64
+    description = ("config 0: reindex-lowered conv2d fp32 [4,32,32,32] * [64,32,3,3] s1 p1 "
+                   "(reindex -> broadcast -> multiply -> sum over [Cin,Kh,Kw], recognised and run as one CUDA-core implicit GEMM)")
+    kernel_of = {"conv-f32": "gemm_simt_kernel<float, ConvLoader>"}
+    launches = {"conv-f32": 1}
+    flush_l2 = True
+    FLOP = 2 * 4 * 64 * 32 * 32 * 32 * 9
+
+    def work(self):
+        return {"conv-f32": 4 * (self.N * self.C * self.H * self.W + self.CO * self.C * 9 + self.N * self.CO * self.H * self.W)}
+
+    def host_inputs(self, seed):
+        rng = np.random.default_rng(seed)
+        x = rng.uniform(-1, 1, size=(self.N, self.C, self.H, self.W)).astype(np.float32)
+        w = (rng.normal(size=(self.CO, self.C, 3, 3)) * 0.05).astype(np.float32)
+        return x, w
+
+    def setup(self, rank, world, jt, torch, multi):
+        from jittor_b200 import nn
+        self.jt, self.torch, self.nn = jt, torch, nn
+        x, w = self.host_inputs(0 + rank)
+        self.hx, self.hw = torch.from_numpy(x).pin_memory(), torch.from_numpy(w).pin_memory()
+        self.x, self.w = jt.array(self.hx), jt.array(self.hw)
+        self.out = torch.empty(self.N, self.CO, self.H, self.W).pin_memory()
+        return ["conv-f32"]
+
+    def run(self, name):
+        return self.nn.conv2d(self.x, self.w, None, 1, 1, 1).sync()
+
+    def run_e2e(self, name):
+        x, w = self.jt.array(self.hx.cuda(non_blocking=True)), self.jt.array(self.hw.cuda(non_blocking=True))
+        self.nn.conv2d(x, w, None, 1, 1, 1).fetch_into(self.out, stream=self.d2h_stream)
+
+    def e2e_bytes(self, names):
+        return (self.hx.numel() + self.hw.numel()) * 4, self.out.numel() * 4
+
+    def extra(self, part_ms):
+        return {"TFLOP/s": self.FLOP / part_ms["conv-f32"] / 1e9, "flop_per_step": self.FLOP}
+
+    def verify(self, env):
+        from oracle import c_oracle as co
+        x, w = self.host_inputs(0 + env["rank"])
+        got = self.run("conv-f32").numpy()
+        want = co.conv2d(x, w, 1, 1, 1)
+        return bool((np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-5 * np.abs(want).max()).all())
+
+    def cpu(self, names):
+        from oracle import c_oracle as co
+        x, w = self.host_inputs(0)
+        reps, t0 = 20, time.perf_counter()
+        for _ in range(reps):
+            co.conv2d(x, w, 1, 1, 1)
+        return self.work()["conv-f32"] * reps, time.perf_counter() - t0, f"full size, {reps} repetitions (OpenMP over image x channel)"
+
+
 class C2Scatter:
     key, metric, unit, bound, dtype, scaling = "c2", "meta-op GB/s", "GB/s", "hbm", "int32/f32", "weak"
     N_VAL, BINS_A, BINS_B = 1 << 24, 1 << 20, 4096
@@ -150,6 +211,31 @@ class C2Scatter:
     def e2e_bytes(self, names):
         h2d = sum(a.numel() * a.element_size() for n in names for a in self.pinned[n][:2] if a is not None)
         return h2d, sum(self.out_host[n].numel() * 4 for n in names)
+
+    def verify(self, env):
+        """Untimed correctness witness. One GPU: the int32 bins equal the CPU oracle's. Several GPUs: the all-reduced bins
+        equal the rank-ordered sum of the ranks' own bins (gathered with NCCL): bit-exact for both dtypes."""
+        torch = self.torch
+        ok = True
+        for name in ("a-uniform", "b-zipf"):
+            val, idx, bins = self.dev[name]
+            local = val.reindex_reduce("add", [bins], ["@e0(i0)"], extras=[idx]).torch().clone()
+            if not env["multi"]:
+                if name.startswith("a-"):
+                    from oracle import c_oracle as co
+                    ok = ok and bool(np.array_equal(local.cpu().numpy(), co.scatter_add(self.host[name][0], self.host[name][1], bins)))
+                continue
+            tdist = env["tdist"]
+            mine = self.jt.array(local).mpi_all_reduce("add").torch()
+            everyone = [torch.empty_like(local) for _ in range(env["world"])]
+            tdist.all_gather(everyone, local)
+            want = everyone[0].clone()
+            for t in everyone[1:]:
+                want = want + t
+            ok = ok and bool(torch.equal(mine, want))
+            if name.startswith("a-"):               # the whole pipeline once more: scatter + all-reduce of integers is exact
+                ok = ok and bool(torch.equal(self._scatter(val, idx, bins).torch(), want))
+        return ok
 
     def cpu(self, names):
         from oracle import c_oracle as co
@@ -333,6 +419,30 @@ class C5ConvBN:
     def e2e_bytes(self, names):
         return len(names) * (self.hx.numel() + self.hw.numel()) * 2, len(names) * self.out.numel() * 2
 
+    def verify(self, env):
+        """Untimed correctness witness: relu(bn(conv)) on this rank's images against the same chain computed by torch from
+        this rank's stored conv output and the statistics of the FULL batch (float64 sums over all ranks, gathered with
+        NCCL) -- what the reference checks sync BatchNorm against (a single process fed the global batch)."""
+        torch = self.torch
+        y = self._op("conv", self.x, self.w).torch()
+        z = self._op("conv-bn-relu", self.x, self.w).torch()
+        yd = y.double()
+        st = torch.stack([yd.sum((0, 2, 3)), (yd * yd).sum((0, 2, 3))])
+        del yd
+        if env["multi"]:
+            env["tdist"].all_reduce(st)
+        cnt = float(self.N * self.H * self.W)
+        mean = st[0] / cnt
+        var = (st[1] / cnt - mean * mean).clamp_min(0)
+        wgt = (1.0 / torch.sqrt(var + 1e-5)).float()
+        bias = (-mean * wgt.double()).float()
+        ok = True
+        for n0 in range(0, y.shape[0], 16):
+            ref = torch.relu(y[n0:n0 + 16].float() * wgt[None, :, None, None] + bias[None, :, None, None])
+            d = (z[n0:n0 + 16].float() - ref).abs()
+            ok = ok and bool((d <= 2e-2 * ref.abs() + 2e-2 * ref.abs().max()).all())
+        return ok
+
     def cpu(self, names):
         from oracle import c_oracle as co
         imgs = 2
@@ -493,144 +603,152 @@ class NextOps:
         return max(done, 1), time.perf_counter() - t0, "2x16 of 64x128 images per pooling part through the numpy oracle (1 core)"
 
 
-WORKLOADS = {w.key: w for w in (C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps, NextOps)}
+WORKLOADS = {w.key: w for w in (C1ConvF32, C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps, NextOps)}
+HEADLINE = "c2"                               # the default run's top-level line; the other configs follow in "workloads"
+CONFIGS = ("c1", "c3", "c4", "c5")
 
 
 def scale_of(unit):
     return 1e6 if unit == "GB/s" else 1e9          # work / ms -> GB/s (1e6) or TFLOP/s (1e9)
 
 
+def cpu_value(wl, names, steps, warmup):
+    """The reference's CPU implementation of the step (C restatement of its loop nests) on a bounded sample."""
+    for _ in range(max(warmup, 0)):
+        wl.cpu(names)
+    done = secs = 0.0
+    sample = ""
+    for _ in range(steps):
+        d, t, sample = wl.cpu(names)
+        done, secs = done + d, secs + t
+    return done / secs / (1e9 if wl.unit == "GB/s" else 1e12), secs / steps * 1e3, sample
+
+
 def run_reference(args, rank, world):
-    """The reference's CPU implementation of the step (C restatement of its loop nests), bounded sample."""
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]()
     names = [n for n in wl.work() if not args.parts or n in args.parts.split(",")]
-    for _ in range(max(args.warmup, 0)):
-        wl.cpu(names)
-    done = secs = 0.0
-    sample = ""
-    for _ in range(args.steps):
-        d, t, sample = wl.cpu(names)
-        done, secs = done + d, secs + t
-    val = done / secs / (1e9 if wl.unit == "GB/s" else 1e12)
-    print(json.dumps({
+    val, ms, sample = cpu_value(wl, names, args.steps, args.warmup)
+    out = {
         "impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype if wl.key == "c2" else "f32", "data": "synthetic",
         "config": {"workload": wl.description, "sample": sample},
         "cpu_baseline": {"value": val, "unit": wl.unit, "cores": os.cpu_count(), "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if args.all and args.workload == HEADLINE and not args.parts:
+        extra = {}
+        for key in CONFIGS:
+            w2 = WORKLOADS[key]()
+            v2, ms2, sample2 = cpu_value(w2, list(w2.work()), min(args.steps, 3), min(args.warmup, 1))
+            extra[key] = {"value": v2, "unit": w2.unit, "ms_per_step": ms2, "cores": os.cpu_count(), "kind": "port", "sample": sample2}
+        out["workloads"] = extra
+    print(json.dumps(out))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200")
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--cpu-baseline", type=int, default=1)
-    ap.add_argument("--parts", default="", help="comma-separated subset of the parts (profiling aid)")
-    ap.add_argument("--e2e", type=int, default=1)
-    ap.add_argument("--graph", type=int, default=1, help="replay the step from a CUDA graph in the timed region")
-    args = ap.parse_args()
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
-        return run_reference(args, rank, world)
+def percentile(sorted_vals, q):
+    return sorted_vals[min(len(sorted_vals) - 1, int(q * len(sorted_vals)))]
 
-    import torch
-    import torch.distributed as tdist
 
-    import jittor_b200 as jt
-    from jittor_b200 import dist
-
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist.init("nccl")
-    multi = dist.in_mpi()
-    peer_kernel = dist.peer_comm() is not None
-    wl = WORKLOADS[args.workload]()
+def measure(wl, args, env, headline):
+    """Times one workload on this rank's GPU and returns its record (max over ranks)."""
+    torch, tdist, jt = env["torch"], env["tdist"], env["jt"]
+    rank, world, multi, local = env["rank"], env["world"], env["multi"], env["local"]
     names = [n for n in wl.setup(rank, world, jt, torch, multi) if not args.parts or n in args.parts.split(",")]
     work = {n: wl.work()[n] for n in names}
     sc = scale_of(wl.unit)
-    # whole-job work per step: weak scaling multiplies the per-rank work, strong scaling keeps the total
     job_work = sum(work.values()) * (world if wl.scaling == "weak" else 1)
+    steps = args.steps if headline else max(20, min(args.steps, 50))
+    flush = None
+    if getattr(wl, "flush_l2", False):
+        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        flush = flush_buf.zero_
 
     def barrier():
         if multi:
             tdist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident throughput ------------------------------------------------------------------
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
+    def step_direct():
         for nm in names:
             wl.run(nm)
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step_direct()
     barrier()
     # (1) per-part times: direct launches with an event after every part
-    psteps = min(args.steps, 10)
+    psteps = min(steps, 10)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(psteps)]
     barrier()
     for s in range(psteps):
+        if flush:
+            flush()
         ev[s][0].record()
         for i, nm in enumerate(names):
             wl.run(nm)
             ev[s][i + 1].record()
     barrier()
-    part_ms = {nm: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(psteps)) / psteps
-               for i, nm in enumerate(names)}
+    part_ms = {nm: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(psteps)) / psteps for i, nm in enumerate(names)}
     # (2) the timed region: K steps. One step (kernels and collectives of all parts) is captured into a CUDA graph and
-    # replayed, so that the device is not waiting for the Python launch path (it matters when the per-rank work is
-    # small); without --graph, or if capture fails, the steps are launched directly.
+    # replayed, so that the device is not waiting for the Python launch path; without --graph, or if capture fails, the
+    # steps are launched directly.
     graph = None
     if args.graph:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                for nm in names:
-                    wl.run(nm)
+                step_direct()
             torch.cuda.current_stream().wait_stream(side)
             barrier()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                keep = [wl.run(nm) for nm in names]
+                keep = [wl.run(nm) for nm in names]      # noqa: F841  (outputs stay alive with the graph)
             graph.replay()
             barrier()
         except Exception as exc:                     # noqa: BLE001
             print(f"[bench] CUDA graph capture unavailable ({type(exc).__name__}: {exc}); launching directly", file=sys.stderr)
             graph = None
             torch.cuda.synchronize()
-    e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # clocks are sampled from here on: through the timed region and the untimed repeats of the same step that follow
+    step = graph.replay if graph is not None else step_direct
     clocks = ClockSampler(local)
     clocks.__enter__()
     barrier()
-    e_beg.record()
-    for s in range(args.steps):
-        if graph is not None:
-            graph.replay()
-        else:
-            for nm in names:
-                wl.run(nm)
-    e_end.record()
-    barrier()
-    # One nvidia-smi query outlasts a short timed region: keep the same step running (untimed, the same count on every
-    # rank) until the sampler has seen the clocks under this load a few times.
-    for s in range(args.steps * 20):
-        if len(clocks.samples) >= 4 and not multi:
-            break
-        if graph is not None:
-            graph.replay()
-        else:
-            for nm in names:
-                wl.run(nm)
-        if s % 50 == 49:
+    if flush is None:
+        e_beg, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e_beg.record()
+        for s in range(steps):
+            step()
+        e_end.record()
+        barrier()
+        step_ms = e_beg.elapsed_time(e_end) / steps
+    else:
+        # inputs smaller than L2: every repetition is preceded by an L2 flush and timed by its own event pair
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for a, b in pairs:
+            flush()
+            a.record()
+            step()
+            b.record()
+        barrier()
+        step_ms = sum(a.elapsed_time(b) for a, b in pairs) / steps
+    # (3) stability: further repetitions (the same count on every rank), each timed by its own event pair; the clocks are
+    # sampled through the timed region and this window
+    reps = max(args.stability, 0)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for k, (a, b) in enumerate(pairs):
+        if flush:
+            flush()
+        a.record()
+        step()
+        b.record()
+        if k % 64 == 63:
             torch.cuda.current_stream().synchronize()
     barrier()
     clocks.__exit__()
-    step_ms = e_beg.elapsed_time(e_end) / args.steps
+    rep_ms = sorted(a.elapsed_time(b) for a, b in pairs)
     status = jt._capi.lib.b200jt_device_status()
 
     # ---- end to end: pinned host -> device -> kernels -> pinned host ------------------------------------
@@ -642,7 +760,7 @@ def main():
         for nm in names:
             wl.run_e2e(nm)
 
-    e2e_steps = max(2, min(args.steps, 5)) if args.e2e else 0
+    e2e_steps = (max(2, min(steps, 5)) if headline else 2) if args.e2e else 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if args.e2e:
         e2e_step()
@@ -657,54 +775,141 @@ def main():
     e2e_ms = e0.elapsed_time(e1) / max(e2e_steps, 1)
     h2d, d2h = wl.e2e_bytes(names)
 
+    # ---- correctness witness (untimed) ----------------------------------------------------------------
+    parity = None
+    if args.verify and hasattr(wl, "verify") and not args.parts:
+        try:
+            parity = bool(wl.verify(env))
+        except Exception as exc:                     # noqa: BLE001
+            print(f"[bench] verify({wl.key}) raised {type(exc).__name__}: {exc}", file=sys.stderr)
+            parity = False
+        status = status or jt._capi.lib.b200jt_device_status()
+
     # ---- max over ranks ------------------------------------------------------------------------------
-    times = torch.tensor([step_ms, e2e_ms] + [part_ms[n] for n in names], device="cuda", dtype=torch.float64)
+    p50, p10, p90 = (percentile(rep_ms, 0.5), percentile(rep_ms, 0.1), percentile(rep_ms, 0.9)) if rep_ms else (0.0, 0.0, 0.0)
+    times = torch.tensor([step_ms, e2e_ms, p50, p10, p90] + [part_ms[n] for n in names], device="cuda", dtype=torch.float64)
+    flags_ = torch.tensor([0 if parity is False else 1, 1 if status == 0 else 0], device="cuda", dtype=torch.int32)
     if multi:
         tdist.all_reduce(times, op=tdist.ReduceOp.MAX)
+        tdist.all_reduce(flags_, op=tdist.ReduceOp.MIN)
     times = times.tolist()
-    step_ms, e2e_ms = times[0], times[1]
-    part_ms = dict(zip(names, times[2:]))
+    step_ms, e2e_ms, p50, p10, p90 = times[:5]
+    part_ms = dict(zip(names, times[5:]))
+    if parity is not None:
+        parity = bool(flags_[0].item())
+    if status == 0 and not bool(flags_[1].item()):
+        status = -2                                  # another rank's status word was set
     if rank != 0:
-        return
+        return None
 
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else None
+    peaks = env["peaks"]
     if wl.bound == "hbm":
         peak, peak_src = (peaks["hbm_gbs"], "measured") if peaks else (6650.0, "fallback")
     else:
         peak, peak_src = (peaks["bf16_tflops"], "measured (burst)") if peaks else (1590.0, "fallback")
     per_rank = wl.per_rank_work if hasattr(wl, "per_rank_work") else (lambda n: work[n])
     parts = [{"part": n, "ms": part_ms[n], wl.unit: per_rank(n) / part_ms[n] / sc,
-              "frac_of_peak": per_rank(n) / part_ms[n] / sc / peak} for n in names]
-    dom = max(names, key=lambda n: part_ms[n])
-    achieved = per_rank(dom) / part_ms[dom] / sc
+              "frac_of_peak": per_rank(n) / part_ms[n] / sc / peak, "kernel": wl.kernel_of[n]} for n in names]
+    # the dominant kernel: largest summed time over the parts of one step
+    by_kernel = {}
+    for n in names:
+        k = by_kernel.setdefault(wl.kernel_of[n], {"ms": 0.0, "work": 0, "parts": [], "launches": 0, "traffic": 0.0})
+        k["ms"] += part_ms[n]
+        k["work"] += per_rank(n)
+        k["parts"].append(n)
+        k["launches"] += 1
+        t = getattr(wl, "traffic", {}).get(n)
+        k["traffic"] = None if (t is None or k["traffic"] is None) else k["traffic"] + t
+    dom_name = max(by_kernel, key=lambda k: by_kernel[k]["ms"])
+    dom = by_kernel[dom_name]
+    achieved = dom["work"] / dom["ms"] / sc
+    per_rank_step = sum(per_rank(n) for n in names)
+    peer_kernel = env["peer_kernel"]
     out = {
         "metric": wl.metric, "value": job_work / step_ms / sc, "unit": wl.unit, "n_gpus": world,
-        "steps": args.steps, "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True,
+        "steps": steps, "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
         "config": {"workload": wl.description, "algorithmic_work_per_step": job_work,
-                   "l2": "no flush: every part touches more than the 126 MB L2 and the parts rotate",
+                   "l2": ("flushed (256 MB fill) before every timed repetition: the operands fit in L2" if flush else
+                          "no flush: every part touches more than the 126 MB L2 and the parts rotate"),
                    "parallelism": f"dp{world}" if world > 1 else "1 GPU"},
         "clocks": clocks.summary(),
         "e2e": {"value": job_work / e2e_ms / sc if e2e_steps else None, "unit": wl.unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": args.steps * sum(wl.launches[n] + (1 if peer_kernel and n in getattr(wl, "all_reduced", ()) else 0)
-                                         for n in names),
+        "gpu_launches": steps * sum(wl.launches[n] + (1 if peer_kernel and n in getattr(wl, "all_reduced", ()) else 0)
+                                    for n in names),
         "collective": None if not multi else ("peer-kernel (NVLink loads/stores, one launch per rank)" if peer_kernel else "nccl"),
-        "roofline": {"bound": wl.bound, "kernel": wl.kernel_of[dom], "part": dom, "achieved": achieved, "peak": peak,
+        "roofline": {"bound": wl.bound, "kernel": dom_name, "parts": dom["parts"], "achieved": achieved, "peak": peak,
                      "unit": wl.unit, "frac": achieved / peak, "peak_source": peak_src,
-                     "traffic": getattr(wl, "traffic", {}).get(dom),
-                     "note": "achieved = algorithmic work of the part / CUDA-event time of the part (its main kernel "
-                             "plus its small helper launches)"},
+                     "traffic": (dom["traffic"] / dom["launches"]) if dom["traffic"] else None,
+                     "step_frac": per_rank_step / step_ms / sc / peak,
+                     "note": "dominant kernel = largest summed time over the parts of one step; achieved = algorithmic work "
+                             "of those parts / their CUDA-event time (main kernel plus small helper launches); traffic = "
+                             "DRAM bytes per launch from the ncu captures under profiles/; step_frac = whole step / peak"},
         "parts": parts,
+        "stability": {"repetitions": reps, "ms_median": p50, "ms_p10": p10, "ms_p90": p90},
         "cuda_graph": graph is not None,
         "device_status": status,
     }
+    if parity is not None:
+        out["parity_ok"] = parity
+    if hasattr(wl, "extra"):
+        out.update(wl.extra(part_ms))
     if args.cpu_baseline and world == 1:
         done, secs, sample = wl.cpu(names)
         out["cpu_baseline"] = {"value": done / secs / (1e9 if wl.unit == "GB/s" else 1e12), "unit": wl.unit,
                                "cores": os.cpu_count(), "kind": "port", "sample": sample}
-    print(json.dumps(out))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
+    ap.add_argument("--all", type=int, default=1, help="default run: after the headline workload also measure c1, c3, c4, c5")
+    ap.add_argument("--cpu-baseline", type=int, default=1)
+    ap.add_argument("--parts", default="", help="comma-separated subset of the parts (profiling aid)")
+    ap.add_argument("--e2e", type=int, default=1)
+    ap.add_argument("--verify", type=int, default=1, help="untimed correctness witness after the timed regions")
+    ap.add_argument("--stability", type=int, default=300, help="individually timed repetitions after the timed region")
+    ap.add_argument("--graph", type=int, default=1, help="replay the step from a CUDA graph in the timed region")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import gc
+
+    import torch
+    import torch.distributed as tdist
+
+    import jittor_b200 as jt
+    from jittor_b200 import dist
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init("nccl")
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    env = {"torch": torch, "tdist": tdist, "jt": jt, "rank": rank, "world": world, "local": local,
+           "multi": dist.in_mpi(), "peer_kernel": dist.peer_comm() is not None,
+           "peaks": json.load(open(peaks_path)) if os.path.exists(peaks_path) else None}
+    out = measure(WORKLOADS[args.workload](), args, env, True)
+    if args.all and args.workload == HEADLINE and not args.parts:
+        others = {}
+        for key in CONFIGS:
+            gc.collect()
+            torch.cuda.empty_cache()
+            rec = measure(WORKLOADS[key](), args, env, False)
+            if rec is not None:
+                others[key] = rec
+        if out is not None:
+            out["workloads"] = others
+            out["gpu_launches_all_workloads"] = out["gpu_launches"] + sum(r["gpu_launches"] for r in others.values())
+    if out is not None:
+        print(json.dumps(out))
 
 
 if __name__ == "__main__":
