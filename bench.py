@@ -302,6 +302,25 @@ class C3Rows:
         b = sum(4 * n if nm.endswith("f32") else 2 * n for nm in names)
         return b, b
 
+    def verify(self, env):
+        """Untimed correctness witness: 64 sampled rows of every part against the CPU oracle's row loops (fp32 1e-5 mixed;
+        bf16 IO: inputs are the bf16 values, result compared after rounding, 2e-2 mixed)."""
+        from oracle import c_oracle as co
+        torch = self.torch
+        pick = torch.randperm(self.ROWS, generator=torch.Generator().manual_seed(5))[:64]
+        g, b = self.gamma.numpy(), self.beta.numpy()
+        ok = True
+        for name in self.kernel_of:
+            f32 = name.endswith("f32")
+            src = (self.h32 if f32 else self.h16)[pick].float().numpy()
+            got = self.run(name).torch()[pick.cuda()].float().cpu().numpy()
+            want = co.softmax_rows(src) if name.startswith("softmax") else co.layernorm_rows(src, g, b)
+            if not f32:
+                want = torch.from_numpy(want).bfloat16().float().numpy()
+            rtol = 1e-5 if f32 else 2e-2
+            ok = ok and bool((np.abs(got - want) <= rtol * np.abs(want) + rtol * np.abs(want).max()).all())
+        return ok
+
     def cpu(self, names):
         from oracle import c_oracle as co
         rows = 2048
@@ -353,6 +372,20 @@ class C4Matmul:
     def e2e_bytes(self, names):
         return (sum(a.numel() * 2 + b.numel() * 2 for a, b in (self.hostab[n] for n in names)),
                 sum(self.out[n].numel() * 2 for n in names))
+
+    def verify(self, env):
+        """Untimed correctness witness: 32 sampled rows of each product against the CPU oracle (fp32 accumulation on the
+        bf16 inputs, result rounded to bf16, 2e-2 mixed)."""
+        from oracle import c_oracle as co
+        torch = self.torch
+        ok = True
+        for name, (m, n, kk) in self.SHAPES.items():
+            a, b = self.hostab[name]
+            pick = torch.randperm(m, generator=torch.Generator().manual_seed(6))[:32]
+            want = torch.from_numpy(co.matmul(a[pick].float().numpy(), b.float().numpy())).bfloat16().float().numpy()
+            got = self.run(name).torch()[pick.cuda()].float().cpu().numpy()
+            ok = ok and bool((np.abs(got - want) <= 2e-2 * np.abs(want) + 2e-2 * np.abs(want).max()).all())
+        return ok
 
     def cpu(self, names):
         from oracle import c_oracle as co

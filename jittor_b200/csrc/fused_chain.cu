@@ -1,0 +1,514 @@
+// Fused element-wise chains around a row reduce: the general form of what the reference's FusedOp produces when it
+// stitches unary / binary / ternary ops, broadcasts and reduces into one loop nest
+// (python/jittor/src/fused_op.cc:41-118, python/jittor/src/op_compiler.cc:839-1045; cases
+// python/jittor/test/test_fused_op.py:144-176). There the fused source is generated and compiled per graph; here the
+// graph arrives as a small postfix program that ONE ahead-of-time kernel interprets, so any chain costs one launch and
+// its intermediates never reach memory.
+//
+// A program is a list of statements over the "full" index space [rows, cols] (cols = the trailing axes a reduce folds,
+// or any split of the tensor if there is no reduce):
+//   ROW_REDUCE j, op   rowval[j] = fold over the row of <chain>           one sweep over the row
+//   ROW_MAP j          rowval[j] = <chain over row values / per-row inputs / constants>
+//   STORE              out[row, col] = <chain>                            one sweep, the output write
+//   STORE_ROW j        out[row] = rowval[j]
+// A chain is postfix code: INPUT k, CONST c, ROWVAL j, UNARY u, BINARY b, TERNARY, TSTORE t / TLOAD t (shared
+// sub-expressions). All arithmetic is the float32 compute class of the element-wise kernels (elementwise.cu), and every
+// op's result is rounded to the dtype the reference's inference gives that node (float32 / bfloat16 / float16 / bool), so a
+// fused chain returns the same bits as the same ops run one by one.
+//
+// Kernel: a group of G threads (a warp, or a CTA of 256) owns a row at a time; every statement that sweeps the row
+// re-reads its inputs, which after the first sweep come from L1/L2 (a row is a few KB), so DRAM sees one read of each
+// input and one write of the output. A thread evaluates 8 consecutive elements per interpreted instruction (one 16- or
+// 32-byte access per operand), which amortises the decode.
+#include "atomic_ops.cuh"
+
+namespace b200jt {
+namespace chain {
+
+constexpr int kMaxInputs = 8;
+constexpr int kMaxCode = 160;
+constexpr int kMaxRowVals = 8;
+constexpr int kStack = 8;
+constexpr int kTmp = 4;
+constexpr int VEC = 8;
+
+enum ChainOp : int {
+    CH_END = 0, CH_INPUT, CH_CONST, CH_ROWVAL, CH_UNARY, CH_BINARY, CH_TERNARY, CH_TSTORE, CH_TLOAD,
+    CH_ROW_REDUCE,      // a = slot | reduce op << 4 : ends a chain, one sweep
+    CH_ROW_MAP,         // a = slot                  : ends a chain evaluated once per row
+    CH_STORE,           // ends a chain, one sweep, writes the output
+    CH_STORE_ROW        // a = slot                  : out[row] = rowval[slot]
+};
+
+// unary codes of elementwise.cu (kept in the same order)
+enum UnaryCode : int {
+    U_CAST = 0, U_NEG, U_ABS, U_LNOT, U_BNOT, U_LOG, U_EXP, U_SQRT, U_ROUND, U_FLOOR, U_CEIL,
+    U_SIN, U_ASIN, U_SINH, U_ASINH, U_TAN, U_ATAN, U_TANH, U_ATANH, U_COS, U_ACOS, U_COSH, U_ACOSH,
+    U_SIGMOID, U_ERF, U_ERFINV, U_INVALID
+};
+
+// How an input is addressed from (row, col):
+enum InMode : int {
+    IN_FULL = 0,        // same shape as the full space: offset row*cols + col
+    IN_SCALAR,          // one element
+    IN_COL,             // constant over the rows, complete along the row (bias): offset col
+    IN_ROW,             // constant along the row: one offset per row, from the row index and the strides of the row axes
+    IN_GENERAL          // broadcast over arbitrary axes: strides per merged axis of the full space
+};
+
+struct Input {
+    const void* ptr;
+    int32_t dtype, mode;
+    int32_t vec_ok;                     // 16-byte aligned base and row pitch: vector loads allowed (FULL / COL)
+    int32_t nd;                         // GENERAL: merged axes of the full space; ROW: merged row axes; innermost last
+    int64_t shape[kMaxDims], stride[kMaxDims];
+};
+
+struct Program {
+    int32_t n_inputs, n_code;
+    Input in[kMaxInputs];
+    int32_t code[kMaxCode];
+    void* out;
+    int32_t out_dtype, out_vec_ok;
+    int64_t rows, cols;
+};
+
+__device__ __forceinline__ float round_to(float v, int dt) {
+    switch (dt) {
+        case B200JT_BFLOAT16: return __bfloat162float(__float2bfloat16(v));
+        case B200JT_FLOAT16: return __half2float(__float2half(v));
+        case B200JT_BOOL: return v != 0.f ? 1.f : 0.f;
+        default: return v;
+    }
+}
+
+__device__ __forceinline__ float binary_f(int op, float a, float b) {
+    switch (op) {
+        case OP_ADD: return a + b;
+        case OP_SUB: return a - b;
+        case OP_MUL: return a * b;
+        case OP_DIV: case OP_FLOORDIV: return a / b;
+        case OP_MOD: return a - floorf(a / b) * b;
+        case OP_POW: return powf(a, b);
+        case OP_MAX: return a > b ? a : b;
+        case OP_MIN: return b < a ? b : a;
+        case OP_LT: return (float)(a < b);
+        case OP_LE: return (float)(a <= b);
+        case OP_GT: return (float)(a > b);
+        case OP_GE: return (float)(a >= b);
+        case OP_EQ: return (float)(a == b);
+        case OP_NE: return (float)(a != b);
+        case OP_LAND: return (float)((a != 0) && (b != 0));
+        case OP_LOR: return (float)((a != 0) || (b != 0));
+        case OP_LXOR: return (float)((a != 0) != (b != 0));
+    }
+    return a;
+}
+
+__device__ __forceinline__ float unary_f(int op, float a) {
+    switch (op) {
+        case U_NEG: return -a;
+        case U_ABS: return fabsf(a);
+        case U_LNOT: return (float)(a == 0);
+        case U_LOG: return logf(a);
+        case U_EXP: return expf(a);
+        case U_SQRT: return sqrtf(a);
+        case U_ROUND: return roundf(a);
+        case U_FLOOR: return floorf(a);
+        case U_CEIL: return ceilf(a);
+        case U_SIN: return sinf(a);
+        case U_ASIN: return asinf(a);
+        case U_SINH: return sinhf(a);
+        case U_ASINH: return asinhf(a);
+        case U_TAN: return tanf(a);
+        case U_ATAN: return atanf(a);
+        case U_TANH: return tanhf(a);
+        case U_ATANH: return atanhf(a);
+        case U_COS: return cosf(a);
+        case U_ACOS: return acosf(a);
+        case U_COSH: return coshf(a);
+        case U_ACOSH: return acoshf(a);
+        case U_SIGMOID: { const float t = -a < 30.f ? -a : 30.f; return 1.f / (1.f + expf(t)); }
+        case U_ERF: return erff(a);
+        case U_ERFINV: return erfinvf(a);
+    }
+    return a;           // U_CAST: the rounding to the result dtype is the cast
+}
+
+// VEC consecutive elements of input k starting at (row, col); `n` of them are inside the row.
+__device__ __forceinline__ int64_t row_offset(const Input& I, int64_t row) {
+    int64_t off = 0;
+    for (int d = I.nd - 1; d >= 0; d--) { off += (row % I.shape[d]) * I.stride[d]; row /= I.shape[d]; }
+    return off;
+}
+
+__device__ __forceinline__ void load_input(const Input& I, int64_t row, int64_t col, int64_t cols, int n, float* o) {
+    switch (I.mode) {
+        case IN_SCALAR: {
+            const float v = load_as<float>(I.ptr, I.dtype, 0);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) o[e] = v;
+            return;
+        }
+        case IN_ROW: {
+            const float v = load_as<float>(I.ptr, I.dtype, row_offset(I, row));
+#pragma unroll
+            for (int e = 0; e < VEC; e++) o[e] = v;
+            return;
+        }
+        case IN_FULL: case IN_COL: {
+            const int64_t off = (I.mode == IN_FULL ? row * cols : 0) + col;
+            if (I.vec_ok && n == VEC) {
+                if (I.dtype == B200JT_FLOAT32) {
+                    const float4 a = __ldg(reinterpret_cast<const float4*>((const float*)I.ptr + off));
+                    const float4 b = __ldg(reinterpret_cast<const float4*>((const float*)I.ptr + off) + 1);
+                    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+                    return;
+                }
+                if (I.dtype == B200JT_BFLOAT16) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4*>((const __nv_bfloat16*)I.ptr + off));
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+                    return;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; e++) o[e] = e < n ? load_as<float>(I.ptr, I.dtype, off + e) : 0.f;
+            return;
+        }
+        default: {
+            // general broadcast: decompose the flat index of the first element, then step like an odometer
+            int64_t idx[kMaxDims];
+            int64_t r = row * cols + col, off = 0;
+            for (int d = I.nd - 1; d >= 0; d--) { idx[d] = r % I.shape[d]; r /= I.shape[d]; off += idx[d] * I.stride[d]; }
+            for (int e = 0; e < VEC; e++) {
+                o[e] = e < n ? load_as<float>(I.ptr, I.dtype, off) : 0.f;
+                for (int d = I.nd - 1; d >= 0; d--) {
+                    off += I.stride[d];
+                    if (++idx[d] < I.shape[d]) break;
+                    off -= I.stride[d] * I.shape[d]; idx[d] = 0;
+                }
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void store_output(const Program& P, int64_t off, int n, const float* v) {
+    if (P.out_vec_ok && n == VEC) {
+        if (P.out_dtype == B200JT_FLOAT32) {
+            float4* p = reinterpret_cast<float4*>((float*)P.out + off);
+            __stcs(p, make_float4(v[0], v[1], v[2], v[3]));
+            __stcs(p + 1, make_float4(v[4], v[5], v[6], v[7]));
+            return;
+        }
+        if (P.out_dtype == B200JT_BFLOAT16) {
+            uint4 u; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            __stcs(reinterpret_cast<uint4*>((__nv_bfloat16*)P.out + off), u);
+            return;
+        }
+    }
+    for (int e = 0; e < n; e++) store_as<float>(P.out, P.out_dtype, off + e, v[e]);
+}
+
+// Runs the chain that starts at code[pc] for VEC elements; returns the pc of the statement word that ends it and leaves
+// the chain's value in `top`.
+__device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row, int64_t col, int n, const float* rowval, float* top) {
+    float st[kStack][VEC];
+    float tmp[kTmp][VEC];
+    int sp = 0;
+    for (;; pc++) {
+        const int32_t w = P.code[pc];
+        const int op = w & 0xff, a = (w >> 8) & 0xffff, rdt = (w >> 24) & 0xff;
+        switch (op) {
+            case CH_INPUT: load_input(P.in[a], row, col, P.cols, n, st[sp]); sp++; break;
+            case CH_CONST: {
+                const float c = __int_as_float(P.code[++pc]);
+#pragma unroll
+                for (int e = 0; e < VEC; e++) st[sp][e] = c;
+                sp++; break;
+            }
+            case CH_ROWVAL: {
+                const float c = rowval[a];
+#pragma unroll
+                for (int e = 0; e < VEC; e++) st[sp][e] = c;
+                sp++; break;
+            }
+            case CH_UNARY:
+#pragma unroll
+                for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(unary_f(a, st[sp - 1][e]), rdt);
+                break;
+            case CH_BINARY:
+                sp--;
+                switch (a) {       // the common ops get straight-line code; the rest share the generic switch
+                    case OP_ADD:
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] + st[sp][e], rdt);
+                        break;
+                    case OP_SUB:
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] - st[sp][e], rdt);
+                        break;
+                    case OP_MUL:
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] * st[sp][e], rdt);
+                        break;
+                    default:
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(binary_f(a, st[sp - 1][e], st[sp][e]), rdt);
+                }
+                break;
+            case CH_TERNARY:     // stack: cond, x, y
+                sp -= 2;
+#pragma unroll
+                for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] != 0.f ? st[sp][e] : st[sp + 1][e], rdt);
+                break;
+            case CH_TSTORE:
+#pragma unroll
+                for (int e = 0; e < VEC; e++) tmp[a][e] = st[sp - 1][e];
+                break;
+            case CH_TLOAD:
+#pragma unroll
+                for (int e = 0; e < VEC; e++) st[sp][e] = tmp[a][e];
+                sp++; break;
+            default:             // a statement word: the chain is complete
+#pragma unroll
+                for (int e = 0; e < VEC; e++) top[e] = st[0][e];
+                return pc;
+        }
+    }
+}
+
+__device__ __forceinline__ float fold(int rop, float a, float b) {
+    switch (rop) {
+        case OP_MAX: return a > b ? a : b;
+        case OP_MIN: return b < a ? b : a;
+        case OP_MUL: return a * b;
+        default: return a + b;          // add, mean
+    }
+}
+__device__ __forceinline__ float fold_init(int rop) {
+    switch (rop) {
+        case OP_MAX: return -FLT_MAX;
+        case OP_MIN: return FLT_MAX;
+        case OP_MUL: return 1.f;
+        default: return 0.f;
+    }
+}
+
+// Pure map (the program is one chain ending in STORE): work items are 8-element vectors of the full space.
+__global__ void __launch_bounds__(256)
+chain_map_kernel(const __grid_constant__ Program P) {
+    const int64_t vpr = (P.cols + VEC - 1) / VEC, items = P.rows * vpr;
+    for (int64_t it = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; it < items; it += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = it / vpr, col = (it - row * vpr) * VEC;
+        const int n = (int)min((int64_t)VEC, P.cols - col);
+        float v[VEC];
+        eval_chain(P, 0, row, col, n, nullptr, v);
+        store_output(P, row * P.cols + col, n, v);
+    }
+}
+
+// G threads per row (32: a warp, shuffles only; 256: the whole CTA, one shared-memory hop).
+template <int G>
+__global__ void __launch_bounds__(256)
+chain_rows_kernel(const __grid_constant__ Program P) {
+    __shared__ float xch[8];
+    constexpr int GROUPS = 256 / G;
+    const int g = threadIdx.x / G, t = threadIdx.x % G;
+    const int64_t n_groups = (int64_t)gridDim.x * GROUPS;
+    const float rcols = 1.f / (float)P.cols;
+    // uniform trip count per CTA so that __syncthreads inside the loop is legal for G == 256
+    for (int64_t row = (int64_t)blockIdx.x * GROUPS + g; row < P.rows; row += n_groups) {
+        float rowval[kMaxRowVals];
+        int pc = 0;
+        while (pc < P.n_code) {
+            // find the statement that ends the chain starting at pc (statement words are >= CH_ROW_REDUCE)
+            int end = pc;
+            while ((P.code[end] & 0xff) < CH_ROW_REDUCE) end += ((P.code[end] & 0xff) == CH_CONST) ? 2 : 1;
+            const int32_t w = P.code[end];
+            const int sop = w & 0xff, a = (w >> 8) & 0xffff, rdt = (w >> 24) & 0xff;
+            if (sop == CH_STORE_ROW) {
+                if (t == 0) store_as<float>(P.out, P.out_dtype, row, rowval[a]);
+            } else if (sop == CH_ROW_MAP) {
+                float v[VEC];
+                eval_chain(P, pc, row, 0, 1, rowval, v);
+                rowval[a] = v[0];
+            } else if (sop == CH_STORE) {
+                for (int64_t col = (int64_t)t * VEC; col < P.cols; col += (int64_t)G * VEC) {
+                    const int n = (int)min((int64_t)VEC, P.cols - col);
+                    float v[VEC];
+                    eval_chain(P, pc, row, col, n, rowval, v);
+                    store_output(P, row * P.cols + col, n, v);
+                }
+            } else {            // CH_ROW_REDUCE
+                const int slot = a & 15, rop = a >> 4;
+                float acc = fold_init(rop);
+                for (int64_t col = (int64_t)t * VEC; col < P.cols; col += (int64_t)G * VEC) {
+                    const int n = (int)min((int64_t)VEC, P.cols - col);
+                    float v[VEC];
+                    eval_chain(P, pc, row, col, n, rowval, v);
+                    if (rop == OP_MEAN) {
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) if (e < n) acc += v[e] * rcols;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) if (e < n) acc = fold(rop, acc, v[e]);
+                    }
+                }
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) acc = fold(rop, acc, __shfl_xor_sync(0xffffffffu, acc, d));
+                if (G == 256) {
+                    __syncthreads();                       // xch free again
+                    if ((threadIdx.x & 31) == 0) xch[threadIdx.x >> 5] = acc;
+                    __syncthreads();
+                    acc = xch[0];
+#pragma unroll
+                    for (int k = 1; k < 8; k++) acc = fold(rop, acc, xch[k]);
+                }
+                rowval[slot] = round_to(acc, rdt);
+            }
+            pc = end + 1;
+        }
+    }
+}
+
+}  // namespace chain
+}  // namespace b200jt
+
+using namespace b200jt;
+
+/* One launch for a fused chain. inputs: n_inputs tensors, each given with the rank of `full_shape` (size 1 on the axes
+ * it is broadcast over); the last `row_axes` axes of full_shape form a row (the axes the program's reduces fold; 0 if
+ * there is none); code: the postfix program described at the top of this file; out: the element-wise result
+ * (full_shape) or, for a program ending in STORE_ROW, one value per row. */
+extern "C" int b200jt_fused_chain(const b200jt_tensor* inputs, int n_inputs, const int64_t* full_shape, int ndim, int row_axes,
+                                  const int32_t* code, int n_code, const b200jt_tensor* out, void* stream) {
+    using namespace chain;
+    B200JT_CHECK_ARG(n_inputs >= 0 && n_inputs <= kMaxInputs, "at most 8 inputs");
+    B200JT_CHECK_ARG(code && n_code > 0 && n_code <= kMaxCode, "program too long");
+    B200JT_CHECK_ARG(ndim >= 1 && ndim <= kMaxDims && row_axes >= 0 && row_axes <= ndim, "bad shape");
+    B200JT_CHECK_ARG(valid_tensor(out), "invalid output descriptor");
+    Program Q; memset(&Q, 0, sizeof(Q));
+    bool has_row_stmt = false, store_row = false;
+    // validate the program: stack depth, operand indices, statement structure
+    {
+        int sp = 0;
+        for (int pc = 0; pc < n_code; pc++) {
+            const int op = code[pc] & 0xff, a = (code[pc] >> 8) & 0xffff;
+            switch (op) {
+                case CH_INPUT: B200JT_CHECK_ARG(a < n_inputs, "program names an input that was not passed"); sp++; break;
+                case CH_CONST: B200JT_CHECK_ARG(pc + 1 < n_code, "truncated constant"); pc++; sp++; break;
+                case CH_ROWVAL: B200JT_CHECK_ARG(a < kMaxRowVals, "row value slot out of range"); sp++; break;
+                case CH_UNARY: B200JT_CHECK_ARG(sp >= 1 && a < U_INVALID, "bad unary"); break;
+                case CH_BINARY: B200JT_CHECK_ARG(sp >= 2, "binary needs two operands"); sp--; break;
+                case CH_TERNARY: B200JT_CHECK_ARG(sp >= 3, "ternary needs three operands"); sp -= 2; break;
+                case CH_TSTORE: B200JT_CHECK_ARG(sp >= 1 && a < kTmp, "bad temporary"); break;
+                case CH_TLOAD: B200JT_CHECK_ARG(a < kTmp, "bad temporary"); sp++; break;
+                case CH_ROW_REDUCE: B200JT_CHECK_ARG(sp == 1 && (a & 15) < kMaxRowVals, "bad row reduce"); sp = 0; has_row_stmt = true; break;
+                case CH_ROW_MAP: B200JT_CHECK_ARG(sp == 1 && a < kMaxRowVals, "bad row map"); sp = 0; has_row_stmt = true; break;
+                case CH_STORE: B200JT_CHECK_ARG(sp == 1 && pc == n_code - 1, "STORE must end the program"); sp = 0; break;
+                case CH_STORE_ROW: B200JT_CHECK_ARG(sp == 0 && a < kMaxRowVals && pc == n_code - 1, "STORE_ROW must end the program"); store_row = true; break;
+                default: return fail(-1, "b200jt_fused_chain: unknown instruction");
+            }
+            B200JT_CHECK_ARG(sp <= kStack, "expression too deep");
+        }
+        const int last = code[n_code - 1] & 0xff;
+        B200JT_CHECK_ARG(last == CH_STORE || last == CH_STORE_ROW, "the program must end in STORE or STORE_ROW");
+    }
+    for (int d = 0; d < ndim; d++) B200JT_CHECK_ARG(full_shape[d] >= 0, "negative extent");
+    for (int k = 0; k < n_inputs; k++) {
+        const b200jt_tensor* t = &inputs[k];
+        B200JT_CHECK_ARG(valid_tensor(t) && t->ndim == ndim, "every input must be given with the rank of full_shape");
+        for (int d = 0; d < ndim; d++)
+            B200JT_CHECK_ARG(t->shape[d] == full_shape[d] || t->shape[d] == 1, "Shape not match " + shape_str(t));
+    }
+    const bool pure_map = !has_row_stmt && !store_row;
+    // How an input relates to a split of the axes into `ra` trailing row axes (cols) and the rest (rows).
+    auto classify = [&](const b200jt_tensor* t, int ra) {
+        if (numel(t) == 1) return (int)IN_SCALAR;
+        bool dep_rows = false, dep_cols = false, full_rows = true, full_cols = true;
+        for (int d = 0; d < ndim; d++) {
+            if (full_shape[d] == 1) continue;
+            const bool bc = t->shape[d] == 1;
+            if (d < ndim - ra) { if (bc) full_rows = false; else dep_rows = true; }
+            else { if (bc) full_cols = false; else dep_cols = true; }
+        }
+        if (full_rows && full_cols) return (int)IN_FULL;
+        if (!dep_rows && full_cols) return (int)IN_COL;
+        if (!dep_cols) return (int)IN_ROW;
+        return (int)IN_GENERAL;
+    };
+    if (pure_map) {
+        // any split is legal: take the one with the longest rows (up to 64 Ki elements) that leaves no input in the
+        // general form, preferring rows that are whole vectors
+        int best = -1; int best_score = -1;
+        for (int ra = 0; ra <= ndim; ra++) {
+            int64_t c = 1;
+            for (int d = ndim - ra; d < ndim; d++) c *= full_shape[d];
+            if (c > (1 << 16) && ra > 1) break;
+            int general = 0;
+            for (int k = 0; k < n_inputs; k++) general += classify(&inputs[k], ra) == IN_GENERAL;
+            const int score = (general == 0 ? 4 : 0) + (c % VEC == 0 ? 2 : 0) + (c >= 64 ? 1 : 0);
+            if (score >= best_score) { best_score = score; best = ra; }
+        }
+        row_axes = best < 0 ? 0 : best;
+    }
+    int64_t rows = 1, cols = 1;
+    for (int d = 0; d < ndim; d++) (d < ndim - row_axes ? rows : cols) *= full_shape[d];
+    B200JT_CHECK_ARG(numel(out) == (store_row ? rows : rows * cols), "out has the wrong size " + shape_str(out));
+    if (numel(out) == 0) return 0;
+    bool all_flat = true;
+    for (int k = 0; k < n_inputs; k++) { const int m = classify(&inputs[k], row_axes); all_flat &= (m == IN_FULL || m == IN_SCALAR); }
+    if (pure_map && all_flat) {
+        // nothing depends on the position inside the tensor: one flat index space cut into rows of whole vectors
+        const int64_t n = rows * cols;
+        cols = n % 2048 == 0 ? 2048 : n;
+        rows = n / cols;
+    }
+    Q.rows = rows; Q.cols = cols;
+    Q.n_inputs = n_inputs; Q.n_code = n_code;
+    memcpy(Q.code, code, sizeof(int32_t) * n_code);
+    Q.out = out->ptr; Q.out_dtype = out->dtype;
+    Q.out_vec_ok = ((uintptr_t)out->ptr % 32 == 0) && cols % VEC == 0;
+    for (int k = 0; k < n_inputs; k++) {
+        const b200jt_tensor* t = &inputs[k];
+        Input& I = Q.in[k];
+        I.ptr = t->ptr; I.dtype = t->dtype;
+        I.mode = classify(t, row_axes);
+        const int es = dtype_size(t->dtype);
+        const bool aligned = ((uintptr_t)t->ptr % 32 == 0) || (es == 2 && (uintptr_t)t->ptr % 16 == 0);
+        I.vec_ok = (I.mode == IN_FULL || I.mode == IN_COL) && aligned && cols % VEC == 0;
+        if (I.mode == IN_ROW || I.mode == IN_GENERAL) {
+            // merged axes (of the row axes only for ROW): neighbours the input walks contiguously or ignores together
+            const int lim = I.mode == IN_ROW ? ndim - row_axes : ndim;
+            int64_t tstride[kMaxDims]; int64_t ts = 1;
+            for (int d = ndim - 1; d >= 0; d--) { tstride[d] = (t->shape[d] == 1 && full_shape[d] != 1) ? 0 : ts; ts *= t->shape[d]; }
+            int nd = 0;
+            for (int d = 0; d < lim; d++) {
+                if (full_shape[d] == 1) continue;
+                if (nd && ((I.stride[nd - 1] == 0 && tstride[d] == 0) ||
+                           (tstride[d] != 0 && I.stride[nd - 1] == tstride[d] * full_shape[d]))) {
+                    I.shape[nd - 1] *= full_shape[d]; I.stride[nd - 1] = tstride[d];
+                } else { I.shape[nd] = full_shape[d]; I.stride[nd] = tstride[d]; nd++; }
+            }
+            if (nd == 0) { I.shape[0] = 1; I.stride[0] = 0; nd = 1; }
+            I.nd = nd;
+        }
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (pure_map) {
+        const int64_t items = Q.rows * ((Q.cols + VEC - 1) / VEC);
+        chain::chain_map_kernel<<<grid_for(items, 256), 256, 0, st>>>(Q);
+    } else if (Q.cols <= 1024) {          // a warp per row for short rows, a CTA per row otherwise
+        const unsigned grid = grid_for((Q.rows + 7) / 8 * 256, 256);
+        chain::chain_rows_kernel<32><<<grid, 256, 0, st>>>(Q);
+    } else {
+        const unsigned grid = grid_for(Q.rows * 256, 256);
+        chain::chain_rows_kernel<256><<<grid, 256, 0, st>>>(Q);
+    }
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}

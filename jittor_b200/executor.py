@@ -23,6 +23,7 @@ from . import dtypes as dt
 from .var import Var
 
 _MATERIALIZE_LIMIT = 1 << 33       # elements; beyond this an unfused intermediate is refused
+counters = {"plans": 0}            # plans run so far: one per kernel group, the analogue of the reference's fused-op count
 
 
 class Plan:
@@ -53,6 +54,7 @@ def realize(roots):
                 if l._pending is not None:           # produced by a collective on another stream
                     l.wait()
             out = plan.run()
+            counters["plans"] += 1
             v._data = out.reshape(list(v.shape))
             plans.pop(id(v), None)
             stack.pop()
@@ -947,4 +949,26 @@ def _match_batchnorm(v):
     return Plan(leaves, run)
 
 
-_MATCHERS = [_match_conv, _match_conv_dgrad, _match_conv_wgrad, _match_pool, _match_matmul, _match_batched_matmul, _match_softmax, _match_layernorm, _match_batchnorm]
+def _match_fused_chain(v):
+    """Whatever no named pattern claimed: the maximal region of element-wise ops, broadcasts and trailing-axis reduces
+    under v as ONE launch of the chain interpreter (fusion.py)."""
+    from . import fusion
+    prog = fusion.build_program(v)
+    if prog is None:
+        return None
+    words, inputs, full, k, _ = prog
+    leaves, seen = [], set()
+    for var, _view in inputs:
+        if id(var) not in seen:
+            seen.add(id(var))
+            leaves.append(var)
+
+    def run():
+        out = _empty(v.shape, v.dtype)
+        return fusion.run_program(words, inputs, full, k, out)
+
+    return Plan(leaves, run)
+
+
+_MATCHERS = [_match_conv, _match_conv_dgrad, _match_conv_wgrad, _match_pool, _match_matmul, _match_batched_matmul, _match_softmax, _match_layernorm, _match_batchnorm,
+             _match_fused_chain]

@@ -1,0 +1,355 @@
+"""General element-wise chain fusion: the part of the reference's fuser that is not a named pattern.
+
+The reference groups any run of element-wise ops, broadcasts and reduces into one FusedOp and generates one loop nest
+for it (python/jittor/src/executor.cc:276-534, python/jittor/src/fused_op.cc:41-118, python/jittor/src/op_compiler.cc:839-1045).
+Here the executor asks `match(v)` for every Var no named pattern (conv, matmul, softmax, ...) claimed: starting at v it
+collects the maximal region of fusable nodes, writes it as the postfix program of `b200jt_fused_chain` (statements that
+reduce a row, compute per-row values, and store) and runs it as ONE launch. Nothing inside the region is materialised.
+
+What can be fused (everything else is a leaf = an input of the chain, computed first):
+  * unary / binary / ternary ops whose arithmetic the element-wise kernels do in the float32 class, with results of dtype
+    float32 / bfloat16 / float16 / bool;
+  * broadcast_to of a leaf (the leaf becomes a broadcast input) or of a per-row value;
+  * reduce add / mean / maximum / minimum / multiply over the trailing axes of the region's full shape;
+  * constants (`fill`).
+"""
+import ctypes
+import struct
+
+from . import _capi as C
+from .var import Var
+
+MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_STACK, MAX_TMP = 8, 160, 8, 8, 4
+
+CH_INPUT, CH_CONST, CH_ROWVAL, CH_UNARY, CH_BINARY, CH_TERNARY, CH_TSTORE, CH_TLOAD = 1, 2, 3, 4, 5, 6, 7, 8
+CH_ROW_REDUCE, CH_ROW_MAP, CH_STORE, CH_STORE_ROW = 9, 10, 11, 12
+
+UNARY_CODES = {n: i for i, n in enumerate(
+    ["cast", "negative", "abs", "logical_not", "bitwise_not", "log", "exp", "sqrt", "round", "floor", "ceil", "sin", "asin",
+     "sinh", "asinh", "tan", "atan", "tanh", "atanh", "cos", "acos", "cosh", "acosh", "sigmoid", "erf", "erfinv"])}
+del UNARY_CODES["bitwise_not"]                 # integer only
+BINARY_CODES = {n: i for i, n in enumerate(
+    ["add", "subtract", "multiply", "divide", "floor_divide", "mod", "pow", "maximum", "minimum", "less", "less_equal",
+     "greater", "greater_equal", "equal", "not_equal", "logical_and", "logical_or", "logical_xor"])}
+REDUCE_CODES = {"add": 0, "multiply": 2, "maximum": 7, "minimum": 8, "mean": 23}
+
+_FLOAT = ("float32", "bfloat16", "float16")
+_VALUE_DTYPES = _FLOAT + ("bool",)
+_LEAF_DTYPES = _FLOAT + ("bool", "int8", "int16", "int32", "uint8")
+
+
+class _Unfusable(Exception):
+    pass
+
+
+def _word(op, arg=0, dtype="float32"):
+    return op | (arg << 8) | (C.DTYPE_CODES[str(dtype)] << 24)
+
+
+def _is_node(v):
+    return isinstance(v, Var) and v._data is None and v._op is not None
+
+
+def _const_of(v):
+    """The Python number behind a constant Var (a scalar made from a number, or a `fill`), else None."""
+    if not _is_node(v) or v._op.kind != "fill":
+        return None
+    val = v._op.attrs["value"]
+    if isinstance(val, bool):
+        return 1.0 if val else 0.0
+    f = float(val)
+    if str(v.dtype) not in _FLOAT and str(v.dtype) != "bool" and abs(f) >= 1 << 24:
+        return None
+    return f
+
+
+def _float_class_node(v):
+    """True if the element-wise kernels would compute node v in the float32 class and its result is a dtype a fused chain
+    can hold."""
+    if not _is_node(v) or str(v.dtype) not in _VALUE_DTYPES:
+        return False
+    op, ins = v._op, v._op.inputs
+    for i in ins:
+        if str(i.dtype) in ("float64", "int64"):
+            return False
+    if op.kind == "binary":
+        name = op.attrs["op"]
+        if name not in BINARY_CODES:
+            return False
+        if str(v.dtype) == "bool":               # comparisons compute in the promoted class of the operands
+            return any(str(i.dtype) in _FLOAT for i in ins)
+        return str(v.dtype) in _FLOAT
+    if op.kind == "unary":
+        name = op.attrs["op"]
+        if name in C.DTYPE_CODES:                # cast: result dtype checked above; the source must fit a float32 exactly enough
+            return str(ins[0].dtype) in _LEAF_DTYPES
+        if name not in UNARY_CODES:
+            return False
+        return str(v.dtype) in _FLOAT or str(ins[0].dtype) in _FLOAT
+    if op.kind == "ternary":
+        return str(v.dtype) in _FLOAT
+    return False
+
+
+class _Builder:
+    """Walks the graph under `root` and writes the program. Shapes are handled as *views*: a node's shape written with
+    the rank of the region's full shape (size 1 on the axes it does not have), which is what decides whether the node is
+    a full-space value, a per-row value, or something the region cannot hold (a leaf)."""
+
+    def __init__(self, root):
+        self.root = root
+        self.inputs = []              # (Var, view)
+        self.input_ids = {}
+        self.statements = []          # finished statements (lists of words)
+        self.row_slots = {}           # (id(node), axes) -> slot
+        self.n_ops = 0
+        if _is_node(root) and root._op.kind == "reduce":
+            x = root._op.inputs[0]
+            self.full = list(x.shape)
+            self.k = self._trailing(root._op.attrs["reduce_mask"], x.ndim) or 0
+            if not self.k:
+                raise _Unfusable
+        else:
+            self.full = list(root.shape)
+            self.k = self._find_reduce_axes(root)
+        self.d = len(self.full)
+        self.rows = self.cols = 1
+        for i, s in enumerate(self.full):
+            if i < self.d - self.k:
+                self.rows *= s
+            else:
+                self.cols *= s
+
+    @staticmethod
+    def _trailing(mask, nd):
+        k = bin(mask).count("1")
+        return k if k and mask == ((1 << k) - 1) << (nd - k) else None
+
+    def _find_reduce_axes(self, root):
+        """Number of trailing axes the region's reduces fold (0 if it has none): the first reduce over the full shape
+        reachable through element-wise nodes decides."""
+        seen, stack = set(), [root]
+        while stack and len(seen) < 256:
+            v = stack.pop()
+            if id(v) in seen or not _is_node(v):
+                continue
+            seen.add(id(v))
+            op = v._op
+            if op.kind == "reduce":
+                x = op.inputs[0]
+                if list(x.shape) == self.full and op.attrs["op"] in REDUCE_CODES:
+                    k = self._trailing(op.attrs["reduce_mask"], x.ndim)
+                    if k is not None:
+                        return k
+            elif op.kind in ("binary", "unary", "ternary", "broadcast_to"):
+                stack.extend(op.inputs)
+        return 0
+
+    # ---- views -----------------------------------------------------------------------------------
+    def _view(self, shape, axes):
+        """Shape `shape` (rank <= len(axes), right-aligned against a node whose axes sit at `axes`) in full rank."""
+        shape = list(shape)
+        if len(shape) > len(axes):
+            raise _Unfusable
+        view = [1] * self.d
+        for s, a in zip(shape, axes[len(axes) - len(shape):]):
+            view[a] = s
+        return view
+
+    def _klass(self, view):
+        if view == self.full:
+            return "full"
+        if self.k and all(s == 1 for s in view[self.d - self.k:]):
+            return "row"
+        return None
+
+    def _input(self, v, view, ctx):
+        if str(v.dtype) not in _LEAF_DTYPES:
+            raise _Unfusable
+        for s, f in zip(view, self.full):
+            if s != f and s != 1:
+                raise _Unfusable
+        if ctx == "row" and any(s != 1 for s in view[self.d - self.k:]):
+            raise _Unfusable                    # a per-row statement cannot read something that varies along the row
+        key = (id(v), tuple(view))
+        if key not in self.input_ids:
+            if len(self.inputs) >= MAX_INPUTS:
+                raise _Unfusable
+            self.input_ids[key] = len(self.inputs)
+            self.inputs.append((v, view))
+        return _word(CH_INPUT, self.input_ids[key], "float32")
+
+    # ---- expressions -----------------------------------------------------------------------------
+    def _fusable(self, v, view):
+        if not _is_node(v) or (v.is_stop_fuse() and v is not self.root):
+            return False
+        op = v._op
+        if op.kind in ("binary", "unary", "ternary"):
+            return _float_class_node(v) and self._klass(view) is not None
+        if op.kind == "reduce":
+            x = op.inputs[0]
+            return (self.k > 0 and list(x.shape) == self.full and op.attrs["op"] in REDUCE_CODES
+                    and self._trailing(op.attrs["reduce_mask"], x.ndim) == self.k and str(v.dtype) in _FLOAT
+                    and str(x.dtype) in _FLOAT)
+        if op.kind == "broadcast_to":
+            return self._klass(view) is not None
+        return False
+
+    def _emit(self, v, axes, code, ctx, memo):
+        """Appends postfix code for the value of v, whose own axes sit at positions `axes` of the full shape.
+        ctx 'full': evaluated per element; 'row': once per row."""
+        c = _const_of(v)
+        if c is not None:
+            code += [_word(CH_CONST, 0, "float32"), struct.unpack("<i", struct.pack("<f", c))[0]]
+            return
+        axes = axes[len(axes) - v.ndim:] if v.ndim <= len(axes) else None
+        if axes is None:
+            raise _Unfusable
+        key = (id(v), tuple(axes))
+        if key in self.row_slots:
+            code.append(_word(CH_ROWVAL, self.row_slots[key], "float32"))
+            return
+        view = self._view(v.shape, axes)
+        if not self._fusable(v, view):
+            code.append(self._input(v, view, ctx))          # a leaf: realised data, or a node another kernel computes first
+            return
+        op = v._op
+        if op.kind == "reduce":
+            code.append(_word(CH_ROWVAL, self._row_reduce(v, key), "float32"))
+            return
+        if op.kind == "broadcast_to":
+            x = op.inputs[0]
+            mask, keep = op.attrs["bcast_mask"], op.attrs["keepdims_mask"]
+            kept = [axes[i] for i in range(v.ndim) if not (mask >> i & 1) or (keep >> i & 1)]
+            self.n_ops += 1
+            self._emit(x, kept, code, ctx, memo)            # the operand simply lacks (or has size 1 on) the new axes
+            return
+        if self._klass(view) == "row" and ctx == "full":
+            code.append(_word(CH_ROWVAL, self._row_map(v, axes, key), "float32"))
+            return
+        if key in memo:                          # shared sub-expression inside this chain
+            start, end, slot = memo[key]
+            if slot is None:
+                slot = sum(1 for m in memo.values() if m[2] is not None)
+                if slot >= MAX_TMP:
+                    raise _Unfusable
+                code.insert(end, _word(CH_TSTORE, slot, "float32"))
+                for k2, (s0, e0, t0) in list(memo.items()):       # spans behind the insertion point move by one word
+                    if s0 >= end:
+                        memo[k2] = (s0 + 1, e0 + 1, t0)
+                    elif e0 > end:
+                        memo[k2] = (s0, e0 + 1, t0)
+                memo[key] = (start, end, slot)
+            code.append(_word(CH_TLOAD, slot, "float32"))
+            return
+        start = len(code)
+        for i in op.inputs:
+            self._emit(i, axes, code, ctx, memo)
+        if op.kind == "unary":
+            name = op.attrs["op"]
+            code.append(_word(CH_UNARY, UNARY_CODES["cast"] if name in C.DTYPE_CODES else UNARY_CODES[name], v.dtype))
+        elif op.kind == "binary":
+            code.append(_word(CH_BINARY, BINARY_CODES[op.attrs["op"]], v.dtype))
+        else:
+            code.append(_word(CH_TERNARY, 0, v.dtype))
+        self.n_ops += 1
+        memo[key] = (start, len(code), None)
+        if len(code) > MAX_CODE:
+            raise _Unfusable
+
+    # ---- statements ------------------------------------------------------------------------------
+    def _new_slot(self):
+        if len(self.row_slots) >= MAX_ROWVALS:
+            raise _Unfusable
+        return len(self.row_slots)
+
+    def _row_reduce(self, v, key):
+        code = []
+        self._emit(v._op.inputs[0], list(range(self.d)), code, "full", {})
+        slot = self._new_slot()
+        code.append(_word(CH_ROW_REDUCE, slot | (REDUCE_CODES[v._op.attrs["op"]] << 4), v.dtype))
+        self.statements.append(code)
+        self.row_slots[key] = slot
+        self.n_ops += 1
+        return slot
+
+    def _row_map(self, v, axes, key):
+        code = []
+        self._emit(v, axes, code, "row", {})
+        slot = self._new_slot()
+        code.append(_word(CH_ROW_MAP, slot, v.dtype))
+        self.statements.append(code)
+        self.row_slots[key] = slot
+        return slot
+
+    def build(self):
+        root = self.root
+        full_axes = list(range(self.d))
+        if _is_node(root) and root._op.kind == "reduce":
+            if not self._fusable(root, None):
+                raise _Unfusable
+            slot = self._row_reduce(root, (id(root), ()))
+            self.statements.append([_word(CH_STORE_ROW, slot, root.dtype)])
+        else:
+            if not self._fusable(root, list(root.shape)) or (_is_node(root) and root._op.kind == "broadcast_to"):
+                raise _Unfusable
+            code = []
+            self._emit(root, full_axes, code, "full", {})
+            code.append(_word(CH_STORE, 0, root.dtype))
+            self.statements.append(code)
+        words = [w for st in self.statements for w in st]
+        if len(words) > MAX_CODE:
+            raise _Unfusable
+        self._check_stack(words)
+        return words
+
+    @staticmethod
+    def _check_stack(words):
+        sp, pc = 0, 0
+        while pc < len(words):
+            op = words[pc] & 0xff
+            if op in (CH_INPUT, CH_ROWVAL, CH_TLOAD):
+                sp += 1
+            elif op == CH_CONST:
+                sp += 1
+                pc += 1
+            elif op == CH_BINARY:
+                sp -= 1
+            elif op == CH_TERNARY:
+                sp -= 2
+            elif op >= CH_ROW_REDUCE:
+                sp = 0
+            if sp > MAX_STACK:
+                raise _Unfusable
+            pc += 1
+
+
+def build_program(v):
+    """(words, inputs [(Var, view shape)], full shape, row axes, n fused ops) for the region rooted at v, or None."""
+    from .flags import flags
+    if not flags.b200_fuse_chains:
+        return None
+    try:
+        b = _Builder(v)
+        words = b.build()
+    except _Unfusable:
+        return None
+    if b.n_ops < 2:
+        return None            # a single op: the dedicated kernels do that better
+    # a reduce whose rows are few and long would leave most of the GPU idle (one group of threads per row)
+    if b.k and b.rows < 64 and b.cols > (1 << 14):
+        return None
+    return words, b.inputs, b.full, b.k, b.n_ops
+
+
+def run_program(words, inputs, full, k, out):
+    """Launches b200jt_fused_chain for realised inputs; `out` is the preallocated result tensor."""
+    n = len(inputs)
+    descs = (C.Tensor * max(n, 1))()
+    for i, (var, view) in enumerate(inputs):
+        descs[i] = C.desc(var._data, view)
+    shp = (ctypes.c_int64 * len(full))(*full)
+    code = (ctypes.c_int32 * len(words))(*words)
+    C.check(C.lib.b200jt_fused_chain(descs, n, shp, len(full), k, code, len(words), C.desc(out), C.stream_ptr()),
+            f"fused chain over {full} ({len(words)} words, {n} inputs)")
+    return out

@@ -100,7 +100,13 @@ class Var:
         return getattr(self, "_stop_grad", False)
 
     def stop_fuse(self):
+        """This Var is computed on its own and stored: no fused chain reaches through it
+        (python/jittor/src/var_holder.h `stop_fuse`, python/jittor/test/test_stop_fuse.py)."""
+        self._stop_fuse = True
         return self
+
+    def is_stop_fuse(self):
+        return getattr(self, "_stop_fuse", False)
 
     def __len__(self):
         return self._shape[0]
@@ -617,6 +623,8 @@ def reshape(x, shape):
         raise ValueError(f"cannot reshape {list(x.shape)} to {shape}")
     if not shape:
         shape = [1]
+    if shape == list(x.shape):
+        return x
     return Var(shape, x.dtype, Op("reshape", [x]))
 
 

@@ -1,0 +1,103 @@
+"""Host logic of the general chain fusion (no GPU): which regions become one program, how their statements are ordered,
+and what stays a leaf. Mirrors the grouping cases of python/jittor/test/test_fused_op.py:144-176 (reduce + broadcast in
+one fused op) and python/jittor/test/test_stop_fuse.py."""
+import jittor_b200 as jt
+from jittor_b200 import fusion, nn, executor
+
+CH = {1: "IN", 2: "CONST", 3: "ROWVAL", 4: "UN", 5: "BIN", 6: "TERN", 7: "TST", 8: "TLD", 9: "RRED", 10: "RMAP", 11: "STORE", 12: "STROW"}
+
+
+def ph(shape, dtype="float32"):
+    return jt.Var(shape, dtype)
+
+
+def ops(words):
+    out, pc = [], 0
+    while pc < len(words):
+        op = words[pc] & 0xff
+        out.append(CH[op])
+        pc += 2 if op == 2 else 1
+    return out
+
+
+def test_scale_shift_is_one_map():
+    x, w, b = ph([64, 4096]), ph([4096]), ph([4096])
+    words, inputs, full, k, n = fusion.build_program(x * w + b)
+    assert ops(words) == ["IN", "IN", "BIN", "IN", "BIN", "STORE"] and k == 0 and full == [64, 4096]
+    assert [view for _, view in inputs] == [[64, 4096], [1, 4096], [1, 4096]]
+    assert executor._match_fused_chain(x * w + b).leaves == [x, w, b]
+
+
+def test_shared_subexpression_uses_a_temporary():
+    x, b = ph([64, 4096]), ph([4096])
+    words, inputs, _, _, _ = fusion.build_program(nn.relu(x + b))
+    assert ops(words) == ["IN", "IN", "BIN", "TST", "CONST", "BIN", "TLD", "CONST", "TERN", "STORE"]
+    assert len(inputs) == 2
+
+
+def test_multiply_then_row_sum_is_one_reduce_statement():
+    a, b = ph([32, 100]), ph([32, 100])
+    words, inputs, full, k, _ = fusion.build_program((a * b).sum(1))
+    assert ops(words) == ["IN", "IN", "BIN", "RRED", "STROW"] and k == 1 and full == [32, 100]
+    words, _, _, k, _ = fusion.build_program((a * b).sum(1, keepdims=True))
+    assert ops(words)[-1] == "STROW" and k == 1
+
+
+def test_reduce_then_broadcast_back_orders_the_statements():
+    x = ph([32, 100])
+    y = (x - x.mean(1, keepdims=True)) / ((x * x).mean(1, keepdims=True) + 1e-5).sqrt()
+    words, inputs, _, k, _ = fusion.build_program(y)
+    o = ops(words)
+    assert k == 1 and len(inputs) == 1
+    assert o.count("RRED") == 2 and o.count("RMAP") == 1 and o[-1] == "STORE"
+    assert o.index("RMAP") > max(i for i, s in enumerate(o) if s == "RRED") - 100      # the per-row map follows its reduce
+    # explicit broadcast_to of a per-row value without keepdims
+    m = x.max(1)
+    z = x - m.broadcast(x, [1])
+    words, inputs, _, k, _ = fusion.build_program(z)
+    assert ops(words) == ["IN", "RRED", "IN", "ROWVAL", "BIN", "STORE"] and len(inputs) == 1
+
+
+def test_softmax_backward_is_one_program():
+    x, dy = ph([128, 1000]), ph([128, 1000])
+    g = jt.grad((nn.softmax(x, -1) * dy).sum(), x)
+    prog = fusion.build_program(g)
+    assert prog is not None
+    words, inputs, full, k, _ = prog
+    assert k == 1 and full == [128, 1000] and {id(v) for v, _ in inputs} == {id(x), id(dy)}
+    assert ops(words)[-1] == "STORE"
+
+
+def test_what_is_not_fused():
+    x = ph([32, 100])
+    assert fusion.build_program(x + 1.0) is None                         # a single op keeps its dedicated kernel
+    xi = ph([32, 100], "int32")
+    assert fusion.build_program(xi * 2 + 1) is None                      # integer arithmetic is not the float32 class
+    xd = ph([32, 100], "float64")
+    assert fusion.build_program(xd * 2.0 + 1.0) is None
+    col = (x * 2.0).sum(0)                                               # a reduce over leading axes is not a row reduce
+    assert fusion.build_program(col) is None
+    y = (x * 2.0).stop_fuse()                                            # stop_fuse makes a leaf
+    words, inputs, _, _, _ = fusion.build_program((y + 1.0) * 3.0)
+    assert [id(v) for v, _ in inputs] == [id(y)]
+    with jt.flag_scope(b200_fuse_chains=0):
+        assert fusion.build_program(x * 2.0 + 1.0) is None
+
+
+def test_named_patterns_keep_their_kernels():
+    x = ph([32, 4096])
+    v = nn.softmax(x, -1)
+    first = next(m for m in executor._MATCHERS if m(v) is not None)
+    assert first is executor._match_softmax
+    a, b = ph([64, 32]), ph([32, 48])
+    v = nn.matmul(a, b)
+    assert next(m for m in executor._MATCHERS if m(v) is not None) is executor._match_matmul
+
+
+def test_bf16_chain_keeps_node_dtypes():
+    xb, w = ph([8, 16, 6, 6], "bfloat16"), ph([16])
+    with jt.flag_scope(amp_reg=2):
+        v = nn.relu(xb * w.broadcast(xb, [0, 2, 3]))
+    words, inputs, full, k, _ = fusion.build_program(v)
+    assert v.dtype == "bfloat16" and (words[-1] >> 24) == 7                      # STORE carries the bfloat16 code
+    assert [view for _, view in inputs] == [[8, 16, 6, 6], [1, 16, 1, 1]]

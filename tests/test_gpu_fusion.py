@@ -1,0 +1,154 @@
+"""GPU parity of the fused-chain kernel (csrc/fused_chain.cu, fusion.py): every case is computed three ways -- fused
+(one launch, asserted through the executor's plan counter), op by op with fusion switched off, and by the CPU oracle's
+element-wise / reduce restatements. Fused and unfused results must be the same bits for element-wise chains (both round
+every intermediate to its dtype); reductions and the oracle are compared with the fp32 1e-5 (bf16 2e-2) mixed tolerance."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import meta_ops_ref as ref
+from tests.golden_cases import check
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def jt():
+    import jittor_b200
+    return jittor_b200
+
+
+def bf16_round(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).bfloat16().float().numpy()
+
+
+def run_both(jt, build, arrays):
+    """build(*Vars) -> Var. Returns (fused numpy, unfused numpy, plans run by the fused sync)."""
+    from jittor_b200 import executor
+    vs = [jt.array(a) for a in arrays]
+    for v in vs:
+        v.sync()
+    out = build(*vs)
+    before = executor.counters["plans"]
+    fused = out.numpy()
+    plans = executor.counters["plans"] - before
+    with jt.flag_scope(b200_fuse_chains=0):
+        unfused = build(*vs).numpy()
+    return fused, unfused, plans
+
+
+@pytest.mark.parametrize("shape", [(32768 // 64, 4096), (37, 53), (5, 6, 7), (1, 9), (300, 1000)])
+def test_scale_shift_and_relu_bias(jt, shape):
+    from jittor_b200 import nn
+    rng = np.random.default_rng(sum(shape))
+    x = rng.normal(size=shape).astype(np.float32)
+    w, b = rng.normal(size=shape[-1:]).astype(np.float32), rng.normal(size=shape[-1:]).astype(np.float32)
+    fused, unfused, plans = run_both(jt, lambda X, W, B: X * W + B, [x, w, b])
+    assert plans == 1 and np.array_equal(fused, unfused)
+    check(fused, ref.binary(ref.binary(x, w, "multiply"), b, "add"), False)
+    fused, unfused, plans = run_both(jt, lambda X, B: nn.relu(X + B), [x, b])
+    assert plans == 1 and np.array_equal(fused, unfused)
+    check(fused, np.maximum(x + b, 0), False)
+
+
+@pytest.mark.parametrize("shape", [(512, 4096), (37, 53), (64, 1000), (3, 5, 70), (130, 8)])
+def test_multiply_then_row_reduce(jt, shape):
+    rng = np.random.default_rng(sum(shape) + 1)
+    a, b = rng.normal(size=shape).astype(np.float32), rng.normal(size=shape).astype(np.float32)
+    for op, npf in (("add", np.sum), ("maximum", np.max), ("minimum", np.min), ("mean", np.mean)):
+        fused, unfused, plans = run_both(jt, lambda A, B: (A * B).reduce(op, -1), [a, b])
+        assert plans == 1
+        want = ref.reduce(ref.binary(a, b, "multiply"), op, (-1,))
+        check(fused, want, False)
+        check(unfused, want, False)
+    # keepdims, and two trailing axes at once
+    if len(shape) == 3:
+        fused, _, plans = run_both(jt, lambda A, B: (A + B).sum([1, 2], keepdims=True), [a, b])
+        assert plans == 1
+        check(fused, ref.reduce(a + b, "add", (1, 2), True), False)
+
+
+def test_centre_and_scale_rows(jt):
+    rng = np.random.default_rng(3)
+    x = (rng.normal(size=(257, 771)) * 3 + 1).astype(np.float32)
+
+    def build(X):
+        m = X.mean(1, keepdims=True)
+        v = ((X - m) * (X - m)).mean(1, keepdims=True)
+        return (X - m) / (v + 1e-5).sqrt()
+
+    fused, unfused, plans = run_both(jt, build, [x])
+    assert plans == 1
+    xd = x.astype(np.float64)
+    want = ((xd - xd.mean(1, keepdims=True)) / np.sqrt(xd.var(1, keepdims=True) + 1e-5)).astype(np.float32)
+    check(fused, want, False, rtol=1e-4)
+    check(unfused, want, False, rtol=1e-4)
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 1000), (7, 10)])
+def test_softmax_backward_one_launch(jt, rows, cols):
+    from jittor_b200 import nn
+    rng = np.random.default_rng(rows)
+    x, dy = rng.normal(size=(rows, cols)).astype(np.float32), rng.normal(size=(rows, cols)).astype(np.float32)
+    fused, unfused, plans = run_both(jt, lambda X, DY: jt.grad((nn.softmax(X, -1) * DY).sum(), X), [x, dy])
+    assert plans == 1
+    y = ref.softmax(x, -1).astype(np.float64)
+    want = (y * (dy - (y * dy).sum(-1, keepdims=True))).astype(np.float32)
+    check(fused, want, False, rtol=1e-4)
+    check(unfused, want, False, rtol=1e-4)
+
+
+def test_channel_scale_shift_relu_bf16(jt):
+    """x[N,C,H,W] * w[C] + b[C] then ReLU with bfloat16 results kept (amp_reg bit 2): inputs broadcast over non-trailing
+    axes, every intermediate rounded to bfloat16 as op by op."""
+    from jittor_b200 import nn
+    rng = np.random.default_rng(9)
+    x = bf16_round(rng.normal(size=(6, 24, 9, 11)))
+    w, b = rng.normal(size=24).astype(np.float32), rng.normal(size=24).astype(np.float32)
+
+    def build(X, W, B):
+        with jt.flag_scope(amp_reg=2):
+            return nn.relu(X * W.broadcast(X, [0, 2, 3]) + B.broadcast(X, [0, 2, 3]))
+
+    from jittor_b200 import executor
+    X, W, B = jt.array(torch.from_numpy(x).bfloat16()), jt.array(w), jt.array(b)
+    out = build(X, W, B)
+    assert out.dtype == "bfloat16"
+    before = executor.counters["plans"]
+    fused = out.numpy()
+    assert executor.counters["plans"] - before == 1
+    with jt.flag_scope(b200_fuse_chains=0):
+        unfused = build(X, W, B).numpy()
+    assert np.array_equal(fused, unfused)
+    want = np.maximum(bf16_round(bf16_round(x * w[None, :, None, None]) + b[None, :, None, None]), 0)
+    check(fused, bf16_round(want), False, rtol=2e-2)
+
+
+def test_mixed_ops_and_comparisons(jt):
+    rng = np.random.default_rng(12)
+    a = rng.uniform(0.5, 2.0, size=(45, 130)).astype(np.float32)
+    b = rng.uniform(0.5, 2.0, size=(45, 130)).astype(np.float32)
+    m = (rng.uniform(size=(45, 1)) > 0.5)
+
+    def build(A, B, M):
+        t = (A / B).log() + (A * B).sqrt() - jt.sigmoid(A - B)
+        return jt.ternary(M, t.exp(), jt.minimum(A, B) ** 2.0) * (A > B)
+
+    fused, unfused, plans = run_both(jt, build, [a, b, m])
+    assert plans == 1 and np.array_equal(fused, unfused)
+    t = np.log(a / b) + np.sqrt(a * b) - 1 / (1 + np.exp(-(a - b)))
+    want = np.where(m, np.exp(t), np.minimum(a, b) ** 2.0) * (a > b)
+    check(fused, want.astype(np.float32), False, rtol=1e-5)
+
+
+def test_unaligned_and_ragged_rows(jt):
+    """Row lengths that are not whole 8-element vectors and views that start off a 32-byte boundary."""
+    rng = np.random.default_rng(21)
+    base = rng.normal(size=(19 * 13 + 3,)).astype(np.float32)
+    t = torch.from_numpy(base).cuda()
+    x = jt.array(t[3:].reshape(19, 13))
+    b = jt.array(rng.normal(size=13).astype(np.float32))
+    got = ((x + b) * 2.0 - 1.0).numpy()
+    check(got, (base[3:].reshape(19, 13) + b.numpy()) * 2.0 - 1.0, False)
+    got = ((x * x) + 1.0).sum(1).numpy()
+    check(got, ((base[3:].reshape(19, 13) ** 2) + 1.0).sum(1), False)
