@@ -1,6 +1,6 @@
 """Benchmark of the meta-operator hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|meta|next] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|meta|fused|next] [--impl reference]
 
 One JSON line on stdout (rank 0). The default run measures c2 (the headline keys of the line) and then c1, c3, c4, c5
 with the same method into "workloads"; --workload X measures X alone. Workloads are the benchmark configurations:
@@ -568,6 +568,91 @@ class MetaOps:
         return max(done, 1), time.perf_counter() - t0, f"{rows} of {self.ROWS} rows per part through the numpy oracle (1 core)"
 
 
+class FusedChains:
+    """Element-wise chains no named pattern covers, each run as ONE launch of the chain interpreter."""
+    key, metric, unit, bound, dtype, scaling = "fused", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
+    ROWS, COLS = 32768, 4096
+    description = ("fused element-wise chains on [32768,4096] fp32, one launch each: x*w+b (w, b per column), relu(x+bias), "
+                   "(a*b).sum(1), and the backward of row softmax (reverse-mode graph of exp/sub/div/max/sum)")
+    kernel_of = {"scale-shift": "chain_map_kernel", "relu-bias": "chain_map_kernel", "mul-rowsum": "chain_rows_kernel",
+                 "softmax-bwd": "chain_rows_kernel"}
+    launches = {k: 1 for k in kernel_of}
+
+    def work(self):
+        n = self.ROWS * self.COLS * 4
+        return {"scale-shift": 2 * n + 8 * self.COLS, "relu-bias": 2 * n + 4 * self.COLS, "mul-rowsum": 2 * n + 4 * self.ROWS,
+                "softmax-bwd": 3 * n}
+
+    def setup(self, rank, world, jt, torch, multi):
+        from jittor_b200 import nn
+        self.jt, self.torch, self.nn = jt, torch, nn
+        g = torch.Generator().manual_seed(13 + rank)
+        self.hx = torch.randn(self.ROWS, self.COLS, generator=g).pin_memory()
+        self.x = [jt.array(self.hx), jt.array(torch.randn(self.ROWS, self.COLS, generator=g)), jt.array(torch.randn(self.ROWS, self.COLS, generator=g))]
+        self.w, self.b = jt.array(torch.randn(self.COLS, generator=g)), jt.array(torch.randn(self.COLS, generator=g))
+        self.k = 0
+        return list(self.kernel_of)
+
+    def _op(self, name, x, y):
+        if name == "scale-shift":
+            return x * self.w + self.b
+        if name == "relu-bias":
+            return self.nn.relu(x + self.b)
+        if name == "mul-rowsum":
+            return (x * y).sum(1)
+        return self.jt.grad((self.nn.softmax(x, -1) * y).sum(), x)
+
+    def run(self, name):
+        self.k += 1
+        return self._op(name, self.x[self.k % 3], self.x[(self.k + 1) % 3]).sync()
+
+    def run_e2e(self, name):
+        x = self.jt.array(self.hx.cuda(non_blocking=True))
+        self._op(name, x, self.x[1]).sync()
+
+    def e2e_bytes(self, names):
+        return len(names) * self.hx.numel() * 4, 0
+
+    def verify(self, env):
+        from oracle import meta_ops_ref as ref
+        x, y = self.x[0].torch()[:64].cpu().numpy(), self.x[1].torch()[:64].cpu().numpy()
+        xv, yv = self.jt.array(x), self.jt.array(y)
+        w, b = self.w.numpy(), self.b.numpy()
+        ok = True
+        for name in self.kernel_of:
+            got = self._op(name, xv, yv).numpy()
+            if name == "scale-shift":
+                want = x * w + b
+            elif name == "relu-bias":
+                want = np.maximum(x + b, 0)
+            elif name == "mul-rowsum":
+                want = (x.astype(np.float64) * y).sum(1).astype(np.float32)
+            else:
+                sm = ref.softmax(x, -1).astype(np.float64)
+                want = (sm * (y - (sm * y).sum(-1, keepdims=True))).astype(np.float32)
+            ok = ok and bool((np.abs(got - want) <= 1e-4 * np.abs(want) + 1e-4 * np.abs(want).max()).all())
+        return ok
+
+    def cpu(self, names):
+        rows = 1024
+        rng = np.random.default_rng(13)
+        x, y = rng.normal(size=(rows, self.COLS)).astype(np.float32), rng.normal(size=(rows, self.COLS)).astype(np.float32)
+        w = np.ones(self.COLS, np.float32)
+        from oracle import meta_ops_ref as ref
+        done, t0 = 0, time.perf_counter()
+        for nm in names:
+            if nm == "scale-shift":
+                ref.binary(ref.binary(x, w, "multiply"), w, "add")
+            elif nm == "relu-bias":
+                ref.ternary(ref.binary(ref.binary(x, w, "add"), np.float32(0), "greater"), x, np.float32(0))
+            elif nm == "mul-rowsum":
+                ref.reduce(ref.binary(x, y, "multiply"), "add", (1,))
+            else:
+                continue
+            done += self.work()[nm] * rows // self.ROWS
+        return max(done, 1), time.perf_counter() - t0, f"{rows} of {self.ROWS} rows per part, op by op through the numpy oracle (1 core)"
+
+
 class NextOps:
     """The callers either side of the path: pooling kernels, getitem gather, setitem scatter-add."""
     key, metric, unit, bound, dtype, scaling = "next", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
@@ -636,7 +721,7 @@ class NextOps:
         return max(done, 1), time.perf_counter() - t0, "2x16 of 64x128 images per pooling part through the numpy oracle (1 core)"
 
 
-WORKLOADS = {w.key: w for w in (C1ConvF32, C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps, NextOps)}
+WORKLOADS = {w.key: w for w in (C1ConvF32, C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps, FusedChains, NextOps)}
 HEADLINE = "c2"                               # the default run's top-level line; the other configs follow in "workloads"
 CONFIGS = ("c1", "c3", "c4", "c5")
 

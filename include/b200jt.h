@@ -145,7 +145,7 @@ int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200
  *               float32 / bfloat16 / float16 / bool; every op computes in float32 and rounds to it):
  *                 1 INPUT k        push input k                  2 CONST   push the float32 in the next word
  *                 3 ROWVAL j       push row value j              4 UNARY u   5 BINARY b   6 TERNARY (cond, x, y)
- *                 7 TSTORE t / 8 TLOAD t   keep / recall a shared sub-expression (t < 4)
+ *                 7 TSTORE t / 8 TLOAD t   keep / recall a shared sub-expression (t < 2)
  *               statements end a chain:
  *                 9 ROW_REDUCE (j | reduce_op << 4)  rowval[j] = fold of the chain over the row (add, mean, maximum, minimum, multiply)
  *                10 ROW_MAP j      rowval[j] = chain (of row values, per-row inputs, constants)

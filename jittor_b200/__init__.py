@@ -10,6 +10,7 @@ from . import dtypes, executor, nn, dist, op_register
 from .op_register import code, has_op, get_op_info, register_op, compile_custom_op, compile_custom_ops
 from .dtypes import binary_dtype_infer
 from .grad import grad
+from .nn import Function, Module
 from . import slicing, optim, pool
 from .slicing import getitem, setitem, scatter, scatter_, gather
 

@@ -28,8 +28,8 @@ namespace chain {
 constexpr int kMaxInputs = 8;
 constexpr int kMaxCode = 160;
 constexpr int kMaxRowVals = 8;
-constexpr int kStack = 8;
-constexpr int kTmp = 4;
+constexpr int kStack = 6;
+constexpr int kTmp = 2;
 constexpr int VEC = 8;
 
 enum ChainOp : int {
@@ -213,72 +213,153 @@ __device__ __forceinline__ void store_output(const Program& P, int64_t off, int 
     for (int e = 0; e < n; e++) store_as<float>(P.out, P.out_dtype, off + e, v[e]);
 }
 
+// ---- the interpreter -------------------------------------------------------------------------------------------
+// The value stack lives in registers: every access to it uses a compile-time index, because each instruction is
+// dispatched first on the current stack depth (Exec<SP>) and only then on its op code. The depth itself is a runtime
+// value that is used for nothing but that dispatch.
+__device__ __noinline__ void rare_unary(int op, float* v) {
+#pragma unroll 1
+    for (int e = 0; e < VEC; e++) v[e] = unary_f(op, v[e]);
+}
+__device__ __noinline__ void rare_binary(int op, float* a, const float* b) {
+#pragma unroll 1
+    for (int e = 0; e < VEC; e++) a[e] = binary_f(op, a[e], b[e]);
+}
+
+template <int SP>
+struct Exec {
+    static __device__ __forceinline__ void step(const Program& P, int op, int a, int rdt, int32_t next_word, int64_t row, int64_t col,
+                                                int n, const float* rowval, float (&st)[kStack][VEC], float (&tmp)[kTmp][VEC]) {
+        if (op == CH_INPUT || op == CH_CONST || op == CH_ROWVAL || op == CH_TLOAD) {
+            if constexpr (SP < kStack) {
+                if (op == CH_INPUT) load_input(P.in[a], row, col, P.cols, n, st[SP]);
+                else if (op == CH_TLOAD) {
+#pragma unroll
+                    for (int t = 0; t < kTmp; t++)
+                        if (t == a) {
+#pragma unroll
+                            for (int e = 0; e < VEC; e++) st[SP][e] = tmp[t][e];
+                        }
+                } else {
+                    const float c = op == CH_CONST ? __int_as_float(next_word) : rowval[a];
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) st[SP][e] = c;
+                }
+            }
+            return;
+        }
+        if (op == CH_TSTORE) {
+            if constexpr (SP >= 1) {
+#pragma unroll
+                for (int t = 0; t < kTmp; t++)
+                    if (t == a) {
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) tmp[t][e] = st[SP - 1][e];
+                    }
+            }
+            return;
+        }
+        if (op == CH_UNARY) {
+            if constexpr (SP >= 1) {
+                float (&x)[VEC] = st[SP - 1];
+                switch (a) {
+                    case U_CAST: break;
+#define B200JT_U(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float v = x[e]; x[e] = (EXPR); } break
+                    B200JT_U(U_NEG, -v);
+                    B200JT_U(U_ABS, fabsf(v));
+                    B200JT_U(U_LNOT, (float)(v == 0));
+                    B200JT_U(U_LOG, logf(v));
+                    B200JT_U(U_EXP, expf(v));
+                    B200JT_U(U_SQRT, sqrtf(v));
+                    B200JT_U(U_TANH, tanhf(v));
+                    B200JT_U(U_SIGMOID, 1.f / (1.f + expf(-v < 30.f ? -v : 30.f)));
+#undef B200JT_U
+                    default: {
+                        float buf[VEC];
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) buf[e] = x[e];
+                        rare_unary(a, buf);
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) x[e] = buf[e];
+                    }
+                }
+                if (rdt != B200JT_FLOAT32) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) x[e] = round_to(x[e], rdt);
+                }
+            }
+            return;
+        }
+        if (op == CH_BINARY) {
+            if constexpr (SP >= 2) {
+                float (&x)[VEC] = st[SP - 2];
+                const float (&y)[VEC] = st[SP - 1];
+                switch (a) {
+#define B200JT_B(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float p = x[e], q = y[e]; x[e] = (EXPR); } break
+                    B200JT_B(OP_ADD, p + q);
+                    B200JT_B(OP_SUB, p - q);
+                    B200JT_B(OP_MUL, p * q);
+                    B200JT_B(OP_DIV, p / q);
+                    B200JT_B(OP_MAX, p > q ? p : q);
+                    B200JT_B(OP_MIN, q < p ? q : p);
+                    B200JT_B(OP_LT, (float)(p < q));
+                    B200JT_B(OP_LE, (float)(p <= q));
+                    B200JT_B(OP_GT, (float)(p > q));
+                    B200JT_B(OP_GE, (float)(p >= q));
+                    B200JT_B(OP_EQ, (float)(p == q));
+                    B200JT_B(OP_NE, (float)(p != q));
+#undef B200JT_B
+                    default: {
+                        float bx[VEC], by[VEC];
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) { bx[e] = x[e]; by[e] = y[e]; }
+                        rare_binary(a, bx, by);
+#pragma unroll
+                        for (int e = 0; e < VEC; e++) x[e] = bx[e];
+                    }
+                }
+                if (rdt != B200JT_FLOAT32) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) x[e] = round_to(x[e], rdt);
+                }
+            }
+            return;
+        }
+        if (op == CH_TERNARY) {             // stack: cond, x, y
+            if constexpr (SP >= 3) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) st[SP - 3][e] = st[SP - 3][e] != 0.f ? st[SP - 2][e] : st[SP - 1][e];
+                if (rdt != B200JT_FLOAT32) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) st[SP - 3][e] = round_to(st[SP - 3][e], rdt);
+                }
+            }
+        }
+    }
+};
+
 // Runs the chain that starts at code[pc] for VEC elements; returns the pc of the statement word that ends it and leaves
 // the chain's value in `top`.
-__device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row, int64_t col, int n, const float* rowval, float* top) {
+__device__ __noinline__ int eval_chain(const Program& P, int pc, int64_t row, int64_t col, int n, const float* rowval, float* top) {
     float st[kStack][VEC];
     float tmp[kTmp][VEC];
     int sp = 0;
     for (;; pc++) {
         const int32_t w = P.code[pc];
         const int op = w & 0xff, a = (w >> 8) & 0xffff, rdt = (w >> 24) & 0xff;
-        switch (op) {
-            case CH_INPUT: load_input(P.in[a], row, col, P.cols, n, st[sp]); sp++; break;
-            case CH_CONST: {
-                const float c = __int_as_float(P.code[++pc]);
-#pragma unroll
-                for (int e = 0; e < VEC; e++) st[sp][e] = c;
-                sp++; break;
-            }
-            case CH_ROWVAL: {
-                const float c = rowval[a];
-#pragma unroll
-                for (int e = 0; e < VEC; e++) st[sp][e] = c;
-                sp++; break;
-            }
-            case CH_UNARY:
-#pragma unroll
-                for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(unary_f(a, st[sp - 1][e]), rdt);
-                break;
-            case CH_BINARY:
-                sp--;
-                switch (a) {       // the common ops get straight-line code; the rest share the generic switch
-                    case OP_ADD:
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] + st[sp][e], rdt);
-                        break;
-                    case OP_SUB:
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] - st[sp][e], rdt);
-                        break;
-                    case OP_MUL:
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] * st[sp][e], rdt);
-                        break;
-                    default:
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(binary_f(a, st[sp - 1][e], st[sp][e]), rdt);
-                }
-                break;
-            case CH_TERNARY:     // stack: cond, x, y
-                sp -= 2;
-#pragma unroll
-                for (int e = 0; e < VEC; e++) st[sp - 1][e] = round_to(st[sp - 1][e] != 0.f ? st[sp][e] : st[sp + 1][e], rdt);
-                break;
-            case CH_TSTORE:
-#pragma unroll
-                for (int e = 0; e < VEC; e++) tmp[a][e] = st[sp - 1][e];
-                break;
-            case CH_TLOAD:
-#pragma unroll
-                for (int e = 0; e < VEC; e++) st[sp][e] = tmp[a][e];
-                sp++; break;
-            default:             // a statement word: the chain is complete
-#pragma unroll
-                for (int e = 0; e < VEC; e++) top[e] = st[0][e];
-                return pc;
+        if (op >= CH_ROW_REDUCE) break;
+        const int32_t next_word = op == CH_CONST ? P.code[pc + 1] : 0;
+        switch (sp) {
+#define B200JT_SP(N) case N: Exec<N>::step(P, op, a, rdt, next_word, row, col, n, rowval, st, tmp); break
+            B200JT_SP(0); B200JT_SP(1); B200JT_SP(2); B200JT_SP(3); B200JT_SP(4); B200JT_SP(5); B200JT_SP(6);
+#undef B200JT_SP
         }
+        if (op == CH_CONST) pc++;
+        sp += (op == CH_INPUT || op == CH_CONST || op == CH_ROWVAL || op == CH_TLOAD) ? 1 : (op == CH_BINARY ? -1 : (op == CH_TERNARY ? -2 : 0));
     }
+#pragma unroll
+    for (int e = 0; e < VEC; e++) top[e] = st[0][e];
+    return pc;
 }
 
 __device__ __forceinline__ float fold(int rop, float a, float b) {
@@ -299,11 +380,12 @@ __device__ __forceinline__ float fold_init(int rop) {
 }
 
 // Pure map (the program is one chain ending in STORE): work items are 8-element vectors of the full space.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 chain_map_kernel(const __grid_constant__ Program P) {
     const int64_t vpr = (P.cols + VEC - 1) / VEC, items = P.rows * vpr;
+    const bool small = items < (1LL << 31);
     for (int64_t it = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; it < items; it += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = it / vpr, col = (it - row * vpr) * VEC;
+        const int64_t row = small ? (int64_t)((uint32_t)it / (uint32_t)vpr) : it / vpr, col = (it - row * vpr) * VEC;
         const int n = (int)min((int64_t)VEC, P.cols - col);
         float v[VEC];
         eval_chain(P, 0, row, col, n, nullptr, v);
@@ -313,7 +395,7 @@ chain_map_kernel(const __grid_constant__ Program P) {
 
 // G threads per row (32: a warp, shuffles only; 256: the whole CTA, one shared-memory hop).
 template <int G>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 chain_rows_kernel(const __grid_constant__ Program P) {
     __shared__ float xch[8];
     constexpr int GROUPS = 256 / G;
@@ -332,25 +414,20 @@ chain_rows_kernel(const __grid_constant__ Program P) {
             const int sop = w & 0xff, a = (w >> 8) & 0xffff, rdt = (w >> 24) & 0xff;
             if (sop == CH_STORE_ROW) {
                 if (t == 0) store_as<float>(P.out, P.out_dtype, row, rowval[a]);
-            } else if (sop == CH_ROW_MAP) {
-                float v[VEC];
-                eval_chain(P, pc, row, 0, 1, rowval, v);
-                rowval[a] = v[0];
-            } else if (sop == CH_STORE) {
-                for (int64_t col = (int64_t)t * VEC; col < P.cols; col += (int64_t)G * VEC) {
-                    const int n = (int)min((int64_t)VEC, P.cols - col);
-                    float v[VEC];
-                    eval_chain(P, pc, row, col, n, rowval, v);
-                    store_output(P, row * P.cols + col, n, v);
-                }
-            } else {            // CH_ROW_REDUCE
-                const int slot = a & 15, rop = a >> 4;
+            } else {
+                // one loop for the three kinds of statement, so that the interpreter is instantiated once: a per-row map
+                // is a single evaluation at column 0 by every thread of the group
+                const bool row_map = sop == CH_ROW_MAP;
+                const int rop = a >> 4;
                 float acc = fold_init(rop);
-                for (int64_t col = (int64_t)t * VEC; col < P.cols; col += (int64_t)G * VEC) {
-                    const int n = (int)min((int64_t)VEC, P.cols - col);
+                const int64_t col_end = row_map ? 1 : P.cols;
+                for (int64_t col = row_map ? 0 : (int64_t)t * VEC; col < col_end; col += (int64_t)G * VEC) {
+                    const int n = (int)min((int64_t)VEC, col_end - col);
                     float v[VEC];
                     eval_chain(P, pc, row, col, n, rowval, v);
-                    if (rop == OP_MEAN) {
+                    if (sop == CH_STORE) store_output(P, row * P.cols + col, n, v);
+                    else if (row_map) acc = v[0];
+                    else if (rop == OP_MEAN) {
 #pragma unroll
                         for (int e = 0; e < VEC; e++) if (e < n) acc += v[e] * rcols;
                     } else {
@@ -358,17 +435,20 @@ chain_rows_kernel(const __grid_constant__ Program P) {
                         for (int e = 0; e < VEC; e++) if (e < n) acc = fold(rop, acc, v[e]);
                     }
                 }
+                if (row_map) rowval[a] = acc;
+                else if (sop == CH_ROW_REDUCE) {
 #pragma unroll
-                for (int d = 16; d > 0; d >>= 1) acc = fold(rop, acc, __shfl_xor_sync(0xffffffffu, acc, d));
-                if (G == 256) {
-                    __syncthreads();                       // xch free again
-                    if ((threadIdx.x & 31) == 0) xch[threadIdx.x >> 5] = acc;
-                    __syncthreads();
-                    acc = xch[0];
+                    for (int d = 16; d > 0; d >>= 1) acc = fold(rop, acc, __shfl_xor_sync(0xffffffffu, acc, d));
+                    if (G == 256) {
+                        __syncthreads();                       // xch free again
+                        if ((threadIdx.x & 31) == 0) xch[threadIdx.x >> 5] = acc;
+                        __syncthreads();
+                        acc = xch[0];
 #pragma unroll
-                    for (int k = 1; k < 8; k++) acc = fold(rop, acc, xch[k]);
+                        for (int k = 1; k < 8; k++) acc = fold(rop, acc, xch[k]);
+                    }
+                    rowval[a & 15] = round_to(acc, rdt);
                 }
-                rowval[slot] = round_to(acc, rdt);
             }
             pc = end + 1;
         }

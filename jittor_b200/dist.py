@@ -89,6 +89,26 @@ def mpi_broadcast(x, root=0):
     return V.Var(x.shape, x.dtype, data=out)
 
 
+def mpi_reduce(x, op="add", root=0):
+    """The root rank receives the sum (or, for "mean", the sum divided by the number of ranks) over all ranks; the other
+    ranks receive zeros (python/jittor/extern/mpi/ops/mpi_reduce_op.cc:28-60,92; CUDA relay
+    ncclReduce, python/jittor/extern/cuda/nccl/ops/nccl_reduce_op.cc:56). Without a process group x is returned unchanged.
+    Eager, like mpi_broadcast."""
+    x = V.to_var(x)
+    if not in_mpi():
+        return x
+    if op == "mean":
+        return mpi_reduce(x, "add", root) / world_size()
+    if op != "add":
+        raise ValueError(f"Not supported MPI op {op}")
+    x.sync()
+    out = x._data.clone()
+    tdist.reduce(out, dst=root, op=tdist.ReduceOp.SUM)
+    if rank() != root:
+        out.zero_()                    # the reference clears the result on the other ranks (mpi_reduce_op.cc:93-95)
+    return V.Var(x.shape, x.dtype, data=out)
+
+
 def all_reduce_buckets(tensors, bucket_bytes=None):
     """Sums a list of tensors over the ranks in as few collectives as possible: tensors of one dtype are packed back
     to back into flat buckets of at most `bucket_bytes` (default: what the peer kernel takes in one call, else 32 MiB),

@@ -19,7 +19,7 @@ import struct
 from . import _capi as C
 from .var import Var
 
-MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_STACK, MAX_TMP = 8, 160, 8, 8, 4
+MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_STACK, MAX_TMP = 8, 160, 8, 6, 2
 
 CH_INPUT, CH_CONST, CH_ROWVAL, CH_UNARY, CH_BINARY, CH_TERNARY, CH_TSTORE, CH_TLOAD = 1, 2, 3, 4, 5, 6, 7, 8
 CH_ROW_REDUCE, CH_ROW_MAP, CH_STORE, CH_STORE_ROW = 9, 10, 11, 12

@@ -46,6 +46,48 @@ class Module:
             p.update(p.mpi_broadcast(root))
 
 
+class Function(Module):
+    """An op with a hand-written backward (python/jittor/__init__.py:1865-2004): `execute(*args)` computes the outputs,
+    `grad(*output_gradients)` returns one gradient per input (None where there is none). Gradients that did not reach
+    an output arrive as None. Each output is re-issued as a pass-through node that carries the backward rule, so
+    `jt.grad` never differentiates through the body of `execute`."""
+
+    def __call__(self, *args):
+        outs = self.execute(*args)
+        single = isinstance(outs, Var)
+        outs = [outs] if single else list(outs)
+        var_pos = [i for i, a in enumerate(args) if isinstance(a, Var)]
+        var_args = [args[i] for i in var_pos]
+
+        def rule_for(k_out):
+            def rule(out, dout, k):
+                if k == 0:
+                    return None                      # input 0 is the value computed by execute
+                douts = [None] * len(outs)
+                douts[k_out] = dout
+                grads = self.grad(*douts)
+                grads = [grads] if isinstance(grads, Var) or grads is None else list(grads)
+                pos = var_pos[k - 1]
+                return grads[pos] if pos < len(grads) else None
+            return rule
+
+        wrapped = []
+        for k_out, o in enumerate(outs):
+            if not isinstance(o, Var):
+                wrapped.append(o)
+                continue
+            node = V.Op("custom", [o] + var_args, fn=lambda first, *rest: first, grad=rule_for(k_out), name="function")
+            wrapped.append(Var(o.shape, o.dtype, node))
+        return wrapped[0] if single else tuple(wrapped)
+
+    def grad(self, *douts):
+        raise NotImplementedError
+
+    @classmethod
+    def apply(cls, *args, **kw):
+        return cls()(*args, **kw)
+
+
 def matmul_transpose(a, b):
     """c[..., n, k] = sum_m a[..., n, m] * b[k, m]  (python/jittor/nn.py:40-58)."""
     a, b = to_var(a), to_var(b)

@@ -10,8 +10,8 @@ names the tuners look up (`cublas_matmul`, `cudnn_conv`, `nccl_all_reduce`), and
 with the macro set of python/jittor/src/ops/code_op.cc:186-231: `@ARGS_DEF`, `@ARGS`, `@PRECALC`, `@inK(i,j,..)`,
 `@out(i,..)` / `@outK(..)`, `inK_shapeJ`, `inK_strideJ`, `inK_type`, leading `__global__` / `__device__` functions
 hoisted out of the body. The source is compiled with nvcc for sm_100a into a cache directory, loaded with ctypes and
-launched on the current stream. C++ op classes written against the reference's own headers cannot be compiled here;
-`compile_custom_op` says so.
+launched on the current stream. C++ op classes in the reference's custom-op form are built by custom_op.py against a
+stand-in for the core headers.
 """
 import ctypes
 import hashlib
@@ -53,13 +53,15 @@ def get_op_info(name):
     return _REGISTRY[name]
 
 
-def compile_custom_op(header, source, op_name, warp=True):
-    raise NotImplementedError(
-        "compile_custom_op builds C++ Op classes against the reference's core headers, which this package does not "
-        "provide; use jittor_b200.code(..., cuda_src=...) for inline CUDA or register_op(name, fn) for a Python op")
+def compile_custom_op(header, source, op_name=None, warp=True):
+    """C++ op classes in the reference's custom-op form: see custom_op.py."""
+    from . import custom_op
+    return custom_op.compile_custom_op(header, source, op_name, warp)
 
 
-compile_custom_ops = compile_custom_op
+def compile_custom_ops(filenames, extra_flags="", return_module=False, **kw):
+    from . import custom_op
+    return custom_op.compile_custom_ops(filenames, extra_flags, return_module, **kw)
 
 
 def _register_builtins():
@@ -120,6 +122,10 @@ def _register_builtins():
     register_op("cudnn_conv_backward_w", cudnn_conv_backward_w)
     register_op("nccl_all_reduce", lambda x: dist.mpi_all_reduce(x, "add"))
     register_op("mpi_all_reduce", dist.mpi_all_reduce)
+    register_op("mpi_reduce", dist.mpi_reduce)
+    register_op("mpi_broadcast", dist.mpi_broadcast)
+    register_op("nccl_reduce", lambda x, root=0: dist.mpi_reduce(x, "add", root))
+    register_op("nccl_broadcast", lambda x, root=0: dist.mpi_broadcast(x, root))
 
 
 # ----------------------------------------------------------------------------------------------- jt.code
@@ -242,10 +248,23 @@ def compile_code_source(text):
     return so
 
 
-def code(shape, dtype, inputs=(), cuda_src="", cuda_header="", cpu_src="", cpu_header="", **unused):
-    """Inline CUDA op. `shape` / `dtype` may be lists for several outputs (then a list of Vars is returned)."""
+def _alias(text, name, target):
+    """@alias(name, target) of python/jittor/src/ops/code_op.cc:108-117: `@name(..)`, `name_shapeK`, `name_strideK`,
+    `name_type`, `name_p` mean the same as for `target`."""
+    text = re.sub(rf"@{name}\(", f"@{target}(", text)
+    return re.sub(rf"\b{name}_(shape\d+|stride\d+|type|p)\b", rf"{target}_\1", text)
+
+
+def code(shape, dtype, inputs=(), cpu_src="", cpu_grad_src=(), cpu_header="", cuda_src="", cuda_grad_src=(), cuda_header="",
+         data=None):
+    """Inline CUDA op, python/jittor/src/ops/code_op.h:24-46,265-271. `shape` / `dtype` may be lists for several outputs
+    (then a list of Vars is returned). `cuda_grad_src[k]` is the source of the gradient with respect to input k: it is run
+    as another inline op with the shape and dtype of that input, whose inputs are the forward inputs followed by the output
+    gradient (`@dout(..)`) and the forward outputs (`@pout(..)`, `@poutK(..)`), python/jittor/src/ops/code_op.cc:100-127."""
     if not cuda_src:
         raise B200Error("jt.code: only cuda_src is supported (there is no CPU path)")
+    if data:
+        raise B200Error("jt.code: the `data` dictionary is not supported; pass scalars as one-element inputs")
     multi = len(shape) > 0 and isinstance(shape[0], (list, tuple, V.Shape))
     shapes = [list(s) for s in shape] if multi else [list(shape)]
     dtypes = list(dtype) if multi else [dtype]
@@ -253,6 +272,16 @@ def code(shape, dtype, inputs=(), cuda_src="", cuda_header="", cpu_src="", cpu_h
     in_meta = [(str(v.dtype), v.ndim) for v in inputs]
     out_meta = [(str(V.dt.canon(d)), len(s)) for d, s in zip(dtypes, shapes)]
     text = expand_code_source(cuda_src, cuda_header, in_meta, out_meta)
+    cuda_grad_src = list(cuda_grad_src or ())
+
+    def grad_rule(out, dout, k):
+        if k >= len(cuda_grad_src) or not cuda_grad_src[k] or multi:
+            return None
+        n = len(inputs)
+        src, header = cuda_grad_src[k], cuda_header
+        for name, target in (("dout", f"in{n}"), ("pout0", f"in{n + 1}"), ("pout", f"in{n + 1}")):
+            src, header = _alias(src, name, target), _alias(header, name, target)
+        return code(list(inputs[k].shape), inputs[k].dtype, inputs + [dout, out], cuda_src=src, cuda_header=header)
 
     def run(*tensors):
         import torch
@@ -274,7 +303,7 @@ def code(shape, dtype, inputs=(), cuda_src="", cuda_header="", cpu_src="", cpu_h
         return outs
 
     if not multi:
-        return V.Var(shapes[0], out_meta[0][0], V.Op("custom", inputs, fn=lambda *t: run(*t)[0]))
+        return V.Var(shapes[0], out_meta[0][0], V.Op("custom", inputs, fn=lambda *t: run(*t)[0], grad=grad_rule))
     # several outputs: one node computes all of them, the others pick their tensor from it
     box = {}
 

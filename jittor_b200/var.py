@@ -280,6 +280,10 @@ class Var:
         from . import dist
         return dist.mpi_all_reduce(self, op)
 
+    def mpi_reduce(self, op="add", root=0):
+        from . import dist
+        return dist.mpi_reduce(self, op, root)
+
     def matmul(self, other):
         from . import nn
         return nn.matmul(self, other)

@@ -57,6 +57,14 @@ def main():
     p._data = torch.full((3,), float(10 + rank))
     b = dist.mpi_broadcast(p, 0)
     assert torch.equal(b._data, torch.full((3,), 10.0))
+    # 6b. reduce to a root: the root holds the sum (or mean), the other rank zeros
+    q = jt.Var([3], "float32")
+    q._data = torch.full((3,), float(1 + rank))
+    for root in (0, 1):
+        r = dist.mpi_reduce(q, "add", root)
+        assert torch.equal(r._data, torch.full((3,), 3.0 if rank == root else 0.0)), (root, r._data)
+    m = q.mpi_reduce("mean", 1)
+    assert m._op.kind == "binary" and m._op.attrs["op"] == "divide"
     # 7. a rank leaves between steps: the other one learns of it from the store, not from a collective that hangs
     import time
     assert dist.departed() == []

@@ -31,7 +31,7 @@ def test_reference_arm_prints_one_contract_line():
 def test_workload_tables_are_consistent():
     sys.path.insert(0, ROOT)
     import bench
-    assert set(bench.WORKLOADS) == {"c1", "c2", "c3", "c4", "c5", "meta", "next"}
+    assert set(bench.WORKLOADS) == {"c1", "c2", "c3", "c4", "c5", "meta", "fused", "next"}
     assert bench.HEADLINE == "c2" and set(bench.CONFIGS) == {"c1", "c3", "c4", "c5"}
     for key, cls in bench.WORKLOADS.items():
         wl = cls()
