@@ -137,19 +137,22 @@ int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200
  * in registers: the general case of FusedOp::jit_run -- the loop nest OpCompiler stitches from the member ops
  * (python/jittor/src/fused_op.cc:41-118,217-238, python/jittor/src/op_compiler.cc:839-1045; fused reduce + broadcast
  * cases python/jittor/test/test_fused_op.py:144-176). The reference generates and compiles source per graph; here the
- * graph is passed as a postfix program that one ahead-of-time kernel interprets.
+ * graph is passed as a small program that one ahead-of-time kernel interprets.
  *   inputs      n_inputs (<= 8) tensors, each with the rank of full_shape, size 1 on the axes it is broadcast over;
  *   full_shape  the index space of the element-wise part; its last row_axes axes form a "row" (the axes the program's
  *               reduces fold; 0 when there is no reduce);
- *   code        32-bit words  op | arg << 8 | result_dtype << 24  (result_dtype: enum b200jt_dtype of the node,
- *               float32 / bfloat16 / float16 / bool; every op computes in float32 and rounds to it):
- *                 1 INPUT k        push input k                  2 CONST   push the float32 in the next word
- *                 3 ROWVAL j       push row value j              4 UNARY u   5 BINARY b   6 TERNARY (cond, x, y)
- *                 7 TSTORE t / 8 TLOAD t   keep / recall a shared sub-expression (t < 2)
+ *   code        32-bit words  op | sub << 4 | kind << 10 | index << 13 | swap << 21 | result_dtype << 24  for an
+ *               accumulator machine (result_dtype: enum b200jt_dtype of the node, float32 / bfloat16 / float16 / bool;
+ *               every op computes in float32 and rounds to it). An operand is (kind, index): 1 input k, 2 constant (the
+ *               float32 in the next word), 3 row value j, 4 temporary t (t < 3).
+ *                 1 LOAD o         acc = o                       2 UNARY (sub = u)     acc = u(acc)
+ *                 3 BINARY (sub = b) o   acc = acc b o, or o b acc if swap
+ *                 4 SELECT o1, then a word with op 0 holding o2      acc = acc != 0 ? o1 : o2
+ *                 5 TSTORE t       tmp[t] = acc
  *               statements end a chain:
- *                 9 ROW_REDUCE (j | reduce_op << 4)  rowval[j] = fold of the chain over the row (add, mean, maximum, minimum, multiply)
- *                10 ROW_MAP j      rowval[j] = chain (of row values, per-row inputs, constants)
- *                11 STORE          out = chain (full_shape; must be last)       12 STORE_ROW j   out[row] = rowval[j] (last)
+ *                 8 ROW_REDUCE (sub = reduce_op, index = j)  rowval[j] = fold of acc over the row (add, mean, maximum, minimum, multiply)
+ *                 9 ROW_MAP j      rowval[j] = acc (a chain of row values, per-row inputs, constants)
+ *                10 STORE          out = acc (full_shape; must be last)       11 STORE_ROW j   out[row] = rowval[j] (last)
  *               u: index in {cast, negative, abs, logical_not, bitwise_not, log, exp, sqrt, round, floor, ceil, sin, asin,
  *               sinh, asinh, tan, atan, tanh, atanh, cos, acos, cosh, acosh, sigmoid, erf, erfinv}; b / reduce_op: index in
  *               {add, subtract, multiply, divide, floor_divide, mod, pow, maximum, minimum, less, less_equal, greater,

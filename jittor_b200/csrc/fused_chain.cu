@@ -11,10 +11,12 @@
 //   ROW_MAP j          rowval[j] = <chain over row values / per-row inputs / constants>
 //   STORE              out[row, col] = <chain>                            one sweep, the output write
 //   STORE_ROW j        out[row] = rowval[j]
-// A chain is postfix code: INPUT k, CONST c, ROWVAL j, UNARY u, BINARY b, TERNARY, TSTORE t / TLOAD t (shared
-// sub-expressions). All arithmetic is the float32 compute class of the element-wise kernels (elementwise.cu), and every
-// op's result is rounded to the dtype the reference's inference gives that node (float32 / bfloat16 / float16 / bool), so a
-// fused chain returns the same bits as the same ops run one by one.
+// A chain is code for an accumulator machine: LOAD o (acc = o), UNARY u (acc = u(acc)), BINARY b, o (acc = acc b o, or
+// o b acc with the swap bit), SELECT o1, o2 (acc = acc ? o1 : o2), TSTORE t (tmp[t] = acc), where an operand o is an
+// input, a constant, a row value or one of three temporaries. The accumulator and the temporaries are fixed registers,
+// so an instruction is dispatched on its op code only. All arithmetic is the float32 compute class of the element-wise
+// kernels (elementwise.cu), and every op's result is rounded to the dtype the reference's inference gives that node
+// (float32 / bfloat16 / float16 / bool), so a fused chain returns the same bits as the same ops run one by one.
 //
 // Kernel: a group of G threads (a warp, or a CTA of 256) owns a row at a time; every statement that sweeps the row
 // re-reads its inputs, which after the first sweep come from L1/L2 (a row is a few KB), so DRAM sees one read of each
@@ -28,17 +30,26 @@ namespace chain {
 constexpr int kMaxInputs = 8;
 constexpr int kMaxCode = 160;
 constexpr int kMaxRowVals = 8;
-constexpr int kStack = 6;
-constexpr int kTmp = 2;
+constexpr int kTmp = 3;
 constexpr int VEC = 8;
 
+// word = op | sub << 4 | operand kind << 10 | operand index << 13 | swap << 21 | result dtype << 24
 enum ChainOp : int {
-    CH_END = 0, CH_INPUT, CH_CONST, CH_ROWVAL, CH_UNARY, CH_BINARY, CH_TERNARY, CH_TSTORE, CH_TLOAD,
-    CH_ROW_REDUCE,      // a = slot | reduce op << 4 : ends a chain, one sweep
-    CH_ROW_MAP,         // a = slot                  : ends a chain evaluated once per row
+    CH_OPERAND = 0,     // second operand of the SELECT before it
+    CH_LOAD, CH_UNARY, CH_BINARY, CH_SELECT, CH_TSTORE,
+    CH_ROW_REDUCE = 8,  // sub = reduce op, index = slot : ends a chain, one sweep
+    CH_ROW_MAP,         // index = slot              : ends a chain evaluated once per row
     CH_STORE,           // ends a chain, one sweep, writes the output
-    CH_STORE_ROW        // a = slot                  : out[row] = rowval[slot]
+    CH_STORE_ROW        // index = slot              : out[row] = rowval[slot]
 };
+enum OperandKind : int { K_NONE = 0, K_INPUT, K_CONST /* the float32 in the next word */, K_ROWVAL, K_TMP };
+
+__host__ __device__ __forceinline__ int w_op(int32_t w) { return w & 15; }
+__host__ __device__ __forceinline__ int w_sub(int32_t w) { return (w >> 4) & 63; }
+__host__ __device__ __forceinline__ int w_kind(int32_t w) { return (w >> 10) & 7; }
+__host__ __device__ __forceinline__ int w_index(int32_t w) { return (w >> 13) & 255; }
+__host__ __device__ __forceinline__ int w_swap(int32_t w) { return (w >> 21) & 1; }
+__host__ __device__ __forceinline__ int w_rdt(int32_t w) { return (w >> 24) & 255; }
 
 // unary codes of elementwise.cu (kept in the same order)
 enum UnaryCode : int {
@@ -214,9 +225,6 @@ __device__ __forceinline__ void store_output(const Program& P, int64_t off, int 
 }
 
 // ---- the interpreter -------------------------------------------------------------------------------------------
-// The value stack lives in registers: every access to it uses a compile-time index, because each instruction is
-// dispatched first on the current stack depth (Exec<SP>) and only then on its op code. The depth itself is a runtime
-// value that is used for nothing but that dispatch.
 __device__ __noinline__ void rare_unary(int op, float* v) {
 #pragma unroll 1
     for (int e = 0; e < VEC; e++) v[e] = unary_f(op, v[e]);
@@ -226,76 +234,72 @@ __device__ __noinline__ void rare_binary(int op, float* a, const float* b) {
     for (int e = 0; e < VEC; e++) a[e] = binary_f(op, a[e], b[e]);
 }
 
-template <int SP>
-struct Exec {
-    static __device__ __forceinline__ void step(const Program& P, int op, int a, int rdt, int32_t next_word, int64_t row, int64_t col,
-                                                int n, const float* rowval, float (&st)[kStack][VEC], float (&tmp)[kTmp][VEC]) {
-        if (op == CH_INPUT || op == CH_CONST || op == CH_ROWVAL || op == CH_TLOAD) {
-            if constexpr (SP < kStack) {
-                if (op == CH_INPUT) load_input(P.in[a], row, col, P.cols, n, st[SP]);
-                else if (op == CH_TLOAD) {
+// Operand of word w into o[]; advances pc over an inline constant.
+__device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int64_t row, int64_t col, int n, const float* rowval,
+                                      const float (&tmp)[kTmp][VEC], float (&o)[VEC]) {
+    const int kind = w_kind(w), idx = w_index(w);
+    if (kind == K_INPUT) { load_input(P.in[idx], row, col, P.cols, n, o); return; }
+    if (kind == K_TMP) {
 #pragma unroll
-                    for (int t = 0; t < kTmp; t++)
-                        if (t == a) {
+        for (int t = 0; t < kTmp; t++)
+            if (t == idx) {
 #pragma unroll
-                            for (int e = 0; e < VEC; e++) st[SP][e] = tmp[t][e];
-                        }
-                } else {
-                    const float c = op == CH_CONST ? __int_as_float(next_word) : rowval[a];
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) st[SP][e] = c;
-                }
+                for (int e = 0; e < VEC; e++) o[e] = tmp[t][e];
             }
-            return;
-        }
+        return;
+    }
+    const float c = kind == K_CONST ? __int_as_float(P.code[++pc]) : rowval[idx];
+#pragma unroll
+    for (int e = 0; e < VEC; e++) o[e] = c;
+}
+
+// Runs the chain that starts at code[pc] for VEC elements; returns the pc of the statement word that ends it and leaves
+// the chain's value in `acc`.
+__device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row, int64_t col, int n, const float* rowval, float (&acc)[VEC]) {
+    float tmp[kTmp][VEC];
+    for (;; pc++) {
+        const int32_t w = P.code[pc];
+        const int op = w_op(w);
+        if (op >= CH_ROW_REDUCE) break;
+        const int sub = w_sub(w), rdt = w_rdt(w);
         if (op == CH_TSTORE) {
-            if constexpr (SP >= 1) {
+            const int idx = w_index(w);
 #pragma unroll
-                for (int t = 0; t < kTmp; t++)
-                    if (t == a) {
+            for (int t = 0; t < kTmp; t++)
+                if (t == idx) {
 #pragma unroll
-                        for (int e = 0; e < VEC; e++) tmp[t][e] = st[SP - 1][e];
-                    }
-            }
-            return;
+                    for (int e = 0; e < VEC; e++) tmp[t][e] = acc[e];
+                }
+            continue;
         }
         if (op == CH_UNARY) {
-            if constexpr (SP >= 1) {
-                float (&x)[VEC] = st[SP - 1];
-                switch (a) {
-                    case U_CAST: break;
-#define B200JT_U(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float v = x[e]; x[e] = (EXPR); } break
-                    B200JT_U(U_NEG, -v);
-                    B200JT_U(U_ABS, fabsf(v));
-                    B200JT_U(U_LNOT, (float)(v == 0));
-                    B200JT_U(U_LOG, logf(v));
-                    B200JT_U(U_EXP, expf(v));
-                    B200JT_U(U_SQRT, sqrtf(v));
-                    B200JT_U(U_TANH, tanhf(v));
-                    B200JT_U(U_SIGMOID, 1.f / (1.f + expf(-v < 30.f ? -v : 30.f)));
+            switch (sub) {
+                case U_CAST: break;
+#define B200JT_U(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float v = acc[e]; acc[e] = (EXPR); } break
+                B200JT_U(U_NEG, -v);
+                B200JT_U(U_ABS, fabsf(v));
+                B200JT_U(U_LNOT, (float)(v == 0));
+                B200JT_U(U_LOG, logf(v));
+                B200JT_U(U_EXP, expf(v));
+                B200JT_U(U_SQRT, sqrtf(v));
+                B200JT_U(U_TANH, tanhf(v));
+                B200JT_U(U_SIGMOID, 1.f / (1.f + expf(-v < 30.f ? -v : 30.f)));
 #undef B200JT_U
-                    default: {
-                        float buf[VEC];
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) buf[e] = x[e];
-                        rare_unary(a, buf);
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) x[e] = buf[e];
-                    }
-                }
-                if (rdt != B200JT_FLOAT32) {
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) x[e] = round_to(x[e], rdt);
-                }
+                default: rare_unary(sub, acc);
             }
-            return;
-        }
-        if (op == CH_BINARY) {
-            if constexpr (SP >= 2) {
-                float (&x)[VEC] = st[SP - 2];
-                const float (&y)[VEC] = st[SP - 1];
-                switch (a) {
-#define B200JT_B(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float p = x[e], q = y[e]; x[e] = (EXPR); } break
+        } else {
+            float o[VEC];
+            fetch(P, w, pc, row, col, n, rowval, tmp, o);
+            if (op == CH_LOAD) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) acc[e] = o[e];
+            } else if (op == CH_BINARY) {
+                if (w_swap(w)) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) { const float t = acc[e]; acc[e] = o[e]; o[e] = t; }
+                }
+                switch (sub) {
+#define B200JT_B(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float p = acc[e], q = o[e]; acc[e] = (EXPR); } break
                     B200JT_B(OP_ADD, p + q);
                     B200JT_B(OP_SUB, p - q);
                     B200JT_B(OP_MUL, p * q);
@@ -309,56 +313,21 @@ struct Exec {
                     B200JT_B(OP_EQ, (float)(p == q));
                     B200JT_B(OP_NE, (float)(p != q));
 #undef B200JT_B
-                    default: {
-                        float bx[VEC], by[VEC];
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) { bx[e] = x[e]; by[e] = y[e]; }
-                        rare_binary(a, bx, by);
-#pragma unroll
-                        for (int e = 0; e < VEC; e++) x[e] = bx[e];
-                    }
+                    default: rare_binary(sub, acc, o);
                 }
-                if (rdt != B200JT_FLOAT32) {
+            } else {                    // CH_SELECT: acc ? o : o2, the second operand is described by the next word
+                float o2[VEC];
+                const int32_t w2 = P.code[++pc];
+                fetch(P, w2, pc, row, col, n, rowval, tmp, o2);
 #pragma unroll
-                    for (int e = 0; e < VEC; e++) x[e] = round_to(x[e], rdt);
-                }
-            }
-            return;
-        }
-        if (op == CH_TERNARY) {             // stack: cond, x, y
-            if constexpr (SP >= 3) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) st[SP - 3][e] = st[SP - 3][e] != 0.f ? st[SP - 2][e] : st[SP - 1][e];
-                if (rdt != B200JT_FLOAT32) {
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) st[SP - 3][e] = round_to(st[SP - 3][e], rdt);
-                }
+                for (int e = 0; e < VEC; e++) acc[e] = acc[e] != 0.f ? o[e] : o2[e];
             }
         }
-    }
-};
-
-// Runs the chain that starts at code[pc] for VEC elements; returns the pc of the statement word that ends it and leaves
-// the chain's value in `top`.
-__device__ __noinline__ int eval_chain(const Program& P, int pc, int64_t row, int64_t col, int n, const float* rowval, float* top) {
-    float st[kStack][VEC];
-    float tmp[kTmp][VEC];
-    int sp = 0;
-    for (;; pc++) {
-        const int32_t w = P.code[pc];
-        const int op = w & 0xff, a = (w >> 8) & 0xffff, rdt = (w >> 24) & 0xff;
-        if (op >= CH_ROW_REDUCE) break;
-        const int32_t next_word = op == CH_CONST ? P.code[pc + 1] : 0;
-        switch (sp) {
-#define B200JT_SP(N) case N: Exec<N>::step(P, op, a, rdt, next_word, row, col, n, rowval, st, tmp); break
-            B200JT_SP(0); B200JT_SP(1); B200JT_SP(2); B200JT_SP(3); B200JT_SP(4); B200JT_SP(5); B200JT_SP(6);
-#undef B200JT_SP
-        }
-        if (op == CH_CONST) pc++;
-        sp += (op == CH_INPUT || op == CH_CONST || op == CH_ROWVAL || op == CH_TLOAD) ? 1 : (op == CH_BINARY ? -1 : (op == CH_TERNARY ? -2 : 0));
-    }
+        if (rdt != B200JT_FLOAT32) {
 #pragma unroll
-    for (int e = 0; e < VEC; e++) top[e] = st[0][e];
+            for (int e = 0; e < VEC; e++) acc[e] = round_to(acc[e], rdt);
+        }
+    }
     return pc;
 }
 
@@ -409,16 +378,16 @@ chain_rows_kernel(const __grid_constant__ Program P) {
         while (pc < P.n_code) {
             // find the statement that ends the chain starting at pc (statement words are >= CH_ROW_REDUCE)
             int end = pc;
-            while ((P.code[end] & 0xff) < CH_ROW_REDUCE) end += ((P.code[end] & 0xff) == CH_CONST) ? 2 : 1;
+            while (w_op(P.code[end]) < CH_ROW_REDUCE) end += (w_kind(P.code[end]) == K_CONST) ? 2 : 1;
             const int32_t w = P.code[end];
-            const int sop = w & 0xff, a = (w >> 8) & 0xffff, rdt = (w >> 24) & 0xff;
+            const int sop = w_op(w), a = w_index(w), rdt = w_rdt(w);
             if (sop == CH_STORE_ROW) {
                 if (t == 0) store_as<float>(P.out, P.out_dtype, row, rowval[a]);
             } else {
                 // one loop for the three kinds of statement, so that the interpreter is instantiated once: a per-row map
                 // is a single evaluation at column 0 by every thread of the group
                 const bool row_map = sop == CH_ROW_MAP;
-                const int rop = a >> 4;
+                const int rop = w_sub(w);
                 float acc = fold_init(rop);
                 const int64_t col_end = row_map ? 1 : P.cols;
                 for (int64_t col = row_map ? 0 : (int64_t)t * VEC; col < col_end; col += (int64_t)G * VEC) {
@@ -447,7 +416,7 @@ chain_rows_kernel(const __grid_constant__ Program P) {
 #pragma unroll
                         for (int k = 1; k < 8; k++) acc = fold(rop, acc, xch[k]);
                     }
-                    rowval[a & 15] = round_to(acc, rdt);
+                    rowval[a] = round_to(acc, rdt);
                 }
             }
             pc = end + 1;
@@ -473,29 +442,39 @@ extern "C" int b200jt_fused_chain(const b200jt_tensor* inputs, int n_inputs, con
     B200JT_CHECK_ARG(valid_tensor(out), "invalid output descriptor");
     Program Q; memset(&Q, 0, sizeof(Q));
     bool has_row_stmt = false, store_row = false;
-    // validate the program: stack depth, operand indices, statement structure
+    // validate the program: operand indices, the accumulator holds a value where one is used, statement structure
     {
-        int sp = 0;
+        bool have_acc = false;
+        auto operand_ok = [&](int32_t w, int& pc) -> bool {
+            const int kind = w_kind(w), idx = w_index(w);
+            if (kind == K_INPUT) return idx < n_inputs;
+            if (kind == K_CONST) return ++pc < n_code;
+            if (kind == K_ROWVAL) return idx < kMaxRowVals;
+            if (kind == K_TMP) return idx < kTmp;
+            return false;
+        };
         for (int pc = 0; pc < n_code; pc++) {
-            const int op = code[pc] & 0xff, a = (code[pc] >> 8) & 0xffff;
+            const int32_t w = code[pc];
+            const int op = w_op(w), idx = w_index(w);
             switch (op) {
-                case CH_INPUT: B200JT_CHECK_ARG(a < n_inputs, "program names an input that was not passed"); sp++; break;
-                case CH_CONST: B200JT_CHECK_ARG(pc + 1 < n_code, "truncated constant"); pc++; sp++; break;
-                case CH_ROWVAL: B200JT_CHECK_ARG(a < kMaxRowVals, "row value slot out of range"); sp++; break;
-                case CH_UNARY: B200JT_CHECK_ARG(sp >= 1 && a < U_INVALID, "bad unary"); break;
-                case CH_BINARY: B200JT_CHECK_ARG(sp >= 2, "binary needs two operands"); sp--; break;
-                case CH_TERNARY: B200JT_CHECK_ARG(sp >= 3, "ternary needs three operands"); sp -= 2; break;
-                case CH_TSTORE: B200JT_CHECK_ARG(sp >= 1 && a < kTmp, "bad temporary"); break;
-                case CH_TLOAD: B200JT_CHECK_ARG(a < kTmp, "bad temporary"); sp++; break;
-                case CH_ROW_REDUCE: B200JT_CHECK_ARG(sp == 1 && (a & 15) < kMaxRowVals, "bad row reduce"); sp = 0; has_row_stmt = true; break;
-                case CH_ROW_MAP: B200JT_CHECK_ARG(sp == 1 && a < kMaxRowVals, "bad row map"); sp = 0; has_row_stmt = true; break;
-                case CH_STORE: B200JT_CHECK_ARG(sp == 1 && pc == n_code - 1, "STORE must end the program"); sp = 0; break;
-                case CH_STORE_ROW: B200JT_CHECK_ARG(sp == 0 && a < kMaxRowVals && pc == n_code - 1, "STORE_ROW must end the program"); store_row = true; break;
+                case CH_LOAD: B200JT_CHECK_ARG(operand_ok(w, pc), "bad operand"); have_acc = true; break;
+                case CH_UNARY: B200JT_CHECK_ARG(have_acc && w_sub(w) < U_INVALID, "bad unary"); break;
+                case CH_BINARY: B200JT_CHECK_ARG(have_acc && operand_ok(w, pc), "bad binary"); break;
+                case CH_SELECT: {
+                    B200JT_CHECK_ARG(have_acc && operand_ok(w, pc) && pc + 1 < n_code, "bad select");
+                    const int32_t w2 = code[++pc];
+                    B200JT_CHECK_ARG(w_op(w2) == CH_OPERAND && operand_ok(w2, pc), "select needs a second operand word");
+                    break;
+                }
+                case CH_TSTORE: B200JT_CHECK_ARG(have_acc && idx < kTmp, "bad temporary"); break;
+                case CH_ROW_REDUCE: B200JT_CHECK_ARG(have_acc && idx < kMaxRowVals, "bad row reduce"); have_acc = false; has_row_stmt = true; break;
+                case CH_ROW_MAP: B200JT_CHECK_ARG(have_acc && idx < kMaxRowVals, "bad row map"); have_acc = false; has_row_stmt = true; break;
+                case CH_STORE: B200JT_CHECK_ARG(have_acc && pc == n_code - 1, "STORE must end the program"); have_acc = false; break;
+                case CH_STORE_ROW: B200JT_CHECK_ARG(!have_acc && idx < kMaxRowVals && pc == n_code - 1, "STORE_ROW must end the program"); store_row = true; break;
                 default: return fail(-1, "b200jt_fused_chain: unknown instruction");
             }
-            B200JT_CHECK_ARG(sp <= kStack, "expression too deep");
         }
-        const int last = code[n_code - 1] & 0xff;
+        const int last = w_op(code[n_code - 1]);
         B200JT_CHECK_ARG(last == CH_STORE || last == CH_STORE_ROW, "the program must end in STORE or STORE_ROW");
     }
     for (int d = 0; d < ndim; d++) B200JT_CHECK_ARG(full_shape[d] >= 0, "negative extent");

@@ -19,10 +19,12 @@ import struct
 from . import _capi as C
 from .var import Var
 
-MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_STACK, MAX_TMP = 8, 160, 8, 6, 2
+MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_TMP = 8, 160, 8, 3
 
-CH_INPUT, CH_CONST, CH_ROWVAL, CH_UNARY, CH_BINARY, CH_TERNARY, CH_TSTORE, CH_TLOAD = 1, 2, 3, 4, 5, 6, 7, 8
-CH_ROW_REDUCE, CH_ROW_MAP, CH_STORE, CH_STORE_ROW = 9, 10, 11, 12
+# word = op | sub << 4 | operand kind << 10 | operand index << 13 | swap << 21 | result dtype << 24
+CH_OPERAND, CH_LOAD, CH_UNARY, CH_BINARY, CH_SELECT, CH_TSTORE = 0, 1, 2, 3, 4, 5
+CH_ROW_REDUCE, CH_ROW_MAP, CH_STORE, CH_STORE_ROW = 8, 9, 10, 11
+K_NONE, K_INPUT, K_CONST, K_ROWVAL, K_TMP = 0, 1, 2, 3, 4
 
 UNARY_CODES = {n: i for i, n in enumerate(
     ["cast", "negative", "abs", "logical_not", "bitwise_not", "log", "exp", "sqrt", "round", "floor", "ceil", "sin", "asin",
@@ -42,8 +44,27 @@ class _Unfusable(Exception):
     pass
 
 
-def _word(op, arg=0, dtype="float32"):
-    return op | (arg << 8) | (C.DTYPE_CODES[str(dtype)] << 24)
+def _word(op, sub=0, operand=(K_NONE, 0), swap=0, dtype="float32"):
+    return op | (sub << 4) | (operand[0] << 10) | (operand[1] << 13) | (swap << 21) | (C.DTYPE_CODES[str(dtype)] << 24)
+
+
+def _const_word(value):
+    return struct.unpack("<i", struct.pack("<f", value))[0]
+
+
+def decode(words):
+    """[(op, sub, kind, index, swap, dtype code, constant or None)] -- for tests and debugging."""
+    out, pc = [], 0
+    while pc < len(words):
+        w = words[pc]
+        kind = (w >> 10) & 7
+        const = None
+        if kind == K_CONST:
+            pc += 1
+            const = struct.unpack("<f", struct.pack("<i", words[pc]))[0]
+        out.append((w & 15, (w >> 4) & 63, kind, (w >> 13) & 255, (w >> 21) & 1, (w >> 24) & 255, const))
+        pc += 1
+    return out
 
 
 def _is_node(v):
@@ -164,6 +185,7 @@ class _Builder:
         return None
 
     def _input(self, v, view, ctx):
+        """Registers leaf v (seen through `view`) and returns its operand."""
         if str(v.dtype) not in _LEAF_DTYPES:
             raise _Unfusable
         for s, f in zip(view, self.full):
@@ -177,7 +199,7 @@ class _Builder:
                 raise _Unfusable
             self.input_ids[key] = len(self.inputs)
             self.inputs.append((v, view))
-        return _word(CH_INPUT, self.input_ids[key], "float32")
+        return (K_INPUT, self.input_ids[key])
 
     # ---- expressions -----------------------------------------------------------------------------
     def _fusable(self, v, view):
@@ -195,67 +217,152 @@ class _Builder:
             return self._klass(view) is not None
         return False
 
-    def _emit(self, v, axes, code, ctx, memo):
-        """Appends postfix code for the value of v, whose own axes sit at positions `axes` of the full shape.
-        ctx 'full': evaluated per element; 'row': once per row."""
+    def _axes_of(self, v, axes):
+        if v.ndim > len(axes):
+            raise _Unfusable
+        return axes[len(axes) - v.ndim:]
+
+    def _through_broadcasts(self, v, axes):
+        """Follows broadcast_to nodes down to what they stretch: (node, axes of that node)."""
+        while True:
+            if _const_of(v) is not None:
+                return v, axes
+            axes = self._axes_of(v, axes)
+            if not (_is_node(v) and v._op.kind == "broadcast_to" and self._fusable(v, self._view(v.shape, axes))):
+                return v, axes
+            mask, keep = v._op.attrs["bcast_mask"], v._op.attrs["keepdims_mask"]
+            axes = [axes[i] for i in range(v.ndim) if not (mask >> i & 1) or (keep >> i & 1)]
+            v = v._op.inputs[0]
+            self.n_ops += 1
+
+    def _simple(self, v, axes, ctx, chain):
+        """The operand that names v's value without touching the accumulator (a constant, an input, a row value, a
+        temporary holding a shared sub-expression), or None if v has to be computed."""
+        v, axes = self._through_broadcasts(v, axes)
         c = _const_of(v)
         if c is not None:
-            code += [_word(CH_CONST, 0, "float32"), struct.unpack("<i", struct.pack("<f", c))[0]]
-            return
-        axes = axes[len(axes) - v.ndim:] if v.ndim <= len(axes) else None
-        if axes is None:
-            raise _Unfusable
+            return (K_CONST, 0, c)
         key = (id(v), tuple(axes))
         if key in self.row_slots:
-            code.append(_word(CH_ROWVAL, self.row_slots[key], "float32"))
-            return
+            return (K_ROWVAL, self.row_slots[key])
+        if key in chain["memo"]:
+            return (K_TMP, chain["memo"][key])
         view = self._view(v.shape, axes)
         if not self._fusable(v, view):
-            code.append(self._input(v, view, ctx))          # a leaf: realised data, or a node another kernel computes first
-            return
-        op = v._op
-        if op.kind == "reduce":
-            code.append(_word(CH_ROWVAL, self._row_reduce(v, key), "float32"))
-            return
-        if op.kind == "broadcast_to":
-            x = op.inputs[0]
-            mask, keep = op.attrs["bcast_mask"], op.attrs["keepdims_mask"]
-            kept = [axes[i] for i in range(v.ndim) if not (mask >> i & 1) or (keep >> i & 1)]
-            self.n_ops += 1
-            self._emit(x, kept, code, ctx, memo)            # the operand simply lacks (or has size 1 on) the new axes
-            return
+            return self._input(v, view, ctx)
+        if v._op.kind == "reduce":
+            return (K_ROWVAL, self._row_reduce(v, key))
         if self._klass(view) == "row" and ctx == "full":
-            code.append(_word(CH_ROWVAL, self._row_map(v, axes, key), "float32"))
-            return
-        if key in memo:                          # shared sub-expression inside this chain
-            start, end, slot = memo[key]
-            if slot is None:
-                slot = sum(1 for m in memo.values() if m[2] is not None)
-                if slot >= MAX_TMP:
-                    raise _Unfusable
-                code.insert(end, _word(CH_TSTORE, slot, "float32"))
-                for k2, (s0, e0, t0) in list(memo.items()):       # spans behind the insertion point move by one word
-                    if s0 >= end:
-                        memo[k2] = (s0 + 1, e0 + 1, t0)
-                    elif e0 > end:
-                        memo[k2] = (s0, e0 + 1, t0)
-                memo[key] = (start, end, slot)
-            code.append(_word(CH_TLOAD, slot, "float32"))
-            return
-        start = len(code)
-        for i in op.inputs:
-            self._emit(i, axes, code, ctx, memo)
-        if op.kind == "unary":
-            name = op.attrs["op"]
-            code.append(_word(CH_UNARY, UNARY_CODES["cast"] if name in C.DTYPE_CODES else UNARY_CODES[name], v.dtype))
-        elif op.kind == "binary":
-            code.append(_word(CH_BINARY, BINARY_CODES[op.attrs["op"]], v.dtype))
-        else:
-            code.append(_word(CH_TERNARY, 0, v.dtype))
-        self.n_ops += 1
-        memo[key] = (start, len(code), None)
+            return (K_ROWVAL, self._row_map(v, axes, key))
+        return None
+
+    @staticmethod
+    def _put(code, op, sub=0, operand=None, swap=0, dtype="float32"):
+        if op == CH_LOAD and operand[0] == K_TMP and code and code[-1] == _word(CH_TSTORE, 0, (K_TMP, operand[1])):
+            return                              # the accumulator still holds what was just parked there
+        code.append(_word(op, sub, operand[:2] if operand else (K_NONE, 0), swap, dtype))
+        if operand is not None and operand[0] == K_CONST:
+            code.append(_const_word(operand[2]))
         if len(code) > MAX_CODE:
             raise _Unfusable
+
+    def _tmp(self, chain):
+        if not chain["free"]:
+            raise _Unfusable
+        return chain["free"].pop()
+
+    def _gen(self, v, axes, code, ctx, chain):
+        """Appends code that leaves the value of v in the accumulator."""
+        opnd = self._simple(v, axes, ctx, chain)
+        if opnd is not None:
+            self._put(code, CH_LOAD, operand=opnd)
+            return
+        v, axes = self._through_broadcasts(v, axes)
+        key = (id(v), tuple(axes))
+        op = v._op
+        if op.kind == "unary":
+            name = op.attrs["op"]
+            self._gen(op.inputs[0], axes, code, ctx, chain)
+            self._put(code, CH_UNARY, UNARY_CODES["cast"] if name in C.DTYPE_CODES else UNARY_CODES[name], dtype=v.dtype)
+        elif op.kind == "binary":
+            x, y = op.inputs
+            sub = BINARY_CODES[op.attrs["op"]]
+            oy = self._simple(y, axes, ctx, chain)
+            if oy is not None:
+                self._gen(x, axes, code, ctx, chain)
+                self._put(code, CH_BINARY, sub, oy, 0, v.dtype)
+            else:
+                ox = self._simple(x, axes, ctx, chain)
+                if ox is not None:
+                    self._gen(y, axes, code, ctx, chain)
+                    self._put(code, CH_BINARY, sub, ox, 1, v.dtype)
+                else:
+                    self._gen(y, axes, code, ctx, chain)
+                    oy, t = self._simple(y, axes, ctx, chain), None
+                    if oy is None:
+                        t = self._tmp(chain)
+                        self._put(code, CH_TSTORE, operand=(K_TMP, t))
+                        oy = (K_TMP, t)
+                    self._gen(x, axes, code, ctx, chain)
+                    self._put(code, CH_BINARY, sub, oy, 0, v.dtype)
+                    if t is not None:
+                        chain["free"].append(t)
+        else:                                   # ternary: cond ? x : y
+            c, x, y = op.inputs
+            held = []
+            ops = []
+            for u in (x, y):
+                o = self._simple(u, axes, ctx, chain)
+                if o is None:
+                    self._gen(u, axes, code, ctx, chain)
+                    o = self._simple(u, axes, ctx, chain)       # a shared value has parked itself in a temporary
+                    if o is None:
+                        t = self._tmp(chain)
+                        self._put(code, CH_TSTORE, operand=(K_TMP, t))
+                        held.append(t)
+                        o = (K_TMP, t)
+                ops.append(o)
+            self._gen(c, axes, code, ctx, chain)
+            self._put(code, CH_SELECT, operand=ops[0], dtype=v.dtype)
+            self._put(code, CH_OPERAND, operand=ops[1])
+            chain["free"] += held
+        self.n_ops += 1
+        # a value other nodes of this chain use again is parked in a temporary (if one is left; else it is recomputed)
+        if chain["uses"].get(key, 0) > 1 and len(chain["free"]) > 1:
+            t = chain["free"].pop(0)
+            self._put(code, CH_TSTORE, operand=(K_TMP, t))
+            chain["memo"][key] = t
+
+    def _count_uses(self, v, axes, uses, ctx, depth=0):
+        """How often each computed node is referenced inside one chain (stops at leaves, row values, constants)."""
+        if depth > 64 or _const_of(v) is not None:
+            return
+        try:
+            v, axes = self._through_broadcasts(v, axes)
+        except _Unfusable:
+            return
+        if _const_of(v) is not None:
+            return
+        key = (id(v), tuple(axes))
+        view = self._view(v.shape, axes)
+        if key in self.row_slots or not self._fusable(v, view) or v._op.kind == "reduce":
+            return
+        if self._klass(view) == "row" and ctx == "full":
+            return
+        uses[key] = uses.get(key, 0) + 1
+        if uses[key] == 1:
+            for i in v._op.inputs:
+                self._count_uses(i, axes, uses, ctx, depth + 1)
+
+    def _chain(self, v, axes, ctx):
+        n_ops = self.n_ops
+        uses = {}
+        self._count_uses(v, axes, uses, ctx)
+        self.n_ops = n_ops                       # counting walks through broadcasts too; only _gen's count is kept
+        chain = {"free": list(range(MAX_TMP - 1, -1, -1)), "memo": {}, "uses": uses}
+        code = []
+        self._gen(v, axes, code, ctx, chain)
+        return code
 
     # ---- statements ------------------------------------------------------------------------------
     def _new_slot(self):
@@ -264,64 +371,39 @@ class _Builder:
         return len(self.row_slots)
 
     def _row_reduce(self, v, key):
-        code = []
-        self._emit(v._op.inputs[0], list(range(self.d)), code, "full", {})
+        code = self._chain(v._op.inputs[0], list(range(self.d)), "full")
         slot = self._new_slot()
-        code.append(_word(CH_ROW_REDUCE, slot | (REDUCE_CODES[v._op.attrs["op"]] << 4), v.dtype))
+        code.append(_word(CH_ROW_REDUCE, REDUCE_CODES[v._op.attrs["op"]], (K_NONE, slot), 0, v.dtype))
         self.statements.append(code)
         self.row_slots[key] = slot
         self.n_ops += 1
         return slot
 
     def _row_map(self, v, axes, key):
-        code = []
-        self._emit(v, axes, code, "row", {})
+        code = self._chain(v, axes, "row")
         slot = self._new_slot()
-        code.append(_word(CH_ROW_MAP, slot, v.dtype))
+        code.append(_word(CH_ROW_MAP, 0, (K_NONE, slot), 0, v.dtype))
         self.statements.append(code)
         self.row_slots[key] = slot
         return slot
 
     def build(self):
         root = self.root
-        full_axes = list(range(self.d))
         if _is_node(root) and root._op.kind == "reduce":
             if not self._fusable(root, None):
                 raise _Unfusable
             slot = self._row_reduce(root, (id(root), ()))
-            self.statements.append([_word(CH_STORE_ROW, slot, root.dtype)])
+            self.statements.append([_word(CH_STORE_ROW, 0, (K_NONE, slot), 0, root.dtype)])
         else:
             if not self._fusable(root, list(root.shape)) or (_is_node(root) and root._op.kind == "broadcast_to"):
                 raise _Unfusable
-            code = []
-            self._emit(root, full_axes, code, "full", {})
-            code.append(_word(CH_STORE, 0, root.dtype))
+            code = self._chain(root, list(range(self.d)), "full")
+            code.append(_word(CH_STORE, 0, (K_NONE, 0), 0, root.dtype))
             self.statements.append(code)
         words = [w for st in self.statements for w in st]
         if len(words) > MAX_CODE:
             raise _Unfusable
-        self._check_stack(words)
         return words
-
-    @staticmethod
-    def _check_stack(words):
-        sp, pc = 0, 0
-        while pc < len(words):
-            op = words[pc] & 0xff
-            if op in (CH_INPUT, CH_ROWVAL, CH_TLOAD):
-                sp += 1
-            elif op == CH_CONST:
-                sp += 1
-                pc += 1
-            elif op == CH_BINARY:
-                sp -= 1
-            elif op == CH_TERNARY:
-                sp -= 2
-            elif op >= CH_ROW_REDUCE:
-                sp = 0
-            if sp > MAX_STACK:
-                raise _Unfusable
-            pc += 1
 
 
 def build_program(v):

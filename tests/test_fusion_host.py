@@ -4,7 +4,7 @@ one fused op) and python/jittor/test/test_stop_fuse.py."""
 import jittor_b200 as jt
 from jittor_b200 import fusion, nn, executor
 
-CH = {1: "IN", 2: "CONST", 3: "ROWVAL", 4: "UN", 5: "BIN", 6: "TERN", 7: "TST", 8: "TLD", 9: "RRED", 10: "RMAP", 11: "STORE", 12: "STROW"}
+OPS = {0: "OPND", 1: "LOAD", 2: "UN", 3: "BIN", 4: "SEL", 5: "TST", 8: "RRED", 9: "RMAP", 10: "STORE", 11: "STROW"}
 
 
 def ph(shape, dtype="float32"):
@@ -12,33 +12,28 @@ def ph(shape, dtype="float32"):
 
 
 def ops(words):
-    out, pc = [], 0
-    while pc < len(words):
-        op = words[pc] & 0xff
-        out.append(CH[op])
-        pc += 2 if op == 2 else 1
-    return out
+    return [OPS[d[0]] for d in fusion.decode(words)]
 
 
 def test_scale_shift_is_one_map():
     x, w, b = ph([64, 4096]), ph([4096]), ph([4096])
     words, inputs, full, k, n = fusion.build_program(x * w + b)
-    assert ops(words) == ["IN", "IN", "BIN", "IN", "BIN", "STORE"] and k == 0 and full == [64, 4096]
-    assert [view for _, view in inputs] == [[64, 4096], [1, 4096], [1, 4096]]
-    assert executor._match_fused_chain(x * w + b).leaves == [x, w, b]
+    assert ops(words) == ["LOAD", "BIN", "BIN", "STORE"] and k == 0 and full == [64, 4096]
+    assert sorted(view for _, view in inputs) == [[1, 4096], [1, 4096], [64, 4096]]
+    assert {id(v) for v in executor._match_fused_chain(x * w + b).leaves} == {id(x), id(w), id(b)}
 
 
 def test_shared_subexpression_uses_a_temporary():
     x, b = ph([64, 4096]), ph([4096])
     words, inputs, _, _, _ = fusion.build_program(nn.relu(x + b))
-    assert ops(words) == ["IN", "IN", "BIN", "TST", "CONST", "BIN", "TLD", "CONST", "TERN", "STORE"]
+    assert ops(words) == ["LOAD", "BIN", "TST", "BIN", "SEL", "OPND", "STORE"]        # x + b is computed once and parked
     assert len(inputs) == 2
 
 
 def test_multiply_then_row_sum_is_one_reduce_statement():
     a, b = ph([32, 100]), ph([32, 100])
     words, inputs, full, k, _ = fusion.build_program((a * b).sum(1))
-    assert ops(words) == ["IN", "IN", "BIN", "RRED", "STROW"] and k == 1 and full == [32, 100]
+    assert ops(words) == ["LOAD", "BIN", "RRED", "STROW"] and k == 1 and full == [32, 100]
     words, _, _, k, _ = fusion.build_program((a * b).sum(1, keepdims=True))
     assert ops(words)[-1] == "STROW" and k == 1
 
@@ -55,7 +50,7 @@ def test_reduce_then_broadcast_back_orders_the_statements():
     m = x.max(1)
     z = x - m.broadcast(x, [1])
     words, inputs, _, k, _ = fusion.build_program(z)
-    assert ops(words) == ["IN", "RRED", "IN", "ROWVAL", "BIN", "STORE"] and len(inputs) == 1
+    assert ops(words) == ["LOAD", "RRED", "LOAD", "BIN", "STORE"] and len(inputs) == 1
 
 
 def test_softmax_backward_is_one_program():
@@ -99,5 +94,5 @@ def test_bf16_chain_keeps_node_dtypes():
     with jt.flag_scope(amp_reg=2):
         v = nn.relu(xb * w.broadcast(xb, [0, 2, 3]))
     words, inputs, full, k, _ = fusion.build_program(v)
-    assert v.dtype == "bfloat16" and (words[-1] >> 24) == 7                      # STORE carries the bfloat16 code
-    assert [view for _, view in inputs] == [[8, 16, 6, 6], [1, 16, 1, 1]]
+    assert v.dtype == "bfloat16" and fusion.decode(words)[-1][5] == 7             # STORE carries the bfloat16 code
+    assert sorted(view for _, view in inputs) == [[1, 16, 1, 1], [8, 16, 6, 6]]
