@@ -234,11 +234,24 @@ __device__ __noinline__ void rare_binary(int op, float* a, const float* b) {
     for (int e = 0; e < VEC; e++) a[e] = binary_f(op, a[e], b[e]);
 }
 
+constexpr int kPre = 4;         // input operands of a chain whose loads are issued before the chain is interpreted
+
 // Operand of word w into o[]; advances pc over an inline constant.
 __device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int64_t row, int64_t col, int n, const float* rowval,
-                                      const float (&tmp)[kTmp][VEC], float (&o)[VEC]) {
+                                      const float (&tmp)[kTmp][VEC], const float (&pre)[kPre][VEC], int n_pre, int& used, float (&o)[VEC]) {
     const int kind = w_kind(w), idx = w_index(w);
-    if (kind == K_INPUT) { load_input(P.in[idx], row, col, P.cols, n, o); return; }
+    if (kind == K_INPUT) {
+        if (used < n_pre) {
+#pragma unroll
+            for (int k = 0; k < kPre; k++)
+                if (k == used) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) o[e] = pre[k][e];
+                }
+            used++;
+        } else load_input(P.in[idx], row, col, P.cols, n, o);
+        return;
+    }
     if (kind == K_TMP) {
 #pragma unroll
         for (int t = 0; t < kTmp; t++)
@@ -256,7 +269,25 @@ __device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int6
 // Runs the chain that starts at code[pc] for VEC elements; returns the pc of the statement word that ends it and leaves
 // the chain's value in `acc`.
 __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row, int64_t col, int n, const float* rowval, float (&acc)[VEC]) {
-    float tmp[kTmp][VEC];
+    // initialised on purpose: a conditional store into an undefined value lets the compiler drop the condition, and
+    // then every TSTORE would write all temporaries
+    float tmp[kTmp][VEC] = {};
+    // The loads of the chain's first input operands are issued together, before any of them is used: the interpreter
+    // consumes operands one instruction at a time, and without this every input would cost its own trip to memory.
+    float pre[kPre][VEC] = {};
+    int n_pre = 0, used = 0;
+    for (int q = pc; n_pre < kPre; q++) {
+        const int32_t w = P.code[q];
+        if (w_op(w) >= CH_ROW_REDUCE) break;
+        const int kind = w_kind(w);
+        if (kind == K_CONST) q++;
+        else if (kind == K_INPUT) {
+#pragma unroll
+            for (int k = 0; k < kPre; k++)
+                if (k == n_pre) load_input(P.in[w_index(w)], row, col, P.cols, n, pre[k]);
+            n_pre++;
+        }
+    }
     for (;; pc++) {
         const int32_t w = P.code[pc];
         const int op = w_op(w);
@@ -289,7 +320,7 @@ __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row,
             }
         } else {
             float o[VEC];
-            fetch(P, w, pc, row, col, n, rowval, tmp, o);
+            fetch(P, w, pc, row, col, n, rowval, tmp, pre, n_pre, used, o);
             if (op == CH_LOAD) {
 #pragma unroll
                 for (int e = 0; e < VEC; e++) acc[e] = o[e];
@@ -318,7 +349,7 @@ __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row,
             } else {                    // CH_SELECT: acc ? o : o2, the second operand is described by the next word
                 float o2[VEC];
                 const int32_t w2 = P.code[++pc];
-                fetch(P, w2, pc, row, col, n, rowval, tmp, o2);
+                fetch(P, w2, pc, row, col, n, rowval, tmp, pre, n_pre, used, o2);
 #pragma unroll
                 for (int e = 0; e < VEC; e++) acc[e] = acc[e] != 0.f ? o[e] : o2[e];
             }

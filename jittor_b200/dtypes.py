@@ -27,12 +27,16 @@ REDUCE_OPS = ("maximum", "minimum", "add", "multiply", "logical_and", "logical_o
 AMP_PREFER32, AMP_PREFER16, AMP_KEEP_REDUCE, AMP_KEEP_WHITE, AMP_ARRAY_PREFER, AMP_NO_REDUCE_UPCAST = 1, 2, 4, 8, 16, 32
 
 
+_ALIASES = {"float": "float32", "int": "int32", "double": "float64", "half": "float16"}
+
+
 class DType(str):
-    """A dtype name that also compares equal to the numpy dtype of the same name."""
+    """A dtype name that also compares equal to the numpy dtype of the same name and to the reference's short names
+    ("float", "int", "double", "half": python/jittor/src/misc/nano_string.cc aliases)."""
 
     def __eq__(self, other):
         if isinstance(other, str):
-            return str.__eq__(self, other)
+            return str.__eq__(self, _ALIASES.get(other, other))
         try:
             return str.__eq__(self, np.dtype(other).name)
         except TypeError:
@@ -55,7 +59,7 @@ def canon(dt):
     if type(dt) is DType:
         return dt
     if isinstance(dt, str):
-        name = {"float": "float32", "int": "int32", "double": "float64", "half": "float16"}.get(dt, dt)
+        name = _ALIASES.get(dt, dt)
     elif dt is float:
         name = "float32"
     elif dt is int:

@@ -96,3 +96,97 @@ def test_bf16_chain_keeps_node_dtypes():
     words, inputs, full, k, _ = fusion.build_program(v)
     assert v.dtype == "bfloat16" and fusion.decode(words)[-1][5] == 7             # STORE carries the bfloat16 code
     assert sorted(view for _, view in inputs) == [[1, 16, 1, 1], [8, 16, 6, 6]]
+
+
+# ---- a reference interpreter of the program, in numpy: checks what the builder emits without a GPU -------------------
+import numpy as np
+
+from oracle import meta_ops_ref as ref
+
+_UN = {v: k for k, v in fusion.UNARY_CODES.items()}
+_BIN = {v: k for k, v in fusion.BINARY_CODES.items()}
+_RED = {v: k for k, v in fusion.REDUCE_CODES.items()}
+_DT = ["bool", "int8", "int16", "int32", "int64", "uint8", "float16", "bfloat16", "float32", "float64"]
+
+
+def interpret(words, inputs, full, k, arrays):
+    """Evaluates a program on numpy arrays (arrays[i] is the value of inputs[i][0]); float32 arithmetic, results of
+    float32 / bool nodes only (enough for the host tests)."""
+    d = len(full)
+    rows_shape = full[:d - k]
+    vals = [np.asarray(arrays[id(v)], dtype=np.float32).reshape(view) for v, view in inputs]
+    rowval, tmp, acc, out = {}, {}, None, None
+    dec = fusion.decode(words)
+    i = 0
+
+    def operand(e):
+        _, _, kind, idx, _, _, const = e
+        return {1: lambda: vals[idx], 2: lambda: np.float32(const), 3: lambda: rowval[idx], 4: lambda: tmp[idx]}[kind]()
+
+    while i < len(dec):
+        op, sub, kind, idx, swap, dt, const = dec[i]
+        if op == 1:
+            acc = operand(dec[i])
+        elif op == 2:
+            acc = acc if _UN[sub] == "cast" else ref.unary(np.asarray(acc, np.float32), _UN[sub])
+        elif op == 3:
+            o = operand(dec[i])
+            a, b = (o, acc) if swap else (acc, o)
+            acc = ref.binary(np.asarray(a, np.float32), np.asarray(b, np.float32), _BIN[sub])
+        elif op == 4:
+            o1 = operand(dec[i])
+            i += 1
+            o2 = operand(dec[i])
+            acc = np.where(np.asarray(acc) != 0, o1, o2)
+        elif op == 5:
+            tmp[idx] = acc
+        elif op == 8:
+            full_acc = np.broadcast_to(np.asarray(acc, np.float32), full)
+            axes = tuple(range(d - k, d))
+            f = {"add": np.sum, "mean": np.mean, "maximum": np.max, "minimum": np.min, "multiply": np.prod}[_RED[sub]]
+            rowval[idx] = f(full_acc.astype(np.float64), axis=axes, keepdims=True).astype(np.float32)
+        elif op == 9:
+            rowval[idx] = np.broadcast_to(np.asarray(acc, np.float32), rows_shape + [1] * k)
+        elif op == 10:
+            out = np.broadcast_to(acc, full)
+        elif op == 11:
+            out = np.broadcast_to(rowval[idx], rows_shape + [1] * k).reshape(rows_shape or [1])
+        if op not in (5, 8, 9) and dt == 0 and op in (2, 3, 4):
+            acc = np.asarray(acc) != 0
+        i += 1
+    return np.asarray(out)
+
+
+def _check_program(build, shapes, seed=0):
+    rng = np.random.default_rng(seed)
+    vars_ = [ph(s) for s in shapes]
+    arrays = {id(v): rng.uniform(0.5, 1.5, size=s).astype(np.float32) for v, s in zip(vars_, shapes)}
+    v = build(*vars_)
+    prog = fusion.build_program(v)
+    assert prog is not None
+    words, inputs, full, k, _ = prog
+    got = interpret(words, inputs, full, k, arrays)
+    return got.reshape(list(v.shape)), [arrays[id(x)] for x in vars_]
+
+
+def test_programs_compute_the_right_thing():
+    got, (x, w, b) = _check_program(lambda X, W, B: X * W + B, [(6, 16), (16,), (16,)])
+    assert np.allclose(got, x * w + b)
+    got, (x, w) = _check_program(lambda X, W: 2.0 - X / W, [(6, 16), (16,)])
+    assert np.allclose(got, 2.0 - x / w)
+    got, (x, w, b) = _check_program(lambda X, W, B: (X + W) * (X - B) / (X * B + W), [(6, 16), (16,), (16,)])
+    assert np.allclose(got, (x + w) * (x - b) / (x * b + w), rtol=1e-5)
+    got, (x, b) = _check_program(lambda X, B: nn.relu(X - B), [(6, 16), (16,)])
+    assert np.allclose(got, np.maximum(x - b, 0))
+    got, (x,) = _check_program(lambda X: (X - X.mean(1, keepdims=True)) / ((X * X).mean(1, keepdims=True) + 1e-5).sqrt(), [(5, 24)])
+    assert np.allclose(got, (x - x.mean(1, keepdims=True)) / np.sqrt((x * x).mean(1, keepdims=True) + 1e-5), rtol=1e-4, atol=1e-6)
+    got, (x, y) = _check_program(lambda X, Y: (X * Y).sum(1), [(5, 24), (5, 24)])
+    assert np.allclose(got, (x * y).sum(1), rtol=1e-5)
+
+
+def test_softmax_backward_program_matches_the_formula():
+    got, (x, dy) = _check_program(lambda X, DY: jt.grad((nn.softmax(X, -1) * DY).sum(), X), [(7, 33), (7, 33)], seed=3)
+    e = np.exp(x - x.max(1, keepdims=True))
+    y = e / e.sum(1, keepdims=True)
+    want = y * (dy - (y * dy).sum(1, keepdims=True))
+    assert np.allclose(got, want, rtol=1e-4, atol=1e-6)
