@@ -199,6 +199,11 @@ class C2Scatter:
         out = val.reindex_reduce("add", [bins], ["@e0(i0)"], extras=[idx])
         return out.mpi_all_reduce("add") if self.multi else out      # shared output across ranks
 
+    def step_context(self):
+        """The bins' all-reduce of one part runs beside the scatter kernel of the next part (side stream, a few CTAs)."""
+        from jittor_b200 import dist
+        return dist.overlap_collectives()
+
     def run(self, name):
         return self._scatter(*self.dev[name]).sync()
 
@@ -788,9 +793,13 @@ def measure(wl, args, env, headline):
             tdist.barrier()
         torch.cuda.synchronize()
 
+    import contextlib
+    step_context = wl.step_context if (multi and hasattr(wl, "step_context") and args.overlap) else contextlib.nullcontext
+
     def step_direct():
-        for nm in names:
-            wl.run(nm)
+        with step_context():
+            for nm in names:
+                wl.run(nm)
 
     warm = max(args.warmup, 3)
     for _ in range(warm):
@@ -804,9 +813,10 @@ def measure(wl, args, env, headline):
         if flush:
             flush()
         ev[s][0].record()
-        for i, nm in enumerate(names):
-            wl.run(nm)
-            ev[s][i + 1].record()
+        with step_context():
+            for i, nm in enumerate(names):
+                wl.run(nm)
+                ev[s][i + 1].record()
     barrier()
     part_ms = {nm: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(psteps)) / psteps for i, nm in enumerate(names)}
     # (2) the timed region: K steps. One step (kernels and collectives of all parts) is captured into a CUDA graph and
@@ -823,7 +833,8 @@ def measure(wl, args, env, headline):
             barrier()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                keep = [wl.run(nm) for nm in names]      # noqa: F841  (outputs stay alive with the graph)
+                with step_context():
+                    keep = [wl.run(nm) for nm in names]      # noqa: F841  (outputs stay alive with the graph)
             graph.replay()
             barrier()
         except Exception as exc:                     # noqa: BLE001
@@ -875,8 +886,9 @@ def measure(wl, args, env, headline):
     def e2e_step():
         # steps pipeline: the read-back of one step overlaps the uploads of the next; everything is drained
         # (both streams synchronised) before the timed region closes
-        for nm in names:
-            wl.run_e2e(nm)
+        with step_context():
+            for nm in names:
+                wl.run_e2e(nm)
 
     e2e_steps = (max(2, min(steps, 5)) if headline else 2) if args.e2e else 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -957,6 +969,7 @@ def measure(wl, args, env, headline):
         "gpu_launches": steps * sum(wl.launches[n] + (1 if peer_kernel and n in getattr(wl, "all_reduced", ()) else 0)
                                     for n in names),
         "collective": None if not multi else ("peer-kernel (NVLink loads/stores, one launch per rank)" if peer_kernel else "nccl"),
+        "collective_overlap": bool(multi and peer_kernel and hasattr(wl, "step_context") and args.overlap),
         "roofline": {"bound": wl.bound, "kernel": dom_name, "parts": dom["parts"], "achieved": achieved, "peak": peak,
                      "unit": wl.unit, "frac": achieved / peak, "peak_source": peak_src,
                      "traffic": (dom["traffic"] / dom["launches"]) if dom["traffic"] else None,
@@ -993,6 +1006,7 @@ def main():
     ap.add_argument("--e2e", type=int, default=1)
     ap.add_argument("--verify", type=int, default=1, help="untimed correctness witness after the timed regions")
     ap.add_argument("--stability", type=int, default=300, help="individually timed repetitions after the timed region")
+    ap.add_argument("--overlap", type=int, default=1, help="N > 1: run a part's all-reduce beside the next part's kernel")
     ap.add_argument("--graph", type=int, default=1, help="replay the step from a CUDA graph in the timed region")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))

@@ -277,6 +277,12 @@ int b200jt_peer_comm_create(int rank, int world, void* own_segment, const unsign
                             size_t data_bytes, double wait_ms, void** comm);
 int b200jt_peer_comm_destroy(void* comm);
 size_t b200jt_peer_max_bytes(const void* comm);
+/* Running the collective BESIDE the next kernel instead of between two kernels (the reference serialises both on stream 0,
+ * python/jittor/extern/cuda/nccl/ops/nccl_all_reduce_op.cc:57): b200jt_peer_comm_set_max_blocks caps the CTAs of one
+ * all-reduce call (0 = no cap; every rank must use the same value), and b200jt_set_sm_reserve(sms) makes the persistent
+ * kernels of this library size their grids for 148 - sms SMs, so that the collective's CTAs find room while they run. */
+int b200jt_peer_comm_set_max_blocks(void* comm, int max_blocks);
+int b200jt_set_sm_reserve(int sms);
 int b200jt_peer_all_reduce(void* comm, const void* src, void* dst, int64_t count, int dtype, const char* op, void* stream);
 /* The same job with all ranks on ONE device (test aid and single-GPU emulation): `world` communicators whose segments
  * live side by side, and one cooperative launch that plays every rank (blocks wait on one another, so they have

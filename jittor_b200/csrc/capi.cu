@@ -1,6 +1,8 @@
 // Error plumbing, dtype/op name tables and version query of the C ABI.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace b200jt {
 
 static thread_local std::string g_last_error;
@@ -34,7 +36,16 @@ OpCode binary_op_from_name(const char* n) {
     return OP_INVALID;
 }
 
+static std::atomic<int> g_sm_reserve{0};
+int sm_reserve() { return g_sm_reserve.load(std::memory_order_relaxed); }
+
 }  // namespace b200jt
+
+extern "C" int b200jt_set_sm_reserve(int sms) {
+    B200JT_CHECK_ARG(sms >= 0 && sms <= 64, "sms must be 0..64");
+    b200jt::g_sm_reserve.store(sms);
+    return 0;
+}
 
 extern "C" const char* b200jt_last_error(void) { return b200jt::g_last_error.c_str(); }
 extern "C" int b200jt_version(void) { return 100; }

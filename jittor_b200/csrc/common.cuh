@@ -93,9 +93,13 @@ __device__ __forceinline__ void store_as(void* p, int dt, int64_t i, T v) {
 // ---- launch sizing -----------------------------------------------------------------------------
 // Grid for a grid-stride loop over `work` threads: enough CTAs to cover it, capped at a whole number
 // of waves over the 148 SMs.
+// SMs the grids leave free for a collective that runs beside them on another stream (0 unless a host asked for it with
+// b200jt_set_sm_reserve): the persistent kernels size themselves as if the GPU had kNumSMs - sm_reserve() SMs.
+int sm_reserve();
+
 inline unsigned grid_for(int64_t work, int block, int ctas_per_sm = 8) {
     int64_t need = (work + block - 1) / block;
-    int64_t cap = (int64_t)kNumSMs * ctas_per_sm;
+    int64_t cap = (int64_t)(kNumSMs - sm_reserve()) * ctas_per_sm;
     if (need < 1) need = 1;
     return (unsigned)(need < cap ? need : cap);
 }

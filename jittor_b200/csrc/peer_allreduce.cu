@@ -195,8 +195,10 @@ struct BlockPacks {
 
 // The message is cut into 16-byte packs (nv of them, the last one possibly partial); which block handles which pack
 // depends on the byte count only, so that all ranks agree whatever the alignment of their src/dst pointers.
-template <typename T, int OP, bool TWO_SHOT>
-__global__ void __launch_bounds__(kThreads) peer_all_reduce_kernel(Launch L, long long count) {
+// LIGHT: built for two CTAs per SM (64 registers), so that a CTA finds room on an SM that another kernel half fills; used
+// when the call is capped to a few blocks to run beside other work (b200jt_peer_comm_set_max_blocks).
+template <typename T, int OP, bool TWO_SHOT, bool LIGHT>
+__global__ void __launch_bounds__(kThreads, LIGHT ? 2 : 1) peer_all_reduce_kernel(Launch L, long long count) {
     constexpr int V = 16 / (int)sizeof(T);
     constexpr int UC = 4;               // packs in flight per thread in the copies
     constexpr int UR = 2;               // ... and per rank in the reduction
@@ -336,6 +338,7 @@ struct Comm {
     unsigned char* segs[kMaxRanks] = {};
     bool opened[kMaxRanks] = {};        // mapped through an IPC handle (to be closed), not owned
     bool owns_segment = false;
+    int max_blocks = 0;                 // 0: no limit below kMaxBlocks (b200jt_peer_comm_set_max_blocks)
     DevComm dev{};                      // what the kernel receives
 };
 
@@ -351,16 +354,19 @@ static int upload(Comm* c, double wait_ms) {
 }
 
 template <typename T, int OP>
-static int launch_t(const Launch& L, int ranks_in_grid, int world, int64_t count, cudaStream_t st) {
+static int launch_t(const Launch& L, int ranks_in_grid, int world, int64_t count, int max_blocks, cudaStream_t st) {
     const size_t bytes = (size_t)count * sizeof(T);
     const long long nv = (long long)((bytes + 15) / 16);
     const bool two = bytes * (size_t)(world - 1) > kOneShotMaxRemoteBytes;
     const long long unit = two ? (nv + world - 1) / world : nv;             // packs one rank reduces
     // an emulated job keeps every rank's blocks co-resident: at most one block per SM over all ranks
-    const int cap = ranks_in_grid == 1 ? kMaxBlocks : std::max(1, std::min(kMaxBlocks, kNumSMs / ranks_in_grid));
+    int cap = ranks_in_grid == 1 ? kMaxBlocks : std::max(1, std::min(kMaxBlocks, kNumSMs / ranks_in_grid));
+    if (max_blocks > 0) cap = std::min(cap, max_blocks);
     const int blocks = (int)std::min<long long>(cap, std::max<long long>(1, (unit + kThreads - 1) / kThreads));
     dim3 grid(blocks, ranks_in_grid);
-    void (*kern)(Launch, long long) = two ? peer_all_reduce_kernel<T, OP, true> : peer_all_reduce_kernel<T, OP, false>;
+    void (*kern)(Launch, long long) = max_blocks > 0
+        ? (two ? peer_all_reduce_kernel<T, OP, true, true> : peer_all_reduce_kernel<T, OP, false, true>)
+        : (two ? peer_all_reduce_kernel<T, OP, true, false> : peer_all_reduce_kernel<T, OP, false, false>);
     if (ranks_in_grid == 1) {
         kern<<<grid, kThreads, 0, st>>>(L, (long long)count);
     } else {
@@ -374,20 +380,20 @@ static int launch_t(const Launch& L, int ranks_in_grid, int world, int64_t count
 }
 
 template <typename T>
-static int launch_op(const Launch& L, int ranks, int world, int64_t count, int op, cudaStream_t st) {
-    if (op == 0) return launch_t<T, 0>(L, ranks, world, count, st);
-    if (op == 1) return launch_t<T, 1>(L, ranks, world, count, st);
-    return launch_t<T, 2>(L, ranks, world, count, st);
+static int launch_op(const Launch& L, int ranks, int world, int64_t count, int op, int max_blocks, cudaStream_t st) {
+    if (op == 0) return launch_t<T, 0>(L, ranks, world, count, max_blocks, st);
+    if (op == 1) return launch_t<T, 1>(L, ranks, world, count, max_blocks, st);
+    return launch_t<T, 2>(L, ranks, world, count, max_blocks, st);
 }
 
-static int launch(const Launch& L, int ranks, int world, int64_t count, int dtype, int op, cudaStream_t st) {
+static int launch(const Launch& L, int ranks, int world, int64_t count, int dtype, int op, int max_blocks, cudaStream_t st) {
     switch (dtype) {
-        case B200JT_FLOAT32: return launch_op<float>(L, ranks, world, count, op, st);
-        case B200JT_FLOAT64: return launch_op<double>(L, ranks, world, count, op, st);
-        case B200JT_INT32: return launch_op<int32_t>(L, ranks, world, count, op, st);
-        case B200JT_INT64: return launch_op<int64_t>(L, ranks, world, count, op, st);
-        case B200JT_BFLOAT16: return launch_op<__nv_bfloat16>(L, ranks, world, count, op, st);
-        case B200JT_FLOAT16: return launch_op<__half>(L, ranks, world, count, op, st);
+        case B200JT_FLOAT32: return launch_op<float>(L, ranks, world, count, op, max_blocks, st);
+        case B200JT_FLOAT64: return launch_op<double>(L, ranks, world, count, op, max_blocks, st);
+        case B200JT_INT32: return launch_op<int32_t>(L, ranks, world, count, op, max_blocks, st);
+        case B200JT_INT64: return launch_op<int64_t>(L, ranks, world, count, op, max_blocks, st);
+        case B200JT_BFLOAT16: return launch_op<__nv_bfloat16>(L, ranks, world, count, op, max_blocks, st);
+        case B200JT_FLOAT16: return launch_op<__half>(L, ranks, world, count, op, max_blocks, st);
     }
     return fail(-1, "b200jt_peer_all_reduce: dtype must be float32/64, int32/64, float16 or bfloat16");
 }
@@ -497,6 +503,12 @@ extern "C" int b200jt_peer_comm_destroy(void* comm) {
     return 0;
 }
 
+extern "C" int b200jt_peer_comm_set_max_blocks(void* comm, int max_blocks) {
+    B200JT_CHECK_ARG(comm && max_blocks >= 0 && max_blocks <= peer::kMaxBlocks, "max_blocks must be 0..128");
+    static_cast<Comm*>(comm)->max_blocks = max_blocks;
+    return 0;
+}
+
 extern "C" size_t b200jt_peer_max_bytes(const void* comm) { return comm ? static_cast<const Comm*>(comm)->data_bytes : 0; }
 
 static int check_call(const Comm* c, const void* src, void* dst, int64_t count, int dtype, int op) {
@@ -514,7 +526,7 @@ extern "C" int b200jt_peer_all_reduce(void* comm, const void* src, void* dst, in
     if (int rc = check_call(c, src, dst, count, dtype, opc)) return rc;
     peer::Launch L{};
     L.comm[0] = c->dev; L.src[0] = src; L.dst[0] = dst;
-    return peer::launch(L, 1, c->world, count, dtype, opc, (cudaStream_t)stream);
+    return peer::launch(L, 1, c->world, count, dtype, opc, c->max_blocks, (cudaStream_t)stream);
 }
 
 extern "C" int b200jt_peer_all_reduce_local(void* const* comms, int world, const void* const* srcs, void* const* dsts,
@@ -528,5 +540,5 @@ extern "C" int b200jt_peer_all_reduce_local(void* const* comms, int world, const
         L.comm[r] = c->dev; L.src[r] = srcs[r]; L.dst[r] = dsts[r];
         B200JT_CHECK_ARG(c->world == world && c->rank == r, "comms must be the ranks 0..world-1 of one local job, in order");
     }
-    return peer::launch(L, world, world, count, dtype, opc, (cudaStream_t)stream);
+    return peer::launch(L, world, world, count, dtype, opc, static_cast<const Comm*>(comms[0])->max_blocks, (cudaStream_t)stream);
 }

@@ -475,16 +475,19 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         const bool e64 = P.extras[0].dtype == B200JT_INT64;
         constexpr int VEC = 16 / sizeof(T);
         const bool aligned = ((uintptr_t)yp % 16 == 0) && ((uintptr_t)P.extras[0].ptr % 16 == 0);
+        const int priv_grid = kPrivGrid - sm_reserve();         // rows of `partial` actually written and folded
+        // the shared-memory opt-in is set once per instantiation, not on every launch
 #define B200JT_PRIV(E, V)                                                                                      \
         do { auto k = rr_privatised_kernel<T, E, V>;                                                            \
-             B200JT_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrivMaxSmemBytes)); \
-             k<<<kPrivGrid, kPrivThreads, plan.smem, st>>>(yp, (const E*)P.extras[0].ptr, partial, n, (int)bins,   \
+             static const cudaError_t attr_ = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrivMaxSmemBytes); \
+             B200JT_CUDA(attr_);                                                                                  \
+             k<<<priv_grid, kPrivThreads, plan.smem, st>>>(yp, (const E*)P.extras[0].ptr, partial, n, (int)bins,   \
                                                            plan.replicas, op, is_bool); } while (0)
         if (e64) { if (aligned) B200JT_PRIV(int64_t, VEC); else B200JT_PRIV(int64_t, 1); }
         else     { if (aligned) B200JT_PRIV(int32_t, VEC); else B200JT_PRIV(int32_t, 1); }
 #undef B200JT_PRIV
         B200JT_LAUNCH_CHECK();
-        rr_fold_partials_kernel<T><<<grid_for((bins + 31) / 32 * 256, 256), 256, 0, st>>>(partial, xp, (int)bins, kPrivGrid, op, is_bool);
+        rr_fold_partials_kernel<T><<<grid_for((bins + 31) / 32 * 256, 256), 256, 0, st>>>(partial, xp, (int)bins, priv_grid, op, is_bool);
         B200JT_LAUNCH_CHECK();
         return 0;
     }
@@ -523,7 +526,7 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         if constexpr (sizeof(T) == 4 || sizeof(T) == 8) {
             if (bins < (1LL << 31)) {
                 const T init = init_value<T>(op, is_bool);
-                const unsigned grid = 2 * kNumSMs;
+                const unsigned grid = 2 * (kNumSMs - sm_reserve());
                 if (e64) {
                     if (aligned) rr_direct_cached_kernel<T, int64_t, VEC><<<grid, kCacheThreads, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op, init);
                     else rr_direct_cached_kernel<T, int64_t, 1><<<grid, kCacheThreads, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op, init);

@@ -52,6 +52,66 @@ def all_reduce_sum(src, out=None):
     return out
 
 
+_OVERLAP = {"active": False, "stream": None}
+
+
+class overlap_collectives:
+    """Inside this block an all-reduce of the path runs on a side stream beside the kernels that follow it, instead of
+    between them: the collective's kernel is capped to a few CTAs and the persistent kernels leave `sms` SMs free for it
+    (the reference runs every collective in order on stream 0, python/jittor/extern/cuda/nccl/ops/nccl_all_reduce_op.cc:57).
+    A result is waited for by whatever reads it first; leaving the block joins the side stream, so everything issued inside
+    is ordered before what follows. Every rank must enter and leave the block at the same points. Without the peer
+    kernel (one process, or NCCL only) the block changes nothing."""
+
+    def __init__(self, sms=8, blocks=16):
+        self.sms, self.blocks = sms, blocks
+
+    def __enter__(self):
+        from . import _capi as C
+        self.on = _PEER is not None and not _OVERLAP["active"]
+        if self.on:
+            if _OVERLAP["stream"] is None:
+                _OVERLAP["stream"] = torch.cuda.Stream(priority=-1)
+            _OVERLAP["active"] = True
+            C.check(C.lib.b200jt_set_sm_reserve(self.sms), "set_sm_reserve")
+            C.check(C.lib.b200jt_peer_comm_set_max_blocks(_PEER._h, self.blocks), "peer max blocks")
+        return self
+
+    def __exit__(self, *exc):
+        from . import _capi as C
+        if self.on:
+            torch.cuda.current_stream().wait_stream(_OVERLAP["stream"])
+            _OVERLAP["active"] = False
+            C.lib.b200jt_set_sm_reserve(0)
+            C.lib.b200jt_peer_comm_set_max_blocks(_PEER._h, 0)
+        return False
+
+
+class _StreamJoin:
+    """Handle kept by a Var whose value is produced on the side stream: wait() orders the current stream after it."""
+
+    def __init__(self, stream):
+        self.event = torch.cuda.Event()
+        self.event.record(stream)
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+def all_reduce_sum_overlapped(src):
+    """(result, join handle or None): the sum over the ranks, issued on the side stream when an overlap block is open and
+    the peer kernel takes the message; otherwise in stream order."""
+    if not (_OVERLAP["active"] and _PEER is not None and _PEER.usable(src)):
+        return all_reduce_sum(src), None
+    side, cur = _OVERLAP["stream"], torch.cuda.current_stream()
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        out = _PEER.all_reduce(src, torch.empty_like(src), "add")
+    src.record_stream(side)
+    out.record_stream(cur)
+    return out, _StreamJoin(side)
+
+
 def in_mpi():
     return tdist.is_available() and tdist.is_initialized() and tdist.get_world_size() > 1
 

@@ -234,12 +234,14 @@ def _run_reshape(v, op):
 
 
 def _run_all_reduce(v, op):
-    """Sum over the ranks, in stream order. (Launching it asynchronously next to the following kernels was measured
-    slower: the persistent one-CTA-per-SM kernels lose an SM to the collective and fall into a second wave.)"""
+    """Sum over the ranks: in stream order, or -- inside dist.overlap_collectives() -- on a side stream beside the kernels
+    that follow, in which case the Var carries a handle that its first reader waits on."""
     x = op.inputs[0]._data
     if tdist.is_available() and tdist.is_initialized() and tdist.get_world_size() > 1:
         from . import dist
-        return dist.all_reduce_sum(x)
+        out, join = dist.all_reduce_sum_overlapped(x)
+        v._pending = join
+        return out
     return x.clone()
 
 

@@ -43,6 +43,38 @@ def main():
     local = torch.zeros(1 << 16, dtype=torch.int32, device="cuda").index_add_(0, idx.long(), val)
     tdist.all_reduce(local)
     assert torch.equal(got, local)
+    # the same all-reduce run BESIDE the next scatter (side stream, capped blocks, reserved SMs): same bits, also from a
+    # captured graph replayed several times
+    parts = []
+    for k in range(3):
+        ik = torch.randint(0, 1 << 20, (1 << 22,), generator=g, device="cuda", dtype=torch.int32)
+        vk = torch.randint(0, 100, (1 << 22,), generator=g, device="cuda", dtype=torch.int32)
+        parts.append((jt.array(vk), jt.array(ik)))
+
+    def step():
+        with dist.overlap_collectives():
+            return [v.reindex_reduce("add", [1 << 20], ["@e0(i0)"], extras=[i]).mpi_all_reduce("add").sync() for v, i in parts]
+
+    want = [v.reindex_reduce("add", [1 << 20], ["@e0(i0)"], extras=[i]).mpi_all_reduce("add").torch().clone() for v, i in parts]
+    for o, w_ in zip(step(), want):
+        assert torch.equal(o.torch(), w_)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    tdist.barrier()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = step()
+    for _ in range(5):
+        graph.replay()
+    torch.cuda.synchronize()
+    for o, w_ in zip(outs, want):
+        assert torch.equal(o._data.view(-1), w_.view(-1))
+    assert C.lib.b200jt_device_status() == 0
     # sync BatchNorm statistics over the ranks' batches
     x = torch.randn(8, 64, 16, 16, generator=g, device="cuda")
     bn = nn.BatchNorm(64, is_train=True, sync=True)
