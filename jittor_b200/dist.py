@@ -63,8 +63,9 @@ class overlap_collectives:
     is ordered before what follows. Every rank must enter and leave the block at the same points. Without the peer
     kernel (one process, or NCCL only) the block changes nothing."""
 
-    def __init__(self, sms=8, blocks=16):
-        self.sms, self.blocks = sms, blocks
+    def __init__(self, sms=None, blocks=None):
+        self.sms = int(os.environ.get("B200JT_OVERLAP_SMS", 8)) if sms is None else sms
+        self.blocks = int(os.environ.get("B200JT_OVERLAP_BLOCKS", 2 * self.sms)) if blocks is None else blocks
 
     def __enter__(self):
         from . import _capi as C
