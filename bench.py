@@ -199,6 +199,23 @@ class C2Scatter:
         out = val.reindex_reduce("add", [bins], ["@e0(i0)"], extras=[idx])
         return out.mpi_all_reduce("add") if self.multi else out      # shared output across ranks
 
+    def extra(self, part_ms):
+        """The atomic units' measured rates beside the HBM fractions: a scatter that issues one red.global per element
+        (parts a-*) cannot run faster than 2^24 / red_global; the fp32 parts lean on shared-memory float adds."""
+        import ctypes
+        C = self.jt._capi
+        scratch = self.torch.empty(self.BINS_A, dtype=self.torch.int32, device="cuda")
+        rates = {}
+        for what, skew in (("red_global", 0), ("smem_int", 0), ("smem_int", 1), ("smem_float", 0), ("smem_float", 1), ("match_any", 0)):
+            g = ctypes.c_double()
+            C.check(C.lib.b200jt_probe_rate(what.encode(), skew, ctypes.c_void_p(scratch.data_ptr()), self.BINS_A, ctypes.byref(g)), "probe")
+            rates[what + ("_skewed" if skew else "")] = round(g.value, 1)
+        floor_ms = self.N_VAL / (rates["red_global"] * 1e9) * 1e3
+        out = {"atomic_rates_gops": rates, "red_global_floor_ms": floor_ms}
+        if "a-uniform" in part_ms:
+            out["a_uniform_frac_of_atomic_ceiling"] = floor_ms / part_ms["a-uniform"]
+        return out
+
     def step_context(self):
         """The bins' all-reduce of one part runs beside the scatter kernel of the next part (side stream, a few CTAs)."""
         from jittor_b200 import dist

@@ -291,6 +291,15 @@ int b200jt_peer_comm_create_local(int world, size_t data_bytes, double wait_ms, 
 int b200jt_peer_all_reduce_local(void* const* comms, int world, const void* const* srcs, void* const* dsts,
                                  int64_t count, int dtype, const char* op, void* stream);
 
+/* ---- diagnostics ---------------------------------------------------------------------------------
+ * Operation rates (1e9 per second) of the atomic units the scatter kernels lean on, each measured with one small kernel:
+ * "red_global" (red.global.add.u32 to random words of a `words`-word table: the ceiling of a one-atomic-per-element
+ * scatter), "smem_int", "smem_float" (shared-memory atomicAdd on 4096 words), "match_any". skewed != 0 sends about 16 % of
+ * the shared-memory operations to one address. Synchronises the device; scratch holds max(words * 4, 1024) bytes.
+ * The reference's profiler reports achieved bandwidth per kernel (python/jittor/src/profiler/profiler.cc:148-183); it has no
+ * counterpart of this probe. */
+int b200jt_probe_rate(const char* what, int skewed, void* scratch, int64_t words, double* gops);
+
 #ifdef __cplusplus
 }
 #endif

@@ -85,6 +85,7 @@ SIGNATURES = [
     ("b200jt_peer_max_bytes", _sz, [_vp]),
     ("b200jt_peer_comm_set_max_blocks", _i, [_vp, _i]),
     ("b200jt_set_sm_reserve", _i, [_i]),
+    ("b200jt_probe_rate", _i, [ctypes.c_char_p, _i, _vp, ctypes.c_int64, ctypes.POINTER(ctypes.c_double)]),
     ("b200jt_peer_all_reduce", _i, [_vp, _vp, _vp, ctypes.c_int64, _i, ctypes.c_char_p, _vp]),
     ("b200jt_peer_comm_create_local", _i, [_i, _sz, _d, ctypes.POINTER(_vp)]),
     ("b200jt_peer_all_reduce_local", _i, [ctypes.POINTER(_vp), _i, ctypes.POINTER(_vp), ctypes.POINTER(_vp),
