@@ -595,15 +595,16 @@ class FusedChains:
     key, metric, unit, bound, dtype, scaling = "fused", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
     ROWS, COLS = 32768, 4096
     description = ("fused element-wise chains on [32768,4096] fp32, one launch each: x*w+b (w, b per column), relu(x+bias), "
-                   "(a*b).sum(1), and the backward of row softmax (reverse-mode graph of exp/sub/div/max/sum)")
-    kernel_of = {"scale-shift": "chain_map_kernel", "relu-bias": "chain_map_kernel", "mul-rowsum": "chain_rows_kernel",
-                 "softmax-bwd": "chain_rows_kernel"}
+                   "(a*b).sum(1), (x-mean)/sqrt(mean(x*x)+eps) (three row statements through the chain interpreter), and the "
+                   "backward of nn.softmax (its own kernel from y and dy)")
+    kernel_of = {"scale-shift": "chain_fast_map_kernel", "relu-bias": "chain_fast_map_kernel", "mul-rowsum": "chain_fast_reduce_kernel",
+                 "centre-scale": "chain_rows_kernel", "softmax-bwd": "softmax_bwd_reg_kernel"}
     launches = {k: 1 for k in kernel_of}
 
     def work(self):
         n = self.ROWS * self.COLS * 4
         return {"scale-shift": 2 * n + 8 * self.COLS, "relu-bias": 2 * n + 4 * self.COLS, "mul-rowsum": 2 * n + 4 * self.ROWS,
-                "softmax-bwd": 3 * n}
+                "centre-scale": 2 * n, "softmax-bwd": 3 * n}
 
     def setup(self, rank, world, jt, torch, multi):
         from jittor_b200 import nn
@@ -612,6 +613,7 @@ class FusedChains:
         self.hx = torch.randn(self.ROWS, self.COLS, generator=g).pin_memory()
         self.x = [jt.array(self.hx), jt.array(torch.randn(self.ROWS, self.COLS, generator=g)), jt.array(torch.randn(self.ROWS, self.COLS, generator=g))]
         self.w, self.b = jt.array(torch.randn(self.COLS, generator=g)), jt.array(torch.randn(self.COLS, generator=g))
+        self.sm = [nn.softmax(v, -1).sync() for v in self.x]          # forward outputs the backward part starts from
         self.k = 0
         return list(self.kernel_of)
 
@@ -622,7 +624,12 @@ class FusedChains:
             return self.nn.relu(x + self.b)
         if name == "mul-rowsum":
             return (x * y).sum(1)
-        return self.jt.grad((self.nn.softmax(x, -1) * y).sum(), x)
+        if name == "centre-scale":
+            return (x - x.mean(1, keepdims=True)) / ((x * x).mean(1, keepdims=True) + 1e-5).sqrt()
+        sm = next((s for v, s in zip(self.x, self.sm) if v is x), None)
+        if sm is None:
+            sm = self.nn.softmax(x, -1)
+        return self.jt.grad((sm * y).sum(), x)
 
     def run(self, name):
         self.k += 1
@@ -649,6 +656,9 @@ class FusedChains:
                 want = np.maximum(x + b, 0)
             elif name == "mul-rowsum":
                 want = (x.astype(np.float64) * y).sum(1).astype(np.float32)
+            elif name == "centre-scale":
+                xd = x.astype(np.float64)
+                want = ((xd - xd.mean(1, keepdims=True)) / np.sqrt((xd * xd).mean(1, keepdims=True) + 1e-5)).astype(np.float32)
             else:
                 sm = ref.softmax(x, -1).astype(np.float64)
                 want = (sm * (y - (sm * y).sum(-1, keepdims=True))).astype(np.float32)

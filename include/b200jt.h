@@ -166,6 +166,11 @@ int b200jt_fused_chain(const b200jt_tensor* inputs, int n_inputs, const int64_t*
  * x, y: float32 or bfloat16 (fp32 math). */
 int b200jt_softmax(const b200jt_tensor* x, const b200jt_tensor* y, int log, void* stream);
 
+/* Gradient of the above over the last axis from the forward OUTPUT y and the output gradient dy:
+ * dx = y * (dy - sum(y*dy)) (softmax) or dy - exp(y) * sum(dy) (log-softmax), one read of y and dy, one write.
+ * Replaces the backward kernel of python/jittor/other/code_softmax.py:109-147. y, dy, dx: float32 or bfloat16, same dtype. */
+int b200jt_softmax_backward(const b200jt_tensor* y, const b200jt_tensor* dy, const b200jt_tensor* dx, int log, void* stream);
+
 /* Row LayerNorm over the last axis: mean, E[x^2], var = max(E[x^2]-E[x]^2, 0), y = x*w + b with
  * w = gamma/sqrt(var+eps), b = beta - mean*w. gamma/beta may be NULL (1 and 0).
  * Replaces the chain of python/jittor/nn.py:778-787. x, y: float32 or bfloat16; gamma, beta: float32 [cols]. */

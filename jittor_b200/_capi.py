@@ -63,6 +63,7 @@ SIGNATURES = [
     ("b200jt_ternary", _i, [_TP, _TP, _TP, _TP, _vp]),
     ("b200jt_fused_chain", _i, [_TP, _i, ctypes.POINTER(ctypes.c_int64), _i, _i, ctypes.POINTER(ctypes.c_int32), _i, _TP, _vp]),
     ("b200jt_softmax", _i, [_TP, _TP, _i, _vp]),
+    ("b200jt_softmax_backward", _i, [_TP, _TP, _TP, _i, _vp]),
     ("b200jt_layer_norm", _i, [_TP, _TP, _TP, _TP, _d, _vp]),
     ("b200jt_matmul_workspace", _sz, [_TP, _TP, _TP, _i, _i]),
     ("b200jt_matmul", _i, [_TP, _TP, _TP, _i, _i, _vp, _sz, _vp]),

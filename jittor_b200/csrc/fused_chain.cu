@@ -205,23 +205,26 @@ __device__ __forceinline__ void load_input(const Input& I, int64_t row, int64_t 
     }
 }
 
-__device__ __forceinline__ void store_output(const Program& P, int64_t off, int n, const float* v) {
-    if (P.out_vec_ok && n == VEC) {
-        if (P.out_dtype == B200JT_FLOAT32) {
-            float4* p = reinterpret_cast<float4*>((float*)P.out + off);
+__device__ __forceinline__ void store_vec(void* out, int out_dtype, int out_vec_ok, int64_t off, int n, const float* v) {
+    if (out_vec_ok && n == VEC) {
+        if (out_dtype == B200JT_FLOAT32) {
+            float4* p = reinterpret_cast<float4*>((float*)out + off);
             __stcs(p, make_float4(v[0], v[1], v[2], v[3]));
             __stcs(p + 1, make_float4(v[4], v[5], v[6], v[7]));
             return;
         }
-        if (P.out_dtype == B200JT_BFLOAT16) {
+        if (out_dtype == B200JT_BFLOAT16) {
             uint4 u; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
 #pragma unroll
             for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-            __stcs(reinterpret_cast<uint4*>((__nv_bfloat16*)P.out + off), u);
+            __stcs(reinterpret_cast<uint4*>((__nv_bfloat16*)out + off), u);
             return;
         }
     }
-    for (int e = 0; e < n; e++) store_as<float>(P.out, P.out_dtype, off + e, v[e]);
+    for (int e = 0; e < n; e++) store_as<float>(out, out_dtype, off + e, v[e]);
+}
+__device__ __forceinline__ void store_output(const Program& P, int64_t off, int n, const float* v) {
+    store_vec(P.out, P.out_dtype, P.out_vec_ok, off, n, v);
 }
 
 // ---- the interpreter -------------------------------------------------------------------------------------------
@@ -232,6 +235,48 @@ __device__ __noinline__ void rare_unary(int op, float* v) {
 __device__ __noinline__ void rare_binary(int op, float* a, const float* b) {
 #pragma unroll 1
     for (int e = 0; e < VEC; e++) a[e] = binary_f(op, a[e], b[e]);
+}
+
+__device__ __forceinline__ void apply_unary(int sub, float (&acc)[VEC]) {
+    switch (sub) {
+        case U_CAST: break;
+#define B200JT_U(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float v = acc[e]; acc[e] = (EXPR); } break
+        B200JT_U(U_NEG, -v);
+        B200JT_U(U_ABS, fabsf(v));
+        B200JT_U(U_LNOT, (float)(v == 0));
+        B200JT_U(U_LOG, logf(v));
+        B200JT_U(U_EXP, expf(v));
+        B200JT_U(U_SQRT, sqrtf(v));
+        B200JT_U(U_TANH, tanhf(v));
+        B200JT_U(U_SIGMOID, 1.f / (1.f + expf(-v < 30.f ? -v : 30.f)));
+#undef B200JT_U
+        default: rare_unary(sub, acc);
+    }
+}
+
+// acc = acc (sub) o, or o (sub) acc with swap
+__device__ __forceinline__ void apply_binary(int sub, int swap, float (&acc)[VEC], float (&o)[VEC]) {
+    if (swap) {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) { const float t = acc[e]; acc[e] = o[e]; o[e] = t; }
+    }
+    switch (sub) {
+#define B200JT_B(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float p = acc[e], q = o[e]; acc[e] = (EXPR); } break
+        B200JT_B(OP_ADD, p + q);
+        B200JT_B(OP_SUB, p - q);
+        B200JT_B(OP_MUL, p * q);
+        B200JT_B(OP_DIV, p / q);
+        B200JT_B(OP_MAX, p > q ? p : q);
+        B200JT_B(OP_MIN, q < p ? q : p);
+        B200JT_B(OP_LT, (float)(p < q));
+        B200JT_B(OP_LE, (float)(p <= q));
+        B200JT_B(OP_GT, (float)(p > q));
+        B200JT_B(OP_GE, (float)(p >= q));
+        B200JT_B(OP_EQ, (float)(p == q));
+        B200JT_B(OP_NE, (float)(p != q));
+#undef B200JT_B
+        default: rare_binary(sub, acc, o);
+    }
 }
 
 constexpr int kPre = 4;         // input operands of a chain whose loads are issued before the chain is interpreted
@@ -304,20 +349,7 @@ __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row,
             continue;
         }
         if (op == CH_UNARY) {
-            switch (sub) {
-                case U_CAST: break;
-#define B200JT_U(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float v = acc[e]; acc[e] = (EXPR); } break
-                B200JT_U(U_NEG, -v);
-                B200JT_U(U_ABS, fabsf(v));
-                B200JT_U(U_LNOT, (float)(v == 0));
-                B200JT_U(U_LOG, logf(v));
-                B200JT_U(U_EXP, expf(v));
-                B200JT_U(U_SQRT, sqrtf(v));
-                B200JT_U(U_TANH, tanhf(v));
-                B200JT_U(U_SIGMOID, 1.f / (1.f + expf(-v < 30.f ? -v : 30.f)));
-#undef B200JT_U
-                default: rare_unary(sub, acc);
-            }
+            apply_unary(sub, acc);
         } else {
             float o[VEC];
             fetch(P, w, pc, row, col, n, rowval, tmp, pre, n_pre, used, o);
@@ -325,27 +357,7 @@ __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row,
 #pragma unroll
                 for (int e = 0; e < VEC; e++) acc[e] = o[e];
             } else if (op == CH_BINARY) {
-                if (w_swap(w)) {
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) { const float t = acc[e]; acc[e] = o[e]; o[e] = t; }
-                }
-                switch (sub) {
-#define B200JT_B(CODE, EXPR) case CODE: _Pragma("unroll") for (int e = 0; e < VEC; e++) { const float p = acc[e], q = o[e]; acc[e] = (EXPR); } break
-                    B200JT_B(OP_ADD, p + q);
-                    B200JT_B(OP_SUB, p - q);
-                    B200JT_B(OP_MUL, p * q);
-                    B200JT_B(OP_DIV, p / q);
-                    B200JT_B(OP_MAX, p > q ? p : q);
-                    B200JT_B(OP_MIN, q < p ? q : p);
-                    B200JT_B(OP_LT, (float)(p < q));
-                    B200JT_B(OP_LE, (float)(p <= q));
-                    B200JT_B(OP_GT, (float)(p > q));
-                    B200JT_B(OP_GE, (float)(p >= q));
-                    B200JT_B(OP_EQ, (float)(p == q));
-                    B200JT_B(OP_NE, (float)(p != q));
-#undef B200JT_B
-                    default: rare_binary(sub, acc, o);
-                }
+                apply_binary(sub, w_swap(w), acc, o);
             } else {                    // CH_SELECT: acc ? o : o2, the second operand is described by the next word
                 float o2[VEC];
                 const int32_t w2 = P.code[++pc];
@@ -452,6 +464,143 @@ chain_rows_kernel(const __grid_constant__ Program P) {
             }
             pc = end + 1;
         }
+    }
+}
+
+// ---- short programs: everything static ---------------------------------------------------------------------------
+// A program that is ONE chain of at most 8 instructions over at most 4 inputs, ending in STORE or in ROW_REDUCE + STORE_ROW,
+// is pre-decoded on the host into a fixed array of steps. The kernel below unrolls over that array, so every field is read
+// with a compile-time offset, the loads of all inputs are issued before the first use, and only the op codes are looked at
+// at run time. This is the path the common chains take (x*w+b, relu(x+bias), (a*b).sum(1)); longer programs run through the
+// interpreter above.
+constexpr int kFastSteps = 8;
+constexpr int kFastInputs = 4;
+
+struct FastStep { int32_t op, sub, kind, idx, swap, rdt, kind2, idx2; float c, c2; };
+struct FastProgram {
+    Input in[kFastInputs];
+    FastStep step[kFastSteps];
+    int32_t n_in, n_steps;
+    int32_t reduce_op, reduce_rdt;       // row reduce after the chain (reduce_op < 0: plain store)
+    void* out;
+    int32_t out_dtype, out_vec_ok;
+    int64_t rows, cols;
+};
+
+__device__ __forceinline__ void fast_operand(int kind, int idx, float c, const float (&in)[kFastInputs][VEC], const float (&tmp)[kTmp][VEC],
+                                             float (&o)[VEC]) {
+    if (kind == K_INPUT) {
+#pragma unroll
+        for (int k = 0; k < kFastInputs; k++)
+            if (k == idx) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) o[e] = in[k][e];
+            }
+    } else if (kind == K_TMP) {
+#pragma unroll
+        for (int k = 0; k < kTmp; k++)
+            if (k == idx) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) o[e] = tmp[k][e];
+            }
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) o[e] = c;
+    }
+}
+
+__device__ __forceinline__ void eval_fast(const FastProgram& P, int64_t row, int64_t col, int n, float (&acc)[VEC]) {
+    float in[kFastInputs][VEC] = {};
+#pragma unroll
+    for (int k = 0; k < kFastInputs; k++)
+        if (k < P.n_in) load_input(P.in[k], row, col, P.cols, n, in[k]);
+    float tmp[kTmp][VEC] = {};
+#pragma unroll
+    for (int i = 0; i < kFastSteps; i++) {
+        if (i >= P.n_steps) break;
+        const FastStep& S = P.step[i];
+        if (S.op == CH_TSTORE) {
+#pragma unroll
+            for (int k = 0; k < kTmp; k++)
+                if (k == S.idx) {
+#pragma unroll
+                    for (int e = 0; e < VEC; e++) tmp[k][e] = acc[e];
+                }
+            continue;
+        }
+        if (S.op == CH_UNARY) apply_unary(S.sub, acc);
+        else {
+            float o[VEC];
+            fast_operand(S.kind, S.idx, S.c, in, tmp, o);
+            if (S.op == CH_LOAD) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) acc[e] = o[e];
+            } else if (S.op == CH_BINARY) apply_binary(S.sub, S.swap, acc, o);
+            else {
+                float o2[VEC];
+                fast_operand(S.kind2, S.idx2, S.c2, in, tmp, o2);
+#pragma unroll
+                for (int e = 0; e < VEC; e++) acc[e] = acc[e] != 0.f ? o[e] : o2[e];
+            }
+        }
+        if (S.rdt != B200JT_FLOAT32) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) acc[e] = round_to(acc[e], S.rdt);
+        }
+    }
+}
+
+__device__ __forceinline__ void store_fast(const FastProgram& P, int64_t off, int n, const float* v) {
+    store_vec(P.out, P.out_dtype, P.out_vec_ok, off, n, v);
+}
+
+__global__ void __launch_bounds__(256, 2)
+chain_fast_map_kernel(const __grid_constant__ FastProgram P) {
+    const int64_t vpr = (P.cols + VEC - 1) / VEC, items = P.rows * vpr;
+    const bool small = items < (1LL << 31);
+    for (int64_t it = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; it < items; it += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = small ? (int64_t)((uint32_t)it / (uint32_t)vpr) : it / vpr, col = (it - row * vpr) * VEC;
+        const int n = (int)min((int64_t)VEC, P.cols - col);
+        float v[VEC];
+        eval_fast(P, row, col, n, v);
+        store_fast(P, row * P.cols + col, n, v);
+    }
+}
+
+template <int G>
+__global__ void __launch_bounds__(256, 2)
+chain_fast_reduce_kernel(const __grid_constant__ FastProgram P) {
+    __shared__ float xch[8];
+    constexpr int GROUPS = 256 / G;
+    const int g = threadIdx.x / G, t = threadIdx.x % G;
+    const int64_t n_groups = (int64_t)gridDim.x * GROUPS;
+    const float rcols = 1.f / (float)P.cols;
+    const int rop = P.reduce_op;
+    for (int64_t row = (int64_t)blockIdx.x * GROUPS + g; row < P.rows; row += n_groups) {
+        float acc = fold_init(rop);
+        for (int64_t col = (int64_t)t * VEC; col < P.cols; col += (int64_t)G * VEC) {
+            const int n = (int)min((int64_t)VEC, P.cols - col);
+            float v[VEC];
+            eval_fast(P, row, col, n, v);
+            if (rop == OP_MEAN) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) if (e < n) acc += v[e] * rcols;
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) if (e < n) acc = fold(rop, acc, v[e]);
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) acc = fold(rop, acc, __shfl_xor_sync(0xffffffffu, acc, d));
+        if (G == 256) {
+            __syncthreads();
+            if ((threadIdx.x & 31) == 0) xch[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            acc = xch[0];
+#pragma unroll
+            for (int k = 1; k < 8; k++) acc = fold(rop, acc, xch[k]);
+        }
+        if (t == 0) store_as<float>(P.out, P.out_dtype, row, round_to(acc, P.reduce_rdt));
     }
 }
 
@@ -589,6 +738,50 @@ extern "C" int b200jt_fused_chain(const b200jt_tensor* inputs, int n_inputs, con
         }
     }
     cudaStream_t st = (cudaStream_t)stream;
+    // short single-chain programs: pre-decoded steps, static kernel
+    {
+        FastProgram F; memset(&F, 0, sizeof(F));
+        bool ok = n_inputs <= kFastInputs;
+        int ns = 0;
+        F.reduce_op = -1;
+        const int last = w_op(code[n_code - 1]);
+        int end = n_code - 1;                                   // index of the word that ends the (only) chain
+        if (last == CH_STORE_ROW) {
+            end = n_code - 2;
+            ok = ok && end >= 1 && w_op(code[end]) == CH_ROW_REDUCE && w_index(code[end]) == w_index(code[n_code - 1]);
+            if (ok) { F.reduce_op = w_sub(code[end]); F.reduce_rdt = w_rdt(code[end]); }
+        }
+        for (int pc = 0; ok && pc < end; pc++) {
+            const int32_t w = code[pc];
+            const int op = w_op(w);
+            if (op >= CH_ROW_REDUCE || ns >= kFastSteps) { ok = false; break; }
+            FastStep& S = F.step[ns++];
+            S.op = op; S.sub = w_sub(w); S.kind = w_kind(w); S.idx = w_index(w); S.swap = w_swap(w); S.rdt = w_rdt(w);
+            if (S.kind == K_ROWVAL) { ok = false; break; }
+            if (S.kind == K_CONST) memcpy(&S.c, &code[++pc], 4);
+            if (op == CH_SELECT) {
+                const int32_t w2 = code[++pc];
+                S.kind2 = w_kind(w2); S.idx2 = w_index(w2);
+                if (S.kind2 == K_ROWVAL) { ok = false; break; }
+                if (S.kind2 == K_CONST) memcpy(&S.c2, &code[++pc], 4);
+            }
+        }
+        if (ok) {
+            for (int k = 0; k < n_inputs; k++) F.in[k] = Q.in[k];
+            F.n_in = n_inputs; F.n_steps = ns;
+            F.out = Q.out; F.out_dtype = Q.out_dtype; F.out_vec_ok = Q.out_vec_ok; F.rows = Q.rows; F.cols = Q.cols;
+            if (F.reduce_op < 0) {
+                const int64_t items = F.rows * ((F.cols + VEC - 1) / VEC);
+                chain::chain_fast_map_kernel<<<grid_for(items, 256), 256, 0, st>>>(F);
+            } else if (F.cols <= 1024) {
+                chain::chain_fast_reduce_kernel<32><<<grid_for((F.rows + 7) / 8 * 256, 256), 256, 0, st>>>(F);
+            } else {
+                chain::chain_fast_reduce_kernel<256><<<grid_for(F.rows * 256, 256), 256, 0, st>>>(F);
+            }
+            B200JT_LAUNCH_CHECK();
+            return 0;
+        }
+    }
     if (pure_map) {
         const int64_t items = Q.rows * ((Q.cols + VEC - 1) / VEC);
         chain::chain_map_kernel<<<grid_for(items, 256), 256, 0, st>>>(Q);

@@ -299,6 +299,94 @@ static int launch_rows(const T* x, T* y, const float* gamma, const float* beta, 
     return 0;
 }
 
+
+// ---- softmax backward ----------------------------------------------------------------------------------------------
+// dx = y * (dy - sum(y * dy))   for y = softmax(x),      dx = dy - exp(y) * sum(dy)   for y = log_softmax(x),
+// the two reductions of the reference's hand-written backward (python/jittor/other/code_softmax.py:109-147). The row of y
+// and of dy live in registers: one read of each, one write of dx.
+template <typename T, int GROUP, int VPT, bool LOG>
+__global__ void __launch_bounds__(256)
+softmax_bwd_reg_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, int64_t rows, int cols) {
+    constexpr int N = Vec16<T>::N;
+    constexpr int ROWS_PER_CTA = 256 / GROUP;
+    __shared__ float sm[32];
+    const int g = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
+    const int nvec = cols / N;
+    for (int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + g; ; row += (int64_t)gridDim.x * ROWS_PER_CTA) {
+        // the CTA-wide reduction has a barrier inside: rows are taken in rounds the whole CTA goes through together
+        const int64_t round0 = row - g;
+        if (round0 >= rows) break;
+        const bool live = row < rows;
+        float a[VPT][N], b[VPT][N];
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int vi = t + k * GROUP;
+            if (live && vi < nvec) {
+                Vec16<T>::load(y + row * cols + (int64_t)vi * N, a[k]);
+                Vec16<T>::load(dy + row * cols + (int64_t)vi * N, b[k]);
+#pragma unroll
+                for (int e = 0; e < N; e++) s += LOG ? b[k][e] : a[k][e] * b[k][e];
+            }
+        }
+        s = group_reduce<GROUP, false>(s, sm);
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int vi = t + k * GROUP;
+            if (live && vi < nvec) {
+                float o[N];
+#pragma unroll
+                for (int e = 0; e < N; e++) o[e] = LOG ? b[k][e] - expf(a[k][e]) * s : a[k][e] * (b[k][e] - s);
+                Vec16<T>::store(dx + row * cols + (int64_t)vi * N, o);
+            }
+        }
+    }
+}
+
+// any cols / alignment: two sweeps by one CTA per row
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(256)
+softmax_bwd_pass_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, int64_t rows, int64_t cols) {
+    __shared__ float sm[32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T* yr = y + row * cols; const T* dr = dy + row * cols; T* xr = dx + row * cols;
+        float s = 0.f;
+        for (int64_t c = threadIdx.x; c < cols; c += 256) s += LOG ? ld1<T>(dr + c) : ld1<T>(yr + c) * ld1<T>(dr + c);
+        s = group_reduce<256, false>(s, sm);
+        for (int64_t c = threadIdx.x; c < cols; c += 256) {
+            const float a = ld1<T>(yr + c), b = ld1<T>(dr + c);
+            st1<T>(xr + c, LOG ? b - expf(a) * s : a * (b - s));
+        }
+    }
+}
+
+template <typename T, bool LOG>
+static int launch_softmax_bwd(const T* y, const T* dy, T* dx, int64_t rows, int64_t cols, cudaStream_t st) {
+    constexpr int N = Vec16<T>::N;
+    const bool vec_ok = cols % N == 0 && ((uintptr_t)y % 16 == 0) && ((uintptr_t)dy % 16 == 0) && ((uintptr_t)dx % 16 == 0);
+    const int64_t nvec = cols / N;
+#define B200JT_SB(GROUP, VPT)                                                                       \
+    do { const int rpc = 256 / GROUP;                                                               \
+         int64_t ctas = (rows + rpc - 1) / rpc;                                                     \
+         unsigned grid = (unsigned)(ctas < (int64_t)kNumSMs * 16 ? ctas : (int64_t)kNumSMs * 16);   \
+         softmax_bwd_reg_kernel<T, GROUP, VPT, LOG><<<grid, 256, 0, st>>>(y, dy, dx, rows, (int)cols); } while (0)
+    if (vec_ok && nvec <= 32 * 4) {
+        if (nvec <= 32) B200JT_SB(32, 1);
+        else if (nvec <= 64) B200JT_SB(32, 2);
+        else B200JT_SB(32, 4);
+    } else if (vec_ok && nvec <= 256 * 4) {
+        if (nvec <= 256) B200JT_SB(256, 1);
+        else if (nvec <= 512) B200JT_SB(256, 2);
+        else B200JT_SB(256, 4);
+    } else {
+        unsigned grid = (unsigned)(rows < (int64_t)kNumSMs * 16 ? rows : (int64_t)kNumSMs * 16);
+        softmax_bwd_pass_kernel<T, LOG><<<grid, 256, 0, st>>>(y, dy, dx, rows, cols);
+    }
+#undef B200JT_SB
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
 static int rows_cols(const b200jt_tensor* x, const b200jt_tensor* y, int64_t* rows, int64_t* cols) {
     B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(y), "invalid tensor descriptor");
     B200JT_CHECK_ARG(x->dtype == y->dtype && (x->dtype == B200JT_FLOAT32 || x->dtype == B200JT_BFLOAT16),
@@ -325,6 +413,22 @@ extern "C" int b200jt_softmax(const b200jt_tensor* x, const b200jt_tensor* y, in
     }
     return log ? launch_rows<__nv_bfloat16, ROW_LOG_SOFTMAX>((const __nv_bfloat16*)x->ptr, (__nv_bfloat16*)y->ptr, nullptr, nullptr, rows, cols, 0.f, st)
                : launch_rows<__nv_bfloat16, ROW_SOFTMAX>((const __nv_bfloat16*)x->ptr, (__nv_bfloat16*)y->ptr, nullptr, nullptr, rows, cols, 0.f, st);
+}
+
+extern "C" int b200jt_softmax_backward(const b200jt_tensor* y, const b200jt_tensor* dy, const b200jt_tensor* dx, int log, void* stream) {
+    int64_t rows, cols;
+    int rc = rows_cols(y, dx, &rows, &cols);
+    if (rc) return rc;
+    B200JT_CHECK_ARG(valid_tensor(dy) && dy->dtype == y->dtype && numel(dy) == numel(y), "dy must have y's dtype and size");
+    if (rows == 0 || cols == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (y->dtype == B200JT_FLOAT32) {
+        return log ? launch_softmax_bwd<float, true>((const float*)y->ptr, (const float*)dy->ptr, (float*)dx->ptr, rows, cols, st)
+                   : launch_softmax_bwd<float, false>((const float*)y->ptr, (const float*)dy->ptr, (float*)dx->ptr, rows, cols, st);
+    }
+    using B = __nv_bfloat16;
+    return log ? launch_softmax_bwd<B, true>((const B*)y->ptr, (const B*)dy->ptr, (B*)dx->ptr, rows, cols, st)
+               : launch_softmax_bwd<B, false>((const B*)y->ptr, (const B*)dy->ptr, (B*)dx->ptr, rows, cols, st);
 }
 
 extern "C" int b200jt_layer_norm(const b200jt_tensor* x, const b200jt_tensor* gamma, const b200jt_tensor* beta,

@@ -149,6 +149,12 @@ def _op_grad(out, dout, k):
     return None
 
 
+def _grad_inputs(v):
+    """The Vars a gradient flows to from v: its op's inputs, or the single input of a Var with its own backward rule."""
+    vjp = getattr(v, "_vjp", None)
+    return [vjp[0]] if vjp is not None else v._op.inputs
+
+
 def grad(loss, targets, retain_graph=True):
     """d(sum(loss)) / d(target) for every target; a list of Vars (a single Var if `targets` is one)."""
     single = isinstance(targets, V.Var)
@@ -162,7 +168,7 @@ def grad(loss, targets, retain_graph=True):
         if done:
             need = id(v) in tids
             if v._op is not None and not v.is_stop_grad():
-                need = need or any(needs.get(id(i), False) for i in v._op.inputs)
+                need = need or any(needs.get(id(i), False) for i in _grad_inputs(v))
             needs[id(v)] = need
             order.append(v)
             continue
@@ -171,7 +177,7 @@ def grad(loss, targets, retain_graph=True):
         seen.add(id(v))
         stack.append((v, True))
         if v._op is not None and id(v) not in tids and not v.is_stop_grad():     # no gradient flows through stop_grad Vars
-            for i in v._op.inputs:
+            for i in _grad_inputs(v):
                 if id(i) not in seen:
                     stack.append((i, False))
     dmap = {id(loss): V.full(list(loss.shape), 1, loss.dtype if loss.dtype.is_float() else "float32")}
@@ -179,6 +185,15 @@ def grad(loss, targets, retain_graph=True):
         if not needs.get(id(v)) or id(v) not in dmap or v._op is None or id(v) in tids:
             continue
         dout = dmap[id(v)]
+        vjp = getattr(v, "_vjp", None)
+        if vjp is not None:                 # a fused op that brings its own backward: one step from v to its input
+            inp, rule = vjp
+            if needs.get(id(inp)):
+                g = rule(v, dout)
+                if g.dtype != inp.dtype and inp.dtype.is_float():
+                    g = g.cast(inp.dtype)
+                dmap[id(inp)] = dmap[id(inp)] + g if id(inp) in dmap else g
+            continue
         for k, inp in enumerate(v._op.inputs):
             if not needs.get(id(inp)):
                 continue

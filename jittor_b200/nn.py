@@ -143,8 +143,29 @@ def relu(x):
     return V.ternary(x > 0.0, x, 0.0)
 
 
+def _softmax_backward(y, dout, log, cols):
+    """dx from the forward output and the output gradient in one launch (b200jt_softmax_backward): what the reference's
+    CUDA softmax brings as its own backward kernel (python/jittor/other/code_softmax.py:109-147)."""
+    from . import _capi as C
+    dout = to_var(dout)
+    if dout.dtype != y.dtype:
+        dout = dout.cast(y.dtype)
+    if list(dout.shape) != list(y.shape):
+        dout = dout.broadcast(y.shape)
+    rows = y.numel() // cols if cols else 0
+
+    def run(yt, dyt):
+        import torch
+        dx = torch.empty_like(yt)
+        C.check(C.lib.b200jt_softmax_backward(C.desc(yt, [rows, cols]), C.desc(dyt.contiguous(), [rows, cols]), C.desc(dx, [rows, cols]),
+                                              int(log), C.stream_ptr()), "softmax_backward")
+        return dx
+
+    return Var(y.shape, y.dtype, V.Op("custom", [y, dout], fn=run, name="softmax_backward"))
+
+
 def softmax(x, dim=None, log=False):
-    x = to_var(x)
+    x0 = x = to_var(x)
     if dim is None:
         dim = ()
     dtype, x = x.dtype, x._to_float()
@@ -154,7 +175,14 @@ def softmax(x, dim=None, log=False):
     else:
         e = (x - x.max(dim, keepdims=True)).exp()
         ret = e / e.sum(dim, keepdims=True)
-    return ret.cast(dtype)
+    ret = ret.cast(dtype)
+    # over the last axis (or over everything) the backward is one fused kernel, as the forward is
+    whole = dim == () or dim == []
+    last = isinstance(dim, int) and dim % max(x0.ndim, 1) == x0.ndim - 1
+    if (whole or last) and str(dtype) in ("float32", "bfloat16") and x0.numel() > 0 and ret is not x0:
+        cols = x0.numel() if whole else x0.shape[-1]
+        ret._vjp = (x0, lambda y, dout: _softmax_backward(y, dout, log, cols))
+    return ret
 
 
 def log_softmax(x, dim=None):

@@ -53,9 +53,24 @@ def test_reduce_then_broadcast_back_orders_the_statements():
     assert ops(words) == ["LOAD", "RRED", "LOAD", "BIN", "STORE"] and len(inputs) == 1
 
 
+def _softmax_by_hand(x):
+    """The meta-op softmax without nn.softmax's own backward rule, so that jt.grad differentiates the chain itself."""
+    e = (x - x.max(-1, keepdims=True)).exp()
+    return e / e.sum(-1, keepdims=True)
+
+
+def test_nn_softmax_brings_its_own_backward():
+    x, dy = ph([128, 1000]), ph([128, 1000])
+    y = nn.softmax(x, -1)
+    g = jt.grad((y * dy).sum(), x)
+    assert g._op.kind == "custom" and g._op.attrs["name"] == "softmax_backward" and g._op.inputs[0] is y
+    g0 = jt.grad((nn.softmax(x, 0) * dy).sum(), x)                      # not the last axis: plain reverse mode
+    assert g0._op.kind != "custom"
+
+
 def test_softmax_backward_is_one_program():
     x, dy = ph([128, 1000]), ph([128, 1000])
-    g = jt.grad((nn.softmax(x, -1) * dy).sum(), x)
+    g = jt.grad((_softmax_by_hand(x) * dy).sum(), x)
     prog = fusion.build_program(g)
     assert prog is not None
     words, inputs, full, k, _ = prog
@@ -185,7 +200,7 @@ def test_programs_compute_the_right_thing():
 
 
 def test_softmax_backward_program_matches_the_formula():
-    got, (x, dy) = _check_program(lambda X, DY: jt.grad((nn.softmax(X, -1) * DY).sum(), X), [(7, 33), (7, 33)], seed=3)
+    got, (x, dy) = _check_program(lambda X, DY: jt.grad((_softmax_by_hand(X) * DY).sum(), X), [(7, 33), (7, 33)], seed=3)
     e = np.exp(x - x.max(1, keepdims=True))
     y = e / e.sum(1, keepdims=True)
     want = y * (dy - (y * dy).sum(1, keepdims=True))

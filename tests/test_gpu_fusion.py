@@ -85,12 +85,17 @@ def test_centre_and_scale_rows(jt):
     check(unfused, want, False, rtol=1e-4)
 
 
+def _softmax_by_hand(x):
+    e = (x - x.max(-1, keepdims=True)).exp()
+    return e / e.sum(-1, keepdims=True)
+
+
 @pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 1000), (7, 10)])
-def test_softmax_backward_one_launch(jt, rows, cols):
-    from jittor_b200 import nn
+def test_softmax_backward_chain_one_launch(jt, rows, cols):
+    """Reverse mode through a softmax written with meta-ops (no backward rule of its own): five row statements, one launch."""
     rng = np.random.default_rng(rows)
     x, dy = rng.normal(size=(rows, cols)).astype(np.float32), rng.normal(size=(rows, cols)).astype(np.float32)
-    fused, unfused, plans = run_both(jt, lambda X, DY: jt.grad((nn.softmax(X, -1) * DY).sum(), X), [x, dy])
+    fused, unfused, plans = run_both(jt, lambda X, DY: jt.grad((_softmax_by_hand(X) * DY).sum(), X), [x, dy])
     assert plans == 1
     y = ref.softmax(x, -1).astype(np.float64)
     want = (y * (dy - (y * dy).sum(-1, keepdims=True))).astype(np.float32)
@@ -152,3 +157,34 @@ def test_unaligned_and_ragged_rows(jt):
     check(got, (base[3:].reshape(19, 13) + b.numpy()) * 2.0 - 1.0, False)
     got = ((x * x) + 1.0).sum(1).numpy()
     check(got, ((base[3:].reshape(19, 13) ** 2) + 1.0).sum(1), False)
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (33, 1000), (7, 10), (5, 9000), (3, 8)])
+@pytest.mark.parametrize("log", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_nn_softmax_backward_kernel(jt, rows, cols, log, dtype):
+    """nn.softmax / log_softmax over the last axis carry their own backward (one kernel from y and dy, as the reference's CUDA
+    softmax does): against float64 formulas, and against reverse mode through the hand-written chain."""
+    from jittor_b200 import nn
+    rng = np.random.default_rng(rows + cols)
+    x, dy = rng.normal(size=(rows, cols)).astype(np.float32), rng.normal(size=(rows, cols)).astype(np.float32)
+    if dtype == "bfloat16":
+        x, dy = bf16_round(x), bf16_round(dy)
+        X, DY = jt.array(torch.from_numpy(x).bfloat16()), jt.array(torch.from_numpy(dy).bfloat16())
+    else:
+        X, DY = jt.array(x), jt.array(dy)
+    y = nn.softmax(X, -1, log)
+    g = jt.grad((y * DY).sum(), X)
+    assert g._op.kind == "custom"
+    got = g.numpy()
+    xd, dd = x.astype(np.float64), dy.astype(np.float64)
+    e = np.exp(xd - xd.max(-1, keepdims=True))
+    sm = e / e.sum(-1, keepdims=True)
+    want = dd - sm * dd.sum(-1, keepdims=True) if log else sm * (dd - (sm * dd).sum(-1, keepdims=True))
+    if dtype == "bfloat16":
+        check(got, bf16_round(want), False, rtol=3e-2)
+    else:
+        check(got, want.astype(np.float32), False, rtol=1e-5)
+        if not log:
+            by_hand = jt.grad((_softmax_by_hand(X) * DY).sum(), X).numpy()
+            check(got, by_hand, False, rtol=1e-5)
