@@ -597,8 +597,8 @@ class FusedChains:
     description = ("fused element-wise chains on [32768,4096] fp32, one launch each: x*w+b (w, b per column), relu(x+bias), "
                    "(a*b).sum(1), (x-mean)/sqrt(mean(x*x)+eps) (three row statements through the chain interpreter), and the "
                    "backward of nn.softmax (its own kernel from y and dy)")
-    kernel_of = {"scale-shift": "chain_fast_map_kernel", "relu-bias": "chain_fast_map_kernel", "mul-rowsum": "chain_fast_reduce_kernel",
-                 "centre-scale": "chain_rows_kernel", "softmax-bwd": "softmax_bwd_reg_kernel"}
+    kernel_of = {"scale-shift": "chain_jit_map_kernel", "relu-bias": "chain_jit_map_kernel", "mul-rowsum": "chain_jit_rows_kernel",
+                 "centre-scale": "chain_jit_rows_kernel", "softmax-bwd": "softmax_bwd_reg_kernel"}
     launches = {k: 1 for k in kernel_of}
 
     def work(self):

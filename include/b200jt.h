@@ -136,8 +136,12 @@ int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200
 /* Any chain of unary / binary / ternary ops, broadcasts and reduces over the trailing axes as ONE launch, intermediates
  * in registers: the general case of FusedOp::jit_run -- the loop nest OpCompiler stitches from the member ops
  * (python/jittor/src/fused_op.cc:41-118,217-238, python/jittor/src/op_compiler.cc:839-1045; fused reduce + broadcast
- * cases python/jittor/test/test_fused_op.py:144-176). The reference generates and compiles source per graph; here the
- * graph is passed as a small program that one ahead-of-time kernel interprets.
+ * cases python/jittor/test/test_fused_op.py:144-176). The reference generates and compiles a loop nest per graph; here
+ * the graph is passed as a small program, and the kernel that runs it is specialised for that program at first use
+ * (straight-line CUDA generated from the program, compiled for sm_100a with NVRTC, cached per process; constants, shapes,
+ * strides and pointers stay arguments, so one compilation serves every size). Without NVRTC, or with
+ * B200JT_CHAIN_JIT=0, an ahead-of-time kernel interprets the program instead (same results, slower);
+ * B200JT_CHAIN_JIT=2 makes a missing compiler or a failed compilation an error.
  *   inputs      n_inputs (<= 8) tensors, each with the rank of full_shape, size 1 on the axes it is broadcast over;
  *   full_shape  the index space of the element-wise part; its last row_axes axes form a "row" (the axes the program's
  *               reduces fold; 0 when there is no reduce);
@@ -160,6 +164,20 @@ int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200
  *   out         full_shape elements (STORE) or one per row (STORE_ROW). */
 int b200jt_fused_chain(const b200jt_tensor* inputs, int n_inputs, const int64_t* full_shape, int ndim, int row_axes,
                        const int32_t* code, int n_code, const b200jt_tensor* out, void* stream);
+
+/* The CUDA source b200jt_fused_chain would compile for the same arguments, without launching anything (the pointers in
+ * the descriptors are only looked at for their alignment; needs no GPU). Copies at most cap bytes, NUL-terminated, into
+ * src (may be NULL), stores the full length in *needed and sets *compiled to 1 if NVRTC accepted the source for sm_100a
+ * (0, with the compiler's log in b200jt_last_error(), otherwise). The counterpart of reading the reference's generated
+ * op source under its cache directory (python/jittor/src/op_compiler.cc:1046-1060 writes it). */
+int b200jt_fused_chain_source(const b200jt_tensor* inputs, int n_inputs, const int64_t* full_shape, int ndim, int row_axes,
+                              const int32_t* code, int n_code, const b200jt_tensor* out, char* src, int64_t cap,
+                              int64_t* needed, int* compiled);
+
+/* Counters of the chain specialiser since the process started: kernels compiled, launches served from the cache,
+ * compilations that failed (those chains run through the interpreting kernel). Any pointer may be NULL.
+ * No reference counterpart (the reference logs its compilations through LOGvv). */
+int b200jt_chain_jit_stats(int* compiled, int* hits, int* failed);
 
 /* Row softmax / log-softmax over the last axis of x[rows, cols], one read and one write.
  * Replaces the chain of python/jittor/nn.py:527-535 and the inline kernel python/jittor/other/code_softmax.py:42-98.

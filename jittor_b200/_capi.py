@@ -62,6 +62,9 @@ SIGNATURES = [
     ("b200jt_unary", _i, [_TP, _TP, ctypes.c_char_p, _vp]),
     ("b200jt_ternary", _i, [_TP, _TP, _TP, _TP, _vp]),
     ("b200jt_fused_chain", _i, [_TP, _i, ctypes.POINTER(ctypes.c_int64), _i, _i, ctypes.POINTER(ctypes.c_int32), _i, _TP, _vp]),
+    ("b200jt_fused_chain_source", _i, [_TP, _i, ctypes.POINTER(ctypes.c_int64), _i, _i, ctypes.POINTER(ctypes.c_int32), _i, _TP,
+                                       ctypes.c_char_p, ctypes.c_int64, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(_i)]),
+    ("b200jt_chain_jit_stats", _i, [ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     ("b200jt_softmax", _i, [_TP, _TP, _i, _vp]),
     ("b200jt_softmax_backward", _i, [_TP, _TP, _TP, _i, _vp]),
     ("b200jt_layer_norm", _i, [_TP, _TP, _TP, _TP, _d, _vp]),

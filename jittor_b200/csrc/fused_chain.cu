@@ -24,65 +24,10 @@
 // 32-byte access per operand), which amortises the decode.
 #include "atomic_ops.cuh"
 
+#include "fused_chain.cuh"
+
 namespace b200jt {
 namespace chain {
-
-constexpr int kMaxInputs = 8;
-constexpr int kMaxCode = 160;
-constexpr int kMaxRowVals = 8;
-constexpr int kTmp = 3;
-constexpr int VEC = 8;
-
-// word = op | sub << 4 | operand kind << 10 | operand index << 13 | swap << 21 | result dtype << 24
-enum ChainOp : int {
-    CH_OPERAND = 0,     // second operand of the SELECT before it
-    CH_LOAD, CH_UNARY, CH_BINARY, CH_SELECT, CH_TSTORE,
-    CH_ROW_REDUCE = 8,  // sub = reduce op, index = slot : ends a chain, one sweep
-    CH_ROW_MAP,         // index = slot              : ends a chain evaluated once per row
-    CH_STORE,           // ends a chain, one sweep, writes the output
-    CH_STORE_ROW        // index = slot              : out[row] = rowval[slot]
-};
-enum OperandKind : int { K_NONE = 0, K_INPUT, K_CONST /* the float32 in the next word */, K_ROWVAL, K_TMP };
-
-__host__ __device__ __forceinline__ int w_op(int32_t w) { return w & 15; }
-__host__ __device__ __forceinline__ int w_sub(int32_t w) { return (w >> 4) & 63; }
-__host__ __device__ __forceinline__ int w_kind(int32_t w) { return (w >> 10) & 7; }
-__host__ __device__ __forceinline__ int w_index(int32_t w) { return (w >> 13) & 255; }
-__host__ __device__ __forceinline__ int w_swap(int32_t w) { return (w >> 21) & 1; }
-__host__ __device__ __forceinline__ int w_rdt(int32_t w) { return (w >> 24) & 255; }
-
-// unary codes of elementwise.cu (kept in the same order)
-enum UnaryCode : int {
-    U_CAST = 0, U_NEG, U_ABS, U_LNOT, U_BNOT, U_LOG, U_EXP, U_SQRT, U_ROUND, U_FLOOR, U_CEIL,
-    U_SIN, U_ASIN, U_SINH, U_ASINH, U_TAN, U_ATAN, U_TANH, U_ATANH, U_COS, U_ACOS, U_COSH, U_ACOSH,
-    U_SIGMOID, U_ERF, U_ERFINV, U_INVALID
-};
-
-// How an input is addressed from (row, col):
-enum InMode : int {
-    IN_FULL = 0,        // same shape as the full space: offset row*cols + col
-    IN_SCALAR,          // one element
-    IN_COL,             // constant over the rows, complete along the row (bias): offset col
-    IN_ROW,             // constant along the row: one offset per row, from the row index and the strides of the row axes
-    IN_GENERAL          // broadcast over arbitrary axes: strides per merged axis of the full space
-};
-
-struct Input {
-    const void* ptr;
-    int32_t dtype, mode;
-    int32_t vec_ok;                     // 16-byte aligned base and row pitch: vector loads allowed (FULL / COL)
-    int32_t nd;                         // GENERAL: merged axes of the full space; ROW: merged row axes; innermost last
-    int64_t shape[kMaxDims], stride[kMaxDims];
-};
-
-struct Program {
-    int32_t n_inputs, n_code;
-    Input in[kMaxInputs];
-    int32_t code[kMaxCode];
-    void* out;
-    int32_t out_dtype, out_vec_ok;
-    int64_t rows, cols;
-};
 
 __device__ __forceinline__ float round_to(float v, int dt) {
     switch (dt) {
@@ -193,6 +138,9 @@ __device__ __forceinline__ void load_input(const Input& I, int64_t row, int64_t 
             int64_t idx[kMaxDims];
             int64_t r = row * cols + col, off = 0;
             for (int d = I.nd - 1; d >= 0; d--) { idx[d] = r % I.shape[d]; r /= I.shape[d]; off += idx[d] * I.stride[d]; }
+            // fully unrolled: a loop that indexes o[] with a run-time counter would put the caller's register array
+            // (and with it every operand of the chain) into local memory
+#pragma unroll
             for (int e = 0; e < VEC; e++) {
                 o[e] = e < n ? load_as<float>(I.ptr, I.dtype, off) : 0.f;
                 for (int d = I.nd - 1; d >= 0; d--) {
@@ -221,7 +169,9 @@ __device__ __forceinline__ void store_vec(void* out, int out_dtype, int out_vec_
             return;
         }
     }
-    for (int e = 0; e < n; e++) store_as<float>(out, out_dtype, off + e, v[e]);
+#pragma unroll
+    for (int e = 0; e < VEC; e++)
+        if (e < n) store_as<float>(out, out_dtype, off + e, v[e]);
 }
 __device__ __forceinline__ void store_output(const Program& P, int64_t off, int n, const float* v) {
     store_vec(P.out, P.out_dtype, P.out_vec_ok, off, n, v);
@@ -250,7 +200,16 @@ __device__ __forceinline__ void apply_unary(int sub, float (&acc)[VEC]) {
         B200JT_U(U_TANH, tanhf(v));
         B200JT_U(U_SIGMOID, 1.f / (1.f + expf(-v < 30.f ? -v : 30.f)));
 #undef B200JT_U
-        default: rare_unary(sub, acc);
+        default: {
+            // through a copy: handing `acc` itself to a function that is not inlined would pin the accumulator in local
+            // memory for the whole kernel
+            float buf[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; e++) buf[e] = acc[e];
+            rare_unary(sub, buf);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) acc[e] = buf[e];
+        }
     }
 }
 
@@ -275,11 +234,19 @@ __device__ __forceinline__ void apply_binary(int sub, int swap, float (&acc)[VEC
         B200JT_B(OP_EQ, (float)(p == q));
         B200JT_B(OP_NE, (float)(p != q));
 #undef B200JT_B
-        default: rare_binary(sub, acc, o);
+        default: {
+            float ba[VEC], bo[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; e++) { ba[e] = acc[e]; bo[e] = o[e]; }
+            rare_binary(sub, ba, bo);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) acc[e] = ba[e];
+        }
     }
 }
 
-constexpr int kPre = 4;         // input operands of a chain whose loads are issued before the chain is interpreted
+constexpr int kPre = 4;
+static_assert(kPre == 4 && kTmp == 3, "the operand selects below are written out for these sizes");         // input operands of a chain whose loads are issued before the chain is interpreted
 
 // Operand of word w into o[]; advances pc over an inline constant.
 __device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int64_t row, int64_t col, int n, const float* rowval,
@@ -288,22 +255,14 @@ __device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int6
     if (kind == K_INPUT) {
         if (used < n_pre) {
 #pragma unroll
-            for (int k = 0; k < kPre; k++)
-                if (k == used) {
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) o[e] = pre[k][e];
-                }
+            for (int e = 0; e < VEC; e++) o[e] = used == 0 ? pre[0][e] : used == 1 ? pre[1][e] : used == 2 ? pre[2][e] : pre[3][e];
             used++;
         } else load_input(P.in[idx], row, col, P.cols, n, o);
         return;
     }
     if (kind == K_TMP) {
 #pragma unroll
-        for (int t = 0; t < kTmp; t++)
-            if (t == idx) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) o[e] = tmp[t][e];
-            }
+        for (int e = 0; e < VEC; e++) o[e] = idx == 0 ? tmp[0][e] : idx == 1 ? tmp[1][e] : tmp[2][e];
         return;
     }
     const float c = kind == K_CONST ? __int_as_float(P.code[++pc]) : rowval[idx];
@@ -328,8 +287,14 @@ __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row,
         if (kind == K_CONST) q++;
         else if (kind == K_INPUT) {
 #pragma unroll
-            for (int k = 0; k < kPre; k++)
-                if (k == n_pre) load_input(P.in[w_index(w)], row, col, P.cols, n, pre[k]);
+            float t[VEC];
+            load_input(P.in[w_index(w)], row, col, P.cols, n, t);
+#pragma unroll
+            for (int k = 0; k < kPre; k++) {
+                const bool hit = k == n_pre;
+#pragma unroll
+                for (int e = 0; e < VEC; e++) pre[k][e] = hit ? t[e] : pre[k][e];
+            }
             n_pre++;
         }
     }
@@ -341,11 +306,13 @@ __device__ __forceinline__ int eval_chain(const Program& P, int pc, int64_t row,
         if (op == CH_TSTORE) {
             const int idx = w_index(w);
 #pragma unroll
-            for (int t = 0; t < kTmp; t++)
-                if (t == idx) {
+            for (int t = 0; t < kTmp; t++) {
+                // a select on the value, not a store under a condition: stores under conditions on t are merged by the
+                // compiler into one store at a computed address, and that puts the array in local memory
+                const bool hit = t == idx;
 #pragma unroll
-                    for (int e = 0; e < VEC; e++) tmp[t][e] = acc[e];
-                }
+                for (int e = 0; e < VEC; e++) tmp[t][e] = hit ? acc[e] : tmp[t][e];
+            }
             continue;
         }
         if (op == CH_UNARY) {
@@ -464,143 +431,6 @@ chain_rows_kernel(const __grid_constant__ Program P) {
             }
             pc = end + 1;
         }
-    }
-}
-
-// ---- short programs: everything static ---------------------------------------------------------------------------
-// A program that is ONE chain of at most 8 instructions over at most 4 inputs, ending in STORE or in ROW_REDUCE + STORE_ROW,
-// is pre-decoded on the host into a fixed array of steps. The kernel below unrolls over that array, so every field is read
-// with a compile-time offset, the loads of all inputs are issued before the first use, and only the op codes are looked at
-// at run time. This is the path the common chains take (x*w+b, relu(x+bias), (a*b).sum(1)); longer programs run through the
-// interpreter above.
-constexpr int kFastSteps = 8;
-constexpr int kFastInputs = 4;
-
-struct FastStep { int32_t op, sub, kind, idx, swap, rdt, kind2, idx2; float c, c2; };
-struct FastProgram {
-    Input in[kFastInputs];
-    FastStep step[kFastSteps];
-    int32_t n_in, n_steps;
-    int32_t reduce_op, reduce_rdt;       // row reduce after the chain (reduce_op < 0: plain store)
-    void* out;
-    int32_t out_dtype, out_vec_ok;
-    int64_t rows, cols;
-};
-
-__device__ __forceinline__ void fast_operand(int kind, int idx, float c, const float (&in)[kFastInputs][VEC], const float (&tmp)[kTmp][VEC],
-                                             float (&o)[VEC]) {
-    if (kind == K_INPUT) {
-#pragma unroll
-        for (int k = 0; k < kFastInputs; k++)
-            if (k == idx) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) o[e] = in[k][e];
-            }
-    } else if (kind == K_TMP) {
-#pragma unroll
-        for (int k = 0; k < kTmp; k++)
-            if (k == idx) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) o[e] = tmp[k][e];
-            }
-    } else {
-#pragma unroll
-        for (int e = 0; e < VEC; e++) o[e] = c;
-    }
-}
-
-__device__ __forceinline__ void eval_fast(const FastProgram& P, int64_t row, int64_t col, int n, float (&acc)[VEC]) {
-    float in[kFastInputs][VEC] = {};
-#pragma unroll
-    for (int k = 0; k < kFastInputs; k++)
-        if (k < P.n_in) load_input(P.in[k], row, col, P.cols, n, in[k]);
-    float tmp[kTmp][VEC] = {};
-#pragma unroll
-    for (int i = 0; i < kFastSteps; i++) {
-        if (i >= P.n_steps) break;
-        const FastStep& S = P.step[i];
-        if (S.op == CH_TSTORE) {
-#pragma unroll
-            for (int k = 0; k < kTmp; k++)
-                if (k == S.idx) {
-#pragma unroll
-                    for (int e = 0; e < VEC; e++) tmp[k][e] = acc[e];
-                }
-            continue;
-        }
-        if (S.op == CH_UNARY) apply_unary(S.sub, acc);
-        else {
-            float o[VEC];
-            fast_operand(S.kind, S.idx, S.c, in, tmp, o);
-            if (S.op == CH_LOAD) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) acc[e] = o[e];
-            } else if (S.op == CH_BINARY) apply_binary(S.sub, S.swap, acc, o);
-            else {
-                float o2[VEC];
-                fast_operand(S.kind2, S.idx2, S.c2, in, tmp, o2);
-#pragma unroll
-                for (int e = 0; e < VEC; e++) acc[e] = acc[e] != 0.f ? o[e] : o2[e];
-            }
-        }
-        if (S.rdt != B200JT_FLOAT32) {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) acc[e] = round_to(acc[e], S.rdt);
-        }
-    }
-}
-
-__device__ __forceinline__ void store_fast(const FastProgram& P, int64_t off, int n, const float* v) {
-    store_vec(P.out, P.out_dtype, P.out_vec_ok, off, n, v);
-}
-
-__global__ void __launch_bounds__(256, 2)
-chain_fast_map_kernel(const __grid_constant__ FastProgram P) {
-    const int64_t vpr = (P.cols + VEC - 1) / VEC, items = P.rows * vpr;
-    const bool small = items < (1LL << 31);
-    for (int64_t it = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; it < items; it += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = small ? (int64_t)((uint32_t)it / (uint32_t)vpr) : it / vpr, col = (it - row * vpr) * VEC;
-        const int n = (int)min((int64_t)VEC, P.cols - col);
-        float v[VEC];
-        eval_fast(P, row, col, n, v);
-        store_fast(P, row * P.cols + col, n, v);
-    }
-}
-
-template <int G>
-__global__ void __launch_bounds__(256, 2)
-chain_fast_reduce_kernel(const __grid_constant__ FastProgram P) {
-    __shared__ float xch[8];
-    constexpr int GROUPS = 256 / G;
-    const int g = threadIdx.x / G, t = threadIdx.x % G;
-    const int64_t n_groups = (int64_t)gridDim.x * GROUPS;
-    const float rcols = 1.f / (float)P.cols;
-    const int rop = P.reduce_op;
-    for (int64_t row = (int64_t)blockIdx.x * GROUPS + g; row < P.rows; row += n_groups) {
-        float acc = fold_init(rop);
-        for (int64_t col = (int64_t)t * VEC; col < P.cols; col += (int64_t)G * VEC) {
-            const int n = (int)min((int64_t)VEC, P.cols - col);
-            float v[VEC];
-            eval_fast(P, row, col, n, v);
-            if (rop == OP_MEAN) {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) if (e < n) acc += v[e] * rcols;
-            } else {
-#pragma unroll
-                for (int e = 0; e < VEC; e++) if (e < n) acc = fold(rop, acc, v[e]);
-            }
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) acc = fold(rop, acc, __shfl_xor_sync(0xffffffffu, acc, d));
-        if (G == 256) {
-            __syncthreads();
-            if ((threadIdx.x & 31) == 0) xch[threadIdx.x >> 5] = acc;
-            __syncthreads();
-            acc = xch[0];
-#pragma unroll
-            for (int k = 1; k < 8; k++) acc = fold(rop, acc, xch[k]);
-        }
-        if (t == 0) store_as<float>(P.out, P.out_dtype, row, round_to(acc, P.reduce_rdt));
     }
 }
 
@@ -738,49 +568,10 @@ extern "C" int b200jt_fused_chain(const b200jt_tensor* inputs, int n_inputs, con
         }
     }
     cudaStream_t st = (cudaStream_t)stream;
-    // short single-chain programs: pre-decoded steps, static kernel
+    // a kernel compiled for exactly this program, when the run-time compiler is there; the interpreter otherwise
     {
-        FastProgram F; memset(&F, 0, sizeof(F));
-        bool ok = n_inputs <= kFastInputs;
-        int ns = 0;
-        F.reduce_op = -1;
-        const int last = w_op(code[n_code - 1]);
-        int end = n_code - 1;                                   // index of the word that ends the (only) chain
-        if (last == CH_STORE_ROW) {
-            end = n_code - 2;
-            ok = ok && end >= 1 && w_op(code[end]) == CH_ROW_REDUCE && w_index(code[end]) == w_index(code[n_code - 1]);
-            if (ok) { F.reduce_op = w_sub(code[end]); F.reduce_rdt = w_rdt(code[end]); }
-        }
-        for (int pc = 0; ok && pc < end; pc++) {
-            const int32_t w = code[pc];
-            const int op = w_op(w);
-            if (op >= CH_ROW_REDUCE || ns >= kFastSteps) { ok = false; break; }
-            FastStep& S = F.step[ns++];
-            S.op = op; S.sub = w_sub(w); S.kind = w_kind(w); S.idx = w_index(w); S.swap = w_swap(w); S.rdt = w_rdt(w);
-            if (S.kind == K_ROWVAL) { ok = false; break; }
-            if (S.kind == K_CONST) memcpy(&S.c, &code[++pc], 4);
-            if (op == CH_SELECT) {
-                const int32_t w2 = code[++pc];
-                S.kind2 = w_kind(w2); S.idx2 = w_index(w2);
-                if (S.kind2 == K_ROWVAL) { ok = false; break; }
-                if (S.kind2 == K_CONST) memcpy(&S.c2, &code[++pc], 4);
-            }
-        }
-        if (ok) {
-            for (int k = 0; k < n_inputs; k++) F.in[k] = Q.in[k];
-            F.n_in = n_inputs; F.n_steps = ns;
-            F.out = Q.out; F.out_dtype = Q.out_dtype; F.out_vec_ok = Q.out_vec_ok; F.rows = Q.rows; F.cols = Q.cols;
-            if (F.reduce_op < 0) {
-                const int64_t items = F.rows * ((F.cols + VEC - 1) / VEC);
-                chain::chain_fast_map_kernel<<<grid_for(items, 256), 256, 0, st>>>(F);
-            } else if (F.cols <= 1024) {
-                chain::chain_fast_reduce_kernel<32><<<grid_for((F.rows + 7) / 8 * 256, 256), 256, 0, st>>>(F);
-            } else {
-                chain::chain_fast_reduce_kernel<256><<<grid_for(F.rows * 256, 256), 256, 0, st>>>(F);
-            }
-            B200JT_LAUNCH_CHECK();
-            return 0;
-        }
+        const int r = chain::jit_launch(Q, pure_map, pure_map && all_flat, st);
+        if (r != chain::kJitUnavailable) return r;
     }
     if (pure_map) {
         const int64_t items = Q.rows * ((Q.cols + VEC - 1) / VEC);

@@ -435,3 +435,33 @@ def run_program(words, inputs, full, k, out):
     C.check(C.lib.b200jt_fused_chain(descs, n, shp, len(full), k, code, len(words), C.desc(out), C.stream_ptr()),
             f"fused chain over {full} ({len(words)} words, {n} inputs)")
     return out
+
+
+def program_source(words, inputs, full, k, out_shape, out_dtype="float32"):
+    """The CUDA source the library generates for a program, and whether NVRTC accepts it for sm_100a: needs no GPU, nothing
+    is launched. inputs: (var, view) pairs as build_program returns them (only dtype and view are used).
+    Returns (source, compiled, log)."""
+    n = len(inputs)
+    descs = (C.Tensor * max(n, 1))()
+
+    def fake(i, dtype, shape):
+        d = C.Tensor()
+        d.ptr = 0x10000 * (i + 1)                  # never dereferenced: only the alignment is looked at
+        d.dtype = C.DTYPE_CODES[str(dtype)]
+        d.ndim = max(len(shape), 1)
+        for j, e in enumerate(list(shape) or [1]):
+            d.shape[j] = int(e)
+        return d
+    for i, (var, view) in enumerate(inputs):
+        descs[i] = fake(i, var.dtype, view)
+    out = fake(n, out_dtype, out_shape)
+    shp = (ctypes.c_int64 * len(full))(*full)
+    code = (ctypes.c_int32 * len(words))(*words)
+    cap = 1 << 18
+    buf = ctypes.create_string_buffer(cap)
+    needed, ok = ctypes.c_int64(0), ctypes.c_int(0)
+    C.check(C.lib.b200jt_fused_chain_source(descs, n, shp, len(full), k, code, len(words), ctypes.byref(out), buf, cap,
+                                            ctypes.byref(needed), ctypes.byref(ok)),
+            f"fused chain source over {full}")
+    log = "" if ok.value else C.lib.b200jt_last_error().decode()
+    return buf.value.decode(), bool(ok.value), log

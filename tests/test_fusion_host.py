@@ -205,3 +205,30 @@ def test_softmax_backward_program_matches_the_formula():
     y = e / e.sum(1, keepdims=True)
     want = y * (dy - (y * dy).sum(1, keepdims=True))
     assert np.allclose(got, want, rtol=1e-4, atol=1e-6)
+
+
+def test_generated_sources_compile_for_sm_100a():
+    """Every kind of program goes through the generator and NVRTC (no GPU involved): map with column / row / general
+    broadcasts, flat maps with a ragged tail, rows kernels of both group widths, bf16 and fp16 nodes, select."""
+    cases = [
+        lambda: ph([64, 4096]) * ph([4096]) + ph([4096]),
+        lambda: nn.relu(ph([64, 4096]) + ph([4096])),
+        lambda: (ph([7, 33]) * 2.0 + 1.0).exp(),
+        lambda: ph([4, 1, 8]) * ph([1, 5, 8]) + ph([4, 5, 1]),
+        lambda: ph([6, 16]) * ph([6, 1]) - ph([1]),
+        lambda: (ph([64, 4096]) * ph([64, 4096])).sum(1),
+        lambda: (ph([64, 100]) * ph([64, 100])).reduce("maximum", 1),
+        lambda: (lambda X: (X - X.mean(1, keepdims=True)) / ((X * X).mean(1, keepdims=True) + 1e-5).sqrt())(ph([5, 24])),
+        lambda: (lambda X: (X - X.mean(1, keepdims=True)) / ((X * X).mean(1, keepdims=True) + 1e-5).sqrt())(ph([5, 2400])),
+        lambda: nn.relu(ph([64, 4096], "bfloat16") * ph([4096], "bfloat16")),
+        lambda: (ph([64, 40], "float16") + ph([40], "float16")).sigmoid(),
+        lambda: (ph([7, 33]).tanh() % 0.7) ** 2.0,
+    ]
+    for i, f in enumerate(cases):
+        v = f()
+        prog = fusion.build_program(v)
+        assert prog is not None, i
+        words, inputs, full, k, _ = prog
+        src, ok, log = fusion.program_source(words, inputs, full, k, list(v.shape), v.dtype)
+        assert ok, (i, log)
+        assert ("chain_jit_map_kernel" in src) != ("chain_jit_rows_kernel" in src)

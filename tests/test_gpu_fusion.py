@@ -1,6 +1,7 @@
-"""GPU parity of the fused-chain kernel (csrc/fused_chain.cu, fusion.py): every case is computed three ways -- fused
-(one launch, asserted through the executor's plan counter), op by op with fusion switched off, and by the CPU oracle's
-element-wise / reduce restatements. Fused and unfused results must be the same bits for element-wise chains (both round
+"""GPU parity of the fused-chain kernels (csrc/chain_jit.cu, csrc/fused_chain.cu, fusion.py): every case is computed four
+ways -- fused through the kernel compiled for the chain (one launch, asserted through the executor's plan counter; a
+failed compilation is an error here), fused through the interpreting kernel (must be the same bits), op by op with fusion
+switched off, and by the CPU oracle's element-wise / reduce restatements. Fused and unfused results must be the same bits for element-wise chains (both round
 every intermediate to its dtype); reductions and the oracle are compared with the fp32 1e-5 (bf16 2e-2) mixed tolerance."""
 import numpy as np
 import pytest
@@ -28,10 +29,22 @@ def run_both(jt, build, arrays):
     vs = [jt.array(a) for a in arrays]
     for v in vs:
         v.sync()
-    out = build(*vs)
-    before = executor.counters["plans"]
-    fused = out.numpy()
-    plans = executor.counters["plans"] - before
+    import os
+    saved = os.environ.get("B200JT_CHAIN_JIT")
+    try:
+        os.environ["B200JT_CHAIN_JIT"] = "2"            # the compiled kernel, or an error
+        out = build(*vs)
+        before = executor.counters["plans"]
+        fused = out.numpy()
+        plans = executor.counters["plans"] - before
+        os.environ["B200JT_CHAIN_JIT"] = "0"            # the interpreting kernel
+        interpreted = build(*vs).numpy()
+    finally:
+        if saved is None:
+            os.environ.pop("B200JT_CHAIN_JIT", None)
+        else:
+            os.environ["B200JT_CHAIN_JIT"] = saved
+    assert np.array_equal(fused, interpreted, equal_nan=True), "compiled and interpreted chains differ"
     with jt.flag_scope(b200_fuse_chains=0):
         unfused = build(*vs).numpy()
     return fused, unfused, plans
@@ -188,3 +201,21 @@ def test_nn_softmax_backward_kernel(jt, rows, cols, log, dtype):
         if not log:
             by_hand = jt.grad((_softmax_by_hand(X) * DY).sum(), X).numpy()
             check(got, by_hand, False, rtol=1e-5)
+
+
+def test_compiled_kernels_are_cached_per_program_not_per_size_or_constant(jt):
+    import ctypes
+    from jittor_b200 import _capi as C
+
+    def stats():
+        c, h, f = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        C.check(C.lib.b200jt_chain_jit_stats(ctypes.byref(c), ctypes.byref(h), ctypes.byref(f)), "stats")
+        return c.value, h.value, f.value
+    rng = np.random.default_rng(5)
+    c0, h0, f0 = stats()
+    for rows, k in ((64, 0.25), (128, 0.5), (256, 3.0)):
+        x = rng.normal(size=(rows, 512)).astype(np.float32)
+        got = ((jt.array(x) * k + 1.0).exp() * 2.0).numpy()
+        check(got, np.exp(x * np.float32(k) + 1) * 2, False)
+    c1, h1, f1 = stats()
+    assert f1 == f0 and c1 - c0 <= 1 and h1 - h0 >= 2
