@@ -71,7 +71,6 @@ const char* kPrelude = R"SRC(
 typedef long long i64;
 typedef unsigned short u16;
 typedef unsigned char u8;
-#define VEC 8
 #define FOR8 _Pragma("unroll") for (int e = 0; e < VEC; e++)
 #define FLT_MAX 3.402823466e+38f
 struct Input { const void* ptr; int dtype, mode, vec_ok, nd; i64 shape[MAXD], stride[MAXD]; };
@@ -126,17 +125,20 @@ template <int ND> __device__ __forceinline__ i64 row_offset(const Input& I, i64 
 // VEC consecutive elements starting at flat offset `off`; WHOLE: all VEC are inside the row
 template <int DT, int VOK, int WHOLE> __device__ __forceinline__ void ld_vec(const void* p, i64 off, int n, float (&o)[VEC]) {
     if (VOK && (WHOLE || n == VEC)) {
-        if (DT == 8) {
-            const float4 a = __ldg((const float4*)((const float*)p + off));
-            const float4 b = __ldg((const float4*)((const float*)p + off) + 1);
-            o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+        if (DT == 8) {                  // 16 bytes per access: one (VEC 4) or two (VEC 8)
+#pragma unroll
+            for (int h = 0; h < VEC / 4; h++) {
+                const float4 a = __ldg((const float4*)((const float*)p + off) + h);
+                o[4 * h] = a.x; o[4 * h + 1] = a.y; o[4 * h + 2] = a.z; o[4 * h + 3] = a.w;
+            }
             return;
         }
-        if (DT == 7 || DT == 6) {
-            const uint4 v = __ldg((const uint4*)((const u16*)p + off));
-            const unsigned w[4] = {v.x, v.y, v.z, v.w};
+        if (DT == 7 || DT == 6) {       // 16 bytes (VEC 8) or 8 bytes (VEC 4)
+            unsigned w[VEC / 2];
+            if (VEC == 8) { const uint4 v = __ldg((const uint4*)((const u16*)p + off)); w[0] = v.x; w[1] = v.y; w[VEC / 2 - 2] = v.z; w[VEC / 2 - 1] = v.w; }
+            else { const uint2 v = __ldg((const uint2*)((const u16*)p + off)); w[0] = v.x; w[1] = v.y; }
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int i = 0; i < VEC / 2; i++) {
                 const u16 lo = (u16)(w[i] & 0xffffu), hi = (u16)(w[i] >> 16);
                 o[2 * i] = DT == 7 ? bf2f(lo) : h2f(lo);
                 o[2 * i + 1] = DT == 7 ? bf2f(hi) : h2f(hi);
@@ -170,19 +172,20 @@ template <int DT, int ND, int WHOLE> __device__ __forceinline__ void ld_general(
 template <int DT, int VOK, int WHOLE> __device__ __forceinline__ void st_vec(void* p, i64 off, int n, const float (&v)[VEC]) {
     if (VOK && (WHOLE || n == VEC)) {
         if (DT == 8) {
-            float4* q = (float4*)((float*)p + off);
-            __stcs(q, make_float4(v[0], v[1], v[2], v[3]));
-            __stcs(q + 1, make_float4(v[4], v[5], v[6], v[7]));
+#pragma unroll
+            for (int h = 0; h < VEC / 4; h++)
+                __stcs((float4*)((float*)p + off) + h, make_float4(v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]));
             return;
         }
         if (DT == 7 || DT == 6) {
-            unsigned w[4];
+            unsigned w[VEC / 2];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int i = 0; i < VEC / 2; i++) {
                 const u16 lo = DT == 7 ? f2bf(v[2 * i]) : f2h(v[2 * i]), hi = DT == 7 ? f2bf(v[2 * i + 1]) : f2h(v[2 * i + 1]);
                 w[i] = (unsigned)lo | ((unsigned)hi << 16);
             }
-            __stcs((uint4*)((u16*)p + off), make_uint4(w[0], w[1], w[2], w[3]));
+            if (VEC == 8) __stcs((uint4*)((u16*)p + off), make_uint4(w[0], w[1], w[VEC / 2 - 2], w[VEC / 2 - 1]));
+            else __stcs((uint2*)((u16*)p + off), make_uint2(w[0], w[1]));
             return;
         }
     }
@@ -194,7 +197,11 @@ struct Gen {
     const Program& Q;
     bool map, flat, whole;
     int G;
+    int V;                              // elements per thread and step: 4 when every streamed tensor has 4-byte elements, else 8
+    int variant;                        // map: 1 = a thread keeps its columns and walks the rows; rows: vectors of a row a thread keeps in registers (0: none)
     std::string s;
+    bool held[kMaxInputs] = {};         // inputs whose vector is already in registers when a chain starts (not loaded by it)
+    int cur_j = -1;                     // rows kernel with kept rows: which of the thread's vectors the chain works on
 
     void add(const std::string& t) { s += t; }
     static std::string num(long long v) { return std::to_string(v); }
@@ -277,6 +284,7 @@ struct Gen {
             case K_INPUT:
                 if (in(idx).mode == IN_SCALAR) return "s" + num(idx);
                 if (in(idx).mode == IN_ROW) return "r" + num(idx);
+                if (held[idx] && cur_j >= 0) return "x" + num(idx) + "_" + num(cur_j) + "[e]";
                 return "i" + num(idx) + "[e]";
             case K_CONST: return "c" + num(++pc);      // the value stays an argument: one kernel for every constant
             case K_ROWVAL: return "rv" + num(idx);
@@ -285,15 +293,15 @@ struct Gen {
     }
 
     // the load of input k at (row, col) into float i<k>[VEC]
-    void load(int k, const std::string& ind) {
+    void load(int k, const std::string& ind, const std::string& dst = "", bool declare = true) {
         const Input& I = in(k);
-        const std::string K = num(k), W = whole ? "1" : "0";
-        add(ind + "float i" + K + "[VEC];\n");
+        const std::string K = num(k), W = whole ? "1" : "0", D = dst.empty() ? "i" + K : dst;
+        if (declare) add(ind + "float " + D + "[VEC];\n");
         if (I.mode == IN_GENERAL)
-            add(ind + "ld_general<" + num(I.dtype) + ", " + num(I.nd) + ", " + W + ">(P.in[" + K + "], " + (flat ? "off" : "row * cols + col") + ", n, i" + K + ");\n");
+            add(ind + "ld_general<" + num(I.dtype) + ", " + num(I.nd) + ", " + W + ">(P.in[" + K + "], " + (flat ? "off" : "row * cols + col") + ", n, " + D + ");\n");
         else
             add(ind + "ld_vec<" + num(I.dtype) + ", " + num(I.vec_ok ? 1 : 0) + ", " + W + ">(P.in[" + K + "].ptr, " +
-                (I.mode == IN_FULL ? (flat ? "off" : "row * cols + col") : "col") + ", n, i" + K + ");\n");
+                (I.mode == IN_FULL ? (flat ? "off" : "row * cols + col") : "col") + ", n, " + D + ");\n");
     }
 
     // the chain that starts at code[pc]: leaves its value in acc[] and returns the pc of the statement word that ends it
@@ -307,7 +315,7 @@ struct Gen {
             const int kind = w_kind(w), idx = w_index(w);
             if (w_op(w) == CH_TSTORE) { tmp_used[idx] = true; continue; }
             if (kind == K_CONST) q++;
-            else if (kind == K_INPUT && per_element(idx) && !seen[idx]) { seen[idx] = true; load(idx, ind); }
+            else if (kind == K_INPUT && per_element(idx) && !seen[idx]) { seen[idx] = true; if (!held[idx]) load(idx, ind); }
             else if (kind == K_TMP) tmp_used[idx] = true;
         }
         for (int t = 0; t < kTmp; t++)
@@ -358,7 +366,7 @@ struct Gen {
 
     void header() {
         add("#define MAXD " + num(kMaxDims) + "\n#define MAXIN " + num(kMaxInputs) + "\n#define MAXCODE " + num(kMaxCode) +
-            "\n#define PROGRAM_BYTES " + num((long long)sizeof(Program)) + "\n");
+            "\n#define PROGRAM_BYTES " + num((long long)sizeof(Program)) + "\n#define VEC " + num(V) + "\n");
         add(kPrelude);
     }
 
@@ -375,6 +383,23 @@ struct Gen {
             add(std::string("        const int n = ") + (whole ? "VEC" : "(total - off < VEC ? (int)(total - off) : VEC)") + ";\n");
             chain(0, "        ");
             add("        " + store("off"));
+            add("    }\n}\n");
+            return;
+        }
+        if (variant == 1) {
+            // inputs that are constant over the rows (bias, scale): a thread keeps its 8 columns, loads those inputs once
+            // and walks down the rows, so the loop has no division and only the full-shape inputs touch memory
+            add("    const i64 vpr = (cols + VEC - 1) / VEC;\n");
+            add("    const i64 cv = (i64)blockIdx.x * blockDim.x + threadIdx.x;\n");
+            add("    if (cv >= vpr) return;\n");
+            add("    const i64 col = cv * VEC;\n");
+            add(std::string("    const int n = ") + (whole ? "VEC" : "(cols - col < VEC ? (int)(cols - col) : VEC)") + ";\n");
+            for (int k = 0; k < Q.n_inputs; k++)
+                if (in(k).mode == IN_COL) { load(k, "    "); held[k] = true; }
+            add("    for (i64 row = (i64)blockIdx.y * blockDim.y + threadIdx.y; row < P.rows; row += (i64)gridDim.y * blockDim.y) {\n");
+            row_inputs("        ");
+            chain(0, "        ");
+            add("        " + store("row * cols + col"));
             add("    }\n}\n");
             return;
         }
@@ -400,8 +425,40 @@ struct Gen {
         add("    const float rcols = 1.f / (float)cols;\n");
         scalars();
         // the trip count is the same for every thread of a CTA, so the barriers inside the loop are legal for G == 256
+        // rows short enough to keep: every full-shape or column input of a sweep is read once per row (column inputs once per
+        // thread) into registers, and the later sweeps work from there instead of going back to L1 / L2
+        bool swept[kMaxInputs] = {};
+        if (variant > 0) {
+            for (int pc = 0; pc < Q.n_code;) {
+                int end = pc;
+                while (w_op(Q.code[end]) < CH_ROW_REDUCE) end += (w_kind(Q.code[end]) == K_CONST) ? 2 : 1;
+                const int sop = w_op(Q.code[end]);
+                if (sop == CH_ROW_REDUCE || sop == CH_STORE)
+                    for (int q = pc; q < end; q++) {
+                        const int32_t w = Q.code[q];
+                        if (w_kind(w) == K_CONST) { q++; continue; }
+                        if (w_op(w) != CH_TSTORE && w_kind(w) == K_INPUT && (in(w_index(w)).mode == IN_FULL || in(w_index(w)).mode == IN_COL)) swept[w_index(w)] = true;
+                    }
+                pc = end + 1;
+            }
+        }
+        auto keep = [&](int mode, const std::string& ind) {
+            for (int k = 0; k < Q.n_inputs; k++)
+                if (swept[k] && in(k).mode == mode)
+                    for (int j = 0; j < variant; j++) {
+                        const std::string D = "x" + num(k) + "_" + num(j);
+                        add(ind + "float " + D + "[VEC];\n");
+                        add(ind + "{ const i64 col = ((i64)t + " + num(j) + " * G) * VEC; if (col < cols) { " +
+                            std::string("const int n = ") + (whole ? "VEC" : "(cols - col < VEC ? (int)(cols - col) : VEC)") + ";\n");
+                        load(k, ind + "    ", D, false);
+                        add(ind + "} else { FOR8 " + D + "[e] = 0.f; } }\n");
+                        held[k] = true;
+                    }
+        };
+        keep(IN_COL, "    ");
         add("    for (i64 row = (i64)blockIdx.x * GROUPS + g; row < P.rows; row += n_groups) {\n");
         row_inputs("        ");
+        keep(IN_FULL, "        ");
         bool rv_used[kMaxRowVals] = {};
         for (int pc = 0; pc < Q.n_code; pc++) {
             const int32_t w = Q.code[pc];
@@ -423,19 +480,29 @@ struct Gen {
                 // evaluated once per row by every thread of the group, at column 0
                 add("        {\n            const i64 col = 0; const int n = 1;\n");
                 const bool w0 = whole; whole = false;
+                bool h0[kMaxInputs];
+                for (int k = 0; k < kMaxInputs; k++) { h0[k] = held[k]; held[k] = false; }
                 chain(pc, "            ");
+                for (int k = 0; k < kMaxInputs; k++) held[k] = h0[k];
                 whole = w0;
                 add("            rv" + num(a) + " = acc[0];\n        }\n");
             } else {
                 add("        {\n");
                 if (sop == CH_ROW_REDUCE) add(std::string("            float racc = ") + fold_init(rop) + ";\n");
-                add("            for (i64 col = (i64)t * VEC; col < cols; col += (i64)G * VEC) {\n");
-                add(std::string("                const int n = ") + (whole ? "VEC" : "(cols - col < VEC ? (int)(cols - col) : VEC)") + ";\n");
-                chain(pc, "                ");
-                if (sop == CH_STORE) add("                " + store("row * cols + col"));
-                else if (rop == OP_MEAN) add(std::string("                FOR8 if (") + (whole ? "true" : "e < n") + ") racc = fmaf(acc[e], rcols, racc);\n");
-                else add(std::string("                FOR8 if (") + (whole ? "true" : "e < n") + ") { const float a = racc, b = acc[e]; racc = " + fold_expr(rop) + "; }\n");
-                add("            }\n");
+                // with kept rows the sweep is written out per vector of the thread (same order as the loop, same bits)
+                for (int j = 0; j < (variant > 0 ? variant : 1); j++) {
+                    if (variant > 0) {
+                        cur_j = j;
+                        add("            { const i64 col = ((i64)t + " + num(j) + " * G) * VEC; if (col < cols) {\n");
+                    } else add("            for (i64 col = (i64)t * VEC; col < cols; col += (i64)G * VEC) {\n");
+                    add(std::string("                const int n = ") + (whole ? "VEC" : "(cols - col < VEC ? (int)(cols - col) : VEC)") + ";\n");
+                    chain(pc, "                ");
+                    if (sop == CH_STORE) add("                " + store("row * cols + col"));
+                    else if (rop == OP_MEAN) add(std::string("                FOR8 if (") + (whole ? "true" : "e < n") + ") racc = fmaf(acc[e], rcols, racc);\n");
+                    else add(std::string("                FOR8 if (") + (whole ? "true" : "e < n") + ") { const float a = racc, b = acc[e]; racc = " + fold_expr(rop) + "; }\n");
+                    add(variant > 0 ? "            } }\n" : "            }\n");
+                }
+                cur_j = -1;
                 if (sop == CH_ROW_REDUCE) {
                     add(std::string("#pragma unroll\n            for (int d = 16; d > 0; d >>= 1) { const float a = racc, b = __shfl_xor_sync(0xffffffffu, racc, d); racc = ") + fold_expr(rop) + "; }\n");
                     if (G == 256) {
@@ -461,10 +528,13 @@ std::unordered_map<std::string, Compiled> g_cache;
 std::atomic<int> g_compiled{0}, g_hits{0}, g_failed{0};
 std::string g_last_log;
 
-std::string make_key(const Program& Q, bool map, bool flat, bool whole, int G) {
+// The form of the kernel a program gets; everything here is part of the cache key.
+struct Form { int V, G, variant; bool whole; };
+
+std::string make_key(const Program& Q, bool map, bool flat, const Form& f) {
     std::string k;
     k.reserve(64 + 4 * Q.n_code);
-    const int32_t head[8] = {Q.n_inputs, Q.n_code, Q.out_dtype, Q.out_vec_ok, map, flat, whole, G};
+    const int32_t head[10] = {Q.n_inputs, Q.n_code, Q.out_dtype, Q.out_vec_ok, map, flat, f.whole, f.G, f.variant, f.V};
     k.append((const char*)head, sizeof head);
     for (int pc = 0; pc < Q.n_code; pc++) {
         const int32_t w = Q.code[pc];
@@ -513,27 +583,70 @@ int jit_mode() {
 
 }  // namespace
 
-// The CUDA source that jit_launch would compile for Q (for tests and for reading).
-std::string jit_source(const Program& Q, bool pure_map, bool flat) {
-    const bool whole = flat ? (Q.rows * Q.cols) % VEC == 0 : Q.cols % VEC == 0;
-    Gen g{Q, pure_map, flat, whole, Q.cols <= 1024 ? 32 : 256, {}};
+static Form pick_form(const Program& Q, bool pure_map, bool flat) {
+    Form f;
+    // 16 bytes per thread and access: 4 elements when every tensor that is streamed has 4-byte elements, else 8
+    bool narrow = dtype_size(Q.out_dtype) < 4;
+    for (int k = 0; k < Q.n_inputs; k++)
+        if (Q.in[k].mode == IN_FULL || Q.in[k].mode == IN_COL || Q.in[k].mode == IN_GENERAL) narrow |= dtype_size(Q.in[k].dtype) < 4;
+    f.V = narrow ? 8 : 4;
+    f.whole = flat ? (Q.rows * Q.cols) % f.V == 0 : Q.cols % f.V == 0;
+    f.G = Q.cols <= 128 * f.V ? 32 : 256;
+    if (pure_map) {
+        // column-keeping map: some input is constant over the rows and the rows are long enough to fill a CTA's x extent
+        bool col_input = false;
+        for (int k = 0; k < Q.n_inputs; k++) col_input |= Q.in[k].mode == IN_COL;
+        f.variant = (!flat && col_input && Q.cols >= 8 * f.V && Q.rows >= 64) ? 1 : 0;
+        f.G = 0;
+        return f;
+    }
+    // rows kernel: keep the row when all kept vectors of a thread fit in 64 registers
+    const int64_t per_thread = (Q.cols + (int64_t)f.G * f.V - 1) / ((int64_t)f.G * f.V);
+    int inputs = 0;
+    for (int k = 0; k < Q.n_inputs; k++) inputs += Q.in[k].mode == IN_FULL || Q.in[k].mode == IN_COL;
+    f.variant = (per_thread >= 1 && inputs > 0 && per_thread * inputs * f.V <= 64) ? (int)per_thread : 0;
+    return f;
+}
+
+// Vector accesses need the base and every row start on a multiple of the access size.
+static void set_vector_flags(Program& Q, bool flat, int V) {
+    auto ok = [&](const void* p, int dt, bool per_row) {
+        const int es = dtype_size(dt);
+        if (es != 4 && es != 2) return false;
+        const uintptr_t access = (uintptr_t)std::min(16, V * es);
+        if ((uintptr_t)p % access != 0) return false;
+        return flat || !per_row || Q.cols % V == 0 || Q.rows == 1;
+    };
+    for (int k = 0; k < Q.n_inputs; k++) {
+        Input& I = Q.in[k];
+        I.vec_ok = (I.mode == IN_FULL && ok(I.ptr, I.dtype, true)) || (I.mode == IN_COL && ok(I.ptr, I.dtype, false) && Q.cols % V == 0);
+    }
+    Q.out_vec_ok = ok(Q.out, Q.out_dtype, true);
+}
+
+static std::string source_for(const Program& Q, bool pure_map, bool flat, const Form& f) {
+    Gen g{Q, pure_map, flat, f.whole, f.G ? f.G : 256, f.V, f.variant, {}};
     if (pure_map) g.gen_map(); else g.gen_rows();
     return g.s;
+}
+
+// The CUDA source that jit_launch would compile for Q (for tests and for reading).
+std::string jit_source(const Program& Q0, bool pure_map, bool flat) {
+    Program Q = Q0;
+    const Form f = pick_form(Q, pure_map, flat);
+    set_vector_flags(Q, flat, f.V);
+    return source_for(Q, pure_map, flat, f);
 }
 
 thread_local DryRun* t_dry_run = nullptr;
 
 int jit_launch(const Program& Q0, bool pure_map, bool flat, cudaStream_t st) {
     Program Q = Q0;
-    if (flat) {
-        // offsets are multiples of VEC elements whatever the row length, so whole vectors only need an aligned base
-        for (int k = 0; k < Q.n_inputs; k++)
-            if (Q.in[k].mode == IN_FULL) Q.in[k].vec_ok = (uintptr_t)Q.in[k].ptr % 32 == 0;
-        Q.out_vec_ok = (uintptr_t)Q.out % 32 == 0;
-    }
+    const Form f = pick_form(Q, pure_map, flat);
+    set_vector_flags(Q, flat, f.V);
     if (t_dry_run) {
         // generate and compile only; nothing is loaded or launched, so this works without a GPU
-        t_dry_run->source = jit_source(Q, pure_map, flat);
+        t_dry_run->source = source_for(Q, pure_map, flat, f);
         const Nvrtc& N = nvrtc();
         std::vector<char> cubin;
         t_dry_run->compiled = N.ok && compile_cubin(t_dry_run->source, cubin, t_dry_run->log);
@@ -544,16 +657,14 @@ int jit_launch(const Program& Q0, bool pure_map, bool flat, cudaStream_t st) {
     if (mode == 0) return kJitUnavailable;
     const Nvrtc& N = nvrtc();
     if (!N.ok) return mode == 2 ? fail(-1, "b200jt_fused_chain: run-time compiler unavailable: " + N.why) : kJitUnavailable;
-    const bool whole = flat ? (Q.rows * Q.cols) % VEC == 0 : Q.cols % VEC == 0;
-    const int G = Q.cols <= 1024 ? 32 : 256;
-    const std::string key = make_key(Q, pure_map, flat, whole, pure_map ? 0 : G);
+    const std::string key = make_key(Q, pure_map, flat, f);
     Compiled c;
     {
         std::lock_guard<std::mutex> lock(g_mu);
         auto it = g_cache.find(key);
         if (it != g_cache.end()) { c = it->second; g_hits++; }
         else {
-            const std::string src = jit_source(Q, pure_map, flat);
+            const std::string src = source_for(Q, pure_map, flat, f);
             std::string log;
             if (!compile(src, pure_map ? "chain_jit_map_kernel" : "chain_jit_rows_kernel", c, log)) {
                 c.failed = true; g_failed++; g_last_log = log;
@@ -562,14 +673,24 @@ int jit_launch(const Program& Q0, bool pure_map, bool flat, cudaStream_t st) {
         }
     }
     if (c.failed) return mode == 2 ? fail(-1, "b200jt_fused_chain: compiling the chain failed: " + g_last_log) : kJitUnavailable;
-    unsigned grid;
-    if (pure_map) {
-        const int64_t items = flat ? (Q.rows * Q.cols + VEC - 1) / VEC : Q.rows * ((Q.cols + VEC - 1) / VEC);
-        grid = grid_for(items, 256);
-    } else if (G == 32) grid = grid_for((Q.rows + 7) / 8 * 256, 256);
-    else grid = grid_for(Q.rows * 256, 256);
+    dim3 grid(1), block(256);
+    const int V = f.V;
+    if (pure_map && f.variant == 1) {
+        // x: the column vectors of a row (a power of two up to 256 wide), y: rows; about 8 CTAs per SM in all
+        const int64_t vpr = (Q.cols + V - 1) / V;
+        int bx = 8;
+        while (bx < 256 && bx < vpr) bx *= 2;
+        block = dim3(bx, 256 / bx);
+        const int64_t gx = (vpr + bx - 1) / bx, row_ctas = (Q.rows + block.y - 1) / block.y;
+        const int64_t cap = std::max<int64_t>(1, (int64_t)grid_for(INT64_MAX / 512, 256) / gx);
+        grid = dim3((unsigned)gx, (unsigned)std::min<int64_t>(std::min(row_ctas, cap), 65535));
+    } else if (pure_map) {
+        const int64_t items = flat ? (Q.rows * Q.cols + V - 1) / V : Q.rows * ((Q.cols + V - 1) / V);
+        grid = dim3(grid_for(items, 256));
+    } else if (f.G == 32) grid = dim3(grid_for((Q.rows + 7) / 8 * 256, 256));
+    else grid = dim3(grid_for(Q.rows * 256, 256));
     void* args[] = {(void*)&Q};
-    B200JT_CUDA(cudaLaunchKernel((const void*)c.kernel, dim3(grid), dim3(256), args, 0, st));
+    B200JT_CUDA(cudaLaunchKernel((const void*)c.kernel, grid, block, args, 0, st));
     return 0;
 }
 
