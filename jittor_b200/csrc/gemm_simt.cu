@@ -22,6 +22,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 // address that depends only on the row m is computed once per thread (Row) because a thread stages the same rows of
 // the A tile in every k step.
 struct MatmulLoader {
+    static constexpr bool kTable = false;
     int64_t a_sm, a_sk, b_sk, b_sn, c_sm;
     struct Row { int64_t off; };
     __device__ __forceinline__ Row row(int64_t m) const { return Row{m * a_sm}; }
@@ -51,11 +52,25 @@ struct ConvLoader {
         return Row{n * Ct * (int64_t)H * W, oh * sh - ph, ow * sw - pw};
     }
     template <typename T> __device__ __forceinline__ float A(const T* x, const Row& r, int64_t k) const {
-        const int kw = (int)(k % KW); const int t2 = (int)(k / KW);
+        const int k32 = (int)k;                                         // K = C*KH*KW of one group: always below 2^31
+        const int kw = k32 % KW; const int t2 = k32 / KW;
         const int kh = t2 % KH; const int c = t2 / KH;
         const int ih = r.ih0 + kh * dh, iw = r.iw0 + kw * dw;
         if (ih < 0 || ih >= H || iw < 0 || iw >= W) return 0.f;
         return to_f<T>(x[r.base + ((int64_t)c * H + ih) * W + iw]);
+    }
+    // The part of A's address that depends only on k, computed once per CTA and k by the deep-staging kernel.
+    static constexpr bool kTable = true;
+    struct KEntry { int plane; short dih, diw; };                       // c*H*W (a group's planes stay below 2^31 elements), kh*dh, kw*dw
+    __device__ __forceinline__ KEntry kentry(int k) const {
+        const int kw = k % KW; const int t2 = k / KW;
+        const int kh = t2 % KH; const int c = t2 / KH;
+        return KEntry{c * H * W, (short)(kh * dh), (short)(kw * dw)};
+    }
+    template <typename T> __device__ __forceinline__ float A_tab(const T* x, const Row& r, const KEntry& e) const {
+        const int ih = r.ih0 + e.dih, iw = r.iw0 + e.diw;
+        if ((unsigned)ih >= (unsigned)H || (unsigned)iw >= (unsigned)W) return 0.f;
+        return to_f<T>(x[r.base + e.plane + ih * W + iw]);
     }
     template <typename T> __device__ __forceinline__ float B(const T* w, int64_t k, int64_t n) const {
         return to_f<T>(w[n * ((int64_t)C_ * KH * KW) + k]);
@@ -73,6 +88,7 @@ struct ConvLoader {
 // w[i,o,kh,kw] wherever the divisions are exact and in range (the scatter of python/jittor/nn.py:1437-1449 read from
 // the output side). M = N*OH*OW output pixels, N = out channels of a group, K = (in channels of a group)*KH*KW.
 struct ConvTLoader {
+    static constexpr bool kTable = false;
     int Ci, CiT, H, W, Co, CoT, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;   // H, W: input extent; OH, OW: output extent
     struct Row { int64_t base; int oh, ow; };
     __device__ __forceinline__ Row row(int64_t m) const {
@@ -107,6 +123,7 @@ struct ConvTLoader {
 // (the reduce over [0,3,4] of reindex(x) * broadcast(dy) that the reduce / broadcast gradient rules produce).
 // M = Cout, N = Cin*KH*KW, K = batch*OH*OW, accumulated in ascending k.
 struct ConvWgradLoader {
+    static constexpr bool kTable = false;
     int Ci, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
     struct Row { int64_t off; };
     __device__ __forceinline__ Row row(int64_t m) const { return Row{m * (int64_t)OH * OW}; }
@@ -188,7 +205,140 @@ gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict
     }
 }
 
-// 64x64 tiles when they fill the machine, 32x32 tiles for small problems (latency-bound: more CTAs in flight).
+// Small problems (fewer tiles than two waves of CTAs) are bound by the latency of the k loop above, not by its arithmetic:
+// every 16-deep step costs a trip to memory and two barriers. This form stages KC = 320 k values of both operands at
+// once -- each thread issues its loads in batches of 8 per operand before it stores any of them, so a CTA pays a few
+// memory latencies per 320 k instead of one per 16 -- and then runs the same ascending-k FMA sequence over the staged
+// slab (same bits as the kernel above).
+constexpr int KC = 320;
+
+template <typename L, bool HAS> struct KTab { struct Entry { int unused; }; };
+template <typename L> struct KTab<L, true> { using Entry = typename L::KEntry; };
+
+template <typename T, typename L, int TM, int TN>
+__global__ void __launch_bounds__(256)
+gemm_simt_deep_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ c,
+                      int64_t M, int64_t N, int64_t K, const L ld) {
+    // PIX (the convolution forward): A and C are contiguous along m (pixels), B along k (a filter's taps). Then threads
+    // walk m when they stage A and store C, walk k when they stage B (kept n-major in shared memory), and in the FMA
+    // loop tx picks the rows and ty the columns, so every global access is coalesced and every shared access is either
+    // conflict-free or a broadcast. Otherwise (matmul: C contiguous along n) tx picks the columns.
+    constexpr bool PIX = L::kTable;
+    constexpr int RM = TM / 16, RN = TN / 16, PA = TM + 4, PB = PIX ? KC + 4 : TN + 4;
+    constexpr int KA = 256 / TM, KB = 256 / TN;                    // k values staged per pass of the CTA
+    constexpr int U = 8;
+    extern __shared__ float deep_smem[];
+    float* As = deep_smem;                                          // [KC][PA]
+    float* Bs = deep_smem + KC * PA;                                // [KC][PB], or for PIX [TN][PB] with PB = KC + 4
+    a += ld.a_group(blockIdx.z); b += ld.b_group(blockIdx.z); c += ld.c_group(blockIdx.z);
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;
+    const int64_t m0 = (int64_t)blockIdx.x * TM, n0 = (int64_t)blockIdx.y * TN;
+    const int a_mm = tid % TM, a_k0 = tid / TM;
+    const int64_t a_m = m0 + a_mm;
+    const typename L::Row arow = ld.row(a_m < M ? a_m : 0);
+    const int b_nn = tid % TN, b_k0 = tid / TN;
+    const int64_t b_n = n0 + b_nn;
+    float acc[RM][RN] = {};
+    [[maybe_unused]] __shared__ typename KTab<L, L::kTable>::Entry ktab[L::kTable ? KC : 1];
+    for (int64_t k0 = 0; k0 < K; k0 += KC) {
+        const int kc = (int)(K - k0 < KC ? K - k0 : KC);
+        if constexpr (L::kTable) {
+            // the divisions that split k into (channel, kh, kw) are done once per k and CTA, not once per staged element
+            for (int kk = tid; kk < kc; kk += 256) ktab[kk] = ld.kentry((int)k0 + kk);
+            __syncthreads();
+        }
+        if constexpr (PIX) {
+            for (int base = 0; base < kc; base += U * KA) {
+                float r[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = base + a_k0 + u * KA;
+                    r[u] = (a_m < M && kk < kc) ? ld.template A_tab<T>(a, arow, ktab[kk]) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = base + a_k0 + u * KA;
+                    if (kk < kc) As[kk * PA + a_mm] = r[u];
+                }
+            }
+            // B: a warp takes one filter row at a time and walks its taps
+            const int lane = tid % 32, wid = tid / 32;
+            for (int nn = wid; nn < TN; nn += 8) {
+                const int64_t n = n0 + nn;
+                for (int base = 0; base < kc; base += U * 32) {
+                    float r[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int kk = base + lane + u * 32;
+                        r[u] = (n < N && kk < kc) ? ld.template B<T>(b, k0 + kk, n) : 0.f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int kk = base + lane + u * 32;
+                        if (kk < kc) Bs[nn * PB + kk] = r[u];
+                    }
+                }
+            }
+        } else {
+            for (int base = 0; base < kc; base += U * KA) {
+                float r[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = base + a_k0 + u * KA;
+                    r[u] = (a_m < M && kk < kc) ? ld.template A<T>(a, arow, k0 + kk) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = base + a_k0 + u * KA;
+                    if (kk < kc) As[kk * PA + a_mm] = r[u];
+                }
+            }
+            for (int base = 0; base < kc; base += U * KB) {
+                float r[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = base + b_k0 + u * KB;
+                    r[u] = (b_n < N && kk < kc) ? ld.template B<T>(b, k0 + kk, b_n) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = base + b_k0 + u * KB;
+                    if (kk < kc) Bs[kk * PB + b_nn] = r[u];
+                }
+            }
+        }
+        __syncthreads();
+        // rows / columns of this thread inside the tile
+        const int rm = (PIX ? tx : ty) * RM, rn = (PIX ? ty : tx) * RN;
+#pragma unroll 4
+        for (int kk = 0; kk < kc; kk++) {
+            float av[RM], bv[RN];
+#pragma unroll
+            for (int i = 0; i < RM; i++) av[i] = As[kk * PA + rm + i];
+#pragma unroll
+            for (int j = 0; j < RN; j++) bv[j] = PIX ? Bs[(rn + j) * PB + kk] : Bs[kk * PB + rn + j];
+#pragma unroll
+            for (int i = 0; i < RM; i++)
+#pragma unroll
+                for (int j = 0; j < RN; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    const int rm = (PIX ? tx : ty) * RM, rn = (PIX ? ty : tx) * RN;
+#pragma unroll
+    for (int i = 0; i < RM; i++) {
+        const int64_t m = m0 + rm + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < RN; j++) {
+            const int64_t n = n0 + rn + j;
+            if (n < N) c[ld.C(m, n)] = from_f<T>(acc[i][j]);
+        }
+    }
+}
+
+// 64x64 tiles when they fill the machine; small problems take 32x32 tiles (more CTAs in flight) with the deep staging.
 template <typename T, typename L>
 static void launch_simt(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, const L& ld, cudaStream_t st,
                         int groups = 1) {
@@ -198,7 +348,12 @@ static void launch_simt(const void* a, const void* b, void* c, int64_t M, int64_
         gemm_simt_kernel<T, L, 64, 64><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
     } else {
         dim3 grid((unsigned)((M + 31) / 32), (unsigned)((N + 31) / 32), (unsigned)groups);
-        gemm_simt_kernel<T, L, 32, 32><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
+        constexpr int smem = (KC * (32 + 4) + (L::kTable ? 32 * (KC + 4) : KC * (32 + 4))) * (int)sizeof(float);
+        static const cudaError_t attr = cudaFuncSetAttribute(gemm_simt_deep_kernel<T, L, 32, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (attr == cudaSuccess && K >= 64)
+            gemm_simt_deep_kernel<T, L, 32, 32><<<grid, 256, smem, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
+        else
+            gemm_simt_kernel<T, L, 32, 32><<<grid, 256, 0, st>>>((const T*)a, (const T*)b, (T*)c, M, N, K, ld);
     }
 }
 
