@@ -1020,13 +1020,47 @@ def measure(wl, args, env, headline):
     return out
 
 
+def allreduce_latency(env):
+    """`--workload allreduce` (N > 1): latency of the NVLink peer all-reduce kernel next to NCCL for the message sizes of the
+    path, fp32 sum, 200 back-to-back calls between CUDA events, max over ranks. Prints one JSON line on rank 0."""
+    torch, tdist, jt = env["torch"], env["tdist"], env["jt"]
+    from jittor_b200 import dist
+    pc = dist.peer_comm()
+
+    def timeit(fn, n=200):
+        for _ in range(10):
+            fn()
+        tdist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device="cuda")
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        return t.item()
+
+    rows = []
+    for nbytes in (2048, 16384, 262144, 1 << 20, 4 << 20, 8 << 20):
+        x = torch.ones(nbytes // 4, device="cuda")
+        y, z = torch.empty_like(x), x.clone()
+        tp = timeit(lambda: pc.all_reduce(x, y)) if pc and pc.usable(x) else None
+        rows.append({"bytes": nbytes, "peer_us": tp, "nccl_us": timeit(lambda: tdist.all_reduce(z))})
+    status = jt._capi.lib.b200jt_device_status()
+    if env["rank"] == 0:
+        print(json.dumps({"metric": "all-reduce latency", "unit": "us", "n_gpus": env["world"], "higher_is_better": False,
+                          "peer_kernel": pc is not None, "device_status": status, "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS) + ["allreduce"])
     ap.add_argument("--all", type=int, default=1, help="default run: after the headline workload also measure c1, c3, c4, c5")
     ap.add_argument("--cpu-baseline", type=int, default=1)
     ap.add_argument("--parts", default="", help="comma-separated subset of the parts (profiling aid)")
@@ -1055,6 +1089,8 @@ def main():
     env = {"torch": torch, "tdist": tdist, "jt": jt, "rank": rank, "world": world, "local": local,
            "multi": dist.in_mpi(), "peer_kernel": dist.peer_comm() is not None,
            "peaks": json.load(open(peaks_path)) if os.path.exists(peaks_path) else None}
+    if args.workload == "allreduce":
+        return allreduce_latency(env)
     out = measure(WORKLOADS[args.workload](), args, env, True)
     if args.all and args.workload == HEADLINE and not args.parts:
         others = {}
