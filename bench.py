@@ -224,6 +224,21 @@ class C2Scatter:
     def run(self, name):
         return self._scatter(*self.dev[name]).sync()
 
+    def run_step(self, names, overlap):
+        """One step as the timed region runs it. N > 1: the four bins' all-reduces are held back while the scatter kernels
+        run (no rank is tied to another in between) and issued together on the side stream when the last scatter has been
+        launched, so that the exchange runs beside the pooling gradient, which needs no collective."""
+        from jittor_b200 import dist
+        if not (overlap and self.multi):
+            return [self.run(nm) for nm in names]
+        with dist.overlap_collectives(defer=True) as scope:
+            keep = []
+            for nm in names:
+                if nm == "pool-bwd":
+                    scope.flush()
+                keep.append(self.run(nm))
+            return keep
+
     def run_e2e(self, name):
         hv, hi, bins = self.pinned[name]
         v = self.jt.array(hv.cuda(non_blocking=True))
@@ -823,10 +838,15 @@ def measure(wl, args, env, headline):
     import contextlib
     step_context = wl.step_context if (multi and hasattr(wl, "step_context") and args.overlap) else contextlib.nullcontext
 
-    def step_direct():
+    def run_step():
+        """One step: the workload's own step runner when it has one (it places the collectives), else part after part."""
+        if hasattr(wl, "run_step"):
+            return wl.run_step(names, bool(args.overlap))
         with step_context():
-            for nm in names:
-                wl.run(nm)
+            return [wl.run(nm) for nm in names]
+
+    def step_direct():
+        run_step()
 
     warm = max(args.warmup, 3)
     for _ in range(warm):
@@ -860,8 +880,7 @@ def measure(wl, args, env, headline):
             barrier()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                with step_context():
-                    keep = [wl.run(nm) for nm in names]      # noqa: F841  (outputs stay alive with the graph)
+                keep = run_step()                            # noqa: F841  (outputs stay alive with the graph)
             graph.replay()
             barrier()
         except Exception as exc:                     # noqa: BLE001

@@ -61,6 +61,17 @@ int b200jt_reindex(const b200jt_tensor* x, const b200jt_tensor* y,
                    const char* const* overflow_conditions, int n_conditions,
                    const b200jt_tensor* extras, int n_extras, void* stream);
 
+/* The CUDA source the library compiles for this reindex once it has seen the same op instance twice (affine index
+ * expressions, every tensor below 2^31 elements, at least 2^16 outputs; B200JT_REINDEX_JIT=0 switches the run-time
+ * specialisation off, =2 compiles at first sight and makes a failure an error). Nothing is launched and the pointers are
+ * only looked at for their alignment, so no GPU is needed. Copies at most cap bytes, NUL-terminated, into src (may be
+ * NULL), stores the full length in *needed (0 when the op is not of the compiled kind) and sets *compiled to 1 if NVRTC
+ * accepted the source for sm_100a. Counterpart of reading the reference's generated reindex source
+ * (python/jittor/src/ops/reindex_op.cc:93-109 fills the index expressions into the loop nest it compiles). */
+int b200jt_reindex_source(const b200jt_tensor* x, const b200jt_tensor* y, const char* const* indexes, int n_indexes,
+                          double overflow_value, const char* const* overflow_conditions, int n_conditions,
+                          const b200jt_tensor* extras, int n_extras, char* src, int64_t cap, int64_t* needed, int* compiled);
+
 /* x[:] = init(op); for every i of y: if !overflow(i): x[index(i)] = op(x[index(i)], y[i]).
  * Replaces ReindexReduceOp(Var* y, NanoString op, NanoVector shape, vector<string>&& indexes,
  *                          vector<string>&& overflow_conditions, vector<Var*>&& extras)
@@ -139,7 +150,8 @@ int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200
  * cases python/jittor/test/test_fused_op.py:144-176). The reference generates and compiles a loop nest per graph; here
  * the graph is passed as a small program, and the kernel that runs it is specialised for that program at first use
  * (straight-line CUDA generated from the program, compiled for sm_100a with NVRTC, cached per process; constants, shapes,
- * strides and pointers stay arguments, so one compilation serves every size). Without NVRTC, or with
+ * strides and pointers stay arguments, so one compilation serves every size; the cubins are also kept on disk under
+ * $B200JT_CACHE_DIR, default ~/.cache/b200jt, "0" = off, so a later process loads instead of compiling). Without NVRTC, or with
  * B200JT_CHAIN_JIT=0, an ahead-of-time kernel interprets the program instead (same results, slower);
  * B200JT_CHAIN_JIT=2 makes a missing compiler or a failed compilation an error.
  *   inputs      n_inputs (<= 8) tensors, each with the rank of full_shape, size 1 on the axes it is broadcast over;

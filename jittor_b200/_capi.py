@@ -50,6 +50,8 @@ SIGNATURES = [
     ("b200jt_index_affine", _i, [ctypes.POINTER(ctypes.c_int64), _i, ctypes.POINTER(ctypes.c_int64), _i, _SP, _i,
                                  ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]),
     ("b200jt_reindex", _i, [_TP, _TP, _SP, _i, _d, _SP, _i, _TP, _i, _vp]),
+    ("b200jt_reindex_source", _i, [_TP, _TP, _SP, _i, _d, _SP, _i, _TP, _i, ctypes.c_char_p, ctypes.c_int64,
+                                   ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(_i)]),
     ("b200jt_reindex_reduce_workspace", _sz, [_TP, _TP, ctypes.c_char_p, _SP, _i, _SP, _i, _TP, _i]),
     ("b200jt_reindex_reduce", _i, [_TP, _TP, ctypes.c_char_p, _SP, _i, _SP, _i, _TP, _i, _vp, _sz, _vp]),
     ("b200jt_reindex_reduce_noalloc_max_scratch", _sz, []),

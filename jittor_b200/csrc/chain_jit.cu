@@ -14,57 +14,14 @@
 // __fmul_rn so that the compiler cannot contract a multiply of one op with the add of the next -- a fused chain returns
 // the bits of the same ops run one by one, exactly like the interpreter.
 //
-// NVRTC is opened with dlopen on first use; without it (or with B200JT_CHAIN_JIT=0) jit_launch reports "not available"
+// NVRTC (jit.cu) is opened with dlopen on first use; without it (or with B200JT_CHAIN_JIT=0) jit_launch reports "not available"
 // and the caller runs the interpreter kernels. B200JT_CHAIN_JIT=2 turns a failed compilation into an error.
 #include "fused_chain.cuh"
-
-#include <dlfcn.h>
-
-#include <atomic>
-#include <mutex>
-#include <unordered_map>
-#include <vector>
+#include "jit.cuh"
 
 namespace b200jt {
 namespace chain {
 namespace {
-
-// ---- NVRTC through dlopen ---------------------------------------------------------------------------------------
-struct Nvrtc {
-    typedef struct _nvrtcProgram* Prog;
-    int (*create)(Prog*, const char*, const char*, int, const char* const*, const char* const*) = nullptr;
-    int (*compile)(Prog, int, const char* const*) = nullptr;
-    int (*cubin_size)(Prog, size_t*) = nullptr;
-    int (*cubin)(Prog, char*) = nullptr;
-    int (*log_size)(Prog, size_t*) = nullptr;
-    int (*log)(Prog, char*) = nullptr;
-    int (*destroy)(Prog*) = nullptr;
-    bool ok = false;
-    std::string why;
-};
-
-const Nvrtc& nvrtc() {
-    static Nvrtc N = [] {
-        Nvrtc n;
-        void* h = nullptr;
-        for (const char* name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12"}) {
-            h = dlopen(name, RTLD_NOW | RTLD_LOCAL);
-            if (h) break;
-        }
-        if (!h) { n.why = "libnvrtc.so.12 not found"; return n; }
-        auto sym = [&](const char* s) { void* p = dlsym(h, s); if (!p) n.why = std::string("missing symbol ") + s; return p; };
-        n.create = (decltype(n.create))sym("nvrtcCreateProgram");
-        n.compile = (decltype(n.compile))sym("nvrtcCompileProgram");
-        n.cubin_size = (decltype(n.cubin_size))sym("nvrtcGetCUBINSize");
-        n.cubin = (decltype(n.cubin))sym("nvrtcGetCUBIN");
-        n.log_size = (decltype(n.log_size))sym("nvrtcGetProgramLogSize");
-        n.log = (decltype(n.log))sym("nvrtcGetProgramLog");
-        n.destroy = (decltype(n.destroy))sym("nvrtcDestroyProgram");
-        n.ok = n.why.empty();
-        return n;
-    }();
-    return N;
-}
 
 // ---- source generation ------------------------------------------------------------------------------------------
 const char* kPrelude = R"SRC(
@@ -520,14 +477,6 @@ struct Gen {
     }
 };
 
-// ---- cache ------------------------------------------------------------------------------------------------------
-struct Compiled { cudaLibrary_t lib = nullptr; cudaKernel_t kernel = nullptr; bool failed = false; };
-
-std::mutex g_mu;
-std::unordered_map<std::string, Compiled> g_cache;
-std::atomic<int> g_compiled{0}, g_hits{0}, g_failed{0};
-std::string g_last_log;
-
 // The form of the kernel a program gets; everything here is part of the cache key.
 struct Form { int V, G, variant; bool whole; };
 
@@ -546,34 +495,6 @@ std::string make_key(const Program& Q, bool map, bool flat, const Form& f) {
         k.append((const char*)v, sizeof v);
     }
     return k;
-}
-
-// source -> cubin
-bool compile_cubin(const std::string& src, std::vector<char>& cubin, std::string& log) {
-    const Nvrtc& N = nvrtc();
-    Nvrtc::Prog prog = nullptr;
-    if (N.create(&prog, src.c_str(), "fused_chain_jit.cu", 0, nullptr, nullptr) != 0) { log = "nvrtcCreateProgram failed"; return false; }
-    const char* opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-lineinfo"};
-    const int rc = N.compile(prog, 3, opts);
-    size_t ls = 0;
-    if (N.log_size(prog, &ls) == 0 && ls > 1) { log.resize(ls); N.log(prog, &log[0]); }
-    if (rc != 0) { N.destroy(&prog); return false; }
-    size_t cs = 0;
-    if (N.cubin_size(prog, &cs) != 0 || cs == 0) { N.destroy(&prog); log += " (no cubin)"; return false; }
-    cubin.resize(cs);
-    N.cubin(prog, cubin.data());
-    N.destroy(&prog);
-    return true;
-}
-
-bool compile(const std::string& src, const char* entry, Compiled& out, std::string& log) {
-    std::vector<char> cubin;
-    if (!compile_cubin(src, cubin, log)) return false;
-    cudaError_t e = cudaLibraryLoadData(&out.lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
-    if (e != cudaSuccess) { log += std::string(" cudaLibraryLoadData: ") + cudaGetErrorString(e); (void)cudaGetLastError(); return false; }
-    e = cudaLibraryGetKernel(&out.kernel, out.lib, entry);
-    if (e != cudaSuccess) { log += std::string(" cudaLibraryGetKernel: ") + cudaGetErrorString(e); (void)cudaGetLastError(); return false; }
-    return true;
 }
 
 int jit_mode() {
@@ -647,32 +568,17 @@ int jit_launch(const Program& Q0, bool pure_map, bool flat, cudaStream_t st) {
     if (t_dry_run) {
         // generate and compile only; nothing is loaded or launched, so this works without a GPU
         t_dry_run->source = source_for(Q, pure_map, flat, f);
-        const Nvrtc& N = nvrtc();
-        std::vector<char> cubin;
-        t_dry_run->compiled = N.ok && compile_cubin(t_dry_run->source, cubin, t_dry_run->log);
-        if (!N.ok) t_dry_run->log = N.why;
+        t_dry_run->compiled = jit::compile_only(t_dry_run->source, &t_dry_run->log);
         return 0;
     }
     const int mode = jit_mode();
     if (mode == 0) return kJitUnavailable;
-    const Nvrtc& N = nvrtc();
-    if (!N.ok) return mode == 2 ? fail(-1, "b200jt_fused_chain: run-time compiler unavailable: " + N.why) : kJitUnavailable;
-    const std::string key = make_key(Q, pure_map, flat, f);
-    Compiled c;
-    {
-        std::lock_guard<std::mutex> lock(g_mu);
-        auto it = g_cache.find(key);
-        if (it != g_cache.end()) { c = it->second; g_hits++; }
-        else {
-            const std::string src = source_for(Q, pure_map, flat, f);
-            std::string log;
-            if (!compile(src, pure_map ? "chain_jit_map_kernel" : "chain_jit_rows_kernel", c, log)) {
-                c.failed = true; g_failed++; g_last_log = log;
-            } else g_compiled++;
-            g_cache.emplace(key, c);
-        }
-    }
-    if (c.failed) return mode == 2 ? fail(-1, "b200jt_fused_chain: compiling the chain failed: " + g_last_log) : kJitUnavailable;
+    std::string why;
+    if (!jit::available(&why)) return mode == 2 ? fail(-1, "b200jt_fused_chain: run-time compiler unavailable: " + why) : kJitUnavailable;
+    std::string log;
+    const cudaKernel_t kernel = jit::get_kernel("chain:" + make_key(Q, pure_map, flat, f), [&] { return source_for(Q, pure_map, flat, f); },
+                                                pure_map ? "chain_jit_map_kernel" : "chain_jit_rows_kernel", &log);
+    if (!kernel) return mode == 2 ? fail(-1, "b200jt_fused_chain: compiling the chain failed: " + log) : kJitUnavailable;
     dim3 grid(1), block(256);
     const int V = f.V;
     if (pure_map && f.variant == 1) {
@@ -690,7 +596,7 @@ int jit_launch(const Program& Q0, bool pure_map, bool flat, cudaStream_t st) {
     } else if (f.G == 32) grid = dim3(grid_for((Q.rows + 7) / 8 * 256, 256));
     else grid = dim3(grid_for(Q.rows * 256, 256));
     void* args[] = {(void*)&Q};
-    B200JT_CUDA(cudaLaunchKernel((const void*)c.kernel, grid, block, args, 0, st));
+    B200JT_CUDA(cudaLaunchKernel((const void*)kernel, grid, block, args, 0, st));
     return 0;
 }
 
@@ -724,8 +630,6 @@ extern "C" int b200jt_fused_chain_source(const b200jt_tensor* inputs, int n_inpu
 /* Counters of the run-time specialiser since the process started: kernels compiled, launches served from the cache,
  * compilations that failed (those chains run through the interpreter kernels). Any pointer may be NULL. */
 extern "C" int b200jt_chain_jit_stats(int* compiled, int* hits, int* failed) {
-    if (compiled) *compiled = chain::g_compiled.load();
-    if (hits) *hits = chain::g_hits.load();
-    if (failed) *failed = chain::g_failed.load();
+    jit::stats(compiled, hits, failed);
     return 0;
 }

@@ -9,16 +9,11 @@
 // The output write stream dominates traffic (the gather source is usually much smaller and L2
 // resident), so both kernels are organised around coalesced output stores.
 #include "index_program.cuh"
+#include "reindex_jit.cuh"
 
 namespace b200jt {
 
-struct AffineArgs {
-    int32_t ndim_loop, ndim_x;
-    int64_t loop_shape[kMaxDims];
-    int64_t x_shape[kMaxDims];
-    int64_t c0[kMaxDims];
-    int64_t coef[kMaxDims][kMaxDims];
-};
+using AffineArgs = ReindexAffine;
 
 // I = index type (32-bit arithmetic when every tensor is below 2^31 elements, as the reference's index_t).
 // NL / NX are compile-time upper bounds of the two ranks: all loops over axes are fully unrolled to them (with
@@ -373,8 +368,10 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
     const bool small = numel(x) < (1LL << 31) && n < (1LL << 31);
     const T* xp = (const T*)x->ptr;
     T* yp = (T*)y->ptr;
+    const bool dry = reindex_jit_dry_running();          // source generation only: nothing may be launched
+    if (dry && !(P.is_affine && numel(x) > 0 && small)) return 0;
     PermArgs PA;
-    if (numel(x) > 0 && make_perm_args(P, &PA)) {
+    if (!dry && numel(x) > 0 && make_perm_args(P, &PA)) {
         if (sizeof(T) == 4 && perm_vec4_ok(PA, xp, yp)) {
             const int64_t total = ((PA.A + 63) / 64) * ((PA.B + 63) / 64) * PA.batch;
             const unsigned grid = (unsigned)(total < (int64_t)kNumSMs * 16 ? total : (int64_t)kNumSMs * 16);
@@ -402,6 +399,14 @@ static int launch_reindex(const b200jt_tensor* x, const b200jt_tensor* y, const 
         const bool vec_ok = VMAX > 1 && inner % VMAX == 0 && ((uintptr_t)yp % (VMAX * sizeof(T))) == 0;
         const bool flat_ok = VMAX > 1 && small && n % VMAX == 0 && ((uintptr_t)yp % (VMAX * sizeof(T))) == 0 &&
                              P.ndim_loop <= 8 && P.ndim_x <= 4;
+        if (small) {
+            // a kernel compiled for this very op instance, when it has been seen before (reindex_jit.cu)
+            const int v = (VMAX > 1 && n % VMAX == 0 && ((uintptr_t)yp % (VMAX * sizeof(T))) == 0) ? VMAX : 1;
+            uint64_t fill_bits = 0;
+            memcpy(&fill_bits, &fill, sizeof(T));
+            const int r = reindex_jit_launch(A, (int)sizeof(T), v, xp, yp, fill_bits, st);
+            if (r != kReindexJitUnavailable) return r;
+        }
         if (vec_ok) launch_affine<T, VMAX>(xp, yp, A, n / VMAX, fill, small, st);
         else if (flat_ok) {
             const uint32_t nv = (uint32_t)(n / VMAX);
@@ -447,4 +452,27 @@ extern "C" int b200jt_reindex(const b200jt_tensor* x, const b200jt_tensor* y,
         case 4: return launch_reindex<uint32_t>(x, y, P, overflow_value, st);
         default: return launch_reindex<uint64_t>(x, y, P, overflow_value, st);
     }
+}
+
+/* The CUDA source the library compiles for this reindex once it has seen it twice (affine index expressions, tensors
+ * below 2^31 elements), without launching anything; the pointers are only looked at for their alignment, no GPU is
+ * needed. Copies at most cap bytes, NUL-terminated, into src (may be NULL), stores the full length in *needed (0 when
+ * the op is not of the compiled kind) and sets *compiled to 1 if NVRTC accepted the source for sm_100a. */
+extern "C" int b200jt_reindex_source(const b200jt_tensor* x, const b200jt_tensor* y, const char* const* indexes, int n_indexes,
+                                     double overflow_value, const char* const* overflow_conditions, int n_conditions,
+                                     const b200jt_tensor* extras, int n_extras, char* src, int64_t cap, int64_t* needed,
+                                     int* compiled) {
+    ReindexDryRun dry;
+    reindex_jit_dry_run(&dry);
+    const int rc = b200jt_reindex(x, y, indexes, n_indexes, overflow_value, overflow_conditions, n_conditions, extras, n_extras, nullptr);
+    reindex_jit_dry_run(nullptr);
+    if (rc != 0) return rc;
+    if (needed) *needed = (int64_t)dry.source.size();
+    if (src && cap > 0) {
+        const size_t n = std::min((size_t)cap - 1, dry.source.size());
+        memcpy(src, dry.source.data(), n); src[n] = 0;
+    }
+    if (compiled) *compiled = dry.compiled ? 1 : 0;
+    if (!dry.source.empty() && !dry.compiled) set_error("b200jt_reindex_source: " + dry.log);
+    return 0;
 }

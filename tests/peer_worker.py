@@ -75,6 +75,37 @@ def main():
     for o, w_ in zip(outs, want):
         assert torch.equal(o._data.view(-1), w_.view(-1))
     assert C.lib.b200jt_device_status() == 0
+
+    # the same step with the all-reduces held back and issued together (defer), directly and from a captured graph;
+    # a result read before the flush makes the block flush by itself
+    def step_deferred():
+        with dist.overlap_collectives(defer=True) as scope:
+            outs = [v.reindex_reduce("add", [1 << 20], ["@e0(i0)"], extras=[i]).mpi_all_reduce("add").sync() for v, i in parts]
+            scope.flush()
+            tail = (parts[0][0] + 1).sync()                  # a kernel that runs beside the exchange
+            return outs, tail
+    outs, _ = step_deferred()
+    for o, w_ in zip(outs, want):
+        assert torch.equal(o.torch(), w_)
+    with dist.overlap_collectives(defer=True):
+        early = parts[0][0].reindex_reduce("add", [1 << 20], ["@e0(i0)"], extras=[parts[0][1]]).mpi_all_reduce("add")
+        assert torch.equal((early + 0).torch(), want[0])   # read inside the block, before any flush
+    torch.cuda.synchronize()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step_deferred()
+    torch.cuda.current_stream().wait_stream(side)
+    tdist.barrier()
+    torch.cuda.synchronize()
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        outs2, _ = step_deferred()
+    for _ in range(5):
+        graph2.replay()
+    torch.cuda.synchronize()
+    for o, w_ in zip(outs2, want):
+        assert torch.equal(o._data.view(-1), w_.view(-1))
+    assert C.lib.b200jt_device_status() == 0
     # sync BatchNorm statistics over the ranks' batches
     x = torch.randn(8, 64, 16, 16, generator=g, device="cuda")
     bn = nn.BatchNorm(64, is_train=True, sync=True)

@@ -187,3 +187,43 @@ def test_error_cases_of_the_reference():
         with pytest.raises(ValueError):
             bad()
     assert list(ph([1]).broadcast([0]).shape) == [0]
+
+
+def test_reindex_sources_compile_for_sm_100a():
+    """The source generated for an affine reindex instance goes through NVRTC without a GPU: a conv window (ragged
+    3x3 inner axes -> odometer with carries), a padded copy (vector never carries), 1- / 2- / 8-byte elements, a
+    scalar-store case; a gather through an index Var is not of the compiled kind."""
+    import ctypes
+    from jittor_b200 import _capi as C
+
+    def fake(i, dtype, shape):
+        d = C.Tensor()
+        d.ptr = 0x10000 * (i + 1)
+        d.dtype = C.DTYPE_CODES[dtype]
+        d.ndim = len(shape)
+        for j, e in enumerate(shape):
+            d.shape[j] = e
+        return d
+
+    def source(xs, ys, idx, dtype="float32", extras=()):
+        x, y = fake(0, dtype, xs), fake(1, dtype, ys)
+        ex = (C.Tensor * max(len(extras), 1))()
+        for i, (dt_, shp) in enumerate(extras):
+            ex[i] = fake(2 + i, dt_, shp)
+        buf = ctypes.create_string_buffer(1 << 16)
+        need, ok = ctypes.c_int64(), ctypes.c_int()
+        C.check(C.lib.b200jt_reindex_source(ctypes.byref(x), ctypes.byref(y), C.strings(idx), len(idx), 0.0, C.strings([]), 0,
+                                            ex, len(extras), buf, 1 << 16, ctypes.byref(need), ctypes.byref(ok)), "reindex source")
+        return buf.value.decode(), need.value, bool(ok.value)
+
+    src, need, ok = source([4, 32, 32, 32], [4, 64, 32, 32, 32, 3, 3], ["i0", "i2", "i3*1-1+i5*1", "i4*1-1+i6*1"])
+    assert ok and "if (i6 == 3)" in src and "uint4" in src and "i1 * " not in src        # broadcast axis: no multiply at all
+    src, need, ok = source([32768, 4096], [32768, 4100], ["i0", "i1-2"])
+    assert ok and "if (i1 ==" not in src and "(unsigned)a0" not in src                   # no carry, no check on the row axis
+    for dtype in ("uint8", "bfloat16", "float64"):
+        src, need, ok = source([64, 48], [64, 56], ["i0", "i1-4"], dtype)
+        assert ok, dtype
+    src, need, ok = source([5, 7], [5, 9], ["i0", "i1-1"])
+    assert ok and "y[v] =" in src
+    src, need, ok = source([100, 8], [10, 8], ["@e0(i0)", "i1"], extras=[("int32", [10])])
+    assert need == 0 and not ok
