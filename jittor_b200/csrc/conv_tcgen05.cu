@@ -9,7 +9,7 @@
 //               negative or past the edge -- TMA zero-fills, which is exactly the reindex overflow value 0;
 //   tile        128 pixels (two 8x8 spatial patches, each one 4-D TMA box of 64 rows x 128 B) x 256 output channels;
 //   pipeline    same persistent warp-specialised ring as the GEMM (TMA warp, MMA warp, 4 epilogue warps, TMEM
-//               double buffering), stride 1 only (the box is a dense window);
+//               double buffering); strides 1..4 through the traversal stride of the x tensor map;
 //   epilogue    tcgen05.ld -> bf16 -> y in NCHW; optionally per-channel sum / sum of squares of the stored values
 //               (the two reduce.mean of BatchNorm, python/jittor/nn.py:674-675) accumulated per CTA in shared memory
 //               and flushed with one atomicAdd per channel.
@@ -35,7 +35,7 @@ constexpr int THREADS = 192;
 constexpr double kNarrowTilePenalty = 1.5;         // measured cost per FLOP of 128-wide tiles relative to 256-wide ones (1.37 ms vs 0.92 ms)
 
 struct ConvArgs {
-    int N, C, H, W, Co, KH, KW, OH, OW, ph, pw, dh, dw;
+    int N, C, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
     int tiles_h, tiles_w;            // patches per image
     int64_t patches;                 // N * tiles_h * tiles_w
     int tiles_m, tiles_n;
@@ -108,8 +108,9 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 11))) break;
                     unsigned char* sa = smem + stage * STAGE_BYTES;
                     mbar_expect_tx(full + stage, A_BYTES + BN_T * BK * 2);
-                    tma_load_4d(sa, &map_x, full + stage, cb * BK, w0 + dx, h0 + dy, n0);
-                    tma_load_4d(sa + A_BYTES / 2, &map_x, full + stage, cb * BK, w1 + dx, h1 + dy, n1);
+                    // a box covers 8 x 8 OUTPUT pixels: with stride s the tensor map steps s input elements per box element
+                    tma_load_4d(sa, &map_x, full + stage, cb * BK, w0 * A.sw + dx, h0 * A.sh + dy, n0);
+                    tma_load_4d(sa + A_BYTES / 2, &map_x, full + stage, cb * BK, w1 * A.sw + dx, h1 * A.sh + dy, n1);
                     tma_load_2d(sa + A_BYTES, &map_w, full + stage, cb * BK, tap * A.Co + tn * BN_T);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -317,8 +318,10 @@ static bool make_map_x(CUtensorMap* map, const void* base, const ConvShape& s) {
     if (!fn) return false;
     cuuint64_t dims[4] = {(cuuint64_t)s.C, (cuuint64_t)s.W, (cuuint64_t)s.H, (cuuint64_t)s.N};
     cuuint64_t strides[3] = {(cuuint64_t)s.C * 2, (cuuint64_t)s.W * s.C * 2, (cuuint64_t)s.H * s.W * s.C * 2};
-    cuuint32_t box[4] = {(cuuint32_t)BK, PATCH, PATCH, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    // strided convolution: the traversal stride of the map skips input pixels, so that a box still delivers 8 x 8 window
+    // origins; the box extent counts tensor elements, i.e. 8 * stride per axis (at most 8 * 8 = 64 <= 256)
+    cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)(PATCH * s.sw), (cuuint32_t)(PATCH * s.sh), 1};
+    cuuint32_t estr[4] = {1, (cuuint32_t)s.sw, (cuuint32_t)s.sh, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -350,7 +353,7 @@ static bool make_map_y(CUtensorMap* map, const void* base, const ConvShape& s) {
 }  // namespace tcconv
 
 bool conv2d_tc_supported(const ConvShape& s, const void* x, const void* w, const void* y) {
-    return s.sh == 1 && s.sw == 1 && s.C % 8 == 0 && s.C >= 64 && s.Co >= 64 && s.H >= 8 && s.W >= 8 &&
+    return s.sh >= 1 && s.sh <= 4 && s.sw >= 1 && s.sw <= 4 && s.C % 8 == 0 && s.C >= 64 && s.Co >= 64 && s.H >= 8 && s.W >= 8 &&
            (int64_t)s.N * s.OH * s.OW >= 1024 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 2 == 0) &&
            ((uintptr_t)y % 2 == 0) && tc::encode_fn() != nullptr;
 }
@@ -380,7 +383,7 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     }
     ConvArgs A;
     A.N = s.N; A.C = s.C; A.H = s.H; A.W = s.W; A.Co = s.Co; A.KH = s.KH; A.KW = s.KW; A.OH = s.OH; A.OW = s.OW;
-    A.ph = s.ph; A.pw = s.pw; A.dh = s.dh; A.dw = s.dw;
+    A.sh = s.sh; A.sw = s.sw; A.ph = s.ph; A.pw = s.pw; A.dh = s.dh; A.dw = s.dw;
     A.tiles_h = (s.OH + PATCH - 1) / PATCH; A.tiles_w = (s.OW + PATCH - 1) / PATCH;
     A.patches = (int64_t)s.N * A.tiles_h * A.tiles_w;
     A.tiles_m = (int)((A.patches + 1) / 2);

@@ -200,8 +200,9 @@ struct BlockPacks {
 template <typename T, int OP, bool TWO_SHOT, bool LIGHT>
 __global__ void __launch_bounds__(kThreads, LIGHT ? 2 : 1) peer_all_reduce_kernel(Launch L, long long count) {
     constexpr int V = 16 / (int)sizeof(T);
-    constexpr int UC = 4;               // packs in flight per thread in the copies
-    constexpr int UR = 2;               // ... and per rank in the reduction
+    // the light form has half the registers: fewer packs in flight per thread, twice the resident threads
+    constexpr int UC = LIGHT ? 2 : 4;   // packs in flight per thread in the copies
+    constexpr int UR = LIGHT ? 1 : 2;   // ... and per rank in the reduction
     __shared__ int ok;
     __shared__ DevComm c;
     if (threadIdx.x == 0) { c = L.comm[blockIdx.y]; ok = 1; }

@@ -24,15 +24,15 @@ def bf16_round(a):
     return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).bfloat16().float().numpy()
 
 
-def conv_capi(x, w, pad, dil, stats=True, force_bn=None):
+def conv_capi(x, w, pad, dil, stats=True, force_bn=None, stride=1):
     """b200jt_conv2d on bf16 CUDA tensors; returns (y, stats or None, used the tensor-core path)."""
     from jittor_b200 import _capi as C
     N, Ci, H, W = x.shape
     Co, _, KH, KW = w.shape
-    OH, OW = H + 2 * pad - dil * (KH - 1), W + 2 * pad - dil * (KW - 1)
+    OH, OW = (H + 2 * pad - dil * (KH - 1) - 1) // stride + 1, (W + 2 * pad - dil * (KW - 1) - 1) // stride + 1
     y = torch.empty(N, Co, OH, OW, dtype=torch.bfloat16, device="cuda")
     st = torch.full((2 * Co,), 7.0, dtype=torch.float32, device="cuda") if stats else None   # the callee zeroes it
-    args = (C.desc(x), C.desc(w), C.desc(y), 1, 1, pad, pad, dil, dil, 1)
+    args = (C.desc(x), C.desc(w), C.desc(y), stride, stride, pad, pad, dil, dil, 1)
     nbytes = C.lib.b200jt_conv2d_workspace(*args)
     ws = torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device="cuda")
     old = os.environ.get("B200JT_CONV_BN")
@@ -85,6 +85,33 @@ CASES = [
     ((3, 64, 24, 24), (512, 64, 3, 3), 1, 1),
     ((5, 136, 17, 19), (72, 136, 3, 3), 1, 1),
 ]
+
+
+# (x shape, w shape, stride, padding, dilation): the same kernel with the x tensor map stepping `stride` input pixels per
+# box element -- the 3x3 stride-2 and 1x1 stride-2 layers of a ResNet, odd extents, stride 3, stride with dilation
+STRIDED = [
+    ((4, 64, 32, 32), (64, 64, 3, 3), 2, 1, 1),
+    ((8, 128, 28, 28), (192, 128, 3, 3), 2, 1, 1),
+    ((4, 64, 33, 35), (64, 64, 1, 1), 2, 0, 1),
+    ((6, 72, 40, 40), (96, 72, 5, 5), 3, 2, 1),
+    ((3, 64, 45, 47), (64, 64, 3, 3), 2, 0, 2),
+    ((2, 256, 56, 56), (256, 256, 3, 3), 2, 1, 1),
+]
+
+
+@pytest.mark.parametrize("xs,wshape,stride,pad,dil", STRIDED)
+def test_conv_tc_strided_against_oracle(xs, wshape, stride, pad, dil):
+    from jittor_b200 import _capi as C
+    rng = np.random.default_rng(sum(xs) + sum(wshape) + stride + pad + dil)
+    x = bf16_round(rng.normal(size=xs))
+    w = bf16_round(rng.normal(size=wshape) * np.sqrt(2.0 / (wshape[1] * wshape[2] * wshape[3])))
+    xt, wt = torch.from_numpy(x).bfloat16().cuda(), torch.from_numpy(w).bfloat16().cuda()
+    y, st, used_tc = conv_capi(xt, wt, pad, dil, stats=True, stride=stride)
+    assert used_tc, "case does not reach the tensor-core kernel"
+    want = co.conv2d(x, w, stride, pad, dil)
+    check(y.float().cpu().numpy(), bf16_round(want), False, rtol=2e-2)
+    check_stats(y, st)
+    assert C.lib.b200jt_device_status() == 0
 
 
 @pytest.mark.parametrize("force_bn", [128, 256])
