@@ -535,8 +535,8 @@ class MetaOps:
     description = ("plain meta-operators on [32768,4096] fp32: reindex (pad by 2 columns; transpose), reduce (row sum, "
                    "column sum), broadcast fused into a binary add, and the conv-window reindex of config 0 "
                    "([4,32,32,32] -> [4,64,32,32,32,3,3])")
-    kernel_of = {"reindex-pad": "reindex_affine_kernel", "reindex-transpose": "reindex_affine_kernel",
-                 "reindex-conv-window": "reindex_affine_kernel", "reduce-row-sum": "reduce_row_kernel",
+    kernel_of = {"reindex-pad": "reindex_jit_kernel", "reindex-transpose": "reindex_permute_vec4_kernel",
+                 "reindex-conv-window": "reindex_jit_kernel", "reduce-row-sum": "reduce_row_kernel",
                  "reduce-col-sum": "reduce_col_kernel", "broadcast-add": "binary_kernel"}
     launches = {"reindex-pad": 1, "reindex-transpose": 1, "reindex-conv-window": 1, "reduce-row-sum": 1,
                 "reduce-col-sum": 2, "broadcast-add": 1}
