@@ -217,7 +217,9 @@ def test_reindex_sources_compile_for_sm_100a():
         return buf.value.decode(), need.value, bool(ok.value)
 
     src, need, ok = source([4, 32, 32, 32], [4, 64, 32, 32, 32, 3, 3], ["i0", "i2", "i3*1-1+i5*1", "i4*1-1+i6*1"])
-    assert ok and "if (i6 == 3)" in src and "uint4" in src and "i1 * " not in src        # broadcast axis: no multiply at all
+    assert ok and "stage[" in src and "uint4" in src and "i1 * " not in src              # tiled form; broadcast axis: no multiply at all
+    src, need, ok = source([100, 66], [100, 70], ["i0", "i1-2"])
+    assert ok and "if (i1 == 70)" in src and "stage[" not in src                         # long ragged rows: odometer with a carry
     src, need, ok = source([32768, 4096], [32768, 4100], ["i0", "i1-2"])
     assert ok and "if (i1 ==" not in src and "(unsigned)a0" not in src                   # no carry, no check on the row axis
     for dtype in ("uint8", "bfloat16", "float64"):
