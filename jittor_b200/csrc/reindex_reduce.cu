@@ -303,7 +303,7 @@ constexpr int kHot = 4;
 template <typename T, typename E, int VEC>
 __global__ void __launch_bounds__(kPrivThreads, 1)
 rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __restrict__ partial,
-                     int64_t n, int bins, int replicas, int op, bool is_bool) {
+                     int64_t n, int bins, int replicas, int op, bool is_bool, bool allow_hot) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sm = reinterpret_cast<T*>(smem_raw);
     const int rstride = bins + 1;
@@ -312,7 +312,7 @@ rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __re
     __shared__ unsigned warp_best[kPrivThreads / 32];
     constexpr bool kHotPath = std::is_same<T, float>::value && VEC > 1;
     bool use_hot = false;
-    if (kHotPath && op == OP_ADD && bins < 8192 && n / VEC >= (int64_t)gridDim.x * blockDim.x * 8) {
+    if (kHotPath && allow_hot && op == OP_ADD && bins < 8192 && n / VEC >= (int64_t)gridDim.x * blockDim.x * 8) {
         // histogram of the sample in the (not yet initialised) replica area
         int* hist = reinterpret_cast<int*>(smem_raw);
         for (int i = threadIdx.x; i < bins; i += blockDim.x) hist[i] = 0;
@@ -327,6 +327,7 @@ rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __re
         }
         __syncthreads();
         const unsigned threshold = (unsigned)(blockDim.x * VEC) / 100u;                       // 1 % of the sample
+        if (threadIdx.x < kHot) hot_bin[threadIdx.x] = -2;
         for (int k = 0; k < kHot; k++) {
             unsigned best = 0;                                                                // count << 13 | bin
             for (int i = threadIdx.x; i < bins; i += blockDim.x) best = max(best, ((unsigned)hist[i] << 13) | (unsigned)i);
@@ -334,42 +335,49 @@ rr_privatised_kernel(const T* __restrict__ y, const E* __restrict__ idx, T* __re
             for (int d = 16; d > 0; d >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, d));
             if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = best;
             __syncthreads();
-            if (threadIdx.x == 0) {
-                unsigned b2 = 0;
-                for (int w = 0; w < (int)(blockDim.x >> 5); w++) b2 = max(b2, warp_best[w]);
-                const bool hot = (b2 >> 13) > threshold;
-                hot_bin[k] = hot ? (int)(b2 & 8191u) : -2;
-                if (hot) hist[b2 & 8191u] = 0;
-            }
+            unsigned b2 = warp_best[threadIdx.x & 31];                                        // 32 warps: every warp folds the 32 maxima
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) b2 = max(b2, __shfl_xor_sync(0xffffffffu, b2, d));
+            const bool hot = (b2 >> 13) > threshold;                                          // the same in every thread
+            if (!hot) break;                                                                  // uniform inputs leave after one look
+            if (threadIdx.x == 0) { hot_bin[k] = (int)(b2 & 8191u); hist[b2 & 8191u] = 0; }
             __syncthreads();
         }
+        __syncthreads();
         use_hot = hot_bin[0] >= 0;                                                            // the same for the whole CTA
         __syncthreads();
     }
     for (int i = threadIdx.x; i < rstride * replicas; i += blockDim.x) sm[i] = init;
     __syncthreads();
     T* mine = sm + (threadIdx.x % replicas) * rstride;
-    if (kHotPath && use_hot) {
+    if constexpr (kHotPath) {
+        // one loop for both cases (with no hot bin the compares never hit): two copies of the unrolled loop in one kernel
+        // cost the plain case 15 % through the register allocation they share
         float hacc[kHot];
 #pragma unroll
         for (int k = 0; k < kHot; k++) hacc[k] = 0.f;
+        int hb[kHot];
+#pragma unroll
+        for (int k = 0; k < kHot; k++) hb[k] = use_hot ? hot_bin[k] : -2;
         for_each_pair<T, E, VEC, 4>(y, idx, n, [&](int64_t b, T v, bool valid) {
             const int bi = (int)b;
             bool hit = false;
 #pragma unroll
             for (int k = 0; k < kHot; k++) {
-                const bool m = bi == hot_bin[k];
+                const bool m = bi == hb[k];
                 hacc[k] += m ? (float)v : 0.f;
                 hit |= m;
             }
             if (!hit && valid && b >= 0 && b < bins) atomic_apply<T>(mine + b, v, op);
         });
+        if (use_hot) {
 #pragma unroll
-        for (int k = 0; k < kHot; k++) {
-            float a = hacc[k];
+            for (int k = 0; k < kHot; k++) {
+                float a = hacc[k];
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) a += __shfl_down_sync(0xffffffffu, a, d);
-            if ((threadIdx.x & 31) == 0 && hot_bin[k] >= 0) atomic_apply<T>(mine + hot_bin[k], (T)a, op);
+                for (int d = 16; d > 0; d >>= 1) a += __shfl_down_sync(0xffffffffu, a, d);
+                if ((threadIdx.x & 31) == 0 && hb[k] >= 0) atomic_apply<T>(mine + hb[k], (T)a, op);
+            }
         }
     } else {
         for_each_pair<T, E, VEC, 4>(y, idx, n, [&](int64_t b, T v, bool valid) {
@@ -550,13 +558,15 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         constexpr int VEC = 16 / sizeof(T);
         const bool aligned = ((uintptr_t)yp % 16 == 0) && ((uintptr_t)P.extras[0].ptr % 16 == 0);
         const int priv_grid = kPrivGrid - sm_reserve();         // rows of `partial` actually written and folded
+        const char* hot_env = getenv("B200JT_RR_HOT");
+        const bool allow_hot = !(hot_env && hot_env[0] == '0');
         // the shared-memory opt-in is set once per instantiation, not on every launch
 #define B200JT_PRIV(E, V)                                                                                      \
         do { auto k = rr_privatised_kernel<T, E, V>;                                                            \
              static const cudaError_t attr_ = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrivMaxSmemBytes); \
              B200JT_CUDA(attr_);                                                                                  \
              k<<<priv_grid, kPrivThreads, plan.smem, st>>>(yp, (const E*)P.extras[0].ptr, partial, n, (int)bins,   \
-                                                           plan.replicas, op, is_bool); } while (0)
+                                                           plan.replicas, op, is_bool, allow_hot); } while (0)
         if (e64) { if (aligned) B200JT_PRIV(int64_t, VEC); else B200JT_PRIV(int64_t, 1); }
         else     { if (aligned) B200JT_PRIV(int32_t, VEC); else B200JT_PRIV(int32_t, 1); }
 #undef B200JT_PRIV

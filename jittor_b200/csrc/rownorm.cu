@@ -3,10 +3,15 @@
 //
 //   reg kernel  -- the row lives in registers: CTA of 256 threads (or one warp for short rows), 128-bit
 //                  loads, warp-shuffle tree + one shared-memory hop, 128-bit stores. HBM-bound: 1R + 1W.
+//   cluster kernel -- rows too long for one CTA's registers (above 8192 float32 / 16384 bfloat16 columns, up to 8x
+//                  that): a thread-block cluster of 2, 4 or 8 CTAs holds the row, every CTA reduces its slice and the
+//                  slices' partial results are exchanged through distributed shared memory. Still 1R + 1W.
 //   pass kernel -- any cols / alignment: three sweeps by one CTA per row (re-reads hit L2).
 // IO dtype float32 or bfloat16; all math in float32.
 #include "common.cuh"
+#include <algorithm>
 #include <cfloat>
+#include <cooperative_groups.h>
 
 namespace b200jt {
 
@@ -230,6 +235,134 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
     }
 }
 
+// ---- rows held by a cluster -------------------------------------------------------------------------------------------
+// CL CTAs of 256 threads share a row: CTA c of the cluster owns the vectors (c*256 + t) + k*256*CL, k < 8. A reduction is
+// the CTA-wide one above followed by an exchange: thread 0 of every CTA publishes its CTA's value in its own shared
+// memory, the cluster synchronises, and every thread reads the CL values through distributed shared memory and combines
+// them in rank order (the same bits in every CTA). Four slots rotate, so a slot is rewritten only after four further
+// cluster barriers; a last barrier keeps every CTA's shared memory alive until all its readers are done.
+template <int CL, bool IS_MAX, int NV>
+__device__ __forceinline__ void cluster_reduce_n(float (&v)[NV], float* sm, float* xch, int& slot) {
+    namespace cg = cooperative_groups;
+    group_reduce_n<256, IS_MAX, NV>(v, sm);
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) xch[slot * 2 + i] = v[i];
+    }
+    cluster.sync();
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        float a = IS_MAX ? -FLT_MAX : 0.f;
+#pragma unroll
+        for (int c = 0; c < CL; c++) {
+            const float p = cluster.map_shared_rank(xch, c)[slot * 2 + i];
+            a = IS_MAX ? fmaxf(a, p) : a + p;
+        }
+        v[i] = a;
+    }
+    slot = (slot + 1) & 3;
+}
+
+template <typename T, int CL, int OP>
+__global__ void __launch_bounds__(256)
+row_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ gamma,
+                   const float* __restrict__ beta, int64_t rows, int cols, float eps) {
+    namespace cg = cooperative_groups;
+    constexpr int N = Vec16<T>::N, VPT = 8;
+    __shared__ float sm[32];
+    __shared__ float xch[8];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int crank = (int)cluster.block_rank(), t = threadIdx.x;
+    const int nvec = cols / N;
+    const int64_t n_clusters = gridDim.x / CL, cid = blockIdx.x / CL;
+    int slot = 0;
+    for (int64_t row = cid; row < rows; row += n_clusters) {                // the same trip count in every CTA of a cluster
+        const T* xr = x + row * cols;
+        T* yr = y + row * cols;
+        float v[VPT][N];
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int vi = crank * 256 + t + k * 256 * CL;
+            if (vi < nvec) Vec16<T>::load(xr + (int64_t)vi * N, v[k]);
+            else {
+#pragma unroll
+                for (int e = 0; e < N; e++) v[k][e] = (OP == ROW_LAYERNORM) ? 0.f : -FLT_MAX;
+            }
+        }
+        if constexpr (OP == ROW_LAYERNORM) {
+            float s[2] = {0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+#pragma unroll
+                for (int e = 0; e < N; e++) { s[0] += v[k][e]; s[1] += v[k][e] * v[k][e]; }
+            cluster_reduce_n<CL, false, 2>(s, sm, xch, slot);
+            const float rc = 1.0f / (float)cols;
+            const float mean = s[0] * rc, m2 = s[1] * rc;
+            const float var = fmaxf(m2 - mean * mean, 0.f);
+            const float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+            for (int k = 0; k < VPT; k++) {
+                const int vi = crank * 256 + t + k * 256 * CL;
+                if (vi < nvec) {
+                    float o[N], g1[N], b1[N];
+                    load_gb<N>(gamma, beta, vi * N, g1, b1);
+#pragma unroll
+                    for (int e = 0; e < N; e++) { const float w = g1[e] * rstd; o[e] = v[k][e] * w + (b1[e] - mean * w); }
+                    Vec16<T>::store(yr + (int64_t)vi * N, o);
+                }
+            }
+        } else {
+            float m[1] = {-FLT_MAX};
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+#pragma unroll
+                for (int e = 0; e < N; e++) m[0] = fmaxf(m[0], v[k][e]);
+            cluster_reduce_n<CL, true, 1>(m, sm, xch, slot);
+            float sum[1] = {0.f};
+#pragma unroll
+            for (int k = 0; k < VPT; k++)
+#pragma unroll
+                for (int e = 0; e < N; e++) {
+                    const float a = v[k][e] - m[0];
+                    const float ex = __expf(a);
+                    sum[0] += (crank * 256 + t + k * 256 * CL < nvec) ? ex : 0.f;
+                    v[k][e] = (OP == ROW_SOFTMAX) ? ex : a;
+                }
+            cluster_reduce_n<CL, false, 1>(sum, sm, xch, slot);
+            const float ls = logf(sum[0]), inv = 1.0f / sum[0];
+#pragma unroll
+            for (int k = 0; k < VPT; k++) {
+                const int vi = crank * 256 + t + k * 256 * CL;
+                if (vi < nvec) {
+                    float o[N];
+#pragma unroll
+                    for (int e = 0; e < N; e++) o[e] = (OP == ROW_SOFTMAX) ? v[k][e] * inv : v[k][e] - ls;
+                    Vec16<T>::store(yr + (int64_t)vi * N, o);
+                }
+            }
+        }
+    }
+    cluster.sync();                     // nobody leaves while its shared memory may still be read
+}
+
+template <typename T, int CL, int OP>
+static cudaError_t launch_cluster(const T* x, T* y, const float* gamma, const float* beta, int64_t rows, int cols, float eps,
+                                  cudaStream_t st) {
+    const int64_t fit = std::max<int64_t>(1, (int64_t)(kNumSMs - sm_reserve()) * 2 / CL);      // clusters resident at once
+    const unsigned clusters = (unsigned)std::min<int64_t>(rows, fit);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(clusters * CL);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, row_cluster_kernel<T, CL, OP>, x, y, gamma, beta, rows, cols, eps);
+}
+
 // Any cols: one CTA per row, three sweeps.
 template <typename T, int OP>
 __global__ void __launch_bounds__(256)
@@ -269,6 +402,12 @@ row_pass_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restr
     }
 }
 
+// B200JT_ROW_CLUSTER=0 sends long rows to the three-sweep kernel instead (for comparison)
+static bool cluster_rows_enabled() {
+    const char* e = getenv("B200JT_ROW_CLUSTER");
+    return !(e && e[0] == '0');
+}
+
 template <typename T, int OP>
 static int launch_rows(const T* x, T* y, const float* gamma, const float* beta, int64_t rows, int64_t cols,
                        float eps, cudaStream_t st) {
@@ -290,6 +429,13 @@ static int launch_rows(const T* x, T* y, const float* gamma, const float* beta, 
         else if (nvec <= 512) B200JT_ROW(256, 2);
         else if (nvec <= 1024) B200JT_ROW(256, 4);
         else B200JT_ROW(256, 8);
+    } else if (vec_ok && nvec <= 256 * 8 * 8 && rows > 0 && cluster_rows_enabled()) {
+        // a cluster of 2 / 4 / 8 CTAs per row
+        cudaError_t e;
+        if (nvec <= 256 * 8 * 2) e = launch_cluster<T, 2, OP>(x, y, gamma, beta, rows, (int)cols, eps, st);
+        else if (nvec <= 256 * 8 * 4) e = launch_cluster<T, 4, OP>(x, y, gamma, beta, rows, (int)cols, eps, st);
+        else e = launch_cluster<T, 8, OP>(x, y, gamma, beta, rows, (int)cols, eps, st);
+        B200JT_CUDA(e);
     } else {
         unsigned grid = (unsigned)(rows < (int64_t)kNumSMs * 16 ? rows : (int64_t)kNumSMs * 16);
         row_pass_kernel<T, OP><<<grid, 256, 0, st>>>(x, y, gamma, beta, rows, cols, eps);

@@ -192,6 +192,30 @@ def test_softmax_layernorm_bf16(jt, rows, cols):
     check(z.numpy(), bf16_round(co.layernorm_rows(xr, g, np.zeros(cols, np.float32))), False, rtol=2e-2)
 
 
+@pytest.mark.parametrize("rows,cols", [(7, 8196), (3, 16384), (5, 20000), (2, 32768), (4, 50000), (1, 65536), (300, 12000)])
+def test_softmax_layernorm_rows_held_by_a_cluster(be, rows, cols):
+    """Rows above 8192 float32 columns: 2 / 4 / 8 CTAs of a thread-block cluster hold a row and exchange their partial
+    results through distributed shared memory (whole and ragged last vectors, more rows than resident clusters)."""
+    rng = np.random.default_rng(rows + cols)
+    x = (rng.normal(size=(rows, cols)) * 2).astype(np.float32)
+    check(be.softmax(x, -1, False), co.softmax_rows(x, False), False)
+    check(be.softmax(x, -1, True), co.softmax_rows(x, True), False)
+    g, b = (1 + 0.02 * rng.normal(size=cols)).astype(np.float32), rng.normal(size=cols).astype(np.float32)
+    check(be.layer_norm(x, (cols,), g, b), co.layernorm_rows(x, g, b), False)
+
+
+@pytest.mark.parametrize("rows,cols", [(6, 16392), (3, 40000), (2, 131072)])
+def test_softmax_layernorm_bf16_rows_held_by_a_cluster(jt, rows, cols):
+    from jittor_b200 import nn
+    rng = np.random.default_rng(cols)
+    xr = bf16_round(rng.normal(size=(rows, cols)))
+    xv = to_bf16_var(jt, xr)
+    check(nn.softmax(xv, -1).numpy(), bf16_round(co.softmax_rows(xr)), False, rtol=2e-2)
+    g = (1 + 0.02 * rng.normal(size=cols)).astype(np.float32)
+    z = nn.layer_norm(xv, (cols,), jt.array(g), jt.array(np.zeros(cols, np.float32)))
+    check(z.numpy(), bf16_round(co.layernorm_rows(xr, g, np.zeros(cols, np.float32))), False, rtol=2e-2)
+
+
 # ------------------------------------------------------------------------------------------------ contractions
 @pytest.mark.parametrize("m,n,k", [(1, 1, 1), (33, 29, 47), (128, 256, 64), (300, 200, 1000), (512, 512, 512)])
 def test_matmul_fp32(be, m, n, k):
