@@ -610,7 +610,11 @@ static int run_typed(const b200jt_tensor* y, const b200jt_tensor* x, int op, con
         if constexpr (sizeof(T) == 4 || sizeof(T) == 8) {
             if (bins < (1LL << 31)) {
                 const T init = init_value<T>(op, is_bool);
-                const unsigned grid = 2 * (kNumSMs - sm_reserve());
+                // two CTAs are resident per SM; three waves of them balance the tail better than one (0.117 -> 0.114 ms
+                // uniform, 0.103 -> 0.097 ms Zipf for 2^24 -> 2^20); B200JT_RR_DIRECT_CTAS overrides the CTAs per SM
+                const char* gm_ = getenv("B200JT_RR_DIRECT_CTAS");
+                const int per_sm = gm_ ? std::max(1, std::min(16, atoi(gm_))) : 6;
+                const unsigned grid = (unsigned)per_sm * (kNumSMs - sm_reserve());
                 if (e64) {
                     if (aligned) rr_direct_cached_kernel<T, int64_t, VEC><<<grid, kCacheThreads, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op, init);
                     else rr_direct_cached_kernel<T, int64_t, 1><<<grid, kCacheThreads, 0, st>>>(yp, (const int64_t*)P.extras[0].ptr, xp, n, bins, op, init);
