@@ -2,15 +2,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|meta|fused|next] [--impl reference]
 
-One JSON line on stdout (rank 0). The default run measures c2 (the headline keys of the line) and then c1, c3, c4, c5
-with the same method into "workloads"; --workload X measures X alone. Workloads are the benchmark configurations:
+One JSON line on stdout (rank 0). The default run measures c2 (the headline keys of the line) and then c1, c3, c4, c5 and
+the meta / fused / next sets with the same method into "workloads"; --workload X measures X alone. Workloads are the benchmark configurations:
     c1            reindex-lowered conv2d fp32 [4,32,32,32] * [64,32,3,3], L2 flushed before every repetition    (GB/s and TFLOP/s)
     c2 (default)  reindex_reduce scatter: 2^24 int32 -> 2^20 bins and 2^24 fp32 -> 4096 bins, uniform and Zipf(1.1)
                   indices, plus the 2x2 max-pool backward [64,128,56,56,2,2] -> [64,128,112,112]      (GB/s, HBM)
     c3            fused row softmax and LayerNorm on [32768, 4096], fp32 and bf16 IO                  (GB/s, HBM)
     c4            broadcast-multiply-sum matmul, bf16: 8192^3 and 16384 x 4096 x 4096                 (TFLOP/s)
-    c5            reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] -> global BatchNorm statistics (one NCCL
-                  all-reduce of 2*C floats) -> normalise + ReLU, batch-sharded over the ranks          (TFLOP/s)
+    c5            reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] -> global BatchNorm statistics (one all-reduce
+                  of 2*C floats) -> normalise + ReLU, batch-sharded over the ranks                     (TFLOP/s)
+    meta          the meta-operators on their own on [32768,4096] fp32 (reindex pad / transpose / conv window, row and
+                  column sum, broadcast add)                                                           (GB/s, HBM)
+    fused         general element-wise chains as one compiled kernel each (x*w+b, relu(x+b), (a*b).sum(1),
+                  centre-and-scale) and the softmax backward, [32768,4096] fp32                        (GB/s, HBM)
+    next          callers of the path: 3x3 s2 max-pool forward / backward, getitem row gather, setitem scatter-add (GB/s)
 One step = one pass over the parts of the workload. `value` is algorithmic work / CUDA-event time with inputs
 resident in HBM (max over ranks); `e2e` is the same step through the public API from pinned host buffers including
 host->device copies and the device->host read of the results. Every part works on more bytes than the 126 MB L2
@@ -770,7 +775,7 @@ class NextOps:
 
 WORKLOADS = {w.key: w for w in (C1ConvF32, C2Scatter, C3Rows, C4Matmul, C5ConvBN, MetaOps, FusedChains, NextOps)}
 HEADLINE = "c2"                               # the default run's top-level line; the other configs follow in "workloads"
-CONFIGS = ("c1", "c3", "c4", "c5")
+CONFIGS = ("c1", "c3", "c4", "c5", "meta", "fused", "next")   # measured after the headline in the default run
 
 
 def scale_of(unit):

@@ -23,7 +23,7 @@ def test_reference_arm_prints_one_contract_line():
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
     # the other configurations ride along, each with its own CPU value
-    assert set(d["workloads"]) == {"c1", "c3", "c4", "c5"}
+    assert set(d["workloads"]) == {"c1", "c3", "c4", "c5", "meta", "fused", "next"}
     for rec in d["workloads"].values():
         assert rec["value"] > 0 and rec["unit"] in ("GB/s", "TFLOP/s") and rec["kind"] == "port" and rec["sample"]
 
@@ -32,7 +32,7 @@ def test_workload_tables_are_consistent():
     sys.path.insert(0, ROOT)
     import bench
     assert set(bench.WORKLOADS) == {"c1", "c2", "c3", "c4", "c5", "meta", "fused", "next"}
-    assert bench.HEADLINE == "c2" and set(bench.CONFIGS) == {"c1", "c3", "c4", "c5"}
+    assert bench.HEADLINE == "c2" and set(bench.CONFIGS) == {"c1", "c3", "c4", "c5", "meta", "fused", "next"}
     for key, cls in bench.WORKLOADS.items():
         wl = cls()
         parts = set(wl.work())
