@@ -611,20 +611,22 @@ class MetaOps:
 
 
 class FusedChains:
-    """Element-wise chains no named pattern covers, each run as ONE launch of the chain interpreter."""
+    """Element-wise chains no named pattern covers, each run as ONE launch of a kernel compiled for it."""
     key, metric, unit, bound, dtype, scaling = "fused", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
     ROWS, COLS = 32768, 4096
-    description = ("fused element-wise chains on [32768,4096] fp32, one launch each: x*w+b (w, b per column), relu(x+bias), "
-                   "(a*b).sum(1), (x-mean)/sqrt(mean(x*x)+eps) (three row statements through the chain interpreter), and the "
-                   "backward of nn.softmax (its own kernel from y and dy)")
+    description = ("fused element-wise chains on [32768,4096] fp32, one launch of a kernel compiled for the chain each: x*w+b "
+                   "(w, b per column), relu(x+bias), (a*b).sum(1), (x-mean)/sqrt(mean(x*x)+eps) (three row statements), the "
+                   "gradient of LayerNorm w.r.t. x as jt.grad builds it (four row reduces), and the backward of nn.softmax "
+                   "(its own kernel from y and dy)")
     kernel_of = {"scale-shift": "chain_jit_map_kernel", "relu-bias": "chain_jit_map_kernel", "mul-rowsum": "chain_jit_rows_kernel",
-                 "centre-scale": "chain_jit_rows_kernel", "softmax-bwd": "softmax_bwd_reg_kernel"}
+                 "centre-scale": "chain_jit_rows_kernel", "layernorm-bwd": "chain_jit_rows_kernel",
+                 "softmax-bwd": "softmax_bwd_reg_kernel"}
     launches = {k: 1 for k in kernel_of}
 
     def work(self):
         n = self.ROWS * self.COLS * 4
         return {"scale-shift": 2 * n + 8 * self.COLS, "relu-bias": 2 * n + 4 * self.COLS, "mul-rowsum": 2 * n + 4 * self.ROWS,
-                "centre-scale": 2 * n, "softmax-bwd": 3 * n}
+                "centre-scale": 2 * n, "layernorm-bwd": 3 * n + 4 * self.COLS, "softmax-bwd": 3 * n}
 
     def setup(self, rank, world, jt, torch, multi):
         from jittor_b200 import nn
@@ -646,6 +648,8 @@ class FusedChains:
             return (x * y).sum(1)
         if name == "centre-scale":
             return (x - x.mean(1, keepdims=True)) / ((x * x).mean(1, keepdims=True) + 1e-5).sqrt()
+        if name == "layernorm-bwd":        # d LayerNorm / dx as jt.grad builds it from the per-op rules: four row reduces, one program
+            return self.jt.grad((self.nn.layer_norm(x, (x.shape[-1],), self.w, self.b) * y).sum(), x)
         sm = next((s for v, s in zip(self.x, self.sm) if v is x), None)
         if sm is None:
             sm = self.nn.softmax(x, -1)
@@ -679,6 +683,11 @@ class FusedChains:
             elif name == "centre-scale":
                 xd = x.astype(np.float64)
                 want = ((xd - xd.mean(1, keepdims=True)) / np.sqrt((xd * xd).mean(1, keepdims=True) + 1e-5)).astype(np.float32)
+            elif name == "layernorm-bwd":
+                xd, dyg = x.astype(np.float64), y.astype(np.float64) * w
+                rstd = 1 / np.sqrt(xd.var(1, keepdims=True) + 1e-5)
+                xh = (xd - xd.mean(1, keepdims=True)) * rstd
+                want = (rstd * (dyg - dyg.mean(1, keepdims=True) - xh * (dyg * xh).mean(1, keepdims=True))).astype(np.float32)
             else:
                 sm = ref.softmax(x, -1).astype(np.float64)
                 want = (sm * (y - (sm * y).sum(-1, keepdims=True))).astype(np.float32)

@@ -160,7 +160,7 @@ int b200jt_ternary(const b200jt_tensor* cond, const b200jt_tensor* x, const b200
  *   code        32-bit words  op | sub << 4 | kind << 10 | index << 13 | swap << 21 | result_dtype << 24  for an
  *               accumulator machine (result_dtype: enum b200jt_dtype of the node, float32 / bfloat16 / float16 / bool;
  *               every op computes in float32 and rounds to it). An operand is (kind, index): 1 input k, 2 constant (the
- *               float32 in the next word), 3 row value j, 4 temporary t (t < 3).
+ *               float32 in the next word), 3 row value j, 4 temporary t (t < 6).
  *                 1 LOAD o         acc = o                       2 UNARY (sub = u)     acc = u(acc)
  *                 3 BINARY (sub = b) o   acc = acc b o, or o b acc if swap
  *                 4 SELECT o1, then a word with op 0 holding o2      acc = acc != 0 ? o1 : o2

@@ -13,7 +13,7 @@
 //   STORE_ROW j        out[row] = rowval[j]
 // A chain is code for an accumulator machine: LOAD o (acc = o), UNARY u (acc = u(acc)), BINARY b, o (acc = acc b o, or
 // o b acc with the swap bit), SELECT o1, o2 (acc = acc ? o1 : o2), TSTORE t (tmp[t] = acc), where an operand o is an
-// input, a constant, a row value or one of three temporaries. The accumulator and the temporaries are fixed registers,
+// input, a constant, a row value or one of six temporaries. The accumulator and the temporaries are fixed registers,
 // so an instruction is dispatched on its op code only. All arithmetic is the float32 compute class of the element-wise
 // kernels (elementwise.cu), and every op's result is rounded to the dtype the reference's inference gives that node
 // (float32 / bfloat16 / float16 / bool), so a fused chain returns the same bits as the same ops run one by one.
@@ -246,7 +246,7 @@ __device__ __forceinline__ void apply_binary(int sub, int swap, float (&acc)[VEC
 }
 
 constexpr int kPre = 4;
-static_assert(kPre == 4 && kTmp == 3, "the operand selects below are written out for these sizes");         // input operands of a chain whose loads are issued before the chain is interpreted
+static_assert(kPre == 4, "the operand select below is written out for this size");         // input operands of a chain whose loads are issued before the chain is interpreted
 
 // Operand of word w into o[]; advances pc over an inline constant.
 __device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int64_t row, int64_t col, int n, const float* rowval,
@@ -262,7 +262,12 @@ __device__ __forceinline__ void fetch(const Program& P, int32_t w, int& pc, int6
     }
     if (kind == K_TMP) {
 #pragma unroll
-        for (int e = 0; e < VEC; e++) o[e] = idx == 0 ? tmp[0][e] : idx == 1 ? tmp[1][e] : tmp[2][e];
+        for (int e = 0; e < VEC; e++) {
+            float r = tmp[0][e];                      // selects on the value: no address depends on idx
+#pragma unroll
+            for (int t = 1; t < kTmp; t++) r = idx == t ? tmp[t][e] : r;
+            o[e] = r;
+        }
         return;
     }
     const float c = kind == K_CONST ? __int_as_float(P.code[++pc]) : rowval[idx];

@@ -9,7 +9,7 @@ namespace chain {
 constexpr int kMaxInputs = 8;
 constexpr int kMaxCode = 160;
 constexpr int kMaxRowVals = 8;
-constexpr int kTmp = 3;
+constexpr int kTmp = 6;
 constexpr int VEC = 8;
 
 // word = op | sub << 4 | operand kind << 10 | operand index << 13 | swap << 21 | result dtype << 24

@@ -19,7 +19,7 @@ import struct
 from . import _capi as C
 from .var import Var
 
-MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_TMP = 8, 160, 8, 3
+MAX_INPUTS, MAX_CODE, MAX_ROWVALS, MAX_TMP = 8, 160, 8, 6
 
 # word = op | sub << 4 | operand kind << 10 | operand index << 13 | swap << 21 | result dtype << 24
 CH_OPERAND, CH_LOAD, CH_UNARY, CH_BINARY, CH_SELECT, CH_TSTORE = 0, 1, 2, 3, 4, 5

@@ -232,3 +232,27 @@ def test_generated_sources_compile_for_sm_100a():
         src, ok, log = fusion.program_source(words, inputs, full, k, list(v.shape), v.dtype)
         assert ok, (i, log)
         assert ("chain_jit_map_kernel" in src) != ("chain_jit_rows_kernel" in src)
+
+
+def test_layernorm_backward_is_one_program():
+    """The gradient of LayerNorm with respect to its input, as jt.grad builds it from the per-op rules: four row reduces and
+    a store sweep over x, dy and gamma in ONE program (five temporaries), checked with the numpy interpreter against the
+    closed form."""
+    rng = np.random.default_rng(11)
+    X, DY, G, B = ph([6, 40]), ph([6, 40]), ph([40]), ph([40])
+    arrays = {id(X): rng.normal(size=(6, 40)).astype(np.float32), id(DY): rng.normal(size=(6, 40)).astype(np.float32),
+              id(G): (1 + 0.1 * rng.normal(size=40)).astype(np.float32), id(B): rng.normal(size=40).astype(np.float32)}
+    dx = jt.grad((nn.layer_norm(X, (40,), G, B) * DY).sum(), X)
+    prog = fusion.build_program(dx)
+    assert prog is not None
+    words, inputs, full, k, _ = prog
+    assert ops(words).count("RRED") == 4 and ops(words)[-1] == "STORE" and len(inputs) == 3
+    got = interpret(words, inputs, full, k, arrays).reshape(6, 40)
+    x, dy, g = (arrays[id(v)].astype(np.float64) for v in (X, DY, G))
+    mean, var = x.mean(1, keepdims=True), x.var(1, keepdims=True)
+    xh, rstd = (x - mean) / np.sqrt(var + 1e-5), 1 / np.sqrt(var + 1e-5)
+    dyg = dy * g
+    want = rstd * (dyg - dyg.mean(1, keepdims=True) - xh * (dyg * xh).mean(1, keepdims=True))
+    assert np.allclose(got, want, rtol=1e-3, atol=1e-4)
+    src, ok, log = fusion.program_source(words, inputs, full, k, [6, 40], "float32")
+    assert ok, log

@@ -224,3 +224,24 @@ def test_compiled_kernels_are_cached_per_program_not_per_size_or_constant(jt):
         check(got, np.exp(x * np.float32(k) + 1) * 2, False)
     c1, h1, f1 = stats()
     assert f1 == f0 and c1 - c0 <= 1 and h1 - h0 >= 2
+
+
+@pytest.mark.parametrize("shape", [(512, 1024), (37, 771), (64, 4096)])
+def test_layernorm_backward_runs_as_one_kernel(jt, shape):
+    """d LayerNorm / dx built by jt.grad from the per-op rules: one plan, the same result as op by op and as torch autograd."""
+    from jittor_b200 import nn
+    rng = np.random.default_rng(shape[1])
+    x = rng.normal(size=shape).astype(np.float32)
+    dy = rng.normal(size=shape).astype(np.float32)
+    g = (1 + 0.1 * rng.normal(size=shape[1])).astype(np.float32)
+    b = rng.normal(size=shape[1]).astype(np.float32)
+
+    def build(X, DY, G, B):
+        return jt.grad((nn.layer_norm(X, (shape[1],), G, B) * DY).sum(), X)
+
+    fused, unfused, plans = run_both(jt, build, [x, dy, g, b], reduces=True)
+    assert plans == 1
+    check(fused, unfused, False, rtol=1e-4)
+    xt = torch.from_numpy(x).requires_grad_()
+    torch.nn.functional.layer_norm(xt, (shape[1],), torch.from_numpy(g), torch.from_numpy(b), 1e-5).backward(torch.from_numpy(dy))
+    check(fused, xt.grad.numpy(), False, rtol=1e-4)
