@@ -588,6 +588,29 @@ class MetaOps:
     def e2e_bytes(self, names):
         return len(names) * self.hx.numel() * 4, 0
 
+    def verify(self, env):
+        """Untimed: every part at full size on the device, a band of it against the numpy oracle (bit-exact for the gathers)."""
+        from oracle import meta_ops_ref as ref
+        x = self.x[0]
+        xh = x.torch()[:96].cpu().numpy()                           # the first rows decide the first rows / columns of each result
+        ok = True
+        got = self._op("reindex-pad", x).torch()[:96].cpu().numpy()
+        ok = ok and bool(np.array_equal(got, ref.reindex(xh, [96, self.COLS + 4], ["i0", "i1-2"])))
+        got = self._op("reindex-transpose", x).torch()[:, :96].cpu().numpy()
+        ok = ok and bool(np.array_equal(got, xh.T))
+        xs = self.xs.numpy()
+        got = self._op("reindex-conv-window", x).numpy()
+        ok = ok and bool(np.array_equal(got, ref.reindex(xs, self.WIN, ["i0", "i2", "i3*1-1+i5*1", "i4*1-1+i6*1"])))
+        got = self._op("reduce-row-sum", x).torch()[:96].cpu().numpy()
+        want = xh.astype(np.float64).sum(1)
+        ok = ok and bool((np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-5 * np.abs(want).max()).all())
+        got = self._op("reduce-col-sum", x).numpy()
+        want = x.torch().double().sum(0).cpu().numpy()
+        ok = ok and bool((np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-5 * np.abs(want).max()).all())
+        got = self._op("broadcast-add", x).torch()[:96].cpu().numpy()
+        ok = ok and bool(np.array_equal(got, xh + self.b.numpy()))
+        return ok
+
     def cpu(self, names):
         rows = 2048
         x = np.random.default_rng(9).normal(size=(rows, self.COLS)).astype(np.float32)
@@ -765,6 +788,25 @@ class NextOps:
 
     def e2e_bytes(self, names):
         return len(names) * self.hx.numel() * 4, 0
+
+    def verify(self, env):
+        """Untimed: the four parts at full size on the device; two images of the pooling parts and the whole gather /
+        scatter-add against the numpy oracle."""
+        from oracle import meta_ops_ref as ref
+        torch = self.torch
+        xh = self.x.torch()[:2, :4].cpu().numpy()
+        y = self._op("maxpool-fwd", self.x).torch()
+        ok = bool(np.array_equal(y[:2, :4].cpu().numpy(), ref.pool2d(xh, 3, "maximum", 2, 1)))
+        dyh = self.dy.torch()[:2, :4].cpu().numpy()
+        dx = self._op("maxpool-bwd", self.x).torch()[:2, :4].cpu().numpy()
+        want = ref.pool2d_backward(xh, dyh, 3, "maximum", 2, 1)
+        ok = ok and bool((np.abs(dx - want) <= 1e-5 * np.abs(want) + 1e-5 * np.abs(want).max()).all())
+        table, idx, vals = self.table.torch(), self.idx.torch().long(), self.vals.torch()
+        ok = ok and bool(torch.equal(self._op("getitem-rows", self.x).torch(), table[idx]))
+        want_t = table.clone()
+        want_t[idx] += vals                                             # the picked rows are distinct (a permutation prefix)
+        ok = ok and bool(torch.allclose(self._op("setitem-add-rows", self.x).torch(), want_t, rtol=1e-6, atol=1e-6))
+        return ok
 
     def cpu(self, names):
         from oracle import meta_ops_ref as ref
