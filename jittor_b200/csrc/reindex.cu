@@ -204,6 +204,37 @@ reindex_rows_kernel(const T* __restrict__ x, T* __restrict__ y, const __grid_con
             }
         }
         const int active = (int)min((int64_t)32, rows - row0);
+        const int64_t nv = inner / V;                       // 16-byte vectors per run
+        if (vec_shape && nv <= 32 && (32 % nv) == 0) {
+            // short runs (an embedding row of 64 floats is 16 vectors): the warp copies 32 / nv runs per access and keeps eight
+            // accesses in flight, instead of one run per access with half of the lanes idle
+            const int per = 32 / (int)nv, sub = lane / (int)nv, li = lane % (int)nv;
+            constexpr int U = 8;
+            for (int k0 = 0; k0 < active; k0 += per * U) {
+                uint4 v[U];
+                long long o[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int k = k0 + u * per + sub;
+                    o[u] = __shfl_sync(0xffffffffu, off, k & 31);
+                    if (k < active) {
+                        if (o[u] >= 0 && o[u] % V == 0) v[u] = reinterpret_cast<const uint4*>(x + o[u])[li];
+                        else if (o[u] < 0) v[u] = f;
+                        else {                              // a run that starts off a 16-byte boundary: element by element
+                            T* t = reinterpret_cast<T*>(&v[u]);
+#pragma unroll
+                            for (int e = 0; e < V; e++) t[e] = x[o[u] + (long long)li * V + e];
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int k = k0 + u * per + sub;
+                    if (k < active) reinterpret_cast<uint4*>(y + (row0 + k) * inner)[li] = v[u];
+                }
+            }
+            continue;
+        }
         for (int k = 0; k < active; k++) {
             const long long o = __shfl_sync(0xffffffffu, off, k);
             T* dst = y + (row0 + k) * inner;
