@@ -75,6 +75,35 @@ rr_rows_kernel(const T* __restrict__ y, T* __restrict__ x, const __grid_constant
             }
         }
         const int active = (int)min((int64_t)32, rows - row0);
+        if constexpr (std::is_same<T, float>::value) {
+            // float add on short aligned runs (a 64-float row is 16 vectors): the warp covers 32 / nv runs per access, one
+            // 16-byte vector reduction per lane instead of four scalar ones, four runs' loads in flight
+            const int64_t nv = inner / 4;
+            if (op == OP_ADD && inner % 4 == 0 && nv <= 32 && (32 % nv) == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
+                const int per = 32 / (int)nv, sub = lane / (int)nv, li = lane % (int)nv;
+                constexpr int U = 4;
+                for (int k0 = 0; k0 < active; k0 += per * U) {
+                    float4 v[U];
+                    long long o[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const int k = k0 + u * per + sub;
+                        o[u] = __shfl_sync(0xffffffffu, off, k & 31);
+                        if (k >= active) o[u] = -1;
+                        if (o[u] >= 0) v[u] = reinterpret_cast<const float4*>(y + (row0 + k) * inner)[li];
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        if (o[u] < 0) continue;
+                        float* dst = x + o[u] + li * 4;
+                        if (o[u] % 4 == 0)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[u].x), "f"(v[u].y), "f"(v[u].z), "f"(v[u].w) : "memory");
+                        else { atomicAdd(dst, v[u].x); atomicAdd(dst + 1, v[u].y); atomicAdd(dst + 2, v[u].z); atomicAdd(dst + 3, v[u].w); }
+                    }
+                }
+                continue;
+            }
+        }
         for (int k = 0; k < active; k++) {
             const long long o = __shfl_sync(0xffffffffu, off, k);
             if (o < 0) continue;
