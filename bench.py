@@ -980,6 +980,35 @@ def measure(wl, args, env, headline):
     barrier()
     clocks.__exit__()
     rep_ms = sorted(a.elapsed_time(b) for a, b in pairs)
+    # (4) per-part times once more, each part replayed from its own CUDA graph: the direct launches of (1) include the
+    # Python launch path, which for small or graph-building parts (a conv of 25 us, a jt.grad chain) is longer than the kernel
+    parts_timing = "direct launches, an event after every part"
+    if graph is not None:
+        try:
+            graphed = {}
+            for nm in names:
+                barrier()
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1):
+                    with step_context():
+                        keep1 = wl.run(nm)                   # noqa: F841
+                g1.replay()
+                barrier()
+                pp = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(psteps)]
+                for a, b in pp:
+                    if flush:
+                        flush()
+                    a.record()
+                    g1.replay()
+                    b.record()
+                barrier()
+                graphed[nm] = sum(a.elapsed_time(b) for a, b in pp) / psteps
+                del g1, keep1
+            part_ms = graphed
+            parts_timing = "each part replayed from its own CUDA graph"
+        except Exception as exc:                     # noqa: BLE001
+            print(f"[bench] per-part graphs unavailable ({type(exc).__name__}: {exc}); keeping the direct per-part times", file=sys.stderr)
+            torch.cuda.synchronize()
     status = jt._capi.lib.b200jt_device_status()
 
     # ---- end to end: pinned host -> device -> kernels -> pinned host ------------------------------------
@@ -1082,6 +1111,7 @@ def measure(wl, args, env, headline):
         "parts": parts,
         "stability": {"repetitions": reps, "ms_median": p50, "ms_p10": p10, "ms_p90": p90},
         "cuda_graph": graph is not None,
+        "parts_timing": parts_timing,
         "device_status": status,
     }
     if parity is not None:
