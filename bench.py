@@ -983,7 +983,8 @@ def measure(wl, args, env, headline):
     # (4) per-part times once more, each part replayed from its own CUDA graph: the direct launches of (1) include the
     # Python launch path, which for small or graph-building parts (a conv of 25 us, a jt.grad chain) is longer than the kernel
     parts_timing = "direct launches, an event after every part"
-    if graph is not None:
+    # (a part whose collective runs on the side stream is not captured on its own: its times stay those of (1))
+    if graph is not None and not (multi and hasattr(wl, "run_step")):
         try:
             graphed = {}
             for nm in names:
