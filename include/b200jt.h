@@ -243,6 +243,21 @@ int b200jt_conv2d(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_t
                   int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
                   float* stats, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same convolution with the layout strings of the reference's relay (CudnnConvOp(..., string xformat, string wformat,
+ * string yformat), python/jittor/extern/cuda/cudnn/ops/cudnn_conv_op.h; ConvTuner derives them,
+ * python/jittor/src/opt/tuner/conv_tuner.cc:292-341): xformat / yformat "abcd" (NCHW) or "acdb" (NHWC, shape given as
+ * [N, H, W, C]), wformat "oihw" or "ohwi" ([Cout, KH, KW, Cin]); an empty yformat follows xformat. groups == 1.
+ * Layouts other than abcd / oihw run on the tensor-core kernel only (bfloat16, in channels a multiple of 8 and >= 64, out
+ * channels >= 64): NHWC is that kernel's native operand layout, so an acdb input skips the layout pass and an acdb output is
+ * written by the epilogue directly -- a conv -> conv chain kept in acdb pays no layout pass at all. */
+size_t b200jt_conv2d_formats_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                                       int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                                       const char* xformat, const char* wformat, const char* yformat);
+int b200jt_conv2d_formats(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                          int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                          const char* xformat, const char* wformat, const char* yformat,
+                          float* stats, void* workspace, size_t workspace_bytes, void* stream);
+
 /* y = conv_transpose2d(x, w): y[n,o,ho,wo] = sum x[n,i,hi,wi] * w[i,o,kh,kw] over ho = hi*stride - pad + kh*dil (same for w),
  * x NCHW, w [Cin, Cout/groups, KH, KW], fp32 accumulation. y's spatial shape carries the output_padding. Replaces the
  * relay CudnnConvBackwardXOp(Var* w, Var* y, int height, int width, int strideh, ..., int groups, ...),

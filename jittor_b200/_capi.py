@@ -76,6 +76,9 @@ SIGNATURES = [
     ("b200jt_device_status", _i, []),
     ("b200jt_conv2d_workspace", _sz, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i]),
     ("b200jt_conv2d", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i, _FP, _vp, _sz, _vp]),
+    ("b200jt_conv2d_formats_workspace", _sz, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p]),
+    ("b200jt_conv2d_formats", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p,
+                                   _FP, _vp, _sz, _vp]),
     ("b200jt_conv2d_transpose", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_conv2d_backward_w", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_bn_stats", _i, [_TP, _FP, _vp]),

@@ -95,6 +95,64 @@ static int conv_shape(const b200jt_tensor* x, const b200jt_tensor* w, const b200
     return 0;
 }
 
+// Layout strings of the reference's conv relays: a = batch / out channel, b = in channel, c/d = rows / columns.
+// Returns the descriptors re-expressed as NCHW / OIHW shapes (the data stays where it is) and the layout flags.
+static int conv_formats(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                        const char* xformat, const char* wformat, const char* yformat,
+                        b200jt_tensor* xl, b200jt_tensor* wl, b200jt_tensor* yl, ConvLayout* lay) {
+    B200JT_CHECK_ARG(valid_tensor(x) && valid_tensor(w) && valid_tensor(y) && x->ndim == 4 && w->ndim == 4 && y->ndim == 4,
+                     "conv2d takes 4-d x, w, y");
+    const std::string xf = xformat && *xformat ? xformat : "abcd", wf = wformat && *wformat ? wformat : "oihw";
+    const std::string yf = yformat && *yformat ? yformat : xf;               // an empty yformat follows x, as in the reference
+    B200JT_CHECK_ARG(xf == "abcd" || xf == "acdb", "xformat must be abcd or acdb, got " + xf);
+    B200JT_CHECK_ARG(yf == "abcd" || yf == "acdb", "yformat must be abcd or acdb, got " + yf);
+    B200JT_CHECK_ARG(wf == "oihw" || wf == "ohwi", "wformat must be oihw or ohwi, got " + wf);
+    lay->x_nhwc = xf == "acdb"; lay->y_nhwc = yf == "acdb"; lay->w_ohwi = wf == "ohwi";
+    auto to_nchw = [](const b200jt_tensor* t, bool last_is_channel, b200jt_tensor* o) {
+        *o = *t;
+        if (last_is_channel) { o->shape[1] = t->shape[3]; o->shape[2] = t->shape[1]; o->shape[3] = t->shape[2]; }
+    };
+    to_nchw(x, lay->x_nhwc, xl); to_nchw(w, lay->w_ohwi, wl); to_nchw(y, lay->y_nhwc, yl);
+    return 0;
+}
+
+extern "C" size_t b200jt_conv2d_formats_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                                                  int sh, int sw, int ph, int pw, int dh, int dw,
+                                                  const char* xformat, const char* wformat, const char* yformat) {
+    b200jt_tensor xl, wl, yl; ConvLayout lay; ConvShape s;
+    if (conv_formats(x, w, y, xformat, wformat, yformat, &xl, &wl, &yl, &lay)) return 0;
+    if (conv_shape(&xl, &wl, &yl, sh, sw, ph, pw, dh, dw, 1, &s)) return 0;
+    if (x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr)) return conv2d_tc_workspace(s);
+    return 0;
+}
+
+extern "C" int b200jt_conv2d_formats(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
+                                     int sh, int sw, int ph, int pw, int dh, int dw,
+                                     const char* xformat, const char* wformat, const char* yformat,
+                                     float* stats, void* workspace, size_t workspace_bytes, void* stream) {
+    b200jt_tensor xl, wl, yl; ConvLayout lay; ConvShape s;
+    int rc = conv_formats(x, w, y, xformat, wformat, yformat, &xl, &wl, &yl, &lay);
+    if (rc) return rc;
+    if (!lay.x_nhwc && !lay.w_ohwi && !lay.y_nhwc)
+        return b200jt_conv2d(x, w, y, sh, sw, ph, pw, dh, dw, 1, stats, workspace, workspace_bytes, stream);
+    rc = conv_shape(&xl, &wl, &yl, sh, sw, ph, pw, dh, dw, 1, &s);
+    if (rc) return rc;
+    if (numel(y) == 0) return 0;
+    if (!(x->dtype == B200JT_BFLOAT16 && conv2d_tc_supported(s, x->ptr, w->ptr, y->ptr) && ((uintptr_t)y->ptr % 16 == 0)))
+        return fail(-5, "b200jt_conv2d_formats: acdb / ohwi layouts run on the tensor-core kernel only (bfloat16, in channels a "
+                        "multiple of 8 and >= 64, out channels >= 64, at least 1024 output pixels, 16-byte aligned tensors)");
+    const size_t need = conv2d_tc_workspace(s);
+    B200JT_CHECK_ARG(workspace_bytes >= need && workspace, "workspace too small: need " + std::to_string(need) + " bytes");
+    rc = conv2d_tc(x->ptr, w->ptr, y->ptr, stats, s, workspace, (cudaStream_t)stream, lay);
+    if (rc == 1) return 0;             // statistics came out of the conv epilogue
+    if (rc) return rc;
+    if (stats) {
+        // wider than the epilogue keeps per CTA: statistics of the stored values by a separate pass are only built for NCHW
+        return fail(-5, "b200jt_conv2d_formats: fused statistics need out channels <= 512 with an acdb output");
+    }
+    return 0;
+}
+
 extern "C" size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                                           int sh, int sw, int ph, int pw, int dh, int dw, int groups) {
     ConvShape s;

@@ -49,12 +49,13 @@ __device__ __forceinline__ void patch_coords(const ConvArgs& A, int64_t q, int& 
     w0 = (r % A.tiles_w) * PATCH;
 }
 
-// TMA_OUT: the epilogue stages 64 channels x 128 pixels of bf16 in shared memory ([patch][channel][8x8]) and writes
+// OUT == 1: the epilogue stages 64 channels x 128 pixels of bf16 in shared memory ([patch][channel][8x8]) and writes
 // them to y (NCHW) with two 4-D TMA box stores; edges are clipped by the tensor map. Needs OW % 8 == 0 (16-byte row
-// pitch); otherwise the lanes store their values directly.
+// pitch); otherwise (OUT == 0) the lanes store their values directly. OUT == 2: y is NHWC ("acdb"), a lane stores the 32
+// consecutive channels of its pixel as four 16-byte vectors.
 // BN_T: output channels per tile (256, or 128 when that fills the last wave of the persistent grid better; the
 // shared-memory ring keeps the 256-channel stage size either way).
-template <bool TMA_OUT, int BN_T>
+template <int OUT, int BN_T>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_y,
@@ -70,6 +71,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* sstat = (float*)(smem + STAGES * STAGE_BYTES + 256);      // [2][STATS_MAX_CO] per-CTA channel sums
     unsigned char* stage_out = smem + STAGES * STAGE_BYTES + 256 + STATS_BYTES;   // [2 patches][64 ch][64 px] bf16
+    constexpr bool TMA_OUT = OUT == 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total = A.tiles_m * A.tiles_n;
@@ -188,6 +190,24 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         sp[e * 64] = b;
                         f[e] = (valid && co0 + e < A.Co) ? __bfloat162float(b) : 0.f;
                     }
+                } else if (OUT == 2) {
+                    // NHWC: this lane's pixel, channels co0 .. co0 + 31 are contiguous
+                    __align__(16) __nv_bfloat16 row[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        row[e] = __float2bfloat16(__uint_as_float(v[e]));
+                        f[e] = (valid && co0 + e < A.Co) ? __bfloat162float(row[e]) : 0.f;
+                    }
+                    if (valid) {
+                        __nv_bfloat16* yq = y + (((int64_t)n * A.OH + oh) * A.OW + ow) * A.Co + co0;
+                        if (co0 + 32 <= A.Co && (A.Co & 7) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 4; q++) reinterpret_cast<uint4*>(yq)[q] = reinterpret_cast<const uint4*>(row)[q];
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; e++) if (co0 + e < A.Co) yq[e] = row[e];
+                        }
+                    }
                 } else {
 #pragma unroll
                     for (int e = 0; e < 32; e++) {
@@ -266,7 +286,7 @@ conv_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 __global__ void __launch_bounds__(256)
 transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int R, int Cn, int wz,
                               const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wt, int Co, int C, int taps,
-                              float* __restrict__ zero, int n_zero) {
+                              float* __restrict__ zero, int n_zero, int w_ohwi) {
     __shared__ __nv_bfloat16 tile[64][66];
     if (zero && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)       // the statistics the conv epilogue adds into
         for (int i = threadIdx.x; i < n_zero; i += blockDim.x) zero[i] = 0.f;
@@ -277,7 +297,7 @@ transpose_bf16_batched_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat1
         for (int64_t i = blk * blockDim.x + threadIdx.x; i < n; i += nblk * blockDim.x) {
             const int c = (int)(i % C); const int64_t t2 = i / C;
             const int co = (int)(t2 % Co); const int tap = (int)(t2 / Co);
-            wt[i] = w[((int64_t)co * C + c) * taps + tap];
+            wt[i] = w_ohwi ? w[((int64_t)co * taps + tap) * C + c] : w[((int64_t)co * C + c) * taps + tap];
         }
         return;
     }
@@ -364,10 +384,12 @@ size_t conv2d_tc_workspace(const ConvShape& s) {
     return xb + wb + 1024;
 }
 
-int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st) {
+int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st,
+              const ConvLayout& lay) {
     using namespace tcconv;
     unsigned char* ws = (unsigned char*)(((uintptr_t)workspace + 1023) & ~(uintptr_t)1023);
-    __nv_bfloat16* xt = (__nv_bfloat16*)ws;
+    // NHWC ("acdb") activations are what the kernel reads: no staging pass for x then
+    __nv_bfloat16* xt = lay.x_nhwc ? (__nv_bfloat16*)const_cast<void*>(x) : (__nv_bfloat16*)ws;
     __nv_bfloat16* wt = (__nv_bfloat16*)(ws + (((size_t)s.N * s.H * s.W * s.C * 2 + 1023) & ~(size_t)1023));
     const int HW = s.H * s.W;
     {   // x[N][C][HW] -> xt[N][HW][C], and the weights tap-major, in one launch
@@ -375,10 +397,10 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
         const unsigned gx = (unsigned)((HW + 63) / 64), gy = (unsigned)((s.C + 63) / 64);
         const int64_t per_slice = (int64_t)gx * gy * 256;
         const unsigned wz = (unsigned)std::min<int64_t>(32, std::max<int64_t>(1, (nw + per_slice - 1) / per_slice));
-        dim3 g(gx, gy, (unsigned)s.N + wz);
+        dim3 g(gx, gy, (lay.x_nhwc ? 0u : (unsigned)s.N) + wz);          // the first wz slices re-order the weights
         float* zero = (stats && s.Co <= STATS_MAX_CO) ? stats : nullptr;   // zeroed here instead of by a memset node
         transpose_bf16_batched_kernel<<<g, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW, (int)wz,
-                                                          (const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW, zero, 2 * s.Co);
+                                                          (const __nv_bfloat16*)w, wt, s.Co, s.C, s.KH * s.KW, zero, 2 * s.Co, lay.w_ohwi ? 1 : 0);
         B200JT_LAUNCH_CHECK();
     }
     ConvArgs A;
@@ -399,21 +421,22 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        const void* kernels[] = {(const void*)conv_bf16_kernel<true, 256>, (const void*)conv_bf16_kernel<false, 256>,
-                                 (const void*)conv_bf16_kernel<true, 128>, (const void*)conv_bf16_kernel<false, 128>};
+        const void* kernels[] = {(const void*)conv_bf16_kernel<1, 256>, (const void*)conv_bf16_kernel<0, 256>,
+                                 (const void*)conv_bf16_kernel<1, 128>, (const void*)conv_bf16_kernel<0, 128>,
+                                 (const void*)conv_bf16_kernel<2, 256>, (const void*)conv_bf16_kernel<2, 128>};
         for (const void* k : kernels)
             if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     });
     B200JT_CUDA(attr_err);
     // TMA stores need a 16-byte aligned base and row pitch
-    const bool tma_out = (s.OW % 8 == 0) && ((uintptr_t)y % 16 == 0);
+    const bool tma_out = !lay.y_nhwc && (s.OW % 8 == 0) && ((uintptr_t)y % 16 == 0);
     CUtensorMap my = mx;
     if (tma_out && !make_map_y(&my, y, s)) return fail(-4, "conv2d: cuTensorMapEncodeTiled failed (y)");
     float* fused = (stats && s.Co <= STATS_MAX_CO) ? stats : nullptr;
     const int total = A.tiles_m * A.tiles_n;
     const int grid = total < kNumSMs ? total : kNumSMs;
-    auto kern = bn == 256 ? (tma_out ? conv_bf16_kernel<true, 256> : conv_bf16_kernel<false, 256>)
-                          : (tma_out ? conv_bf16_kernel<true, 128> : conv_bf16_kernel<false, 128>);
+    auto kern = bn == 256 ? (lay.y_nhwc ? conv_bf16_kernel<2, 256> : tma_out ? conv_bf16_kernel<1, 256> : conv_bf16_kernel<0, 256>)
+                          : (lay.y_nhwc ? conv_bf16_kernel<2, 128> : tma_out ? conv_bf16_kernel<1, 128> : conv_bf16_kernel<0, 128>);
     kern<<<grid, THREADS, SMEM_BYTES, st>>>(mx, mw, my, (__nv_bfloat16*)y, fused, A);
     B200JT_LAUNCH_CHECK();
     return fused ? 1 : 0;      // 1: statistics were produced by the epilogue

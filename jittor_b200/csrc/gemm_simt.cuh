@@ -8,6 +8,8 @@ struct ConvShape {
     int N, C, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
     int groups = 1;
 };
+// Memory layouts other than the default NCHW / OIHW (tensor-core path only): x and y as NHWC ("acdb"), w as OHWI ("ohwi").
+struct ConvLayout { bool x_nhwc = false, w_ohwi = false, y_nhwc = false; };
 
 int matmul_simt(const void* a, const void* b, void* c, int dtype, int64_t M, int64_t N, int64_t K,
                 bool trans_a, bool trans_b, cudaStream_t st);
@@ -27,7 +29,8 @@ int tc_status_fetch_and_clear();
 bool conv2d_tc_supported(const ConvShape& s, const void* x, const void* w, const void* y);
 size_t conv2d_tc_workspace(const ConvShape& s);
 // returns < 0 / > 1 on error, 0 on success, 1 on success with `stats` filled by the epilogue
-int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st);
+int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st,
+              const ConvLayout& lay = ConvLayout());
 int tcconv_status_fetch_and_clear();
 int peer_status_fetch_and_clear();          // peer_allreduce.cu
 

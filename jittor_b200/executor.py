@@ -464,6 +464,24 @@ def run_conv2d(x, w, geo, out_dtype, stats=None, groups=1):
     return _cast(out, out_dtype)
 
 
+def run_conv2d_formats(x, w, geo, xformat, wformat, yformat, out_dtype):
+    """Convolution with the relay's layout strings (cudnn_conv_op.h): x / y "abcd" or "acdb", w "oihw" or "ohwi"."""
+    sh, sw, ph, pw, dh, dw = geo
+    yformat = yformat or xformat
+    N, Ci, H, W = x.shape if xformat == "abcd" else (x.shape[0], x.shape[3], x.shape[1], x.shape[2])
+    Co, KH, KW = (w.shape[0], w.shape[2], w.shape[3]) if wformat == "oihw" else (w.shape[0], w.shape[1], w.shape[2])
+    OH = (H + 2 * ph - KH * dh + dh - 1) // sh + 1
+    OW = (W + 2 * pw - KW * dw + dw - 1) // sw + 1
+    xd, wd = x._data, _cast(w._data, x.dtype)
+    out = _empty([N, Co, OH, OW] if yformat == "abcd" else [N, OH, OW, Co], x.dtype)
+    args = (C.desc(xd), C.desc(wd), C.desc(out), sh, sw, ph, pw, dh, dw, xformat.encode(), wformat.encode(), yformat.encode())
+    nbytes = C.lib.b200jt_conv2d_formats_workspace(*args)
+    ws, wsp = _workspace(nbytes)
+    C.check(C.lib.b200jt_conv2d_formats(*args, None, wsp, nbytes, C.stream_ptr()),
+            f"conv2d x{list(x.shape)} ({xformat}) w{list(w.shape)} ({wformat}) -> {yformat} geo{geo}")
+    return _cast(out, out_dtype)
+
+
 def _match_conv(v):
     got = _mul_operands(v, 7)
     if got is None:

@@ -84,10 +84,25 @@ def _register_builtins():
 
     def cudnn_conv(x, w, strideh, stridew, paddingh, paddingw, dilationh=1, dilationw=1, groups=1,
                    xformat="abcd", wformat="oihw", yformat=""):
-        """Relay signature of conv_tuner.cc:370-373 (NCHW / OIHW only)."""
-        if xformat != "abcd" or wformat != "oihw" or yformat not in ("", "abcd"):
-            raise NotImplementedError("only abcd / oihw layouts")
-        return nn.conv2d(x, w, None, (strideh, stridew), (paddingh, paddingw), (dilationh, dilationw), groups)
+        """Relay signature of conv_tuner.cc:370-373. Layouts as ConvTuner derives them (conv_tuner.cc:292-341): x / y "abcd"
+        (NCHW) or "acdb" (NHWC, the tensor-core kernel's own operand layout: no layout pass on that side), w "oihw" or
+        "ohwi"; an empty yformat follows xformat."""
+        if xformat == "abcd" and wformat == "oihw" and yformat in ("", "abcd"):
+            return nn.conv2d(x, w, None, (strideh, stridew), (paddingh, paddingw), (dilationh, dilationw), groups)
+        if xformat not in ("abcd", "acdb") or wformat not in ("oihw", "ohwi") or yformat not in ("", "abcd", "acdb"):
+            raise ValueError(f"unknown conv layouts x {xformat!r} w {wformat!r} y {yformat!r}")
+        if groups != 1:
+            raise NotImplementedError("acdb / ohwi layouts with groups > 1")
+        from . import executor
+        x, w = V.to_var(x), V.to_var(w)
+        yf = yformat or xformat
+        n, h, wd_ = (x.shape[0], x.shape[2], x.shape[3]) if xformat == "abcd" else (x.shape[0], x.shape[1], x.shape[2])
+        co, kh, kw = (w.shape[0], w.shape[2], w.shape[3]) if wformat == "oihw" else (w.shape[0], w.shape[1], w.shape[2])
+        oh = (h + 2 * paddingh - kh * dilationh + dilationh - 1) // strideh + 1
+        ow = (wd_ + 2 * paddingw - kw * dilationw + dilationw - 1) // stridew + 1
+        shape = [n, co, oh, ow] if yf == "abcd" else [n, oh, ow, co]
+        geo = (strideh, stridew, paddingh, paddingw, dilationh, dilationw)
+        return _relayed(x, w, shape, lambda xd, wd: executor.run_conv2d_formats(x, w, geo, xformat, wformat, yf, x.dtype))
 
     def _relayed(x, w_or_dy, shape, run):
         """A Var produced by one relay launch (inputs synced by the executor first)."""

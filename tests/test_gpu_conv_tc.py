@@ -235,3 +235,52 @@ def test_config4_conv_bn_relu_full_size(c5_data):
     want = np.maximum(conv * wgt.cpu().numpy()[None] + bias.cpu().numpy()[None], 0)
     got = torch.stack([zt[n, :, oh, ow] for n, oh, ow in pix]).float().cpu().numpy()
     check(got, bf16_round(want), False, rtol=2e-2)
+
+
+# (x NCHW shape, w OIHW shape, stride, padding, xformat, wformat, yformat): NHWC ("acdb") activations are the kernel's own
+# operand layout (no layout pass on that side), "ohwi" weights only change the re-ordering pass, an acdb output is written
+# by the epilogue as 32 contiguous channels per pixel (vector stores, or element stores for a ragged last chunk)
+LAYOUTS = [
+    ((4, 64, 16, 16), (64, 64, 3, 3), 1, 1, "acdb", "oihw", "acdb"),
+    ((4, 64, 16, 16), (64, 64, 3, 3), 1, 1, "acdb", "ohwi", "abcd"),
+    ((4, 64, 16, 16), (64, 64, 3, 3), 1, 1, "abcd", "ohwi", "acdb"),
+    ((2, 96, 28, 28), (192, 96, 3, 3), 1, 1, "acdb", "ohwi", ""),
+    ((3, 128, 21, 19), (72, 128, 3, 3), 1, 1, "acdb", "oihw", "acdb"),
+    ((8, 72, 28, 28), (100, 72, 5, 5), 2, 2, "acdb", "ohwi", "acdb"),
+    ((2, 256, 28, 28), (320, 256, 1, 1), 1, 0, "acdb", "oihw", "acdb"),
+]
+
+
+@pytest.mark.parametrize("xs,wshape,stride,pad,xf,wf,yf", LAYOUTS)
+def test_conv_layouts_of_the_relay_against_oracle(xs, wshape, stride, pad, xf, wf, yf):
+    """cudnn_conv with the layout strings ConvTuner derives (python/jittor/src/opt/tuner/conv_tuner.cc:292-341)."""
+    import jittor_b200 as jt
+    from jittor_b200 import _capi as C
+    rng = np.random.default_rng(sum(xs) + sum(wshape) + stride)
+    x = bf16_round(rng.normal(size=xs))
+    w = bf16_round(rng.normal(size=wshape) * np.sqrt(2.0 / (wshape[1] * wshape[2] * wshape[3])))
+    want = bf16_round(co.conv2d(x, w, stride, pad, 1))
+    xin = x if xf == "abcd" else np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+    win = w if wf == "oihw" else np.ascontiguousarray(w.transpose(0, 2, 3, 1))
+    conv = jt.get_op_info("cudnn_conv").get_constructor()
+    xv = jt.array(torch.from_numpy(xin).bfloat16())
+    wv = jt.array(torch.from_numpy(win).bfloat16())
+    y = conv(xv, wv, stride, stride, pad, pad, 1, 1, 1, xf, wf, yf)
+    got = y.torch().float().cpu().numpy()
+    if (yf or xf) == "acdb":
+        assert list(got.shape) == [want.shape[0], want.shape[2], want.shape[3], want.shape[1]]
+        got = got.transpose(0, 3, 1, 2)
+    check(np.ascontiguousarray(got), want, False, rtol=2e-2)
+    assert C.lib.b200jt_device_status() == 0
+
+
+def test_conv_layouts_outside_the_tensor_core_path_are_refused():
+    import jittor_b200 as jt
+    from jittor_b200 import _capi as C
+    conv = jt.get_op_info("cudnn_conv").get_constructor()
+    x = jt.array(torch.randn(2, 8, 8, 16).bfloat16())            # 16 channels: not a tensor-core shape
+    w = jt.array(torch.randn(32, 16, 3, 3).bfloat16())
+    with pytest.raises(C.B200Error, match="tensor-core kernel only"):
+        conv(x, w, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb").sync()
+    with pytest.raises(ValueError):
+        conv(x, w, 1, 1, 1, 1, 1, 1, 1, "bacd", "oihw", "")
