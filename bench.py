@@ -448,15 +448,18 @@ class C5ConvBN:
     key, metric, unit, bound, dtype, scaling = "c5", "conv TFLOP/s", "TFLOP/s", "tensor", "bf16 (fp32 accumulate)", "strong"
     N, C, H, W, CO = 256, 256, 56, 56, 256
     description = ("config 4: reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] s1 p1, then global BatchNorm statistics "
-                   "(one NCCL all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks")
-    kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)"}
-    launches = {"conv": 2, "conv-bn-relu": 3}
+                   "(one all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks; third part: the same "
+                   "convolution through the relay with acdb (NHWC) activations in and out, the layout ConvTuner derives for "
+                   "tensor-core kernels, which needs no layout pass")
+    kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)",
+                 "conv-acdb": "conv_bf16_kernel (tcgen05)"}
+    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2}
     all_reduced = ("conv-bn-relu",)
-    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6}
+    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6, "conv-acdb": 776.5e6}
 
     def work(self):
         f = 2 * self.N * self.H * self.W * self.CO * self.C * 9
-        return {"conv": f, "conv-bn-relu": f}
+        return {"conv": f, "conv-bn-relu": f, "conv-acdb": f}
 
     def setup(self, rank, world, jt, torch, multi):
         from jittor_b200 import nn
@@ -471,12 +474,17 @@ class C5ConvBN:
         self.bn.weight.sync()
         self.bn.bias.sync()
         self.out = torch.empty(n, self.CO, self.H, self.W, dtype=torch.bfloat16).pin_memory()
-        return ["conv", "conv-bn-relu"]
+        self.hxn = self.hx.permute(0, 2, 3, 1).contiguous().pin_memory()          # the same images, NHWC
+        self.xn = jt.array(self.hxn)
+        self.relay = jt.get_op_info("cudnn_conv").get_constructor()
+        return ["conv", "conv-bn-relu", "conv-acdb"]
 
     def per_rank_work(self, name):
         return self.work()[name] // self.world
 
     def _op(self, name, x, w):
+        if name == "conv-acdb":
+            return self.relay(x, w, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb")
         y = self.nn.conv2d(x, w, None, 1, 1, 1)
         if name == "conv":
             return y
@@ -484,12 +492,13 @@ class C5ConvBN:
             return self.nn.relu(self.bn(y))
 
     def run(self, name):
-        return self._op(name, self.x, self.w).sync()
+        return self._op(name, self.xn if name == "conv-acdb" else self.x, self.w).sync()
 
     def run_e2e(self, name):
-        x = self.jt.array(self.hx.cuda(non_blocking=True))
+        x = self.jt.array((self.hxn if name == "conv-acdb" else self.hx).cuda(non_blocking=True))
         w = self.jt.array(self.hw.cuda(non_blocking=True))
-        self._op(name, x, w).fetch_into(self.out, stream=self.d2h_stream)
+        out = self.out.view(self.hxn.shape[0], self.H, self.W, self.CO) if name == "conv-acdb" else self.out
+        self._op(name, x, w).fetch_into(out, stream=self.d2h_stream)
 
     def e2e_bytes(self, names):
         return len(names) * (self.hx.numel() + self.hw.numel()) * 2, len(names) * self.out.numel() * 2
@@ -511,7 +520,7 @@ class C5ConvBN:
         var = (st[1] / cnt - mean * mean).clamp_min(0)
         wgt = (1.0 / torch.sqrt(var + 1e-5)).float()
         bias = (-mean * wgt.double()).float()
-        ok = True
+        ok = bool(torch.equal(self._op("conv-acdb", self.xn, self.w).torch()[:8], y[:8].permute(0, 2, 3, 1)))   # same sums, other store
         for n0 in range(0, y.shape[0], 16):
             ref = torch.relu(y[n0:n0 + 16].float() * wgt[None, :, None, None] + bias[None, :, None, None])
             d = (z[n0:n0 + 16].float() - ref).abs()
@@ -527,7 +536,7 @@ class C5ConvBN:
         done, t0 = 0, time.perf_counter()
         for nm in names:
             y = co.conv2d(x, w, 1, 1, 1)
-            if nm != "conv":
+            if nm == "conv-bn-relu":
                 co.bn_relu(y, np.ones(self.CO, np.float32), np.zeros(self.CO, np.float32))
             done += self.work()[nm] * imgs // self.N
         return done, time.perf_counter() - t0, f"{imgs} of {self.N} images per part, fp32 (OpenMP over image x channel)"
