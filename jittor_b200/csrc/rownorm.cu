@@ -50,6 +50,11 @@ template <typename T> __device__ __forceinline__ void st1(T* p, float v);
 template <> __device__ __forceinline__ void st1<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void st1<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
@@ -208,10 +213,17 @@ row_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restri
                 for (int k = 0; k < VPT; k++)
 #pragma unroll
                     for (int e = 0; e < N; e++) {
-                        const float a = v[r][k][e] - m[r];
-                        const float ex = __expf(a);         // ex2.approx(a * log2 e): relative error ~1e-6 for a in [-88, 0]
-                        sum[r] += (t + k * GROUP < nvec) ? ex : 0.f;
-                        v[r][k][e] = (OP == ROW_SOFTMAX) ? ex : a;
+                        if constexpr (OP == ROW_SOFTMAX) {
+                            // exp(x - m) as ex2(x * log2e - m * log2e): one FMA and one ex2.approx per element (relative error
+                            // ~1e-6 for arguments in [-88, 0]); the padding lanes hold -FLT_MAX and come out as exactly 0
+                            const float ex = ex2_approx(fmaf(v[r][k][e], 1.4426950408889634f, -m[r] * 1.4426950408889634f));
+                            sum[r] += ex;
+                            v[r][k][e] = ex;
+                        } else {
+                            const float a = v[r][k][e] - m[r];
+                            sum[r] += (t + k * GROUP < nvec) ? __expf(a) : 0.f;
+                            v[r][k][e] = a;
+                        }
                     }
             }
             group_reduce_n<GROUP, false, RPI>(sum, sm);
@@ -324,10 +336,15 @@ row_cluster_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __re
             for (int k = 0; k < VPT; k++)
 #pragma unroll
                 for (int e = 0; e < N; e++) {
-                    const float a = v[k][e] - m[0];
-                    const float ex = __expf(a);
-                    sum[0] += (crank * 256 + t + k * 256 * CL < nvec) ? ex : 0.f;
-                    v[k][e] = (OP == ROW_SOFTMAX) ? ex : a;
+                    if constexpr (OP == ROW_SOFTMAX) {
+                        const float ex = ex2_approx(fmaf(v[k][e], 1.4426950408889634f, -m[0] * 1.4426950408889634f));
+                        sum[0] += ex;
+                        v[k][e] = ex;
+                    } else {
+                        const float a = v[k][e] - m[0];
+                        sum[0] += (crank * 256 + t + k * 256 * CL < nvec) ? __expf(a) : 0.f;
+                        v[k][e] = a;
+                    }
                 }
             cluster_reduce_n<CL, false, 1>(sum, sm, xch, slot);
             const float ls = logf(sum[0]), inv = 1.0f / sum[0];
