@@ -94,7 +94,7 @@ class C1ConvF32:
     N, C, H, W, CO = 4, 32, 32, 32, 64
     description = ("config 0: reindex-lowered conv2d fp32 [4,32,32,32] * [64,32,3,3] s1 p1 "
                    "(reindex -> broadcast -> multiply -> sum over [Cin,Kh,Kw], recognised and run as one CUDA-core implicit GEMM)")
-    kernel_of = {"conv-f32": "gemm_simt_kernel<float, ConvLoader>"}
+    kernel_of = {"conv-f32": "gemm_simt_deep_kernel<float, ConvLoader, 32, 32>"}
     launches = {"conv-f32": 1}
     flush_l2 = True
     FLOP = 2 * 4 * 64 * 32 * 32 * 32 * 9
