@@ -427,9 +427,53 @@ def _match_conv_wgrad(v):
     return Plan([x, dy], lambda: run_conv2d_backward_w(x, dy, geo, [Co, Ci, KH, KW], v.dtype))
 
 
+def _swap01(t):
+    """[a, b, c, d] -> [b, a, c, d] by the reindex kernel (a pure permutation: tiled through shared memory)."""
+    a, b, c, d = t.shape
+    out = _empty([b, a, c, d], C.DTYPE_NAMES[t.dtype])
+    idx = ["i1", "i0", "i2", "i3"]
+    C.check(C.lib.b200jt_reindex(C.desc(t), C.desc(out), C.strings(idx), 4, 0.0, C.strings([]), 0, None, 0, C.stream_ptr()),
+            "reindex (swap of the two leading axes)")
+    return out
+
+
+def _wgrad_as_conv(xd, dyd, geo, w_shape):
+    """The weight gradient on the tensor-core convolution: dw[o,c,kh,kw] = sum over (n,oh,ow) of dy[n,o,oh,ow] *
+    x[n,c,oh*s-p+kh*d, ...] IS a convolution of x with the batch and channel axes exchanged (images = in channels, channels =
+    batch) by dy with its two leading axes exchanged as the filter (out channels = o, in channels = n, an OH x OW window),
+    with the roles of stride and dilation exchanged; its [C, Co, KH, KW] result only needs its leading axes swapped back.
+    cuDNN has a dedicated kernel for this (cudnn_conv_backward_w_op.cc:292); here the forward kernel serves, at the price of
+    8x8 output patches of which KH x KW pixels are real. Returns None when the shapes miss the tensor-core path."""
+    sh, sw, ph, pw, dh, dw = geo
+    Co, Ci, KH, KW = w_shape
+    N, _, H, W = xd.shape
+    OH, OW = dyd.shape[2], dyd.shape[3]
+    if xd.dtype != torch.bfloat16 or max(sh, sw, dh, dw) > 4:
+        return None
+    # extents of the exchanged convolution must come out as the filter's
+    if (H + 2 * ph - sh * (OH - 1) - 1) // dh + 1 != KH or (W + 2 * pw - sw * (OW - 1) - 1) // dw + 1 != KW:
+        return None
+    if N % 8 or N < 64 or Co < 64 or Ci * KH * KW < 1024 or H < 8 or W < 8:
+        return None
+    xt, dyt = _swap01(xd), _swap01(dyd)                   # [C, N, H, W], [Co, N, OH, OW]
+    out = _empty([Ci, Co, KH, KW], "bfloat16")
+    args = (C.desc(xt), C.desc(dyt), C.desc(out), dh, dw, ph, pw, sh, sw, 1)
+    nbytes = C.lib.b200jt_conv2d_workspace(*args)
+    if nbytes == 0:
+        return None                                       # not a tensor-core shape after all
+    ws, wsp = _workspace(nbytes)
+    C.check(C.lib.b200jt_conv2d(*args, ctypes.c_void_p(0), wsp, nbytes, C.stream_ptr()), "conv2d (weight gradient form)")
+    return _swap01(out)
+
+
 def run_conv2d_backward_w(x, dy, geo, w_shape, out_dtype):
     xd = x._data.view(list(x.shape))
     dyd = _cast(dy._data.view(list(dy.shape)), x.dtype)
+    from .flags import flags
+    if getattr(flags, "use_tensorcore", 0) or getattr(flags, "b200_wgrad_tc", 1):
+        got = _wgrad_as_conv(xd, dyd, geo, w_shape)
+        if got is not None:
+            return _cast(got, out_dtype)
     out = _empty(w_shape, x.dtype)
     C.check(C.lib.b200jt_conv2d_backward_w(C.desc(xd), C.desc(dyd), C.desc(out), *geo, C.stream_ptr()),
             f"conv2d_backward_w x{list(x.shape)} dy{list(dy.shape)} geo{geo}")

@@ -11,7 +11,8 @@ class _Flags:
     _defaults = dict(use_cuda=1, amp_reg=0, amp_level=0, lazy_execution=1, enable_tuner=1, use_tensorcore=0,
                      try_use_32bit_index=1, compile_options={}, exclude_pass="", log_silent=0,
                      use_device_mpi=1,
-                     b200_fuse_chains=1)        # 0: run element-wise chains op by op (the fused result has the same bits)
+                     b200_fuse_chains=1,        # 0: run element-wise chains op by op (the fused result has the same bits)
+                     b200_wgrad_tc=1)           # 0: weight gradients always on the CUDA-core kernel (fp32 sums in ascending order)
 
     def __init__(self):
         object.__setattr__(self, "_v", dict(self._defaults))

@@ -284,3 +284,39 @@ def test_conv_layouts_outside_the_tensor_core_path_are_refused():
         conv(x, w, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb").sync()
     with pytest.raises(ValueError):
         conv(x, w, 1, 1, 1, 1, 1, 1, 1, "bacd", "oihw", "")
+
+
+# (x shape, w shape, stride, padding, dilation): the weight gradient as a convolution with batch and channels exchanged, run by
+# the tensor-core kernel (needs a batch that can serve as the channel axis: a multiple of 8, at least 64)
+WGRAD = [
+    ((64, 128, 12, 12), (64, 128, 3, 3), 1, 1, 1),
+    ((64, 128, 14, 14), (96, 128, 3, 3), 2, 1, 1),
+    ((72, 256, 9, 11), (64, 256, 1, 1), 1, 0, 1),
+    ((64, 128, 16, 16), (64, 128, 3, 3), 1, 2, 2),
+]
+
+
+@pytest.mark.parametrize("xs,wshape,stride,pad,dil", WGRAD)
+def test_weight_gradient_on_the_tensor_core_kernel(xs, wshape, stride, pad, dil):
+    """Checked against the CUDA-core weight-gradient kernel (itself pinned to the reference's conv_wgrad fixtures through the
+    oracle) and against a float32 torch convolution's gradient; the oracle's own 7-d formulation needs minutes at these sizes."""
+    import jittor_b200 as jt
+    from jittor_b200 import _capi as C, nn
+    rng = np.random.default_rng(sum(xs) + sum(wshape) + stride + dil)
+    x = bf16_round(rng.normal(size=xs))
+    w = bf16_round(rng.normal(size=wshape) * 0.05)
+    oh = (xs[2] + 2 * pad - dil * (wshape[2] - 1) - 1) // stride + 1
+    ow = (xs[3] + 2 * pad - dil * (wshape[3] - 1) - 1) // stride + 1
+    dy = bf16_round(rng.normal(size=(xs[0], wshape[0], oh, ow)) * 0.1)
+    xv, wv, dyv = (jt.array(torch.from_numpy(a).bfloat16()) for a in (x, w, dy))
+    loss = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
+    got = jt.grad(loss, wv).torch().float().cpu().numpy()
+    tw = torch.from_numpy(w).cuda().requires_grad_()
+    ty = torch.nn.functional.conv2d(torch.from_numpy(x).cuda(), tw, None, stride, pad, dil)
+    (ty * torch.from_numpy(dy).cuda()).sum().backward()
+    check(got, bf16_round(tw.grad.cpu().numpy()), False, rtol=2e-2)
+    with jt.flag_scope(b200_wgrad_tc=0):                       # the CUDA-core kernel agrees (fp32 sums, bf16 result)
+        loss2 = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
+        simt = jt.grad(loss2, wv).torch().float().cpu().numpy()
+    check(got, simt, False, rtol=2e-2)
+    assert C.lib.b200jt_device_status() == 0
