@@ -274,6 +274,19 @@ int b200jt_conv2d_transpose(const b200jt_tensor* x, const b200jt_tensor* w, cons
 int b200jt_conv2d_backward_w(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
                              int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, void* stream);
 
+/* The same weight gradient with a workspace: bfloat16 layers (in and out channels multiples of 8 and >= 64, strides <= 4,
+ * output at least 8 x 8 per image and 4096 pixels in all, 16-byte aligned x and dy) run on the tensor cores -- x and dy
+ * are copied to channels-last form, each CTA accumulates one (tap, 128 in channels, 256 out channels) block over a range
+ * of pixels in fp32, and the ranges are added in a fixed order, so results repeat bit for bit. The _workspace query
+ * returns the bytes that path needs (0: it does not apply; the call then runs the kernel of b200jt_conv2d_backward_w and
+ * takes no workspace). Replaces the same relay, cudnnConvolutionBackwardFilter with its workspace,
+ * python/jittor/extern/cuda/cudnn/ops/cudnn_conv_backward_w_op.cc:292. */
+size_t b200jt_conv2d_backward_w_workspace(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                          int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w);
+int b200jt_conv2d_backward_w_tc(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 /* Per-channel sum(x) and sum(x*x) of x[N,C,H,W] into stats[2*C] (float32): the two reduce.mean of
  * BatchNorm.execute, python/jittor/nn.py:674-675, in one pass, unnormalised so that ranks can be
  * summed by an all-reduce (python/jittor/nn.py:676-678). */

@@ -216,3 +216,27 @@ extern "C" int b200jt_conv2d_backward_w(const b200jt_tensor* x, const b200jt_ten
     if (numel(dy) == 0) return fail(-1, "b200jt_conv2d_backward_w: empty dy");
     return conv2d_backward_w_simt(x->ptr, dy->ptr, dw->ptr, x->dtype, s, (cudaStream_t)stream);
 }
+
+extern "C" size_t b200jt_conv2d_backward_w_workspace(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                                     int sh, int sw, int ph, int pw, int dh, int dw_) {
+    ConvShape s;
+    if (conv_shape(x, dw, dy, sh, sw, ph, pw, dh, dw_, 1, &s)) return 0;
+    if (x->dtype == B200JT_BFLOAT16 && conv2d_wgrad_tc_supported(s, x->ptr, dy->ptr, dw->ptr)) return conv2d_wgrad_tc_workspace(s);
+    return 0;
+}
+
+extern "C" int b200jt_conv2d_backward_w_tc(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                           int sh, int sw, int ph, int pw, int dh, int dw_,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
+    ConvShape s;
+    int rc = conv_shape(x, dw, dy, sh, sw, ph, pw, dh, dw_, 1, &s);        // same shape relations as the forward conv
+    if (rc) return rc;
+    if (numel(dw) == 0) return 0;
+    if (numel(dy) == 0) return fail(-1, "b200jt_conv2d_backward_w_tc: empty dy");
+    if (x->dtype == B200JT_BFLOAT16 && conv2d_wgrad_tc_supported(s, x->ptr, dy->ptr, dw->ptr)) {
+        const size_t need = conv2d_wgrad_tc_workspace(s);
+        B200JT_CHECK_ARG(workspace_bytes >= need && workspace, "workspace too small: need " + std::to_string(need) + " bytes");
+        return conv2d_wgrad_tc(x->ptr, dy->ptr, dw->ptr, s, workspace, (cudaStream_t)stream);
+    }
+    return conv2d_backward_w_simt(x->ptr, dy->ptr, dw->ptr, x->dtype, s, (cudaStream_t)stream);
+}

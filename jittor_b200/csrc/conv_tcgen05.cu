@@ -442,6 +442,261 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
     return fused ? 1 : 0;      // 1: statistics were produced by the epilogue
 }
 
+// ---- weight gradient ---------------------------------------------------------------------------------------
+// dw[o,c,kh,kw] = sum over (n,oh,ow) of dy[n,o,oh,ow] * x[n,c,oh*stride-pad+kh*dil, ow*stride-pad+kw*dil]: the reduce.add
+// over (batch, rows, columns) of reindex(x) * broadcast(dy) that ConvTuner relays to cudnnConvolutionBackwardFilter
+// (python/jittor/extern/cuda/cudnn/ops/cudnn_conv_backward_w_op.cc:292). As a GEMM per filter tap:
+//   D[c, o] = sum over pixels of X_tap[pixel, c] * DY[pixel, o],     M = Cin (128 per CTA), N = Cout (256), K = N*OH*OW.
+// x and dy are first copied to NHWC, so a 4-D TMA box of 8 x 8 output pixels x 64 channels lands as 64 rows of 128 B with
+// the channel axis contiguous: both operands are MN-major (their own axis contiguous, K = pixel strided), and the same box
+// geometry as the forward kernel carries the tap's shift and the stride in its coordinates. One CTA owns one
+// (tap, 128 input channels, 256 output channels) accumulator in TMEM and walks a contiguous range of pixel patches; the
+// K axis is split over `splits` CTAs per accumulator to fill the GPU, each writing fp32 partial sums that a second kernel
+// adds in split order (deterministic) and stores as bf16 in OIHW order.
+namespace tcwgrad {
+
+using namespace tc;
+
+constexpr int BM = 128, PIX = 64, PATCH = 8, STAGES = 4, THREADS = 192;
+constexpr int CHUNK_BYTES = PIX * 64 * 2;                    // one box: 64 pixels x 64 channels of bf16
+constexpr int MAX_STAGE_BYTES = (BM / 64 + 256 / 64) * CHUNK_BYTES;
+constexpr int SMEM_BYTES = STAGES * MAX_STAGE_BYTES + 1024 + 256;
+
+struct WgradArgs {
+    int N, C, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+    int tiles_h, tiles_w;            // patches per image
+    int64_t patches;                 // N * tiles_h * tiles_w: the K axis in units of 64 pixels
+    int tiles_m, tiles_n, splits;
+};
+
+template <int BN_T>
+__global__ void __launch_bounds__(THREADS, 1)
+wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy,
+                  float* __restrict__ part, const __grid_constant__ WgradArgs A) {
+    constexpr int STAGE_BYTES = (BM / 64 + BN_T / 64) * CHUNK_BYTES;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * MAX_STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* acc_full = bars + 2 * STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int taps = A.KH * A.KW;
+    const int base = taps * A.tiles_m * A.tiles_n;
+    const int split = blockIdx.x / base;
+    int tile = blockIdx.x - split * base;
+    const int tap = tile % taps; tile /= taps;
+    const int tn = tile % A.tiles_n, tm = tile / A.tiles_n;
+    const int64_t p0 = A.patches * split / A.splits, p1 = A.patches * (split + 1) / A.splits;
+    const int k_blocks = (int)(p1 - p0);                     // >= 1: the host keeps splits <= patches
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(BN_T) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int kh = tap / A.KW, kw = tap - kh * A.KW;
+            const int dy = kh * A.dh - A.ph, dx = kw * A.dw - A.pw;
+            const int per_img = A.tiles_h * A.tiles_w;
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; kb++) {
+                const int64_t q = p0 + kb;
+                const int n = (int)(q / per_img);
+                const int r = (int)(q - (int64_t)n * per_img);
+                const int oh0 = (r / A.tiles_w) * PATCH, ow0 = (r % A.tiles_w) * PATCH;
+                if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 21))) break;
+                unsigned char* sa = smem + stage * MAX_STAGE_BYTES;
+                mbar_expect_tx(full + stage, STAGE_BYTES);
+                // pixels past the edge of x (padding, ragged patches) and channels past C / Co are zero-filled by TMA
+#pragma unroll
+                for (int j = 0; j < BM / 64; j++)
+                    tma_load_4d(sa + j * CHUNK_BYTES, &map_x, full + stage, tm * BM + j * 64, ow0 * A.sw + dx, oh0 * A.sh + dy, n);
+#pragma unroll
+                for (int j = 0; j < BN_T / 64; j++)
+                    tma_load_4d(sa + (BM / 64 + j) * CHUNK_BYTES, &map_dy, full + stage, tn * BN_T + j * 64, ow0, oh0, n);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) {
+                for (int s = 0; s < STAGES; s++)
+                    for (uint32_t i = 0; i < 4096 && !mbar_try(full + s, 0) && !mbar_try(full + s, 1); i++) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN_T, true) | (1u << 15);      // A and B both MN-major
+            constexpr int KSTEP = (UMMA_K * 128) / 16;                                // 16 pixel rows of 128 B, in 16-byte units
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; kb++) {
+                if (!(ok = mbar_wait(full + stage, phase, abort_flag, 22))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem_u32(smem + stage * MAX_STAGE_BYTES);
+                const uint64_t da = make_smem_desc_mn(sa, CHUNK_BYTES, 1024);
+                const uint64_t db = make_smem_desc_mn(sa + (BM / 64) * CHUNK_BYTES, CHUNK_BYTES, 1024);
+#pragma unroll
+                for (int k = 0; k < PIX / UMMA_K; k++) umma_f16(tmem_base, da + KSTEP * k, db + KSTEP * k, idesc, (kb | k) != 0);
+                umma_commit(empty + stage);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        const int quad = warp & 3;
+        bool ok = mbar_wait(acc_full, 0, abort_flag, 23);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int c = tm * BM + quad * 32 + lane;                        // TMEM lane = input channel
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            float* prow = part + (((int64_t)split * taps + tap) * A.C + c) * A.Co;
+            const bool vec = (A.Co & 3) == 0;
+#pragma unroll 1
+            for (int ch = 0; ch < BN_T / 32; ch++) {
+                uint32_t v[32];
+                tmem_ld32(taddr + ch * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int o0 = tn * BN_T + ch * 32;
+                if (c < A.C && o0 < A.Co) {
+                    if (vec && o0 + 32 <= A.Co) {
+#pragma unroll
+                        for (int q = 0; q < 8; q++)
+                            *reinterpret_cast<uint4*>(prow + o0 + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; e++) if (o0 + e < A.Co) prow[o0 + e] = __uint_as_float(v[e]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(BN_T) : "memory");
+    }
+}
+
+// dw[o][c][tap] = sum over splits (ascending) of part[split][tap][c][o], rounded to bf16 once.
+__global__ void __launch_bounds__(256)
+wgrad_fold_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dw, int splits, int taps, int C, int Co) {
+    const int64_t n = (int64_t)taps * C * Co;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int o = (int)(i % Co); const int64_t t = i / Co;
+        const int c = (int)(t % C); const int tap = (int)(t / C);
+        float acc = 0.f;
+        for (int s = 0; s < splits; s++) acc += part[(int64_t)s * n + i];
+        dw[((int64_t)o * C + c) * taps + tap] = __float2bfloat16(acc);
+    }
+}
+
+// NHWC tensor [N][H][W][C] as a 4-D map whose box is 64 channels x (8 * sw) x (8 * sh) x 1 with traversal strides
+// (1, sw, sh, 1): 64 pixels x 128 B in shared memory.
+static bool make_map_nhwc(CUtensorMap* map, const void* base, int N, int H, int W, int C, int sh, int sw) {
+    auto fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t strides[3] = {(cuuint64_t)C * 2, (cuuint64_t)W * C * 2, (cuuint64_t)H * W * C * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)(PATCH * sw), (cuuint32_t)(PATCH * sh), 1};
+    cuuint32_t estr[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Plan { int bn, tiles_m, tiles_n, splits; int64_t patches; size_t xb, dyb, pb; };
+
+static Plan plan_for(const ConvShape& s) {
+    Plan p;
+    p.bn = s.Co <= 128 ? 128 : 256;
+    p.tiles_m = (s.C + BM - 1) / BM;
+    p.tiles_n = (s.Co + p.bn - 1) / p.bn;
+    p.patches = (int64_t)s.N * ((s.OH + PATCH - 1) / PATCH) * ((s.OW + PATCH - 1) / PATCH);
+    const int64_t base = (int64_t)s.KH * s.KW * p.tiles_m * p.tiles_n;
+    // fill the GPU once when the accumulators alone do not; every split keeps at least 16 patches (1024 pixels) of K
+    int64_t splits = base >= kNumSMs ? 1 : kNumSMs / base;
+    splits = std::max<int64_t>(1, std::min<int64_t>(splits, p.patches / 16));
+    p.splits = (int)splits;
+    p.xb = ((size_t)s.N * s.H * s.W * s.C * 2 + 1023) & ~(size_t)1023;
+    p.dyb = ((size_t)s.N * s.OH * s.OW * s.Co * 2 + 1023) & ~(size_t)1023;
+    p.pb = ((size_t)p.splits * s.KH * s.KW * s.C * s.Co * 4 + 1023) & ~(size_t)1023;
+    return p;
+}
+
+}  // namespace tcwgrad
+
+bool conv2d_wgrad_tc_supported(const ConvShape& s, const void* x, const void* dy, const void* dw) {
+    const int64_t taps = (int64_t)s.KH * s.KW;
+    return s.groups == 1 && s.sh >= 1 && s.sh <= 4 && s.sw >= 1 && s.sw <= 4 && s.C % 8 == 0 && s.Co % 8 == 0 && s.C >= 64 &&
+           s.Co >= 64 && s.H >= 8 * s.sh && s.W >= 8 * s.sw && s.OH >= 8 && s.OW >= 8 && (int64_t)s.N * s.OH * s.OW >= 4096 &&
+           taps * ((s.C + 127) / 128) * ((s.Co + 255) / 256) <= (1 << 20) &&
+           ((uintptr_t)x % 16 == 0) && ((uintptr_t)dy % 16 == 0) && ((uintptr_t)dw % 2 == 0) && tc::encode_fn() != nullptr;
+}
+
+size_t conv2d_wgrad_tc_workspace(const ConvShape& s) {
+    const tcwgrad::Plan p = tcwgrad::plan_for(s);
+    return p.xb + p.dyb + p.pb + 1024;
+}
+
+int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s, void* workspace, cudaStream_t st) {
+    using namespace tcwgrad;
+    const Plan p = plan_for(s);
+    unsigned char* ws = (unsigned char*)(((uintptr_t)workspace + 1023) & ~(uintptr_t)1023);
+    __nv_bfloat16* xt = (__nv_bfloat16*)ws;
+    __nv_bfloat16* dyt = (__nv_bfloat16*)(ws + p.xb);
+    float* part = (float*)(ws + p.xb + p.dyb);
+    {   // x[N][C][HW] -> [N][HW][C] and dy[N][Co][OH*OW] -> [N][OH*OW][Co]
+        const int HW = s.H * s.W, OHW = s.OH * s.OW;
+        dim3 gx((unsigned)((HW + 63) / 64), (unsigned)((s.C + 63) / 64), (unsigned)s.N);
+        tcconv::transpose_bf16_batched_kernel<<<gx, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW, 0, nullptr, nullptr, 0, 0, 0, nullptr, 0, 0);
+        B200JT_LAUNCH_CHECK();
+        dim3 gy((unsigned)((OHW + 63) / 64), (unsigned)((s.Co + 63) / 64), (unsigned)s.N);
+        tcconv::transpose_bf16_batched_kernel<<<gy, 256, 0, st>>>((const __nv_bfloat16*)dy, dyt, s.Co, OHW, 0, nullptr, nullptr, 0, 0, 0, nullptr, 0, 0);
+        B200JT_LAUNCH_CHECK();
+    }
+    WgradArgs A;
+    A.N = s.N; A.C = s.C; A.H = s.H; A.W = s.W; A.Co = s.Co; A.KH = s.KH; A.KW = s.KW; A.OH = s.OH; A.OW = s.OW;
+    A.sh = s.sh; A.sw = s.sw; A.ph = s.ph; A.pw = s.pw; A.dh = s.dh; A.dw = s.dw;
+    A.tiles_h = (s.OH + PATCH - 1) / PATCH; A.tiles_w = (s.OW + PATCH - 1) / PATCH;
+    A.patches = p.patches; A.tiles_m = p.tiles_m; A.tiles_n = p.tiles_n; A.splits = p.splits;
+    CUtensorMap mx, mdy;
+    if (!make_map_nhwc(&mx, xt, s.N, s.H, s.W, s.C, s.sh, s.sw) || !make_map_nhwc(&mdy, dyt, s.N, s.OH, s.OW, s.Co, 1, 1))
+        return fail(-4, "conv2d_backward_w: cuTensorMapEncodeTiled failed");
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute((const void*)wgrad_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute((const void*)wgrad_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
+    B200JT_CUDA(attr_err);
+    const int taps = s.KH * s.KW;
+    const unsigned grid = (unsigned)((int64_t)taps * p.tiles_m * p.tiles_n * p.splits);
+    if (p.bn == 256) wgrad_bf16_kernel<256><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mdy, part, A);
+    else wgrad_bf16_kernel<128><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mdy, part, A);
+    B200JT_LAUNCH_CHECK();
+    const int64_t n = (int64_t)taps * s.C * s.Co;
+    wgrad_fold_kernel<<<grid_for(n, 256), 256, 0, st>>>(part, (__nv_bfloat16*)dw, p.splits, taps, s.C, s.Co);
+    B200JT_LAUNCH_CHECK();
+    return 0;
+}
+
 int tcconv_status_fetch_and_clear() { return tc::status_fetch_and_clear(); }
 
 }  // namespace b200jt

@@ -31,6 +31,10 @@ size_t conv2d_tc_workspace(const ConvShape& s);
 // returns < 0 / > 1 on error, 0 on success, 1 on success with `stats` filled by the epilogue
 int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvShape& s, void* workspace, cudaStream_t st,
               const ConvLayout& lay = ConvLayout());
+// weight gradient on tcgen05 (bf16, groups == 1): K = N*OH*OW pixels, split over CTAs, fp32 partial sums folded in a fixed order
+bool conv2d_wgrad_tc_supported(const ConvShape& s, const void* x, const void* dy, const void* dw);
+size_t conv2d_wgrad_tc_workspace(const ConvShape& s);
+int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s, void* workspace, cudaStream_t st);
 int tcconv_status_fetch_and_clear();
 int peer_status_fetch_and_clear();          // peer_allreduce.cu
 

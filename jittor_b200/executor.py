@@ -467,15 +467,26 @@ def _wgrad_as_conv(xd, dyd, geo, w_shape):
 
 
 def run_conv2d_backward_w(x, dy, geo, w_shape, out_dtype):
+    """Weight gradient. flags.b200_wgrad_tc: 1 (default) the tensor-core weight-gradient kernel where its shape rules hold,
+    then the exchanged-axes convolution, then the CUDA-core kernel; 2 skips the dedicated kernel; 0 CUDA cores only."""
     xd = x._data.view(list(x.shape))
     dyd = _cast(dy._data.view(list(dy.shape)), x.dtype)
     from .flags import flags
-    if getattr(flags, "use_tensorcore", 0) or getattr(flags, "b200_wgrad_tc", 1):
+    mode = int(getattr(flags, "b200_wgrad_tc", 1))
+    out = _empty(w_shape, x.dtype)
+    args = (C.desc(xd), C.desc(dyd), C.desc(out), *geo)
+    if mode == 1:
+        nbytes = C.lib.b200jt_conv2d_backward_w_workspace(*args)
+        if nbytes:
+            ws, wsp = _workspace(nbytes)
+            C.check(C.lib.b200jt_conv2d_backward_w_tc(*args, wsp, nbytes, C.stream_ptr()),
+                    f"conv2d_backward_w (tensor cores) x{list(x.shape)} dy{list(dy.shape)} geo{geo}")
+            return _cast(out, out_dtype)
+    if mode:
         got = _wgrad_as_conv(xd, dyd, geo, w_shape)
         if got is not None:
             return _cast(got, out_dtype)
-    out = _empty(w_shape, x.dtype)
-    C.check(C.lib.b200jt_conv2d_backward_w(C.desc(xd), C.desc(dyd), C.desc(out), *geo, C.stream_ptr()),
+    C.check(C.lib.b200jt_conv2d_backward_w(*args, C.stream_ptr()),
             f"conv2d_backward_w x{list(x.shape)} dy{list(dy.shape)} geo{geo}")
     return _cast(out, out_dtype)
 

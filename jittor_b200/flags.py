@@ -12,7 +12,8 @@ class _Flags:
                      try_use_32bit_index=1, compile_options={}, exclude_pass="", log_silent=0,
                      use_device_mpi=1,
                      b200_fuse_chains=1,        # 0: run element-wise chains op by op (the fused result has the same bits)
-                     b200_wgrad_tc=1)           # 0: weight gradients always on the CUDA-core kernel (fp32 sums in ascending order)
+                     b200_wgrad_tc=1)           # weight gradients: 1 tensor-core kernel where it applies, 2 only the exchanged-axes
+                                                # convolution, 0 always the CUDA-core kernel (fp32 sums in ascending order)
 
     def __init__(self):
         object.__setattr__(self, "_v", dict(self._defaults))

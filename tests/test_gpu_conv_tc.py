@@ -286,18 +286,24 @@ def test_conv_layouts_outside_the_tensor_core_path_are_refused():
         conv(x, w, 1, 1, 1, 1, 1, 1, 1, "bacd", "oihw", "")
 
 
-# (x shape, w shape, stride, padding, dilation): the weight gradient as a convolution with batch and channels exchanged, run by
-# the tensor-core kernel (needs a batch that can serve as the channel axis: a multiple of 8, at least 64)
+# (x shape, w shape, stride, padding, dilation, path): weight gradients of bf16 layers. "tc": the tensor-core weight-gradient
+# kernel (K = pixels; outputs of at least 8 x 8 per image); "exchanged": the forward kernel on x and dy with batch and channel
+# axes exchanged (needs a batch that can serve as the channel axis: a multiple of 8, at least 64).
 WGRAD = [
-    ((64, 128, 12, 12), (64, 128, 3, 3), 1, 1, 1),
-    ((64, 128, 14, 14), (96, 128, 3, 3), 2, 1, 1),
-    ((72, 256, 9, 11), (64, 256, 1, 1), 1, 0, 1),
-    ((64, 128, 16, 16), (64, 128, 3, 3), 1, 2, 2),
+    ((64, 128, 12, 12), (64, 128, 3, 3), 1, 1, 1, "tc"),            # one 128 x 128 accumulator per tap, 16 pixel ranges
+    ((72, 256, 9, 11), (64, 256, 1, 1), 1, 0, 1, "tc"),             # 1 x 1 filter, ragged patches
+    ((64, 128, 16, 16), (64, 128, 3, 3), 1, 2, 2, "tc"),            # dilation 2
+    ((20, 192, 30, 34), (320, 192, 3, 3), 2, 1, 1, "tc"),           # stride 2; ragged channel tiles (128 + 64, 256 + 64)
+    ((8, 256, 28, 28), (256, 256, 3, 3), 1, 1, 1, "tc"),            # the 256-wide tile, 18 accumulators x 8 ranges
+    ((40, 72, 28, 32), (136, 72, 5, 5), 3, 2, 1, "tc"),             # stride 3, 5 x 5, channel counts that are only multiples of 8
+    ((64, 128, 12, 12), (64, 128, 3, 3), 1, 1, 1, "exchanged"),
+    ((64, 128, 14, 14), (96, 128, 3, 3), 2, 1, 1, "exchanged"),     # 7 x 7 output: below the dedicated kernel's patch size
+    ((64, 128, 16, 16), (64, 128, 3, 3), 1, 2, 2, "exchanged"),
 ]
 
 
-@pytest.mark.parametrize("xs,wshape,stride,pad,dil", WGRAD)
-def test_weight_gradient_on_the_tensor_core_kernel(xs, wshape, stride, pad, dil):
+@pytest.mark.parametrize("xs,wshape,stride,pad,dil,path", WGRAD)
+def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path):
     """Checked against the CUDA-core weight-gradient kernel (itself pinned to the reference's conv_wgrad fixtures through the
     oracle) and against a float32 torch convolution's gradient; the oracle's own 7-d formulation needs minutes at these sizes."""
     import jittor_b200 as jt
@@ -309,8 +315,13 @@ def test_weight_gradient_on_the_tensor_core_kernel(xs, wshape, stride, pad, dil)
     ow = (xs[3] + 2 * pad - dil * (wshape[3] - 1) - 1) // stride + 1
     dy = bf16_round(rng.normal(size=(xs[0], wshape[0], oh, ow)) * 0.1)
     xv, wv, dyv = (jt.array(torch.from_numpy(a).bfloat16()) for a in (x, w, dy))
-    loss = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
-    got = jt.grad(loss, wv).torch().float().cpu().numpy()
+    geo = (stride, stride, pad, pad, dil, dil)
+    applies = C.lib.b200jt_conv2d_backward_w_workspace(C.desc(xv.torch()), C.desc(dyv.torch()), C.desc(wv.torch()), *geo)
+    if path == "tc":
+        assert applies > 0, "case does not reach the tensor-core weight-gradient kernel"
+    with jt.flag_scope(b200_wgrad_tc=1 if path == "tc" else 2):
+        loss = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
+        got = jt.grad(loss, wv).torch().float().cpu().numpy()
     tw = torch.from_numpy(w).cuda().requires_grad_()
     ty = torch.nn.functional.conv2d(torch.from_numpy(x).cuda(), tw, None, stride, pad, dil)
     (ty * torch.from_numpy(dy).cuda()).sum().backward()
@@ -319,4 +330,9 @@ def test_weight_gradient_on_the_tensor_core_kernel(xs, wshape, stride, pad, dil)
         loss2 = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
         simt = jt.grad(loss2, wv).torch().float().cpu().numpy()
     check(got, simt, False, rtol=2e-2)
+    if path == "tc":                                           # partial sums are folded in a fixed order: results repeat
+        with jt.flag_scope(b200_wgrad_tc=1):
+            loss3 = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
+            again = jt.grad(loss3, wv).torch().float().cpu().numpy()
+        assert np.array_equal(got, again)
     assert C.lib.b200jt_device_status() == 0
