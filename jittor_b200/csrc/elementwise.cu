@@ -217,6 +217,63 @@ broadcast_kernel(const T* __restrict__ x, T* __restrict__ z, const __grid_consta
     }
 }
 
+// Broadcast over ONE contiguous group of axes: z[o][m][i] = x[o][i] (a scalar: O = I = 1; a row vector stretched over rows:
+// O = 1; a per-row value stretched along the row: I = 1). 16-byte stores, no per-axis index arithmetic.
+//   INNER: I * sizeof(T) is a multiple of 16 -- both sides move as uint4, z4[(o*M + m)*I4 + i4] = x4[o*I4 + i4];
+//  !INNER: I == 1 and M * sizeof(T) is a multiple of 16 -- a 16-byte vector of z lies inside one o and repeats x[o].
+template <typename T, bool INNER>
+__global__ void __launch_bounds__(256)
+broadcast_group_kernel(const T* __restrict__ x, uint4* __restrict__ z4, int64_t nvec, int64_t M, int64_t I4) {
+    constexpr int PER = 16 / sizeof(T);
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+        if (INNER) {
+            const int64_t t = v / I4, i4 = v - t * I4;
+            z4[v] = __ldg(reinterpret_cast<const uint4*>(x) + (t / M) * I4 + i4);
+        } else {
+            const T val = __ldg(x + v / (M / PER));
+            __align__(16) T rep[PER];
+#pragma unroll
+            for (int e = 0; e < PER; e++) rep[e] = val;
+            z4[v] = *reinterpret_cast<const uint4*>(rep);
+        }
+    }
+}
+
+// Splits z's axes as outer x (one contiguous run of broadcast axes) x inner; false if the broadcast axes (extent > 1) are
+// not one run. Axes of extent 1 belong to whichever side they touch.
+static bool broadcast_group(const b200jt_tensor* z, uint32_t mask, int64_t* O, int64_t* M, int64_t* I) {
+    int first = -1, last = -1;
+    for (int d = 0; d < z->ndim; d++)
+        if ((mask >> d & 1) && z->shape[d] != 1) { if (first < 0) first = d; last = d; }
+    if (first < 0) return false;                               // nothing is stretched: a plain copy, left to the general kernel
+    *O = *M = *I = 1;
+    for (int d = 0; d < z->ndim; d++) {
+        if (d < first) *O *= z->shape[d];
+        else if (d > last) *I *= z->shape[d];
+        else if ((mask >> d & 1) || z->shape[d] == 1) *M *= z->shape[d];
+        else return false;                                     // a kept axis between two stretched ones
+    }
+    return true;
+}
+
+template <typename T>
+static bool launch_broadcast_group(const b200jt_tensor* x, const b200jt_tensor* z, uint32_t mask, cudaStream_t st) {
+    int64_t O, M, I;
+    if (!broadcast_group(z, mask, &O, &M, &I)) return false;
+    if (((uintptr_t)z->ptr & 15) != 0) return false;
+    constexpr int PER = 16 / sizeof(T);
+    const int64_t nvec = O * M * I / PER;
+    if (I % PER == 0 && ((uintptr_t)x->ptr & 15) == 0) {
+        broadcast_group_kernel<T, true><<<grid_for(nvec, 256), 256, 0, st>>>((const T*)x->ptr, (uint4*)z->ptr, nvec, M, I / PER);
+        return true;
+    }
+    if (I == 1 && M % PER == 0) {
+        broadcast_group_kernel<T, false><<<grid_for(nvec, 256), 256, 0, st>>>((const T*)x->ptr, (uint4*)z->ptr, nvec, M, 1);
+        return true;
+    }
+    return false;
+}
+
 static bool fill_strides(const b200jt_tensor* t, const b200jt_tensor* z, int64_t* stride, bool* same) {
     if (t->ndim != z->ndim) return false;
     int64_t st = 1;
@@ -433,6 +490,14 @@ extern "C" int b200jt_broadcast_to(const b200jt_tensor* x, const b200jt_tensor* 
     const int64_t n = numel(z);
     if (n == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
+    bool done = false;
+    switch (dtype_size(x->dtype)) {
+        case 1: done = launch_broadcast_group<uint8_t>(x, z, bcast_mask, st); break;
+        case 2: done = launch_broadcast_group<uint16_t>(x, z, bcast_mask, st); break;
+        case 4: done = launch_broadcast_group<uint32_t>(x, z, bcast_mask, st); break;
+        default: done = launch_broadcast_group<uint64_t>(x, z, bcast_mask, st);
+    }
+    if (done) { B200JT_LAUNCH_CHECK(); return 0; }
     const unsigned grid = grid_for(n, 256);
     switch (dtype_size(x->dtype)) {
         case 1: broadcast_kernel<uint8_t><<<grid, 256, 0, st>>>((const uint8_t*)x->ptr, (uint8_t*)z->ptr, A, n); break;

@@ -171,7 +171,9 @@ class _Builder:
         """Shape `shape` (rank <= len(axes), right-aligned against a node whose axes sit at `axes`) in full rank."""
         shape = list(shape)
         if len(shape) > len(axes):
-            raise _Unfusable
+            if any(s != 1 for s in shape[:len(shape) - len(axes)]):
+                raise _Unfusable
+            shape = shape[len(shape) - len(axes):]
         view = [1] * self.d
         for s, a in zip(shape, axes[len(axes) - len(shape):]):
             view[a] = s
@@ -218,8 +220,10 @@ class _Builder:
         return False
 
     def _axes_of(self, v, axes):
-        if v.ndim > len(axes):
-            raise _Unfusable
+        if v.ndim > len(axes):                  # leading axes of extent 1 (a [1] scalar stretched over every axis) carry nothing
+            if any(s != 1 for s in v.shape[:v.ndim - len(axes)]):
+                raise _Unfusable
+            return axes
         return axes[len(axes) - v.ndim:]
 
     def _through_broadcasts(self, v, axes):

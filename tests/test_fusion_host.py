@@ -3,6 +3,7 @@ and what stays a leaf. Mirrors the grouping cases of python/jittor/test/test_fus
 one fused op) and python/jittor/test/test_stop_fuse.py."""
 import jittor_b200 as jt
 from jittor_b200 import fusion, nn, executor
+from jittor_b200 import var as var_mod
 
 OPS = {0: "OPND", 1: "LOAD", 2: "UN", 3: "BIN", 4: "SEL", 5: "TST", 8: "RRED", 9: "RMAP", 10: "STORE", 11: "STROW"}
 
@@ -256,3 +257,20 @@ def test_layernorm_backward_is_one_program():
     assert np.allclose(got, want, rtol=1e-3, atol=1e-4)
     src, ok, log = fusion.program_source(words, inputs, full, k, [6, 40], "float32")
     assert ok, log
+
+
+def test_scalar_stretched_over_every_axis_is_a_broadcast_input():
+    """The gradient of `.sum()` is a [1] value broadcast over all axes of its operand; multiplied by another tensor it must
+    be one map kernel (the scalar as a broadcast input), not a materialised tensor of ones."""
+    x, dy = ph([8, 16, 12, 12], "bfloat16"), ph([8, 16, 12, 12], "bfloat16")
+    seed = ph([1], "float32")
+    full = jt.Var([8, 16, 12, 12], "float32", var_mod.Op("broadcast_to", [seed], bcast_mask=15, keepdims_mask=0))   # the reduce rule's form
+    z = full.bfloat16() * dy
+    words, inputs, shape, k, n = fusion.build_program(z)
+    assert ops(words) == ["LOAD", "UN", "BIN", "STORE"] and k == 0 and shape == [8, 16, 12, 12]
+    assert sorted(view for _, view in inputs) == [[1, 1, 1, 1], [8, 16, 12, 12]]
+    src, ok, log = fusion.program_source(words, inputs, shape, k, shape, "bfloat16")
+    assert ok, log
+    # as jt.grad builds it
+    g = jt.grad((x * dy).sum(), x)
+    assert fusion.build_program(g) is not None
