@@ -450,16 +450,18 @@ class C5ConvBN:
     description = ("config 4: reindex conv2d bf16 [256,256,56,56] * [256,256,3,3] s1 p1, then global BatchNorm statistics "
                    "(one all-reduce of 2*C fp32) and fused normalise+ReLU; batch split over the ranks; third part: the same "
                    "convolution through the relay with acdb (NHWC) activations in and out, the layout ConvTuner derives for "
-                   "tensor-core kernels, which needs no layout pass")
+                   "tensor-core kernels, which needs no layout pass; fourth part: the weight gradient of the same layer as "
+                   "jt.grad builds it (reduce.add over batch and pixels of reindex(x) * broadcast(dy)), each rank over its own "
+                   "images")
     kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)",
-                 "conv-acdb": "conv_bf16_kernel (tcgen05)"}
-    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2}
+                 "conv-acdb": "conv_bf16_kernel (tcgen05)", "conv-wgrad": "wgrad_bf16_kernel (tcgen05)"}
+    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2, "conv-wgrad": 8}
     all_reduced = ("conv-bn-relu",)
-    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6, "conv-acdb": 776.5e6}
+    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6, "conv-acdb": 776.5e6, "conv-wgrad": None}
 
     def work(self):
         f = 2 * self.N * self.H * self.W * self.CO * self.C * 9
-        return {"conv": f, "conv-bn-relu": f, "conv-acdb": f}
+        return {"conv": f, "conv-bn-relu": f, "conv-acdb": f, "conv-wgrad": f}
 
     def setup(self, rank, world, jt, torch, multi):
         from jittor_b200 import nn
@@ -477,14 +479,20 @@ class C5ConvBN:
         self.hxn = self.hx.permute(0, 2, 3, 1).contiguous().pin_memory()          # the same images, NHWC
         self.xn = jt.array(self.hxn)
         self.relay = jt.get_op_info("cudnn_conv").get_constructor()
-        return ["conv", "conv-bn-relu", "conv-acdb"]
+        gd = torch.Generator().manual_seed(40 + rank)
+        self.hdy = (torch.randn(n, self.CO, self.H, self.W, generator=gd) * 0.1).bfloat16().pin_memory()
+        self.dy = jt.array(self.hdy)
+        self.hdw = torch.empty(self.CO, self.C, 3, 3, dtype=torch.bfloat16).pin_memory()
+        return ["conv", "conv-bn-relu", "conv-acdb", "conv-wgrad"]
 
     def per_rank_work(self, name):
         return self.work()[name] // self.world
 
-    def _op(self, name, x, w):
+    def _op(self, name, x, w, dy=None):
         if name == "conv-acdb":
             return self.relay(x, w, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb")
+        if name == "conv-wgrad":
+            return self.jt.grad((self.nn.conv2d(x, w, None, 1, 1, 1) * (self.dy if dy is None else dy)).sum(), w)
         y = self.nn.conv2d(x, w, None, 1, 1, 1)
         if name == "conv":
             return y
@@ -497,11 +505,18 @@ class C5ConvBN:
     def run_e2e(self, name):
         x = self.jt.array((self.hxn if name == "conv-acdb" else self.hx).cuda(non_blocking=True))
         w = self.jt.array(self.hw.cuda(non_blocking=True))
+        if name == "conv-wgrad":
+            dy = self.jt.array(self.hdy.cuda(non_blocking=True))
+            self._op(name, x, w, dy).fetch_into(self.hdw, stream=self.d2h_stream)
+            return
         out = self.out.view(self.hxn.shape[0], self.H, self.W, self.CO) if name == "conv-acdb" else self.out
         self._op(name, x, w).fetch_into(out, stream=self.d2h_stream)
 
     def e2e_bytes(self, names):
-        return len(names) * (self.hx.numel() + self.hw.numel()) * 2, len(names) * self.out.numel() * 2
+        fwd = sum(1 for n in names if n != "conv-wgrad")
+        bwd = len(names) - fwd
+        return (len(names) * (self.hx.numel() + self.hw.numel()) * 2 + bwd * self.hdy.numel() * 2,
+                fwd * self.out.numel() * 2 + bwd * self.hdw.numel() * 2)
 
     def verify(self, env):
         """Untimed correctness witness: relu(bn(conv)) on this rank's images against the same chain computed by torch from
@@ -525,6 +540,11 @@ class C5ConvBN:
             ref = torch.relu(y[n0:n0 + 16].float() * wgt[None, :, None, None] + bias[None, :, None, None])
             d = (z[n0:n0 + 16].float() - ref).abs()
             ok = ok and bool((d <= 2e-2 * ref.abs() + 2e-2 * ref.abs().max()).all())
+        del y, z
+        # this rank's weight gradient against torch's float32 one over the same images
+        dw = self._op("conv-wgrad", self.x, self.w).torch().float()
+        ref = torch.nn.grad.conv2d_weight(self.x.torch().float(), list(self.hw.shape), self.dy.torch().float(), stride=1, padding=1)
+        ok = ok and bool(((dw - ref).abs() <= 2e-2 * ref.abs() + 2e-2 * ref.abs().max()).all())
         return ok
 
     def cpu(self, names):
@@ -535,11 +555,13 @@ class C5ConvBN:
         w = (rng.normal(size=(self.CO, self.C, 3, 3)) * (2 / (9 * self.C)) ** 0.5).astype(np.float32)
         done, t0 = 0, time.perf_counter()
         for nm in names:
+            if nm == "conv-wgrad":
+                continue                                # the C port has no weight gradient: the forward parts are the sample
             y = co.conv2d(x, w, 1, 1, 1)
             if nm == "conv-bn-relu":
                 co.bn_relu(y, np.ones(self.CO, np.float32), np.zeros(self.CO, np.float32))
             done += self.work()[nm] * imgs // self.N
-        return done, time.perf_counter() - t0, f"{imgs} of {self.N} images per part, fp32 (OpenMP over image x channel)"
+        return max(done, 1), time.perf_counter() - t0, f"{imgs} of {self.N} images per forward part, fp32 (OpenMP over image x channel)"
 
 
 class MetaOps:
@@ -547,13 +569,15 @@ class MetaOps:
     key, metric, unit, bound, dtype, scaling = "meta", "meta-op GB/s", "GB/s", "hbm", "f32", "weak"
     ROWS, COLS = 32768, 4096
     description = ("plain meta-operators on [32768,4096] fp32: reindex (pad by 2 columns; transpose), reduce (row sum, "
-                   "column sum), broadcast fused into a binary add, and the conv-window reindex of config 0 "
+                   "column sum), broadcast fused into a binary add and on its own (a row stretched over all rows), and the conv-window "
+                   "reindex of config 0 "
                    "([4,32,32,32] -> [4,64,32,32,32,3,3])")
     kernel_of = {"reindex-pad": "reindex_jit_kernel", "reindex-transpose": "reindex_permute_vec4_kernel",
                  "reindex-conv-window": "reindex_jit_kernel", "reduce-row-sum": "reduce_row_kernel",
-                 "reduce-col-sum": "reduce_col_kernel", "broadcast-add": "binary_kernel"}
+                 "reduce-col-sum": "reduce_col_kernel", "broadcast-add": "binary_kernel",
+                 "broadcast-rows": "broadcast_group_kernel"}
     launches = {"reindex-pad": 1, "reindex-transpose": 1, "reindex-conv-window": 1, "reduce-row-sum": 1,
-                "reduce-col-sum": 2, "broadcast-add": 1}
+                "reduce-col-sum": 2, "broadcast-add": 1, "broadcast-rows": 1}
     WIN = [4, 64, 32, 32, 32, 3, 3]
 
     def work(self):
@@ -561,7 +585,8 @@ class MetaOps:
         win = int(np.prod(self.WIN))
         return {"reindex-pad": 4 * n + 4 * self.ROWS * (self.COLS + 4), "reindex-transpose": 8 * n,
                 "reindex-conv-window": 4 * win + 4 * 4 * 32 * 32 * 32, "reduce-row-sum": 4 * n + 4 * self.ROWS,
-                "reduce-col-sum": 4 * n + 4 * self.COLS, "broadcast-add": 8 * n + 4 * self.COLS}
+                "reduce-col-sum": 4 * n + 4 * self.COLS, "broadcast-add": 8 * n + 4 * self.COLS,
+                "broadcast-rows": 4 * n + 4 * self.COLS}
 
     def setup(self, rank, world, jt, torch, multi):
         self.jt, self.torch = jt, torch
@@ -584,6 +609,8 @@ class MetaOps:
             return x.sum(1)
         if name == "reduce-col-sum":
             return x.sum(0)
+        if name == "broadcast-rows":
+            return self.b.broadcast([self.ROWS, self.COLS])
         return x + self.b
 
     def run(self, name):
@@ -618,6 +645,8 @@ class MetaOps:
         ok = ok and bool((np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-5 * np.abs(want).max()).all())
         got = self._op("broadcast-add", x).torch()[:96].cpu().numpy()
         ok = ok and bool(np.array_equal(got, xh + self.b.numpy()))
+        got = self._op("broadcast-rows", x).torch()
+        ok = ok and bool(self.torch.equal(got, self.b.torch()[None, :].expand(self.ROWS, self.COLS)))
         return ok
 
     def cpu(self, names):
@@ -636,6 +665,8 @@ class MetaOps:
                 ref.reduce(x, "add", (0,))
             elif nm == "broadcast-add":
                 ref.binary(x, np.ones(self.COLS, np.float32), "add")
+            elif nm == "broadcast-rows":
+                ref.broadcast(np.ones(self.COLS, np.float32), [rows, self.COLS])
             else:
                 continue
             done += self.work()[nm] * rows // self.ROWS

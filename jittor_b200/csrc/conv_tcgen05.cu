@@ -509,33 +509,38 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            const int kh = tap / A.KW, kw = tap - kh * A.KW;
-            const int dy = kh * A.dh - A.ph, dx = kw * A.dw - A.pw;
-            const int per_img = A.tiles_h * A.tiles_w;
-            int stage = 0; uint32_t phase = 0;
-            bool ok = true;
-            for (int kb = 0; kb < k_blocks; kb++) {
-                const int64_t q = p0 + kb;
-                const int n = (int)(q / per_img);
-                const int r = (int)(q - (int64_t)n * per_img);
-                const int oh0 = (r / A.tiles_w) * PATCH, ow0 = (r % A.tiles_w) * PATCH;
-                if (!(ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 21))) break;
-                unsigned char* sa = smem + stage * MAX_STAGE_BYTES;
-                mbar_expect_tx(full + stage, STAGE_BYTES);
-                // pixels past the edge of x (padding, ragged patches) and channels past C / Co are zero-filled by TMA
-#pragma unroll
-                for (int j = 0; j < BM / 64; j++)
-                    tma_load_4d(sa + j * CHUNK_BYTES, &map_x, full + stage, tm * BM + j * 64, ow0 * A.sw + dx, oh0 * A.sh + dy, n);
-#pragma unroll
-                for (int j = 0; j < BN_T / 64; j++)
-                    tma_load_4d(sa + (BM / 64 + j) * CHUNK_BYTES, &map_dy, full + stage, tn * BN_T + j * 64, ow0, oh0, n);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        // The whole warp walks the patches; lane 0 waits for the slot and announces the bytes, then lanes 0 .. 1 + BN_T/64 issue
+        // one box each (x chunks first, then dy chunks: chunk j of the stage belongs to lane j).
+        const int kh = tap / A.KW, kw = tap - kh * A.KW;
+        const int dy = kh * A.dh - A.ph, dx = kw * A.dw - A.pw;
+        const int per_img = A.tiles_h * A.tiles_w;
+        int n = (int)(p0 / per_img);
+        const int r0 = (int)(p0 - (int64_t)n * per_img);
+        int th = r0 / A.tiles_w, tw = r0 - th * A.tiles_w;
+        constexpr int NBOX = BM / 64 + BN_T / 64;
+        const bool is_x = lane < BM / 64;
+        const CUtensorMap* map = is_x ? &map_x : &map_dy;
+        const int c0 = is_x ? tm * BM + lane * 64 : tn * BN_T + (lane - BM / 64) * 64;
+        const int sw = is_x ? A.sw : 1, sh = is_x ? A.sh : 1, ox = is_x ? dx : 0, oy = is_x ? dy : 0;
+        int stage = 0; uint32_t phase = 0;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; kb++) {
+            if (lane == 0) {
+                ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 21);
+                if (ok) mbar_expect_tx(full + stage, STAGE_BYTES);
             }
-            if (!ok) {
-                for (int s = 0; s < STAGES; s++)
-                    for (uint32_t i = 0; i < 4096 && !mbar_try(full + s, 0) && !mbar_try(full + s, 1); i++) __nanosleep(64);
-            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            // pixels past the edge of x (padding, ragged patches) and channels past C / Co are zero-filled by TMA
+            if (lane < NBOX)
+                tma_load_4d(smem + stage * MAX_STAGE_BYTES + lane * CHUNK_BYTES, map, full + stage, c0,
+                            tw * PATCH * sw + ox, th * PATCH * sh + oy, n);
+            if (++tw == A.tiles_w) { tw = 0; if (++th == A.tiles_h) { th = 0; n++; } }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok && lane == 0) {
+            for (int s = 0; s < STAGES; s++)
+                for (uint32_t i = 0; i < 4096 && !mbar_try(full + s, 0) && !mbar_try(full + s, 1); i++) __nanosleep(64);
         }
     } else if (warp == 1) {
         if (lane == 0) {
