@@ -42,6 +42,22 @@ def _unbroadcast(g, shape):
     return g.reshape(list(shape))
 
 
+def _is_ones(v):
+    """v is the constant 1 stretched to its shape (the seed of a gradient pushed through sums and casts): an unrealised chain
+    of broadcast_to / float casts over fill(1)."""
+    for _ in range(8):
+        op = v._op
+        if v._data is not None or op is None:
+            return False
+        if op.kind == "fill":
+            return op.attrs["value"] == 1 and not isinstance(op.attrs["value"], bool)
+        if op.kind == "broadcast_to" or (op.kind == "unary" and op.attrs["op"] in ("float32", "bfloat16", "float16", "float64")):
+            v = op.inputs[0]
+            continue
+        return False
+    return False
+
+
 def _zeros_like(v):
     return V.full(list(v.shape), 0, v.dtype)
 
@@ -93,7 +109,13 @@ def _op_grad(out, dout, k):
         elif bop == "subtract":
             g = dout if k == 0 else -dout
         elif bop == "multiply":
-            g = (q if k == 0 else p) * dout
+            other = q if k == 0 else p
+            # 1 * y is y bit for bit: the gradient of (p * q).sum() is the other factor itself, not a pass over it
+            # (not when the factor is the reindex / broadcast operand of a convolution: its gradient graphs are recognised
+            # with the product in place)
+            same = (list(other.shape) == list(dout.shape) and str(other.dtype) == str(dout.dtype) and other.dtype.is_float()
+                    and (other._op is None or other._op.kind not in ("broadcast_to", "reindex")))
+            g = other if same and _is_ones(dout) else other * dout
         elif bop == "divide":
             g = dout / q if k == 0 else (-dout * p) / (q * q)
         elif bop in ("maximum", "minimum"):

@@ -271,6 +271,7 @@ def test_scalar_stretched_over_every_axis_is_a_broadcast_input():
     assert sorted(view for _, view in inputs) == [[1, 1, 1, 1], [8, 16, 12, 12]]
     src, ok, log = fusion.program_source(words, inputs, shape, k, shape, "bfloat16")
     assert ok, log
-    # as jt.grad builds it
-    g = jt.grad((x * dy).sum(), x)
+    # as jt.grad builds it: a scaled sum leaves broadcast(scale) * dy, one map kernel; a plain sum leaves dy itself
+    g = jt.grad((x * dy).sum() * 3.0, x)
     assert fusion.build_program(g) is not None
+    assert jt.grad((x * dy).sum(), x) is dy
