@@ -455,7 +455,7 @@ class C5ConvBN:
                    "images")
     kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)",
                  "conv-acdb": "conv_bf16_kernel (tcgen05)", "conv-wgrad": "wgrad_bf16_kernel (tcgen05)"}
-    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2, "conv-wgrad": 8}
+    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2, "conv-wgrad": 6}
     all_reduced = ("conv-bn-relu",)
     traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6, "conv-acdb": 776.5e6, "conv-wgrad": None}
 
