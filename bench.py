@@ -452,16 +452,17 @@ class C5ConvBN:
                    "convolution through the relay with acdb (NHWC) activations in and out, the layout ConvTuner derives for "
                    "tensor-core kernels, which needs no layout pass; fourth part: the weight gradient of the same layer as "
                    "jt.grad builds it (reduce.add over batch and pixels of reindex(x) * broadcast(dy)), each rank over its own "
-                   "images")
+                   "images; fifth part: the same weight gradient through the relay with acdb x and dy")
     kernel_of = {"conv": "conv_bf16_kernel (tcgen05)", "conv-bn-relu": "conv_bf16_kernel (tcgen05)",
-                 "conv-acdb": "conv_bf16_kernel (tcgen05)", "conv-wgrad": "wgrad_bf16_kernel (tcgen05)"}
-    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2, "conv-wgrad": 6}
+                 "conv-acdb": "conv_bf16_kernel (tcgen05)", "conv-wgrad": "wgrad_bf16_kernel (tcgen05)",
+                 "conv-wgrad-acdb": "wgrad_bf16_kernel (tcgen05)"}
+    launches = {"conv": 2, "conv-bn-relu": 3, "conv-acdb": 2, "conv-wgrad": 6, "conv-wgrad-acdb": 2}
     all_reduced = ("conv-bn-relu",)
-    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6, "conv-acdb": 776.5e6, "conv-wgrad": None}
+    traffic = {"conv": 776.5e6, "conv-bn-relu": 776.5e6, "conv-acdb": 776.5e6, "conv-wgrad": 826.0e6, "conv-wgrad-acdb": 826.0e6}
 
     def work(self):
         f = 2 * self.N * self.H * self.W * self.CO * self.C * 9
-        return {"conv": f, "conv-bn-relu": f, "conv-acdb": f, "conv-wgrad": f}
+        return {"conv": f, "conv-bn-relu": f, "conv-acdb": f, "conv-wgrad": f, "conv-wgrad-acdb": f}
 
     def setup(self, rank, world, jt, torch, multi):
         from jittor_b200 import nn
@@ -483,7 +484,10 @@ class C5ConvBN:
         self.hdy = (torch.randn(n, self.CO, self.H, self.W, generator=gd) * 0.1).bfloat16().pin_memory()
         self.dy = jt.array(self.hdy)
         self.hdw = torch.empty(self.CO, self.C, 3, 3, dtype=torch.bfloat16).pin_memory()
-        return ["conv", "conv-bn-relu", "conv-acdb", "conv-wgrad"]
+        self.hdyn = self.hdy.permute(0, 2, 3, 1).contiguous().pin_memory()        # the same gradient, NHWC
+        self.dyn = jt.array(self.hdyn)
+        self.relay_w = jt.get_op_info("cudnn_conv_backward_w").get_constructor()
+        return ["conv", "conv-bn-relu", "conv-acdb", "conv-wgrad", "conv-wgrad-acdb"]
 
     def per_rank_work(self, name):
         return self.work()[name] // self.world
@@ -493,6 +497,8 @@ class C5ConvBN:
             return self.relay(x, w, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb")
         if name == "conv-wgrad":
             return self.jt.grad((self.nn.conv2d(x, w, None, 1, 1, 1) * (self.dy if dy is None else dy)).sum(), w)
+        if name == "conv-wgrad-acdb":
+            return self.relay_w(x, self.dyn if dy is None else dy, 3, 3, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb")
         y = self.nn.conv2d(x, w, None, 1, 1, 1)
         if name == "conv":
             return y
@@ -500,20 +506,20 @@ class C5ConvBN:
             return self.nn.relu(self.bn(y))
 
     def run(self, name):
-        return self._op(name, self.xn if name == "conv-acdb" else self.x, self.w).sync()
+        return self._op(name, self.xn if name.endswith("-acdb") else self.x, self.w).sync()
 
     def run_e2e(self, name):
-        x = self.jt.array((self.hxn if name == "conv-acdb" else self.hx).cuda(non_blocking=True))
+        x = self.jt.array((self.hxn if name.endswith("-acdb") else self.hx).cuda(non_blocking=True))
         w = self.jt.array(self.hw.cuda(non_blocking=True))
-        if name == "conv-wgrad":
-            dy = self.jt.array(self.hdy.cuda(non_blocking=True))
+        if name.startswith("conv-wgrad"):
+            dy = self.jt.array((self.hdyn if name.endswith("-acdb") else self.hdy).cuda(non_blocking=True))
             self._op(name, x, w, dy).fetch_into(self.hdw, stream=self.d2h_stream)
             return
         out = self.out.view(self.hxn.shape[0], self.H, self.W, self.CO) if name == "conv-acdb" else self.out
         self._op(name, x, w).fetch_into(out, stream=self.d2h_stream)
 
     def e2e_bytes(self, names):
-        fwd = sum(1 for n in names if n != "conv-wgrad")
+        fwd = sum(1 for n in names if not n.startswith("conv-wgrad"))
         bwd = len(names) - fwd
         return (len(names) * (self.hx.numel() + self.hw.numel()) * 2 + bwd * self.hdy.numel() * 2,
                 fwd * self.out.numel() * 2 + bwd * self.hdw.numel() * 2)
@@ -545,6 +551,7 @@ class C5ConvBN:
         dw = self._op("conv-wgrad", self.x, self.w).torch().float()
         ref = torch.nn.grad.conv2d_weight(self.x.torch().float(), list(self.hw.shape), self.dy.torch().float(), stride=1, padding=1)
         ok = ok and bool(((dw - ref).abs() <= 2e-2 * ref.abs() + 2e-2 * ref.abs().max()).all())
+        ok = ok and bool(torch.equal(self._op("conv-wgrad-acdb", self.xn, self.w).torch().float(), dw))    # same sums, no copies
         return ok
 
     def cpu(self, names):
@@ -555,7 +562,7 @@ class C5ConvBN:
         w = (rng.normal(size=(self.CO, self.C, 3, 3)) * (2 / (9 * self.C)) ** 0.5).astype(np.float32)
         done, t0 = 0, time.perf_counter()
         for nm in names:
-            if nm == "conv-wgrad":
+            if nm.startswith("conv-wgrad"):
                 continue                                # the C port has no weight gradient: the forward parts are the sample
             y = co.conv2d(x, w, 1, 1, 1)
             if nm == "conv-bn-relu":

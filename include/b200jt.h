@@ -287,6 +287,19 @@ int b200jt_conv2d_backward_w_tc(const b200jt_tensor* x, const b200jt_tensor* dy,
                                 int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
                                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* The weight gradient with the relay's layout strings (CudnnConvBackwardWOp(..., string xformat, string wformat, string
+ * yformat), python/jittor/extern/cuda/cudnn/ops/cudnn_conv_backward_w_op.h:20; layouts as ConvTuner derives them,
+ * python/jittor/src/opt/tuner/conv_tuner.cc:292-341): xformat describes x and yformat dy, "abcd" (NCHW) or "acdb" (NHWC, read
+ * by the kernel as they are: no copy on that side); wformat describes dw, "oihw" or "ohwi". Layouts other than
+ * abcd / oihw / abcd exist on the tensor-core kernel only (status -5 where it does not apply). */
+size_t b200jt_conv2d_backward_w_formats_workspace(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                                  int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                                                  const char* xformat, const char* wformat, const char* yformat);
+int b200jt_conv2d_backward_w_formats(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                     int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                                     const char* xformat, const char* wformat, const char* yformat,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* Per-channel sum(x) and sum(x*x) of x[N,C,H,W] into stats[2*C] (float32): the two reduce.mean of
  * BatchNorm.execute, python/jittor/nn.py:674-675, in one pass, unnormalised so that ranks can be
  * summed by an all-reduce (python/jittor/nn.py:676-678). */

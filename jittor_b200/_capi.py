@@ -83,6 +83,9 @@ SIGNATURES = [
     ("b200jt_conv2d_backward_w", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _vp]),
     ("b200jt_conv2d_backward_w_workspace", _sz, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i]),
     ("b200jt_conv2d_backward_w_tc", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    ("b200jt_conv2d_backward_w_formats_workspace", _sz, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p]),
+    ("b200jt_conv2d_backward_w_formats", _i, [_TP, _TP, _TP, _i, _i, _i, _i, _i, _i, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p,
+                                              _vp, _sz, _vp]),
     ("b200jt_bn_stats", _i, [_TP, _FP, _vp]),
     ("b200jt_bn_apply", _i, [_TP, _FP, _d, _FP, _FP, _d, _i, _TP, _FP, _FP, _d, _vp]),
     ("b200jt_pool2d", _i, [_TP, _TP, _vp, ctypes.c_char_p, _i, _i, _i, _i, _i, _i, _i, _vp]),

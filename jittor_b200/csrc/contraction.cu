@@ -153,6 +153,37 @@ extern "C" int b200jt_conv2d_formats(const b200jt_tensor* x, const b200jt_tensor
     return 0;
 }
 
+extern "C" size_t b200jt_conv2d_backward_w_formats_workspace(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                                             int sh, int sw, int ph, int pw, int dh, int dw_,
+                                                             const char* xformat, const char* wformat, const char* yformat) {
+    b200jt_tensor xl, wl, yl; ConvLayout lay; ConvShape s;
+    if (conv_formats(x, dw, dy, xformat, wformat, yformat, &xl, &wl, &yl, &lay)) return 0;
+    if (conv_shape(&xl, &wl, &yl, sh, sw, ph, pw, dh, dw_, 1, &s)) return 0;
+    if (x->dtype == B200JT_BFLOAT16 && conv2d_wgrad_tc_supported(s, x->ptr, dy->ptr, dw->ptr)) return conv2d_wgrad_tc_workspace(s);
+    return 0;
+}
+
+extern "C" int b200jt_conv2d_backward_w_formats(const b200jt_tensor* x, const b200jt_tensor* dy, const b200jt_tensor* dw,
+                                                int sh, int sw, int ph, int pw, int dh, int dw_,
+                                                const char* xformat, const char* wformat, const char* yformat,
+                                                void* workspace, size_t workspace_bytes, void* stream) {
+    b200jt_tensor xl, wl, yl; ConvLayout lay; ConvShape s;
+    int rc = conv_formats(x, dw, dy, xformat, wformat, yformat, &xl, &wl, &yl, &lay);
+    if (rc) return rc;
+    if (!lay.x_nhwc && !lay.w_ohwi && !lay.y_nhwc)
+        return b200jt_conv2d_backward_w_tc(x, dy, dw, sh, sw, ph, pw, dh, dw_, workspace, workspace_bytes, stream);
+    rc = conv_shape(&xl, &wl, &yl, sh, sw, ph, pw, dh, dw_, 1, &s);
+    if (rc) return rc;
+    if (numel(dw) == 0) return 0;
+    if (!(x->dtype == B200JT_BFLOAT16 && conv2d_wgrad_tc_supported(s, x->ptr, dy->ptr, dw->ptr)))
+        return fail(-5, "b200jt_conv2d_backward_w_formats: acdb / ohwi layouts run on the tensor-core kernel only (bfloat16, in and "
+                        "out channels multiples of 8 and >= 64, outputs of at least 8 x 8 per image and 4096 pixels in all, "
+                        "16-byte aligned x and dy)");
+    const size_t need = conv2d_wgrad_tc_workspace(s);
+    B200JT_CHECK_ARG(workspace_bytes >= need && workspace, "workspace too small: need " + std::to_string(need) + " bytes");
+    return conv2d_wgrad_tc(x->ptr, dy->ptr, dw->ptr, s, workspace, (cudaStream_t)stream, lay);
+}
+
 extern "C" size_t b200jt_conv2d_workspace(const b200jt_tensor* x, const b200jt_tensor* w, const b200jt_tensor* y,
                                           int sh, int sw, int ph, int pw, int dh, int dw, int groups) {
     ConvShape s;

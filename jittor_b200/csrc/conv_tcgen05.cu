@@ -598,16 +598,16 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
 }
 
-// dw[o][c][tap] = sum over splits (ascending) of part[split][tap][c][o], rounded to bf16 once.
+// dw[o][c][tap] (or [o][tap][c] for the "ohwi" layout) = sum over splits (ascending) of part[split][tap][c][o], rounded to bf16 once.
 __global__ void __launch_bounds__(256)
-wgrad_fold_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dw, int splits, int taps, int C, int Co) {
+wgrad_fold_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dw, int splits, int taps, int C, int Co, int ohwi) {
     const int64_t n = (int64_t)taps * C * Co;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const int o = (int)(i % Co); const int64_t t = i / Co;
         const int c = (int)(t % C); const int tap = (int)(t / C);
         float acc = 0.f;
         for (int s = 0; s < splits; s++) acc += part[(int64_t)s * n + i];
-        dw[((int64_t)o * C + c) * taps + tap] = __float2bfloat16(acc);
+        dw[ohwi ? ((int64_t)o * taps + tap) * C + c : ((int64_t)o * C + c) * taps + tap] = __float2bfloat16(acc);
     }
 }
 
@@ -659,18 +659,22 @@ size_t conv2d_wgrad_tc_workspace(const ConvShape& s) {
     return p.xb + p.dyb + p.pb + 1024;
 }
 
-int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s, void* workspace, cudaStream_t st) {
+int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s, void* workspace, cudaStream_t st,
+                    const ConvLayout& lay) {
     using namespace tcwgrad;
     const Plan p = plan_for(s);
     unsigned char* ws = (unsigned char*)(((uintptr_t)workspace + 1023) & ~(uintptr_t)1023);
-    __nv_bfloat16* xt = (__nv_bfloat16*)ws;
-    __nv_bfloat16* dyt = (__nv_bfloat16*)(ws + p.xb);
+    // channels-last ("acdb") x / dy are what the kernel reads: no copy on that side (lay.y_nhwc describes dy)
+    __nv_bfloat16* xt = lay.x_nhwc ? (__nv_bfloat16*)const_cast<void*>(x) : (__nv_bfloat16*)ws;
+    __nv_bfloat16* dyt = lay.y_nhwc ? (__nv_bfloat16*)const_cast<void*>(dy) : (__nv_bfloat16*)(ws + p.xb);
     float* part = (float*)(ws + p.xb + p.dyb);
-    {   // x[N][C][HW] -> [N][HW][C] and dy[N][Co][OH*OW] -> [N][OH*OW][Co]
-        const int HW = s.H * s.W, OHW = s.OH * s.OW;
+    const int HW = s.H * s.W, OHW = s.OH * s.OW;
+    if (!lay.x_nhwc) {   // x[N][C][HW] -> [N][HW][C]
         dim3 gx((unsigned)((HW + 63) / 64), (unsigned)((s.C + 63) / 64), (unsigned)s.N);
         tcconv::transpose_bf16_batched_kernel<<<gx, 256, 0, st>>>((const __nv_bfloat16*)x, xt, s.C, HW, 0, nullptr, nullptr, 0, 0, 0, nullptr, 0, 0);
         B200JT_LAUNCH_CHECK();
+    }
+    if (!lay.y_nhwc) {   // dy[N][Co][OH*OW] -> [N][OH*OW][Co]
         dim3 gy((unsigned)((OHW + 63) / 64), (unsigned)((s.Co + 63) / 64), (unsigned)s.N);
         tcconv::transpose_bf16_batched_kernel<<<gy, 256, 0, st>>>((const __nv_bfloat16*)dy, dyt, s.Co, OHW, 0, nullptr, nullptr, 0, 0, 0, nullptr, 0, 0);
         B200JT_LAUNCH_CHECK();
@@ -697,7 +701,7 @@ int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s,
     else wgrad_bf16_kernel<128><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mdy, part, A);
     B200JT_LAUNCH_CHECK();
     const int64_t n = (int64_t)taps * s.C * s.Co;
-    wgrad_fold_kernel<<<grid_for(n, 256), 256, 0, st>>>(part, (__nv_bfloat16*)dw, p.splits, taps, s.C, s.Co);
+    wgrad_fold_kernel<<<grid_for(n, 256), 256, 0, st>>>(part, (__nv_bfloat16*)dw, p.splits, taps, s.C, s.Co, lay.w_ohwi ? 1 : 0);
     B200JT_LAUNCH_CHECK();
     return 0;
 }

@@ -34,7 +34,9 @@ int conv2d_tc(const void* x, const void* w, void* y, float* stats, const ConvSha
 // weight gradient on tcgen05 (bf16, groups == 1): K = N*OH*OW pixels, split over CTAs, fp32 partial sums folded in a fixed order
 bool conv2d_wgrad_tc_supported(const ConvShape& s, const void* x, const void* dy, const void* dw);
 size_t conv2d_wgrad_tc_workspace(const ConvShape& s);
-int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s, void* workspace, cudaStream_t st);
+// lay: x_nhwc / y_nhwc say that x / dy are channels-last already (no copy), w_ohwi that dw is written [Co][KH][KW][C]
+int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s, void* workspace, cudaStream_t st,
+                    const ConvLayout& lay = ConvLayout());
 int tcconv_status_fetch_and_clear();
 int peer_status_fetch_and_clear();          // peer_allreduce.cu
 

@@ -491,6 +491,22 @@ def run_conv2d_backward_w(x, dy, geo, w_shape, out_dtype):
     return _cast(out, out_dtype)
 
 
+def run_conv2d_backward_w_formats(x, dy, geo, kh, kw, xformat, wformat, yformat, out_dtype):
+    """Weight gradient with the relay's layout strings (cudnn_conv_backward_w_op.h): x "abcd" / "acdb", dy (yformat) likewise,
+    dw "oihw" / "ohwi". Layouts other than the defaults exist on the tensor-core kernel only."""
+    Ci = x.shape[1] if xformat == "abcd" else x.shape[3]
+    Co = dy.shape[1] if yformat == "abcd" else dy.shape[3]
+    xd = x._data.view(list(x.shape))
+    dyd = _cast(dy._data.view(list(dy.shape)), x.dtype)
+    out = _empty([Co, Ci, kh, kw] if wformat == "oihw" else [Co, kh, kw, Ci], x.dtype)
+    args = (C.desc(xd), C.desc(dyd), C.desc(out), *geo, xformat.encode(), wformat.encode(), yformat.encode())
+    nbytes = C.lib.b200jt_conv2d_backward_w_formats_workspace(*args)
+    ws, wsp = _workspace(nbytes)
+    C.check(C.lib.b200jt_conv2d_backward_w_formats(*args, wsp, nbytes, C.stream_ptr()),
+            f"conv2d_backward_w x{list(x.shape)} ({xformat}) dy{list(dy.shape)} ({yformat}) -> {wformat} geo{geo}")
+    return _cast(out, out_dtype)
+
+
 def run_conv2d_transpose(x, w, geo, groups, out_shape, out_dtype):
     sh, sw, ph, pw, dh, dw = geo
     xd = x._data

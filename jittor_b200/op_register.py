@@ -122,14 +122,23 @@ def _register_builtins():
 
     def cudnn_conv_backward_w(x, dy, kh, kw, strideh, stridew, paddingh, paddingw, dilationh=1, dilationw=1, groups=1,
                               xformat="abcd", wformat="oihw", yformat="abcd"):
-        """Relay signature of conv_tuner.cc:390-396: dw[Cout, Cin, kh, kw] from x and dy."""
-        if xformat != "abcd" or wformat != "oihw" or yformat != "abcd" or groups != 1:
-            raise NotImplementedError("only abcd / oihw layouts, groups == 1")
+        """Relay signature of conv_tuner.cc:390-396: dw[Cout, Cin, kh, kw] from x and dy. xformat / yformat "acdb": x / dy are
+        channels-last (read by the tensor-core kernel as they are); wformat "ohwi": dw comes out [Cout, kh, kw, Cin]."""
+        if xformat not in ("abcd", "acdb") or wformat not in ("oihw", "ohwi") or yformat not in ("abcd", "acdb"):
+            raise ValueError(f"unknown conv layouts x {xformat!r} w {wformat!r} y {yformat!r}")
+        if groups != 1:
+            raise NotImplementedError("weight gradient relay with groups > 1")
         from . import executor
         x, dy = V.to_var(x), V.to_var(dy)
-        shape = [dy.shape[1], x.shape[1], kh, kw]
         geo = (strideh, stridew, paddingh, paddingw, dilationh, dilationw)
-        return _relayed(x, dy, shape, lambda xd, dyd: executor.run_conv2d_backward_w(x, dy, geo, shape, x.dtype))
+        if xformat == "abcd" and wformat == "oihw" and yformat == "abcd":
+            shape = [dy.shape[1], x.shape[1], kh, kw]
+            return _relayed(x, dy, shape, lambda xd, dyd: executor.run_conv2d_backward_w(x, dy, geo, shape, x.dtype))
+        ci = x.shape[1] if xformat == "abcd" else x.shape[3]
+        co = dy.shape[1] if yformat == "abcd" else dy.shape[3]
+        shape = [co, ci, kh, kw] if wformat == "oihw" else [co, kh, kw, ci]
+        return _relayed(x, dy, shape, lambda xd, dyd: executor.run_conv2d_backward_w_formats(
+            x, dy, geo, kh, kw, xformat, wformat, yformat, x.dtype))
 
     register_op("cublas_matmul", cublas_matmul)
     register_op("cudnn_conv", cudnn_conv)

@@ -336,3 +336,50 @@ def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path)
             again = jt.grad(loss3, wv).torch().float().cpu().numpy()
         assert np.array_equal(got, again)
     assert C.lib.b200jt_device_status() == 0
+
+
+WGRAD_LAYOUTS = [
+    ((20, 192, 30, 34), (320, 192, 3, 3), 2, 1, "acdb", "oihw", "acdb"),
+    ((8, 256, 28, 28), (256, 256, 3, 3), 1, 1, "acdb", "ohwi", "acdb"),
+    ((64, 128, 12, 12), (64, 128, 3, 3), 1, 1, "abcd", "ohwi", "acdb"),
+    ((72, 256, 9, 11), (64, 256, 1, 1), 1, 0, "acdb", "oihw", "abcd"),
+]
+
+
+@pytest.mark.parametrize("xs,wshape,stride,pad,xf,wf,yf", WGRAD_LAYOUTS)
+def test_weight_gradient_layouts_of_the_relay(xs, wshape, stride, pad, xf, wf, yf):
+    """cudnn_conv_backward_w with the layout strings ConvTuner derives (python/jittor/src/opt/tuner/conv_tuner.cc:292-341,
+    390-396): channels-last x / dy are read as they are, dw comes out in the asked order -- same bits as the abcd / oihw call."""
+    import jittor_b200 as jt
+    from jittor_b200 import _capi as C
+    rng = np.random.default_rng(sum(xs) + sum(wshape) + stride)
+    x = bf16_round(rng.normal(size=xs))
+    oh = (xs[2] + 2 * pad - (wshape[2] - 1) - 1) // stride + 1
+    ow = (xs[3] + 2 * pad - (wshape[3] - 1) - 1) // stride + 1
+    dy = bf16_round(rng.normal(size=(xs[0], wshape[0], oh, ow)) * 0.1)
+    relay = jt.get_op_info("cudnn_conv_backward_w").get_constructor()
+    xv, dyv = jt.array(torch.from_numpy(x).bfloat16()), jt.array(torch.from_numpy(dy).bfloat16())
+    want = relay(xv, dyv, wshape[2], wshape[3], stride, stride, pad, pad, 1, 1, 1).torch()
+    xin = x if xf == "abcd" else np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+    dyin = dy if yf == "abcd" else np.ascontiguousarray(dy.transpose(0, 2, 3, 1))
+    got = relay(jt.array(torch.from_numpy(xin).bfloat16()), jt.array(torch.from_numpy(dyin).bfloat16()),
+                wshape[2], wshape[3], stride, stride, pad, pad, 1, 1, 1, xf, wf, yf).torch()
+    if wf == "ohwi":
+        assert list(got.shape) == [wshape[0], wshape[2], wshape[3], wshape[1]]
+        got = got.permute(0, 3, 1, 2)
+    assert torch.equal(got, want)
+    tw = torch.zeros(wshape, device="cuda").requires_grad_()
+    ty = torch.nn.functional.conv2d(torch.from_numpy(x).cuda(), tw, None, stride, pad, 1)
+    (ty * torch.from_numpy(dy).cuda()).sum().backward()
+    check(got.float().cpu().numpy(), bf16_round(tw.grad.cpu().numpy()), False, rtol=2e-2)
+    assert C.lib.b200jt_device_status() == 0
+
+
+def test_weight_gradient_layouts_are_refused_off_the_tensor_core_kernel():
+    import jittor_b200 as jt
+    from jittor_b200 import _capi as C
+    relay = jt.get_op_info("cudnn_conv_backward_w").get_constructor()
+    x = jt.array(torch.zeros(2, 8, 8, 16, device="cuda"))                 # float32, 16 channels: CUDA-core territory
+    dy = jt.array(torch.zeros(2, 8, 8, 16, device="cuda"))
+    with pytest.raises(C.B200Error):
+        relay(x, dy, 3, 3, 1, 1, 1, 1, 1, 1, 1, "acdb", "oihw", "acdb").sync()
