@@ -457,23 +457,30 @@ namespace tcwgrad {
 
 using namespace tc;
 
-constexpr int BM = 128, PIX = 64, PATCH = 8, STAGES = 4, THREADS = 192;
+constexpr int BM = 128, PIX = 64, PATCH = 8, THREADS = 192;
 constexpr int CHUNK_BYTES = PIX * 64 * 2;                    // one box: 64 pixels x 64 channels of bf16
-constexpr int MAX_STAGE_BYTES = (BM / 64 + 256 / 64) * CHUNK_BYTES;
-constexpr int SMEM_BYTES = STAGES * MAX_STAGE_BYTES + 1024 + 256;
+// TAPS filter taps per CTA share the dy tile of a stage (their x tiles differ by the tap's shift): with two taps a stage is
+// 2 * 16 KB of x + 32 KB of dy for twice the MMAs, i.e. two thirds of the operand bytes per FLOP -- the feed from L2 into
+// shared memory is what bounds the one-tap form. Two accumulators fill the 512 TMEM columns; three 64 KB stages.
+template <int TAPS> struct Ring {
+    static constexpr int STAGES = TAPS == 2 ? 3 : 4;
+    static constexpr int MAX_STAGE_BYTES = (TAPS * (BM / 64) + 256 / 64) * CHUNK_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * MAX_STAGE_BYTES + 1024 + 256;
+};
 
 struct WgradArgs {
     int N, C, H, W, Co, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
     int tiles_h, tiles_w;            // patches per image
     int64_t patches;                 // N * tiles_h * tiles_w: the K axis in units of 64 pixels
-    int tiles_m, tiles_n, splits;
+    int tiles_m, tiles_n, splits, groups;      // groups: ceil(taps / TAPS) tap groups
 };
 
-template <int BN_T>
+template <int BN_T, int TAPS>
 __global__ void __launch_bounds__(THREADS, 1)
 wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy,
                   float* __restrict__ part, const __grid_constant__ WgradArgs A) {
-    constexpr int STAGE_BYTES = (BM / 64 + BN_T / 64) * CHUNK_BYTES;
+    constexpr int STAGES = Ring<TAPS>::STAGES, MAX_STAGE_BYTES = Ring<TAPS>::MAX_STAGE_BYTES;
+    constexpr int XBOX = BM / 64, YBOX = BN_T / 64;           // boxes per tap of x, boxes of dy
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * MAX_STAGE_BYTES);
@@ -485,11 +492,13 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int taps = A.KH * A.KW;
-    const int base = taps * A.tiles_m * A.tiles_n;
+    const int base = A.groups * A.tiles_m * A.tiles_n;
     const int split = blockIdx.x / base;
     int tile = blockIdx.x - split * base;
-    const int tap = tile % taps; tile /= taps;
+    const int group = tile % A.groups; tile /= A.groups;
     const int tn = tile % A.tiles_n, tm = tile / A.tiles_n;
+    const int tap0 = group * TAPS;
+    const int ntap = min(TAPS, taps - tap0);                 // the last group of an odd tap count holds one tap
     const int64_t p0 = A.patches * split / A.splits, p1 = A.patches * (split + 1) / A.splits;
     const int k_blocks = (int)(p1 - p0);                     // >= 1: the host keeps splits <= patches
 
@@ -500,7 +509,7 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(BN_T) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "n"(TAPS * BN_T) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -509,30 +518,33 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // The whole warp walks the patches; lane 0 waits for the slot and announces the bytes, then lanes 0 .. 1 + BN_T/64 issue
-        // one box each (x chunks first, then dy chunks: chunk j of the stage belongs to lane j).
+        // The whole warp walks the patches; lane 0 waits for the slot and announces the bytes, then every lane that owns a box
+        // issues it: chunk j of a stage belongs to lane j -- x chunks of tap 0, x chunks of tap 1, then the dy chunks.
+        const bool is_x = lane < TAPS * XBOX;
+        const int t = is_x ? lane / XBOX : 0;                 // which of this CTA's taps the lane's x box serves
+        const int tap = min(tap0 + t, taps - 1);
         const int kh = tap / A.KW, kw = tap - kh * A.KW;
-        const int dy = kh * A.dh - A.ph, dx = kw * A.dw - A.pw;
         const int per_img = A.tiles_h * A.tiles_w;
         int n = (int)(p0 / per_img);
         const int r0 = (int)(p0 - (int64_t)n * per_img);
         int th = r0 / A.tiles_w, tw = r0 - th * A.tiles_w;
-        constexpr int NBOX = BM / 64 + BN_T / 64;
-        const bool is_x = lane < BM / 64;
+        const bool owns = is_x ? t < ntap : lane < TAPS * XBOX + YBOX;
         const CUtensorMap* map = is_x ? &map_x : &map_dy;
-        const int c0 = is_x ? tm * BM + lane * 64 : tn * BN_T + (lane - BM / 64) * 64;
-        const int sw = is_x ? A.sw : 1, sh = is_x ? A.sh : 1, ox = is_x ? dx : 0, oy = is_x ? dy : 0;
+        const int c0 = is_x ? tm * BM + (lane - t * XBOX) * 64 : tn * BN_T + (lane - TAPS * XBOX) * 64;
+        const int sw = is_x ? A.sw : 1, sh = is_x ? A.sh : 1;
+        const int ox = is_x ? kw * A.dw - A.pw : 0, oy = is_x ? kh * A.dh - A.ph : 0;
+        const uint32_t stage_bytes = (uint32_t)(ntap * XBOX + YBOX) * CHUNK_BYTES;
         int stage = 0; uint32_t phase = 0;
         bool ok = true;
         for (int kb = 0; kb < k_blocks; kb++) {
             if (lane == 0) {
                 ok = mbar_wait(empty + stage, phase ^ 1, abort_flag, 21);
-                if (ok) mbar_expect_tx(full + stage, STAGE_BYTES);
+                if (ok) mbar_expect_tx(full + stage, stage_bytes);
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             // pixels past the edge of x (padding, ragged patches) and channels past C / Co are zero-filled by TMA
-            if (lane < NBOX)
+            if (owns)
                 tma_load_4d(smem + stage * MAX_STAGE_BYTES + lane * CHUNK_BYTES, map, full + stage, c0,
                             tw * PATCH * sw + ox, th * PATCH * sh + oy, n);
             if (++tw == A.tiles_w) { tw = 0; if (++th == A.tiles_h) { th = 0; n++; } }
@@ -552,10 +564,16 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 if (!(ok = mbar_wait(full + stage, phase, abort_flag, 22))) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = smem_u32(smem + stage * MAX_STAGE_BYTES);
-                const uint64_t da = make_smem_desc_mn(sa, CHUNK_BYTES, 1024);
-                const uint64_t db = make_smem_desc_mn(sa + (BM / 64) * CHUNK_BYTES, CHUNK_BYTES, 1024);
+                const uint64_t db = make_smem_desc_mn(sa + TAPS * XBOX * CHUNK_BYTES, CHUNK_BYTES, 1024);
 #pragma unroll
-                for (int k = 0; k < PIX / UMMA_K; k++) umma_f16(tmem_base, da + KSTEP * k, db + KSTEP * k, idesc, (kb | k) != 0);
+                for (int t = 0; t < TAPS; t++) {
+                    if (t < ntap) {
+                        const uint64_t da = make_smem_desc_mn(sa + t * XBOX * CHUNK_BYTES, CHUNK_BYTES, 1024);
+#pragma unroll
+                        for (int k = 0; k < PIX / UMMA_K; k++)
+                            umma_f16(tmem_base + t * BN_T, da + KSTEP * k, db + KSTEP * k, idesc, (kb | k) != 0);
+                    }
+                }
                 umma_commit(empty + stage);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
@@ -568,23 +586,25 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int c = tm * BM + quad * 32 + lane;                        // TMEM lane = input channel
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-            float* prow = part + (((int64_t)split * taps + tap) * A.C + c) * A.Co;
             const bool vec = (A.Co & 3) == 0;
+            for (int t = 0; t < ntap; t++) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + t * BN_T;
+                float* prow = part + (((int64_t)split * taps + tap0 + t) * A.C + c) * A.Co;
 #pragma unroll 1
-            for (int ch = 0; ch < BN_T / 32; ch++) {
-                uint32_t v[32];
-                tmem_ld32(taddr + ch * 32, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int o0 = tn * BN_T + ch * 32;
-                if (c < A.C && o0 < A.Co) {
-                    if (vec && o0 + 32 <= A.Co) {
+                for (int ch = 0; ch < BN_T / 32; ch++) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int o0 = tn * BN_T + ch * 32;
+                    if (c < A.C && o0 < A.Co) {
+                        if (vec && o0 + 32 <= A.Co) {
 #pragma unroll
-                        for (int q = 0; q < 8; q++)
-                            *reinterpret_cast<uint4*>(prow + o0 + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                    } else {
+                            for (int q = 0; q < 8; q++)
+                                *reinterpret_cast<uint4*>(prow + o0 + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                        } else {
 #pragma unroll
-                        for (int e = 0; e < 32; e++) if (o0 + e < A.Co) prow[o0 + e] = __uint_as_float(v[e]);
+                            for (int e = 0; e < 32; e++) if (o0 + e < A.Co) prow[o0 + e] = __uint_as_float(v[e]);
+                        }
                     }
                 }
             }
@@ -594,7 +614,7 @@ wgrad_bf16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(BN_T) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(TAPS * BN_T) : "memory");
     }
 }
 
@@ -625,22 +645,29 @@ static bool make_map_nhwc(CUtensorMap* map, const void* base, int N, int H, int 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-struct Plan { int bn, tiles_m, tiles_n, splits; int64_t patches; size_t xb, dyb, pb; };
+struct Plan { int bn, taps_per_cta, groups, tiles_m, tiles_n, splits; int64_t patches; size_t xb, dyb, pb; };
 
 static Plan plan_for(const ConvShape& s) {
     Plan p;
+    const int taps = s.KH * s.KW;
+    const char* env = getenv("B200JT_WGRAD_TAPS");           // 1 forces one tap per CTA (tests run both forms)
     p.bn = s.Co <= 128 ? 128 : 256;
+    p.taps_per_cta = (taps >= 2 && !(env && atoi(env) == 1)) ? 2 : 1;
+    p.groups = (taps + p.taps_per_cta - 1) / p.taps_per_cta;
     p.tiles_m = (s.C + BM - 1) / BM;
     p.tiles_n = (s.Co + p.bn - 1) / p.bn;
     p.patches = (int64_t)s.N * ((s.OH + PATCH - 1) / PATCH) * ((s.OW + PATCH - 1) / PATCH);
-    const int64_t base = (int64_t)s.KH * s.KW * p.tiles_m * p.tiles_n;
     // fill the GPU once when the accumulators alone do not; every split keeps at least 16 patches (1024 pixels) of K
-    int64_t splits = base >= kNumSMs ? 1 : kNumSMs / base;
-    splits = std::max<int64_t>(1, std::min<int64_t>(splits, p.patches / 16));
-    p.splits = (int)splits;
+    auto splits_for = [&](int64_t groups) {
+        const int64_t base = groups * p.tiles_m * p.tiles_n;
+        return std::max<int64_t>(1, std::min<int64_t>(base >= kNumSMs ? 1 : kNumSMs / base, p.patches / 16));
+    };
+    p.splits = (int)splits_for(p.groups);
     p.xb = ((size_t)s.N * s.H * s.W * s.C * 2 + 1023) & ~(size_t)1023;
     p.dyb = ((size_t)s.N * s.OH * s.OW * s.Co * 2 + 1023) & ~(size_t)1023;
-    p.pb = ((size_t)p.splits * s.KH * s.KW * s.C * s.Co * 4 + 1023) & ~(size_t)1023;
+    // the partial sums are sized for whichever form splits K more finely, so the workspace query does not depend on the switch
+    const int64_t most = std::max(splits_for(taps), splits_for((taps + 1) / 2));
+    p.pb = ((size_t)most * taps * s.C * s.Co * 4 + 1023) & ~(size_t)1023;
     return p;
 }
 
@@ -683,22 +710,29 @@ int conv2d_wgrad_tc(const void* x, const void* dy, void* dw, const ConvShape& s,
     A.N = s.N; A.C = s.C; A.H = s.H; A.W = s.W; A.Co = s.Co; A.KH = s.KH; A.KW = s.KW; A.OH = s.OH; A.OW = s.OW;
     A.sh = s.sh; A.sw = s.sw; A.ph = s.ph; A.pw = s.pw; A.dh = s.dh; A.dw = s.dw;
     A.tiles_h = (s.OH + PATCH - 1) / PATCH; A.tiles_w = (s.OW + PATCH - 1) / PATCH;
-    A.patches = p.patches; A.tiles_m = p.tiles_m; A.tiles_n = p.tiles_n; A.splits = p.splits;
+    A.patches = p.patches; A.tiles_m = p.tiles_m; A.tiles_n = p.tiles_n; A.splits = p.splits; A.groups = p.groups;
     CUtensorMap mx, mdy;
     if (!make_map_nhwc(&mx, xt, s.N, s.H, s.W, s.C, s.sh, s.sw) || !make_map_nhwc(&mdy, dyt, s.N, s.OH, s.OW, s.Co, 1, 1))
         return fail(-4, "conv2d_backward_w: cuTensorMapEncodeTiled failed");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute((const void*)wgrad_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute((const void*)wgrad_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        const std::pair<const void*, int> kernels[] = {
+            {(const void*)wgrad_bf16_kernel<256, 1>, Ring<1>::SMEM_BYTES}, {(const void*)wgrad_bf16_kernel<128, 1>, Ring<1>::SMEM_BYTES},
+            {(const void*)wgrad_bf16_kernel<256, 2>, Ring<2>::SMEM_BYTES}, {(const void*)wgrad_bf16_kernel<128, 2>, Ring<2>::SMEM_BYTES}};
+        for (auto& k : kernels)
+            if (attr_err == cudaSuccess) attr_err = cudaFuncSetAttribute(k.first, cudaFuncAttributeMaxDynamicSharedMemorySize, k.second);
     });
     B200JT_CUDA(attr_err);
     const int taps = s.KH * s.KW;
-    const unsigned grid = (unsigned)((int64_t)taps * p.tiles_m * p.tiles_n * p.splits);
-    if (p.bn == 256) wgrad_bf16_kernel<256><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mdy, part, A);
-    else wgrad_bf16_kernel<128><<<grid, THREADS, SMEM_BYTES, st>>>(mx, mdy, part, A);
+    const unsigned grid = (unsigned)((int64_t)p.groups * p.tiles_m * p.tiles_n * p.splits);
+    if (p.taps_per_cta == 2) {
+        if (p.bn == 256) wgrad_bf16_kernel<256, 2><<<grid, THREADS, Ring<2>::SMEM_BYTES, st>>>(mx, mdy, part, A);
+        else wgrad_bf16_kernel<128, 2><<<grid, THREADS, Ring<2>::SMEM_BYTES, st>>>(mx, mdy, part, A);
+    } else {
+        if (p.bn == 256) wgrad_bf16_kernel<256, 1><<<grid, THREADS, Ring<1>::SMEM_BYTES, st>>>(mx, mdy, part, A);
+        else wgrad_bf16_kernel<128, 1><<<grid, THREADS, Ring<1>::SMEM_BYTES, st>>>(mx, mdy, part, A);
+    }
     B200JT_LAUNCH_CHECK();
     const int64_t n = (int64_t)taps * s.C * s.Co;
     wgrad_fold_kernel<<<grid_for(n, 256), 256, 0, st>>>(part, (__nv_bfloat16*)dw, p.splits, taps, s.C, s.Co, lay.w_ohwi ? 1 : 0);

@@ -303,7 +303,7 @@ WGRAD = [
 
 
 @pytest.mark.parametrize("xs,wshape,stride,pad,dil,path", WGRAD)
-def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path):
+def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path, monkeypatch):
     """Checked against the CUDA-core weight-gradient kernel (itself pinned to the reference's conv_wgrad fixtures through the
     oracle) and against a float32 torch convolution's gradient; the oracle's own 7-d formulation needs minutes at these sizes."""
     import jittor_b200 as jt
@@ -322,6 +322,12 @@ def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path)
     with jt.flag_scope(b200_wgrad_tc=1 if path == "tc" else 2):
         loss = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
         got = jt.grad(loss, wv).torch().float().cpu().numpy()
+        if path == "tc":                                       # one tap per CTA instead of two (K is then split differently: equal within rounding)
+            monkeypatch.setenv("B200JT_WGRAD_TAPS", "1")
+            loss1 = (nn.conv2d(xv, wv, None, stride, pad, dil) * dyv).sum()
+            one_tap = jt.grad(loss1, wv).torch().float().cpu().numpy()
+            monkeypatch.delenv("B200JT_WGRAD_TAPS")
+            check(got, one_tap, False, rtol=2e-2)
     tw = torch.from_numpy(w).cuda().requires_grad_()
     ty = torch.nn.functional.conv2d(torch.from_numpy(x).cuda(), tw, None, stride, pad, dil)
     (ty * torch.from_numpy(dy).cuda()).sum().backward()
