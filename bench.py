@@ -128,7 +128,22 @@ class C1ConvF32:
         return (self.hx.numel() + self.hw.numel()) * 4, self.out.numel() * 4
 
     def extra(self, part_ms):
-        return {"TFLOP/s": self.FLOP / part_ms["conv-f32"] / 1e9, "flop_per_step": self.FLOP}
+        return {"TFLOP/s": self.FLOP / part_ms["conv-f32"] / 1e9, "flop_per_step": self.FLOP, "launch_path": self.launch_path()}
+
+    def launch_path(self, calls=300):
+        """The public call WITHOUT a CUDA graph, back to back: wall-clock per call until the call returns (Python builds
+        the four-op graph, plans it and launches) and until the GPU has finished all of them."""
+        for _ in range(20):
+            self.run("conv-f32")
+        self.torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            self.run("conv-f32")
+        t1 = time.perf_counter()
+        self.torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        return {"calls": calls, "us_per_call_returned": (t1 - t0) / calls * 1e6, "us_per_call_finished": (t2 - t0) / calls * 1e6,
+                "what": "nn.conv2d(x, w).sync() launched directly, no CUDA graph, no L2 flush between calls"}
 
     def verify(self, env):
         from oracle import c_oracle as co
