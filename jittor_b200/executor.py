@@ -66,15 +66,15 @@ def realize(roots):
 
 
 def _make_plan(v):
-    if v._op is None:
-        raise C.B200Error("Var has neither data nor a producer")
     relay = getattr(v, "_relay", None)
-    if relay is not None:                       # grouped / transposed convolution built by nn with its relay record
+    if relay is not None:                       # a convolution built by nn with its relay record (its graph may not be written yet)
         kind, x, w, geo, groups = relay
         if x.dtype in ("float32", "bfloat16") and w.dtype in ("float32", "bfloat16"):
             if kind == "conv2d":
                 return Plan([x, w], lambda: run_conv2d(x, w, geo, v.dtype, groups=groups))
             return Plan([x, w], lambda: run_conv2d_transpose(x, w, geo, groups, list(v.shape), v.dtype))
+    if v._op is None:
+        raise C.B200Error("Var has neither data nor a producer")
     for matcher in _MATCHERS:
         p = matcher(v)
         if p is not None:
@@ -530,8 +530,9 @@ def run_conv2d(x, w, geo, out_dtype, stats=None, groups=1):
     nbytes = C.lib.b200jt_conv2d_workspace(*args)
     ws, wsp = _workspace(nbytes)
     sp = ctypes.c_void_p(stats.data_ptr()) if stats is not None else ctypes.c_void_p(0)
-    C.check(C.lib.b200jt_conv2d(*args, sp, wsp, nbytes, C.stream_ptr()),
-            f"conv2d x{list(x.shape)} w{list(w.shape)} geo{geo}")
+    rc = C.lib.b200jt_conv2d(*args, sp, wsp, nbytes, C.stream_ptr())
+    if rc:                                       # the message is only put together when there is one to show
+        C.check(rc, f"conv2d x{list(x.shape)} w{list(w.shape)} geo{geo}")
     return _cast(out, out_dtype)
 
 

@@ -4,6 +4,7 @@ softmax (:523-535), LayerNorm (:766-787), BatchNorm (:651-689), relu (:166-183),
 import numpy as np
 
 from . import var as V
+from . import dtypes
 from .flags import flags, flag_scope
 from .var import Var, to_var
 
@@ -220,17 +221,26 @@ def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
             y = y + to_var(bias).broadcast(y.shape, [0, 2, 3])
         return y
     assert C == Cw
-    with flag_scope(amp_reg=flags.amp_reg | 36):
-        xx = x.reindex([N, out_channels, C, oh, ow, Kh, Kw], [
-            "i0",
-            "i2",
-            f"i3*{stride[0]}-{padding[0]}+i5*{dilation[0]}",
-            f"i4*{stride[1]}-{padding[1]}+i6*{dilation[1]}",
-        ])
-        ww = weight.broadcast(xx.shape, [0, 3, 4])
-        yy = xx * ww
-        y = yy.sum([2, 5, 6])
-    # the executor would find the same operands and geometry in the index strings; the record spares it the search on every call
+    amp = flags.amp_reg | 36
+
+    def graph():
+        with flag_scope(amp_reg=amp):
+            xx = x.reindex([N, out_channels, C, oh, ow, Kh, Kw], [
+                "i0",
+                "i2",
+                f"i3*{stride[0]}-{padding[0]}+i5*{dilation[0]}",
+                f"i4*{stride[1]}-{padding[1]}+i6*{dilation[1]}",
+            ])
+            ww = weight.broadcast(xx.shape, [0, 3, 4])
+            yy = xx * ww
+            return yy.sum([2, 5, 6])
+
+    # The four-op graph is written down when something reads it (jt.grad, a consumer's pattern match, the fuser); a plain
+    # forward call runs from the relay record alone: the executor would only find the same operands and geometry in the
+    # index strings. Shape and dtype are what the graph's own inference gives.
+    with flag_scope(amp_reg=amp):
+        ydt = dtypes.reduce_dtype_infer("add", dtypes.binary_dtype_infer("multiply", x.dtype, weight.dtype, x.is_scalar, weight.is_scalar))
+    y = V.LazyVar([N, out_channels, oh, ow], ydt, lambda: graph()._op)
     y._relay = ("conv2d", x, weight, stride + padding + dilation, 1)
     if bias is not None:
         y = y + to_var(bias).broadcast(y.shape, [0, 2, 3])

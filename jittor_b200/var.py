@@ -561,6 +561,25 @@ def reduce(x, op, dims=(), keepdims=False):
     return Var(yshape, ydt, Op("reduce", [x], op=op, reduce_mask=mask, keepdims_mask=keep_mask))
 
 
+class LazyVar(Var):
+    """A Var whose producer graph is written down only when something reads `_op`. A caller that hands the executor a relay
+    record with the result (nn.conv2d) can be planned and run without the graph; jt.grad, the fuser and the pattern
+    matchers of consumers read `_op` and find the same meta-operator graph the eager construction would have made."""
+
+    def __init__(self, shape, dtype, builder):
+        Var.__init__(self, shape, dtype, None)
+        del self.__dict__["_op"]
+        self.__dict__["_op_builder"] = builder
+
+    def __getattr__(self, name):               # only reached for attributes the instance does not have
+        if name == "_op":
+            builder = self.__dict__.pop("_op_builder", None)
+            op = builder() if builder is not None else None
+            self.__dict__["_op"] = op
+            return op
+        raise AttributeError(name)
+
+
 # ------------------------------------------------------------------------------------ element-wise
 def _bshape(a, b):
     """Result shape of a binary op on shapes a, b: right-aligned, size-1 axes stretch
