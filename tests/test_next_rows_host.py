@@ -116,3 +116,28 @@ def test_pooling_lowering_is_recognised():
     y = pool.avg_pool2d(bf, 2)
     assert str(y.dtype) == "bfloat16" and y._op.kind == "unary"
     assert executor._match_pool(y._op.inputs[0]) is not None
+
+
+def test_conv2d_writes_its_graph_only_when_it_is_read():
+    """nn.conv2d returns a Var that can be planned from its relay record; the four-op meta-operator graph appears when
+    something reads the producer (jt.grad, a consumer's pattern match) and is the one the eager construction makes."""
+    x, w = jt.Var([4, 32, 32, 32], "float32"), jt.Var([64, 32, 3, 3], "float32")
+    y = nn.conv2d(x, w, None, 2, 1, 1)
+    assert "_op" not in y.__dict__ and list(y.shape) == [4, 64, 16, 16] and y.dtype == "float32"
+    p = executor._make_plan(y)
+    assert p.leaves[0] is x and p.leaves[1] is w and "_op" not in y.__dict__          # planned without the graph
+    op = y._op                                                                        # now it is written
+    assert op.kind == "reduce" and op.attrs["reduce_mask"] == 0b1100100
+    mul = op.inputs[0]
+    assert mul._op.kind == "binary" and {i._op.kind for i in mul._op.inputs} == {"reindex", "broadcast_to"}
+    assert y._op is op                                                                # once
+    assert executor._match_conv(y) is not None                                        # the search finds the same operands
+    for dtype in ("bfloat16", "float16"):
+        for amp in (0, 2, 4, 16):
+            with jt.flag_scope(amp_reg=amp):
+                xb, wb = jt.Var([4, 64, 16, 16], dtype), jt.Var([64, 64, 3, 3], dtype)
+                yb = nn.conv2d(xb, wb, None, 1, 1, 1)
+                with jt.flag_scope(amp_reg=amp | 36):
+                    eager = (xb.reindex([4, 64, 64, 16, 16, 3, 3], ["i0", "i2", "i3*1-1+i5*1", "i4*1-1+i6*1"])
+                             * wb.broadcast([4, 64, 64, 16, 16, 3, 3], [0, 3, 4])).sum([2, 5, 6])
+                assert str(yb.dtype) == str(eager.dtype) and yb._op.kind == eager._op.kind
