@@ -576,14 +576,19 @@ class C5ConvBN:
         x = rng.normal(size=(imgs, self.C, self.H, self.W)).astype(np.float32)
         w = (rng.normal(size=(self.CO, self.C, 3, 3)) * (2 / (9 * self.C)) ** 0.5).astype(np.float32)
         done, t0 = 0, time.perf_counter()
+        dy = None
         for nm in names:
             if nm.startswith("conv-wgrad"):
-                continue                                # the C port has no weight gradient: the forward parts are the sample
+                if dy is None:
+                    dy = (rng.normal(size=(imgs, self.CO, self.H, self.W)) * 0.1).astype(np.float32)
+                co.conv2d_backward_w(x, dy, 3, 3, 1, 1, 1)
+                done += self.work()[nm] * imgs // self.N
+                continue
             y = co.conv2d(x, w, 1, 1, 1)
             if nm == "conv-bn-relu":
                 co.bn_relu(y, np.ones(self.CO, np.float32), np.zeros(self.CO, np.float32))
             done += self.work()[nm] * imgs // self.N
-        return max(done, 1), time.perf_counter() - t0, f"{imgs} of {self.N} images per forward part, fp32 (OpenMP over image x channel)"
+        return max(done, 1), time.perf_counter() - t0, f"{imgs} of {self.N} images per part, fp32 (OpenMP over image x channel; weight gradients over out x in channel)"
 
 
 class MetaOps:

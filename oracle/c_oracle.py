@@ -14,7 +14,8 @@ def build():
 
 
 def load():
-    if not os.path.exists(_LIB):
+    src = os.path.join(_HERE, "meta_ops.c")
+    if not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
         build()
     return ctypes.CDLL(_LIB)
 
@@ -85,6 +86,16 @@ def conv2d(x, w, stride=1, padding=1, dilation=1):
     lib().oracle_conv2d_f32(_p(x), _p(w), _p(y), _i64(N), _i64(C), _i64(H), _i64(W), _i64(Co), _i64(KH), _i64(KW),
                             _i64(stride), _i64(padding), _i64(dilation))
     return y
+
+
+def conv2d_backward_w(x, dy, kh, kw, stride=1, padding=1, dilation=1):
+    x, dy = np.ascontiguousarray(x, dtype=np.float32), np.ascontiguousarray(dy, dtype=np.float32)
+    N, C, H, W = x.shape
+    Co = dy.shape[1]
+    dw = np.empty((Co, C, kh, kw), np.float32)
+    lib().oracle_conv2d_backward_w_f32(_p(x), _p(dy), _p(dw), _i64(N), _i64(C), _i64(H), _i64(W), _i64(Co), _i64(kh), _i64(kw),
+                                       _i64(stride), _i64(padding), _i64(dilation))
+    return dw
 
 
 def bn_relu(x, gamma, beta, eps=1e-5, relu=True):

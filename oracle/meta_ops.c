@@ -137,6 +137,33 @@ void oracle_conv2d_f32(const float* x, const float* w, float* y, int64_t N, int6
         }
 }
 
+/* Weight gradient of the reindex-lowered conv2d as the gradient rules build it: the multiply's rule gives
+ * reindex(x) * broadcast(dy) (binary_op.cc:491-550), the broadcast's rule sums it over the axes the weight was stretched
+ * along, [N, OH, OW] of the 7-deep space (broadcast_to_op.cc:112-117, reduce_op.cc:386-394):
+ * dw[co,c,kh,kw] = sum_{n,oh,ow} x[n,c,oh*s-p+kh*d,ow*s-p+kw*d] * dy[n,co,oh,ow], out-of-range taps contribute 0
+ * (reindex_op.cc:131-138). ConvTuner relays this graph to the cuDNN filter gradient (conv_tuner.cc:375-397). */
+void oracle_conv2d_backward_w_f32(const float* x, const float* dy, float* dw, int64_t N, int64_t C, int64_t H, int64_t W,
+                                  int64_t Co, int64_t KH, int64_t KW, int64_t s, int64_t p, int64_t d) {
+    const int64_t OH = (H + p * 2 - KH * d + d - 1) / s + 1, OW = (W + p * 2 - KW * d + d - 1) / s + 1;
+#pragma omp parallel for collapse(2)
+    for (int64_t co = 0; co < Co; co++)
+        for (int64_t c = 0; c < C; c++) {
+            float* wp = dw + (co * C + c) * KH * KW;
+            for (int64_t i = 0; i < KH * KW; i++) wp[i] = 0.f;
+            for (int64_t n = 0; n < N; n++)
+                for (int64_t oh = 0; oh < OH; oh++)
+                    for (int64_t ow = 0; ow < OW; ow++) {
+                        const float g = dy[((n * Co + co) * OH + oh) * OW + ow];
+                        for (int64_t kh = 0; kh < KH; kh++)
+                            for (int64_t kw = 0; kw < KW; kw++) {
+                                int64_t ih = oh * s - p + kh * d, iw = ow * s - p + kw * d;
+                                if (ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+                                wp[kh * KW + kw] += x[((n * C + c) * H + ih) * W + iw] * g;
+                            }
+                    }
+        }
+}
+
 /* Per-channel mean / mean of squares over [0,2,3] then normalise (+ReLU), python/jittor/nn.py:674-683. */
 void oracle_bn_relu_f32(const float* x, const float* gamma, const float* beta, float* y,
                         int64_t N, int64_t C, int64_t HW, float eps, int relu) {

@@ -304,8 +304,8 @@ WGRAD = [
 
 @pytest.mark.parametrize("xs,wshape,stride,pad,dil,path", WGRAD)
 def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path, monkeypatch):
-    """Checked against the CUDA-core weight-gradient kernel (itself pinned to the reference's conv_wgrad fixtures through the
-    oracle) and against a float32 torch convolution's gradient; the oracle's own 7-d formulation needs minutes at these sizes."""
+    """Checked against the C restatement of the weight-gradient graph (oracle_conv2d_backward_w_f32, pinned to the reference's
+    conv_wgrad fixtures), a float32 torch convolution's gradient and the CUDA-core weight-gradient kernel."""
     import jittor_b200 as jt
     from jittor_b200 import _capi as C, nn
     rng = np.random.default_rng(sum(xs) + sum(wshape) + stride + dil)
@@ -328,6 +328,7 @@ def test_weight_gradient_on_the_tensor_cores(xs, wshape, stride, pad, dil, path,
             one_tap = jt.grad(loss1, wv).torch().float().cpu().numpy()
             monkeypatch.delenv("B200JT_WGRAD_TAPS")
             check(got, one_tap, False, rtol=2e-2)
+    check(got, bf16_round(co.conv2d_backward_w(x, dy, wshape[2], wshape[3], stride, pad, dil)), False, rtol=2e-2)
     tw = torch.from_numpy(w).cuda().requires_grad_()
     ty = torch.nn.functional.conv2d(torch.from_numpy(x).cuda(), tw, None, stride, pad, dil)
     (ty * torch.from_numpy(dy).cuda()).sum().backward()

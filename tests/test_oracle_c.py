@@ -40,3 +40,24 @@ def test_contractions():
         check(co.conv2d(x, w, s, p, d), ref.conv2d(x, w, s, p, d), False)
     g, bb = rng.uniform(0.5, 1.5, 5).astype(np.float32), rng.normal(size=5).astype(np.float32)
     check(co.bn_relu(x, g, bb), ref.batch_norm_train(x, g, bb, relu=True), False)
+
+
+def test_conv_weight_gradient_against_the_reference_fixtures():
+    """oracle_conv2d_backward_w_f32 against the weight gradients the reference's own jt.grad produced on its CPU executor
+    (tests/golden/make_golden_next.py:do_conv_grad)."""
+    from tests.golden_cases import CASES, arrays
+    seen = 0
+    for c in CASES:
+        if c["op"] != "conv_wgrad":
+            continue
+        A = arrays(c["file"])
+        x, w, dy = (A[k] for k in c["inputs"])
+        a = c["args"]
+        st, pd, dl = a["stride"], a["padding"], a["dilation"]
+        if any(isinstance(v, (list, tuple)) and len(set(v)) > 1 for v in (st, pd, dl)):
+            continue                                        # the C restatement takes one stride / padding / dilation for both axes
+        one = lambda v: int(v[0]) if isinstance(v, (list, tuple)) else int(v)
+        got = co.conv2d_backward_w(x, dy, w.shape[2], w.shape[3], one(st), one(pd), one(dl))
+        check(got, A[c["out"]], False)
+        seen += 1
+    assert seen >= 4
